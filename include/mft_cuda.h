@@ -1,0 +1,307 @@
+/*
+ * mft_cuda.h - C ABI of libmft_cuda.so, the sm_100a kernel library behind the
+ * LoRA fine-tuning step (forward + backward + Adam) of MobileFineTuner's
+ * operator API.
+ *
+ * The reference has no FFI for this path: its boundary is the C++ source API of
+ * the `operators` target (operator/finetune_ops/core/ops.h, lm_loss.h,
+ * nn/lora_linear.h, optim/adam.h).  Each entry point below names the reference
+ * function whose arithmetic it replaces; a C++ host layer (or any FFI: ctypes,
+ * cgo, JNI) binds these symbols.
+ *
+ * Conventions
+ *  - every function returns an int32 status: 0 = ok, negative = MFT_ERR_*;
+ *    mft_last_error() gives the message of the calling thread's last failure;
+ *  - all tensor pointers are DEVICE pointers unless the name ends in `_host`;
+ *  - tensors are contiguous row-major; `bf16` buffers hold raw IEEE bfloat16;
+ *  - every launch is asynchronous on the given stream (a cudaStream_t passed as
+ *    void*; NULL = the default stream); nothing synchronises except
+ *    mft_stream_sync and the *_host copies;
+ *  - there is no CPU fallback: without a CUDA device every call fails.
+ */
+#ifndef MFT_CUDA_H
+#define MFT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MFT_OK 0
+#define MFT_ERR_INVALID_ARG (-1)
+#define MFT_ERR_OOM (-2)
+#define MFT_ERR_CUDA (-3)
+#define MFT_ERR_TIMEOUT (-5)
+#define MFT_ERR_BOUNDS (-6)
+#define MFT_ERR_UNSUPPORTED (-7)
+
+typedef void* mft_stream_t;
+
+/* ---- runtime ------------------------------------------------------------ */
+/* Selects the device for the calling thread, creates library state (the
+ * TMA-descriptor encoder, the device status word).  Idempotent. */
+int32_t mft_init(int32_t device);
+int32_t mft_shutdown(void);
+const char* mft_last_error(void);
+int32_t mft_version(void);
+/* Number of kernels this library has launched since the last reset. */
+int64_t mft_launch_count(void);
+void mft_launch_count_reset(void);
+int32_t mft_stream_sync(mft_stream_t stream);
+/* Reads and clears the device status word that kernels with bounded waits set
+ * when a wait ran out (0 = no error).  Synchronises the stream. */
+int32_t mft_device_status(mft_stream_t stream, int32_t* status_host);
+
+/* ---- memory: the device analogue of MemoryManager / MemoryPool
+ *      (operator/finetune_ops/core/memory_manager.h:103-153) ----------------
+ * Size-bucketed caching allocator: freed blocks are kept for reuse and only
+ * returned to the driver by mft_empty_cache (what force_cleanup maps to). */
+int32_t mft_malloc(size_t bytes, void** ptr);
+int32_t mft_free(void* ptr);
+int32_t mft_empty_cache(void);
+/* stats_host[0..3] = bytes in use, bytes cached, peak bytes in use, #cudaMalloc calls */
+int32_t mft_mem_stats(int64_t* stats_host);
+int32_t mft_memcpy_h2d(void* dst, const void* src_host, size_t bytes, mft_stream_t stream);
+int32_t mft_memcpy_d2h(void* dst_host, const void* src, size_t bytes, mft_stream_t stream);
+int32_t mft_memcpy_d2d(void* dst, const void* src, size_t bytes, mft_stream_t stream);
+int32_t mft_memset(void* dst, int32_t byte_value, size_t bytes, mft_stream_t stream);
+
+/* ---- casts (ops::cast, operator/finetune_ops/core/ops.cpp:2894-2952;
+ *      bf16 conversion is round-to-nearest-even as core/dtype.h:114-121) ---- */
+int32_t mft_cast_f32_to_bf16(const float* src, void* dst_bf16, int64_t n, mft_stream_t stream);
+int32_t mft_cast_bf16_to_f32(const void* src_bf16, float* dst, int64_t n, mft_stream_t stream);
+/* dst[c, r] = src[r, c] with conversion f32 -> bf16 (weight packing: the
+ * reference stores linears as [in, out]; the GEMMs here want K-major [out, in]). */
+int32_t mft_transpose_f32_to_bf16(const float* src, void* dst_bf16, int64_t rows, int64_t cols,
+                                  mft_stream_t stream);
+int32_t mft_transpose_bf16(const void* src_bf16, void* dst_bf16, int64_t rows, int64_t cols,
+                           mft_stream_t stream);
+
+/* ---- embedding gather
+ *      (GPT2Model::embedding_lookup gpt2_model.cpp:464-492 + positions :349-369,
+ *       QwenModel::embedding_lookup qwen_model.cpp:249-272,
+ *       GemmaModel::embedding_lookup gemma_model.cpp:222-259) ---------------
+ * out[t, :] = table[ids[t], :] * scale (+ pos_table[t % seq_len, :]).
+ * table is bf16 [vocab, hidden]; pos_table (may be NULL) bf16 [n_pos, hidden];
+ * out is f32 [n_tokens, hidden].  An id outside [0, vocab) sets status
+ * MFT_ERR_BOUNDS in *status_dev (device int32, may be NULL) and writes zeros. */
+int32_t mft_embedding_gather(const int32_t* ids, const void* table_bf16, const void* pos_table_bf16,
+                             float* out, int64_t n_tokens, int64_t seq_len, int64_t hidden,
+                             int64_t vocab, float scale, int32_t* status_dev, mft_stream_t stream);
+
+/* ---- normalisation
+ *      rms_norm (1+w)   ops.cpp:1677-1725, RMSNormBackward backward_functions.cpp:492-532
+ *      rms_norm_affine  ops.cpp:1728-1762, RMSNormAffineBackward        :534-570
+ *      layer_norm       ops.cpp:1592-1646, LayerNormBackward            :434-490 --------
+ * x is [rows, dim] in x_dtype (MFT_F32 or MFT_BF16); y in y_dtype; weights f32.
+ * rstd (f32 [rows], may be NULL) receives 1/sqrt(mean(x^2)+eps) for the backward.
+ * unit_offset = 1 multiplies by (1 + w) (Gemma), 0 by w (Qwen).
+ * If residual != NULL (f32 [rows, dim]) the forward also writes
+ * sum_out = residual + y (f32), the fused "norm then residual add". */
+#define MFT_F32 0
+#define MFT_BF16 1
+#define MFT_I32 2
+int32_t mft_rmsnorm_fwd(const void* x, int32_t x_dtype, const float* weight, float eps,
+                        int32_t unit_offset, void* y, int32_t y_dtype, float* rstd,
+                        const float* residual, float* sum_out,
+                        int64_t rows, int64_t dim, mft_stream_t stream);
+/* dx = rms-norm backward of dy; dx_dtype f32 or bf16.  If accumulate != 0
+ * (f32 dx only) the result is added to dx.  dweight (f32 [dim], may be NULL)
+ * is accumulated with atomics (only needed for trainable norms). */
+int32_t mft_rmsnorm_bwd(const void* dy, int32_t dy_dtype, const void* x, int32_t x_dtype,
+                        const float* weight, const float* rstd, float eps, int32_t unit_offset,
+                        void* dx, int32_t dx_dtype, int32_t accumulate, float* dweight,
+                        int64_t rows, int64_t dim, mft_stream_t stream);
+int32_t mft_layernorm_fwd(const void* x, int32_t x_dtype, const float* weight, const float* bias,
+                          float eps, void* y, int32_t y_dtype, float* mean, float* rstd,
+                          int64_t rows, int64_t dim, mft_stream_t stream);
+int32_t mft_layernorm_bwd(const void* dy, int32_t dy_dtype, const void* x, int32_t x_dtype,
+                          const float* weight, const float* mean, const float* rstd,
+                          void* dx, int32_t dx_dtype, int32_t accumulate,
+                          float* dweight, float* dbias,
+                          int64_t rows, int64_t dim, mft_stream_t stream);
+
+/* ---- activations and residuals
+ *      gelu ops.cpp:1243-1267 / GeluBackward backward_functions.cpp:164-186
+ *      swiglu ops.cpp:2416-2452 / SwiGLUBackward :277-295
+ *      Gemma GeGLU = mul(gelu(gate), up), gemma_model.cpp:538-546
+ *      add ops.cpp:415-442 ------------------------------------------------ */
+#define MFT_ACT_GELU 0    /* y = gelu_tanh(x)               (x = gate, up unused)   */
+#define MFT_ACT_SWIGLU 1  /* y = silu(gate) * up                                      */
+#define MFT_ACT_GEGLU 2   /* y = gelu_tanh(gate) * up                                 */
+/* gate/up are bf16 [rows, ld] slices: element (r, c) at base[r*ld + c], c < cols.
+ * y is bf16 [rows, cols] contiguous. */
+int32_t mft_act_fwd(int32_t kind, const void* gate_bf16, const void* up_bf16, int64_t ld,
+                    void* y_bf16, int64_t rows, int64_t cols, mft_stream_t stream);
+int32_t mft_act_bwd(int32_t kind, const void* dy_bf16, const void* gate_bf16, const void* up_bf16,
+                    int64_t ld, void* dgate_bf16, void* dup_bf16, int64_t rows, int64_t cols,
+                    mft_stream_t stream);
+/* out = a + b (f32, n elements); a may alias out. */
+int32_t mft_add_f32(const float* a, const float* b, float* out, int64_t n, mft_stream_t stream);
+/* out(f32) = a(f32) + b(bf16) */
+int32_t mft_add_f32_bf16(const float* a, const void* b_bf16, float* out, int64_t n, mft_stream_t stream);
+int32_t mft_scale_f32(float* x, float alpha, int64_t n, mft_stream_t stream);
+
+/* ---- RoPE (apply_rope ops.cpp:2337-2414, ApplyRoPEBackward
+ *      backward_functions.cpp:728-774) and Gemma's per-head QK RMSNorm ------
+ * mft_rope_table fills cos/sin f32 [seq_len, head_dim/2] on the HOST with the
+ * reference's own expression (freq = 1/powf(theta, 2d/hd); angle = pos*freq in
+ * fp32; std::cos/std::sin of float), so device angles are bit-identical. */
+int32_t mft_rope_table_host(float* cos_host, float* sin_host, int64_t seq_len, int64_t head_dim, float theta);
+/* x: bf16 rows of `n_heads` heads of `head_dim`, token-major: element
+ * (token, head, d) at x[token*ld + head*head_dim + d]; token position =
+ * token % seq_len.  norm_weight (f32 [head_dim], may be NULL) applies
+ * rms_norm(1+w) per head BEFORE the rotation (Gemma, gemma_model.cpp:459-482);
+ * rstd (f32 [n_tokens*n_heads]) is then written for the backward.
+ * cos/sin may be NULL to skip the rotation. */
+int32_t mft_headnorm_rope_fwd(const void* x_bf16, int64_t ld, const float* norm_weight, float eps,
+                              const float* cos_tab, const float* sin_tab,
+                              void* y_bf16, int64_t ld_y, float* rstd,
+                              int64_t n_tokens, int64_t seq_len, int64_t n_heads, int64_t head_dim,
+                              mft_stream_t stream);
+int32_t mft_headnorm_rope_bwd(const void* dy_bf16, int64_t ld_dy, const void* x_bf16, int64_t ld,
+                              const float* norm_weight, const float* rstd,
+                              const float* cos_tab, const float* sin_tab,
+                              void* dx_bf16, int64_t ld_dx,
+                              int64_t n_tokens, int64_t seq_len, int64_t n_heads, int64_t head_dim,
+                              mft_stream_t stream);
+
+/* ---- repeat_kv_heads (ops.cpp:2260-2335, RepeatKVHeadsBackward
+ *      backward_functions.cpp:693-726): standalone gather, [B,nkv,S,hd] ->
+ *      [B,nkv*rep,S,hd]; the attention kernels never call it (h -> h/rep). -- */
+int32_t mft_repeat_kv(const void* kv, int32_t dtype, void* out, int64_t batch, int64_t n_kv,
+                      int64_t seq, int64_t head_dim, int64_t repeat, mft_stream_t stream);
+int32_t mft_repeat_kv_bwd(const float* dout, float* dkv, int64_t batch, int64_t n_kv,
+                          int64_t seq, int64_t head_dim, int64_t repeat, mft_stream_t stream);
+
+/* ---- GEMM (ops::matmul ops.cpp:619-822, ops::matmul_rhs_T :824-988,
+ *      MatmulBackward backward_functions.cpp:94-147, and the LoRA branch of
+ *      LoRALinear::forward nn/lora_linear.cpp:336-468) ----------------------
+ * "NT" product on the tcgen05 tensor cores, bf16 operands, fp32 accumulation
+ * in tensor memory:
+ *     D[m,n] = alpha * ( sum_k A[m,k]*B[n,k] + sum_j A2[m,j]*B2[n,j] ) + bias[n] (+ D[m,n])
+ * A [M,K] and B [N,K] are bf16 with the contraction index contiguous (row
+ * strides lda/ldb in elements, multiples of 8; base pointers 16-byte aligned).
+ * The optional second segment (A2 [M,K2], B2 [N,K2], K2 <= 64) is how the
+ * rank-r LoRA update rides in the same accumulator: A2 = scale*(X*A),
+ * B2 = B^T, so Y = X*W + scale*(X*A)*B costs one extra 64-wide k-block.
+ * bias is f32 [N] or NULL.  D is bf16 or f32 (d_dtype), row stride ldd.
+ * accumulate != 0 adds the previous contents of D (f32 D only). */
+int32_t mft_gemm_nt(const void* a_bf16, int64_t lda, const void* b_bf16, int64_t ldb,
+                    int64_t m, int64_t n, int64_t k,
+                    const void* a2_bf16, int64_t lda2, const void* b2_bf16, int64_t ldb2, int64_t k2,
+                    const float* bias, float alpha,
+                    void* d, int64_t ldd, int32_t d_dtype, int32_t accumulate,
+                    mft_stream_t stream);
+/* "TN" product with the long dimension contracted (the LoRA weight gradients
+ * dA = s*X^T*(dY*B^T), dB = s*(X*A)^T*dY of the generic MatmulBackward):
+ *     out[p,q] (+)= alpha * sum_t U[t,p]*V[t,q]
+ * U [T,P], V [T,Q] bf16 row-major (ldu, ldv); out f32 [P,Q] with row stride
+ * ldo.  Split over T across CTAs with fp32 atomics, so `out` must hold the
+ * value to accumulate onto (zero for a fresh result). */
+int32_t mft_gemm_tn_acc(const void* u_bf16, int64_t ldu, const void* v_bf16, int64_t ldv,
+                        int64_t t, int64_t p, int64_t q, float alpha,
+                        float* out, int64_t ldo, mft_stream_t stream);
+
+/* Table-driven block copies between the fp32 LoRA tensors (reference layouts:
+ * GPT-2/Qwen A[in,r], B[r,out]; Gemma A[r,in], B[out,r]) and the bf16 / f32
+ * operand panels the GEMMs use.  One launch handles every entry. */
+typedef struct {
+    const void* src;   /* f32 (pack) */
+    void* dst;         /* bf16 (pack) or f32 (unpack-accumulate) */
+    int32_t rows;      /* rows of the source block */
+    int32_t cols;      /* cols of the source block */
+    int32_t src_ld;
+    int32_t dst_ld;
+    int32_t transpose; /* 1: dst[c, r] = src[r, c] */
+    int32_t pad;
+} mft_block_copy_t;
+/* dst(bf16) = src(f32) for every table entry (table lives in device memory). */
+int32_t mft_pack_blocks_bf16(const mft_block_copy_t* table_dev, int32_t n_entries, mft_stream_t stream);
+/* dst(f32) += src(f32) for every table entry. */
+int32_t mft_accumulate_blocks_f32(const mft_block_copy_t* table_dev, int32_t n_entries, mft_stream_t stream);
+
+/* ---- attention: the chain repeat_kv_heads -> transpose -> matmul ->
+ *      mul(scale) -> add(mask) -> softmax -> matmul of the model graphs
+ *      (qwen_model.cpp:311-318, gemma_model.cpp:487-505, gpt2_model.cpp:630-657;
+ *      softmax ops.cpp:1307-1363, SoftmaxBackward backward_functions.cpp:306-349;
+ *      masks ops.cpp:2167-2180 and gemma_model.cpp:272-285) -----------------
+ * Fused causal / sliding-window GQA attention.  Element (b, s, h, d) of a
+ * tensor lives at base[b*stride_b + s*stride_s + h*stride_h + d] (bf16).
+ * Query head h reads KV head h / (n_heads / n_kv_heads): repeat_kv is an index
+ * remap, never a copy.  Key j is visible to query i iff j <= i and
+ * (window <= 0 or i - j < window).  lse is f32 [batch, n_heads, seq]. */
+typedef struct {
+    int64_t stride_b, stride_s, stride_h;
+} mft_strides_t;
+int32_t mft_attn_fwd(const void* q, mft_strides_t sq, const void* k, mft_strides_t sk,
+                     const void* v, mft_strides_t sv, void* o, mft_strides_t so, float* lse,
+                     int64_t batch, int64_t seq, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim,
+                     float scale, int64_t window, mft_stream_t stream);
+/* dq/dk/dv are bf16 with the strides of q/k/v; dk/dv are per KV head (the sum
+ * over the query heads of a group, RepeatKVHeadsBackward).  `delta` is an f32
+ * [batch, n_heads, seq] scratch buffer supplied by the caller; dk/dv
+ * accumulate in f32 scratch `dkv_acc` of 2*batch*seq*n_kv_heads*head_dim
+ * floats supplied by the caller. */
+int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, mft_strides_t sk,
+                     const void* v, mft_strides_t sv, const void* o, mft_strides_t so,
+                     const void* d_o, mft_strides_t sdo, const float* lse,
+                     void* dq, void* dk, void* dv, float* delta, float* dkv_acc,
+                     int64_t batch, int64_t seq, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim,
+                     float scale, int64_t window, mft_stream_t stream);
+
+/* ---- lm head + shifted cross-entropy (lm_cross_entropy core/lm_loss.cpp:268-382,
+ *      LMCrossEntropyBackward :75-163, streaming variant :384-481 / :165-266) -
+ * hidden bf16 [batch*seq, H]; table bf16 [V, H] (tied embedding); labels int32
+ * [batch, seq] UNSHIFTED: row (b, s < seq-1) is scored against labels[b, s+1],
+ * labels equal to ignore_index are skipped, the mean runs over the valid rows.
+ * The [T, V] logits never reach memory: the vocabulary is processed in panels.
+ * Forward writes loss_dev[0] (f32 mean NLL; NaN when nothing is valid),
+ * n_valid_dev[0] (int32) and lse (f32 [batch*seq]).  A label >= V or < 0 (other
+ * than ignore_index) sets *status_dev = MFT_ERR_BOUNDS.
+ * Backward writes dhidden (bf16 [T,H]) = dloss * d(mean NLL)/d(hidden), with the
+ * 1/n_valid coefficient read from n_valid_dev, or 1/n_valid_override if > 0
+ * (data-parallel runs pass the global count).
+ * workspace: mft_lmhead_ce_workspace_bytes() bytes of device scratch. */
+int64_t mft_lmhead_ce_workspace_bytes(int64_t n_tokens, int64_t hidden, int64_t vocab);
+int32_t mft_lmhead_ce_fwd(const void* hidden_bf16, const void* table_bf16, const int32_t* labels,
+                          int64_t batch, int64_t seq, int64_t hidden, int64_t vocab, int32_t ignore_index,
+                          float* loss_dev, int32_t* n_valid_dev, float* lse, int32_t* status_dev,
+                          void* workspace, int64_t workspace_bytes, mft_stream_t stream);
+int32_t mft_lmhead_ce_bwd(const void* hidden_bf16, const void* table_bf16, const void* table_t_bf16,
+                          const int32_t* labels, int64_t batch, int64_t seq, int64_t hidden, int64_t vocab,
+                          int32_t ignore_index, const float* lse, const int32_t* n_valid_dev,
+                          int64_t n_valid_override, float dloss, void* dhidden_bf16,
+                          void* workspace, int64_t workspace_bytes, mft_stream_t stream);
+/* Dense-logits variants (API completeness: lm_cross_entropy on a materialised
+ * [batch, seq, V] f32 tensor). */
+int32_t mft_ce_dense_fwd(const float* logits, const int32_t* labels, int64_t batch, int64_t seq, int64_t vocab,
+                         int32_t ignore_index, float* loss_dev, int32_t* n_valid_dev, float* lse,
+                         int32_t* status_dev, mft_stream_t stream);
+int32_t mft_ce_dense_bwd(const float* logits, const int32_t* labels, int64_t batch, int64_t seq, int64_t vocab,
+                         int32_t ignore_index, const float* lse, const int32_t* n_valid_dev, float dloss,
+                         float* dlogits, mft_stream_t stream);
+
+/* ---- optimizer (Adam::step optim/adam.cpp:25-90, Optimizer::clip_grad_norm
+ *      optim/optimizer.cpp:6-38, Tensor::zero_grad core/tensor.cpp:602-607) ---
+ * All LoRA parameters live in one flat f32 bucket (params / grads / m / v of n
+ * elements).  mft_grad_sqnorm writes sum(g^2) to sqnorm_dev[0].
+ * mft_adam_step applies, per element (the reference's L2-style rule):
+ *     g = clip * grads[i] + wd * p;  m = b1*m + (1-b1)*g;  v = b2*v + (1-b2)*g*g
+ *     p -= lr * (m / (1 - b1^step)) / (sqrt(v / (1 - b2^step)) + eps)
+ * where clip = 1 if max_norm <= 0 or norm <= max_norm, else
+ * max_norm / (norm + clip_eps) with norm = sqrt(sqnorm_dev[0]) (clip_eps = 0
+ * for Optimizer::clip_grad_norm, 1e-6 for the trainers' variant).
+ * zero_grad != 0 clears grads in the same pass. */
+int32_t mft_grad_sqnorm(const float* grads, int64_t n, float* sqnorm_dev, mft_stream_t stream);
+int32_t mft_adam_step(float* params, float* grads, float* m, float* v, int64_t n, int64_t step,
+                      float lr, float beta1, float beta2, float eps, float weight_decay,
+                      const float* sqnorm_dev, float max_norm, float clip_eps, int32_t zero_grad,
+                      mft_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MFT_CUDA_H */

@@ -1,0 +1,139 @@
+"""ctypes binding of libmft_cuda.so (the C ABI declared in include/mft_cuda.h).
+
+There is no fallback: if the shared object is missing or a call fails, an
+exception is raised.  PyTorch is only used by callers for device memory and
+streams; pointers cross this boundary as plain integers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "libmft_cuda.so"
+
+MFT_F32, MFT_BF16, MFT_I32 = 0, 1, 2
+ACT_GELU, ACT_SWIGLU, ACT_GEGLU = 0, 1, 2
+
+
+class MftError(RuntimeError):
+    pass
+
+
+class Strides(C.Structure):
+    _fields_ = [("stride_b", C.c_int64), ("stride_s", C.c_int64), ("stride_h", C.c_int64)]
+
+
+class BlockCopy(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("rows", C.c_int32), ("cols", C.c_int32),
+                ("src_ld", C.c_int32), ("dst_ld", C.c_int32), ("transpose", C.c_int32), ("pad", C.c_int32)]
+
+
+_lib = None
+
+i32, i64, f32, vp, sz = C.c_int32, C.c_int64, C.c_float, C.c_void_p, C.c_size_t
+
+# name -> argument types (every function returns int32 unless listed in _RET)
+_SIGS = {
+    "mft_init": [i32],
+    "mft_shutdown": [],
+    "mft_version": [],
+    "mft_stream_sync": [vp],
+    "mft_device_status": [vp, C.POINTER(i32)],
+    "mft_malloc": [sz, C.POINTER(vp)],
+    "mft_free": [vp],
+    "mft_empty_cache": [],
+    "mft_mem_stats": [C.POINTER(i64)],
+    "mft_memcpy_h2d": [vp, vp, sz, vp],
+    "mft_memcpy_d2h": [vp, vp, sz, vp],
+    "mft_memcpy_d2d": [vp, vp, sz, vp],
+    "mft_memset": [vp, i32, sz, vp],
+    "mft_cast_f32_to_bf16": [vp, vp, i64, vp],
+    "mft_cast_bf16_to_f32": [vp, vp, i64, vp],
+    "mft_transpose_f32_to_bf16": [vp, vp, i64, i64, vp],
+    "mft_transpose_bf16": [vp, vp, i64, i64, vp],
+    "mft_embedding_gather": [vp, vp, vp, vp, i64, i64, i64, i64, f32, vp, vp],
+    "mft_rmsnorm_fwd": [vp, i32, vp, f32, i32, vp, i32, vp, vp, vp, i64, i64, vp],
+    "mft_rmsnorm_bwd": [vp, i32, vp, i32, vp, vp, f32, i32, vp, i32, i32, vp, i64, i64, vp],
+    "mft_layernorm_fwd": [vp, i32, vp, vp, f32, vp, i32, vp, vp, i64, i64, vp],
+    "mft_layernorm_bwd": [vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, vp, vp, i64, i64, vp],
+    "mft_act_fwd": [i32, vp, vp, i64, vp, i64, i64, vp],
+    "mft_act_bwd": [i32, vp, vp, vp, i64, vp, vp, i64, i64, vp],
+    "mft_add_f32": [vp, vp, vp, i64, vp],
+    "mft_add_f32_bf16": [vp, vp, vp, i64, vp],
+    "mft_scale_f32": [vp, f32, i64, vp],
+    "mft_rope_table_host": [vp, vp, i64, i64, f32],
+    "mft_headnorm_rope_fwd": [vp, i64, vp, f32, vp, vp, vp, i64, vp, i64, i64, i64, i64, vp],
+    "mft_headnorm_rope_bwd": [vp, i64, vp, i64, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, vp],
+    "mft_repeat_kv": [vp, i32, vp, i64, i64, i64, i64, i64, vp],
+    "mft_repeat_kv_bwd": [vp, vp, i64, i64, i64, i64, i64, vp],
+    "mft_gemm_nt": [vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, f32, vp, i64, i32, i32, vp],
+    "mft_gemm_tn_acc": [vp, i64, vp, i64, i64, i64, i64, f32, vp, i64, vp],
+    "mft_pack_blocks_bf16": [vp, i32, vp],
+    "mft_accumulate_blocks_f32": [vp, i32, vp],
+    "mft_attn_fwd": [vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, i64, i64, i64, i64, i64, f32, i64, vp],
+    "mft_attn_bwd": [vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, vp, vp, vp, vp, vp,
+                     i64, i64, i64, i64, i64, f32, i64, vp],
+    "mft_lmhead_ce_workspace_bytes": [i64, i64, i64],
+    "mft_lmhead_ce_fwd": [vp, vp, vp, i64, i64, i64, i64, i32, vp, vp, vp, vp, vp, i64, vp],
+    "mft_lmhead_ce_bwd": [vp, vp, vp, vp, i64, i64, i64, i64, i32, vp, vp, i64, f32, vp, vp, i64, vp],
+    "mft_ce_dense_fwd": [vp, vp, i64, i64, i64, i32, vp, vp, vp, vp, vp],
+    "mft_ce_dense_bwd": [vp, vp, i64, i64, i64, i32, vp, vp, f32, vp, vp],
+    "mft_grad_sqnorm": [vp, i64, vp, vp],
+    "mft_adam_step": [vp, vp, vp, vp, i64, i64, f32, f32, f32, f32, f32, vp, f32, f32, i32, vp],
+}
+_RET = {"mft_launch_count": i64, "mft_last_error": C.c_char_p, "mft_lmhead_ce_workspace_bytes": i64}
+_NO_STATUS = {"mft_version", "mft_lmhead_ce_workspace_bytes"}
+
+
+def exported_names() -> list[str]:
+    return sorted(set(_SIGS) | {"mft_launch_count", "mft_launch_count_reset", "mft_last_error"})
+
+
+def load() -> C.CDLL:
+    """Load the shared object (building nothing: see mobilefinetuner_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise MftError(f"{_LIB_PATH} is missing: run `python -m mobilefinetuner_b200.build` (there is no CPU fallback)")
+    lib = C.CDLL(str(_LIB_PATH))
+    for name, args in _SIGS.items():
+        fn = getattr(lib, name, None)
+        if fn is None:   # reported by missing_symbols(); calling it raises
+            continue
+        fn.argtypes = args
+        fn.restype = _RET.get(name, i32)
+    lib.mft_launch_count.argtypes = []
+    lib.mft_launch_count.restype = i64
+    lib.mft_launch_count_reset.argtypes = []
+    lib.mft_launch_count_reset.restype = None
+    lib.mft_last_error.argtypes = []
+    lib.mft_last_error.restype = C.c_char_p
+    _lib = lib
+    return lib
+
+
+def missing_symbols() -> list[str]:
+    lib = load()
+    return [n for n in exported_names() if getattr(lib, n, None) is None]
+
+
+def call(name: str, *args):
+    """Call an entry point and raise MftError on a non-zero status."""
+    lib = load()
+    fn = getattr(lib, name)
+    rc = fn(*args)
+    if name in _NO_STATUS or name in _RET:
+        return rc
+    if rc != 0:
+        raise MftError(f"{name} failed with status {rc}: {lib.mft_last_error().decode(errors='replace')}")
+    return rc
+
+
+_initialised = set()
+
+
+def init(device: int = 0) -> None:
+    if device not in _initialised:
+        call("mft_init", device)
+        _initialised.add(device)

@@ -1,0 +1,346 @@
+// bf16 "NT" GEMM on the 5th-generation tensor cores (tcgen05) for sm_100a:
+//     D[m,n] = alpha * ( A[m,:K].B[n,:K] + A2[m,:K2].B2[n,:K2] ) + bias[n] (+ D[m,n])
+// The second (A2,B2) segment carries the rank-r LoRA update in the same
+// accumulator (A2 = scale*(X*A), B2 = B^T), see include/mft_cuda.h.
+//
+// Structure: persistent kernel, one CTA per SM, 128 x BLOCK_N output tiles,
+// 64-wide k-blocks.  Warp 0 = TMA producer (cp.async.bulk.tensor into a
+// multi-stage shared-memory ring, 128-byte swizzle), warp 1 = MMA issuer (one
+// thread issues tcgen05.mma, accumulators live in tensor memory, two
+// accumulator buffers so the epilogue of tile i overlaps the main loop of tile
+// i+1), warps 2..5 = epilogue (tcgen05.ld -> registers -> alpha/bias/convert ->
+// global).  All mbarrier waits are bounded; a wait that runs out sets the
+// library status word to MFT_ERR_TIMEOUT and the CTA leaves after freeing its
+// tensor memory.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace mft {
+
+using namespace ptx;
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+    int m, n, k, k2;
+    int num_m_tiles, num_n_tiles;
+    float alpha;
+    const float* bias;
+    void* d;
+    long long ldd;
+    int d_is_f32;
+    int accumulate;
+    int32_t* status;
+};
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+    static constexpr int B_BYTES = BN * GEMM_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;   // two accumulators; power of two >= 32
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
+               const GemmParams p) {
+    using Cfg = GemmCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: required by the 128-byte swizzle atoms (8 rows x 128 B)
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full_bar = bars;                         // [STAGES]
+    uint64_t* empty_bar = bars + Cfg::STAGES;          // [STAGES]
+    uint64_t* tmem_full_bar = bars + 2 * Cfg::STAGES;  // [2]
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;      // [2]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int num_kb_main = (p.k + GEMM_BK - 1) / GEMM_BK;
+    const int num_kb = num_kb_main + (p.k2 > 0 ? 1 : 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full_bar[b], 1); mbar_init(&tmem_empty_bar[b], 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+        if (p.k2 > 0) { tma_prefetch_desc(&map_a2); tma_prefetch_desc(&map_b2); }
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.num_m_tiles) * GEMM_BM;
+                const int n0 = (tile / p.num_m_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
+                    uint8_t* sb = sa + Cfg::A_BYTES;
+                    mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                    if (kb < num_kb_main) {
+                        tma_load_2d(sa, &map_a, &full_bar[stage], kb * GEMM_BK, m0);
+                        tma_load_2d(sb, &map_b, &full_bar[stage], kb * GEMM_BK, n0);
+                    } else {
+                        tma_load_2d(sa, &map_a2, &full_bar[stage], 0, m0);
+                        tma_load_2d(sb, &map_b2, &full_bar[stage], 0, n0);
+                    }
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // give loads still in flight a bounded chance to land before the CTA leaves
+                for (int s = 0; s < Cfg::STAGES; ++s)
+                    for (int i = 0; i < 4096 && !mbar_try_wait(&full_bar[s], 0) && !mbar_try_wait(&full_bar[s], 1); ++i) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(GEMM_BM, BN);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
+                    const uint32_t sb = sa + Cfg::A_BYTES;
+                    const uint64_t adesc = smem_desc_sw128(sa);
+                    const uint64_t bdesc = smem_desc_sw128(sb);
+                    const int kvalid = (kb < num_kb_main) ? min(GEMM_BK, p.k - kb * GEMM_BK) : p.k2;
+                    const int nmma = (kvalid + 15) / 16;
+                    for (int j = 0; j < nmma; ++j) {
+                        // advance 16 bf16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
+                        umma_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb | j) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);   // frees the stage once these MMAs have read it
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(&tmem_full_bar[acc]);
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;                    // tensor-memory lane quarter this warp may read
+        const int row_in_tile = q * 32 + lane;
+        int it = 0;
+        bool ok = true;
+        const bool vec_ok = p.d_is_f32 ? ((p.ldd % 4) == 0 && (reinterpret_cast<uintptr_t>(p.d) % 16) == 0)
+                                       : ((p.ldd % 8) == 0 && (reinterpret_cast<uintptr_t>(p.d) % 16) == 0);
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            const int acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            const int m0 = (tile % p.num_m_tiles) * GEMM_BM;
+            const int n0 = (tile / p.num_m_tiles) * BN;
+            if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + row_in_tile;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                if (n0 + c >= p.n) break;          // uniform across the warp
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + (uint32_t)c, r);
+                tmem_ld_wait();
+                if (row < p.m) {
+                    const int col0 = n0 + c;
+                    const bool full = vec_ok && (col0 + 32 <= p.n);
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                    if (p.bias) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
+                    }
+                    if (p.d_is_f32) {
+                        float* drow = static_cast<float*>(p.d) + (long long)row * p.ldd + col0;
+                        if (full) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                if (p.accumulate) {
+                                    const float4 prev = *reinterpret_cast<const float4*>(drow + j);
+                                    o.x += prev.x; o.y += prev.y; o.z += prev.z; o.w += prev.w;
+                                }
+                                *reinterpret_cast<float4*>(drow + j) = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.n) drow[j] = v[j] + (p.accumulate ? drow[j] : 0.f);
+                        }
+                    } else {
+                        __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + col0;
+                        if (full) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                float t[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) t[e] = v[j + e];
+                                store8(drow + j, t);
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.n) drow[j] = f32_to_bf16(v[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+        }
+    }
+
+    // ------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static std::once_flag g_encode_once;
+
+static EncodeTiledFn get_encode() {
+    std::call_once(g_encode_once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    });
+    return g_encode;
+}
+
+// Tensor map over a row-major bf16 matrix [rows, cols] (row stride ld elements),
+// box = {64 columns, box_rows rows}, 128-byte swizzle, zero fill outside.
+int32_t make_tmap_bf16(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail(MFT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return fail(MFT_ERR_INVALID_ARG, "GEMM operand base must be 16-byte aligned");
+    if (ld % 8 != 0) return fail(MFT_ERR_INVALID_ARG, "GEMM operand row stride must be a multiple of 8 elements");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MFT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return MFT_OK;
+}
+
+static int g_num_sms = 0;
+int num_sms() {
+    if (g_num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_num_sms <= 0) g_num_sms = 148;
+    }
+    return g_num_sms;
+}
+
+template <int BN>
+static int32_t launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2,
+                           GemmParams p, cudaStream_t stream) {
+    using Cfg = GemmCfg<BN>;
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm smem attr")) return s;
+        configured = true;
+    }
+    p.num_m_tiles = (p.m + GEMM_BM - 1) / GEMM_BM;
+    p.num_n_tiles = (p.n + BN - 1) / BN;
+    const int tiles = p.num_m_tiles * p.num_n_tiles;
+    const int grid = tiles < num_sms() ? tiles : num_sms();
+    gemm_nt_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, p);
+    MFT_LAUNCH_CHECK("gemm_nt");
+    return MFT_OK;
+}
+
+static int pick_bn(int64_t n) {
+    // padded columns weighted by a rough per-tile efficiency: wide tiles amortise the A loads
+    const int cand[3] = {256, 128, 64};
+    const double eff[3] = {1.0, 1.08, 1.35};
+    int best = 256; double best_cost = 1e30;
+    for (int i = 0; i < 3; ++i) {
+        const double cost = (double)((n + cand[i] - 1) / cand[i] * cand[i]) * eff[i];
+        if (cost < best_cost) { best_cost = cost; best = cand[i]; }
+    }
+    return best;
+}
+
+}  // namespace mft
+
+using namespace mft;
+
+extern "C" int32_t mft_gemm_nt(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,
+                               const void* a2, int64_t lda2, const void* b2, int64_t ldb2, int64_t k2, const float* bias,
+                               float alpha, void* d, int64_t ldd, int32_t d_dtype, int32_t accumulate, mft_stream_t stream) {
+    MFT_CHECK_ARG(a && b && d && m > 0 && n > 0 && k > 0, "mft_gemm_nt: bad argument");
+    MFT_CHECK_ARG(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "mft_gemm_nt: dimension too large");
+    MFT_CHECK_ARG(d_dtype == MFT_F32 || d_dtype == MFT_BF16, "mft_gemm_nt: D must be f32 or bf16");
+    MFT_CHECK_ARG(!accumulate || d_dtype == MFT_F32, "mft_gemm_nt: accumulate needs f32 D");
+    MFT_CHECK_ARG(k2 >= 0 && k2 <= GEMM_BK, "mft_gemm_nt: k2 must be in [0, 64]");
+    MFT_CHECK_ARG(k2 == 0 || (a2 && b2), "mft_gemm_nt: second segment needs a2 and b2");
+    MFT_CHECK_ARG(ldd >= n && lda >= k && ldb >= k, "mft_gemm_nt: leading dimension too small");
+    if (!device_status_word()) return fail(MFT_ERR_INVALID_ARG, "mft_gemm_nt: call mft_init first");
+    const int bn = pick_bn(n);
+    CUtensorMap ma, mb, ma2, mb2;
+    if (int32_t s = make_tmap_bf16(&ma, a, m, k, lda, GEMM_BM)) return s;
+    if (int32_t s = make_tmap_bf16(&mb, b, n, k, ldb, bn)) return s;
+    if (k2 > 0) {
+        if (int32_t s = make_tmap_bf16(&ma2, a2, m, k2, lda2, GEMM_BM)) return s;
+        if (int32_t s = make_tmap_bf16(&mb2, b2, n, k2, ldb2, bn)) return s;
+    } else {
+        ma2 = ma; mb2 = mb;
+    }
+    GemmParams p{};
+    p.m = (int)m; p.n = (int)n; p.k = (int)k; p.k2 = (int)k2;
+    p.alpha = alpha; p.bias = bias; p.d = d; p.ldd = ldd;
+    p.d_is_f32 = d_dtype == MFT_F32; p.accumulate = accumulate;
+    p.status = device_status_word();
+    if (bn == 256) return launch_gemm<256>(ma, mb, ma2, mb2, p, as_stream(stream));
+    if (bn == 128) return launch_gemm<128>(ma, mb, ma2, mb2, p, as_stream(stream));
+    return launch_gemm<64>(ma, mb, ma2, mb2, p, as_stream(stream));
+}

@@ -1,0 +1,420 @@
+// RMSNorm / LayerNorm forward and backward, and the fused per-head
+// RMSNorm + rotary embedding used on Q and K.  One CTA per row for the
+// model-width norms (row cached in registers between the reduction and the
+// write), one warp per (token, head) for the per-head kernel.  HBM-bound:
+// every element is read once and written once with 128-bit accesses.
+#include <cmath>
+#include <vector>
+
+#include "common.cuh"
+
+namespace mft {
+
+constexpr int NORM_THREADS = 128;
+constexpr int NORM_VPT = 4;   // up to 4 x 8 elements cached per thread -> dim <= 4096 with 128 threads
+
+template <typename T> struct dtype_of;
+template <> struct dtype_of<float> { static constexpr int v = MFT_F32; };
+template <> struct dtype_of<__nv_bfloat16> { static constexpr int v = MFT_BF16; };
+
+// ---------------------------------------------------------------- RMSNorm forward
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, float eps, int unit_offset,
+                   TY* __restrict__ y, float* __restrict__ rstd_out, const float* __restrict__ residual,
+                   float* __restrict__ sum_out, int64_t dim) {
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const TX* xr = x + row * dim;
+    const int nvec = (int)(dim / 8);
+    float v[NORM_VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            load8(xr + i * 8, v[k]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)dim + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            float wv[8], o[8];
+            load8(w + i * 8, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = v[k][j] * rstd * (unit_offset ? 1.0f + wv[j] : wv[j]);
+            if (y) store8(y + row * dim + i * 8, o);
+            if (residual) {
+                float r[8];
+                load8(residual + row * dim + i * 8, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) r[j] += o[j];
+                store8(sum_out + row * dim + i * 8, r);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- RMSNorm backward
+// g = dy * w_eff ; dx = g*rstd - x * rstd^3/D * sum(g*x)
+template <typename TDY, typename TX, typename TDX>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
+                   const float* __restrict__ rstd_in, float eps, int unit_offset, TDX* __restrict__ dx,
+                   int accumulate, float* __restrict__ dweight, int64_t dim) {
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const int nvec = (int)(dim / 8);
+    float xv[NORM_VPT][8], g[NORM_VPT][8];
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            float wv[8];
+            load8(x + row * dim + i * 8, xv[k]);
+            load8(dy + row * dim + i * 8, g[k]);
+            load8(w + i * 8, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (dweight) atomicAdd(dweight + i * 8 + j, g[k][j] * xv[k][j] * (rstd_in ? rstd_in[row] : 0.f));
+                g[k][j] *= (unit_offset ? 1.0f + wv[j] : wv[j]);
+                dot += g[k][j] * xv[k][j];
+                ss += xv[k][j] * xv[k][j];
+            }
+        }
+    }
+    dot = block_sum(dot, scratch);
+    float rstd;
+    if (rstd_in) rstd = rstd_in[row];
+    else {
+        ss = block_sum(ss, scratch);
+        rstd = rsqrtf(ss / (float)dim + eps);
+    }
+    const float coeff = rstd * rstd * rstd / (float)dim * dot;
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = g[k][j] * rstd - xv[k][j] * coeff;
+            if (accumulate) {
+                float prev[8];
+                load8(dx + row * dim + i * 8, prev);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] += prev[j];
+            }
+            store8(dx + row * dim + i * 8, o);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- LayerNorm
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
+                     TY* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t dim) {
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const int nvec = (int)(dim / 8);
+    float v[NORM_VPT][8];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            load8(x + row * dim + i * 8, v[k]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += v[k][j];
+        }
+    }
+    const float mean = block_sum(s, scratch) / (float)dim;
+    float var = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { float d = v[k][j] - mean; var += d * d; }
+        }
+    }
+    var = block_sum(var, scratch) / (float)dim;
+    const float rstd = 1.0f / sqrtf(var + eps);
+    if (threadIdx.x == 0) {
+        if (mean_out) mean_out[row] = mean;
+        if (rstd_out) rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            float wv[8], bv[8], o[8];
+            load8(w + i * 8, wv);
+            load8(b + i * 8, bv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = (v[k][j] - mean) * rstd * wv[j] + bv[j];
+            store8(y + row * dim + i * 8, o);
+        }
+    }
+}
+
+// dx = rstd/D * (D*g - sum(g) - xhat*sum(g*xhat)),  g = dy*w
+template <typename TDY, typename TX, typename TDX>
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
+                     const float* __restrict__ mean_in, const float* __restrict__ rstd_in, TDX* __restrict__ dx,
+                     int accumulate, float* __restrict__ dweight, float* __restrict__ dbias, int64_t dim) {
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const int nvec = (int)(dim / 8);
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[NORM_VPT][8], g[NORM_VPT][8];
+    float sg = 0.f, sgx = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            float wv[8];
+            load8(x + row * dim + i * 8, xh[k]);
+            load8(dy + row * dim + i * 8, g[k]);
+            load8(w + i * 8, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                xh[k][j] = (xh[k][j] - mean) * rstd;
+                if (dweight) atomicAdd(dweight + i * 8 + j, g[k][j] * xh[k][j]);
+                if (dbias) atomicAdd(dbias + i * 8 + j, g[k][j]);
+                g[k][j] *= wv[j];
+                sg += g[k][j];
+                sgx += g[k][j] * xh[k][j];
+            }
+        }
+    }
+    sg = block_sum(sg, scratch);
+    sgx = block_sum(sgx, scratch);
+    const float D = (float)dim;
+#pragma unroll
+    for (int k = 0; k < NORM_VPT; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = (rstd / D) * (D * g[k][j] - sg - xh[k][j] * sgx);
+            if (accumulate) {
+                float prev[8];
+                load8(dx + row * dim + i * 8, prev);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] += prev[j];
+            }
+            store8(dx + row * dim + i * 8, o);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- per-head norm + RoPE
+// One warp per (token, head).  Lane l owns PER = head_dim/64 consecutive
+// elements of the first half (d = l*PER ..) and the paired elements d + hd/2.
+template <int PER, bool BWD>
+__global__ void headnorm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64_t ld_in,   // fwd: x ; bwd: dy
+                                     const __nv_bfloat16* __restrict__ x, int64_t ld_x,     // bwd only: forward input
+                                     const float* __restrict__ nw, float eps,
+                                     float* __restrict__ rstd_buf,                           // fwd: out ; bwd: in
+                                     const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                     __nv_bfloat16* __restrict__ out, int64_t ld_out,
+                                     int64_t n_tokens, int64_t seq_len, int64_t n_heads) {
+    constexpr int HD = PER * 64, HALF = PER * 32;
+    const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= n_tokens * n_heads) return;
+    const int64_t tok = wid / n_heads, head = wid % n_heads;
+    const int64_t pos = tok % seq_len;
+    const int d0 = lane * PER;
+    float a[PER], b[PER];   // first-half / second-half values of `in`
+    {
+        const __nv_bfloat16* p = in + tok * ld_in + head * HD;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) { a[j] = bf16_to_f32(p[d0 + j]); b[j] = bf16_to_f32(p[HALF + d0 + j]); }
+    }
+    float c[PER], s[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        if (cos_tab) { c[j] = cos_tab[pos * HALF + d0 + j]; s[j] = sin_tab[pos * HALF + d0 + j]; }
+        else { c[j] = 1.f; s[j] = 0.f; }
+    }
+    float w1[PER], w2[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        w1[j] = nw ? 1.0f + nw[d0 + j] : 1.0f;
+        w2[j] = nw ? 1.0f + nw[HALF + d0 + j] : 1.0f;
+    }
+    __nv_bfloat16* o = out + tok * ld_out + head * HD;
+    if (!BWD) {
+        float rstd = 1.0f;
+        if (nw) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) ss += a[j] * a[j] + b[j] * b[j];
+            ss = warp_sum(ss);
+            rstd = rsqrtf(ss / (float)HD + eps);
+            if (lane == 0 && rstd_buf) rstd_buf[wid] = rstd;
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const float x1 = a[j] * rstd * w1[j], x2 = b[j] * rstd * w2[j];
+            o[d0 + j] = f32_to_bf16(x1 * c[j] - x2 * s[j]);
+            o[HALF + d0 + j] = f32_to_bf16(x1 * s[j] + x2 * c[j]);
+        }
+    } else {
+        // undo the rotation: dxn1 = dy1*c + dy2*s ; dxn2 = -dy1*s + dy2*c
+        float g1[PER], g2[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            g1[j] = a[j] * c[j] + b[j] * s[j];
+            g2[j] = -a[j] * s[j] + b[j] * c[j];
+        }
+        if (nw) {
+            const __nv_bfloat16* xp = x + tok * ld_x + head * HD;
+            float x1[PER], x2[PER];
+            float dot = 0.f;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                x1[j] = bf16_to_f32(xp[d0 + j]); x2[j] = bf16_to_f32(xp[HALF + d0 + j]);
+                g1[j] *= w1[j]; g2[j] *= w2[j];
+                dot += g1[j] * x1[j] + g2[j] * x2[j];
+            }
+            dot = warp_sum(dot);
+            const float rstd = rstd_buf[wid];
+            const float coeff = rstd * rstd * rstd / (float)HD * dot;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                g1[j] = g1[j] * rstd - x1[j] * coeff;
+                g2[j] = g2[j] * rstd - x2[j] * coeff;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j) { o[d0 + j] = f32_to_bf16(g1[j]); o[HALF + d0 + j] = f32_to_bf16(g2[j]); }
+    }
+}
+
+}  // namespace mft
+
+using namespace mft;
+
+#define DISPATCH_2(XD, YD, CALL)                                                         \
+    if (XD == MFT_F32 && YD == MFT_F32) { CALL(float, float) }                           \
+    else if (XD == MFT_F32 && YD == MFT_BF16) { CALL(float, __nv_bfloat16) }             \
+    else if (XD == MFT_BF16 && YD == MFT_F32) { CALL(__nv_bfloat16, float) }             \
+    else if (XD == MFT_BF16 && YD == MFT_BF16) { CALL(__nv_bfloat16, __nv_bfloat16) }    \
+    else return fail(MFT_ERR_INVALID_ARG, "dtype must be MFT_F32 or MFT_BF16");
+
+extern "C" {
+
+int32_t mft_rmsnorm_fwd(const void* x, int32_t xd, const float* w, float eps, int32_t unit_offset, void* y, int32_t yd,
+                        float* rstd, const float* residual, float* sum_out, int64_t rows, int64_t dim, mft_stream_t stream) {
+    MFT_CHECK_ARG(x && w && rows > 0 && dim > 0, "mft_rmsnorm_fwd: bad argument");
+    MFT_CHECK_ARG(y || (residual && sum_out), "mft_rmsnorm_fwd: nothing to write");
+    MFT_CHECK_ARG(!residual || sum_out, "mft_rmsnorm_fwd: residual needs sum_out");
+    MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_rmsnorm_fwd: dim must be a multiple of 8 and <= 4096");
+#define CALL(TX, TY) rmsnorm_fwd_kernel<TX, TY><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TX*)x, w, eps, unit_offset, (TY*)y, rstd, residual, sum_out, dim);
+    DISPATCH_2(xd, yd, CALL)
+#undef CALL
+    MFT_LAUNCH_CHECK("rmsnorm_fwd");
+    return MFT_OK;
+}
+
+int32_t mft_rmsnorm_bwd(const void* dy, int32_t dyd, const void* x, int32_t xd, const float* w, const float* rstd, float eps,
+                        int32_t unit_offset, void* dx, int32_t dxd, int32_t accumulate, float* dweight, int64_t rows,
+                        int64_t dim, mft_stream_t stream) {
+    MFT_CHECK_ARG(dy && x && w && dx && rows > 0 && dim > 0, "mft_rmsnorm_bwd: bad argument");
+    MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_rmsnorm_bwd: dim must be a multiple of 8 and <= 4096");
+    MFT_CHECK_ARG(!accumulate || dxd == MFT_F32, "mft_rmsnorm_bwd: accumulate needs f32 dx");
+    MFT_CHECK_ARG(!dweight || rstd, "mft_rmsnorm_bwd: dweight needs rstd");
+#define LAUNCH(TDY, TX, TDX) rmsnorm_bwd_kernel<TDY, TX, TDX><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TDY*)dy, (const TX*)x, w, rstd, eps, unit_offset, (TDX*)dx, accumulate, dweight, dim);
+#define CALL(TDY, TX) if (dxd == MFT_F32) { LAUNCH(TDY, TX, float) } else if (dxd == MFT_BF16) { LAUNCH(TDY, TX, __nv_bfloat16) } else return fail(MFT_ERR_INVALID_ARG, "mft_rmsnorm_bwd: bad dx dtype");
+    DISPATCH_2(dyd, xd, CALL)
+#undef CALL
+#undef LAUNCH
+    MFT_LAUNCH_CHECK("rmsnorm_bwd");
+    return MFT_OK;
+}
+
+int32_t mft_layernorm_fwd(const void* x, int32_t xd, const float* w, const float* b, float eps, void* y, int32_t yd,
+                          float* mean, float* rstd, int64_t rows, int64_t dim, mft_stream_t stream) {
+    MFT_CHECK_ARG(x && w && b && y && rows > 0 && dim > 0, "mft_layernorm_fwd: bad argument");
+    MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_layernorm_fwd: dim must be a multiple of 8 and <= 4096");
+#define CALL(TX, TY) layernorm_fwd_kernel<TX, TY><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TX*)x, w, b, eps, (TY*)y, mean, rstd, dim);
+    DISPATCH_2(xd, yd, CALL)
+#undef CALL
+    MFT_LAUNCH_CHECK("layernorm_fwd");
+    return MFT_OK;
+}
+
+int32_t mft_layernorm_bwd(const void* dy, int32_t dyd, const void* x, int32_t xd, const float* w, const float* mean,
+                          const float* rstd, void* dx, int32_t dxd, int32_t accumulate, float* dweight, float* dbias,
+                          int64_t rows, int64_t dim, mft_stream_t stream) {
+    MFT_CHECK_ARG(dy && x && w && mean && rstd && dx && rows > 0 && dim > 0, "mft_layernorm_bwd: bad argument");
+    MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_layernorm_bwd: dim must be a multiple of 8 and <= 4096");
+    MFT_CHECK_ARG(!accumulate || dxd == MFT_F32, "mft_layernorm_bwd: accumulate needs f32 dx");
+#define LAUNCH(TDY, TX, TDX) layernorm_bwd_kernel<TDY, TX, TDX><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TDY*)dy, (const TX*)x, w, mean, rstd, (TDX*)dx, accumulate, dweight, dbias, dim);
+#define CALL(TDY, TX) if (dxd == MFT_F32) { LAUNCH(TDY, TX, float) } else if (dxd == MFT_BF16) { LAUNCH(TDY, TX, __nv_bfloat16) } else return fail(MFT_ERR_INVALID_ARG, "mft_layernorm_bwd: bad dx dtype");
+    DISPATCH_2(dyd, xd, CALL)
+#undef CALL
+#undef LAUNCH
+    MFT_LAUNCH_CHECK("layernorm_bwd");
+    return MFT_OK;
+}
+
+int32_t mft_rope_table_host(float* cos_host, float* sin_host, int64_t seq_len, int64_t head_dim, float theta) {
+    MFT_CHECK_ARG(cos_host && sin_host && seq_len > 0 && head_dim > 0 && head_dim % 2 == 0, "mft_rope_table_host: bad argument");
+    const int64_t half = head_dim / 2;
+    for (int64_t pos = 0; pos < seq_len; ++pos)
+        for (int64_t d = 0; d < half; ++d) {
+            // identical expression (and float types) to apply_rope in the reference
+            float freq = 1.0f / std::pow(theta, 2.0f * d / head_dim);
+            float angle = pos * freq;
+            cos_host[pos * half + d] = std::cos(angle);
+            sin_host[pos * half + d] = std::sin(angle);
+        }
+    return MFT_OK;
+}
+
+static int32_t launch_headnorm_rope(bool bwd, const void* in, int64_t ld_in, const void* x, int64_t ld_x, const float* nw,
+                                    float eps, float* rstd, const float* cos_tab, const float* sin_tab, void* out,
+                                    int64_t ld_out, int64_t n_tokens, int64_t seq_len, int64_t n_heads, int64_t hd,
+                                    mft_stream_t stream) {
+    const int64_t warps = n_tokens * n_heads;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
+#define HL(PER, B) headnorm_rope_kernel<PER, B><<<blocks, threads, 0, as_stream(stream)>>>((const __nv_bfloat16*)in, ld_in, (const __nv_bfloat16*)x, ld_x, nw, eps, rstd, cos_tab, sin_tab, (__nv_bfloat16*)out, ld_out, n_tokens, seq_len, n_heads)
+    if (hd == 64) { if (bwd) HL(1, true); else HL(1, false); }
+    else if (hd == 128) { if (bwd) HL(2, true); else HL(2, false); }
+    else if (hd == 256) { if (bwd) HL(4, true); else HL(4, false); }
+    else return fail(MFT_ERR_UNSUPPORTED, "headnorm_rope: head_dim must be 64, 128 or 256");
+#undef HL
+    MFT_LAUNCH_CHECK("headnorm_rope");
+    return MFT_OK;
+}
+
+int32_t mft_headnorm_rope_fwd(const void* x, int64_t ld, const float* nw, float eps, const float* cos_tab,
+                              const float* sin_tab, void* y, int64_t ld_y, float* rstd, int64_t n_tokens, int64_t seq_len,
+                              int64_t n_heads, int64_t hd, mft_stream_t stream) {
+    MFT_CHECK_ARG(x && y && n_tokens > 0 && seq_len > 0 && n_heads > 0, "mft_headnorm_rope_fwd: bad argument");
+    MFT_CHECK_ARG((cos_tab == nullptr) == (sin_tab == nullptr), "mft_headnorm_rope_fwd: cos and sin tables go together");
+    MFT_CHECK_ARG(!nw || rstd, "mft_headnorm_rope_fwd: norm needs an rstd buffer");
+    return launch_headnorm_rope(false, x, ld, nullptr, 0, nw, eps, rstd, cos_tab, sin_tab, y, ld_y, n_tokens, seq_len, n_heads, hd, stream);
+}
+int32_t mft_headnorm_rope_bwd(const void* dy, int64_t ld_dy, const void* x, int64_t ld, const float* nw, const float* rstd,
+                              const float* cos_tab, const float* sin_tab, void* dx, int64_t ld_dx, int64_t n_tokens,
+                              int64_t seq_len, int64_t n_heads, int64_t hd, mft_stream_t stream) {
+    MFT_CHECK_ARG(dy && dx && n_tokens > 0 && seq_len > 0 && n_heads > 0, "mft_headnorm_rope_bwd: bad argument");
+    MFT_CHECK_ARG(!nw || (rstd && x), "mft_headnorm_rope_bwd: norm needs x and rstd");
+    return launch_headnorm_rope(true, dy, ld_dy, x, ld, nw, 0.f, const_cast<float*>(rstd), cos_tab, sin_tab, dx, ld_dx, n_tokens, seq_len, n_heads, hd, stream);
+}
+
+}  // extern "C"
