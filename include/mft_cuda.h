@@ -263,7 +263,8 @@ int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, mft_strides
  * than ignore_index) sets *status_dev = MFT_ERR_BOUNDS.
  * Backward writes dhidden (bf16 [T,H]) = dloss * d(mean NLL)/d(hidden), with the
  * 1/n_valid coefficient read from n_valid_dev, or 1/n_valid_override if > 0
- * (data-parallel runs pass the global count).
+ * (data-parallel runs pass the global count).  table_t is the transposed table,
+ * bf16 [H, table_t_ld] with table_t_ld >= V a multiple of 8 (built once at load).
  * workspace: mft_lmhead_ce_workspace_bytes() bytes of device scratch. */
 int64_t mft_lmhead_ce_workspace_bytes(int64_t n_tokens, int64_t hidden, int64_t vocab);
 int32_t mft_lmhead_ce_fwd(const void* hidden_bf16, const void* table_bf16, const int32_t* labels,
@@ -271,18 +272,20 @@ int32_t mft_lmhead_ce_fwd(const void* hidden_bf16, const void* table_bf16, const
                           float* loss_dev, int32_t* n_valid_dev, float* lse, int32_t* status_dev,
                           void* workspace, int64_t workspace_bytes, mft_stream_t stream);
 int32_t mft_lmhead_ce_bwd(const void* hidden_bf16, const void* table_bf16, const void* table_t_bf16,
-                          const int32_t* labels, int64_t batch, int64_t seq, int64_t hidden, int64_t vocab,
+                          int64_t table_t_ld, const int32_t* labels, int64_t batch, int64_t seq, int64_t hidden, int64_t vocab,
                           int32_t ignore_index, const float* lse, const int32_t* n_valid_dev,
                           int64_t n_valid_override, float dloss, void* dhidden_bf16,
                           void* workspace, int64_t workspace_bytes, mft_stream_t stream);
 /* Dense-logits variants (API completeness: lm_cross_entropy on a materialised
- * [batch, seq, V] f32 tensor). */
+ * [batch, seq, V] f32 tensor).  tgt_scratch is int32 [batch*seq] and
+ * loss_scratch one double, both device scratch; the forward fills tgt_scratch
+ * with the shifted labels, which the backward then reads. */
 int32_t mft_ce_dense_fwd(const float* logits, const int32_t* labels, int64_t batch, int64_t seq, int64_t vocab,
                          int32_t ignore_index, float* loss_dev, int32_t* n_valid_dev, float* lse,
-                         int32_t* status_dev, mft_stream_t stream);
-int32_t mft_ce_dense_bwd(const float* logits, const int32_t* labels, int64_t batch, int64_t seq, int64_t vocab,
-                         int32_t ignore_index, const float* lse, const int32_t* n_valid_dev, float dloss,
-                         float* dlogits, mft_stream_t stream);
+                         int32_t* tgt_scratch, double* loss_scratch, int32_t* status_dev, mft_stream_t stream);
+int32_t mft_ce_dense_bwd(const float* logits, const int32_t* tgt_scratch, int64_t batch, int64_t seq, int64_t vocab,
+                         const float* lse, const int32_t* n_valid_dev, float dloss, float* dlogits,
+                         mft_stream_t stream);
 
 /* ---- optimizer (Adam::step optim/adam.cpp:25-90, Optimizer::clip_grad_norm
  *      optim/optimizer.cpp:6-38, Tensor::zero_grad core/tensor.cpp:602-607) ---

@@ -17,6 +17,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "gemm_sm100.h"
 #include "sm100_ptx.cuh"
 
 namespace mft {
@@ -37,7 +38,18 @@ struct GemmParams {
     int d_is_f32;
     int accumulate;
     int32_t* status;
+    // cross-entropy epilogues (lm head): see lmhead_ce.cu
+    const int32_t* ce_tgt;        // [m] shifted label per row, -1 = row not scored
+    const float* ce_lse;          // [m] row log-sum-exp (GRAD mode)
+    const int32_t* ce_nvalid;     // device count of scored rows (GRAD mode)
+    long long ce_nvalid_override; // > 0: use instead of *ce_nvalid
+    float ce_dloss;
+    int ce_col_offset;            // vocabulary index of column 0 of this GEMM
+    float2* ce_partials;          // [m, ce_partial_ld] (max, sum exp) per row and column tile (STATS mode)
+    int ce_partial_ld;
+    float* ce_tgt_logit;          // [m] logit of the label column (STATS mode)
 };
+
 
 template <int BN>
 struct GemmCfg {
@@ -49,7 +61,7 @@ struct GemmCfg {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-template <int BN>
+template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
@@ -168,41 +180,112 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int row = m0 + row_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            if constexpr (EPI == EPI_STORE) {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                if (n0 + c >= p.n) break;          // uniform across the warp
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + (uint32_t)c, r);
-                tmem_ld_wait();
-                if (row < p.m) {
-                    const int col0 = n0 + c;
-                    const bool full = vec_ok && (col0 + 32 <= p.n);
-                    float v[32];
+                for (int c = 0; c < BN; c += 32) {
+                    if (n0 + c >= p.n) break;          // uniform across the warp
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    if (row < p.m) {
+                        const int col0 = n0 + c;
+                        const bool full = vec_ok && (col0 + 32 <= p.n);
+                        float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-                    if (p.bias) {
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                        if (p.bias) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
-                    }
-                    if (p.d_is_f32) {
-                        float* drow = static_cast<float*>(p.d) + (long long)row * p.ldd + col0;
-                        if (full) {
+                            for (int j = 0; j < 32; ++j) if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
+                        }
+                        if (p.d_is_f32) {
+                            float* drow = static_cast<float*>(p.d) + (long long)row * p.ldd + col0;
+                            if (full) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                                if (p.accumulate) {
-                                    const float4 prev = *reinterpret_cast<const float4*>(drow + j);
-                                    o.x += prev.x; o.y += prev.y; o.z += prev.z; o.w += prev.w;
+                                for (int j = 0; j < 32; j += 4) {
+                                    float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                    if (p.accumulate) {
+                                        const float4 prev = *reinterpret_cast<const float4*>(drow + j);
+                                        o.x += prev.x; o.y += prev.y; o.z += prev.z; o.w += prev.w;
+                                    }
+                                    *reinterpret_cast<float4*>(drow + j) = o;
                                 }
-                                *reinterpret_cast<float4*>(drow + j) = o;
+                            } else {
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < p.n) drow[j] = v[j] + (p.accumulate ? drow[j] : 0.f);
                             }
                         } else {
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.n) drow[j] = v[j] + (p.accumulate ? drow[j] : 0.f);
+                            __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + col0;
+                            if (full) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 8) {
+                                    float t[8];
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) t[e] = v[j + e];
+                                    store8(drow + j, t);
+                                }
+                            } else {
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < p.n) drow[j] = f32_to_bf16(v[j]);
+                            }
                         }
-                    } else {
+                    }
+                }
+            } else if constexpr (EPI == EPI_CE_STATS) {
+                const int tgt = (row < p.m) ? p.ce_tgt[row] - p.ce_col_offset : -1;
+                float mx = -INFINITY, sum = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    if (n0 + c >= p.n) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    const int col0 = n0 + c;
+                    float cm = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float v = __uint_as_float(r[j]) * p.alpha;
+                        if (col0 + j >= p.n) v = -INFINITY;
+                        r[j] = __float_as_uint(v);
+                        cm = fmaxf(cm, v);
+                    }
+                    if (tgt >= col0 && tgt < col0 + 32 && row < p.m) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (col0 + j == tgt) p.ce_tgt_logit[row] = __uint_as_float(r[j]);
+                    }
+                    const float nm = fmaxf(mx, cm);
+                    float cs = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) cs += __expf(__uint_as_float(r[j]) - nm);
+                    sum = sum * __expf(mx - nm) + cs;     // mx = -inf on the first chunk -> factor 0
+                    mx = nm;
+                }
+                if (row < p.m) p.ce_partials[(long long)row * p.ce_partial_ld + (n0 / BN)] = make_float2(mx, sum);
+            } else {
+                float lse = 0.f, coef = 0.f;
+                int tgt = -1;
+                if (row < p.m) {
+                    tgt = p.ce_tgt[row];
+                    lse = p.ce_lse[row];
+                    const long long nv = p.ce_nvalid_override > 0 ? p.ce_nvalid_override : (long long)*p.ce_nvalid;
+                    coef = (tgt >= 0 && nv > 0) ? p.ce_dloss / (float)nv : 0.f;
+                    tgt -= p.ce_col_offset;
+                }
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    if (n0 + c >= p.n) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    if (row < p.m) {
+                        const int col0 = n0 + c;
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float pr = __expf(__uint_as_float(r[j]) * p.alpha - lse);
+                            v[j] = (pr - (col0 + j == tgt ? 1.f : 0.f)) * coef;
+                        }
                         __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + col0;
-                        if (full) {
+                        if (vec_ok && col0 + 32 <= p.n) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 8) {
                                 float t[8];
@@ -280,20 +363,20 @@ int num_sms() {
     return g_num_sms;
 }
 
-template <int BN>
+template <int BN, int EPI>
 static int32_t launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2,
                            GemmParams p, cudaStream_t stream) {
     using Cfg = GemmCfg<BN>;
     static bool configured = false;
     if (!configured) {
-        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm smem attr")) return s;
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm smem attr")) return s;
         configured = true;
     }
     p.num_m_tiles = (p.m + GEMM_BM - 1) / GEMM_BM;
     p.num_n_tiles = (p.n + BN - 1) / BN;
     const int tiles = p.num_m_tiles * p.num_n_tiles;
     const int grid = tiles < num_sms() ? tiles : num_sms();
-    gemm_nt_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, p);
+    gemm_nt_kernel<BN, EPI><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, p);
     MFT_LAUNCH_CHECK("gemm_nt");
     return MFT_OK;
 }
@@ -310,6 +393,40 @@ static int pick_bn(int64_t n) {
     return best;
 }
 
+int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream) {
+    MFT_CHECK_ARG(c.a && c.b && c.m > 0 && c.n > 0 && c.k > 0, "gemm_nt: bad argument");
+    MFT_CHECK_ARG(c.m < (1ll << 31) && c.n < (1ll << 31) && c.k < (1ll << 31), "gemm_nt: dimension too large");
+    MFT_CHECK_ARG(c.epi == EPI_CE_STATS || c.d, "gemm_nt: null output");
+    MFT_CHECK_ARG(!c.accumulate || c.d_is_f32, "gemm_nt: accumulate needs f32 D");
+    MFT_CHECK_ARG(c.k2 >= 0 && c.k2 <= GEMM_BK, "gemm_nt: k2 must be in [0, 64]");
+    MFT_CHECK_ARG(c.k2 == 0 || (c.a2 && c.b2), "gemm_nt: second segment needs a2 and b2");
+    MFT_CHECK_ARG((c.epi == EPI_CE_STATS || c.ldd >= c.n) && c.lda >= c.k && c.ldb >= c.k, "gemm_nt: leading dimension too small");
+    if (!device_status_word()) return fail(MFT_ERR_INVALID_ARG, "gemm_nt: call mft_init first");
+    const int bn = c.epi == EPI_STORE ? pick_bn(c.n) : CE_TILE_N;
+    CUtensorMap ma, mb, ma2, mb2;
+    if (int32_t s = make_tmap_bf16(&ma, c.a, c.m, c.k, c.lda, GEMM_BM)) return s;
+    if (int32_t s = make_tmap_bf16(&mb, c.b, c.n, c.k, c.ldb, bn)) return s;
+    if (c.k2 > 0) {
+        if (int32_t s = make_tmap_bf16(&ma2, c.a2, c.m, c.k2, c.lda2, GEMM_BM)) return s;
+        if (int32_t s = make_tmap_bf16(&mb2, c.b2, c.n, c.k2, c.ldb2, bn)) return s;
+    } else {
+        ma2 = ma; mb2 = mb;
+    }
+    GemmParams p{};
+    p.m = (int)c.m; p.n = (int)c.n; p.k = (int)c.k; p.k2 = (int)c.k2;
+    p.alpha = c.alpha; p.bias = c.bias; p.d = c.d; p.ldd = c.ldd;
+    p.d_is_f32 = c.d_is_f32; p.accumulate = c.accumulate;
+    p.status = device_status_word();
+    p.ce_tgt = c.ce_tgt; p.ce_lse = c.ce_lse; p.ce_nvalid = c.ce_nvalid; p.ce_nvalid_override = c.ce_nvalid_override;
+    p.ce_dloss = c.ce_dloss; p.ce_col_offset = c.ce_col_offset; p.ce_partials = c.ce_partials;
+    p.ce_partial_ld = c.ce_partial_ld; p.ce_tgt_logit = c.ce_tgt_logit;
+    if (c.epi == EPI_CE_STATS) return launch_gemm<CE_TILE_N, EPI_CE_STATS>(ma, mb, ma2, mb2, p, stream);
+    if (c.epi == EPI_CE_GRAD) return launch_gemm<CE_TILE_N, EPI_CE_GRAD>(ma, mb, ma2, mb2, p, stream);
+    if (bn == 256) return launch_gemm<256, EPI_STORE>(ma, mb, ma2, mb2, p, stream);
+    if (bn == 128) return launch_gemm<128, EPI_STORE>(ma, mb, ma2, mb2, p, stream);
+    return launch_gemm<64, EPI_STORE>(ma, mb, ma2, mb2, p, stream);
+}
+
 }  // namespace mft
 
 using namespace mft;
@@ -317,30 +434,10 @@ using namespace mft;
 extern "C" int32_t mft_gemm_nt(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,
                                const void* a2, int64_t lda2, const void* b2, int64_t ldb2, int64_t k2, const float* bias,
                                float alpha, void* d, int64_t ldd, int32_t d_dtype, int32_t accumulate, mft_stream_t stream) {
-    MFT_CHECK_ARG(a && b && d && m > 0 && n > 0 && k > 0, "mft_gemm_nt: bad argument");
-    MFT_CHECK_ARG(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "mft_gemm_nt: dimension too large");
     MFT_CHECK_ARG(d_dtype == MFT_F32 || d_dtype == MFT_BF16, "mft_gemm_nt: D must be f32 or bf16");
-    MFT_CHECK_ARG(!accumulate || d_dtype == MFT_F32, "mft_gemm_nt: accumulate needs f32 D");
-    MFT_CHECK_ARG(k2 >= 0 && k2 <= GEMM_BK, "mft_gemm_nt: k2 must be in [0, 64]");
-    MFT_CHECK_ARG(k2 == 0 || (a2 && b2), "mft_gemm_nt: second segment needs a2 and b2");
-    MFT_CHECK_ARG(ldd >= n && lda >= k && ldb >= k, "mft_gemm_nt: leading dimension too small");
-    if (!device_status_word()) return fail(MFT_ERR_INVALID_ARG, "mft_gemm_nt: call mft_init first");
-    const int bn = pick_bn(n);
-    CUtensorMap ma, mb, ma2, mb2;
-    if (int32_t s = make_tmap_bf16(&ma, a, m, k, lda, GEMM_BM)) return s;
-    if (int32_t s = make_tmap_bf16(&mb, b, n, k, ldb, bn)) return s;
-    if (k2 > 0) {
-        if (int32_t s = make_tmap_bf16(&ma2, a2, m, k2, lda2, GEMM_BM)) return s;
-        if (int32_t s = make_tmap_bf16(&mb2, b2, n, k2, ldb2, bn)) return s;
-    } else {
-        ma2 = ma; mb2 = mb;
-    }
-    GemmParams p{};
-    p.m = (int)m; p.n = (int)n; p.k = (int)k; p.k2 = (int)k2;
-    p.alpha = alpha; p.bias = bias; p.d = d; p.ldd = ldd;
-    p.d_is_f32 = d_dtype == MFT_F32; p.accumulate = accumulate;
-    p.status = device_status_word();
-    if (bn == 256) return launch_gemm<256>(ma, mb, ma2, mb2, p, as_stream(stream));
-    if (bn == 128) return launch_gemm<128>(ma, mb, ma2, mb2, p, as_stream(stream));
-    return launch_gemm<64>(ma, mb, ma2, mb2, p, as_stream(stream));
+    GemmCall c;
+    c.a = a; c.lda = lda; c.b = b; c.ldb = ldb; c.m = m; c.n = n; c.k = k;
+    c.a2 = a2; c.lda2 = lda2; c.b2 = b2; c.ldb2 = ldb2; c.k2 = k2;
+    c.bias = bias; c.alpha = alpha; c.d = d; c.ldd = ldd; c.d_is_f32 = d_dtype == MFT_F32; c.accumulate = accumulate;
+    return gemm_nt_run(c, as_stream(stream));
 }

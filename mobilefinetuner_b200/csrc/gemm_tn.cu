@@ -1,0 +1,141 @@
+// "TN" GEMM with the long token dimension contracted:
+//     out[p,q] += alpha * sum_t U[t,p] * V[t,q]        (U [T,P], V [T,Q] bf16 row-major)
+// This is the shape of the LoRA weight gradients (dA = X^T (dY B^T), dB = (XA)^T dY):
+// one of P,Q is the padded rank panel (64), T is 10^3..10^5.  The kernel is bound
+// by reading U and V once from HBM; the tiny fp32 result is reduced across the
+// T-splits with atomics.  Warp-level mma.sync (m16n8k16, bf16 -> f32) with
+// ldmatrix.trans on both operands, cp.async double buffering.
+#include "common.cuh"
+
+namespace mft {
+
+constexpr int TN_PT = 128;      // p-tile
+constexpr int TN_QT = 64;       // q-tile
+constexpr int TN_TC = 32;       // tokens per pipeline step
+constexpr int TN_THREADS = 256;
+constexpr int TN_US = TN_PT + 8;   // padded row strides (elements): conflict-free ldmatrix
+constexpr int TN_VS = TN_QT + 8;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int sz = valid ? 16 : 0;   // src-size 0 -> the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(TN_THREADS)
+gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bfloat16* __restrict__ V, int64_t ldv,
+               int64_t T, int P, int Q, float alpha, float* __restrict__ out, int64_t ldo, int64_t t_per_split) {
+    __shared__ __align__(16) __nv_bfloat16 Us[2][TN_TC][TN_US];
+    __shared__ __align__(16) __nv_bfloat16 Vs[2][TN_TC][TN_VS];
+    const int p0 = blockIdx.x * TN_PT, q0 = blockIdx.y * TN_QT;
+    const int64_t t_begin = (int64_t)blockIdx.z * t_per_split;
+    const int64_t t_end = min(T, t_begin + t_per_split);
+    if (t_begin >= t_end) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nsteps = (int)((t_end - t_begin + TN_TC - 1) / TN_TC);
+
+    auto load_step = [&](int step, int buf) {
+        const int64_t t0 = t_begin + (int64_t)step * TN_TC;
+        // U chunk: 32 rows x 16 vectors of 8
+        for (int i = threadIdx.x; i < TN_TC * (TN_PT / 8); i += TN_THREADS) {
+            const int r = i / (TN_PT / 8), c = (i % (TN_PT / 8)) * 8;
+            const bool ok = (t0 + r < t_end) && (p0 + c < P);
+            cp_async16(&Us[buf][r][c], ok ? U + (t0 + r) * ldu + p0 + c : U, ok);
+        }
+        for (int i = threadIdx.x; i < TN_TC * (TN_QT / 8); i += TN_THREADS) {
+            const int r = i / (TN_QT / 8), c = (i % (TN_QT / 8)) * 8;
+            const bool ok = (t0 + r < t_end) && (q0 + c < Q);
+            cp_async16(&Vs[buf][r][c], ok ? V + (t0 + r) * ldv + q0 + c : V, ok);
+        }
+        cp_async_commit();
+    };
+
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    load_step(0, 0);
+    for (int step = 0; step < nsteps; ++step) {
+        const int buf = step & 1;
+        if (step + 1 < nsteps) { load_step(step + 1, buf ^ 1); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TN_TC; kk += 16) {
+            uint32_t a[4];
+            {   // A = U^T tile: rows p (16 per warp), cols t
+                const int t = kk + (lane & 7) + ((lane >> 4) << 3);
+                const int p = warp * 16 + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4_trans(a, &Us[buf][t][p]);
+            }
+#pragma unroll
+            for (int nb = 0; nb < 8; nb += 2) {
+                uint32_t b[4];
+                const int t = kk + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int q = nb * 8 + (lane >> 4) * 8;
+                ldmatrix_x4_trans(b, &Vs[buf][t][q]);
+                mma_bf16_16816(acc[nb], a, b[0], b[1]);
+                mma_bf16_16816(acc[nb + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int p = p0 + warp * 16 + g + h * 8;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int q = q0 + nb * 8 + tq * 2 + e;
+                if (p < P && q < Q) atomicAdd(out + (int64_t)p * ldo + q, alpha * acc[nb][h * 2 + e]);
+            }
+        }
+    }
+}
+
+}  // namespace mft
+
+using namespace mft;
+
+extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, int64_t ldv, int64_t t, int64_t p, int64_t q,
+                                   float alpha, float* out, int64_t ldo, mft_stream_t stream) {
+    MFT_CHECK_ARG(u && v && out && t > 0 && p > 0 && q > 0, "mft_gemm_tn_acc: bad argument");
+    MFT_CHECK_ARG(p % 8 == 0 && q % 8 == 0 && ldu % 8 == 0 && ldv % 8 == 0, "mft_gemm_tn_acc: P, Q and the row strides must be multiples of 8");
+    MFT_CHECK_ARG(reinterpret_cast<uintptr_t>(u) % 16 == 0 && reinterpret_cast<uintptr_t>(v) % 16 == 0, "mft_gemm_tn_acc: operands must be 16-byte aligned");
+    MFT_CHECK_ARG(ldo >= q && p < (1 << 30) && q < (1 << 30), "mft_gemm_tn_acc: bad leading dimension");
+    const int tiles_p = (int)((p + TN_PT - 1) / TN_PT), tiles_q = (int)((q + TN_QT - 1) / TN_QT);
+    const int64_t tiles = (int64_t)tiles_p * tiles_q;
+    int64_t splits = (148 * 4 + tiles - 1) / tiles;
+    const int64_t max_splits = (t + 4 * TN_TC - 1) / (4 * TN_TC);
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    if (splits > 65535) splits = 65535;
+    int64_t t_per = (t + splits - 1) / splits;
+    t_per = (t_per + TN_TC - 1) / TN_TC * TN_TC;
+    splits = (t + t_per - 1) / t_per;
+    MFT_CHECK_ARG(tiles_q <= 65535, "mft_gemm_tn_acc: Q too large");
+    dim3 grid((unsigned)tiles_p, (unsigned)tiles_q, (unsigned)splits);
+    gemm_tn_kernel<<<grid, TN_THREADS, 0, as_stream(stream)>>>((const __nv_bfloat16*)u, ldu, (const __nv_bfloat16*)v, ldv, t,
+                                                               (int)p, (int)q, alpha, out, ldo, t_per);
+    MFT_LAUNCH_CHECK("gemm_tn");
+    return MFT_OK;
+}

@@ -1,0 +1,373 @@
+"""GPU parity suite, operator level: every call goes through the C ABI of libmft_cuda.so
+and is compared with (a) the committed outputs of the compiled reference
+(tests/golden/ops_golden.npz) and (b) the pinned numpy restatement on other seeded
+shapes.  Integer / indexing work must be bit-exact; bf16 tensor-core paths are held to
+cosine >= 0.999 and max-norm relative error <= 2e-2 (the tolerance of the path's spec),
+fp32 paths to 1e-5."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import cosine, rel_err
+from oracle import restate as R
+
+pytestmark = pytest.mark.gpu
+
+BF16_REL, BF16_COS = 2e-2, 0.999
+
+
+def dev(x, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+def rb(x):
+    return R.bf16_round(np.asarray(x, np.float32))
+
+
+def close_bf16(got, want, rel=BF16_REL, cos=BF16_COS):
+    assert np.isfinite(got).all()
+    assert cosine(got, want) >= cos, f"cosine {cosine(got, want)}"
+    assert rel_err(got, want) <= rel, f"rel err {rel_err(got, want)}"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mobilefinetuner_b200 import ops as O
+    return O
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("m,n,k", [(128, 64, 64), (1, 8, 8), (130, 72, 200), (257, 1152, 640), (512, 1536, 1152),
+                                   (384, 256, 6912), (100, 2304, 768)])
+def test_gemm_nt_matches_float64(ops, m, n, k):
+    g = np.random.Generator(np.random.PCG64(m * 7 + n * 3 + k))
+    a, b = rb(g.standard_normal((m, k))), rb(g.standard_normal((n, k)))
+    want = a.astype(np.float64) @ b.astype(np.float64).T
+    got = host(ops.gemm_nt(dev(a, torch.bfloat16), dev(b, torch.bfloat16), out_dtype=torch.float32))
+    assert rel_err(got, want) < 1e-5
+    got16 = host(ops.gemm_nt(dev(a, torch.bfloat16), dev(b, torch.bfloat16)))
+    close_bf16(got16, want, rel=6e-3)
+    assert ops.device_status() == 0
+
+
+def test_gemm_nt_lora_segment_bias_alpha_accumulate(ops):
+    g = np.random.Generator(np.random.PCG64(5))
+    m, n, k, r = 300, 200, 136, 16
+    a, b = rb(g.standard_normal((m, k))), rb(g.standard_normal((n, k)))
+    a2, b2 = rb(g.standard_normal((m, r))), rb(g.standard_normal((n, r)))
+    bias = g.standard_normal(n).astype(np.float32)
+    prev = g.standard_normal((m, n)).astype(np.float32)
+    want = 0.5 * (a.astype(np.float64) @ b.T + a2.astype(np.float64) @ b2.T) + bias + prev
+    # the second segment lives in 64-wide zero-padded panels, as the LoRA step stores it
+    a2p = np.zeros((m, 64), np.float32); a2p[:, :r] = a2
+    b2p = np.zeros((n, 64), np.float32); b2p[:, :r] = b2
+    out = dev(prev)
+    ops.gemm_nt(dev(a, torch.bfloat16), dev(b, torch.bfloat16), a2=dev(a2p, torch.bfloat16)[:, :r], b2=dev(b2p, torch.bfloat16)[:, :r],
+                bias=dev(bias), alpha=0.5, out=out, accumulate=True)
+    assert rel_err(host(out), want) < 1e-5
+
+
+def test_gemm_rejects_bad_arguments(ops):
+    from mobilefinetuner_b200._lib import MftError
+    a = torch.zeros(8, 12, device="cuda", dtype=torch.bfloat16)   # row stride 12: not a multiple of 8
+    b = torch.zeros(8, 12, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(MftError):
+        ops.gemm_nt(a, b)
+
+
+@pytest.mark.parametrize("t,p,q", [(64, 8, 8), (1000, 136, 64), (4096, 64, 1536), (777, 1152, 64)])
+def test_gemm_tn_acc(ops, t, p, q):
+    g = np.random.Generator(np.random.PCG64(t + p + q))
+    u, v = rb(g.standard_normal((t, p))), rb(g.standard_normal((t, q)))
+    base = g.standard_normal((p, q)).astype(np.float32)
+    want = base + 0.25 * (u.astype(np.float64).T @ v.astype(np.float64))
+    out = dev(base)
+    ops.gemm_tn_acc(dev(u, torch.bfloat16), dev(v, torch.bfloat16), out, alpha=0.25)
+    assert rel_err(host(out), want) < 2e-5
+
+
+def lora_linear_cuda(ops, x, W, bias, A, B, scale, dY):
+    """The LoRA-augmented linear as the step composes it: the rank-r update rides in the base
+    GEMM as an extra 64-wide k-block (forward and dX); dA/dB are token-contracting TN products."""
+    bf = torch.bfloat16
+    T, K = x.shape[0] * x.shape[1], x.shape[2]
+    N, r = W.shape[1], A.shape[1]
+    x2 = dev(x.reshape(T, K), bf)
+    Wt = dev(W.T, bf)                 # [N, K]  forward operand (K-major)
+    Wn = dev(W, bf)                   # [K, N]  backward operand
+    A_nk = torch.zeros(64, K, device="cuda", dtype=bf); A_nk[:r] = dev(A.T, bf)     # [64, K]
+    A_kn = torch.zeros(K, 64, device="cuda", dtype=bf); A_kn[:, :r] = dev(A, bf)    # [K, 64]
+    B_nk = torch.zeros(N, 64, device="cuda", dtype=bf); B_nk[:, :r] = dev(B.T, bf)  # [N, 64]
+    B_kn = torch.zeros(64, N, device="cuda", dtype=bf); B_kn[:r] = dev(B, bf)       # [64, N]
+    xa = ops.gemm_nt(x2, A_nk, alpha=scale)                                         # s * x A   [T, 64]
+    y = ops.gemm_nt(x2, Wt, a2=xa, b2=B_nk, bias=None if bias is None else dev(bias))
+    g = dev(dY.reshape(T, N), bf)
+    gb = ops.gemm_nt(g, B_kn, alpha=scale)                                          # s * dY B^T [T, 64]
+    dx = ops.gemm_nt(g, Wn, a2=gb, b2=A_kn)
+    dA = torch.zeros(K, 64, device="cuda"); ops.gemm_tn_acc(x2, gb, dA)
+    dB = torch.zeros(64, N, device="cuda"); ops.gemm_tn_acc(xa, g, dB)
+    return host(y).reshape(*x.shape[:2], N), host(dx).reshape(x.shape), host(dA)[:, :r], host(dB)[:r]
+
+
+def test_lora_linear_golden(ops, golden):
+    i, o, p = golden.case("lora_linear")
+    y, dx, dA, dB = lora_linear_cuda(ops, i["x"], i["W"], i["bias"], i["A"], i["B"], p["scale"], i["dY"])
+    close_bf16(y, o["y"]); close_bf16(dx, o["dx"]); close_bf16(dA, o["dA"]); close_bf16(dB, o["dB"])
+
+
+def test_lora_linear_model_width(ops):
+    g = np.random.Generator(np.random.PCG64(77))
+    x = g.standard_normal((2, 160, 1152)).astype(np.float32)
+    W = (g.standard_normal((1152, 1536)) * 0.02).astype(np.float32)
+    A = (g.uniform(-1, 1, (1152, 16)) / np.sqrt(1152)).astype(np.float32)
+    B = (g.standard_normal((16, 1536)) * 0.02).astype(np.float32)
+    dY = g.standard_normal((2, 160, 1536)).astype(np.float32)
+    y, dx, dA, dB = lora_linear_cuda(ops, x, W, None, A, B, 2.0, dY)
+    xr, Wr, Ar, Br, dYr = rb(x), rb(W), rb(A), rb(B), rb(dY)
+    want_y = R.lora_linear_fwd(xr, Wr, None, Ar, Br, 2.0)
+    want_dx, want_dA, want_dB = R.lora_linear_bwd(xr, Wr, Ar, Br, 2.0, dYr)
+    close_bf16(y, want_y); close_bf16(dx, want_dx); close_bf16(dA, want_dA); close_bf16(dB, want_dB)
+
+
+# ------------------------------------------------------------------ attention
+def run_attention(ops, q, k, v, dO, scale, window, theta):
+    bf = torch.bfloat16
+    B, nh, S, hd = q.shape
+    nkv = k.shape[1]
+
+    def to_dev(x):   # [B,H,S,D] -> token-major storage [B,S,H,D], viewed back as [B,H,S,D]
+        return dev(np.ascontiguousarray(x.transpose(0, 2, 1, 3)), bf).permute(0, 2, 1, 3)
+
+    qd, kd, vd, dod = to_dev(q), to_dev(k), to_dev(v), to_dev(dO)
+    if theta > 0:
+        cos, sin = ops.rope_tables(S, hd, theta, "cuda")
+        q_in, k_in = qd, kd
+        qd = ops.headnorm_rope_fwd(q_in.permute(0, 2, 1, 3).reshape(B * S, nh * hd), S, nh, hd, cos, sin)[0].view(B, S, nh, hd).permute(0, 2, 1, 3)
+        kd = ops.headnorm_rope_fwd(k_in.permute(0, 2, 1, 3).reshape(B * S, nkv * hd), S, nkv, hd, cos, sin)[0].view(B, S, nkv, hd).permute(0, 2, 1, 3)
+    o, lse = ops.attention_fwd(qd, kd, vd, scale, window)
+    dq, dk, dv = ops.attention_bwd(qd, kd, vd, o, dod, lse, scale, window)
+    if theta > 0:
+        dq = ops.headnorm_rope_bwd(dq.permute(0, 2, 1, 3).reshape(B * S, nh * hd), None, S, nh, hd, cos, sin).view(B, S, nh, hd).permute(0, 2, 1, 3)
+        dk = ops.headnorm_rope_bwd(dk.permute(0, 2, 1, 3).reshape(B * S, nkv * hd), None, S, nkv, hd, cos, sin).view(B, S, nkv, hd).permute(0, 2, 1, 3)
+    return host(o), host(dq), host(dk), host(dv)
+
+
+@pytest.mark.parametrize("name", ["attn_causal_gqa", "attn_window_rope", "attn_hd256_window", "attn_hd128"])
+def test_attention_golden(ops, golden, name):
+    i, o, p = golden.case(name)
+    out, dq, dk, dv = run_attention(ops, i["q"], i["k"], i["v"], i["dO"], p["scale"], int(p["window"]), p["rope_theta"])
+    close_bf16(out, o["O"]); close_bf16(dq, o["dQ"]); close_bf16(dk, o["dK"]); close_bf16(dv, o["dV"])
+
+
+@pytest.mark.parametrize("S", [256, 512])
+def test_attention_operator_sweep_shapes(ops, S):
+    """The operator-level benchmark shape: batch 8, 14 query heads, 2 KV heads, head_dim 64, N(0,1) inputs."""
+    g = np.random.Generator(np.random.PCG64(4000 + S))
+    B, nh, nkv, hd = 8, 14, 2, 64
+    q, k, v, dO = (rb(g.standard_normal(s)) for s in [(B, nh, S, hd), (B, nkv, S, hd), (B, nkv, S, hd), (B, nh, S, hd)])
+    out, dq, dk, dv = run_attention(ops, q, k, v, dO, 0.125, 0, 0.0)
+    w_out, w_dq, w_dk, w_dv = R.attention_fwd_bwd(q, k, v, dO, 0.125)
+    close_bf16(out, w_out); close_bf16(dq, w_dq); close_bf16(dk, w_dk); close_bf16(dv, w_dv)
+
+
+def test_attention_mask_predicate_is_exact(ops):
+    """With V = one-hot rows the output reveals exactly which keys were visible: the causal /
+    sliding-window pattern must equal the reference predicate (j <= i and i - j < window)."""
+    B, nh, S, hd, window = 1, 1, 200, 256, 37
+    q = np.zeros((B, nh, S, hd), np.float32)
+    k = np.zeros((B, nh, S, hd), np.float32)
+    v = np.zeros((B, nh, S, hd), np.float32)
+    for j in range(S):
+        v[0, 0, j, j] = 1.0        # S <= hd: column j marks key j
+    out, *_ = run_attention(ops, q, k, v, np.zeros_like(q), 1.0, window, 0.0)
+    visible = out[0, 0, :, :S] > 0
+    i, j = np.arange(S)[:, None], np.arange(S)[None, :]
+    assert np.array_equal(visible, (j <= i) & (i - j < window))
+
+
+def test_attention_full_size_properties(ops):
+    """S = 4096 (too large for the dense CPU chain): uniform-attention identity.  With Q = 0 every
+    visible key gets the same weight, so O[i] is the running mean of V and dV[j] = sum_{i>=j} dO[i]/(i+1)."""
+    B, nh, nkv, S, hd = 1, 2, 1, 4096, 64
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.zeros(B, S, nh, hd, device="cuda", dtype=torch.bfloat16).permute(0, 2, 1, 3)
+    k = torch.randn(B, S, nkv, hd, device="cuda", generator=g).bfloat16().permute(0, 2, 1, 3)
+    v = torch.randn(B, S, nkv, hd, device="cuda", generator=g).bfloat16().permute(0, 2, 1, 3)
+    o, lse = ops.attention_fwd(q, k, v, 0.125, 0)
+    want = torch.cumsum(v.float(), dim=2) / torch.arange(1, S + 1, device="cuda").view(1, 1, S, 1)
+    assert (o.float() - want.expand(B, nh, S, hd)).abs().max().item() < 2e-2
+    assert torch.allclose(lse, torch.log(torch.arange(1, S + 1, device="cuda").float()).expand(B, nh, S), atol=1e-3)
+
+
+# ------------------------------------------------------------------ norms, activations, RoPE, gathers
+@pytest.mark.parametrize("name,unit", [("rms_norm", 1), ("rms_norm_affine", 0)])
+def test_rms_norm_golden_fp32(ops, golden, name, unit):
+    i, o, p = golden.case(name)
+    x, w, dy = dev(i["x"]), dev(i["w"]), dev(i["dY"])
+    y, rstd = ops.rms_norm_fwd(x, w, p["eps"], unit, out_dtype=torch.float32)
+    assert rel_err(host(y), o["y"]) < 1e-5
+    dw = torch.zeros_like(w)
+    dx = ops.rms_norm_bwd(dy, x, w, rstd, p["eps"], unit, dweight=dw)
+    assert rel_err(host(dx), o["dx"]) < 1e-5 and rel_err(host(dw), o["dw"]) < 1e-5
+
+
+def test_rms_norm_fused_residual_and_bf16(ops):
+    g = np.random.Generator(np.random.PCG64(3))
+    x, res, w = g.standard_normal((300, 1152)).astype(np.float32), g.standard_normal((300, 1152)).astype(np.float32), (g.standard_normal(1152) * 0.1).astype(np.float32)
+    y, rstd, s = ops.rms_norm_fwd(dev(rb(x), torch.bfloat16), dev(w), 1e-6, 1, out_dtype=torch.bfloat16, residual=dev(res))
+    want = R.rms_norm_fwd(rb(x), w, 1e-6, True)
+    close_bf16(host(y), want, rel=8e-3)
+    assert rel_err(host(s), want + res) < 1e-5 * 50
+
+
+def test_layer_norm_golden(ops, golden):
+    i, o, p = golden.case("layer_norm")
+    x, w, b, dy = dev(i["x"]), dev(i["w"]), dev(i["b"]), dev(i["dY"])
+    y, mean, rstd = ops.layer_norm_fwd(x, w, b, p["eps"], out_dtype=torch.float32)
+    assert rel_err(host(y), o["y"]) < 1e-5
+    dw, db = torch.zeros_like(w), torch.zeros_like(b)
+    dx = ops.layer_norm_bwd(dy, x, w, mean, rstd, dweight=dw, dbias=db)
+    assert rel_err(host(dx), o["dx"]) < 5e-5 and rel_err(host(dw), o["dw"]) < 1e-5 and rel_err(host(db), o["db"]) < 1e-5
+
+
+@pytest.mark.parametrize("name,kind", [("gelu", 0), ("swiglu", 1), ("geglu", 2)])
+def test_activations_golden(ops, golden, name, kind):
+    i, o, _ = golden.case(name)
+    bf = torch.bfloat16
+    gate = i["x"] if name == "gelu" else i["gate"]
+    up = None if name == "gelu" else i["up"]
+    g2 = dev(gate.reshape(-1, gate.shape[-1]), bf)
+    u2 = None if up is None else dev(up.reshape(-1, up.shape[-1]), bf)
+    dy = dev(i["dY"].reshape(-1, gate.shape[-1]), bf)
+    y = ops.act_fwd(kind, g2, u2)
+    dg, du = ops.act_bwd(kind, dy, g2, u2)
+    close_bf16(host(y).reshape(gate.shape), o["y"], rel=1e-2)
+    close_bf16(host(dg).reshape(gate.shape), o["dx" if name == "gelu" else "dgate"], rel=1.5e-2)
+    if up is not None:
+        close_bf16(host(du).reshape(gate.shape), o["dup"], rel=1.5e-2)
+
+
+@pytest.mark.parametrize("name", ["rope_1e4", "rope_1e6"])
+def test_rope_golden_and_table_bits(ops, golden, name):
+    i, o, p = golden.case(name)
+    B, H, S, hd = i["x"].shape
+    cos, sin = ops.rope_tables(S, hd, p["rope_theta"], "cuda")
+    rc, rs = R.rope_tables(S, hd, p["rope_theta"])
+    # angles are computed on the host with the reference's own float expression
+    assert np.abs(host(cos) - rc).max() < 1e-6 and np.abs(host(sin) - rs).max() < 1e-6
+    x = dev(np.ascontiguousarray(i["x"].transpose(0, 2, 1, 3)).reshape(B * S, H * hd), torch.bfloat16)
+    y, _ = ops.headnorm_rope_fwd(x, S, H, hd, cos, sin)
+    close_bf16(host(y).reshape(B, S, H, hd).transpose(0, 2, 1, 3), o["y"], rel=1e-2)
+    dy = dev(np.ascontiguousarray(i["dY"].transpose(0, 2, 1, 3)).reshape(B * S, H * hd), torch.bfloat16)
+    dx = ops.headnorm_rope_bwd(dy, None, S, H, hd, cos, sin)
+    close_bf16(host(dx).reshape(B, S, H, hd).transpose(0, 2, 1, 3), o["dx"], rel=1e-2)
+
+
+def test_headnorm_rope_matches_norm_then_rope(ops):
+    """Gemma applies rms_norm(1+w) per head, then RoPE (gemma_model.cpp:459-482)."""
+    g = np.random.Generator(np.random.PCG64(9))
+    B, S, H, hd = 2, 50, 4, 256
+    x = rb(g.standard_normal((B, H, S, hd)))
+    w = (g.standard_normal(hd) * 0.1).astype(np.float32)
+    dy = rb(g.standard_normal((B, H, S, hd)))
+    want = R.rope_fwd(R.rms_norm_fwd(x, w, 1e-6, True), 10000.0)
+    want_dx, _ = R.rms_norm_bwd(R.rope_bwd(dy, 10000.0), x, w, 1e-6, True)
+    cos, sin = ops.rope_tables(S, hd, 10000.0, "cuda")
+    xt = dev(np.ascontiguousarray(x.transpose(0, 2, 1, 3)).reshape(B * S, H * hd), torch.bfloat16)
+    y, rstd = ops.headnorm_rope_fwd(xt, S, H, hd, cos, sin, norm_weight=dev(w), eps=1e-6)
+    close_bf16(host(y).reshape(B, S, H, hd).transpose(0, 2, 1, 3), want, rel=1e-2)
+    dyt = dev(np.ascontiguousarray(dy.transpose(0, 2, 1, 3)).reshape(B * S, H * hd), torch.bfloat16)
+    dx = ops.headnorm_rope_bwd(dyt, xt, S, H, hd, cos, sin, norm_weight=dev(w), rstd=rstd)
+    close_bf16(host(dx).reshape(B, S, H, hd).transpose(0, 2, 1, 3), want_dx, rel=1.5e-2)
+
+
+def test_repeat_kv_bit_exact(ops, golden):
+    i, o, p = golden.case("repeat_kv")
+    rep = int(p["repeat"])
+    assert np.array_equal(host(ops.repeat_kv(dev(i["x"]), rep)), o["y"])
+    assert rel_err(host(ops.repeat_kv_bwd(dev(i["dY"]), rep)), o["dx"]) < 1e-6
+
+
+def test_embedding_gather_bit_exact(ops):
+    g = np.random.Generator(np.random.PCG64(21))
+    V, H, B, S = 1000, 640, 3, 17
+    table = rb(g.standard_normal((V, H)) * 0.02)
+    ids = g.integers(0, V, size=(B, S)).astype(np.int32)
+    got = host(ops.embedding_gather(dev(ids), dev(table, torch.bfloat16), 1.0))
+    assert np.array_equal(got, table[ids.ravel()])             # pure gather: exact bits
+    scale = np.float32(np.sqrt(np.float32(H)))
+    got = host(ops.embedding_gather(dev(ids), dev(table, torch.bfloat16), float(scale)))
+    assert np.array_equal(got, table[ids.ravel()] * scale)
+    pos = rb(g.standard_normal((32, H)) * 0.02)
+    got = host(ops.embedding_gather(dev(ids), dev(table, torch.bfloat16), 1.0, dev(pos, torch.bfloat16), S))
+    assert np.array_equal(got.reshape(B, S, H), table[ids] + pos[:S][None])
+    ids[1, 2] = V
+    with pytest.raises(IndexError):
+        ops.embedding_gather(dev(ids), dev(table, torch.bfloat16), 1.0)
+
+
+# ------------------------------------------------------------------ loss
+def test_lm_head_ce_golden(ops, golden):
+    i, o, _ = golden.case("lm_head_ce")
+    ce = ops.LmHeadCE(dev(i["W"], torch.bfloat16))
+    hid = dev(i["hidden"], torch.bfloat16)
+    labels = dev(i["labels"])
+    loss = ce.forward(hid, labels)
+    assert int(ce.n_valid.item()) == int((i["labels"][:, 1:] != -100).sum())   # integer work: exact
+    assert abs(loss.item() - o["loss"][0]) <= 2e-3 * abs(o["loss"][0])
+    dh = ce.backward(hid, labels)
+    close_bf16(host(dh), o["dhidden"])
+    assert ops.device_status() == 0
+
+
+def test_lm_head_ce_large_vocab_vs_restatement(ops):
+    g = np.random.Generator(np.random.PCG64(31))
+    B, S, H, V = 2, 70, 640, 20000          # several vocabulary panels, ragged last tile
+    hid = rb(g.standard_normal((B, S, H)))
+    W = rb(g.standard_normal((V, H)) * 0.05)
+    labels = g.integers(0, V, size=(B, S)).astype(np.int32)
+    labels[0, 5:9] = -100
+    want_loss, want_dh = R.lm_head_ce(hid, W, labels)
+    ce = ops.LmHeadCE(dev(W, torch.bfloat16))
+    loss = ce.forward(dev(hid, torch.bfloat16), dev(labels))
+    assert abs(loss.item() - want_loss) <= 2e-3 * abs(want_loss)
+    dh = host(ce.backward(dev(hid, torch.bfloat16), dev(labels)))
+    close_bf16(dh, want_dh)
+    assert np.all(dh[:, -1, :] == 0) and np.all(dh[0, 4:8, :] == 0)    # unscored rows get exactly zero
+
+
+def test_lm_ce_all_ignored_and_out_of_range(ops, golden):
+    i, o, _ = golden.case("lm_ce_all_ignored")
+    ce = ops.LmHeadCE(dev(i["W"], torch.bfloat16))
+    hid, labels = dev(i["hidden"], torch.bfloat16), dev(i["labels"])
+    assert np.isnan(ce.forward(hid, labels).item()) and np.isnan(o["loss"][0])
+    assert np.all(host(ce.backward(hid, labels)) == 0)
+    bad = i["labels"].copy(); bad[0, 3] = i["W"].shape[0]
+    with pytest.raises(IndexError):
+        ce.forward(hid, dev(bad))
+
+
+def test_ce_dense_golden(ops, golden):
+    i, o, _ = golden.case("lm_ce")
+    loss, dlogits = ops.ce_dense(dev(i["logits"]), dev(i["labels"]))
+    assert abs(loss.item() - o["loss"][0]) < 1e-5 * abs(o["loss"][0])
+    assert rel_err(host(dlogits), o["dlogits"]) < 1e-5
+
+
+# ------------------------------------------------------------------ optimizer
+@pytest.mark.parametrize("name", ["adam_clip", "adam_wd"])
+def test_adam_golden(ops, golden, name):
+    i, o, p = golden.case(name)
+    params = dev(i["p"].ravel().copy())
+    m, v = torch.zeros_like(params), torch.zeros_like(params)
+    for step in range(int(p["steps"])):
+        grads = dev(i[f"g{step}"].ravel().copy())
+        ops.adam_step(params, grads, m, v, step + 1, p["lr"], weight_decay=p.get("weight_decay", 0.0),
+                      max_norm=p.get("max_grad_norm", 0.0), clip_eps=0.0, zero_grad=True)
+        assert float(grads.abs().max()) == 0.0
+    assert rel_err(host(params), o["p"].ravel()) < 2e-6
