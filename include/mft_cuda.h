@@ -78,6 +78,9 @@ int32_t mft_transpose_f32_to_bf16(const float* src, void* dst_bf16, int64_t rows
                                   mft_stream_t stream);
 int32_t mft_transpose_bf16(const void* src_bf16, void* dst_bf16, int64_t rows, int64_t cols,
                            mft_stream_t stream);
+/* Same with a padded destination: dst[c * dst_ld + r] = src[r, c], dst_ld >= rows. */
+int32_t mft_transpose_bf16_ld(const void* src_bf16, void* dst_bf16, int64_t rows, int64_t cols,
+                              int64_t dst_ld, mft_stream_t stream);
 
 /* ---- embedding gather
  *      (GPT2Model::embedding_lookup gpt2_model.cpp:464-492 + positions :349-369,

@@ -1,0 +1,110 @@
+/*
+ * mft_step.h - C ABI of the LoRA fine-tuning step engine in libmft_cuda.so.
+ *
+ * The engine is the device-side counterpart of the reference's model graphs and
+ * step driver: GPT2Model / QwenModel / GemmaModel ::forward
+ * (operator/finetune_ops/graph/gpt2_model.cpp:320-406, qwen_model.cpp:335-394,
+ * gemma_model.cpp:579-646), lm_cross_entropy + Tensor::backward
+ * (core/lm_loss.cpp:268-382, core/autograd_engine.cpp:144-273) and
+ * Optimizer::clip_grad_norm + Adam::step + zero_grad
+ * (optim/auto_trainer.cpp:20-46).  It schedules the kernels of mft_cuda.h on one
+ * stream over preallocated activations; nothing here runs on the CPU.
+ *
+ * Parameter order and layouts are the reference's: mft_model_param_* walks
+ * XModel::parameters(), mft_model_lora_* walks get_lora_parameters() (A then B
+ * per LoRA'd linear; GPT-2/Qwen A[in,r], B[r,out]; Gemma A[r,in], B[out,r]).
+ * Host-side values are fp32; frozen weights are rounded to bf16 on upload.
+ */
+#ifndef MFT_STEP_H
+#define MFT_STEP_H
+
+#include <stdint.h>
+
+#include "mft_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MFT_FAMILY_GPT2 0
+#define MFT_FAMILY_QWEN 1
+#define MFT_FAMILY_GEMMA 2
+
+/* LoRA target bits.  GPT-2: c_attn, c_proj, c_fc, mlp_c_proj reuse Q, O, GATE, DOWN. */
+#define MFT_LORA_Q 1
+#define MFT_LORA_K 2
+#define MFT_LORA_V 4
+#define MFT_LORA_O 8
+#define MFT_LORA_GATE 16
+#define MFT_LORA_UP 32
+#define MFT_LORA_DOWN 64
+
+typedef struct {
+    int32_t family;
+    int32_t vocab, hidden, inter, layers, n_heads, n_kv_heads, head_dim;
+    int32_t n_positions;        /* GPT-2 learned positions */
+    float norm_eps;
+    float rope_theta;           /* Qwen; Gemma global layers */
+    float rope_local_theta;     /* Gemma sliding layers */
+    float attn_scale;           /* 1/sqrt(head_dim), or query_pre_attn_scalar^-0.5 for Gemma */
+    int32_t sliding_window;     /* Gemma: keys i-j < window on sliding layers */
+    int32_t global_every;       /* Gemma: layer i is global iff (i+1) % global_every == 0; 0 = all sliding */
+    int32_t lora_rank;
+    float lora_alpha;
+    uint32_t lora_targets;
+    int32_t gpt2_detach_attn;   /* 1 = reproduce the reference: no gradient through GPT-2 attention */
+    int32_t max_batch, max_seq;
+} mft_model_config_t;
+
+typedef struct mft_model mft_model_t;
+
+int32_t mft_model_create(const mft_model_config_t* cfg, mft_stream_t stream, mft_model_t** out);
+int32_t mft_model_destroy(mft_model_t* m);
+
+/* Frozen parameters, in XModel::parameters() order. */
+int32_t mft_model_param_count(const mft_model_t* m);
+int32_t mft_model_param_shape(const mft_model_t* m, int32_t idx, int64_t* rows, int64_t* cols);
+int32_t mft_model_set_param_host(mft_model_t* m, int32_t idx, const float* data_host);
+/* Same, from a device f32 buffer (weights generated on the device). */
+int32_t mft_model_set_param_dev(mft_model_t* m, int32_t idx, const float* data_dev);
+
+/* Trainable LoRA tensors, in get_lora_parameters() order. */
+int32_t mft_model_lora_count(const mft_model_t* m);
+int32_t mft_model_lora_shape(const mft_model_t* m, int32_t idx, int64_t* rows, int64_t* cols);
+int32_t mft_model_set_lora_host(mft_model_t* m, int32_t idx, const float* data_host);
+int32_t mft_model_get_lora_host(mft_model_t* m, int32_t idx, float* data_host);
+int32_t mft_model_get_lora_grad_host(mft_model_t* m, int32_t idx, float* data_host);
+/* 1 if the reference's graph delivers a gradient to this tensor (GPT-2 c_attn does not). */
+int32_t mft_model_lora_has_grad(const mft_model_t* m, int32_t idx);
+/* The flat f32 buckets every LoRA tensor lives in (params, grads): what a
+ * data-parallel caller all-reduces between backward and the optimizer. */
+int32_t mft_model_buckets(mft_model_t* m, float** params_dev, float** grads_dev, int64_t* n);
+
+/* forward + shifted cross-entropy + backward for one batch.  ids / labels are
+ * int32 [batch, seq] HOST buffers (pinned for overlap); they are copied to the
+ * device inside the call.  Gradients are ACCUMULATED into the grad bucket.
+ * n_valid_global > 0 overrides the local count of scored tokens in the 1/n
+ * coefficient (data parallel).  loss_host receives the local mean loss. */
+int32_t mft_model_forward_backward(mft_model_t* m, const int32_t* ids_host, const int32_t* labels_host,
+                                   int32_t batch, int32_t seq, int64_t n_valid_global,
+                                   float* loss_host, int32_t* n_valid_host);
+/* Same with ids/labels already in device memory; the loss stays on the device
+ * (loss_dev, n_valid_dev may be read later) and nothing synchronises. */
+int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t* ids_dev, const int32_t* labels_dev,
+                                       int32_t batch, int32_t seq, int64_t n_valid_global,
+                                       float** loss_dev, int32_t** n_valid_dev);
+/* Forward only: mean loss for a batch (evaluation). */
+int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_host, const int32_t* labels_host,
+                               int32_t batch, int32_t seq, float* loss_host);
+/* clip (max_norm <= 0: none; clip_eps 0 = Optimizer::clip_grad_norm, 1e-6 = trainers) + Adam + zero_grad. */
+int32_t mft_model_optimizer_step(mft_model_t* m, float lr, float beta1, float beta2, float eps,
+                                 float weight_decay, float max_norm, float clip_eps);
+int32_t mft_model_zero_grad(mft_model_t* m);
+/* Debug/parity taps: copy the final hidden states (f32 [batch*seq, hidden], after the last norm). */
+int32_t mft_model_get_final_hidden_host(mft_model_t* m, float* out_host, int64_t n_elements);
+int64_t mft_model_activation_bytes(const mft_model_t* m);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MFT_STEP_H */

@@ -28,6 +28,17 @@ class BlockCopy(C.Structure):
                 ("src_ld", C.c_int32), ("dst_ld", C.c_int32), ("transpose", C.c_int32), ("pad", C.c_int32)]
 
 
+class ModelConfig(C.Structure):
+    """mft_model_config_t of include/mft_step.h."""
+    _fields_ = [("family", C.c_int32), ("vocab", C.c_int32), ("hidden", C.c_int32), ("inter", C.c_int32),
+                ("layers", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("n_positions", C.c_int32), ("norm_eps", C.c_float), ("rope_theta", C.c_float),
+                ("rope_local_theta", C.c_float), ("attn_scale", C.c_float), ("sliding_window", C.c_int32),
+                ("global_every", C.c_int32), ("lora_rank", C.c_int32), ("lora_alpha", C.c_float),
+                ("lora_targets", C.c_uint32), ("gpt2_detach_attn", C.c_int32), ("max_batch", C.c_int32),
+                ("max_seq", C.c_int32)]
+
+
 _lib = None
 
 i32, i64, f32, vp, sz = C.c_int32, C.c_int64, C.c_float, C.c_void_p, C.c_size_t
@@ -51,6 +62,7 @@ _SIGS = {
     "mft_cast_bf16_to_f32": [vp, vp, i64, vp],
     "mft_transpose_f32_to_bf16": [vp, vp, i64, i64, vp],
     "mft_transpose_bf16": [vp, vp, i64, i64, vp],
+    "mft_transpose_bf16_ld": [vp, vp, i64, i64, i64, vp],
     "mft_embedding_gather": [vp, vp, vp, vp, i64, i64, i64, i64, f32, vp, vp],
     "mft_rmsnorm_fwd": [vp, i32, vp, f32, i32, vp, i32, vp, vp, vp, i64, i64, vp],
     "mft_rmsnorm_bwd": [vp, i32, vp, i32, vp, vp, f32, i32, vp, i32, i32, vp, i64, i64, vp],
@@ -79,10 +91,33 @@ _SIGS = {
     "mft_ce_dense_fwd": [vp, vp, i64, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp],
     "mft_ce_dense_bwd": [vp, vp, i64, i64, i64, vp, vp, f32, vp, vp],
     "mft_grad_sqnorm": [vp, i64, vp, vp],
+    # ---- include/mft_step.h
+    "mft_model_create": [C.POINTER(ModelConfig), vp, C.POINTER(vp)],
+    "mft_model_destroy": [vp],
+    "mft_model_param_count": [vp],
+    "mft_model_param_shape": [vp, i32, C.POINTER(i64), C.POINTER(i64)],
+    "mft_model_set_param_host": [vp, i32, vp],
+    "mft_model_set_param_dev": [vp, i32, vp],
+    "mft_model_lora_count": [vp],
+    "mft_model_lora_shape": [vp, i32, C.POINTER(i64), C.POINTER(i64)],
+    "mft_model_set_lora_host": [vp, i32, vp],
+    "mft_model_get_lora_host": [vp, i32, vp],
+    "mft_model_get_lora_grad_host": [vp, i32, vp],
+    "mft_model_lora_has_grad": [vp, i32],
+    "mft_model_buckets": [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(i64)],
+    "mft_model_forward_backward": [vp, vp, vp, i32, i32, i64, C.POINTER(f32), C.POINTER(i32)],
+    "mft_model_forward_backward_dev": [vp, vp, vp, i32, i32, i64, C.POINTER(vp), C.POINTER(vp)],
+    "mft_model_forward_loss": [vp, vp, vp, i32, i32, C.POINTER(f32)],
+    "mft_model_optimizer_step": [vp, f32, f32, f32, f32, f32, f32, f32],
+    "mft_model_zero_grad": [vp],
+    "mft_model_get_final_hidden_host": [vp, vp, i64],
+    "mft_model_activation_bytes": [vp],
     "mft_adam_step": [vp, vp, vp, vp, i64, i64, f32, f32, f32, f32, f32, vp, f32, f32, i32, vp],
 }
-_RET = {"mft_launch_count": i64, "mft_last_error": C.c_char_p, "mft_lmhead_ce_workspace_bytes": i64}
-_NO_STATUS = {"mft_version", "mft_lmhead_ce_workspace_bytes"}
+_RET = {"mft_launch_count": i64, "mft_last_error": C.c_char_p, "mft_lmhead_ce_workspace_bytes": i64,
+        "mft_model_activation_bytes": i64}
+_NO_STATUS = {"mft_version", "mft_lmhead_ce_workspace_bytes", "mft_model_param_count", "mft_model_lora_count",
+              "mft_model_lora_has_grad"}
 
 
 def exported_names() -> list[str]:

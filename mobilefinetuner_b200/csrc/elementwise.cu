@@ -38,7 +38,7 @@ __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, floa
 // dst[c, r] = (bf16) src[r, c]; 32x32 tiles through padded shared memory.
 template <typename TS>
 __global__ void transpose_to_bf16_kernel(const TS* __restrict__ src, __nv_bfloat16* __restrict__ dst,
-                                         int64_t rows, int64_t cols) {
+                                         int64_t rows, int64_t cols, int64_t dst_ld) {
     __shared__ float tile[32][33];
     const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
     for (int j = threadIdx.y; j < 32; j += blockDim.y) {
@@ -53,7 +53,7 @@ __global__ void transpose_to_bf16_kernel(const TS* __restrict__ src, __nv_bfloat
     __syncthreads();
     for (int j = threadIdx.y; j < 32; j += blockDim.y) {
         int64_t c = c0 + j, r = r0 + threadIdx.x;
-        if (r < rows && c < cols) dst[c * rows + r] = f32_to_bf16(tile[threadIdx.x][j]);
+        if (r < rows && c < cols) dst[c * dst_ld + r] = f32_to_bf16(tile[threadIdx.x][j]);
     }
 }
 
@@ -260,15 +260,18 @@ int32_t mft_transpose_f32_to_bf16(const float* src, void* dst, int64_t rows, int
     MFT_CHECK_ARG(src && dst && rows > 0 && cols > 0, "mft_transpose_f32_to_bf16: bad argument");
     dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
     MFT_CHECK_ARG(grid.y <= 65535, "mft_transpose_f32_to_bf16: too many rows");
-    transpose_to_bf16_kernel<float><<<grid, dim3(32, 8), 0, as_stream(stream)>>>(src, (__nv_bfloat16*)dst, rows, cols);
+    transpose_to_bf16_kernel<float><<<grid, dim3(32, 8), 0, as_stream(stream)>>>(src, (__nv_bfloat16*)dst, rows, cols, rows);
     MFT_LAUNCH_CHECK("transpose_f32_bf16");
     return MFT_OK;
 }
 int32_t mft_transpose_bf16(const void* src, void* dst, int64_t rows, int64_t cols, mft_stream_t stream) {
-    MFT_CHECK_ARG(src && dst && rows > 0 && cols > 0, "mft_transpose_bf16: bad argument");
+    return mft_transpose_bf16_ld(src, dst, rows, cols, rows, stream);
+}
+int32_t mft_transpose_bf16_ld(const void* src, void* dst, int64_t rows, int64_t cols, int64_t dst_ld, mft_stream_t stream) {
+    MFT_CHECK_ARG(src && dst && rows > 0 && cols > 0 && dst_ld >= rows, "mft_transpose_bf16_ld: bad argument");
     dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
-    MFT_CHECK_ARG(grid.y <= 65535, "mft_transpose_bf16: too many rows");
-    transpose_to_bf16_kernel<__nv_bfloat16><<<grid, dim3(32, 8), 0, as_stream(stream)>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, rows, cols);
+    MFT_CHECK_ARG(grid.y <= 65535, "mft_transpose_bf16_ld: too many rows");
+    transpose_to_bf16_kernel<__nv_bfloat16><<<grid, dim3(32, 8), 0, as_stream(stream)>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, rows, cols, dst_ld);
     MFT_LAUNCH_CHECK("transpose_bf16");
     return MFT_OK;
 }

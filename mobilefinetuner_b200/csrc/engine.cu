@@ -1,0 +1,472 @@
+// Step engine: builds the device-resident model (frozen bf16 weights in both
+// GEMM layouts, fp32 LoRA buckets, per-layer activation buffers) and runs the
+// LoRA fine-tuning step as a fixed sequence of kernels from mft_cuda.h.
+// Model construction and parameter upload live in this file; the forward and
+// backward schedules are in engine_step.cu.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "common.cuh"
+#include "engine.h"
+
+using namespace mft;
+
+namespace {
+
+#define TRY(expr)                         \
+    do {                                  \
+        int32_t s__ = (expr);             \
+        if (s__ != MFT_OK) return s__;    \
+    } while (0)
+
+template <typename T>
+int32_t dalloc(mft_model* m, T** out, int64_t n, bool zero = false, bool activation = false) {
+    void* p = nullptr;
+    const size_t bytes = (size_t)std::max<int64_t>(n, 1) * sizeof(T);
+    TRY(mft_malloc(bytes, &p));
+    m->allocations.push_back(p);
+    if (zero) TRY(mft_memset(p, 0, bytes, m->stream));
+    if (activation) m->activation_bytes += (int64_t)bytes;
+    *out = static_cast<T*>(p);
+    return MFT_OK;
+}
+
+int32_t build_group(mft_model* m, LinearGroup& g, int in, const std::vector<int>& outs, const std::vector<bool>& lora,
+                    bool with_bias, int rank) {
+    g.in = in;
+    g.n_total = 0;
+    g.slots.clear();
+    int panel = 0;
+    for (size_t i = 0; i < outs.size(); ++i) {
+        LinearSlot s;
+        s.in = in; s.out = outs[i]; s.col0 = g.n_total; s.has_lora = lora[i];
+        if (s.has_lora) { s.panel_col = panel; panel += rank; g.any_lora = true; }
+        g.n_total += outs[i];
+        g.slots.push_back(s);
+    }
+    if (panel > 64) return fail(MFT_ERR_UNSUPPORTED, "LoRA rank x fused linears exceeds the 64-column panel");
+    g.k2 = panel;
+    TRY(dalloc(m, &g.w_nk, (int64_t)g.n_total * in));
+    TRY(dalloc(m, &g.w_kn, (int64_t)in * g.n_total));
+    if (with_bias) TRY(dalloc(m, &g.bias, g.n_total, true));
+    if (g.any_lora) {
+        TRY(dalloc(m, &g.a_nk, (int64_t)64 * in, true));
+        TRY(dalloc(m, &g.a_kn, (int64_t)in * 64, true));
+        TRY(dalloc(m, &g.b_nk, (int64_t)g.n_total * 64, true));
+        TRY(dalloc(m, &g.b_kn, (int64_t)64 * g.n_total, true));
+    }
+    return MFT_OK;
+}
+
+void add_param(mft_model* m, const std::string& name, int64_t rows, int64_t cols, ParamInfo::Kind kind, float* f32_dst = nullptr,
+               LinearGroup* g = nullptr, int slot = 0) {
+    ParamInfo p;
+    p.name = name; p.rows = rows; p.cols = cols; p.kind = kind; p.f32_dst = f32_dst; p.group = g; p.slot = slot;
+    m->params.push_back(p);
+}
+
+// Registers A and B of one LoRA'd slot in the reference's order and layout.
+void add_lora(mft_model* m, LinearSlot& s, int rank, bool peft_layout, bool has_grad) {
+    s.lora_idx = (int)m->loras.size();
+    LoraInfo a, b;
+    if (peft_layout) { a.rows = rank; a.cols = s.in; b.rows = s.out; b.cols = rank; }
+    else { a.rows = s.in; a.cols = rank; b.rows = rank; b.cols = s.out; }
+    a.has_grad = b.has_grad = has_grad;
+    a.offset = m->bucket_n; m->bucket_n += a.rows * a.cols;
+    m->bucket_n = (m->bucket_n + 3) / 4 * 4;     // keep every tensor 16-byte aligned
+    b.offset = m->bucket_n; m->bucket_n += b.rows * b.cols;
+    m->bucket_n = (m->bucket_n + 3) / 4 * 4;
+    m->loras.push_back(a);
+    m->loras.push_back(b);
+}
+
+}  // namespace
+
+extern "C" int32_t mft_model_destroy(mft_model_t* m) {
+    if (!m) return MFT_OK;
+    cudaStreamSynchronize(m->stream);
+    for (void* p : m->allocations) mft_free(p);
+    delete m;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_model_create(const mft_model_config_t* cfg, mft_stream_t stream, mft_model_t** out) {
+    MFT_CHECK_ARG(cfg && out, "mft_model_create: null argument");
+    MFT_CHECK_ARG(cfg->family >= 0 && cfg->family <= 2, "mft_model_create: unknown family");
+    MFT_CHECK_ARG(cfg->vocab > 0 && cfg->hidden > 0 && cfg->inter > 0 && cfg->layers > 0 && cfg->n_heads > 0 &&
+                  cfg->n_kv_heads > 0 && cfg->head_dim > 0 && cfg->max_batch > 0 && cfg->max_seq > 0, "mft_model_create: bad size");
+    MFT_CHECK_ARG(cfg->hidden % 8 == 0 && cfg->inter % 8 == 0, "mft_model_create: hidden and inter must be multiples of 8");
+    MFT_CHECK_ARG(cfg->n_heads % cfg->n_kv_heads == 0, "mft_model_create: n_heads must be a multiple of n_kv_heads");
+    MFT_CHECK_ARG(cfg->head_dim == 64 || cfg->head_dim == 128 || cfg->head_dim == 256, "mft_model_create: head_dim must be 64, 128 or 256");
+    MFT_CHECK_ARG(cfg->lora_rank >= 0 && cfg->lora_rank <= 64 && cfg->lora_rank % 8 == 0, "mft_model_create: LoRA rank must be a multiple of 8, at most 64");
+    if (!device_status_word()) return fail(MFT_ERR_INVALID_ARG, "mft_model_create: call mft_init first");
+    const bool gpt2 = cfg->family == MFT_FAMILY_GPT2, qwen = cfg->family == MFT_FAMILY_QWEN, gemma = cfg->family == MFT_FAMILY_GEMMA;
+    MFT_CHECK_ARG(!gpt2 || (cfg->n_heads == cfg->n_kv_heads && cfg->n_heads * cfg->head_dim == cfg->hidden && cfg->n_positions >= cfg->max_seq),
+                  "mft_model_create: inconsistent GPT-2 geometry");
+    auto* m = new mft_model();
+    m->cfg = *cfg;
+    m->stream = as_stream(stream);
+    m->max_tokens = (int64_t)cfg->max_batch * cfg->max_seq;
+    const int H = cfg->hidden, I = cfg->inter, V = cfg->vocab, L = cfg->layers;
+    const int nh = cfg->n_heads, nkv = cfg->n_kv_heads, hd = cfg->head_dim, r = cfg->lora_rank;
+    const int QD = nh * hd, KD = nkv * hd;
+    const uint32_t tg = r > 0 ? cfg->lora_targets : 0;
+    const int64_t T = m->max_tokens;
+    int32_t st = MFT_OK;
+    auto guard = [&](int32_t s) { if (s != MFT_OK && st == MFT_OK) st = s; return s == MFT_OK; };
+#define G(expr) if (!guard(expr)) { mft_model_destroy(m); return st; }
+
+    G(dalloc(m, &m->embed, (int64_t)V * H));
+    m->ld_t = ((int64_t)V + 63) / 64 * 64;
+    G(dalloc(m, &m->embed_t, (int64_t)H * m->ld_t, true));
+    G(dalloc(m, &m->final_w, H, true));
+    if (gpt2) {
+        G(dalloc(m, &m->final_b, H, true));
+        G(dalloc(m, &m->pos_embed, (int64_t)cfg->n_positions * H));
+    }
+    m->layers.resize(L);
+    m->bufs.resize(L);
+
+    // ---- frozen parameters in the reference's parameters() order
+    if (gpt2) {
+        add_param(m, "wte", V, H, ParamInfo::EMBED);
+        add_param(m, "wpe", cfg->n_positions, H, ParamInfo::POS_EMBED);
+    } else if (qwen) {
+        add_param(m, "embed_tokens", V, H, ParamInfo::EMBED);
+        add_param(m, "final_norm", 1, H, ParamInfo::NORM, m->final_w);
+    } else {
+        add_param(m, "embed_tokens", V, H, ParamInfo::EMBED);
+        add_param(m, "norm", 1, H, ParamInfo::NORM, m->final_w);
+        add_param(m, "lm_head(copy of embed^T)", H, V, ParamInfo::LM_HEAD_COPY);
+    }
+    for (int l = 0; l < L; ++l) {
+        LayerWeights& w = m->layers[l];
+        const std::string pre = "layer" + std::to_string(l) + ".";
+        G(dalloc(m, &w.ln1_w, H, true));
+        G(dalloc(m, &w.ln2_w, H, true));
+        if (gpt2) {
+            G(dalloc(m, &w.ln1_b, H, true));
+            G(dalloc(m, &w.ln2_b, H, true));
+            G(build_group(m, w.qkv, H, {3 * H}, {(tg & MFT_LORA_Q) != 0}, true, r));
+            G(build_group(m, w.o, H, {H}, {(tg & MFT_LORA_O) != 0}, true, r));
+            G(build_group(m, w.gu, H, {I}, {(tg & MFT_LORA_GATE) != 0}, true, r));
+            G(build_group(m, w.down, I, {H}, {(tg & MFT_LORA_DOWN) != 0}, true, r));
+            add_param(m, pre + "ln_1.weight", 1, H, ParamInfo::NORM, w.ln1_w);
+            add_param(m, pre + "ln_1.bias", 1, H, ParamInfo::NORM, w.ln1_b);
+            add_param(m, pre + "attn.c_attn.weight", H, 3 * H, ParamInfo::LINEAR, nullptr, &w.qkv, 0);
+            add_param(m, pre + "attn.c_attn.bias", 1, 3 * H, ParamInfo::BIAS, nullptr, &w.qkv, 0);
+            add_param(m, pre + "attn.c_proj.weight", H, H, ParamInfo::LINEAR, nullptr, &w.o, 0);
+            add_param(m, pre + "attn.c_proj.bias", 1, H, ParamInfo::BIAS, nullptr, &w.o, 0);
+            add_param(m, pre + "ln_2.weight", 1, H, ParamInfo::NORM, w.ln2_w);
+            add_param(m, pre + "ln_2.bias", 1, H, ParamInfo::NORM, w.ln2_b);
+            add_param(m, pre + "mlp.c_fc.weight", H, I, ParamInfo::LINEAR, nullptr, &w.gu, 0);
+            add_param(m, pre + "mlp.c_fc.bias", 1, I, ParamInfo::BIAS, nullptr, &w.gu, 0);
+            add_param(m, pre + "mlp.c_proj.weight", I, H, ParamInfo::LINEAR, nullptr, &w.down, 0);
+            add_param(m, pre + "mlp.c_proj.bias", 1, H, ParamInfo::BIAS, nullptr, &w.down, 0);
+        } else if (qwen) {
+            G(build_group(m, w.qkv, H, {QD, KD, KD}, {(tg & MFT_LORA_Q) != 0, (tg & MFT_LORA_K) != 0, (tg & MFT_LORA_V) != 0}, true, r));
+            G(build_group(m, w.o, QD, {H}, {(tg & MFT_LORA_O) != 0}, false, r));
+            G(build_group(m, w.gu, H, {I, I}, {false, false}, false, r));
+            G(build_group(m, w.down, I, {H}, {false}, false, r));
+            add_param(m, pre + "input_layernorm", 1, H, ParamInfo::NORM, w.ln1_w);
+            add_param(m, pre + "post_attention_layernorm", 1, H, ParamInfo::NORM, w.ln2_w);
+            add_param(m, pre + "q_proj.weight", H, QD, ParamInfo::LINEAR, nullptr, &w.qkv, 0);
+            add_param(m, pre + "q_proj.bias", 1, QD, ParamInfo::BIAS, nullptr, &w.qkv, 0);
+            add_param(m, pre + "k_proj.weight", H, KD, ParamInfo::LINEAR, nullptr, &w.qkv, 1);
+            add_param(m, pre + "k_proj.bias", 1, KD, ParamInfo::BIAS, nullptr, &w.qkv, 1);
+            add_param(m, pre + "v_proj.weight", H, KD, ParamInfo::LINEAR, nullptr, &w.qkv, 2);
+            add_param(m, pre + "v_proj.bias", 1, KD, ParamInfo::BIAS, nullptr, &w.qkv, 2);
+            add_param(m, pre + "o_proj.weight", QD, H, ParamInfo::LINEAR, nullptr, &w.o, 0);
+            add_param(m, pre + "gate_proj.weight", H, I, ParamInfo::LINEAR, nullptr, &w.gu, 0);
+            add_param(m, pre + "up_proj.weight", H, I, ParamInfo::LINEAR, nullptr, &w.gu, 1);
+            add_param(m, pre + "down_proj.weight", I, H, ParamInfo::LINEAR, nullptr, &w.down, 0);
+        } else {
+            G(dalloc(m, &w.post_attn_w, H, true));
+            G(dalloc(m, &w.post_ffn_w, H, true));
+            G(dalloc(m, &w.q_norm_w, hd, true));
+            G(dalloc(m, &w.k_norm_w, hd, true));
+            w.sliding = !(cfg->global_every > 0 && (l + 1) % cfg->global_every == 0);
+            G(build_group(m, w.qkv, H, {QD, KD, KD}, {(tg & MFT_LORA_Q) != 0, (tg & MFT_LORA_K) != 0, (tg & MFT_LORA_V) != 0}, false, r));
+            G(build_group(m, w.o, QD, {H}, {(tg & MFT_LORA_O) != 0}, false, r));
+            G(build_group(m, w.gu, H, {I, I}, {(tg & MFT_LORA_GATE) != 0, (tg & MFT_LORA_UP) != 0}, false, r));
+            G(build_group(m, w.down, I, {H}, {(tg & MFT_LORA_DOWN) != 0}, false, r));
+            add_param(m, pre + "input_layernorm", 1, H, ParamInfo::NORM, w.ln1_w);
+            add_param(m, pre + "post_attention_layernorm", 1, H, ParamInfo::NORM, w.post_attn_w);
+            add_param(m, pre + "pre_feedforward_layernorm", 1, H, ParamInfo::NORM, w.ln2_w);
+            add_param(m, pre + "post_feedforward_layernorm", 1, H, ParamInfo::NORM, w.post_ffn_w);
+            add_param(m, pre + "q_proj.weight", H, QD, ParamInfo::LINEAR, nullptr, &w.qkv, 0);
+            add_param(m, pre + "k_proj.weight", H, KD, ParamInfo::LINEAR, nullptr, &w.qkv, 1);
+            add_param(m, pre + "v_proj.weight", H, KD, ParamInfo::LINEAR, nullptr, &w.qkv, 2);
+            add_param(m, pre + "o_proj.weight", QD, H, ParamInfo::LINEAR, nullptr, &w.o, 0);
+            add_param(m, pre + "q_norm", 1, hd, ParamInfo::NORM, w.q_norm_w);
+            add_param(m, pre + "k_norm", 1, hd, ParamInfo::NORM, w.k_norm_w);
+            add_param(m, pre + "gate_proj.weight", H, I, ParamInfo::LINEAR, nullptr, &w.gu, 0);
+            add_param(m, pre + "up_proj.weight", H, I, ParamInfo::LINEAR, nullptr, &w.gu, 1);
+            add_param(m, pre + "down_proj.weight", I, H, ParamInfo::LINEAR, nullptr, &w.down, 0);
+        }
+    }
+    if (gpt2) {
+        add_param(m, "ln_f.weight", 1, H, ParamInfo::NORM, m->final_w);
+        add_param(m, "ln_f.bias", 1, H, ParamInfo::NORM, m->final_b);
+    }
+
+    // ---- LoRA tensors in get_lora_parameters() order
+    for (int l = 0; l < L; ++l) {
+        LayerWeights& w = m->layers[l];
+        auto reg = [&](LinearSlot& s, bool has_grad) { if (s.has_lora) add_lora(m, s, r, gemma, has_grad); };
+        if (gpt2) {
+            reg(w.qkv.slots[0], cfg->gpt2_detach_attn == 0);   // the reference severs autograd at the QKV split
+            reg(w.o.slots[0], true); reg(w.gu.slots[0], true); reg(w.down.slots[0], true);
+        } else if (qwen) {
+            reg(w.qkv.slots[0], true); reg(w.qkv.slots[2], true); reg(w.qkv.slots[1], true); reg(w.o.slots[0], true);   // q, v, k, o
+        } else {
+            reg(w.qkv.slots[0], true); reg(w.qkv.slots[1], true); reg(w.qkv.slots[2], true); reg(w.o.slots[0], true);
+            reg(w.gu.slots[0], true); reg(w.gu.slots[1], true); reg(w.down.slots[0], true);
+        }
+    }
+    if (m->bucket_n > 0) {
+        G(dalloc(m, &m->p_bucket, m->bucket_n, true));
+        G(dalloc(m, &m->g_bucket, m->bucket_n, true));
+        G(dalloc(m, &m->m_bucket, m->bucket_n, true));
+        G(dalloc(m, &m->v_bucket, m->bucket_n, true));
+    }
+    G(dalloc(m, &m->sqnorm, 4, true));
+
+    // ---- gradient panels (one allocation) and the pack / unpack tables
+    {
+        int64_t total = 0;
+        for (auto& w : m->layers)
+            for (LinearGroup* g : {&w.qkv, &w.o, &w.gu, &w.down})
+                if (g->any_lora) total += (int64_t)g->in * 64 + (int64_t)64 * g->n_total;
+        m->grad_pan_floats = total;
+        if (total > 0) G(dalloc(m, &m->grad_pan_base, total, true));
+        int64_t off = 0;
+        std::vector<mft_block_copy_t> pack, unpack;
+        for (auto& w : m->layers)
+            for (LinearGroup* g : {&w.qkv, &w.o, &w.gu, &w.down}) {
+                if (!g->any_lora) continue;
+                g->da_pan = m->grad_pan_base + off; off += (int64_t)g->in * 64;
+                g->db_pan = m->grad_pan_base + off; off += (int64_t)64 * g->n_total;
+                for (auto& s : g->slots) {
+                    if (!s.has_lora) continue;
+                    const LoraInfo& A = m->loras[s.lora_idx];
+                    const LoraInfo& B = m->loras[s.lora_idx + 1];
+                    float* pa = m->p_bucket + A.offset; float* pb = m->p_bucket + B.offset;
+                    float* ga = m->g_bucket + A.offset; float* gb = m->g_bucket + B.offset;
+                    const int pc = s.panel_col;
+                    auto E = [](const void* src, void* dst, int rows, int cols, int sld, int dld, int tr) {
+                        mft_block_copy_t e; e.src = src; e.dst = dst; e.rows = rows; e.cols = cols; e.src_ld = sld; e.dst_ld = dld; e.transpose = tr; e.pad = 0; return e;
+                    };
+                    if (gemma) {   // A [r,in], B [out,r]
+                        pack.push_back(E(pa, g->a_nk + (int64_t)pc * g->in, r, s.in, s.in, g->in, 0));
+                        pack.push_back(E(pa, g->a_kn + pc, r, s.in, s.in, 64, 1));
+                        pack.push_back(E(pb, g->b_nk + (int64_t)s.col0 * 64 + pc, s.out, r, r, 64, 0));
+                        pack.push_back(E(pb, g->b_kn + (int64_t)pc * g->n_total + s.col0, s.out, r, r, g->n_total, 1));
+                        if (A.has_grad) {
+                            unpack.push_back(E(g->da_pan + pc, ga, s.in, r, 64, s.in, 1));                                  // [in,r] block -> [r,in]
+                            unpack.push_back(E(g->db_pan + (int64_t)pc * g->n_total + s.col0, gb, r, s.out, g->n_total, r, 1));  // [r,out] block -> [out,r]
+                        }
+                    } else {       // A [in,r], B [r,out]
+                        pack.push_back(E(pa, g->a_nk + (int64_t)pc * g->in, s.in, r, r, g->in, 1));
+                        pack.push_back(E(pa, g->a_kn + pc, s.in, r, r, 64, 0));
+                        pack.push_back(E(pb, g->b_nk + (int64_t)s.col0 * 64 + pc, r, s.out, s.out, 64, 1));
+                        pack.push_back(E(pb, g->b_kn + (int64_t)pc * g->n_total + s.col0, r, s.out, s.out, g->n_total, 0));
+                        if (A.has_grad) {
+                            unpack.push_back(E(g->da_pan + pc, ga, s.in, r, 64, r, 0));
+                            unpack.push_back(E(g->db_pan + (int64_t)pc * g->n_total + s.col0, gb, r, s.out, g->n_total, s.out, 0));
+                        }
+                    }
+                }
+            }
+        m->n_pack = (int)pack.size(); m->n_unpack = (int)unpack.size();
+        if (m->n_pack) {
+            G(dalloc(m, &m->pack_table, m->n_pack));
+            G(mft_memcpy_h2d(m->pack_table, pack.data(), pack.size() * sizeof(mft_block_copy_t), m->stream));
+        }
+        if (m->n_unpack) {
+            G(dalloc(m, &m->unpack_table, m->n_unpack));
+            G(mft_memcpy_h2d(m->unpack_table, unpack.data(), unpack.size() * sizeof(mft_block_copy_t), m->stream));
+        }
+        G(check_cuda(cudaStreamSynchronize(m->stream), "table upload"));   // the host vectors go out of scope
+    }
+
+    // ---- RoPE tables (host expression identical to the reference's)
+    if (!gpt2) {
+        const int64_t n = (int64_t)cfg->max_seq * (hd / 2);
+        std::vector<float> c(n), s(n);
+        G(dalloc(m, &m->cos_g, n)); G(dalloc(m, &m->sin_g, n));
+        G(mft_rope_table_host(c.data(), s.data(), cfg->max_seq, hd, cfg->rope_theta));
+        G(mft_memcpy_h2d(m->cos_g, c.data(), n * 4, m->stream)); G(mft_memcpy_h2d(m->sin_g, s.data(), n * 4, m->stream));
+        G(check_cuda(cudaStreamSynchronize(m->stream), "rope upload"));
+        if (gemma) {
+            G(dalloc(m, &m->cos_l, n)); G(dalloc(m, &m->sin_l, n));
+            G(mft_rope_table_host(c.data(), s.data(), cfg->max_seq, hd, cfg->rope_local_theta));
+            G(mft_memcpy_h2d(m->cos_l, c.data(), n * 4, m->stream)); G(mft_memcpy_h2d(m->sin_l, s.data(), n * 4, m->stream));
+            G(check_cuda(cudaStreamSynchronize(m->stream), "rope upload"));
+        }
+    }
+
+    // ---- activations
+    const int64_t QKV = QD + 2 * KD, GU = gpt2 ? I : 2 * I;
+    for (int l = 0; l < L; ++l) {
+        LayerBuffers& b = m->bufs[l];
+        LayerWeights& w = m->layers[l];
+        G(dalloc(m, &b.x, T * H, false, true));
+        G(dalloc(m, &b.h1, T * H, false, true));
+        G(dalloc(m, &b.rstd1, T, false, true));
+        if (gpt2) { G(dalloc(m, &b.mean1, T, false, true)); G(dalloc(m, &b.mean3, T, false, true)); }
+        G(dalloc(m, &b.qkv, T * QKV, false, true));
+        if (!gpt2) G(dalloc(m, &b.qk_r, T * (QD + KD), false, true));
+        if (gemma) { G(dalloc(m, &b.rstd_q, T * nh, false, true)); G(dalloc(m, &b.rstd_k, T * nkv, false, true)); }
+        G(dalloc(m, &b.o, T * QD, false, true));
+        G(dalloc(m, &b.lse, T * nh, false, true));
+        G(dalloc(m, &b.attn_out, T * H, false, true));
+        G(dalloc(m, &b.x_mid, T * H, false, true));
+        G(dalloc(m, &b.h2, T * H, false, true));
+        G(dalloc(m, &b.rstd3, T, false, true));
+        G(dalloc(m, &b.gu, T * GU, false, true));
+        G(dalloc(m, &b.act, T * I, false, true));
+        G(dalloc(m, &b.mlp_out, T * H, false, true));
+        if (gemma) { G(dalloc(m, &b.rstd2, T, false, true)); G(dalloc(m, &b.rstd4, T, false, true)); }
+        if (w.qkv.any_lora) G(dalloc(m, &b.xa_qkv, T * 64, false, true));
+        if (w.o.any_lora) G(dalloc(m, &b.xa_o, T * 64, false, true));
+        if (w.gu.any_lora) G(dalloc(m, &b.xa_gu, T * 64, false, true));
+        if (w.down.any_lora) G(dalloc(m, &b.xa_d, T * 64, false, true));
+    }
+    G(dalloc(m, &m->ids, T)); G(dalloc(m, &m->labels, T));
+    G(dalloc(m, &m->x_final, T * H, false, true));
+    G(dalloc(m, &m->hf, T * H, false, true));
+    G(dalloc(m, &m->rstd_f, T)); G(dalloc(m, &m->mean_f, T));
+    G(dalloc(m, &m->dx, T * H, false, true));
+    G(dalloc(m, &m->t_h, T * H, false, true));
+    G(dalloc(m, &m->t_i, T * I, false, true));
+    G(dalloc(m, &m->t_gu, T * GU, false, true));
+    G(dalloc(m, &m->t_o, T * QD, false, true));
+    G(dalloc(m, &m->t_qk, T * (QD + KD), false, true));
+    G(dalloc(m, &m->t_qkv, T * QKV, false, true));
+    G(dalloc(m, &m->t_pan, T * 64, false, true));
+    G(dalloc(m, &m->attn_delta, T * nh, false, true));
+    G(dalloc(m, &m->loss_dev, 4, true)); G(dalloc(m, &m->n_valid_dev, 4, true)); G(dalloc(m, &m->status_dev, 4, true));
+    G(dalloc(m, &m->ce_lse, T));
+    m->ce_ws_bytes = mft_lmhead_ce_workspace_bytes(T, H, V);
+    { uint8_t* ws = nullptr; G(dalloc(m, &ws, m->ce_ws_bytes, false, true)); m->ce_ws = ws; }
+    m->stage_floats = 32ll << 20;
+    G(dalloc(m, &m->stage_f32, m->stage_floats));
+    G(check_cuda(cudaStreamSynchronize(m->stream), "model create"));
+#undef G
+    *out = m;
+    return MFT_OK;
+}
+
+// ---------------------------------------------------------------- parameter access
+extern "C" int32_t mft_model_param_count(const mft_model_t* m) { return m ? (int32_t)m->params.size() : 0; }
+extern "C" int32_t mft_model_param_shape(const mft_model_t* m, int32_t idx, int64_t* rows, int64_t* cols) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->params.size() && rows && cols, "mft_model_param_shape: bad argument");
+    *rows = m->params[idx].rows; *cols = m->params[idx].cols;
+    return MFT_OK;
+}
+
+namespace {
+// Installs rows [r0, r0+nr) of parameter `p` from a device f32 buffer holding exactly those rows.
+int32_t install_rows(mft_model* m, const ParamInfo& p, const float* src_dev, int64_t r0, int64_t nr) {
+    mft_stream_t st = m->stream;
+    switch (p.kind) {
+        case ParamInfo::EMBED:
+            return mft_cast_f32_to_bf16(src_dev, m->embed + r0 * p.cols, nr * p.cols, st);
+        case ParamInfo::POS_EMBED:
+            return mft_cast_f32_to_bf16(src_dev, m->pos_embed + r0 * p.cols, nr * p.cols, st);
+        case ParamInfo::LM_HEAD_COPY:
+            return MFT_OK;   // the device keeps a single table; its transpose is derived from the embedding
+        case ParamInfo::NORM:
+            return mft_memcpy_d2d(p.f32_dst, src_dev, p.cols * 4, st);
+        case ParamInfo::BIAS: {
+            const LinearSlot& s = p.group->slots[p.slot];
+            return mft_memcpy_d2d(p.group->bias + s.col0, src_dev, p.cols * 4, st);
+        }
+        case ParamInfo::LINEAR: {
+            // host layout [in, out]; whole matrix at once (r0 == 0, nr == in)
+            LinearGroup* g = p.group;
+            const LinearSlot& s = g->slots[p.slot];
+            TRY(mft_transpose_f32_to_bf16(src_dev, g->w_nk + (int64_t)s.col0 * g->in, s.in, s.out, st));
+            mft_block_copy_t e; e.src = src_dev; e.dst = g->w_kn + s.col0; e.rows = s.in; e.cols = s.out; e.src_ld = s.out; e.dst_ld = g->n_total; e.transpose = 0; e.pad = 0;
+            // one-entry copy table, parked in the last 256 bytes of the staging buffer
+            mft_block_copy_t* tbl = reinterpret_cast<mft_block_copy_t*>(m->stage_f32 + m->stage_floats - 64);
+            TRY(mft_memcpy_h2d(tbl, &e, sizeof(e), st));
+            TRY(check_cuda(cudaStreamSynchronize(m->stream), "table upload"));
+            return mft_pack_blocks_bf16(tbl, 1, st);
+        }
+    }
+    return MFT_OK;
+}
+
+int32_t finish_param(mft_model* m, const ParamInfo& p) {
+    if (p.kind == ParamInfo::EMBED)
+        return mft_transpose_bf16_ld(m->embed, m->embed_t, p.rows, p.cols, m->ld_t, m->stream);
+    return MFT_OK;
+}
+}  // namespace
+
+extern "C" int32_t mft_model_set_param_dev(mft_model_t* m, int32_t idx, const float* data_dev) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->params.size() && data_dev, "mft_model_set_param_dev: bad argument");
+    const ParamInfo& p = m->params[idx];
+    TRY(install_rows(m, p, data_dev, 0, p.rows));
+    return finish_param(m, p);
+}
+
+extern "C" int32_t mft_model_set_param_host(mft_model_t* m, int32_t idx, const float* data_host) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->params.size() && data_host, "mft_model_set_param_host: bad argument");
+    const ParamInfo& p = m->params[idx];
+    if (p.kind == ParamInfo::LM_HEAD_COPY) return MFT_OK;
+    const int64_t usable = m->stage_floats - 64;
+    if (p.kind == ParamInfo::LINEAR) {
+        MFT_CHECK_ARG(p.rows * p.cols <= usable, "mft_model_set_param_host: linear larger than the staging buffer");
+        TRY(mft_memcpy_h2d(m->stage_f32, data_host, (size_t)p.rows * p.cols * 4, m->stream));
+        TRY(install_rows(m, p, m->stage_f32, 0, p.rows));
+        return check_cuda(cudaStreamSynchronize(m->stream), "param upload");
+    }
+    const int64_t rows_per = std::max<int64_t>(1, usable / p.cols);
+    for (int64_t r0 = 0; r0 < p.rows; r0 += rows_per) {
+        const int64_t nr = std::min(rows_per, p.rows - r0);
+        TRY(mft_memcpy_h2d(m->stage_f32, data_host + r0 * p.cols, (size_t)nr * p.cols * 4, m->stream));
+        TRY(install_rows(m, p, m->stage_f32, r0, nr));
+        TRY(check_cuda(cudaStreamSynchronize(m->stream), "param upload"));
+    }
+    TRY(finish_param(m, p));
+    return check_cuda(cudaStreamSynchronize(m->stream), "param upload");
+}
+
+extern "C" int32_t mft_model_lora_count(const mft_model_t* m) { return m ? (int32_t)m->loras.size() : 0; }
+extern "C" int32_t mft_model_lora_shape(const mft_model_t* m, int32_t idx, int64_t* rows, int64_t* cols) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->loras.size() && rows && cols, "mft_model_lora_shape: bad argument");
+    *rows = m->loras[idx].rows; *cols = m->loras[idx].cols;
+    return MFT_OK;
+}
+extern "C" int32_t mft_model_lora_has_grad(const mft_model_t* m, int32_t idx) {
+    return (m && idx >= 0 && idx < (int)m->loras.size() && m->loras[idx].has_grad) ? 1 : 0;
+}
+extern "C" int32_t mft_model_set_lora_host(mft_model_t* m, int32_t idx, const float* data_host) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->loras.size() && data_host, "mft_model_set_lora_host: bad argument");
+    const LoraInfo& t = m->loras[idx];
+    TRY(mft_memcpy_h2d(m->p_bucket + t.offset, data_host, (size_t)t.rows * t.cols * 4, m->stream));
+    m->panels_dirty = true;
+    return check_cuda(cudaStreamSynchronize(m->stream), "lora upload");
+}
+extern "C" int32_t mft_model_get_lora_host(mft_model_t* m, int32_t idx, float* data_host) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->loras.size() && data_host, "mft_model_get_lora_host: bad argument");
+    const LoraInfo& t = m->loras[idx];
+    return mft_memcpy_d2h(data_host, m->p_bucket + t.offset, (size_t)t.rows * t.cols * 4, m->stream);
+}
+extern "C" int32_t mft_model_get_lora_grad_host(mft_model_t* m, int32_t idx, float* data_host) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->loras.size() && data_host, "mft_model_get_lora_grad_host: bad argument");
+    const LoraInfo& t = m->loras[idx];
+    return mft_memcpy_d2h(data_host, m->g_bucket + t.offset, (size_t)t.rows * t.cols * 4, m->stream);
+}
+extern "C" int32_t mft_model_buckets(mft_model_t* m, float** params_dev, float** grads_dev, int64_t* n) {
+    MFT_CHECK_ARG(m, "mft_model_buckets: null model");
+    if (params_dev) *params_dev = m->p_bucket;
+    if (grads_dev) *grads_dev = m->g_bucket;
+    if (n) *n = m->bucket_n;
+    return MFT_OK;
+}
+extern "C" int64_t mft_model_activation_bytes(const mft_model_t* m) { return m ? m->activation_bytes : 0; }

@@ -1,0 +1,279 @@
+// Forward / backward / optimizer schedules of the step engine: one stream, a
+// fixed sequence of launches per layer, every kernel called through the C ABI
+// of mft_cuda.h.  Order of operations follows the reference graphs
+// (graph/gemma_model.cpp:358-646, graph/qwen_model.cpp:278-394,
+// graph/gpt2_model.cpp:494-764) with the fusions listed next to each call.
+#include <algorithm>
+#include <cmath>
+
+#include "common.cuh"
+#include "engine.h"
+
+using namespace mft;
+
+namespace {
+
+#define TRY(expr)                         \
+    do {                                  \
+        int32_t s__ = (expr);             \
+        if (s__ != MFT_OK) return s__;    \
+    } while (0)
+
+struct Ctx {
+    mft_model* m;
+    int64_t B, S, T;
+    mft_stream_t st;
+    float lora_scale;
+};
+
+// y[T, n_total] = x W (+ bias) + scale (x A) B for every linear of the group, one GEMM
+// (plus the 64-column x A panel product when the group carries LoRA).
+int32_t group_fwd(const Ctx& c, LinearGroup& g, const bf16* x, bf16* xa, bf16* y) {
+    if (g.any_lora) {
+        TRY(mft_gemm_nt(x, g.in, g.a_nk, g.in, c.T, 64, g.in, nullptr, 0, nullptr, 0, 0, nullptr, c.lora_scale, xa, 64, MFT_BF16, 0, c.st));
+        return mft_gemm_nt(x, g.in, g.w_nk, g.in, c.T, g.n_total, g.in, xa, 64, g.b_nk, 64, g.k2, g.bias, 1.0f, y, g.n_total, MFT_BF16, 0, c.st);
+    }
+    return mft_gemm_nt(x, g.in, g.w_nk, g.in, c.T, g.n_total, g.in, nullptr, 0, nullptr, 0, 0, g.bias, 1.0f, y, g.n_total, MFT_BF16, 0, c.st);
+}
+
+// dx = dy W^T + scale (dy B^T) A^T ; dA-panel += x^T (scale dy B^T) ; dB-panel += (scale x A)^T dy.
+int32_t group_bwd(const Ctx& c, LinearGroup& g, const bf16* dy, const bf16* x, const bf16* xa, bf16* dx, bool lora_grads) {
+    if (g.any_lora) {
+        bf16* gb = c.m->t_pan;
+        TRY(mft_gemm_nt(dy, g.n_total, g.b_kn, g.n_total, c.T, 64, g.n_total, nullptr, 0, nullptr, 0, 0, nullptr, c.lora_scale, gb, 64, MFT_BF16, 0, c.st));
+        if (dx) TRY(mft_gemm_nt(dy, g.n_total, g.w_kn, g.n_total, c.T, g.in, g.n_total, gb, 64, g.a_kn, 64, g.k2, nullptr, 1.0f, dx, g.in, MFT_BF16, 0, c.st));
+        if (lora_grads) {
+            TRY(mft_gemm_tn_acc(x, g.in, gb, 64, c.T, g.in, 64, 1.0f, g.da_pan, 64, c.st));
+            TRY(mft_gemm_tn_acc(xa, 64, dy, g.n_total, c.T, 64, g.n_total, 1.0f, g.db_pan, g.n_total, c.st));
+        }
+        return MFT_OK;
+    }
+    if (dx) return mft_gemm_nt(dy, g.n_total, g.w_kn, g.n_total, c.T, g.in, g.n_total, nullptr, 0, nullptr, 0, 0, nullptr, 1.0f, dx, g.in, MFT_BF16, 0, c.st);
+    return MFT_OK;
+}
+
+mft_strides_t tok_strides(int64_t S, int64_t ld, int64_t hd) {
+    mft_strides_t s; s.stride_b = S * ld; s.stride_s = ld; s.stride_h = hd; return s;
+}
+
+int32_t forward(Ctx& c, bool for_training) {
+    mft_model* m = c.m;
+    const mft_model_config_t& cfg = m->cfg;
+    const bool gpt2 = cfg.family == MFT_FAMILY_GPT2, gemma = cfg.family == MFT_FAMILY_GEMMA;
+    const int H = cfg.hidden, I = cfg.inter, nh = cfg.n_heads, nkv = cfg.n_kv_heads, hd = cfg.head_dim, L = cfg.layers;
+    const int QD = nh * hd, KD = nkv * hd, QKV = QD + 2 * KD;
+    const int64_t T = c.T, S = c.S;
+    (void)for_training;
+    if (m->panels_dirty && m->n_pack > 0) {
+        TRY(mft_pack_blocks_bf16(m->pack_table, m->n_pack, c.st));
+        m->panels_dirty = false;
+    }
+    TRY(mft_memset(m->status_dev, 0, 4, c.st));
+    const float emb_scale = gemma ? std::sqrt((float)H) : 1.0f;
+    TRY(mft_embedding_gather(m->ids, m->embed, gpt2 ? m->pos_embed : nullptr, m->bufs[0].x, T, S, H, cfg.vocab, emb_scale, m->status_dev, c.st));
+
+    for (int l = 0; l < L; ++l) {
+        LayerWeights& w = m->layers[l];
+        LayerBuffers& b = m->bufs[l];
+        float* x_next = (l + 1 < L) ? m->bufs[l + 1].x : m->x_final;
+        // ---- attention block
+        if (gpt2) TRY(mft_layernorm_fwd(b.x, MFT_F32, w.ln1_w, w.ln1_b, 1e-5f, b.h1, MFT_BF16, b.mean1, b.rstd1, T, H, c.st));
+        else TRY(mft_rmsnorm_fwd(b.x, MFT_F32, w.ln1_w, cfg.norm_eps, gemma ? 1 : 0, b.h1, MFT_BF16, b.rstd1, nullptr, nullptr, T, H, c.st));
+        TRY(group_fwd(c, w.qkv, b.h1, b.xa_qkv, b.qkv));
+        const bf16 *q, *k, *v = b.qkv + QD + KD;
+        int64_t ldqk;
+        if (gpt2) { q = b.qkv; k = b.qkv + QD; ldqk = QKV; }
+        else {
+            const float* cs = (gemma && w.sliding) ? m->cos_l : m->cos_g;
+            const float* sn = (gemma && w.sliding) ? m->sin_l : m->sin_g;
+            // per-head RMSNorm (Gemma) fused with the rotary embedding and the head split
+            TRY(mft_headnorm_rope_fwd(b.qkv, QKV, gemma ? w.q_norm_w : nullptr, cfg.norm_eps, cs, sn, b.qk_r, QD + KD, b.rstd_q, T, S, nh, hd, c.st));
+            TRY(mft_headnorm_rope_fwd(b.qkv + QD, QKV, gemma ? w.k_norm_w : nullptr, cfg.norm_eps, cs, sn, b.qk_r + QD, QD + KD, b.rstd_k, T, S, nkv, hd, c.st));
+            q = b.qk_r; k = b.qk_r + QD; ldqk = QD + KD;
+        }
+        const int64_t window = (gemma && w.sliding) ? cfg.sliding_window : 0;
+        TRY(mft_attn_fwd(q, tok_strides(S, ldqk, hd), k, tok_strides(S, ldqk, hd), v, tok_strides(S, QKV, hd), b.o, tok_strides(S, QD, hd),
+                         b.lse, c.B, S, nh, nkv, hd, cfg.attn_scale, window, c.st));
+        TRY(group_fwd(c, w.o, b.o, b.xa_o, b.attn_out));
+        if (gemma) {
+            // x_mid = x + rms_norm(attn_out) in one pass, then the pre-feedforward norm
+            TRY(mft_rmsnorm_fwd(b.attn_out, MFT_BF16, w.post_attn_w, cfg.norm_eps, 1, nullptr, MFT_BF16, b.rstd2, b.x, b.x_mid, T, H, c.st));
+            TRY(mft_rmsnorm_fwd(b.x_mid, MFT_F32, w.ln2_w, cfg.norm_eps, 1, b.h2, MFT_BF16, b.rstd3, nullptr, nullptr, T, H, c.st));
+        } else {
+            TRY(mft_add_f32_bf16(b.x, b.attn_out, b.x_mid, T * H, c.st));
+            if (gpt2) TRY(mft_layernorm_fwd(b.x_mid, MFT_F32, w.ln2_w, w.ln2_b, 1e-5f, b.h2, MFT_BF16, b.mean3, b.rstd3, T, H, c.st));
+            else TRY(mft_rmsnorm_fwd(b.x_mid, MFT_F32, w.ln2_w, cfg.norm_eps, 0, b.h2, MFT_BF16, b.rstd3, nullptr, nullptr, T, H, c.st));
+        }
+        // ---- MLP block
+        TRY(group_fwd(c, w.gu, b.h2, b.xa_gu, b.gu));
+        if (gpt2) TRY(mft_act_fwd(MFT_ACT_GELU, b.gu, nullptr, I, b.act, T, I, c.st));
+        else TRY(mft_act_fwd(gemma ? MFT_ACT_GEGLU : MFT_ACT_SWIGLU, b.gu, b.gu + I, 2 * I, b.act, T, I, c.st));
+        TRY(group_fwd(c, w.down, b.act, b.xa_d, b.mlp_out));
+        if (gemma) TRY(mft_rmsnorm_fwd(b.mlp_out, MFT_BF16, w.post_ffn_w, cfg.norm_eps, 1, nullptr, MFT_BF16, b.rstd4, b.x_mid, x_next, T, H, c.st));
+        else TRY(mft_add_f32_bf16(b.x_mid, b.mlp_out, x_next, T * H, c.st));
+    }
+    if (gpt2) TRY(mft_layernorm_fwd(m->x_final, MFT_F32, m->final_w, m->final_b, 1e-5f, m->hf, MFT_BF16, m->mean_f, m->rstd_f, T, H, c.st));
+    else TRY(mft_rmsnorm_fwd(m->x_final, MFT_F32, m->final_w, cfg.norm_eps, gemma ? 1 : 0, m->hf, MFT_BF16, m->rstd_f, nullptr, nullptr, T, H, c.st));
+    // lm head + shifted cross entropy; the [T,V] logits are never written
+    return mft_lmhead_ce_fwd(m->hf, m->embed, m->labels, c.B, S, H, cfg.vocab, -100, m->loss_dev, m->n_valid_dev, m->ce_lse, m->status_dev,
+                             m->ce_ws, m->ce_ws_bytes, c.st);
+}
+
+int32_t backward(Ctx& c, int64_t n_valid_global) {
+    mft_model* m = c.m;
+    const mft_model_config_t& cfg = m->cfg;
+    const bool gpt2 = cfg.family == MFT_FAMILY_GPT2, gemma = cfg.family == MFT_FAMILY_GEMMA;
+    const bool detach = gpt2 && cfg.gpt2_detach_attn != 0;
+    const int H = cfg.hidden, I = cfg.inter, nh = cfg.n_heads, nkv = cfg.n_kv_heads, hd = cfg.head_dim, L = cfg.layers;
+    const int QD = nh * hd, KD = nkv * hd, QKV = QD + 2 * KD;
+    const int64_t T = c.T, S = c.S;
+    if (m->grad_pan_floats > 0) TRY(mft_memset(m->grad_pan_base, 0, (size_t)m->grad_pan_floats * 4, c.st));
+    // d(loss)/d(final hidden), then through the final norm into the residual gradient dx (f32)
+    TRY(mft_lmhead_ce_bwd(m->hf, m->embed, m->embed_t, m->ld_t, m->labels, c.B, S, H, cfg.vocab, -100, m->ce_lse, m->n_valid_dev,
+                          n_valid_global, 1.0f, m->t_h, m->ce_ws, m->ce_ws_bytes, c.st));
+    if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, m->x_final, MFT_F32, m->final_w, m->mean_f, m->rstd_f, m->dx, MFT_F32, 0, nullptr, nullptr, T, H, c.st));
+    else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, m->x_final, MFT_F32, m->final_w, m->rstd_f, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 0, nullptr, T, H, c.st));
+
+    for (int l = L - 1; l >= 0; --l) {
+        LayerWeights& w = m->layers[l];
+        LayerBuffers& b = m->bufs[l];
+        // ---- MLP block: dx is d(loss)/d(x_next) on entry
+        const bf16* d_mlp_out;
+        if (gemma) {
+            TRY(mft_rmsnorm_bwd(m->dx, MFT_F32, b.mlp_out, MFT_BF16, w.post_ffn_w, b.rstd4, cfg.norm_eps, 1, m->t_h, MFT_BF16, 0, nullptr, T, H, c.st));
+        } else {
+            TRY(mft_cast_f32_to_bf16(m->dx, m->t_h, T * H, c.st));
+        }
+        d_mlp_out = m->t_h;
+        TRY(group_bwd(c, w.down, d_mlp_out, b.act, b.xa_d, m->t_i, true));
+        if (gpt2) TRY(mft_act_bwd(MFT_ACT_GELU, m->t_i, b.gu, nullptr, I, m->t_gu, nullptr, T, I, c.st));
+        else TRY(mft_act_bwd(gemma ? MFT_ACT_GEGLU : MFT_ACT_SWIGLU, m->t_i, b.gu, b.gu + I, 2 * I, m->t_gu, m->t_gu + I, T, I, c.st));
+        TRY(group_bwd(c, w.gu, m->t_gu, b.h2, b.xa_gu, m->t_h, true));
+        // through the pre-MLP norm, accumulated onto the residual gradient: dx = d(loss)/d(x_mid)
+        if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, b.x_mid, MFT_F32, w.ln2_w, b.mean3, b.rstd3, m->dx, MFT_F32, 1, nullptr, nullptr, T, H, c.st));
+        else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, b.x_mid, MFT_F32, w.ln2_w, b.rstd3, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 1, nullptr, T, H, c.st));
+        // ---- attention block
+        if (gemma) TRY(mft_rmsnorm_bwd(m->dx, MFT_F32, b.attn_out, MFT_BF16, w.post_attn_w, b.rstd2, cfg.norm_eps, 1, m->t_h, MFT_BF16, 0, nullptr, T, H, c.st));
+        else TRY(mft_cast_f32_to_bf16(m->dx, m->t_h, T * H, c.st));
+        if (detach) {
+            // Reference-parity GPT-2: the QKV split severs autograd, so c_proj gets its LoRA gradients
+            // (its input is a constant) and nothing flows back through attention, c_attn or ln_1.
+            TRY(group_bwd(c, w.o, m->t_h, b.o, b.xa_o, nullptr, true));
+            continue;
+        }
+        TRY(group_bwd(c, w.o, m->t_h, b.o, b.xa_o, m->t_o, true));
+        const bf16 *q, *k, *v = b.qkv + QD + KD;
+        int64_t ldqk;
+        bf16 *dq, *dk, *dv = m->t_qkv + QD + KD;
+        if (gpt2) { q = b.qkv; k = b.qkv + QD; ldqk = QKV; dq = m->t_qkv; dk = m->t_qkv + QD; }
+        else { q = b.qk_r; k = b.qk_r + QD; ldqk = QD + KD; dq = m->t_qk; dk = m->t_qk + QD; }
+        const int64_t window = (gemma && w.sliding) ? cfg.sliding_window : 0;
+        TRY(mft_attn_bwd(q, tok_strides(S, ldqk, hd), k, tok_strides(S, ldqk, hd), v, tok_strides(S, QKV, hd), b.o, tok_strides(S, QD, hd),
+                         m->t_o, tok_strides(S, QD, hd), b.lse, dq, dk, dv, m->attn_delta, nullptr, c.B, S, nh, nkv, hd, cfg.attn_scale, window, c.st));
+        if (!gpt2) {
+            const float* cs = (gemma && w.sliding) ? m->cos_l : m->cos_g;
+            const float* sn = (gemma && w.sliding) ? m->sin_l : m->sin_g;
+            TRY(mft_headnorm_rope_bwd(m->t_qk, QD + KD, b.qkv, QKV, gemma ? w.q_norm_w : nullptr, b.rstd_q, cs, sn, m->t_qkv, QKV, T, S, nh, hd, c.st));
+            TRY(mft_headnorm_rope_bwd(m->t_qk + QD, QD + KD, b.qkv + QD, QKV, gemma ? w.k_norm_w : nullptr, b.rstd_k, cs, sn, m->t_qkv + QD, QKV, T, S, nkv, hd, c.st));
+        }
+        const bool need_dx = l > 0;   // the embedding table is frozen: layer 0 needs no input gradient
+        TRY(group_bwd(c, w.qkv, m->t_qkv, b.h1, b.xa_qkv, need_dx ? m->t_h : nullptr, true));
+        if (need_dx) {
+            if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, b.x, MFT_F32, w.ln1_w, b.mean1, b.rstd1, m->dx, MFT_F32, 1, nullptr, nullptr, T, H, c.st));
+            else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, b.x, MFT_F32, w.ln1_w, b.rstd1, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 1, nullptr, T, H, c.st));
+        }
+    }
+    if (m->n_unpack > 0) TRY(mft_accumulate_blocks_f32(m->unpack_table, m->n_unpack, c.st));
+    return MFT_OK;
+}
+
+int32_t make_ctx(mft_model* m, int32_t batch, int32_t seq, Ctx* c) {
+    MFT_CHECK_ARG(m && batch > 0 && seq > 1, "step: bad batch/seq");
+    MFT_CHECK_ARG((int64_t)batch * seq <= m->max_tokens && seq <= m->cfg.max_seq, "step: batch*seq exceeds the model's capacity");
+    c->m = m; c->B = batch; c->S = seq; c->T = (int64_t)batch * seq; c->st = m->stream;
+    c->lora_scale = m->cfg.lora_rank > 0 ? m->cfg.lora_alpha / (float)m->cfg.lora_rank : 0.f;
+    return MFT_OK;
+}
+
+int32_t check_status(mft_model* m) {
+    int32_t st = 0;
+    TRY(mft_memcpy_d2h(&st, m->status_dev, 4, m->stream));
+    if (st == MFT_ERR_BOUNDS) return fail(MFT_ERR_BOUNDS, "token id or label out of range");
+    int32_t dev = 0;
+    TRY(mft_device_status(m->stream, &dev));
+    if (dev != 0) return fail(dev, "a kernel wait ran out (device status word set)");
+    return MFT_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t* ids_dev, const int32_t* labels_dev, int32_t batch,
+                                                  int32_t seq, int64_t n_valid_global, float** loss_dev, int32_t** n_valid_dev) {
+    Ctx c;
+    TRY(make_ctx(m, batch, seq, &c));
+    MFT_CHECK_ARG(ids_dev && labels_dev, "mft_model_forward_backward_dev: null input");
+    if (ids_dev != m->ids) TRY(mft_memcpy_d2d(m->ids, ids_dev, (size_t)c.T * 4, c.st));
+    if (labels_dev != m->labels) TRY(mft_memcpy_d2d(m->labels, labels_dev, (size_t)c.T * 4, c.st));
+    TRY(forward(c, true));
+    TRY(backward(c, n_valid_global));
+    if (loss_dev) *loss_dev = m->loss_dev;
+    if (n_valid_dev) *n_valid_dev = m->n_valid_dev;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_model_forward_backward(mft_model_t* m, const int32_t* ids_host, const int32_t* labels_host, int32_t batch,
+                                              int32_t seq, int64_t n_valid_global, float* loss_host, int32_t* n_valid_host) {
+    Ctx c;
+    TRY(make_ctx(m, batch, seq, &c));
+    MFT_CHECK_ARG(ids_host && labels_host, "mft_model_forward_backward: null input");
+    TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)c.T * 4, c.st));
+    TRY(mft_memcpy_h2d(m->labels, labels_host, (size_t)c.T * 4, c.st));
+    TRY(forward(c, true));
+    TRY(backward(c, n_valid_global));
+    if (loss_host) TRY(mft_memcpy_d2h(loss_host, m->loss_dev, 4, c.st));
+    if (n_valid_host) TRY(mft_memcpy_d2h(n_valid_host, m->n_valid_dev, 4, c.st));
+    return check_status(m);
+}
+
+extern "C" int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_host, const int32_t* labels_host, int32_t batch,
+                                          int32_t seq, float* loss_host) {
+    Ctx c;
+    TRY(make_ctx(m, batch, seq, &c));
+    MFT_CHECK_ARG(ids_host && labels_host && loss_host, "mft_model_forward_loss: null argument");
+    TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)c.T * 4, c.st));
+    TRY(mft_memcpy_h2d(m->labels, labels_host, (size_t)c.T * 4, c.st));
+    TRY(forward(c, false));
+    TRY(mft_memcpy_d2h(loss_host, m->loss_dev, 4, c.st));
+    return check_status(m);
+}
+
+extern "C" int32_t mft_model_optimizer_step(mft_model_t* m, float lr, float beta1, float beta2, float eps, float weight_decay,
+                                            float max_norm, float clip_eps) {
+    MFT_CHECK_ARG(m, "mft_model_optimizer_step: null model");
+    if (m->bucket_n == 0) return MFT_OK;
+    m->adam_step += 1;
+    const float* sq = nullptr;
+    if (max_norm > 0.f) {
+        TRY(mft_grad_sqnorm(m->g_bucket, m->bucket_n, m->sqnorm, m->stream));
+        sq = m->sqnorm;
+    }
+    // Tensors the reference never gives a gradient (GPT-2 c_attn) keep a zero gradient and zero Adam
+    // moments, so the update leaves them untouched, as Adam::step skips them.
+    TRY(mft_adam_step(m->p_bucket, m->g_bucket, m->m_bucket, m->v_bucket, m->bucket_n, m->adam_step, lr, beta1, beta2, eps,
+                      weight_decay, sq, max_norm, clip_eps, 1, m->stream));
+    m->panels_dirty = true;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_model_zero_grad(mft_model_t* m) {
+    MFT_CHECK_ARG(m, "mft_model_zero_grad: null model");
+    if (m->bucket_n == 0) return MFT_OK;
+    return mft_memset(m->g_bucket, 0, (size_t)m->bucket_n * 4, m->stream);
+}
+
+extern "C" int32_t mft_model_get_final_hidden_host(mft_model_t* m, float* out_host, int64_t n) {
+    MFT_CHECK_ARG(m && out_host && n > 0 && n <= m->max_tokens * m->cfg.hidden, "mft_model_get_final_hidden_host: bad argument");
+    MFT_CHECK_ARG(n <= m->stage_floats - 64, "mft_model_get_final_hidden_host: too large for the staging buffer");
+    TRY(mft_cast_bf16_to_f32(m->hf, m->stage_f32, n, m->stream));
+    return mft_memcpy_d2h(out_host, m->stage_f32, (size_t)n * 4, m->stream);
+}

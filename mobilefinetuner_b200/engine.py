@@ -1,0 +1,177 @@
+"""LoRA fine-tuning step engine: Python handle over the C ABI of include/mft_step.h.
+
+Mirrors the reference's step driver (AutoModelForCausalLM + AutoTrainer::train_step,
+operator/finetune_ops/optim/auto_trainer.cpp:20-46): parameters()/trainable_parameters()
+orders and layouts are the reference's, `train_step` is forward -> lm_cross_entropy ->
+backward -> clip -> Adam -> zero_grad.  All compute runs in libmft_cuda.so; torch supplies
+pinned host buffers, the stream and (for data parallel runs) torch.distributed.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from .configs import ModelSpec, StepConfig
+
+
+class LoraStepEngine:
+    def __init__(self, spec: ModelSpec, max_batch: int, max_seq: int, device: int = 0):
+        if not torch.cuda.is_available():
+            raise L.MftError("no CUDA device: the LoRA step engine has no CPU path")
+        torch.cuda.set_device(device)
+        L.init(device)
+        self.spec, self.device = spec, device
+        cfg = L.ModelConfig(
+            family=spec.family, vocab=spec.vocab, hidden=spec.hidden, inter=spec.inter, layers=spec.layers,
+            n_heads=spec.n_heads, n_kv_heads=spec.n_kv_heads, head_dim=spec.head_dim, n_positions=spec.n_positions,
+            norm_eps=spec.norm_eps, rope_theta=spec.rope_theta, rope_local_theta=spec.rope_local_theta,
+            attn_scale=spec.attn_scale, sliding_window=spec.sliding_window, global_every=spec.global_every,
+            lora_rank=spec.lora_rank, lora_alpha=spec.lora_alpha, lora_targets=spec.lora_mask,
+            gpt2_detach_attn=1 if spec.gpt2_detach_attn else 0, max_batch=max_batch, max_seq=max_seq)
+        self.stream = torch.cuda.current_stream().cuda_stream
+        h = C.c_void_p()
+        L.call("mft_model_create", C.byref(cfg), self.stream, C.byref(h))
+        self._h = h
+        self.max_batch, self.max_seq = max_batch, max_seq
+        self._pin_ids = torch.empty(max_batch * max_seq, dtype=torch.int32).pin_memory()
+        self._pin_labels = torch.empty(max_batch * max_seq, dtype=torch.int32).pin_memory()
+        p, g, n = C.c_void_p(), C.c_void_p(), C.c_int64()
+        L.call("mft_model_buckets", self._h, C.byref(p), C.byref(g), C.byref(n))
+        self.bucket_n = n.value
+        self._grad_ptr, self._param_ptr = g.value, p.value
+
+    def close(self):
+        if getattr(self, "_h", None):
+            L.call("mft_model_destroy", self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- parameters (reference order and layout)
+    def param_shapes(self):
+        out = []
+        for i in range(L.call("mft_model_param_count", self._h)):
+            r, c = C.c_int64(), C.c_int64()
+            L.call("mft_model_param_shape", self._h, i, C.byref(r), C.byref(c))
+            out.append((r.value, c.value))
+        return out
+
+    def lora_shapes(self):
+        out = []
+        for i in range(L.call("mft_model_lora_count", self._h)):
+            r, c = C.c_int64(), C.c_int64()
+            L.call("mft_model_lora_shape", self._h, i, C.byref(r), C.byref(c))
+            out.append((r.value, c.value))
+        return out
+
+    def set_params(self, arrays):
+        shapes = self.param_shapes()
+        assert len(arrays) == len(shapes), (len(arrays), len(shapes))
+        for i, (a, (r, c)) in enumerate(zip(arrays, shapes)):
+            if isinstance(a, torch.Tensor):
+                assert a.is_cuda and a.dtype == torch.float32 and a.numel() == r * c
+                L.call("mft_model_set_param_dev", self._h, i, a.contiguous().data_ptr())
+            else:
+                a = np.ascontiguousarray(a, dtype=np.float32)
+                assert a.size == r * c, (i, a.shape, (r, c))
+                L.call("mft_model_set_param_host", self._h, i, a.ctypes.data)
+        torch.cuda.synchronize()
+
+    def set_lora(self, arrays):
+        shapes = self.lora_shapes()
+        assert len(arrays) == len(shapes), (len(arrays), len(shapes))
+        for i, (a, (r, c)) in enumerate(zip(arrays, shapes)):
+            a = np.ascontiguousarray(a, dtype=np.float32)
+            assert a.shape == (r, c), (i, a.shape, (r, c))
+            L.call("mft_model_set_lora_host", self._h, i, a.ctypes.data)
+
+    def get_lora(self):
+        out = []
+        for i, (r, c) in enumerate(self.lora_shapes()):
+            a = np.empty((r, c), np.float32)
+            L.call("mft_model_get_lora_host", self._h, i, a.ctypes.data)
+            out.append(a)
+        return out
+
+    def get_lora_grads(self):
+        out = []
+        for i, (r, c) in enumerate(self.lora_shapes()):
+            if not L.call("mft_model_lora_has_grad", self._h, i):
+                out.append(None)
+                continue
+            a = np.empty((r, c), np.float32)
+            L.call("mft_model_get_lora_grad_host", self._h, i, a.ctypes.data)
+            out.append(a)
+        return out
+
+    def grad_bucket(self) -> torch.Tensor:
+        """The flat f32 LoRA-gradient bucket as a torch view (what data parallel all-reduces)."""
+        return _as_tensor(self._grad_ptr, self.bucket_n, self.device)
+
+    def param_bucket(self) -> torch.Tensor:
+        return _as_tensor(self._param_ptr, self.bucket_n, self.device)
+
+    # ---- the step
+    def forward_backward(self, ids: np.ndarray, labels: np.ndarray, n_valid_global: int = 0):
+        b, s = ids.shape
+        n = b * s
+        self._pin_ids[:n].copy_(torch.from_numpy(np.ascontiguousarray(ids, np.int32).ravel()))
+        self._pin_labels[:n].copy_(torch.from_numpy(np.ascontiguousarray(labels, np.int32).ravel()))
+        return self.forward_backward_pinned(b, s, n_valid_global)
+
+    def forward_backward_pinned(self, b: int, s: int, n_valid_global: int = 0):
+        """ids / labels were already written to self._pin_ids / self._pin_labels."""
+        loss, nv = C.c_float(), C.c_int32()
+        L.call("mft_model_forward_backward", self._h, self._pin_ids.data_ptr(), self._pin_labels.data_ptr(), b, s,
+               int(n_valid_global), C.byref(loss), C.byref(nv))
+        return loss.value, nv.value
+
+    def forward_loss(self, ids: np.ndarray, labels: np.ndarray) -> float:
+        b, s = ids.shape
+        ids = np.ascontiguousarray(ids, np.int32)
+        labels = np.ascontiguousarray(labels, np.int32)
+        loss = C.c_float()
+        L.call("mft_model_forward_loss", self._h, ids.ctypes.data, labels.ctypes.data, b, s, C.byref(loss))
+        return loss.value
+
+    def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, max_grad_norm=0.0, clip_eps=0.0):
+        L.call("mft_model_optimizer_step", self._h, float(lr), float(beta1), float(beta2), float(eps), float(weight_decay),
+               float(max_grad_norm), float(clip_eps))
+
+    def zero_grad(self):
+        L.call("mft_model_zero_grad", self._h)
+
+    def train_step(self, ids, labels, cfg: StepConfig, world=None):
+        """forward + loss + backward (+ all-reduce of the LoRA gradients) + clip + Adam + zero_grad."""
+        n_global = 0
+        if world is not None and world.size > 1:
+            n_global = world.global_valid_count(labels)
+        loss, _ = self.forward_backward(ids, labels, n_global)
+        if world is not None and world.size > 1:
+            world.all_reduce_sum(self.grad_bucket())
+        self.optimizer_step(cfg.lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.max_grad_norm, 0.0)
+        return loss
+
+    def final_hidden(self, n_tokens: int) -> np.ndarray:
+        out = np.empty((n_tokens, self.spec.hidden), np.float32)
+        L.call("mft_model_get_final_hidden_host", self._h, out.ctypes.data, out.size)
+        return out
+
+    def activation_bytes(self) -> int:
+        return L.call("mft_model_activation_bytes", self._h)
+
+
+def _as_tensor(ptr: int, n: int, device: int) -> torch.Tensor:
+    """Wrap device memory owned by the engine as a 1-D float32 torch tensor (no copy)."""
+    class _Holder:
+        pass
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+    return torch.as_tensor(h, device=f"cuda:{device}")

@@ -116,5 +116,34 @@ def main():
     print(out, out.stat().st_size, "bytes,", len(store), "arrays; driver:", refrun.kind(refrun.driver()))
 
 
+
+
+def make_model_golden():
+    """Whole-model LoRA step of the reference on the reduced cases of tests/model_cases.py.
+    Inputs are regenerated from seeds (mobilefinetuner_b200.synth), so only outputs are stored."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    from model_cases import CASES, STEP
+    from mobilefinetuner_b200 import synth
+    from oracle import model_case
+    store = {}
+    for name, c in CASES.items():
+        spec = c["spec"]
+        params = synth.make_params(spec, c["seeds"][0], c["norm_jitter"])
+        lora = synth.make_lora(spec, c["seeds"][1])
+        ids, labels = synth.make_batch(spec, c["batch"], c["seq"], c["seeds"][2])
+        r = model_case.run_reference_step(spec, params, lora, ids, labels, **STEP)
+        store[f"{name}/loss"] = r["loss"]
+        for i, g in enumerate(r["grads"]):
+            if g is not None:
+                store[f"{name}/grad/{i}"] = g
+        for i, a in enumerate(r["lora_after"]):
+            store[f"{name}/after/{i}"] = a
+        print(name, "loss", r["loss"], "tensors", len(lora))
+    out = Path(__file__).with_name("model_golden.npz")
+    np.savez_compressed(out, **store)
+    print(out, out.stat().st_size, "bytes")
+
+
 if __name__ == "__main__":
     main()
+    make_model_golden()
