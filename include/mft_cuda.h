@@ -198,6 +198,13 @@ int32_t mft_gemm_nt(const void* a_bf16, int64_t lda, const void* b_bf16, int64_t
                     const float* bias, float alpha,
                     void* d, int64_t ldd, int32_t d_dtype, int32_t accumulate,
                     mft_stream_t stream);
+/* Measurement aid: while enabled, every tensor-core GEMM launch (mft_gemm_nt and the GEMMs inside
+ * the lm-head routines) is bracketed by CUDA events on its stream.  The report sums the
+ * executed MACs*2 (including the LoRA k-block) and the device time over the launches recorded
+ * since the last call of mft_profile_gemm. */
+int32_t mft_profile_gemm(int32_t enable);
+int32_t mft_profile_gemm_report(double* flops_host, double* ms_host, int64_t* launches_host);
+
 /* "TN" product with the long dimension contracted (the LoRA weight gradients
  * dA = s*X^T*(dY*B^T), dB = s*(X*A)^T*dY of the generic MatmulBackward):
  *     out[p,q] (+)= alpha * sum_t U[t,p]*V[t,q]

@@ -79,6 +79,8 @@ _SIGS = {
     "mft_repeat_kv": [vp, i32, vp, i64, i64, i64, i64, i64, vp],
     "mft_repeat_kv_bwd": [vp, vp, i64, i64, i64, i64, i64, vp],
     "mft_gemm_nt": [vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, f32, vp, i64, i32, i32, vp],
+    "mft_profile_gemm": [i32],
+    "mft_profile_gemm_report": [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(i64)],
     "mft_gemm_tn_acc": [vp, i64, vp, i64, i64, i64, i64, f32, vp, i64, vp],
     "mft_pack_blocks_bf16": [vp, i32, vp],
     "mft_accumulate_blocks_f32": [vp, i32, vp],

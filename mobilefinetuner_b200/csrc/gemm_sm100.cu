@@ -15,6 +15,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "gemm_sm100.h"
@@ -393,7 +394,26 @@ static int pick_bn(int64_t n) {
     return best;
 }
 
+// ---- optional per-launch timing (bench / profiling only): CUDA events around every GEMM launch
+struct ProfEntry { cudaEvent_t e0, e1; double flops; };
+static std::vector<ProfEntry> g_prof;
+static bool g_prof_on = false;
+
+static int32_t gemm_nt_run_inner(const GemmCall& c, cudaStream_t stream);
+
 int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream) {
+    if (!g_prof_on) return gemm_nt_run_inner(c, stream);
+    ProfEntry e;
+    cudaEventCreate(&e.e0); cudaEventCreate(&e.e1);
+    e.flops = 2.0 * (double)c.m * (double)c.n * ((double)c.k + (double)c.k2);
+    cudaEventRecord(e.e0, stream);
+    const int32_t s = gemm_nt_run_inner(c, stream);
+    cudaEventRecord(e.e1, stream);
+    g_prof.push_back(e);
+    return s;
+}
+
+static int32_t gemm_nt_run_inner(const GemmCall& c, cudaStream_t stream) {
     MFT_CHECK_ARG(c.a && c.b && c.m > 0 && c.n > 0 && c.k > 0, "gemm_nt: bad argument");
     MFT_CHECK_ARG(c.m < (1ll << 31) && c.n < (1ll << 31) && c.k < (1ll << 31), "gemm_nt: dimension too large");
     MFT_CHECK_ARG(c.epi == EPI_CE_STATS || c.d, "gemm_nt: null output");
@@ -430,6 +450,26 @@ int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream) {
 }  // namespace mft
 
 using namespace mft;
+
+extern "C" int32_t mft_profile_gemm(int32_t enable) {
+    for (auto& e : g_prof) { cudaEventDestroy(e.e0); cudaEventDestroy(e.e1); }
+    g_prof.clear();
+    g_prof_on = enable != 0;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_profile_gemm_report(double* flops, double* ms, int64_t* launches) {
+    MFT_CHECK_ARG(flops && ms && launches, "mft_profile_gemm_report: null pointer");
+    double f = 0, t = 0;
+    for (auto& e : g_prof) {
+        if (int32_t s = check_cuda(cudaEventSynchronize(e.e1), "profile sync")) return s;
+        float dt = 0.f;
+        cudaEventElapsedTime(&dt, e.e0, e.e1);
+        f += e.flops; t += dt;
+    }
+    *flops = f; *ms = t; *launches = (int64_t)g_prof.size();
+    return MFT_OK;
+}
 
 extern "C" int32_t mft_gemm_nt(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,
                                const void* a2, int64_t lda2, const void* b2, int64_t ldb2, int64_t k2, const float* bias,

@@ -43,7 +43,7 @@ def make_params(spec: ModelSpec, seed: int, norm_jitter: float = 0.0) -> list[np
     embed = None
     for kind, shape in spec.param_shapes():
         if kind in ("wte", "wpe", "embed", "linear", "bias"):
-            a = (g.standard_normal(shape) * 0.02).astype(f32)
+            a = g.standard_normal(shape, dtype=f32) * f32(0.02)
             if spec.weights_bf16 and kind != "bias":
                 a = bf16_round(a)
             if kind in ("wte", "embed"):
