@@ -38,6 +38,7 @@ struct GemmParams {
     long long ldd;
     int d_is_f32;
     int accumulate;
+    int tma_store;                // bf16 D written through shared memory + TMA tensor stores
     int32_t* status;
     // cross-entropy epilogues (lm head): see lmhead_ce.cu
     const int32_t* ce_tgt;        // [m] shifted label per row, -1 = row not scored
@@ -57,21 +58,24 @@ struct GemmCfg {
     static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
     static constexpr int B_BYTES = BN * GEMM_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;   // two accumulators; power of two >= 32
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8));
+    static constexpr int TMEM_COLS = (BN > 128) ? 512 : 2 * BN;     // two accumulators; a power of two >= 32
+    static constexpr int STORE_BOX_BYTES = 32 * 64 * 2;               // 32 rows x 64 bf16 columns
+    static constexpr int STORE_BYTES = 4 * 2 * STORE_BOX_BYTES;       // 4 epilogue warps x 2 buffers
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atoms (8 rows x 128 B)
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint8_t* store_smem = tiles + Cfg::STAGES * Cfg::STAGE_BYTES;   // 1024-byte aligned: STAGE_BYTES is a multiple of 1024
+    uint64_t* bars = reinterpret_cast<uint64_t*>(store_smem + Cfg::STORE_BYTES);
     uint64_t* full_bar = bars;                         // [STAGES]
     uint64_t* empty_bar = bars + Cfg::STAGES;          // [STAGES]
     uint64_t* tmem_full_bar = bars + 2 * Cfg::STAGES;  // [2]
@@ -169,6 +173,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int q = warp & 3;                    // tensor-memory lane quarter this warp may read
         const int row_in_tile = q * 32 + lane;
         int it = 0;
+        int box_ctr = 0;
         bool ok = true;
         const bool vec_ok = p.d_is_f32 ? ((p.ldd % 4) == 0 && (reinterpret_cast<uintptr_t>(p.d) % 16) == 0)
                                        : ((p.ldd % 8) == 0 && (reinterpret_cast<uintptr_t>(p.d) % 16) == 0);
@@ -181,7 +186,67 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int row = m0 + row_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            if constexpr (EPI == EPI_STORE) {
+            if (EPI != EPI_CE_STATS && p.tma_store) {
+                // ---- bf16 output: registers -> swizzled shared-memory box (32 rows x 64 columns) -> TMA tensor store
+                float lse = 0.f, coef = 0.f;
+                int tgt = -1;
+                if constexpr (EPI == EPI_CE_GRAD) {
+                    if (row < p.m) {
+                        tgt = p.ce_tgt[row];
+                        lse = p.ce_lse[row];
+                        const long long nv = p.ce_nvalid_override > 0 ? p.ce_nvalid_override : (long long)*p.ce_nvalid;
+                        coef = (tgt >= 0 && nv > 0) ? p.ce_dloss / (float)nv : 0.f;
+                        tgt -= p.ce_col_offset;
+                    }
+                }
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 64) {
+                    if (n0 + c >= p.n) break;          // uniform across the warp
+                    uint8_t* buf = store_smem + (q * 2 + (box_ctr & 1)) * Cfg::STORE_BOX_BYTES;
+                    const uint32_t buf_addr = smem_u32(buf) + (uint32_t)lane * 128u;
+                    if (lane == 0) tma_store_wait_read<1>();   // the store that last used this buffer has read it
+                    __syncwarp();
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(taddr + (uint32_t)(c + half * 32), r);
+                        tmem_ld_wait();
+                        const int col0 = n0 + c + half * 32;
+                        float v[32];
+                        if constexpr (EPI == EPI_STORE) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                            if (p.bias) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const float pr = __expf(__uint_as_float(r[j]) * p.alpha - lse);
+                                v[j] = (pr - (col0 + j == tgt ? 1.f : 0.f)) * coef;
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t pos = (uint32_t)((half * 4 + j) ^ (lane & 7));   // 128-byte swizzle
+                            const __nv_bfloat162 w0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+                            const __nv_bfloat162 w1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                            const __nv_bfloat162 w2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                            const __nv_bfloat162 w3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                            st_shared_v4(buf_addr + pos * 16u, *reinterpret_cast<const uint32_t*>(&w0), *reinterpret_cast<const uint32_t*>(&w1),
+                                         *reinterpret_cast<const uint32_t*>(&w2), *reinterpret_cast<const uint32_t*>(&w3));
+                        }
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&map_d, buf, n0 + c, m0 + q * 32);   // rows / columns outside D are clipped
+                        tma_store_commit();
+                    }
+                    ++box_ctr;
+                }
+            } else if constexpr (EPI == EPI_STORE) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
                     if (n0 + c >= p.n) break;          // uniform across the warp
@@ -305,6 +370,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
         }
+        if (lane == 0) tma_store_wait<0>();   // every tensor store of this warp has completed
     }
 
     // ------------------------------------------------ teardown
@@ -365,7 +431,7 @@ int num_sms() {
 }
 
 template <int BN, int EPI>
-static int32_t launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2,
+static int32_t launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2, const CUtensorMap& md,
                            GemmParams p, cudaStream_t stream) {
     using Cfg = GemmCfg<BN>;
     static bool configured = false;
@@ -377,17 +443,17 @@ static int32_t launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const C
     p.num_n_tiles = (p.n + BN - 1) / BN;
     const int tiles = p.num_m_tiles * p.num_n_tiles;
     const int grid = tiles < num_sms() ? tiles : num_sms();
-    gemm_nt_kernel<BN, EPI><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, p);
+    gemm_nt_kernel<BN, EPI><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, md, p);
     MFT_LAUNCH_CHECK("gemm_nt");
     return MFT_OK;
 }
 
 static int pick_bn(int64_t n) {
     // padded columns weighted by a rough per-tile efficiency: wide tiles amortise the A loads
-    const int cand[3] = {256, 128, 64};
-    const double eff[3] = {1.0, 1.08, 1.35};
+    const int cand[4] = {256, 192, 128, 64};
+    const double eff[4] = {1.0, 1.05, 1.5, 2.5};   // narrow tiles are bound by shared-memory operand traffic
     int best = 256; double best_cost = 1e30;
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < 4; ++i) {
         const double cost = (double)((n + cand[i] - 1) / cand[i] * cand[i]) * eff[i];
         if (cost < best_cost) { best_cost = cost; best = cand[i]; }
     }
@@ -432,19 +498,27 @@ static int32_t gemm_nt_run_inner(const GemmCall& c, cudaStream_t stream) {
     } else {
         ma2 = ma; mb2 = mb;
     }
+    // bf16 outputs go through shared memory and TMA tensor stores (coalesced 128-byte rows, edges clipped by the
+    // tensor map); f32 / accumulating outputs and oddly strided D keep the direct register -> global path
+    CUtensorMap md = ma;
+    const bool tma_store = c.epi != EPI_CE_STATS && !c.d_is_f32 && (c.ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(c.d) % 16 == 0);
+    if (tma_store) {
+        if (int32_t s = make_tmap_bf16(&md, c.d, c.m, c.n, c.ldd, 32)) return s;
+    }
     GemmParams p{};
     p.m = (int)c.m; p.n = (int)c.n; p.k = (int)c.k; p.k2 = (int)c.k2;
     p.alpha = c.alpha; p.bias = c.bias; p.d = c.d; p.ldd = c.ldd;
-    p.d_is_f32 = c.d_is_f32; p.accumulate = c.accumulate;
+    p.d_is_f32 = c.d_is_f32; p.accumulate = c.accumulate; p.tma_store = tma_store ? 1 : 0;
     p.status = device_status_word();
     p.ce_tgt = c.ce_tgt; p.ce_lse = c.ce_lse; p.ce_nvalid = c.ce_nvalid; p.ce_nvalid_override = c.ce_nvalid_override;
     p.ce_dloss = c.ce_dloss; p.ce_col_offset = c.ce_col_offset; p.ce_partials = c.ce_partials;
     p.ce_partial_ld = c.ce_partial_ld; p.ce_tgt_logit = c.ce_tgt_logit;
-    if (c.epi == EPI_CE_STATS) return launch_gemm<CE_TILE_N, EPI_CE_STATS>(ma, mb, ma2, mb2, p, stream);
-    if (c.epi == EPI_CE_GRAD) return launch_gemm<CE_TILE_N, EPI_CE_GRAD>(ma, mb, ma2, mb2, p, stream);
-    if (bn == 256) return launch_gemm<256, EPI_STORE>(ma, mb, ma2, mb2, p, stream);
-    if (bn == 128) return launch_gemm<128, EPI_STORE>(ma, mb, ma2, mb2, p, stream);
-    return launch_gemm<64, EPI_STORE>(ma, mb, ma2, mb2, p, stream);
+    if (c.epi == EPI_CE_STATS) return launch_gemm<CE_TILE_N, EPI_CE_STATS>(ma, mb, ma2, mb2, md, p, stream);
+    if (c.epi == EPI_CE_GRAD) return launch_gemm<CE_TILE_N, EPI_CE_GRAD>(ma, mb, ma2, mb2, md, p, stream);
+    if (bn == 256) return launch_gemm<256, EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);
+    if (bn == 192) return launch_gemm<192, EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);
+    if (bn == 128) return launch_gemm<128, EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);
+    return launch_gemm<64, EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);
 }
 
 }  // namespace mft

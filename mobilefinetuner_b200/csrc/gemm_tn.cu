@@ -11,7 +11,8 @@ namespace mft {
 
 constexpr int TN_PT = 128;      // p-tile
 constexpr int TN_QT = 64;       // q-tile
-constexpr int TN_TC = 32;       // tokens per pipeline step
+constexpr int TN_TC = 64;       // tokens per pipeline step
+constexpr int TN_STAGES = 3;    // cp.async ring depth
 constexpr int TN_THREADS = 256;
 constexpr int TN_US = TN_PT + 8;   // padded row strides (elements): conflict-free ldmatrix
 constexpr int TN_VS = TN_QT + 8;
@@ -40,8 +41,11 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 __global__ void __launch_bounds__(TN_THREADS)
 gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bfloat16* __restrict__ V, int64_t ldv,
                int64_t T, int P, int Q, float alpha, float* __restrict__ out, int64_t ldo, int64_t t_per_split) {
-    __shared__ __align__(16) __nv_bfloat16 Us[2][TN_TC][TN_US];
-    __shared__ __align__(16) __nv_bfloat16 Vs[2][TN_TC][TN_VS];
+    extern __shared__ __align__(16) uint8_t tn_smem[];
+    typedef __nv_bfloat16 (*UsT)[TN_TC][TN_US];
+    typedef __nv_bfloat16 (*VsT)[TN_TC][TN_VS];
+    UsT Us = reinterpret_cast<UsT>(tn_smem);
+    VsT Vs = reinterpret_cast<VsT>(tn_smem + sizeof(__nv_bfloat16) * TN_STAGES * TN_TC * TN_US);
     const int p0 = blockIdx.x * TN_PT, q0 = blockIdx.y * TN_QT;
     const int64_t t_begin = (int64_t)blockIdx.z * t_per_split;
     const int64_t t_end = min(T, t_begin + t_per_split);
@@ -71,12 +75,16 @@ gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bflo
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-    load_step(0, 0);
+    // prologue: fill STAGES-1 slots (empty commit groups keep the group count uniform)
+    for (int s = 0; s < TN_STAGES - 1; ++s) {
+        if (s < nsteps) load_step(s, s); else cp_async_commit();
+    }
     for (int step = 0; step < nsteps; ++step) {
-        const int buf = step & 1;
-        if (step + 1 < nsteps) { load_step(step + 1, buf ^ 1); cp_async_wait<1>(); }
-        else cp_async_wait<0>();
-        __syncthreads();
+        const int buf = step % TN_STAGES;
+        cp_async_wait<TN_STAGES - 2>();      // the group of `step` has landed
+        __syncthreads();                     // ...for every thread, and slot (step-1)%STAGES is free again
+        if (step + TN_STAGES - 1 < nsteps) load_step(step + TN_STAGES - 1, (step + TN_STAGES - 1) % TN_STAGES);
+        else cp_async_commit();
 #pragma unroll
         for (int kk = 0; kk < TN_TC; kk += 16) {
             uint32_t a[4];
@@ -95,7 +103,6 @@ gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bflo
                 mma_bf16_16816(acc[nb + 1], a, b[2], b[3]);
             }
         }
-        __syncthreads();
     }
     const int g = lane >> 2, tq = lane & 3;
 #pragma unroll
@@ -124,8 +131,8 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
     MFT_CHECK_ARG(ldo >= q && p < (1 << 30) && q < (1 << 30), "mft_gemm_tn_acc: bad leading dimension");
     const int tiles_p = (int)((p + TN_PT - 1) / TN_PT), tiles_q = (int)((q + TN_QT - 1) / TN_QT);
     const int64_t tiles = (int64_t)tiles_p * tiles_q;
-    int64_t splits = (148 * 4 + tiles - 1) / tiles;
-    const int64_t max_splits = (t + 4 * TN_TC - 1) / (4 * TN_TC);
+    int64_t splits = (148 * 6 + tiles - 1) / tiles;
+    const int64_t max_splits = (t + 2 * TN_TC - 1) / (2 * TN_TC);
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
     if (splits > 65535) splits = 65535;
@@ -134,7 +141,13 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
     splits = (t + t_per - 1) / t_per;
     MFT_CHECK_ARG(tiles_q <= 65535, "mft_gemm_tn_acc: Q too large");
     dim3 grid((unsigned)tiles_p, (unsigned)tiles_q, (unsigned)splits);
-    gemm_tn_kernel<<<grid, TN_THREADS, 0, as_stream(stream)>>>((const __nv_bfloat16*)u, ldu, (const __nv_bfloat16*)v, ldv, t,
+    constexpr int smem = (int)(sizeof(__nv_bfloat16) * TN_STAGES * TN_TC * (TN_US + TN_VS));
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tn smem attr")) return s;
+        configured = true;
+    }
+    gemm_tn_kernel<<<grid, TN_THREADS, smem, as_stream(stream)>>>((const __nv_bfloat16*)u, ldu, (const __nv_bfloat16*)v, ldv, t,
                                                                (int)p, (int)q, alpha, out, ldo, t_per);
     MFT_LAUNCH_CHECK("gemm_tn");
     return MFT_OK;
