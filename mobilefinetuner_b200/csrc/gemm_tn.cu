@@ -40,7 +40,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 
 __global__ void __launch_bounds__(TN_THREADS)
 gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bfloat16* __restrict__ V, int64_t ldv,
-               int64_t T, int P, int Q, float alpha, float* __restrict__ out, int64_t ldo, int64_t t_per_split) {
+               int64_t T, int P, int Q, float alpha, float* __restrict__ out, int64_t stride_p, int64_t stride_q, int64_t t_per_split) {
     extern __shared__ __align__(16) uint8_t tn_smem[];
     typedef __nv_bfloat16 (*UsT)[TN_TC][TN_US];
     typedef __nv_bfloat16 (*VsT)[TN_TC][TN_VS];
@@ -113,7 +113,7 @@ gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bflo
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int q = q0 + nb * 8 + tq * 2 + e;
-                if (p < P && q < Q) atomicAdd(out + (int64_t)p * ldo + q, alpha * acc[nb][h * 2 + e]);
+                if (p < P && q < Q) atomicAdd(out + (int64_t)p * stride_p + (int64_t)q * stride_q, alpha * acc[nb][h * 2 + e]);
             }
         }
     }
@@ -129,7 +129,14 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
     MFT_CHECK_ARG(p % 8 == 0 && q % 8 == 0 && ldu % 8 == 0 && ldv % 8 == 0, "mft_gemm_tn_acc: P, Q and the row strides must be multiples of 8");
     MFT_CHECK_ARG(reinterpret_cast<uintptr_t>(u) % 16 == 0 && reinterpret_cast<uintptr_t>(v) % 16 == 0, "mft_gemm_tn_acc: operands must be 16-byte aligned");
     MFT_CHECK_ARG(ldo >= q && p < (1 << 30) && q < (1 << 30), "mft_gemm_tn_acc: bad leading dimension");
-    const int tiles_p = (int)((p + TN_PT - 1) / TN_PT), tiles_q = (int)((q + TN_QT - 1) / TN_QT);
+    // The kernel streams a 128-column slab of U and a 64-column slab of V: put the wide operand on the U side
+    // (longer contiguous row pieces) and write the result transposed when the operands are swapped.
+    const bool swap = q > p;
+    const void* uu = swap ? v : u; const void* vv = swap ? u : v;
+    const int64_t ldu2 = swap ? ldv : ldu, ldv2 = swap ? ldu : ldv;
+    const int64_t pp = swap ? q : p, qq = swap ? p : q;
+    const int64_t stride_p = swap ? 1 : ldo, stride_q = swap ? ldo : 1;
+    const int tiles_p = (int)((pp + TN_PT - 1) / TN_PT), tiles_q = (int)((qq + TN_QT - 1) / TN_QT);
     const int64_t tiles = (int64_t)tiles_p * tiles_q;
     int64_t splits = (148 * 6 + tiles - 1) / tiles;
     const int64_t max_splits = (t + 2 * TN_TC - 1) / (2 * TN_TC);
@@ -147,8 +154,8 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
         if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tn smem attr")) return s;
         configured = true;
     }
-    gemm_tn_kernel<<<grid, TN_THREADS, smem, as_stream(stream)>>>((const __nv_bfloat16*)u, ldu, (const __nv_bfloat16*)v, ldv, t,
-                                                               (int)p, (int)q, alpha, out, ldo, t_per);
+    gemm_tn_kernel<<<grid, TN_THREADS, smem, as_stream(stream)>>>((const __nv_bfloat16*)uu, ldu2, (const __nv_bfloat16*)vv, ldv2, t,
+                                                                  (int)pp, (int)qq, alpha, out, stride_p, stride_q, t_per);
     MFT_LAUNCH_CHECK("gemm_tn");
     return MFT_OK;
 }
