@@ -262,6 +262,29 @@ int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, mft_strides
                      int64_t batch, int64_t seq, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim,
                      float scale, int64_t window, mft_stream_t stream);
 
+/* Allocation-free variant of mft_attn_bwd.  It has no counterpart in the reference.
+ * Some hosts of this library may not create device memory at the point where they run a
+ * backward pass: code executing inside a memory-budgeted or real-time section, a plugin whose
+ * embedding application owns every allocation, or a caller that simply holds no allocator
+ * handle.  For them the `delta` scratch of mft_attn_bwd ([batch, n_heads, seq] floats) lives in
+ * a fixed 4 MiB array compiled into the library (one copy on every GPU that loads it, kept until
+ * the process exits) and `dkv_acc` is not needed.  Inputs and outputs are still the caller's.
+ *  - limit: batch * n_heads * seq <= 1,048,576; larger problems are rejected with
+ *    MFT_ERR_INVALID_ARG and a message naming mft_attn_bwd as the alternative;
+ *  - the first call on each device looks up the array's device address (no allocation); make
+ *    that first call outside any stream capture;
+ *  - all calls on a device share the one array: calls that may overlap on the GPU (different
+ *    streams, or the same stream from two threads) race on it and must be serialised by the
+ *    caller.  The array keeps the previous call's contents between calls; each call overwrites
+ *    the rows it uses before reading them, so no clearing is required;
+ *  - it calls no cudaMalloc / cudaFree and no allocating library routine. */
+int32_t mft_attn_bwd_noalloc(const void* q, mft_strides_t sq, const void* k, mft_strides_t sk,
+                             const void* v, mft_strides_t sv, const void* o, mft_strides_t so,
+                             const void* d_o, mft_strides_t sdo, const float* lse,
+                             void* dq, void* dk, void* dv,
+                             int64_t batch, int64_t seq, int64_t n_heads, int64_t n_kv_heads, int64_t head_dim,
+                             float scale, int64_t window, mft_stream_t stream);
+
 /* ---- lm head + shifted cross-entropy (lm_cross_entropy core/lm_loss.cpp:268-382,
  *      LMCrossEntropyBackward :75-163, streaming variant :384-481 / :165-266) -
  * hidden bf16 [batch*seq, H]; table bf16 [V, H] (tied embedding); labels int32

@@ -87,6 +87,8 @@ _SIGS = {
     "mft_attn_fwd": [vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, i64, i64, i64, i64, i64, f32, i64, vp],
     "mft_attn_bwd": [vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, vp, vp, vp, vp, vp,
                      i64, i64, i64, i64, i64, f32, i64, vp],
+    "mft_attn_bwd_noalloc": [vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, vp, vp, vp,
+                             i64, i64, i64, i64, i64, f32, i64, vp],
     "mft_lmhead_ce_workspace_bytes": [i64, i64, i64],
     "mft_lmhead_ce_fwd": [vp, vp, vp, i64, i64, i64, i64, i32, vp, vp, vp, vp, vp, i64, vp],
     "mft_lmhead_ce_bwd": [vp, vp, vp, i64, vp, i64, i64, i64, i64, i32, vp, vp, i64, f32, vp, vp, i64, vp],

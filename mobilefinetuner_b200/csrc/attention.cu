@@ -547,3 +547,44 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
 #undef BWD
     return MFT_OK;
 }
+
+// ---------------------------------------------------------------- allocation-free backward
+// Scratch for mft_attn_bwd_noalloc: the per-row sums delta[b,h,i] = sum_d O*dO live in this
+// fixed array instead of a caller-supplied buffer.  Every GPU that loads the library holds
+// these 4 MiB until the process exits.
+constexpr int64_t MFT_ATTN_NOALLOC_MAX_ROWS = 1 << 20;
+static __device__ __align__(256) float g_attn_noalloc_delta[MFT_ATTN_NOALLOC_MAX_ROWS];
+
+#include <mutex>
+
+extern "C" int32_t mft_attn_bwd_noalloc(const void* q, mft_strides_t sq, const void* k, mft_strides_t sk, const void* v,
+                                        mft_strides_t sv, const void* o, mft_strides_t so, const void* d_o, mft_strides_t sdo,
+                                        const float* lse, void* dq, void* dk, void* dv, int64_t batch, int64_t seq,
+                                        int64_t n_heads, int64_t n_kv, int64_t hd, float scale, int64_t window,
+                                        mft_stream_t stream) {
+    MFT_CHECK_ARG(batch > 0 && seq > 0 && n_heads > 0, "mft_attn_bwd_noalloc: bad size");
+    if (batch * n_heads * seq > MFT_ATTN_NOALLOC_MAX_ROWS)
+        return fail(MFT_ERR_INVALID_ARG, "mft_attn_bwd_noalloc: batch*n_heads*seq = " + std::to_string(batch * n_heads * seq) +
+                                             " exceeds the built-in scratch of " + std::to_string(MFT_ATTN_NOALLOC_MAX_ROWS) +
+                                             " rows; use mft_attn_bwd with a caller-supplied delta buffer");
+    // The array's name is only a host-side handle: kernels need its device address, which differs per GPU.
+    // Resolve it once per device, with that device current (this is the set-up the first call performs).
+    static std::mutex mu;
+    static float* dev_ptr[64] = {};
+    int dev = 0;
+    if (int32_t s = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return s;
+    MFT_CHECK_ARG(dev >= 0 && dev < 64, "mft_attn_bwd_noalloc: device index out of range");
+    float* delta = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!dev_ptr[dev]) {
+            void* p = nullptr;
+            if (int32_t s = check_cuda(cudaGetSymbolAddress(&p, g_attn_noalloc_delta), "cudaGetSymbolAddress(attention scratch)")) return s;
+            dev_ptr[dev] = static_cast<float*>(p);
+        }
+        delta = dev_ptr[dev];
+    }
+    // Every row the kernels read is first overwritten by the delta kernel of this call, so nothing needs clearing.
+    return mft_attn_bwd(q, sq, k, sk, v, sv, o, so, d_o, sdo, lse, dq, dk, dv, delta, nullptr, batch, seq, n_heads, n_kv, hd, scale,
+                        window, stream);
+}

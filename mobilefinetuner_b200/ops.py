@@ -188,6 +188,21 @@ def attention_bwd(q, k, v, o, d_o, lse, scale, window=0):
     return dq, dk, dv
 
 
+def attention_bwd_noalloc(q, k, v, o, d_o, lse, scale, window=0):
+    """attention_bwd for callers that cannot allocate device memory: the row-sum scratch is a fixed
+    array inside the library (at most 2**20 rows = batch * heads * seq).  The outputs are written
+    into tensors the caller made beforehand; here they are created up front only for convenience."""
+    _init(q)
+    b, nh, s, hd = q.shape
+    nkv = k.shape[1]
+    dq = torch.empty_strided(q.shape, q.stride(), device=q.device, dtype=BF16)
+    dk = torch.empty_strided(k.shape, k.stride(), device=q.device, dtype=BF16)
+    dv = torch.empty_strided(v.shape, v.stride(), device=q.device, dtype=BF16)
+    L.call("mft_attn_bwd_noalloc", _p(q), _strides_bhsd(q), _p(k), _strides_bhsd(k), _p(v), _strides_bhsd(v), _p(o), _strides_bhsd(o),
+           _p(d_o), _strides_bhsd(d_o), _p(lse), _p(dq), _p(dk), _p(dv), b, s, nh, nkv, hd, float(scale), int(window), _stream())
+    return dq, dk, dv
+
+
 # ---------------------------------------------------------------- lm head + CE
 class LmHeadCE:
     """Shifted-label cross entropy over hidden x table^T (the logits never hit memory)."""
