@@ -233,8 +233,9 @@ def run_ours(args):
     roofline = None
     if world.rank == 0:
         L.call("mft_profile_gemm", 1)
-        step_resident(0)
-        torch.cuda.synchronize()
+    step_resident(0)                 # every rank runs it: the step contains the gradient all-reduce
+    torch.cuda.synchronize()
+    if world.rank == 0:
         fl, tms, n = C.c_double(), C.c_double(), C.c_int64()
         L.call("mft_profile_gemm_report", C.byref(fl), C.byref(tms), C.byref(n))
         L.call("mft_profile_gemm", 0)

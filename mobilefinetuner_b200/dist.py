@@ -5,6 +5,7 @@ summed bucket IS the global-batch mean gradient).  torch.distributed (NCCL on GP
 tests) carries the collective; nothing else crosses ranks."""
 from __future__ import annotations
 
+import datetime
 import os
 
 import numpy as np
@@ -25,7 +26,9 @@ class World:
             if self.backend == "nccl":
                 torch.cuda.set_device(self.local_rank)
                 kw["device_id"] = torch.device("cuda", self.local_rank)
-            dist.init_process_group(self.backend, rank=self.rank, world_size=self.size, **kw)
+            # a short timeout: a rank that never joins a collective ends the job with an error instead of a long hang
+            timeout = datetime.timedelta(seconds=int(os.environ.get("MFT_DIST_TIMEOUT_S", "120")))
+            dist.init_process_group(self.backend, rank=self.rank, world_size=self.size, timeout=timeout, **kw)
 
     @property
     def device(self):
