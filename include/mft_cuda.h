@@ -337,6 +337,48 @@ int32_t mft_adam_step(float* params, float* grads, float* m, float* v, int64_t n
                       const float* sqnorm_dev, float max_norm, float clip_eps, int32_t zero_grad,
                       mft_stream_t stream);
 
+/* ---- generic fp32 operators behind the eager ops:: surface (add/sub/mul/div with broadcasting
+ *      ops.cpp:299-560, unary maps :1221-1305, sum/mean :1970-2127, transpose/permute :990-1149,
+ *      matmul :619-988 in full fp32, softmax :1307-1363 / SoftmaxBackward backward_functions.cpp:306-349,
+ *      apply_rope on [B,H,S,D] :2337-2414, swiglu :2416-2452).  Contiguous tensors, fp32 accuracy. ---- */
+#define MFT_EW_ADD 0
+#define MFT_EW_SUB 1
+#define MFT_EW_MUL 2
+#define MFT_EW_DIV 3
+#define MFT_UN_GELU 0
+#define MFT_UN_GELU_GRAD 1
+#define MFT_UN_SILU 2
+#define MFT_UN_SIGMOID 3
+#define MFT_UN_TANH 4
+#define MFT_UN_RELU 5
+#define MFT_UN_EXP 6
+#define MFT_UN_LOG 7
+#define MFT_UN_SQRT 8
+#define MFT_UN_ABS 9
+#define MFT_UN_POW 10
+#define MFT_UN_NEG 11
+#define MFT_UN_COPY 12
+/* out = a (op) b with right-aligned (numpy-style) broadcasting; at most 6 dimensions. */
+int32_t mft_ew_binary_f32(int32_t op, const float* a, const int64_t* a_shape_host, int32_t a_nd,
+                          const float* b, const int64_t* b_shape_host, int32_t b_nd,
+                          float* out, const int64_t* out_shape_host, int32_t out_nd, mft_stream_t stream);
+int32_t mft_ew_scalar_f32(int32_t op, const float* a, float scalar, int32_t scalar_first, float* out, int64_t n, mft_stream_t stream);
+int32_t mft_ew_unary_f32(int32_t op, const float* a, float param, float* out, int64_t n, mft_stream_t stream);
+/* out[o, i] = scale * sum_r in[o, r, i] */
+int32_t mft_reduce_sum_f32(const float* in, float* out, int64_t outer, int64_t reduce, int64_t inner, float scale, mft_stream_t stream);
+/* out = in permuted: out dim k is in dim perm[k]; 32-bit elements of any type. */
+int32_t mft_permute_b32(const void* in, void* out, const int64_t* in_shape_host, const int32_t* perm_host, int32_t nd, mft_stream_t stream);
+/* C[b] (m x n) = A[b] (m x k) * B[b] with B [k,n] (trans_b = 0) or [n,k] (trans_b = 1); batch strides in elements (0 = shared). */
+int32_t mft_matmul_f32(const float* a, const float* b, float* c, int64_t batch, int64_t m, int64_t n, int64_t k,
+                       int64_t stride_a, int64_t stride_b, int64_t stride_c, int32_t trans_b, mft_stream_t stream);
+int32_t mft_softmax_f32(const float* x, float* y, int64_t rows, int64_t dim, mft_stream_t stream);
+int32_t mft_softmax_bwd_f32(const float* y, const float* dy, float* dx, int64_t rows, int64_t dim, mft_stream_t stream);
+/* x, y: [rows, seq, head_dim] f32 (rows = batch*heads); backward != 0 applies the transposed rotation. */
+int32_t mft_rope_f32(const float* x, float* y, const float* cos_tab, const float* sin_tab, int64_t rows, int64_t seq,
+                     int64_t head_dim, int32_t backward, mft_stream_t stream);
+/* dy == NULL: out1 = silu(gate)*up.  Otherwise out1 = d(gate), out2 = d(up). */
+int32_t mft_swiglu_f32(const float* gate, const float* up, const float* dy, float* out1, float* out2, int64_t n, mft_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

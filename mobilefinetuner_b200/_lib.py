@@ -95,6 +95,16 @@ _SIGS = {
     "mft_ce_dense_fwd": [vp, vp, i64, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp],
     "mft_ce_dense_bwd": [vp, vp, i64, i64, i64, vp, vp, f32, vp, vp],
     "mft_grad_sqnorm": [vp, i64, vp, vp],
+    "mft_ew_binary_f32": [i32, vp, vp, i32, vp, vp, i32, vp, vp, i32, vp],
+    "mft_ew_scalar_f32": [i32, vp, f32, i32, vp, i64, vp],
+    "mft_ew_unary_f32": [i32, vp, f32, vp, i64, vp],
+    "mft_reduce_sum_f32": [vp, vp, i64, i64, i64, f32, vp],
+    "mft_permute_b32": [vp, vp, vp, vp, i32, vp],
+    "mft_matmul_f32": [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i32, vp],
+    "mft_softmax_f32": [vp, vp, i64, i64, vp],
+    "mft_softmax_bwd_f32": [vp, vp, vp, i64, i64, vp],
+    "mft_rope_f32": [vp, vp, vp, vp, i64, i64, i64, i32, vp],
+    "mft_swiglu_f32": [vp, vp, vp, vp, vp, i64, vp],
     # ---- include/mft_step.h
     "mft_model_create": [C.POINTER(ModelConfig), vp, C.POINTER(vp)],
     "mft_model_destroy": [vp],

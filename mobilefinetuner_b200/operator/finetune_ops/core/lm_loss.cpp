@@ -1,0 +1,56 @@
+#include "lm_loss.h"
+
+#include <stdexcept>
+
+#include "../../../../include/mft_cuda.h"
+#include "ops.h"
+
+namespace ops {
+
+using detail::check;
+using detail::stream;
+
+TensorPtr lm_cross_entropy(const TensorPtr& logits, const TensorPtr& labels, int ignore_index, const std::string& reduction) {
+    if (!logits || !labels) throw std::runtime_error("lm_cross_entropy: null tensor");
+    if (logits->dtype() != kFloat32 || labels->dtype() != kInt32) throw std::runtime_error("lm_cross_entropy: expects float32 logits and int32 labels");
+    if (logits->shape().size() != 3 || labels->shape().size() != 2) throw std::runtime_error("lm_cross_entropy: expects logits [B,S,V] and labels [B,S]");
+    if (reduction != "mean" && reduction != "sum") throw std::runtime_error("lm_cross_entropy: reduction must be 'mean' or 'sum' on this backend");
+    const int64_t B = logits->shape()[0], S = logits->shape()[1], V = logits->shape()[2];
+    if (labels->shape()[0] != B || labels->shape()[1] != S) throw std::runtime_error("lm_cross_entropy: labels shape mismatch");
+    auto loss = std::make_shared<Tensor>(std::vector<int64_t>{1}, kFloat32, kCPU);
+    auto n_valid = std::make_shared<Tensor>(std::vector<int64_t>{1}, kInt32, kCPU);
+    auto lse = std::make_shared<Tensor>(std::vector<int64_t>{B * S}, kFloat32, kCPU);
+    auto tgt = std::make_shared<Tensor>(std::vector<int64_t>{B * S}, kInt32, kCPU);
+    auto acc = std::make_shared<Tensor>(std::vector<int64_t>{2}, kFloat32, kCPU);      // 8 bytes: one double
+    auto status = std::make_shared<Tensor>(std::vector<int64_t>{1}, kInt32, kCPU);
+    check(mft_ce_dense_fwd((const float*)logits->device_read(), (const int32_t*)labels->device_read(), B, S, V, ignore_index, (float*)loss->device_write(),
+                           (int32_t*)n_valid->device_write(), (float*)lse->device_write(), (int32_t*)tgt->device_write(), (double*)acc->device_write(),
+                           (int32_t*)status->device_readwrite(), stream()), "lm_cross_entropy");
+    if (status->data<int32_t>()[0] != 0) throw std::runtime_error("lm_cross_entropy: label out of range");
+    const int32_t n = n_valid->data<int32_t>()[0];
+    const bool is_sum = reduction == "sum";
+    if (is_sum) loss->data<float>()[0] = n > 0 ? loss->data<float>()[0] * (float)n : 0.0f;
+    register_backward(loss, {logits}, std::make_shared<ClosureBackward>([logits, tgt, lse, n_valid, B, S, V, is_sum, n](const TensorPtr& g) {
+        auto d = std::make_shared<Tensor>(logits->shape(), kFloat32, kCPU);
+        const float outer = g ? g->data<float>()[0] : 1.0f;
+        check(mft_ce_dense_bwd((const float*)logits->device_read(), (const int32_t*)tgt->device_read(), B, S, V, (const float*)lse->device_read(),
+                               (const int32_t*)n_valid->device_read(), is_sum ? outer * (float)n : outer, (float*)d->device_write(), stream()),
+              "lm_cross_entropy backward");
+        return std::vector<TensorPtr>{d};
+    }));
+    return loss;
+}
+
+TensorPtr selected_token_lm_cross_entropy(const TensorPtr& hidden, const TensorPtr& W, const TensorPtr& labels, int ignore_index, const std::string& reduction) {
+    if (!hidden || !W || !labels) throw std::runtime_error("selected_token_lm_cross_entropy: null tensor");
+    if (hidden->shape().size() != 3 || W->shape().size() != 2 || W->shape()[1] != hidden->shape()[2])
+        throw std::runtime_error("selected_token_lm_cross_entropy: expects hidden [B,S,H] and weight [V,H]");
+    // fp32 operator path: logits are formed by the generic matmul so that loss and gradients keep fp32 accuracy;
+    // the training step uses the fused tensor-core lm head (mft_lmhead_ce_*), which never materialises them.
+    return lm_cross_entropy(matmul_rhs_T(hidden, W), labels, ignore_index, reduction);
+}
+TensorPtr streaming_lm_cross_entropy(const TensorPtr& hidden, const TensorPtr& W, const TensorPtr& labels, int ignore_index, const std::string& reduction) {
+    return selected_token_lm_cross_entropy(hidden, W, labels, ignore_index, reduction);
+}
+
+}  // namespace ops
