@@ -14,6 +14,7 @@
 // tensor memory.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -29,28 +30,6 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
 
-struct GemmParams {
-    int m, n, k, k2;
-    int num_m_tiles, num_n_tiles;
-    float alpha;
-    const float* bias;
-    void* d;
-    long long ldd;
-    int d_is_f32;
-    int accumulate;
-    int tma_store;                // bf16 D written through shared memory + TMA tensor stores
-    int32_t* status;
-    // cross-entropy epilogues (lm head): see lmhead_ce.cu
-    const int32_t* ce_tgt;        // [m] shifted label per row, -1 = row not scored
-    const float* ce_lse;          // [m] row log-sum-exp (GRAD mode)
-    const int32_t* ce_nvalid;     // device count of scored rows (GRAD mode)
-    long long ce_nvalid_override; // > 0: use instead of *ce_nvalid
-    float ce_dloss;
-    int ce_col_offset;            // vocabulary index of column 0 of this GEMM
-    float2* ce_partials;          // [m, ce_partial_ld] (max, sum exp) per row and column tile (STATS mode)
-    int ce_partial_ld;
-    float* ce_tgt_logit;          // [m] logit of the label column (STATS mode)
-};
 
 
 template <int BN>
@@ -113,8 +92,8 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % p.num_m_tiles) * GEMM_BM;
-                const int n0 = (tile / p.num_m_tiles) * BN;
+                const int m0 = tile_m(tile, p) * GEMM_BM;
+                const int n0 = tile_n(tile, p) * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
@@ -180,8 +159,8 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            const int m0 = (tile % p.num_m_tiles) * GEMM_BM;
-            const int n0 = (tile / p.num_m_tiles) * BN;
+            const int m0 = tile_m(tile, p) * GEMM_BM;
+            const int n0 = tile_n(tile, p) * BN;
             if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + row_in_tile;
@@ -480,6 +459,12 @@ int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream) {
 }
 
 static int32_t gemm_nt_run_inner(const GemmCall& c, cudaStream_t stream) {
+    // CTA-pair kernel first (256 x 256 cluster tiles); MFT_GEMM_2CTA=0 selects the single-CTA kernel everywhere
+    static const int use_pair = [] { const char* e = std::getenv("MFT_GEMM_2CTA"); return e ? std::atoi(e) : 1; }();
+    if (use_pair && device_status_word()) {
+        const int32_t s2 = gemm_nt_run_2cta(c, stream);
+        if (s2 != MFT_ERR_UNSUPPORTED) return s2;
+    }
     MFT_CHECK_ARG(c.a && c.b && c.m > 0 && c.n > 0 && c.k > 0, "gemm_nt: bad argument");
     MFT_CHECK_ARG(c.m < (1ll << 31) && c.n < (1ll << 31) && c.k < (1ll << 31), "gemm_nt: dimension too large");
     MFT_CHECK_ARG(c.epi == EPI_CE_STATS || c.d, "gemm_nt: null output");

@@ -35,7 +35,50 @@ struct GemmCall {
     float* ce_tgt_logit = nullptr;
 };
 
+// Kernel-side parameter block (by value in the launch).
+struct GemmParams {
+    int m, n, k, k2;
+    int num_m_tiles, num_n_tiles;
+    float alpha;
+    const float* bias;
+    void* d;
+    long long ldd;
+    int d_is_f32;
+    int accumulate;
+    int tma_store;                // bf16 D written through shared memory + TMA tensor stores
+    int32_t* status;
+    // cross-entropy epilogues (lm head): see lmhead_ce.cu
+    const int32_t* ce_tgt;        // [m] shifted label per row, -1 = row not scored
+    const float* ce_lse;          // [m] row log-sum-exp (GRAD mode)
+    const int32_t* ce_nvalid;     // device count of scored rows (GRAD mode)
+    long long ce_nvalid_override; // > 0: use instead of *ce_nvalid
+    float ce_dloss;
+    int ce_col_offset;            // vocabulary index of column 0 of this GEMM
+    float2* ce_partials;          // [m, ce_partial_ld] (max, sum exp) per row and column tile (STATS mode)
+    int ce_partial_ld;
+    float* ce_tgt_logit;          // [m] logit of the label column (STATS mode)
+};
+
+// Tile order: groups of RASTER_GROUP column tiles, row tiles within a group, columns fastest.  CTAs that run at
+// the same time then share a few A row-panels and a few B column-panels (instead of one B panel and every A panel),
+// which keeps both operands L2-resident when M*K or N*K exceeds the L2.
+constexpr int RASTER_GROUP = 8;
+__host__ __device__ inline int tile_group_width(int tile, const GemmParams& p) {
+    const int g = tile / (RASTER_GROUP * p.num_m_tiles);
+    const int rest = p.num_n_tiles - g * RASTER_GROUP;
+    return rest < RASTER_GROUP ? rest : RASTER_GROUP;
+}
+__host__ __device__ inline int tile_m(int tile, const GemmParams& p) {
+    return (tile % (RASTER_GROUP * p.num_m_tiles)) / tile_group_width(tile, p);
+}
+__host__ __device__ inline int tile_n(int tile, const GemmParams& p) {
+    return (tile / (RASTER_GROUP * p.num_m_tiles)) * RASTER_GROUP + (tile % (RASTER_GROUP * p.num_m_tiles)) % tile_group_width(tile, p);
+}
+
 int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream);
+// CTA-pair (cta_group::2) variant for 256 x 256 cluster tiles; returns MFT_ERR_UNSUPPORTED when the call does not qualify.
+int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream);
+int32_t make_tmap_bf16(struct CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
 int num_sms();
 
 }  // namespace mft

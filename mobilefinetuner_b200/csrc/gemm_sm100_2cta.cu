@@ -1,0 +1,301 @@
+// CTA-pair variant of the bf16 "NT" tcgen05 GEMM: two CTAs of a cluster (two SMs) cooperate on one
+// 256 x 256 output tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and HALF
+// of the B tile (128 of the 256 columns of the output), so the shared-memory operand traffic per SM
+// is 2/3 of the single-CTA kernel's (which is bound by it), while each SM's tensor memory holds the
+// accumulator rows of its own half of the tile.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = tensor-memory allocation and - in the
+// leader CTA (cluster rank 0) only - the one MMA-issuing thread, warps 2..5 = epilogue for this CTA's
+// 128 rows.  Barriers: `full` and `tmem_empty` live in the leader (both CTAs arrive there, the peer
+// through the cluster shared-memory window); `empty` and `tmem_full` exist in both CTAs and are
+// signalled for both by one tcgen05.commit.  TMA loads are plain per-CTA loads (each CTA fetches its
+// own tiles; nothing is broadcast).  All waits are bounded, as in the single-CTA kernel.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace mft {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int BM = 128, BK = 64, BN2 = 256, THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2, BH_BYTES = (BN2 / 2) * BK * 2, STAGE_BYTES = A_BYTES + BH_BYTES;   // 32 KB
+constexpr int STAGES = 6;
+constexpr int STORE_BOX_BYTES = 32 * 64 * 2, STORE_BYTES = 4 * 2 * STORE_BOX_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 + 256;
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;   // clears the bit that distinguishes the two CTAs of a pair: -> address in the leader
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+// per-CTA tile load whose completion bytes are credited to a barrier in the leader CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_addr, int32_t c0, int32_t c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// one arrive on the barrier at the same shared-memory offset in BOTH CTAs of the pair, once all prior MMAs are done
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
+                    const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* store_smem = tiles + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(store_smem + STORE_BYTES);
+    uint64_t* full_bar = bars;                    // [STAGES]  used in the leader
+    uint64_t* empty_bar = bars + STAGES;          // [STAGES]  both CTAs
+    uint64_t* tmem_full_bar = bars + 2 * STAGES;  // [2]       both CTAs
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2; // [2]       used in the leader
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    const int num_clusters = gridDim.x / 2, cluster_id = blockIdx.x / 2;
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles;            // 256 x 256 tiles
+    const int num_kb_main = (p.k + BK - 1) / BK;
+    const int num_kb = num_kb_main + (p.k2 > 0 ? 1 : 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full_bar[b], 1); mbar_init(&tmem_empty_bar[b], 8); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_b); tma_prefetch_desc(&map_d);
+    }
+    __syncthreads();
+    if (warp == 1) { tmem_alloc2(tmem_slot, 512); tmem_relinquish2(); }
+    tc_fence_before();
+    cluster_sync();             // barrier inits of both CTAs are visible before anyone arrives remotely
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer (one per CTA)
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+                const int m0 = tile_m(tile, p) * 2 * BM + (int)rank * BM;
+                const int n0 = tile_n(tile, p) * BN2 + (int)rank * (BN2 / 2);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = tiles + stage * STAGE_BYTES;
+                    uint8_t* sb = sa + A_BYTES;
+                    const uint32_t full_in_leader = smem_u32(&full_bar[stage]) & PEER_MASK;
+                    mbar_arrive_expect_tx_cluster(full_in_leader, STAGE_BYTES);
+                    if (kb < num_kb_main) {
+                        tma_load_2d_pair(sa, &map_a, full_in_leader, kb * BK, m0);
+                        tma_load_2d_pair(sb, &map_b, full_in_leader, kb * BK, n0);
+                    } else {
+                        tma_load_2d_pair(sa, &map_a2, full_in_leader, 0, m0);
+                        tma_load_2d_pair(sb, &map_b2, full_in_leader, 0, n0);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer (leader CTA only)
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN2);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN2;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
+                    const uint64_t adesc = smem_desc_sw128(sa);
+                    const uint64_t bdesc = smem_desc_sw128(sa + A_BYTES);
+                    const int kvalid = (kb < num_kb_main) ? min(BK, p.k - kb * BK) : p.k2;
+                    const int nmma = (kvalid + 15) / 16;
+                    for (int j = 0; j < nmma; ++j)
+                        umma2_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb | j) != 0 ? 1u : 0u);
+                    umma2_commit_both(&empty_bar[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma2_commit_both(&tmem_full_bar[acc]);
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue: this CTA's 128 rows of the pair tile
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        int it = 0, box_ctr = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+            const int acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            const int m0 = tile_m(tile, p) * 2 * BM + (int)rank * BM;
+            const int n0 = tile_n(tile, p) * BN2;
+            if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + row_in_tile;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN2);
+            float lse = 0.f, coef = 0.f;
+            int tgt = -1;
+            if constexpr (EPI == EPI_CE_GRAD) {
+                if (row < p.m) {
+                    tgt = p.ce_tgt[row];
+                    lse = p.ce_lse[row];
+                    const long long nv = p.ce_nvalid_override > 0 ? p.ce_nvalid_override : (long long)*p.ce_nvalid;
+                    coef = (tgt >= 0 && nv > 0) ? p.ce_dloss / (float)nv : 0.f;
+                    tgt -= p.ce_col_offset;
+                }
+            }
+#pragma unroll 1
+            for (int c = 0; c < BN2; c += 64) {
+                if (n0 + c >= p.n) break;
+                uint8_t* buf = store_smem + (q * 2 + (box_ctr & 1)) * STORE_BOX_BYTES;
+                const uint32_t buf_addr = smem_u32(buf) + (uint32_t)lane * 128u;
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + (uint32_t)(c + half * 32), r);
+                    tmem_ld_wait();
+                    const int col0 = n0 + c + half * 32;
+                    float v[32];
+                    if constexpr (EPI == EPI_STORE) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                        if (p.bias) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float pr = __expf(__uint_as_float(r[j]) * p.alpha - lse);
+                            v[j] = (pr - (col0 + j == tgt ? 1.f : 0.f)) * coef;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t pos = (uint32_t)((half * 4 + j) ^ (lane & 7));
+                        const __nv_bfloat162 w0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+                        const __nv_bfloat162 w1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                        const __nv_bfloat162 w2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                        const __nv_bfloat162 w3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                        st_shared_v4(buf_addr + pos * 16u, *reinterpret_cast<const uint32_t*>(&w0), *reinterpret_cast<const uint32_t*>(&w1),
+                                     *reinterpret_cast<const uint32_t*>(&w2), *reinterpret_cast<const uint32_t*>(&w3));
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) { tma_store_2d(&map_d, buf, n0 + c, m0 + q * 32); tma_store_commit(); }
+                ++box_ctr;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc]) & PEER_MASK);   // the accumulator buffer is free (count 8: 4 warps x 2 CTAs)
+        }
+        if (lane == 0) tma_store_wait<0>();
+    }
+
+    // ------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
+    cluster_sync();             // the peer may still be read by the leader's MMAs / written by its commits until here
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, 512);
+    }
+}
+
+template <int EPI>
+int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2, const CUtensorMap& md,
+               GemmParams p, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_2cta_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), "gemm 2cta smem attr")) return s;
+        configured = true;
+    }
+    p.num_m_tiles = (p.m + 2 * BM - 1) / (2 * BM);
+    p.num_n_tiles = (p.n + BN2 - 1) / BN2;
+    const int tiles = p.num_m_tiles * p.num_n_tiles;
+    int clusters = num_sms() / 2;
+    if (tiles < clusters) clusters = tiles;
+    gemm_nt_2cta_kernel<EPI><<<2 * clusters, THREADS, SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, md, p);
+    MFT_LAUNCH_CHECK("gemm_nt_2cta");
+    return MFT_OK;
+}
+
+}  // namespace
+
+int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
+    const bool ok = (c.epi == EPI_STORE || c.epi == EPI_CE_GRAD) && !c.d_is_f32 && !c.accumulate && c.d && (c.ldd % 8 == 0) &&
+                    (reinterpret_cast<uintptr_t>(c.d) % 16 == 0) && c.m >= 256 && c.n >= 192;
+    if (!ok) return MFT_ERR_UNSUPPORTED;
+    CUtensorMap ma, mb, ma2, mb2, md;
+    if (int32_t s = make_tmap_bf16(&ma, c.a, c.m, c.k, c.lda, BM)) return s;
+    if (int32_t s = make_tmap_bf16(&mb, c.b, c.n, c.k, c.ldb, BN2 / 2)) return s;
+    if (c.k2 > 0) {
+        if (int32_t s = make_tmap_bf16(&ma2, c.a2, c.m, c.k2, c.lda2, BM)) return s;
+        if (int32_t s = make_tmap_bf16(&mb2, c.b2, c.n, c.k2, c.ldb2, BN2 / 2)) return s;
+    } else {
+        ma2 = ma; mb2 = mb;
+    }
+    if (int32_t s = make_tmap_bf16(&md, c.d, c.m, c.n, c.ldd, 32)) return s;
+    GemmParams p{};
+    p.m = (int)c.m; p.n = (int)c.n; p.k = (int)c.k; p.k2 = (int)c.k2;
+    p.alpha = c.alpha; p.bias = c.bias; p.d = c.d; p.ldd = c.ldd; p.tma_store = 1;
+    p.status = device_status_word();
+    p.ce_tgt = c.ce_tgt; p.ce_lse = c.ce_lse; p.ce_nvalid = c.ce_nvalid; p.ce_nvalid_override = c.ce_nvalid_override;
+    p.ce_dloss = c.ce_dloss; p.ce_col_offset = c.ce_col_offset;
+    if (c.epi == EPI_CE_GRAD) return launch<EPI_CE_GRAD>(ma, mb, ma2, mb2, md, p, stream);
+    return launch<EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);
+}
+
+}  // namespace mft
