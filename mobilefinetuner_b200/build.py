@@ -88,6 +88,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
     build_operators(force)
+    build_cpp_tests()
     return LIB
 
 
@@ -106,6 +107,21 @@ def build_operators(force: bool = False) -> Path:
     if res.returncode != 0:
         raise RuntimeError(f"building libmft_operators.so failed:\n{res.stdout}\n{res.stderr}")
     return OPERATORS_LIB
+
+
+def build_cpp_tests() -> Path:
+    """Compile tests/cpp/auto_trainer_step.cpp (the C++ API driven like the reference's own AutoTrainer test)."""
+    src = PKG.parent / "tests" / "cpp" / "auto_trainer_step.cpp"
+    exe = OBJ / "auto_trainer_step"
+    if exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, OPERATORS_LIB.stat().st_mtime):
+        return exe
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-std=c++17", "-O1", f"-I{OPERATORS}", f"-I{OPERATORS / 'finetune_ops'}", f"-I{OPERATORS / 'include'}", str(src),
+           f"-L{PKG}", "-lmft_operators", "-lmft_cuda", f"-Wl,-rpath,{PKG}", "-Wl,-rpath,$ORIGIN/../..", "-o", str(exe)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building auto_trainer_step failed:\n{res.stdout}\n{res.stderr}")
+    return exe
 
 
 if __name__ == "__main__":
