@@ -309,6 +309,21 @@ int32_t mft_lmhead_ce_bwd(const void* hidden_bf16, const void* table_bf16, const
                           int32_t ignore_index, const float* lse, const int32_t* n_valid_dev,
                           int64_t n_valid_override, float dloss, void* dhidden_bf16,
                           void* workspace, int64_t workspace_bytes, mft_stream_t stream);
+/* Forward AND backward in one sweep over the vocabulary, for a training step
+ * (the reference runs lm_cross_entropy and, from loss->backward(),
+ * LMCrossEntropyBackward; both recompute or re-read the logits): the logits
+ * are formed once, as un-normalised softmax numerators relative to a per-row
+ * reference value, and folded straight into dHidden; the normalisation is
+ * applied at the end.  Outputs are those of mft_lmhead_ce_fwd (loss_dev,
+ * n_valid_dev, lse) plus dhidden of mft_lmhead_ce_bwd, with the same meaning
+ * of n_valid_override and dloss.  Rows whose logits leave the range the sweep
+ * can represent are detected and recomputed exactly, so results do not depend
+ * on the logits' magnitude.  hidden must be a multiple of 8. */
+int32_t mft_lmhead_ce_fused(const void* hidden_bf16, const void* table_bf16, const void* table_t_bf16,
+                            int64_t table_t_ld, const int32_t* labels, int64_t batch, int64_t seq, int64_t hidden,
+                            int64_t vocab, int32_t ignore_index, int64_t n_valid_override, float dloss,
+                            float* loss_dev, int32_t* n_valid_dev, float* lse, void* dhidden_bf16,
+                            int32_t* status_dev, void* workspace, int64_t workspace_bytes, mft_stream_t stream);
 /* Dense-logits variants (API completeness: lm_cross_entropy on a materialised
  * [batch, seq, V] f32 tensor).  tgt_scratch is int32 [batch*seq] and
  * loss_scratch one double, both device scratch; the forward fills tgt_scratch

@@ -92,6 +92,7 @@ _SIGS = {
     "mft_lmhead_ce_workspace_bytes": [i64, i64, i64],
     "mft_lmhead_ce_fwd": [vp, vp, vp, i64, i64, i64, i64, i32, vp, vp, vp, vp, vp, i64, vp],
     "mft_lmhead_ce_bwd": [vp, vp, vp, i64, vp, i64, i64, i64, i64, i32, vp, vp, i64, f32, vp, vp, i64, vp],
+    "mft_lmhead_ce_fused": [vp, vp, vp, i64, vp, i64, i64, i64, i64, i32, i64, f32, vp, vp, vp, vp, vp, vp, i64, vp],
     "mft_ce_dense_fwd": [vp, vp, i64, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp],
     "mft_ce_dense_bwd": [vp, vp, i64, i64, i64, vp, vp, f32, vp, vp],
     "mft_grad_sqnorm": [vp, i64, vp, vp],

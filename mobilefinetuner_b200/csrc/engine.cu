@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "engine.h"
+#include <cstdlib>
 
 using namespace mft;
 
@@ -350,6 +351,7 @@ extern "C" int32_t mft_model_create(const mft_model_config_t* cfg, mft_stream_t 
     G(dalloc(m, &m->loss_dev, 4, true)); G(dalloc(m, &m->n_valid_dev, 4, true)); G(dalloc(m, &m->status_dev, 4, true));
     G(dalloc(m, &m->ce_lse, T));
     m->ce_ws_bytes = mft_lmhead_ce_workspace_bytes(T, H, V);
+    if (const char* e = std::getenv("MFT_CE_ONEPASS")) m->ce_onepass = std::atoi(e) != 0;
     { uint8_t* ws = nullptr; G(dalloc(m, &ws, m->ce_ws_bytes, false, true)); m->ce_ws = ws; }
     m->stage_floats = 32ll << 20;
     G(dalloc(m, &m->stage_f32, m->stage_floats));

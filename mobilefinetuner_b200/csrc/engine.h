@@ -128,5 +128,6 @@ struct mft_model {
     float *attn_delta = nullptr;
     float* loss_dev = nullptr; int32_t* n_valid_dev = nullptr; float* ce_lse = nullptr; int32_t* status_dev = nullptr;
     void* ce_ws = nullptr; int64_t ce_ws_bytes = 0;
+    bool ce_onepass = true;          // training steps use mft_lmhead_ce_fused (MFT_CE_ONEPASS=0 selects the two-sweep pair)
     float* stage_f32 = nullptr; int64_t stage_floats = 0;   // upload staging
 };

@@ -56,7 +56,7 @@ mft_strides_t tok_strides(int64_t S, int64_t ld, int64_t hd) {
     mft_strides_t s; s.stride_b = S * ld; s.stride_s = ld; s.stride_h = hd; return s;
 }
 
-int32_t forward(Ctx& c, bool for_training) {
+int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
     mft_model* m = c.m;
     const mft_model_config_t& cfg = m->cfg;
     const bool gpt2 = cfg.family == MFT_FAMILY_GPT2, gemma = cfg.family == MFT_FAMILY_GEMMA;
@@ -114,7 +114,11 @@ int32_t forward(Ctx& c, bool for_training) {
     }
     if (gpt2) TRY(mft_layernorm_fwd(m->x_final, MFT_F32, m->final_w, m->final_b, 1e-5f, m->hf, MFT_BF16, m->mean_f, m->rstd_f, T, H, c.st));
     else TRY(mft_rmsnorm_fwd(m->x_final, MFT_F32, m->final_w, cfg.norm_eps, gemma ? 1 : 0, m->hf, MFT_BF16, m->rstd_f, nullptr, nullptr, T, H, c.st));
-    // lm head + shifted cross entropy; the [T,V] logits are never written
+    // lm head + shifted cross entropy; the [T,V] logits are never written.  A training step gets the loss and
+    // d(loss)/d(final hidden) (into t_h) from one sweep over the vocabulary.
+    if (for_training && m->ce_onepass)
+        return mft_lmhead_ce_fused(m->hf, m->embed, m->embed_t, m->ld_t, m->labels, c.B, S, H, cfg.vocab, -100, n_valid_global, 1.0f,
+                                   m->loss_dev, m->n_valid_dev, m->ce_lse, m->t_h, m->status_dev, m->ce_ws, m->ce_ws_bytes, c.st);
     return mft_lmhead_ce_fwd(m->hf, m->embed, m->labels, c.B, S, H, cfg.vocab, -100, m->loss_dev, m->n_valid_dev, m->ce_lse, m->status_dev,
                              m->ce_ws, m->ce_ws_bytes, c.st);
 }
@@ -129,8 +133,9 @@ int32_t backward(Ctx& c, int64_t n_valid_global) {
     const int64_t T = c.T, S = c.S;
     if (m->grad_pan_floats > 0) TRY(mft_memset(m->grad_pan_base, 0, (size_t)m->grad_pan_floats * 4, c.st));
     // d(loss)/d(final hidden), then through the final norm into the residual gradient dx (f32)
-    TRY(mft_lmhead_ce_bwd(m->hf, m->embed, m->embed_t, m->ld_t, m->labels, c.B, S, H, cfg.vocab, -100, m->ce_lse, m->n_valid_dev,
-                          n_valid_global, 1.0f, m->t_h, m->ce_ws, m->ce_ws_bytes, c.st));
+    if (!m->ce_onepass)
+        TRY(mft_lmhead_ce_bwd(m->hf, m->embed, m->embed_t, m->ld_t, m->labels, c.B, S, H, cfg.vocab, -100, m->ce_lse, m->n_valid_dev,
+                              n_valid_global, 1.0f, m->t_h, m->ce_ws, m->ce_ws_bytes, c.st));
     if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, m->x_final, MFT_F32, m->final_w, m->mean_f, m->rstd_f, m->dx, MFT_F32, 0, nullptr, nullptr, T, H, c.st));
     else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, m->x_final, MFT_F32, m->final_w, m->rstd_f, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 0, nullptr, T, H, c.st));
 
@@ -214,7 +219,7 @@ extern "C" int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t*
     MFT_CHECK_ARG(ids_dev && labels_dev, "mft_model_forward_backward_dev: null input");
     if (ids_dev != m->ids) TRY(mft_memcpy_d2d(m->ids, ids_dev, (size_t)c.T * 4, c.st));
     if (labels_dev != m->labels) TRY(mft_memcpy_d2d(m->labels, labels_dev, (size_t)c.T * 4, c.st));
-    TRY(forward(c, true));
+    TRY(forward(c, true, n_valid_global));
     TRY(backward(c, n_valid_global));
     if (loss_dev) *loss_dev = m->loss_dev;
     if (n_valid_dev) *n_valid_dev = m->n_valid_dev;
@@ -228,7 +233,7 @@ extern "C" int32_t mft_model_forward_backward(mft_model_t* m, const int32_t* ids
     MFT_CHECK_ARG(ids_host && labels_host, "mft_model_forward_backward: null input");
     TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)c.T * 4, c.st));
     TRY(mft_memcpy_h2d(m->labels, labels_host, (size_t)c.T * 4, c.st));
-    TRY(forward(c, true));
+    TRY(forward(c, true, n_valid_global));
     TRY(backward(c, n_valid_global));
     if (loss_host) TRY(mft_memcpy_d2h(loss_host, m->loss_dev, 4, c.st));
     if (n_valid_host) TRY(mft_memcpy_d2h(n_valid_host, m->n_valid_dev, 4, c.st));

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 #include "gemm_sm100.h"
 #include "sm100_ptx.cuh"
 
@@ -166,65 +167,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int row = m0 + row_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
             if (EPI != EPI_CE_STATS && p.tma_store) {
-                // ---- bf16 output: registers -> swizzled shared-memory box (32 rows x 64 columns) -> TMA tensor store
-                float lse = 0.f, coef = 0.f;
-                int tgt = -1;
-                if constexpr (EPI == EPI_CE_GRAD) {
-                    if (row < p.m) {
-                        tgt = p.ce_tgt[row];
-                        lse = p.ce_lse[row];
-                        const long long nv = p.ce_nvalid_override > 0 ? p.ce_nvalid_override : (long long)*p.ce_nvalid;
-                        coef = (tgt >= 0 && nv > 0) ? p.ce_dloss / (float)nv : 0.f;
-                        tgt -= p.ce_col_offset;
-                    }
-                }
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 64) {
-                    if (n0 + c >= p.n) break;          // uniform across the warp
-                    uint8_t* buf = store_smem + (q * 2 + (box_ctr & 1)) * Cfg::STORE_BOX_BYTES;
-                    const uint32_t buf_addr = smem_u32(buf) + (uint32_t)lane * 128u;
-                    if (lane == 0) tma_store_wait_read<1>();   // the store that last used this buffer has read it
-                    __syncwarp();
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint32_t r[32];
-                        tmem_ld_32x32(taddr + (uint32_t)(c + half * 32), r);
-                        tmem_ld_wait();
-                        const int col0 = n0 + c + half * 32;
-                        float v[32];
-                        if constexpr (EPI == EPI_STORE) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-                            if (p.bias) {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const float pr = __expf(__uint_as_float(r[j]) * p.alpha - lse);
-                                v[j] = (pr - (col0 + j == tgt ? 1.f : 0.f)) * coef;
-                            }
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t pos = (uint32_t)((half * 4 + j) ^ (lane & 7));   // 128-byte swizzle
-                            const __nv_bfloat162 w0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
-                            const __nv_bfloat162 w1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                            const __nv_bfloat162 w2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-                            const __nv_bfloat162 w3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-                            st_shared_v4(buf_addr + pos * 16u, *reinterpret_cast<const uint32_t*>(&w0), *reinterpret_cast<const uint32_t*>(&w1),
-                                         *reinterpret_cast<const uint32_t*>(&w2), *reinterpret_cast<const uint32_t*>(&w3));
-                        }
-                    }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&map_d, buf, n0 + c, m0 + q * 32);   // rows / columns outside D are clipped
-                        tma_store_commit();
-                    }
-                    ++box_ctr;
-                }
+                epilogue_bf16_tma<EPI, BN>(p, &map_d, store_smem, taddr, q, lane, row, m0 + q * 32, n0, box_ctr);
             } else if constexpr (EPI == EPI_STORE) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
@@ -304,7 +247,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     sum = sum * __expf(mx - nm) + cs;     // mx = -inf on the first chunk -> factor 0
                     mx = nm;
                 }
-                if (row < p.m) p.ce_partials[(long long)row * p.ce_partial_ld + (n0 / BN)] = make_float2(mx, sum);
+                if (row < p.m) p.ce_partials[(long long)row * p.ce_partial_ld + (p.ce_col_offset + n0) / BN] = make_float2(mx, sum);
             } else {
                 float lse = 0.f, coef = 0.f;
                 int tgt = -1;
@@ -497,9 +440,13 @@ static int32_t gemm_nt_run_inner(const GemmCall& c, cudaStream_t stream) {
     p.status = device_status_word();
     p.ce_tgt = c.ce_tgt; p.ce_lse = c.ce_lse; p.ce_nvalid = c.ce_nvalid; p.ce_nvalid_override = c.ce_nvalid_override;
     p.ce_dloss = c.ce_dloss; p.ce_col_offset = c.ce_col_offset; p.ce_partials = c.ce_partials;
-    p.ce_partial_ld = c.ce_partial_ld; p.ce_tgt_logit = c.ce_tgt_logit;
+    p.ce_partial_ld = c.ce_partial_ld; p.ce_tgt_logit = c.ce_tgt_logit; p.ce_flag = c.ce_flag;
     if (c.epi == EPI_CE_STATS) return launch_gemm<CE_TILE_N, EPI_CE_STATS>(ma, mb, ma2, mb2, md, p, stream);
     if (c.epi == EPI_CE_GRAD) return launch_gemm<CE_TILE_N, EPI_CE_GRAD>(ma, mb, ma2, mb2, md, p, stream);
+    if (c.epi == EPI_CE_P) {
+        if (!tma_store) return fail(MFT_ERR_INVALID_ARG, "gemm_nt: the softmax-numerator epilogue needs an aligned bf16 output");
+        return launch_gemm<CE_TILE_N, EPI_CE_P>(ma, mb, ma2, mb2, md, p, stream);
+    }
     if (bn == 256) return launch_gemm<256, EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);
     if (bn == 192) return launch_gemm<192, EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);
     if (bn == 128) return launch_gemm<128, EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);

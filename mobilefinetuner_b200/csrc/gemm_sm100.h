@@ -9,6 +9,7 @@ namespace mft {
 constexpr int EPI_STORE = 0;     // D = alpha*acc + bias (+ D)
 constexpr int EPI_CE_STATS = 1;  // per-row (max, sum exp) over each 256-column tile; nothing stored
 constexpr int EPI_CE_GRAD = 2;   // D(bf16) = (exp(acc - lse[row]) - [col == label[row]]) * dloss / n_valid
+constexpr int EPI_CE_P = 3;      // D(bf16) = exp(acc - m_ref[row]); per-row sums of the stored values; label logit; overflow flag
 constexpr int CE_TILE_N = 256;   // column tile of the CE epilogues (fixes the layout of the partials)
 
 struct GemmCall {
@@ -33,6 +34,7 @@ struct GemmCall {
     float2* ce_partials = nullptr;
     int ce_partial_ld = 0;
     float* ce_tgt_logit = nullptr;
+    int32_t* ce_flag = nullptr;
 };
 
 // Kernel-side parameter block (by value in the launch).
@@ -56,7 +58,8 @@ struct GemmParams {
     int ce_col_offset;            // vocabulary index of column 0 of this GEMM
     float2* ce_partials;          // [m, ce_partial_ld] (max, sum exp) per row and column tile (STATS mode)
     int ce_partial_ld;
-    float* ce_tgt_logit;          // [m] logit of the label column (STATS mode)
+    float* ce_tgt_logit;          // [m] logit of the label column (STATS / P modes)
+    int32_t* ce_flag;             // [m] set to 1 for a row whose exp(acc - m_ref) leaves the trusted range (P mode)
 };
 
 // Tile order: groups of RASTER_GROUP column tiles, row tiles within a group, columns fastest.  CTAs that run at

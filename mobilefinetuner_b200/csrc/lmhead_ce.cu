@@ -8,6 +8,13 @@
 //           logits are recomputed by the same GEMM with an epilogue that writes
 //           G = (softmax - onehot) * dloss / n_valid as bf16 [T, PANEL], and a
 //           second GEMM accumulates dHidden += G x table[panel, :] in fp32.
+// Fused  : forward and backward in ONE sweep over the vocabulary (training step).  A first GEMM over panel 0
+//           gives every row a reference value m_ref (the log-sum-exp of that panel, a lower bound of the full
+//           one).  Then per panel GEMM 1 writes the un-normalised numerators P = exp(logit - m_ref) as bf16
+//           and their per-row sums, GEMM 2 accumulates D += P x table[panel, :] in fp32, and a last kernel
+//           forms lse = m_ref + log(sum P), the loss and dHidden = (D / sum P - table[label]) * dloss / n_valid.
+//           The logits are computed once instead of twice.  A row whose logits exceed m_ref by more than the
+//           trusted range is flagged by GEMM 1 and recomputed exactly on the CUDA cores.
 // Semantics follow lm_cross_entropy of the reference: row (b, s) is scored
 // against labels[b, s+1]; the last position of a sequence and labels equal to
 // ignore_index contribute nothing; mean over scored rows; NaN if none.
@@ -29,6 +36,8 @@ struct CeWorkspace {
     int32_t* count;        // [1] scratch count for the backward
     __nv_bfloat16* g;      // [T, panel]
     float* dh_acc;         // [T, H]
+    float* m_ref;          // [T] reference exponent of the fused sweep
+    int32_t* row_flag;     // [T] rows the fused sweep must recompute exactly
     int64_t ntiles, panel, total;
 };
 
@@ -46,6 +55,8 @@ CeWorkspace carve(void* base, int64_t T, int64_t H, int64_t V) {
     w.count = reinterpret_cast<int32_t*>(take(4));
     w.g = reinterpret_cast<__nv_bfloat16*>(take(T * w.panel * 2));
     w.dh_acc = reinterpret_cast<float*>(take(T * H * 4));
+    w.m_ref = reinterpret_cast<float*>(take(T * 4));
+    w.row_flag = reinterpret_cast<int32_t*>(take(T * 4));
     w.total = off;
     return w;
 }
@@ -72,7 +83,7 @@ __global__ void ce_prepare_kernel(const int32_t* __restrict__ labels, int64_t ba
     if (threadIdx.x == 0 && tot > 0.f) atomicAdd(n_valid, (int32_t)tot);
 }
 
-__global__ void ce_reduce_kernel(const float2* __restrict__ partials, int64_t ntiles, const int32_t* __restrict__ tgt,
+__global__ void ce_reduce_kernel(const float2* __restrict__ partials, int64_t ntiles, int64_t ld, const int32_t* __restrict__ tgt,
                                  const float* __restrict__ tgt_logit, float* __restrict__ lse, double* __restrict__ loss_sum,
                                  int64_t T) {
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -80,7 +91,7 @@ __global__ void ce_reduce_kernel(const float2* __restrict__ partials, int64_t nt
     if (row >= T) return;
     float m = -INFINITY, s = 0.f;
     for (int64_t i = lane; i < ntiles; i += 32) {
-        const float2 pr = partials[row * ntiles + i];
+        const float2 pr = partials[row * ld + i];
         const float nm = fmaxf(m, pr.x);
         s = s * __expf(m - nm) + pr.y * __expf(pr.x - nm);
         m = nm;
@@ -95,13 +106,114 @@ __global__ void ce_reduce_kernel(const float2* __restrict__ partials, int64_t nt
     if (lane == 0) {
         const float l = m + logf(s);
         lse[row] = l;
-        if (tgt[row] >= 0) atomicAdd(loss_sum, (double)(l - tgt_logit[row]));
+        if (loss_sum && tgt[row] >= 0) atomicAdd(loss_sum, (double)(l - tgt_logit[row]));
     }
 }
 
 __global__ void ce_finalize_kernel(const double* loss_sum, const int32_t* n_valid, float* loss) {
     const int n = *n_valid;
     *loss = n > 0 ? (float)(*loss_sum / (double)n) : NAN;
+}
+
+
+// ---- fused sweep: last step for the rows GEMM 1 did not flag.  One block per row.
+__global__ void ce_fused_finish_kernel(const float2* __restrict__ partials, int64_t ntiles, const int32_t* __restrict__ tgt,
+                                       const float* __restrict__ tgt_logit, const float* __restrict__ m_ref,
+                                       const int32_t* __restrict__ row_flag, const float* __restrict__ dacc,
+                                       const __nv_bfloat16* __restrict__ table, int64_t H, const int32_t* __restrict__ n_valid,
+                                       int64_t nv_override, float dloss, float* __restrict__ lse, double* __restrict__ loss_sum,
+                                       __nv_bfloat16* __restrict__ dh) {
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    if (row_flag[row]) return;
+    float s = 0.f;
+    for (int64_t i = threadIdx.x; i < ntiles; i += blockDim.x) s += partials[row * ntiles + i].y;
+    s = block_sum(s, scratch);
+    const int t = tgt[row];
+    if (threadIdx.x == 0) {
+        const float l = m_ref[row] + logf(s);
+        lse[row] = l;
+        if (t >= 0) atomicAdd(loss_sum, (double)(l - tgt_logit[row]));
+    }
+    const long long nv = nv_override > 0 ? nv_override : (long long)*n_valid;
+    const float coef = (t >= 0 && nv > 0) ? dloss / (float)nv : 0.f;
+    __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(dh + row * H);
+    if (coef == 0.f) {
+        for (int64_t i = threadIdx.x; i < H / 2; i += blockDim.x) out[i] = __floats2bfloat162_rn(0.f, 0.f);
+        return;
+    }
+    const float inv = 1.f / s;
+    const float2* d2 = reinterpret_cast<const float2*>(dacc + row * H);
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(table + (int64_t)t * H);
+    for (int64_t i = threadIdx.x; i < H / 2; i += blockDim.x) {
+        const float2 d = d2[i];
+        const float2 w = __bfloat1622float2(w2[i]);
+        out[i] = __floats2bfloat162_rn((d.x * inv - w.x) * coef, (d.y * inv - w.y) * coef);
+    }
+}
+
+// ---- fused sweep: exact recomputation of the flagged rows on the CUDA cores (two sweeps over the vocabulary
+// per row; slow, and only ever run for rows whose logits left the range GEMM 1 trusts).
+// Dynamic shared memory: hidden row [H] + one dHidden accumulator [H] per warp.
+__global__ void ce_row_fixup_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* __restrict__ table,
+                                    const int32_t* __restrict__ tgt, const int32_t* __restrict__ row_flag, int64_t T, int64_t H,
+                                    int64_t V, const int32_t* __restrict__ n_valid, int64_t nv_override, float dloss,
+                                    float* __restrict__ lse, double* __restrict__ loss_sum, __nv_bfloat16* __restrict__ dh) {
+    extern __shared__ float fix_smem[];
+    __shared__ float red_m[32], red_s[32], tgt_l, row_lse;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    float* hrow = fix_smem;
+    float* dw = fix_smem + H + (int64_t)warp * H;
+    for (int64_t row = blockIdx.x; row < T; row += gridDim.x) {
+        if (!row_flag[row]) continue;
+        __syncthreads();
+        for (int64_t i = threadIdx.x; i < H; i += blockDim.x) hrow[i] = __bfloat162float(hidden[row * H + i]);
+        for (int64_t i = lane; i < H; i += 32) dw[i] = 0.f;
+        __syncthreads();
+        const int t = tgt[row];
+        float m = -INFINITY, s = 0.f;
+        for (int64_t j = warp; j < V; j += nwarps) {
+            const __nv_bfloat16* wr = table + j * H;
+            float dot = 0.f;
+            for (int64_t i = lane; i < H; i += 32) dot += hrow[i] * __bfloat162float(wr[i]);
+            dot = warp_sum(dot);
+            if (j == t && lane == 0) tgt_l = dot;
+            const float nm = fmaxf(m, dot);
+            s = s * __expf(m - nm) + __expf(dot - nm);
+            m = nm;
+        }
+        if (lane == 0) { red_m[warp] = m; red_s[warp] = s; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float mm = -INFINITY, ss = 0.f;
+            for (int w = 0; w < nwarps; ++w) mm = fmaxf(mm, red_m[w]);
+            for (int w = 0; w < nwarps; ++w) if (red_m[w] > -INFINITY) ss += red_s[w] * __expf(red_m[w] - mm);
+            const float l = mm + logf(ss);
+            row_lse = l;
+            lse[row] = l;
+            if (t >= 0) atomicAdd(loss_sum, (double)(l - tgt_l));
+        }
+        __syncthreads();
+        const long long nv = nv_override > 0 ? nv_override : (long long)*n_valid;
+        const float coef = (t >= 0 && nv > 0) ? dloss / (float)nv : 0.f;
+        if (coef != 0.f) {
+            const float l = row_lse;
+            for (int64_t j = warp; j < V; j += nwarps) {
+                const __nv_bfloat16* wr = table + j * H;
+                float dot = 0.f;
+                for (int64_t i = lane; i < H; i += 32) dot += hrow[i] * __bfloat162float(wr[i]);
+                dot = warp_sum(dot);
+                const float pj = __expf(dot - l) - (j == t ? 1.f : 0.f);
+                for (int64_t i = lane; i < H; i += 32) dw[i] += pj * __bfloat162float(wr[i]);
+            }
+        }
+        __syncthreads();
+        for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
+            float acc = 0.f;
+            for (int w = 0; w < nwarps; ++w) acc += fix_smem[H + (int64_t)w * H + i];
+            dh[row * H + i] = __float2bfloat16_rn(acc * coef);
+        }
+    }
 }
 
 // ---- dense-logits variants
@@ -174,7 +286,7 @@ extern "C" int32_t mft_lmhead_ce_fwd(const void* hidden_bf16, const void* table_
     c.a = hidden_bf16; c.lda = hidden; c.b = table_bf16; c.ldb = hidden; c.m = T; c.n = vocab; c.k = hidden;
     c.epi = EPI_CE_STATS; c.ce_tgt = w.tgt; c.ce_partials = w.partials; c.ce_partial_ld = (int)w.ntiles; c.ce_tgt_logit = w.tgt_logit;
     if (int32_t s = gemm_nt_run(c, st)) return s;
-    ce_reduce_kernel<<<(unsigned)((T * 32 + 255) / 256), 256, 0, st>>>(w.partials, w.ntiles, w.tgt, w.tgt_logit, lse, w.loss_sum, T);
+    ce_reduce_kernel<<<(unsigned)((T * 32 + 255) / 256), 256, 0, st>>>(w.partials, w.ntiles, w.ntiles, w.tgt, w.tgt_logit, lse, w.loss_sum, T);
     MFT_LAUNCH_CHECK("ce_reduce");
     ce_finalize_kernel<<<1, 1, 0, st>>>(w.loss_sum, n_valid_dev, loss_dev);
     MFT_LAUNCH_CHECK("ce_finalize");
@@ -213,6 +325,74 @@ extern "C" int32_t mft_lmhead_ce_bwd(const void* hidden_bf16, const void* table_
         if (int32_t s = gemm_nt_run(d, st)) return s;
     }
     return mft_cast_f32_to_bf16(w.dh_acc, dhidden_bf16, T * hidden, stream);
+}
+
+
+extern "C" int32_t mft_lmhead_ce_fused(const void* hidden_bf16, const void* table_bf16, const void* table_t_bf16, int64_t table_t_ld,
+                                       const int32_t* labels, int64_t batch, int64_t seq, int64_t hidden, int64_t vocab,
+                                       int32_t ignore_index, int64_t n_valid_override, float dloss, float* loss_dev,
+                                       int32_t* n_valid_dev, float* lse, void* dhidden_bf16, int32_t* status_dev, void* workspace,
+                                       int64_t workspace_bytes, mft_stream_t stream) {
+    MFT_CHECK_ARG(hidden_bf16 && table_bf16 && table_t_bf16 && labels && loss_dev && n_valid_dev && lse && dhidden_bf16 && workspace,
+                  "mft_lmhead_ce_fused: null pointer");
+    MFT_CHECK_ARG(batch > 0 && seq > 0 && hidden > 0 && vocab > 0 && hidden % 8 == 0 && table_t_ld >= vocab && table_t_ld % 8 == 0,
+                  "mft_lmhead_ce_fused: bad size");
+    const int64_t T = batch * seq, H = hidden;
+    CeWorkspace w = carve(workspace, T, H, vocab);
+    MFT_CHECK_ARG(workspace_bytes >= w.total, "mft_lmhead_ce_fused: workspace too small");
+    constexpr int FIX_THREADS = 256;
+    const size_t fix_smem = (size_t)(1 + FIX_THREADS / 32) * H * sizeof(float);
+    MFT_CHECK_ARG(fix_smem <= 200 * 1024, "mft_lmhead_ce_fused: hidden size too large");
+    cudaStream_t st = as_stream(stream);
+    if (int32_t s = check_cuda(cudaMemsetAsync(n_valid_dev, 0, 4, st), "ce memset")) return s;
+    if (int32_t s = check_cuda(cudaMemsetAsync(w.loss_sum, 0, 8, st), "ce memset")) return s;
+    if (int32_t s = check_cuda(cudaMemsetAsync(w.row_flag, 0, (size_t)T * 4, st), "ce memset")) return s;
+    ce_prepare_kernel<<<(unsigned)std::min<int64_t>((T + 255) / 256, 1024), 256, 0, st>>>(labels, batch, seq, vocab, ignore_index, w.tgt, n_valid_dev, status_dev);
+    MFT_LAUNCH_CHECK("ce_prepare");
+    // reference exponent per row: log-sum-exp of panel 0
+    {
+        const int64_t vc = std::min(w.panel, vocab);
+        GemmCall c;
+        c.a = hidden_bf16; c.lda = H; c.b = table_bf16; c.ldb = H; c.m = T; c.n = vc; c.k = H;
+        c.epi = EPI_CE_STATS; c.ce_tgt = w.tgt; c.ce_partials = w.partials; c.ce_partial_ld = (int)w.ntiles; c.ce_tgt_logit = w.tgt_logit;
+        if (int32_t s = gemm_nt_run(c, st)) return s;
+        ce_reduce_kernel<<<(unsigned)((T * 32 + 255) / 256), 256, 0, st>>>(w.partials, (vc + CE_TILE_N - 1) / CE_TILE_N, w.ntiles, w.tgt,
+                                                                         w.tgt_logit, w.m_ref, nullptr, T);
+        MFT_LAUNCH_CHECK("ce_reduce");
+    }
+    for (int64_t v0 = 0; v0 < vocab; v0 += w.panel) {
+        const int64_t vc = std::min(w.panel, vocab - v0);
+        GemmCall c;
+        c.a = hidden_bf16; c.lda = H;
+        c.b = static_cast<const __nv_bfloat16*>(table_bf16) + v0 * H; c.ldb = H;
+        c.m = T; c.n = vc; c.k = H;
+        c.d = w.g; c.ldd = w.panel; c.d_is_f32 = 0;
+        c.epi = EPI_CE_P; c.ce_tgt = w.tgt; c.ce_lse = w.m_ref; c.ce_col_offset = (int)v0;
+        c.ce_partials = w.partials; c.ce_partial_ld = (int)w.ntiles; c.ce_tgt_logit = w.tgt_logit; c.ce_flag = w.row_flag;
+        if (int32_t s = gemm_nt_run(c, st)) return s;
+        GemmCall d;
+        d.a = w.g; d.lda = w.panel;
+        d.b = static_cast<const __nv_bfloat16*>(table_t_bf16) + v0; d.ldb = table_t_ld;
+        d.m = T; d.n = H; d.k = vc;
+        d.d = w.dh_acc; d.ldd = H; d.d_is_f32 = 1; d.accumulate = v0 > 0;
+        if (int32_t s = gemm_nt_run(d, st)) return s;
+    }
+    ce_fused_finish_kernel<<<(unsigned)T, 128, 0, st>>>(w.partials, w.ntiles, w.tgt, w.tgt_logit, w.m_ref, w.row_flag, w.dh_acc,
+                                                       static_cast<const __nv_bfloat16*>(table_bf16), H, n_valid_dev, n_valid_override,
+                                                       dloss, lse, w.loss_sum, static_cast<__nv_bfloat16*>(dhidden_bf16));
+    MFT_LAUNCH_CHECK("ce_fused_finish");
+    static bool fix_attr = false;
+    if (!fix_attr) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(ce_row_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "ce fixup attribute")) return s;
+        fix_attr = true;
+    }
+    ce_row_fixup_kernel<<<(unsigned)std::min<int64_t>(T, 148 * 4), FIX_THREADS, fix_smem, st>>>(
+        static_cast<const __nv_bfloat16*>(hidden_bf16), static_cast<const __nv_bfloat16*>(table_bf16), w.tgt, w.row_flag, T, H, vocab,
+        n_valid_dev, n_valid_override, dloss, lse, w.loss_sum, static_cast<__nv_bfloat16*>(dhidden_bf16));
+    MFT_LAUNCH_CHECK("ce_row_fixup");
+    ce_finalize_kernel<<<1, 1, 0, st>>>(w.loss_sum, n_valid_dev, loss_dev);
+    MFT_LAUNCH_CHECK("ce_finalize");
+    return MFT_OK;
 }
 
 extern "C" int32_t mft_ce_dense_fwd(const float* logits, const int32_t* labels, int64_t batch, int64_t seq, int64_t vocab,

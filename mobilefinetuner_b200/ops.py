@@ -249,6 +249,25 @@ class LmHeadCE:
         return dh
 
 
+    def fused(self, hidden, labels, dloss=1.0, ignore_index=-100, n_valid_override=0):
+        """Loss and d(loss)/d(hidden) from one sweep over the vocabulary: returns (loss, dhidden)."""
+        b, s, h = hidden.shape
+        v = self.table.shape[0]
+        ws = self._workspace(b * s, h, v)
+        dev = hidden.device
+        self.loss = torch.empty(1, device=dev, dtype=F32)
+        self.n_valid = torch.zeros(1, device=dev, dtype=torch.int32)
+        self.lse = torch.empty(b * s, device=dev, dtype=F32)
+        self.status = torch.zeros(1, device=dev, dtype=torch.int32)
+        dh = torch.empty(b, s, h, device=dev, dtype=BF16)
+        L.call("mft_lmhead_ce_fused", _p(hidden), _p(self.table), _p(self.table_t), self.ld_t, _p(labels), b, s, h, v,
+               ignore_index, int(n_valid_override), float(dloss), _p(self.loss), _p(self.n_valid), _p(self.lse), _p(dh),
+               _p(self.status), _p(ws), ws.numel(), _stream())
+        if int(self.status.item()) != 0:
+            raise IndexError("lm_cross_entropy: label out of range")
+        return self.loss, dh
+
+
 def ce_dense(logits, labels, ignore_index=-100, dloss=1.0):
     """lm_cross_entropy on dense f32 logits [B,S,V]: returns (loss, dlogits)."""
     _init(logits)

@@ -342,12 +342,67 @@ def test_lm_head_ce_large_vocab_vs_restatement(ops):
     assert np.all(dh[:, -1, :] == 0) and np.all(dh[0, 4:8, :] == 0)    # unscored rows get exactly zero
 
 
+def test_lm_head_ce_fused_golden_and_two_sweep(ops, golden):
+    """One sweep over the vocabulary gives the loss and dHidden of the forward + backward pair."""
+    i, o, _ = golden.case("lm_head_ce")
+    ce = ops.LmHeadCE(dev(i["W"], torch.bfloat16))
+    hid, labels = dev(i["hidden"], torch.bfloat16), dev(i["labels"])
+    loss, dh = ce.fused(hid, labels)
+    assert int(ce.n_valid.item()) == int((i["labels"][:, 1:] != -100).sum())
+    assert abs(loss.item() - o["loss"][0]) <= 2e-3 * abs(o["loss"][0])
+    close_bf16(host(dh), o["dhidden"])
+    lse1 = host(ce.lse).copy()
+    ce.forward(hid, labels)
+    np.testing.assert_allclose(lse1, host(ce.lse), rtol=0, atol=2e-3)
+    assert ops.device_status() == 0
+
+
+def test_lm_head_ce_fused_large_vocab_dp_scaling(ops):
+    g = np.random.Generator(np.random.PCG64(32))
+    B, S, H, V = 2, 70, 640, 20000
+    hid = rb(g.standard_normal((B, S, H)))
+    W = rb(g.standard_normal((V, H)) * 0.05)
+    labels = g.integers(0, V, size=(B, S)).astype(np.int32)
+    labels[1, 10:20] = -100
+    want_loss, want_dh = R.lm_head_ce(hid, W, labels)
+    ce = ops.LmHeadCE(dev(W, torch.bfloat16))
+    loss, dh = ce.fused(dev(hid, torch.bfloat16), dev(labels))
+    assert abs(loss.item() - want_loss) <= 2e-3 * abs(want_loss)
+    dh = host(dh)
+    close_bf16(dh, want_dh)
+    assert np.all(dh[:, -1, :] == 0) and np.all(dh[1, 9:19, :] == 0)
+    n = int(ce.n_valid.item())
+    _, dh2 = ce.fused(dev(hid, torch.bfloat16), dev(labels), n_valid_override=2 * n)   # a data-parallel rank: global count
+    close_bf16(host(dh2), want_dh / 2)
+
+
+def test_lm_head_ce_fused_recomputes_rows_out_of_range(ops):
+    """Logits far above the first panel's log-sum-exp: the sweep flags those rows and recomputes them exactly."""
+    g = np.random.Generator(np.random.PCG64(33))
+    B, S, H, V = 1, 40, 128, 16384 + 300       # second panel holds the large logits
+    hid = rb(g.standard_normal((B, S, H)))
+    W = rb(g.standard_normal((V, H)) * 0.05)
+    for r in range(0, S, 3):                   # every third row points at its own column of panel 2
+        W[16384 + r] = rb(hid[0, r] * (150.0 / float(hid[0, r] @ hid[0, r])))
+    labels = g.integers(0, V, size=(B, S)).astype(np.int32)
+    labels[0, 4] = 16384 + 3
+    want_loss, want_dh = R.lm_head_ce(hid, W, labels)
+    ce = ops.LmHeadCE(dev(W, torch.bfloat16))
+    loss, dh = ce.fused(dev(hid, torch.bfloat16), dev(labels))
+    assert np.isfinite(loss.item()) and abs(loss.item() - want_loss) <= 2e-3 * abs(want_loss)
+    close_bf16(host(dh), want_dh)
+    ce.forward(dev(hid, torch.bfloat16), dev(labels))
+    assert abs(loss.item() - ce.loss.item()) <= 1e-3 * abs(want_loss)
+
+
 def test_lm_ce_all_ignored_and_out_of_range(ops, golden):
     i, o, _ = golden.case("lm_ce_all_ignored")
     ce = ops.LmHeadCE(dev(i["W"], torch.bfloat16))
     hid, labels = dev(i["hidden"], torch.bfloat16), dev(i["labels"])
     assert np.isnan(ce.forward(hid, labels).item()) and np.isnan(o["loss"][0])
     assert np.all(host(ce.backward(hid, labels)) == 0)
+    loss, dh = ce.fused(hid, labels)
+    assert np.isnan(loss.item()) and np.all(host(dh) == 0)
     bad = i["labels"].copy(); bad[0, 3] = i["W"].shape[0]
     with pytest.raises(IndexError):
         ce.forward(hid, dev(bad))
