@@ -4,24 +4,28 @@
 // matmul -> mul(scale) -> add(mask) -> softmax -> matmul and its autograd
 // (four [B,nh,S,S] fp32 tensors forward, as many backward) by flash-style
 // kernels that keep scores on chip:
-//   forward : one CTA per (64 queries, head, batch); online softmax in fp32
+//   forward : one CTA per (BM queries, head, batch); online softmax in fp32
 //             (exp2 domain); masks are index predicates, fully masked key
 //             blocks are skipped; writes O (bf16) and the row log-sum-exp.
 //   backward: delta = rowsum(O * dO); a query-stationary kernel for dQ and a
 //             key-stationary kernel for dK/dV, both recomputing P from the
-//             saved log-sum-exp.  The key-stationary kernel loops over the
-//             query heads of a KV group, so dK/dV come out per KV head with no
-//             repeat_kv copy and no atomics.
+//             saved log-sum-exp.  The key-stationary kernel either loops over
+//             the query heads of a KV group (dK/dV come out per KV head with
+//             no repeat_kv copy and no atomics) or, given an fp32 scratch,
+//             runs one CTA per query head and adds into the scratch (4x the
+//             CTAs for a 4:1 group; a small kernel converts to bf16).
+// All three stream their moving tiles through a two-stage cp.async ring: the
+// loads of tile t+1 are in flight while tile t is multiplied.
 // Query head h uses KV head h / (n_heads / n_kv_heads).
 // Tensor-core path: warp-level mma.sync m16n8k16 (bf16 in, fp32 accumulate).
 #include "common.cuh"
+
+#include <cstdlib>
 
 namespace mft {
 
 namespace {
 
-constexpr int ATT_BM = 64;   // queries per tile
-constexpr int ATT_BN = 64;   // keys per tile
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void cp_async16z(void* smem, const void* gmem, bool valid) {
@@ -29,6 +33,13 @@ __device__ __forceinline__ void cp_async16z(void* smem, const void* gmem, bool v
     const int sz = valid ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(sz) : "memory");
 }
+__device__ __forceinline__ void cp_async4z(void* smem, const void* gmem, bool valid) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int sz = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(s), "l"(gmem), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void cp_commit_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
@@ -58,6 +69,7 @@ struct AttnParams {
     __nv_bfloat16 *out, *dq, *dk, *dv;
     float* lse;
     float* delta;
+    float* dkv_acc;          // optional f32 [2][batch, seq, n_kv, hd] accumulator of the per-head dK/dV kernel
     mft_strides_t sq, sk, sv, so, sdo;
     int batch, seq, n_heads, n_kv, rep;
     float scale;
@@ -76,10 +88,10 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* s, const __nv_bfloat16*
     }
 }
 
-// acc[nb] (16 x 64 slab, 8 n-blocks) = A[16 rows of `a_s`] * B^T where both tiles
+// acc[nb] (16 x 8*NB slab) = A[16 rows of `a_s`] * B^T where both tiles
 // are stored [row][HD] (contraction along HD): S = Q K^T, dP = dO V^T.
-template <int HD>
-__device__ __forceinline__ void mma_rowrow(float (&acc)[8][4], const __nv_bfloat16* a_s, int a_row0,
+template <int HD, int NB>
+__device__ __forceinline__ void mma_rowrow(float (&acc)[NB][4], const __nv_bfloat16* a_s, int a_row0,
                                            const __nv_bfloat16* b_s, int lane) {
     constexpr int LD = HD + 8;
 #pragma unroll
@@ -87,7 +99,7 @@ __device__ __forceinline__ void mma_rowrow(float (&acc)[8][4], const __nv_bfloat
         uint32_t a[4];
         ldsm_x4(a, a_s + (a_row0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk + (lane >> 4) * 8);
 #pragma unroll
-        for (int nb = 0; nb < 8; nb += 2) {
+        for (int nb = 0; nb < NB; nb += 2) {
             uint32_t b[4];
             ldsm_x4(b, b_s + (nb * 8 + (lane & 7) + (lane >> 4) * 8) * LD + kk + ((lane >> 3) & 1) * 8);
             mma16816(acc[nb], a, b[0], b[1]);
@@ -101,28 +113,37 @@ __device__ __forceinline__ bool visible(int i, int j, int seq, int window) {
 }
 
 // ---------------------------------------------------------------- forward
-template <int HD>
-__global__ void __launch_bounds__(128)
+// BM queries per CTA (one warp per 16), BN keys per tile.
+template <int HD, int BM, int BN>
+__global__ void __launch_bounds__(BM * 2)
 attn_fwd_kernel(const AttnParams p) {
-    constexpr int LD = HD + 8;
+    constexpr int LD = HD + 8, THREADS = BM * 2, NB = BN / 8;
     extern __shared__ __align__(16) uint8_t smem_attn[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_attn);
-    __nv_bfloat16* Ks = Qs + ATT_BM * LD;
-    __nv_bfloat16* Vs = Ks + ATT_BN * LD;
+    __nv_bfloat16* KV = Qs + BM * LD;             // 2 stages of { K [BN][LD], V [BN][LD] }
     const int qb = gridDim.x - 1 - blockIdx.x;   // longest rows first
     const int h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / p.rep;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
-    const int i0 = qb * ATT_BM;
-    const int rows_q = min(ATT_BM, p.seq - i0);
+    const int i0 = qb * BM;
+    const int rows_q = min(BM, p.seq - i0);
+    const __nv_bfloat16* kbase = p.k + (int64_t)b * p.sk.stride_b + (int64_t)kvh * p.sk.stride_h;
+    const __nv_bfloat16* vbase = p.v + (int64_t)b * p.sv.stride_b + (int64_t)kvh * p.sv.stride_h;
+    auto prefetch = [&](int jb, int st) {
+        const int j0 = jb * BN, rows_k = min(BN, p.seq - j0);
+        __nv_bfloat16* Ks = KV + st * 2 * BN * LD;
+        load_tile<BN, HD, THREADS>(Ks, kbase + (int64_t)j0 * p.sk.stride_s, p.sk.stride_s, rows_k);
+        load_tile<BN, HD, THREADS>(Ks + BN * LD, vbase + (int64_t)j0 * p.sv.stride_s, p.sv.stride_s, rows_k);
+        cp_commit();
+    };
 
-    load_tile<ATT_BM, HD, 128>(Qs, p.q + (int64_t)b * p.sq.stride_b + (int64_t)i0 * p.sq.stride_s + (int64_t)h * p.sq.stride_h, p.sq.stride_s, rows_q);
-
-    const int i_last = min(i0 + ATT_BM - 1, p.seq - 1);
-    const int jb_hi = i_last / ATT_BN;
-    const int jb_lo = p.window > 0 ? max(0, i0 - p.window + 1) / ATT_BN : 0;
+    const int i_last = min(i0 + BM - 1, p.seq - 1);
+    const int jb_hi = i_last / BN;
+    const int jb_lo = p.window > 0 ? max(0, i0 - p.window + 1) / BN : 0;
     const float sl2 = p.scale * LOG2E;
+    load_tile<BM, HD, THREADS>(Qs, p.q + (int64_t)b * p.sq.stride_b + (int64_t)i0 * p.sq.stride_s + (int64_t)h * p.sq.stride_h, p.sq.stride_s, rows_q);
+    prefetch(jb_lo, 0);
 
     float o[HD / 8][4];
 #pragma unroll
@@ -131,24 +152,24 @@ attn_fwd_kernel(const AttnParams p) {
     const int row_a = i0 + warp * 16 + g;       // rows of c0,c1 ; c2,c3 belong to row_a + 8
 
     for (int jb = jb_lo; jb <= jb_hi; ++jb) {
-        const int j0 = jb * ATT_BN;
-        const int rows_k = min(ATT_BN, p.seq - j0);
-        __syncthreads();   // previous iteration done with Ks/Vs
-        load_tile<ATT_BN, HD, 128>(Ks, p.k + (int64_t)b * p.sk.stride_b + (int64_t)j0 * p.sk.stride_s + (int64_t)kvh * p.sk.stride_h, p.sk.stride_s, rows_k);
-        load_tile<ATT_BN, HD, 128>(Vs, p.v + (int64_t)b * p.sv.stride_b + (int64_t)j0 * p.sv.stride_s + (int64_t)kvh * p.sv.stride_h, p.sv.stride_s, rows_k);
-        cp_commit_wait_all();
-        __syncthreads();
+        const int j0 = jb * BN;
+        const int st = (jb - jb_lo) & 1;
+        cp_wait_all();
+        __syncthreads();   // tile jb has landed; everyone is done with the other stage
+        if (jb < jb_hi) prefetch(jb + 1, st ^ 1);
+        const __nv_bfloat16* Ks = KV + st * 2 * BN * LD;
+        const __nv_bfloat16* Vs = Ks + BN * LD;
 
-        float s[8][4];
+        float s[NB][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-        mma_rowrow<HD>(s, Qs, warp * 16, Ks, lane);
+        for (int i = 0; i < NB; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+        mma_rowrow<HD, NB>(s, Qs, warp * 16, Ks, lane);
 
-        const bool need_mask = (j0 + ATT_BN - 1 > i0) || (j0 + ATT_BN > p.seq) ||
-                               (p.window > 0 && j0 < i0 + ATT_BM - p.window);
+        const bool need_mask = (j0 + BN - 1 > i0) || (j0 + BN > p.seq) ||
+                               (p.window > 0 && j0 < i0 + BM - p.window);
         float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
-        for (int nb = 0; nb < 8; ++nb)
+        for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int i = row_a + (e >> 1) * 8, j = j0 + nb * 8 + tq * 2 + (e & 1);
@@ -170,7 +191,7 @@ attn_fwd_kernel(const AttnParams p) {
             m_run[r] = m_new[r];
         }
 #pragma unroll
-        for (int nb = 0; nb < 8; ++nb)
+        for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float pv = exp2f(s[nb][e] - m_use[e >> 1]);
@@ -184,7 +205,7 @@ attn_fwd_kernel(const AttnParams p) {
 
         // O += P V : P from registers (bf16), V tile [key][d] via transposing ldmatrix
 #pragma unroll
-        for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+        for (int kk = 0; kk < BN / 16; ++kk) {
             uint32_t a[4];
             a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
             a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -242,28 +263,37 @@ __global__ void attn_delta_kernel(const AttnParams p) {
 }
 
 // ---------------------------------------------------------------- backward: dQ (query-stationary)
-template <int HD>
-__global__ void __launch_bounds__(128)
+template <int HD, int BM, int BN>
+__global__ void __launch_bounds__(BM * 2)
 attn_bwd_dq_kernel(const AttnParams p) {
-    constexpr int LD = HD + 8;
+    constexpr int LD = HD + 8, THREADS = BM * 2, NB = BN / 8;
     extern __shared__ __align__(16) uint8_t smem_attn[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_attn);
-    __nv_bfloat16* dOs = Qs + ATT_BM * LD;
-    __nv_bfloat16* Ks = dOs + ATT_BM * LD;
-    __nv_bfloat16* Vs = Ks + ATT_BN * LD;
+    __nv_bfloat16* dOs = Qs + BM * LD;
+    __nv_bfloat16* KV = dOs + BM * LD;            // 2 stages of { K [BN][LD], V [BN][LD] }
     const int qb = gridDim.x - 1 - blockIdx.x;
     const int h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / p.rep;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
-    const int i0 = qb * ATT_BM;
-    const int rows_q = min(ATT_BM, p.seq - i0);
-    load_tile<ATT_BM, HD, 128>(Qs, p.q + (int64_t)b * p.sq.stride_b + (int64_t)i0 * p.sq.stride_s + (int64_t)h * p.sq.stride_h, p.sq.stride_s, rows_q);
-    load_tile<ATT_BM, HD, 128>(dOs, p.d_o + (int64_t)b * p.sdo.stride_b + (int64_t)i0 * p.sdo.stride_s + (int64_t)h * p.sdo.stride_h, p.sdo.stride_s, rows_q);
+    const int i0 = qb * BM;
+    const int rows_q = min(BM, p.seq - i0);
+    const __nv_bfloat16* kbase = p.k + (int64_t)b * p.sk.stride_b + (int64_t)kvh * p.sk.stride_h;
+    const __nv_bfloat16* vbase = p.v + (int64_t)b * p.sv.stride_b + (int64_t)kvh * p.sv.stride_h;
+    auto prefetch = [&](int jb, int st) {
+        const int j0 = jb * BN, rows_k = min(BN, p.seq - j0);
+        __nv_bfloat16* Ks = KV + st * 2 * BN * LD;
+        load_tile<BN, HD, THREADS>(Ks, kbase + (int64_t)j0 * p.sk.stride_s, p.sk.stride_s, rows_k);
+        load_tile<BN, HD, THREADS>(Ks + BN * LD, vbase + (int64_t)j0 * p.sv.stride_s, p.sv.stride_s, rows_k);
+        cp_commit();
+    };
+    const int i_last = min(i0 + BM - 1, p.seq - 1);
+    const int jb_hi = i_last / BN;
+    const int jb_lo = p.window > 0 ? max(0, i0 - p.window + 1) / BN : 0;
+    load_tile<BM, HD, THREADS>(Qs, p.q + (int64_t)b * p.sq.stride_b + (int64_t)i0 * p.sq.stride_s + (int64_t)h * p.sq.stride_h, p.sq.stride_s, rows_q);
+    load_tile<BM, HD, THREADS>(dOs, p.d_o + (int64_t)b * p.sdo.stride_b + (int64_t)i0 * p.sdo.stride_s + (int64_t)h * p.sdo.stride_h, p.sdo.stride_s, rows_q);
+    prefetch(jb_lo, 0);
 
-    const int i_last = min(i0 + ATT_BM - 1, p.seq - 1);
-    const int jb_hi = i_last / ATT_BN;
-    const int jb_lo = p.window > 0 ? max(0, i0 - p.window + 1) / ATT_BN : 0;
     const float sl2 = p.scale * LOG2E;
     const int row_a = i0 + warp * 16 + g;
     float lse2[2], dlt[2];
@@ -280,20 +310,20 @@ attn_bwd_dq_kernel(const AttnParams p) {
     for (int i = 0; i < HD / 8; ++i) { dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f; }
 
     for (int jb = jb_lo; jb <= jb_hi; ++jb) {
-        const int j0 = jb * ATT_BN;
-        const int rows_k = min(ATT_BN, p.seq - j0);
+        const int j0 = jb * BN;
+        const int st = (jb - jb_lo) & 1;
+        cp_wait_all();
         __syncthreads();
-        load_tile<ATT_BN, HD, 128>(Ks, p.k + (int64_t)b * p.sk.stride_b + (int64_t)j0 * p.sk.stride_s + (int64_t)kvh * p.sk.stride_h, p.sk.stride_s, rows_k);
-        load_tile<ATT_BN, HD, 128>(Vs, p.v + (int64_t)b * p.sv.stride_b + (int64_t)j0 * p.sv.stride_s + (int64_t)kvh * p.sv.stride_h, p.sv.stride_s, rows_k);
-        cp_commit_wait_all();
-        __syncthreads();
-        float s[8][4], dp[8][4];
+        if (jb < jb_hi) prefetch(jb + 1, st ^ 1);
+        const __nv_bfloat16* Ks = KV + st * 2 * BN * LD;
+        const __nv_bfloat16* Vs = Ks + BN * LD;
+        float s[NB][4], dp[NB][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; dp[i][0] = dp[i][1] = dp[i][2] = dp[i][3] = 0.f; }
-        mma_rowrow<HD>(s, Qs, warp * 16, Ks, lane);
-        mma_rowrow<HD>(dp, dOs, warp * 16, Vs, lane);
+        for (int i = 0; i < NB; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; dp[i][0] = dp[i][1] = dp[i][2] = dp[i][3] = 0.f; }
+        mma_rowrow<HD, NB>(s, Qs, warp * 16, Ks, lane);
+        mma_rowrow<HD, NB>(dp, dOs, warp * 16, Vs, lane);
 #pragma unroll
-        for (int nb = 0; nb < 8; ++nb)
+        for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int i = row_a + (e >> 1) * 8, j = j0 + nb * 8 + tq * 2 + (e & 1);
@@ -303,7 +333,7 @@ attn_bwd_dq_kernel(const AttnParams p) {
             }
         // dQ += dS K : K tile [key][d] as the [k][n] operand via transposing ldmatrix
 #pragma unroll
-        for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+        for (int kk = 0; kk < BN / 16; ++kk) {
             uint32_t a[4];
             a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
             a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -335,119 +365,132 @@ attn_bwd_dq_kernel(const AttnParams p) {
 // [wn*HD/WN, (wn+1)*HD/WN).  S^T and dP^T (keys x queries) are computed with the
 // 64 queries split across the WN warps of a row, written to shared memory as
 // bf16 and re-read as the A operand of the two accumulating products.
-template <int HD, int WN>
+// SPLIT = false: grid.y = KV heads, the CTA walks all query heads of its group and stores bf16 dK/dV.
+// SPLIT = true : grid.y = query heads, the CTA adds its head's contribution into the f32 accumulator.
+template <int HD, int WN, bool SPLIT>
 __global__ void __launch_bounds__(128 * WN)
 attn_bwd_dkv_kernel(const AttnParams p) {
+    constexpr int BM = 64, BN = 64;
     constexpr int LD = HD + 8;
     constexpr int THREADS = 128 * WN;
-    constexpr int PLD = ATT_BM + 8;        // row stride of the P^T / dS^T tiles
+    constexpr int PLD = BM + 8;            // row stride of the P^T / dS^T tiles
     constexpr int DW = HD / WN;            // d-columns per warp
-    constexpr int QW = ATT_BM / WN;        // queries per warp in the score products
+    constexpr int QW = BM / WN;            // queries per warp in the score products
+    constexpr int STAGE = 2 * BM * LD;     // elements of one { Q, dO } stage
     extern __shared__ __align__(16) uint8_t smem_attn[];
     __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_attn);
-    __nv_bfloat16* Vs = Ks + ATT_BN * LD;
-    __nv_bfloat16* Qs = Vs + ATT_BN * LD;
-    __nv_bfloat16* dOs = Qs + ATT_BM * LD;
-    __nv_bfloat16* Pt = dOs + ATT_BM * LD;          // [64 keys][PLD]
-    __nv_bfloat16* dSt = Pt + ATT_BN * PLD;
-    float* lse_s = reinterpret_cast<float*>(dSt + ATT_BN * PLD);   // [64] (already * log2e)
-    float* dlt_s = lse_s + ATT_BM;
+    __nv_bfloat16* Vs = Ks + BN * LD;
+    __nv_bfloat16* QdO = Vs + BN * LD;                       // 2 stages of { Q [BM][LD], dO [BM][LD] }
+    __nv_bfloat16* Pt = QdO + 2 * STAGE;                     // [64 keys][PLD]
+    __nv_bfloat16* dSt = Pt + BN * PLD;
+    float* stats = reinterpret_cast<float*>(dSt + BN * PLD);  // 2 stages of { lse [BM], delta [BM] }
 
-    const int jb = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int jb = blockIdx.x, b = blockIdx.z;
+    const int kvh = SPLIT ? blockIdx.y / p.rep : blockIdx.y;
+    const int h_first = SPLIT ? blockIdx.y : kvh * p.rep;
+    const int n_heads_here = SPLIT ? 1 : p.rep;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wm = warp % 4, wn = warp / 4;
     const int g = lane >> 2, tq = lane & 3;
-    const int j0 = jb * ATT_BN;
-    const int rows_k = min(ATT_BN, p.seq - j0);
-    load_tile<ATT_BN, HD, THREADS>(Ks, p.k + (int64_t)b * p.sk.stride_b + (int64_t)j0 * p.sk.stride_s + (int64_t)kvh * p.sk.stride_h, p.sk.stride_s, rows_k);
-    load_tile<ATT_BN, HD, THREADS>(Vs, p.v + (int64_t)b * p.sv.stride_b + (int64_t)j0 * p.sv.stride_s + (int64_t)kvh * p.sv.stride_h, p.sv.stride_s, rows_k);
+    const int j0 = jb * BN;
+    const int rows_k = min(BN, p.seq - j0);
+    load_tile<BN, HD, THREADS>(Ks, p.k + (int64_t)b * p.sk.stride_b + (int64_t)j0 * p.sk.stride_s + (int64_t)kvh * p.sk.stride_h, p.sk.stride_s, rows_k);
+    load_tile<BN, HD, THREADS>(Vs, p.v + (int64_t)b * p.sv.stride_b + (int64_t)j0 * p.sv.stride_s + (int64_t)kvh * p.sv.stride_h, p.sv.stride_s, rows_k);
 
     // queries that can see keys j0 .. j0+63: i >= j0 and i - j < window
-    const int i_max = p.window > 0 ? min(p.seq - 1, j0 + ATT_BN - 1 + p.window - 1) : p.seq - 1;
-    const int qb_lo = j0 / ATT_BM, qb_hi = i_max / ATT_BM;
+    const int i_max = p.window > 0 ? min(p.seq - 1, j0 + BN - 1 + p.window - 1) : p.seq - 1;
+    const int qb_lo = j0 / BM, qb_hi = i_max / BM;
+    const int nq = qb_hi - qb_lo + 1, n_it = nq * n_heads_here;
     const float sl2 = p.scale * LOG2E;
+    auto prefetch = [&](int it, int st) {
+        const int h = h_first + it / nq, i0 = (qb_lo + it % nq) * BM;
+        const int rows_q = min(BM, p.seq - i0);
+        __nv_bfloat16* Qs = QdO + st * STAGE;
+        load_tile<BM, HD, THREADS>(Qs, p.q + (int64_t)b * p.sq.stride_b + (int64_t)i0 * p.sq.stride_s + (int64_t)h * p.sq.stride_h, p.sq.stride_s, rows_q);
+        load_tile<BM, HD, THREADS>(Qs + BM * LD, p.d_o + (int64_t)b * p.sdo.stride_b + (int64_t)i0 * p.sdo.stride_s + (int64_t)h * p.sdo.stride_h, p.sdo.stride_s, rows_q);
+        if (threadIdx.x < 2 * BM) {
+            const int r = threadIdx.x % BM;
+            const bool ok = i0 + r < p.seq;
+            const int64_t idx = ((int64_t)b * p.n_heads + h) * p.seq + (ok ? i0 + r : 0);
+            cp_async4z(stats + st * 2 * BM + threadIdx.x, (threadIdx.x < BM ? p.lse : p.delta) + idx, ok);
+        }
+        cp_commit();
+    };
+    prefetch(0, 0);
 
     float dk[DW / 8][4], dv[DW / 8][4];
 #pragma unroll
     for (int i = 0; i < DW / 8; ++i) { dk[i][0] = dk[i][1] = dk[i][2] = dk[i][3] = 0.f; dv[i][0] = dv[i][1] = dv[i][2] = dv[i][3] = 0.f; }
 
-    for (int hr = 0; hr < p.rep; ++hr) {
-        const int h = kvh * p.rep + hr;
-        for (int qb = qb_lo; qb <= qb_hi; ++qb) {
-            const int i0 = qb * ATT_BM;
-            const int rows_q = min(ATT_BM, p.seq - i0);
-            __syncthreads();
-            load_tile<ATT_BM, HD, THREADS>(Qs, p.q + (int64_t)b * p.sq.stride_b + (int64_t)i0 * p.sq.stride_s + (int64_t)h * p.sq.stride_h, p.sq.stride_s, rows_q);
-            load_tile<ATT_BM, HD, THREADS>(dOs, p.d_o + (int64_t)b * p.sdo.stride_b + (int64_t)i0 * p.sdo.stride_s + (int64_t)h * p.sdo.stride_h, p.sdo.stride_s, rows_q);
-            if (threadIdx.x < ATT_BM) {
-                const int i = i0 + threadIdx.x;
-                const bool ok = i < p.seq;
-                const int64_t idx = ((int64_t)b * p.n_heads + h) * p.seq + (ok ? i : 0);
-                lse_s[threadIdx.x] = ok ? p.lse[idx] * LOG2E : 0.f;
-                dlt_s[threadIdx.x] = ok ? p.delta[idx] : 0.f;
-            }
-            cp_commit_wait_all();
-            __syncthreads();
+    for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        const int i0 = (qb_lo + it % nq) * BM;
+        cp_wait_all();
+        __syncthreads();     // stage `st` has landed; everyone is done with the other stage and with Pt / dSt
+        if (it + 1 < n_it) prefetch(it + 1, st ^ 1);
+        const __nv_bfloat16* Qs = QdO + st * STAGE;
+        const __nv_bfloat16* dOs = Qs + BM * LD;
+        const float* lse_s = stats + st * 2 * BM;
+        const float* dlt_s = lse_s + BM;
 
-            // S^T[key, query] and dP^T[key, query] for this warp's 16 keys x QW queries
-            float st[QW / 8][4], dpt[QW / 8][4];
+        // S^T[key, query] and dP^T[key, query] for this warp's 16 keys x QW queries
+        float st_[QW / 8][4], dpt[QW / 8][4];
 #pragma unroll
-            for (int i = 0; i < QW / 8; ++i) { st[i][0] = st[i][1] = st[i][2] = st[i][3] = 0.f; dpt[i][0] = dpt[i][1] = dpt[i][2] = dpt[i][3] = 0.f; }
+        for (int i = 0; i < QW / 8; ++i) { st_[i][0] = st_[i][1] = st_[i][2] = st_[i][3] = 0.f; dpt[i][0] = dpt[i][1] = dpt[i][2] = dpt[i][3] = 0.f; }
 #pragma unroll
-            for (int kk = 0; kk < HD; kk += 16) {
-                uint32_t ak[4], av[4];
-                const int arow = wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                ldsm_x4(ak, Ks + arow * LD + kk + (lane >> 4) * 8);
-                ldsm_x4(av, Vs + arow * LD + kk + (lane >> 4) * 8);
+        for (int kk = 0; kk < HD; kk += 16) {
+            uint32_t ak[4], av[4];
+            const int arow = wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            ldsm_x4(ak, Ks + arow * LD + kk + (lane >> 4) * 8);
+            ldsm_x4(av, Vs + arow * LD + kk + (lane >> 4) * 8);
 #pragma unroll
-                for (int nb = 0; nb < QW / 8; nb += 2) {
-                    uint32_t bq[4], bd[4];
-                    const int brow = wn * QW + nb * 8 + (lane & 7) + (lane >> 4) * 8;
-                    ldsm_x4(bq, Qs + brow * LD + kk + ((lane >> 3) & 1) * 8);
-                    ldsm_x4(bd, dOs + brow * LD + kk + ((lane >> 3) & 1) * 8);
-                    mma16816(st[nb], ak, bq[0], bq[1]);
-                    mma16816(st[nb + 1], ak, bq[2], bq[3]);
-                    mma16816(dpt[nb], av, bd[0], bd[1]);
-                    mma16816(dpt[nb + 1], av, bd[2], bd[3]);
-                }
+            for (int nb = 0; nb < QW / 8; nb += 2) {
+                uint32_t bq[4], bd[4];
+                const int brow = wn * QW + nb * 8 + (lane & 7) + (lane >> 4) * 8;
+                ldsm_x4(bq, Qs + brow * LD + kk + ((lane >> 3) & 1) * 8);
+                ldsm_x4(bd, dOs + brow * LD + kk + ((lane >> 3) & 1) * 8);
+                mma16816(st_[nb], ak, bq[0], bq[1]);
+                mma16816(st_[nb + 1], ak, bq[2], bq[3]);
+                mma16816(dpt[nb], av, bd[0], bd[1]);
+                mma16816(dpt[nb + 1], av, bd[2], bd[3]);
             }
+        }
 #pragma unroll
-            for (int nb = 0; nb < QW / 8; ++nb)
+        for (int nb = 0; nb < QW / 8; ++nb)
 #pragma unroll
-                for (int e = 0; e < 4; e += 2) {
-                    const int jl = wm * 16 + g + (e >> 1) * 8;          // key within tile
-                    const int il = wn * QW + nb * 8 + tq * 2;            // query within tile
-                    float pv[2], ds[2];
+            for (int e = 0; e < 4; e += 2) {
+                const int jl = wm * 16 + g + (e >> 1) * 8;          // key within tile
+                const int il = wn * QW + nb * 8 + tq * 2;            // query within tile
+                float pv[2], ds[2];
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const int i = i0 + il + c, j = j0 + jl;
-                        const bool vis = i < p.seq && visible(i, j, p.seq, p.window);
-                        pv[c] = vis ? exp2f(st[nb][e + c] * sl2 - lse_s[il + c]) : 0.f;
-                        ds[c] = pv[c] * (dpt[nb][e + c] - dlt_s[il + c]);
-                    }
-                    *reinterpret_cast<uint32_t*>(Pt + jl * PLD + il) = pack_bf16(pv[0], pv[1]);
-                    *reinterpret_cast<uint32_t*>(dSt + jl * PLD + il) = pack_bf16(ds[0], ds[1]);
+                for (int c = 0; c < 2; ++c) {
+                    const int i = i0 + il + c, j = j0 + jl;
+                    const bool vis = i < p.seq && visible(i, j, p.seq, p.window);
+                    pv[c] = vis ? exp2f(st_[nb][e + c] * sl2 - lse_s[il + c] * LOG2E) : 0.f;
+                    ds[c] = pv[c] * (dpt[nb][e + c] - dlt_s[il + c]);
                 }
-            __syncthreads();
-            // dV += P^T dO ; dK += dS^T Q  (contraction over the 64 queries)
+                *reinterpret_cast<uint32_t*>(Pt + jl * PLD + il) = pack_bf16(pv[0], pv[1]);
+                *reinterpret_cast<uint32_t*>(dSt + jl * PLD + il) = pack_bf16(ds[0], ds[1]);
+            }
+        __syncthreads();
+        // dV += P^T dO ; dK += dS^T Q  (contraction over the 64 queries)
 #pragma unroll
-            for (int kk = 0; kk < ATT_BM; kk += 16) {
-                uint32_t ap[4], ad[4];
-                const int arow = wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                ldsm_x4(ap, Pt + arow * PLD + kk + (lane >> 4) * 8);
-                ldsm_x4(ad, dSt + arow * PLD + kk + (lane >> 4) * 8);
+        for (int kk = 0; kk < BM; kk += 16) {
+            uint32_t ap[4], ad[4];
+            const int arow = wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            ldsm_x4(ap, Pt + arow * PLD + kk + (lane >> 4) * 8);
+            ldsm_x4(ad, dSt + arow * PLD + kk + (lane >> 4) * 8);
 #pragma unroll
-                for (int db = 0; db < DW / 8; db += 2) {
-                    uint32_t b1[4], b2[4];
-                    const int brow = kk + (lane & 7) + ((lane >> 3) & 1) * 8;
-                    const int bcol = wn * DW + db * 8 + (lane >> 4) * 8;
-                    ldsm_x4_t(b1, dOs + brow * LD + bcol);
-                    ldsm_x4_t(b2, Qs + brow * LD + bcol);
-                    mma16816(dv[db], ap, b1[0], b1[1]);
-                    mma16816(dv[db + 1], ap, b1[2], b1[3]);
-                    mma16816(dk[db], ad, b2[0], b2[1]);
-                    mma16816(dk[db + 1], ad, b2[2], b2[3]);
-                }
+            for (int db = 0; db < DW / 8; db += 2) {
+                uint32_t b1[4], b2[4];
+                const int brow = kk + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int bcol = wn * DW + db * 8 + (lane >> 4) * 8;
+                ldsm_x4_t(b1, dOs + brow * LD + bcol);
+                ldsm_x4_t(b2, Qs + brow * LD + bcol);
+                mma16816(dv[db], ap, b1[0], b1[1]);
+                mma16816(dv[db + 1], ap, b1[2], b1[3]);
+                mma16816(dk[db], ad, b2[0], b2[1]);
+                mma16816(dk[db + 1], ad, b2[2], b2[3]);
             }
         }
     }
@@ -455,15 +498,53 @@ attn_bwd_dkv_kernel(const AttnParams p) {
     for (int r = 0; r < 2; ++r) {
         const int j = j0 + wm * 16 + g + r * 8;
         if (j < p.seq) {
-            __nv_bfloat16* krow = p.dk + (int64_t)b * p.sk.stride_b + (int64_t)j * p.sk.stride_s + (int64_t)kvh * p.sk.stride_h + wn * DW;
-            __nv_bfloat16* vrow = p.dv + (int64_t)b * p.sv.stride_b + (int64_t)j * p.sv.stride_s + (int64_t)kvh * p.sv.stride_h + wn * DW;
+            if constexpr (SPLIT) {
+                const int64_t half = (int64_t)p.batch * p.seq * p.n_kv * HD;
+                float* krow = p.dkv_acc + (((int64_t)b * p.seq + j) * p.n_kv + kvh) * HD + wn * DW;
+                float* vrow = krow + half;
 #pragma unroll
-            for (int db = 0; db < DW / 8; ++db) {
-                *reinterpret_cast<uint32_t*>(krow + db * 8 + tq * 2) = pack_bf16(dk[db][r * 2] * p.scale, dk[db][r * 2 + 1] * p.scale);
-                *reinterpret_cast<uint32_t*>(vrow + db * 8 + tq * 2) = pack_bf16(dv[db][r * 2], dv[db][r * 2 + 1]);
+                for (int db = 0; db < DW / 8; ++db) {
+                    atomicAdd(krow + db * 8 + tq * 2, dk[db][r * 2] * p.scale);
+                    atomicAdd(krow + db * 8 + tq * 2 + 1, dk[db][r * 2 + 1] * p.scale);
+                    atomicAdd(vrow + db * 8 + tq * 2, dv[db][r * 2]);
+                    atomicAdd(vrow + db * 8 + tq * 2 + 1, dv[db][r * 2 + 1]);
+                }
+            } else {
+                __nv_bfloat16* krow = p.dk + (int64_t)b * p.sk.stride_b + (int64_t)j * p.sk.stride_s + (int64_t)kvh * p.sk.stride_h + wn * DW;
+                __nv_bfloat16* vrow = p.dv + (int64_t)b * p.sv.stride_b + (int64_t)j * p.sv.stride_s + (int64_t)kvh * p.sv.stride_h + wn * DW;
+#pragma unroll
+                for (int db = 0; db < DW / 8; ++db) {
+                    *reinterpret_cast<uint32_t*>(krow + db * 8 + tq * 2) = pack_bf16(dk[db][r * 2] * p.scale, dk[db][r * 2 + 1] * p.scale);
+                    *reinterpret_cast<uint32_t*>(vrow + db * 8 + tq * 2) = pack_bf16(dv[db][r * 2], dv[db][r * 2 + 1]);
+                }
             }
         }
     }
+}
+
+// f32 accumulator [2][batch, seq, n_kv, HD] -> bf16 dK / dV with the caller's strides
+template <int HD>
+__global__ void attn_dkv_store_kernel(const AttnParams p) {
+    const int64_t half = (int64_t)p.batch * p.seq * p.n_kv * HD;
+    const int64_t total = 2 * half / 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = i * 4;
+        const bool is_v = e >= half;
+        const int64_t r = is_v ? e - half : e;
+        const int d = (int)(r % HD), kvh = (int)((r / HD) % p.n_kv);
+        const int64_t tok = r / ((int64_t)HD * p.n_kv);
+        const int j = (int)(tok % p.seq), b = (int)(tok / p.seq);
+        const float4 a = *reinterpret_cast<const float4*>(p.dkv_acc + e);
+        const mft_strides_t& ss = is_v ? p.sv : p.sk;
+        __nv_bfloat16* out = (is_v ? p.dv : p.dk) + (int64_t)b * ss.stride_b + (int64_t)j * ss.stride_s + (int64_t)kvh * ss.stride_h + d;
+        *reinterpret_cast<uint2*>(out) = make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+    }
+}
+
+// MFT_ATTN_SHAPE selects an alternative tile shape of the head_dim 256 kernels (tuning aid; 0 = default).
+int attn_shape_override() {
+    static const int v = [] { const char* e = std::getenv("MFT_ATTN_SHAPE"); return e ? std::atoi(e) : 0; }();
+    return v;
 }
 
 template <typename K>
@@ -496,14 +577,16 @@ extern "C" int32_t mft_attn_fwd(const void* q, mft_strides_t sq, const void* k, 
     p.batch = (int)batch; p.seq = (int)seq; p.n_heads = (int)n_heads; p.n_kv = (int)n_kv; p.rep = (int)(n_heads / n_kv);
     p.scale = scale; p.window = (int)window;
     if (int32_t s = check_common(p, hd)) return s;
-    dim3 grid((unsigned)((seq + ATT_BM - 1) / ATT_BM), (unsigned)n_heads, (unsigned)batch);
-#define FWD(HD)                                                                              \
+#define FWD(HD, BM, BN)                                                                      \
     {                                                                                        \
-        const int bytes = 3 * 64 * (HD + 8) * 2;                                             \
-        if (int32_t s = set_smem(attn_fwd_kernel<HD>, bytes)) return s;                      \
-        attn_fwd_kernel<HD><<<grid, 128, bytes, as_stream(stream)>>>(p);                     \
+        dim3 grid((unsigned)((seq + BM - 1) / BM), (unsigned)n_heads, (unsigned)batch);      \
+        const int bytes = (BM + 4 * BN) * (HD + 8) * 2;                                      \
+        if (int32_t s = set_smem(attn_fwd_kernel<HD, BM, BN>, bytes)) return s;              \
+        attn_fwd_kernel<HD, BM, BN><<<grid, BM * 2, bytes, as_stream(stream)>>>(p);          \
     }
-    if (hd == 64) FWD(64) else if (hd == 128) FWD(128) else FWD(256)
+    const int shape = attn_shape_override();
+    if (hd == 64) FWD(64, 128, 64) else if (hd == 128) FWD(128, 128, 64)
+    else if (shape == 1) FWD(256, 64, 64) else if (shape == 2) FWD(256, 128, 32) else FWD(256, 128, 64)
 #undef FWD
     MFT_LAUNCH_CHECK("attn_fwd");
     return MFT_OK;
@@ -514,36 +597,55 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
                                 const float* lse, void* dq, void* dk, void* dv, float* delta, float* dkv_acc, int64_t batch,
                                 int64_t seq, int64_t n_heads, int64_t n_kv, int64_t hd, float scale, int64_t window,
                                 mft_stream_t stream) {
-    (void)dkv_acc;   // dK/dV are produced per KV head without a reduction buffer
     MFT_CHECK_ARG(q && k && v && o && d_o && lse && dq && dk && dv && delta, "mft_attn_bwd: null pointer");
     MFT_CHECK_ARG(batch > 0 && seq > 0 && n_heads > 0 && n_kv > 0 && batch <= 65535 && n_heads <= 65535, "mft_attn_bwd: bad size");
     AttnParams p{};
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.o = (const __nv_bfloat16*)o; p.d_o = (const __nv_bfloat16*)d_o;
     p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
-    p.lse = const_cast<float*>(lse); p.delta = delta;
+    p.lse = const_cast<float*>(lse); p.delta = delta; p.dkv_acc = dkv_acc;
     p.sq = sq; p.sk = sk; p.sv = sv; p.so = so; p.sdo = sdo;
     p.batch = (int)batch; p.seq = (int)seq; p.n_heads = (int)n_heads; p.n_kv = (int)n_kv; p.rep = (int)(n_heads / n_kv);
     p.scale = scale; p.window = (int)window;
     if (int32_t s = check_common(p, hd)) return s;
     const int64_t rows = batch * n_heads * seq;
     const unsigned dblocks = (unsigned)((rows * 32 + 255) / 256);
-    dim3 gq((unsigned)((seq + ATT_BM - 1) / ATT_BM), (unsigned)n_heads, (unsigned)batch);
-    dim3 gk((unsigned)((seq + ATT_BN - 1) / ATT_BN), (unsigned)n_kv, (unsigned)batch);
-#define BWD(HD, WN)                                                                                         \
+    // One CTA per query head adding into the f32 scratch when a KV group has several heads (more, shorter CTAs)
+    const bool split = dkv_acc != nullptr && p.rep > 1;
+    const int shape = attn_shape_override();
+    if (split)
+        if (int32_t s = check_cuda(cudaMemsetAsync(dkv_acc, 0, (size_t)(2 * batch * seq * n_kv * hd) * sizeof(float), as_stream(stream)), "attention dkv memset")) return s;
+    dim3 gk((unsigned)((seq + 63) / 64), (unsigned)(split ? n_heads : n_kv), (unsigned)batch);
+#define DQ(HD, BM, BN)                                                                                      \
+    {                                                                                                       \
+        dim3 gq((unsigned)((seq + BM - 1) / BM), (unsigned)n_heads, (unsigned)batch);                       \
+        const int b1 = (2 * BM + 4 * BN) * (HD + 8) * 2;                                                    \
+        if (int32_t s = set_smem(attn_bwd_dq_kernel<HD, BM, BN>, b1)) return s;                             \
+        attn_bwd_dq_kernel<HD, BM, BN><<<gq, BM * 2, b1, as_stream(stream)>>>(p);                           \
+        MFT_LAUNCH_CHECK("attn_bwd_dq");                                                                    \
+    }
+#define DKV(HD, WN, SPLIT)                                                                                  \
+    {                                                                                                       \
+        const int b2 = 6 * 64 * (HD + 8) * 2 + 2 * 64 * (64 + 8) * 2 + 4 * 64 * 4;                          \
+        if (int32_t s = set_smem(attn_bwd_dkv_kernel<HD, WN, SPLIT>, b2)) return s;                         \
+        attn_bwd_dkv_kernel<HD, WN, SPLIT><<<gk, 128 * WN, b2, as_stream(stream)>>>(p);                     \
+        MFT_LAUNCH_CHECK("attn_bwd_dkv");                                                                   \
+        if (SPLIT) {                                                                                        \
+            attn_dkv_store_kernel<HD><<<148 * 8, 256, 0, as_stream(stream)>>>(p);                           \
+            MFT_LAUNCH_CHECK("attn_dkv_store");                                                             \
+        }                                                                                                   \
+    }
+#define BWD(HD, WN, BM, BN)                                                                                 \
     {                                                                                                       \
         attn_delta_kernel<HD><<<dblocks, 256, 0, as_stream(stream)>>>(p);                                   \
         MFT_LAUNCH_CHECK("attn_delta");                                                                     \
-        const int b1 = 4 * 64 * (HD + 8) * 2;                                                               \
-        if (int32_t s = set_smem(attn_bwd_dq_kernel<HD>, b1)) return s;                                     \
-        attn_bwd_dq_kernel<HD><<<gq, 128, b1, as_stream(stream)>>>(p);                                      \
-        MFT_LAUNCH_CHECK("attn_bwd_dq");                                                                    \
-        const int b2 = 4 * 64 * (HD + 8) * 2 + 2 * 64 * (64 + 8) * 2 + 2 * 64 * 4;                          \
-        if (int32_t s = set_smem(attn_bwd_dkv_kernel<HD, WN>, b2)) return s;                                \
-        attn_bwd_dkv_kernel<HD, WN><<<gk, 128 * WN, b2, as_stream(stream)>>>(p);                            \
-        MFT_LAUNCH_CHECK("attn_bwd_dkv");                                                                   \
+        DQ(HD, BM, BN)                                                                                      \
+        if (split) DKV(HD, WN, true) else DKV(HD, WN, false)                                                \
     }
-    if (hd == 64) BWD(64, 1) else if (hd == 128) BWD(128, 1) else BWD(256, 2)
+    if (hd == 64) BWD(64, 1, 128, 64) else if (hd == 128) BWD(128, 1, 64, 64)
+    else if (shape == 2) BWD(256, 2, 128, 32) else BWD(256, 2, 64, 64)
+#undef DQ
+#undef DKV
 #undef BWD
     return MFT_OK;
 }

@@ -94,6 +94,25 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const __nv_bfl
 }
 
 // ---------------------------------------------------------------- activations
+// bf16 in / bf16 out: the hardware tanh approximation (relative error ~2^-11) is below the output rounding
+// (2^-9), and keeps these kernels at memory speed; the f32 operators use the exact tanhf.
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// value and derivative of the tanh-form GELU from one tanh
+__device__ __forceinline__ void gelu_tanh_both(float x, float& val, float& grad) {
+    const float x2 = x * x;
+    const float t = tanh_fast(0.7978845608f * (x + 0.044715f * x * x2));
+    const float dt = 0.7978845608f * (1.0f + 3.0f * 0.044715f * x2);
+    val = 0.5f * x * (1.0f + t);
+    grad = 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * dt;
+}
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+    return 0.5f * x * (1.0f + tanh_fast(0.7978845608f * (x + 0.044715f * x * x * x)));
+}
+
 template <int KIND>
 __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
                                int64_t ld, __nv_bfloat16* __restrict__ y, int64_t rows, int64_t cols) {
@@ -107,9 +126,9 @@ __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __n
         if (KIND != MFT_ACT_GELU) load8(up + r * ld + c, u);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            if (KIND == MFT_ACT_GELU) o[j] = gelu_tanh_f(g[j]);
+            if (KIND == MFT_ACT_GELU) o[j] = gelu_tanh_fast(g[j]);
             else if (KIND == MFT_ACT_SWIGLU) o[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
-            else o[j] = gelu_tanh_f(g[j]) * u[j];
+            else o[j] = gelu_tanh_fast(g[j]) * u[j];
         }
         store8(y + r * cols + c, o);
     }
@@ -131,14 +150,18 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             if (KIND == MFT_ACT_GELU) {
-                dg[j] = d[j] * gelu_tanh_grad_f(g[j]);
+                float val, grad;
+                gelu_tanh_both(g[j], val, grad);
+                dg[j] = d[j] * grad;
             } else if (KIND == MFT_ACT_SWIGLU) {
                 float s = 1.0f / (1.0f + __expf(-g[j]));
                 dg[j] = d[j] * u[j] * (s * (1.0f + g[j] * (1.0f - s)));
                 du[j] = d[j] * g[j] * s;
             } else {
-                dg[j] = d[j] * u[j] * gelu_tanh_grad_f(g[j]);
-                du[j] = d[j] * gelu_tanh_f(g[j]);
+                float val, grad;
+                gelu_tanh_both(g[j], val, grad);
+                dg[j] = d[j] * u[j] * grad;
+                du[j] = d[j] * val;
             }
         }
         store8(dgate + r * ld + c, dg);

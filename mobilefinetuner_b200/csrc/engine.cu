@@ -348,6 +348,7 @@ extern "C" int32_t mft_model_create(const mft_model_config_t* cfg, mft_stream_t 
     G(dalloc(m, &m->t_qkv, T * QKV, false, true));
     G(dalloc(m, &m->t_pan, T * 64, false, true));
     G(dalloc(m, &m->attn_delta, T * nh, false, true));
+    if (nh > nkv) G(dalloc(m, &m->attn_dkv_acc, 2 * T * nkv * hd, false, true));
     G(dalloc(m, &m->loss_dev, 4, true)); G(dalloc(m, &m->n_valid_dev, 4, true)); G(dalloc(m, &m->status_dev, 4, true));
     G(dalloc(m, &m->ce_lse, T));
     m->ce_ws_bytes = mft_lmhead_ce_workspace_bytes(T, H, V);

@@ -126,6 +126,7 @@ struct mft_model {
     float* dx = nullptr;             // running gradient of the residual stream [T,H] f32
     mft::bf16 *t_h = nullptr, *t_i = nullptr, *t_gu = nullptr, *t_o = nullptr, *t_qk = nullptr, *t_qkv = nullptr, *t_pan = nullptr;
     float *attn_delta = nullptr;
+    float* attn_dkv_acc = nullptr;   // f32 [2][T, n_kv, hd]: per-head dK/dV contributions are added here (grouped-query models)
     float* loss_dev = nullptr; int32_t* n_valid_dev = nullptr; float* ce_lse = nullptr; int32_t* status_dev = nullptr;
     void* ce_ws = nullptr; int64_t ce_ws_bytes = 0;
     bool ce_onepass = true;          // training steps use mft_lmhead_ce_fused (MFT_CE_ONEPASS=0 selects the two-sweep pair)

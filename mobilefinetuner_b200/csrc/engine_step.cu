@@ -174,7 +174,7 @@ int32_t backward(Ctx& c, int64_t n_valid_global) {
         else { q = b.qk_r; k = b.qk_r + QD; ldqk = QD + KD; dq = m->t_qk; dk = m->t_qk + QD; }
         const int64_t window = (gemma && w.sliding) ? cfg.sliding_window : 0;
         TRY(mft_attn_bwd(q, tok_strides(S, ldqk, hd), k, tok_strides(S, ldqk, hd), v, tok_strides(S, QKV, hd), b.o, tok_strides(S, QD, hd),
-                         m->t_o, tok_strides(S, QD, hd), b.lse, dq, dk, dv, m->attn_delta, nullptr, c.B, S, nh, nkv, hd, cfg.attn_scale, window, c.st));
+                         m->t_o, tok_strides(S, QD, hd), b.lse, dq, dk, dv, m->attn_delta, m->attn_dkv_acc, c.B, S, nh, nkv, hd, cfg.attn_scale, window, c.st));
         if (!gpt2) {
             const float* cs = (gemma && w.sliding) ? m->cos_l : m->cos_g;
             const float* sn = (gemma && w.sliding) ? m->sin_l : m->sin_g;

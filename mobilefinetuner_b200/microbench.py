@@ -36,6 +36,7 @@ def _time(fn, iters, warm=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kind", choices=["gemm", "attn", "tn", "ce"])
+    ap.add_argument("--no-split", action="store_true", help="attn: one CTA per KV group in the dK/dV kernel")
     ap.add_argument("--m", type=int, default=16384); ap.add_argument("--n", type=int, default=13824); ap.add_argument("--k", type=int, default=1152)
     ap.add_argument("--k2", type=int, default=0); ap.add_argument("--f32", action="store_true")
     ap.add_argument("--batch", type=int, default=8); ap.add_argument("--heads", type=int, default=4); ap.add_argument("--kv-heads", type=int, default=1)
@@ -65,7 +66,7 @@ def main():
         scale = hd ** -0.5
         o, lse = O.attention_fwd(q, k, v, scale, a.window)
         ms_f = _time(lambda: O.attention_fwd(q, k, v, scale, a.window), a.iters)
-        ms_b = _time(lambda: O.attention_bwd(q, k, v, o, do, lse, scale, a.window), a.iters)
+        ms_b = _time(lambda: O.attention_bwd(q, k, v, o, do, lse, scale, a.window, split_heads=not a.no_split), a.iters)
         pairs = sum(min(i + 1, a.window) if a.window > 0 else i + 1 for i in range(s)) * b * nh
         out.update(batch=b, heads=nh, kv_heads=nkv, seq=s, head_dim=hd, window=a.window, fwd_ms=ms_f, bwd_ms=ms_b,
                    fwd_tflops=4.0 * hd * pairs / ms_f / 1e9, bwd_tflops=8.0 * hd * pairs / ms_b / 1e9)

@@ -174,16 +174,19 @@ def attention_fwd(q, k, v, scale, window=0):
     return o, lse
 
 
-def attention_bwd(q, k, v, o, d_o, lse, scale, window=0):
+def attention_bwd(q, k, v, o, d_o, lse, scale, window=0, split_heads=True):
+    """dQ, dK, dV.  With grouped KV heads and split_heads, each query head runs in its own CTAs and adds its
+    dK/dV share into an f32 scratch; otherwise one CTA walks the whole group."""
     _init(q)
     b, nh, s, hd = q.shape
     nkv = k.shape[1]
+    acc = torch.empty(2 * b * s * nkv * hd, device=q.device, dtype=F32) if (split_heads and nh > nkv) else None
     dq = torch.empty_strided(q.shape, q.stride(), device=q.device, dtype=BF16)
     dk = torch.empty_strided(k.shape, k.stride(), device=q.device, dtype=BF16)
     dv = torch.empty_strided(v.shape, v.stride(), device=q.device, dtype=BF16)
     delta = torch.empty(b, nh, s, device=q.device, dtype=F32)
     L.call("mft_attn_bwd", _p(q), _strides_bhsd(q), _p(k), _strides_bhsd(k), _p(v), _strides_bhsd(v), _p(o), _strides_bhsd(o),
-           _p(d_o), _strides_bhsd(d_o), _p(lse), _p(dq), _p(dk), _p(dv), _p(delta), None,
+           _p(d_o), _strides_bhsd(d_o), _p(lse), _p(dq), _p(dk), _p(dv), _p(delta), _p(acc) if acc is not None else None,
            b, s, nh, nkv, hd, float(scale), int(window), _stream())
     return dq, dk, dv
 

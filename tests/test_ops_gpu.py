@@ -135,7 +135,7 @@ def test_lora_linear_model_width(ops):
 
 
 # ------------------------------------------------------------------ attention
-def run_attention(ops, q, k, v, dO, scale, window, theta):
+def run_attention(ops, q, k, v, dO, scale, window, theta, split_heads=True):
     bf = torch.bfloat16
     B, nh, S, hd = q.shape
     nkv = k.shape[1]
@@ -150,17 +150,18 @@ def run_attention(ops, q, k, v, dO, scale, window, theta):
         qd = ops.headnorm_rope_fwd(q_in.permute(0, 2, 1, 3).reshape(B * S, nh * hd), S, nh, hd, cos, sin)[0].view(B, S, nh, hd).permute(0, 2, 1, 3)
         kd = ops.headnorm_rope_fwd(k_in.permute(0, 2, 1, 3).reshape(B * S, nkv * hd), S, nkv, hd, cos, sin)[0].view(B, S, nkv, hd).permute(0, 2, 1, 3)
     o, lse = ops.attention_fwd(qd, kd, vd, scale, window)
-    dq, dk, dv = ops.attention_bwd(qd, kd, vd, o, dod, lse, scale, window)
+    dq, dk, dv = ops.attention_bwd(qd, kd, vd, o, dod, lse, scale, window, split_heads=split_heads)
     if theta > 0:
         dq = ops.headnorm_rope_bwd(dq.permute(0, 2, 1, 3).reshape(B * S, nh * hd), None, S, nh, hd, cos, sin).view(B, S, nh, hd).permute(0, 2, 1, 3)
         dk = ops.headnorm_rope_bwd(dk.permute(0, 2, 1, 3).reshape(B * S, nkv * hd), None, S, nkv, hd, cos, sin).view(B, S, nkv, hd).permute(0, 2, 1, 3)
     return host(o), host(dq), host(dk), host(dv)
 
 
+@pytest.mark.parametrize("split_heads", [True, False])
 @pytest.mark.parametrize("name", ["attn_causal_gqa", "attn_window_rope", "attn_hd256_window", "attn_hd128"])
-def test_attention_golden(ops, golden, name):
+def test_attention_golden(ops, golden, name, split_heads):
     i, o, p = golden.case(name)
-    out, dq, dk, dv = run_attention(ops, i["q"], i["k"], i["v"], i["dO"], p["scale"], int(p["window"]), p["rope_theta"])
+    out, dq, dk, dv = run_attention(ops, i["q"], i["k"], i["v"], i["dO"], p["scale"], int(p["window"]), p["rope_theta"], split_heads)
     close_bf16(out, o["O"]); close_bf16(dq, o["dQ"]); close_bf16(dk, o["dK"]); close_bf16(dv, o["dV"])
 
 

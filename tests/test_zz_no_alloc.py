@@ -22,7 +22,7 @@ def test_noalloc_backward_matches_regular_entry_point_twice():
         q, k, v, d_o = _problem(seed, *shape)
         scale = shape[-1] ** -0.5
         o, lse = O.attention_fwd(q, k, v, scale, window)
-        want = O.attention_bwd(q, k, v, o, d_o, lse, scale, window)
+        want = O.attention_bwd(q, k, v, o, d_o, lse, scale, window, split_heads=False)   # the same kernels: bit-identical
         got = O.attention_bwd_noalloc(q, k, v, o, d_o, lse, scale, window)
         torch.cuda.synchronize()
         for name, a, b in zip(("dq", "dk", "dv"), got, want):
