@@ -300,6 +300,11 @@ int32_t mft_attn_bwd_noalloc(const void* q, mft_strides_t sq, const void* k, mft
  * bf16 [H, table_t_ld] with table_t_ld >= V a multiple of 8 (built once at load).
  * workspace: mft_lmhead_ce_workspace_bytes() bytes of device scratch. */
 int64_t mft_lmhead_ce_workspace_bytes(int64_t n_tokens, int64_t hidden, int64_t vocab);
+/* The panel width is the largest multiple of 8192 columns whose bf16 [n_tokens, panel]
+ * buffer fits a byte budget (default 12 GiB; the whole vocabulary when it fits).  Sets
+ * the budget (bytes > 0) and returns the previous one; changes workspace_bytes, so call
+ * it before sizing the workspace. */
+int64_t mft_lmhead_ce_set_panel_budget(int64_t bytes);
 int32_t mft_lmhead_ce_fwd(const void* hidden_bf16, const void* table_bf16, const int32_t* labels,
                           int64_t batch, int64_t seq, int64_t hidden, int64_t vocab, int32_t ignore_index,
                           float* loss_dev, int32_t* n_valid_dev, float* lse, int32_t* status_dev,

@@ -90,6 +90,7 @@ _SIGS = {
     "mft_attn_bwd_noalloc": [vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, Strides, vp, vp, vp, vp,
                              i64, i64, i64, i64, i64, f32, i64, vp],
     "mft_lmhead_ce_workspace_bytes": [i64, i64, i64],
+    "mft_lmhead_ce_set_panel_budget": [i64],
     "mft_lmhead_ce_fwd": [vp, vp, vp, i64, i64, i64, i64, i32, vp, vp, vp, vp, vp, i64, vp],
     "mft_lmhead_ce_bwd": [vp, vp, vp, i64, vp, i64, i64, i64, i64, i32, vp, vp, i64, f32, vp, vp, i64, vp],
     "mft_lmhead_ce_fused": [vp, vp, vp, i64, vp, i64, i64, i64, i64, i32, i64, f32, vp, vp, vp, vp, vp, vp, i64, vp],
@@ -130,8 +131,9 @@ _SIGS = {
     "mft_adam_step": [vp, vp, vp, vp, i64, i64, f32, f32, f32, f32, f32, vp, f32, f32, i32, vp],
 }
 _RET = {"mft_launch_count": i64, "mft_last_error": C.c_char_p, "mft_lmhead_ce_workspace_bytes": i64,
+        "mft_lmhead_ce_set_panel_budget": i64,
         "mft_model_activation_bytes": i64}
-_NO_STATUS = {"mft_version", "mft_lmhead_ce_workspace_bytes", "mft_model_param_count", "mft_model_lora_count",
+_NO_STATUS = {"mft_version", "mft_lmhead_ce_workspace_bytes", "mft_lmhead_ce_set_panel_budget", "mft_model_param_count", "mft_model_lora_count",
               "mft_model_lora_has_grad"}
 
 

@@ -114,7 +114,7 @@ __device__ __forceinline__ bool visible(int i, int j, int seq, int window) {
 
 // ---------------------------------------------------------------- forward
 // BM queries per CTA (one warp per 16), BN keys per tile.
-template <int HD, int BM, int BN>
+template <int HD, int BM, int BN, int STAGES>
 __global__ void __launch_bounds__(BM * 2)
 attn_fwd_kernel(const AttnParams p) {
     constexpr int LD = HD + 8, THREADS = BM * 2, NB = BN / 8;
@@ -153,10 +153,14 @@ attn_fwd_kernel(const AttnParams p) {
 
     for (int jb = jb_lo; jb <= jb_hi; ++jb) {
         const int j0 = jb * BN;
-        const int st = (jb - jb_lo) & 1;
+        const int st = STAGES == 2 ? (jb - jb_lo) & 1 : 0;
+        if (STAGES == 1 && jb > jb_lo) {
+            __syncthreads();   // everyone is done with the single stage
+            prefetch(jb, 0);
+        }
         cp_wait_all();
-        __syncthreads();   // tile jb has landed; everyone is done with the other stage
-        if (jb < jb_hi) prefetch(jb + 1, st ^ 1);
+        __syncthreads();   // tile jb has landed; with two stages everyone is also done with the other one
+        if (STAGES == 2 && jb < jb_hi) prefetch(jb + 1, st ^ 1);
         const __nv_bfloat16* Ks = KV + st * 2 * BN * LD;
         const __nv_bfloat16* Vs = Ks + BN * LD;
 
@@ -263,7 +267,7 @@ __global__ void attn_delta_kernel(const AttnParams p) {
 }
 
 // ---------------------------------------------------------------- backward: dQ (query-stationary)
-template <int HD, int BM, int BN>
+template <int HD, int BM, int BN, int STAGES>
 __global__ void __launch_bounds__(BM * 2)
 attn_bwd_dq_kernel(const AttnParams p) {
     constexpr int LD = HD + 8, THREADS = BM * 2, NB = BN / 8;
@@ -311,10 +315,14 @@ attn_bwd_dq_kernel(const AttnParams p) {
 
     for (int jb = jb_lo; jb <= jb_hi; ++jb) {
         const int j0 = jb * BN;
-        const int st = (jb - jb_lo) & 1;
+        const int st = STAGES == 2 ? (jb - jb_lo) & 1 : 0;
+        if (STAGES == 1 && jb > jb_lo) {
+            __syncthreads();   // everyone is done with the single stage
+            prefetch(jb, 0);
+        }
         cp_wait_all();
-        __syncthreads();
-        if (jb < jb_hi) prefetch(jb + 1, st ^ 1);
+        __syncthreads();   // tile jb has landed; with two stages everyone is also done with the other one
+        if (STAGES == 2 && jb < jb_hi) prefetch(jb + 1, st ^ 1);
         const __nv_bfloat16* Ks = KV + st * 2 * BN * LD;
         const __nv_bfloat16* Vs = Ks + BN * LD;
         float s[NB][4], dp[NB][4];
@@ -577,16 +585,19 @@ extern "C" int32_t mft_attn_fwd(const void* q, mft_strides_t sq, const void* k, 
     p.batch = (int)batch; p.seq = (int)seq; p.n_heads = (int)n_heads; p.n_kv = (int)n_kv; p.rep = (int)(n_heads / n_kv);
     p.scale = scale; p.window = (int)window;
     if (int32_t s = check_common(p, hd)) return s;
-#define FWD(HD, BM, BN)                                                                      \
+#define FWD(HD, BM, BN, ST)                                                                  \
     {                                                                                        \
         dim3 grid((unsigned)((seq + BM - 1) / BM), (unsigned)n_heads, (unsigned)batch);      \
-        const int bytes = (BM + 4 * BN) * (HD + 8) * 2;                                      \
-        if (int32_t s = set_smem(attn_fwd_kernel<HD, BM, BN>, bytes)) return s;              \
-        attn_fwd_kernel<HD, BM, BN><<<grid, BM * 2, bytes, as_stream(stream)>>>(p);          \
+        const int bytes = (BM + 2 * ST * BN) * (HD + 8) * 2;                                 \
+        if (int32_t s = set_smem(attn_fwd_kernel<HD, BM, BN, ST>, bytes)) return s;          \
+        attn_fwd_kernel<HD, BM, BN, ST><<<grid, BM * 2, bytes, as_stream(stream)>>>(p);      \
     }
     const int shape = attn_shape_override();
-    if (hd == 64) FWD(64, 128, 64) else if (hd == 128) FWD(128, 128, 64)
-    else if (shape == 1) FWD(256, 64, 64) else if (shape == 2) FWD(256, 128, 32) else FWD(256, 128, 64)
+    // measured best on B200: 64-query CTAs (two resident per SM) beat 128-query ones; at head_dim 256 the
+    // second stage costs a resident CTA and loses
+    if (hd == 64) { if (shape == 1) FWD(64, 128, 64, 2) else FWD(64, 64, 64, 2) }
+    else if (hd == 128) { if (shape == 1) FWD(128, 128, 64, 2) else FWD(128, 64, 64, 2) }
+    else if (shape == 1) FWD(256, 128, 64, 2) else if (shape == 2) FWD(256, 64, 32, 2) else FWD(256, 64, 64, 1)
 #undef FWD
     MFT_LAUNCH_CHECK("attn_fwd");
     return MFT_OK;
@@ -616,12 +627,12 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
     if (split)
         if (int32_t s = check_cuda(cudaMemsetAsync(dkv_acc, 0, (size_t)(2 * batch * seq * n_kv * hd) * sizeof(float), as_stream(stream)), "attention dkv memset")) return s;
     dim3 gk((unsigned)((seq + 63) / 64), (unsigned)(split ? n_heads : n_kv), (unsigned)batch);
-#define DQ(HD, BM, BN)                                                                                      \
+#define DQ(HD, BM, BN, ST)                                                                                  \
     {                                                                                                       \
         dim3 gq((unsigned)((seq + BM - 1) / BM), (unsigned)n_heads, (unsigned)batch);                       \
-        const int b1 = (2 * BM + 4 * BN) * (HD + 8) * 2;                                                    \
-        if (int32_t s = set_smem(attn_bwd_dq_kernel<HD, BM, BN>, b1)) return s;                             \
-        attn_bwd_dq_kernel<HD, BM, BN><<<gq, BM * 2, b1, as_stream(stream)>>>(p);                           \
+        const int b1 = (2 * BM + 2 * ST * BN) * (HD + 8) * 2;                                               \
+        if (int32_t s = set_smem(attn_bwd_dq_kernel<HD, BM, BN, ST>, b1)) return s;                         \
+        attn_bwd_dq_kernel<HD, BM, BN, ST><<<gq, BM * 2, b1, as_stream(stream)>>>(p);                       \
         MFT_LAUNCH_CHECK("attn_bwd_dq");                                                                    \
     }
 #define DKV(HD, WN, SPLIT)                                                                                  \
@@ -635,15 +646,16 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
             MFT_LAUNCH_CHECK("attn_dkv_store");                                                             \
         }                                                                                                   \
     }
-#define BWD(HD, WN, BM, BN)                                                                                 \
+#define BWD(HD, WN, BM, BN, ST)                                                                             \
     {                                                                                                       \
         attn_delta_kernel<HD><<<dblocks, 256, 0, as_stream(stream)>>>(p);                                   \
         MFT_LAUNCH_CHECK("attn_delta");                                                                     \
-        DQ(HD, BM, BN)                                                                                      \
+        DQ(HD, BM, BN, ST)                                                                                  \
         if (split) DKV(HD, WN, true) else DKV(HD, WN, false)                                                \
     }
-    if (hd == 64) BWD(64, 1, 128, 64) else if (hd == 128) BWD(128, 1, 64, 64)
-    else if (shape == 2) BWD(256, 2, 128, 32) else BWD(256, 2, 64, 64)
+    if (hd == 64) { if (shape == 1) BWD(64, 1, 128, 64, 2) else BWD(64, 1, 64, 64, 2) }
+    else if (hd == 128) BWD(128, 1, 64, 64, 2)
+    else if (shape == 1) BWD(256, 2, 64, 64, 2) else if (shape == 2) BWD(256, 2, 64, 32, 2) else BWD(256, 2, 64, 32, 1)
 #undef DQ
 #undef DKV
 #undef BWD

@@ -99,4 +99,43 @@ __device__ __forceinline__ void epilogue_bf16_tma(const GemmParams& p, const CUt
     }
 }
 
+// f32 outputs: boxes of 32 rows x 32 columns (128-byte rows, same swizzle), written with a tensor store or,
+// when D already holds a partial result (accumulate / K split), added to memory by a tensor reduction.
+template <int BN>
+__device__ __forceinline__ void epilogue_f32_tma(const GemmParams& p, const CUtensorMap* map_d, uint8_t* store_smem, uint32_t taddr,
+                                                 int q, int lane, int store_row0, int n0, bool add_bias, int& box_ctr) {
+    using namespace ptx;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+        if (n0 + c >= p.n) break;          // uniform across the warp
+        uint8_t* buf = store_smem + (q * 2 + (box_ctr & 1)) * EPI_BOX_BYTES;
+        const uint32_t buf_addr = smem_u32(buf) + (uint32_t)lane * 128u;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + (uint32_t)c, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * p.alpha);
+        if (add_bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (col0 + j < p.n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(p.bias + col0 + j));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t pos = (uint32_t)(j ^ (lane & 7));   // 128-byte swizzle
+            st_shared_v4(buf_addr + pos * 16u, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            if (p.f32_reduce) tma_reduce_add_2d(map_d, buf, col0, store_row0);
+            else tma_store_2d(map_d, buf, col0, store_row0);
+            tma_store_commit();
+        }
+        ++box_ctr;
+    }
+}
+
 }  // namespace mft

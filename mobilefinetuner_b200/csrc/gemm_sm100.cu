@@ -65,9 +65,9 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int num_tiles = p.tiles_mn * p.splits;
     const int num_kb_main = (p.k + GEMM_BK - 1) / GEMM_BK;
-    const int num_kb = num_kb_main + (p.k2 > 0 ? 1 : 0);
+    const int num_kb = num_kb_main + (p.k2 > 0 ? 1 : 0);     // splits > 1 only without the second segment
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -93,9 +93,11 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = tile_m(tile, p) * GEMM_BM;
-                const int n0 = tile_n(tile, p) * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int t2 = tile % p.tiles_mn, split = tile / p.tiles_mn;
+                const int m0 = tile_m(t2, p) * GEMM_BM;
+                const int n0 = tile_n(t2, p) * BN;
+                const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
                     uint8_t* sb = sa + Cfg::A_BYTES;
@@ -119,7 +121,6 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = idesc_bf16_f32(GEMM_BM, BN);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
@@ -129,7 +130,12 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int split = tile / p.tiles_mn;
+                const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+                // a ragged last column tile issues narrower MMAs (existing columns rounded up to 16)
+                const int n_left = p.n - tile_n(tile % p.tiles_mn, p) * BN;
+                const uint32_t idesc = idesc_bf16_f32(GEMM_BM, (uint32_t)min(BN, (n_left + 15) & ~15));
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
@@ -140,7 +146,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int nmma = (kvalid + 15) / 16;
                     for (int j = 0; j < nmma; ++j) {
                         // advance 16 bf16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
-                        umma_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb | j) != 0 ? 1u : 0u);
+                        umma_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb > kb0 || j != 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[stage]);   // frees the stage once these MMAs have read it
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
@@ -160,13 +166,16 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            const int m0 = tile_m(tile, p) * GEMM_BM;
-            const int n0 = tile_n(tile, p) * BN;
+            const int t2 = tile % p.tiles_mn;
+            const int m0 = tile_m(t2, p) * GEMM_BM;
+            const int n0 = tile_n(t2, p) * BN;
             if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + row_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            if (EPI != EPI_CE_STATS && p.tma_store) {
+            if (EPI == EPI_STORE && p.tma_store && p.d_is_f32) {
+                epilogue_f32_tma<BN>(p, &map_d, store_smem, taddr, q, lane, m0 + q * 32, n0, p.bias != nullptr && tile < p.tiles_mn, box_ctr);
+            } else if (EPI != EPI_CE_STATS && p.tma_store) {
                 epilogue_bf16_tma<EPI, BN>(p, &map_d, store_smem, taddr, q, lane, row, m0 + q * 32, n0, box_ctr);
             } else if constexpr (EPI == EPI_STORE) {
 #pragma unroll 1
@@ -341,6 +350,21 @@ int32_t make_tmap_bf16(CUtensorMap* map, const void* base, int64_t rows, int64_t
     return MFT_OK;
 }
 
+// Tensor map over a row-major f32 matrix [rows, cols]: box = {32 columns, 32 rows}, 128-byte swizzle.
+int32_t make_tmap_f32_out(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail(MFT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MFT_ERR_CUDA, "cuTensorMapEncodeTiled (f32 output) failed with code " + std::to_string((int)r));
+    return MFT_OK;
+}
+
 static int g_num_sms = 0;
 int num_sms() {
     if (g_num_sms == 0) {
@@ -363,7 +387,26 @@ static int32_t launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const C
     }
     p.num_m_tiles = (p.m + GEMM_BM - 1) / GEMM_BM;
     p.num_n_tiles = (p.n + BN - 1) / BN;
-    const int tiles = p.num_m_tiles * p.num_n_tiles;
+    p.tiles_mn = p.num_m_tiles * p.num_n_tiles;
+    const int num_kb = (p.k + GEMM_BK - 1) / GEMM_BK + (p.k2 > 0 ? 1 : 0);
+    if (p.splits == 0) {
+        // choose the K split that fills the last wave best (each range keeps >= 32 k-blocks)
+        double best = 0.0;
+        p.splits = 1;
+        for (int sp = 1; sp <= 8 && num_kb / sp >= 32; ++sp) {
+            const long long t = (long long)p.tiles_mn * sp, waves = (t + num_sms() - 1) / num_sms();
+            const double eff = (double)t / (double)(waves * num_sms());
+            if (eff > best + 0.02) { best = eff; p.splits = sp; }
+        }
+    }
+    p.kb_per_split = (num_kb + p.splits - 1) / p.splits;
+    p.splits = (num_kb + p.kb_per_split - 1) / p.kb_per_split;       // no empty range
+    if (p.splits > 1 && !p.f32_reduce) {
+        // the partial tiles are added into D: start from zero
+        if (int32_t s = check_cuda(cudaMemset2DAsync(p.d, (size_t)p.ldd * 4, 0, (size_t)p.n * 4, (size_t)p.m, stream), "gemm split-K memset")) return s;
+        p.f32_reduce = 1;
+    }
+    const int tiles = p.tiles_mn * p.splits;
     const int grid = tiles < num_sms() ? tiles : num_sms();
     gemm_nt_kernel<BN, EPI><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, md, p);
     MFT_LAUNCH_CHECK("gemm_nt");
@@ -429,14 +472,22 @@ static int32_t gemm_nt_run_inner(const GemmCall& c, cudaStream_t stream) {
     // bf16 outputs go through shared memory and TMA tensor stores (coalesced 128-byte rows, edges clipped by the
     // tensor map); f32 / accumulating outputs and oddly strided D keep the direct register -> global path
     CUtensorMap md = ma;
-    const bool tma_store = c.epi != EPI_CE_STATS && !c.d_is_f32 && (c.ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(c.d) % 16 == 0);
-    if (tma_store) {
+    const bool f32_tma = c.epi == EPI_STORE && c.d_is_f32 && (c.ldd % 4 == 0) && (reinterpret_cast<uintptr_t>(c.d) % 16 == 0);
+    const bool tma_store = f32_tma || (c.epi != EPI_CE_STATS && !c.d_is_f32 && (c.ldd % 8 == 0) && (reinterpret_cast<uintptr_t>(c.d) % 16 == 0));
+    if (f32_tma) {
+        if (int32_t s = make_tmap_f32_out(&md, c.d, c.m, c.n, c.ldd)) return s;
+    } else if (tma_store) {
         if (int32_t s = make_tmap_bf16(&md, c.d, c.m, c.n, c.ldd, 32)) return s;
     }
+    MFT_CHECK_ARG(c.splits >= 0 && c.splits <= 64, "gemm_nt: bad K split");
+    const bool can_split = f32_tma && c.k2 == 0;
+    MFT_CHECK_ARG(c.splits <= 1 || can_split, "gemm_nt: a K split needs an aligned f32 output and no second segment");
+    const int splits = (c.splits == 0 && !can_split) ? 1 : c.splits;
     GemmParams p{};
     p.m = (int)c.m; p.n = (int)c.n; p.k = (int)c.k; p.k2 = (int)c.k2;
     p.alpha = c.alpha; p.bias = c.bias; p.d = c.d; p.ldd = c.ldd;
     p.d_is_f32 = c.d_is_f32; p.accumulate = c.accumulate; p.tma_store = tma_store ? 1 : 0;
+    p.f32_reduce = (f32_tma && c.accumulate) ? 1 : 0; p.splits = splits;
     p.status = device_status_word();
     p.ce_tgt = c.ce_tgt; p.ce_lse = c.ce_lse; p.ce_nvalid = c.ce_nvalid; p.ce_nvalid_override = c.ce_nvalid_override;
     p.ce_dloss = c.ce_dloss; p.ce_col_offset = c.ce_col_offset; p.ce_partials = c.ce_partials;
@@ -485,5 +536,6 @@ extern "C" int32_t mft_gemm_nt(const void* a, int64_t lda, const void* b, int64_
     c.a = a; c.lda = lda; c.b = b; c.ldb = ldb; c.m = m; c.n = n; c.k = k;
     c.a2 = a2; c.lda2 = lda2; c.b2 = b2; c.ldb2 = ldb2; c.k2 = k2;
     c.bias = bias; c.alpha = alpha; c.d = d; c.ldd = ldd; c.d_is_f32 = d_dtype == MFT_F32; c.accumulate = accumulate;
+    c.splits = 0;     // f32 outputs: K is split when that fills the last wave of tiles better
     return gemm_nt_run(c, as_stream(stream));
 }

@@ -24,6 +24,7 @@ struct GemmCall {
     void* d = nullptr; int64_t ldd = 0;
     int d_is_f32 = 0;
     int accumulate = 0;
+    int splits = 1;               // f32 D only: cut K into this many ranges whose partial tiles are added in memory (0 = choose)
     int epi = EPI_STORE;
     const int32_t* ce_tgt = nullptr;
     const float* ce_lse = nullptr;
@@ -47,7 +48,9 @@ struct GemmParams {
     long long ldd;
     int d_is_f32;
     int accumulate;
-    int tma_store;                // bf16 D written through shared memory + TMA tensor stores
+    int tma_store;                // D written through shared memory + TMA tensor stores (bf16) / stores or reductions (f32)
+    int f32_reduce;               // f32 D through TMA: add into memory (accumulate, or K split) instead of overwrite
+    int splits, kb_per_split, tiles_mn;   // K split: tile index = split * tiles_mn + (m, n) tile
     int32_t* status;
     // cross-entropy epilogues (lm head): see lmhead_ce.cu
     const int32_t* ce_tgt;        // [m] shifted label per row, -1 = row not scored
@@ -82,6 +85,7 @@ int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant for 256 x 256 cluster tiles; returns MFT_ERR_UNSUPPORTED when the call does not qualify.
 int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream);
 int32_t make_tmap_bf16(struct CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
+int32_t make_tmap_f32_out(struct CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld);
 int num_sms();
 
 }  // namespace mft

@@ -12,6 +12,8 @@
 // own tiles; nothing is broadcast).  All waits are bounded, as in the single-CTA kernel.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include "gemm_sm100.h"
@@ -23,11 +25,19 @@ using namespace ptx;
 
 namespace {
 
-constexpr int BM = 128, BK = 64, BN2 = 256, THREADS = 192;
-constexpr int A_BYTES = BM * BK * 2, BH_BYTES = (BN2 / 2) * BK * 2, STAGE_BYTES = A_BYTES + BH_BYTES;   // 32 KB
-constexpr int STAGES = 6;
+constexpr int BM = 128, BK = 64, THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;
 constexpr int STORE_BYTES = 4 * 2 * EPI_BOX_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 + 256;
+// BN2 = columns of the pair's tile.  256 is the only width in use: 192 measured 17 % slower per column and 128
+// 40 % slower (their operand loads per MMA cycle outrun what the L2 delivers), which costs more than the tile
+// quantisation they would save.  Each CTA stages A (16 KB) and BN2/2 rows of B per k-block.
+template <int BN2>
+struct PairCfg {
+    static constexpr int BH_BYTES = (BN2 / 2) * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + BH_BYTES;                  // 32 / 28 KB, multiples of 1024
+    static constexpr int STAGES = 6;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 + 256;
+};
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;   // clears the bit that distinguishes the two CTAs of a pair: -> address in the leader
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -75,11 +85,12 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
-template <int EPI>
+template <int EPI, int BN2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                     const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
+    constexpr int STAGES = PairCfg<BN2>::STAGES, STAGE_BYTES = PairCfg<BN2>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* store_smem = tiles + STAGES * STAGE_BYTES;
@@ -95,9 +106,9 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
     const int num_clusters = gridDim.x / 2, cluster_id = blockIdx.x / 2;
-    const int num_tiles = p.num_m_tiles * p.num_n_tiles;            // 256 x 256 tiles
+    const int num_tiles = p.tiles_mn * p.splits;                    // 256 x BN2 tiles, times the K ranges
     const int num_kb_main = (p.k + BK - 1) / BK;
-    const int num_kb = num_kb_main + (p.k2 > 0 ? 1 : 0);
+    const int num_kb = num_kb_main + (p.k2 > 0 ? 1 : 0);            // splits > 1 only without the second segment
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
@@ -119,9 +130,15 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-                const int m0 = tile_m(tile, p) * 2 * BM + (int)rank * BM;
-                const int n0 = tile_n(tile, p) * BN2 + (int)rank * (BN2 / 2);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int t2 = tile % p.tiles_mn, split = tile / p.tiles_mn;
+                const int m0 = tile_m(t2, p) * 2 * BM + (int)rank * BM;
+                // the MMA of a ragged last column tile is narrowed to the columns that exist (rounded up to 16); a
+                // pair MMA of width n_eff reads n_eff/2 rows of B from each CTA, so the halves are cut there
+                const int n_base = tile_n(t2, p) * BN2;
+                const int n_eff = min(BN2, (p.n - n_base + 15) & ~15);
+                const int n0 = n_base + (int)rank * (n_eff / 2);
+                const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* sa = tiles + stage * STAGE_BYTES;
                     uint8_t* sb = sa + A_BYTES;
@@ -141,7 +158,6 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer (leader CTA only)
         if (leader && lane == 0) {
-            constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN2);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
@@ -151,7 +167,11 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN2;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int split = tile / p.tiles_mn;
+                const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+                const int n_base = tile_n(tile % p.tiles_mn, p) * BN2;
+                const uint32_t idesc = idesc_bf16_f32(2 * BM, (uint32_t)min(BN2, (p.n - n_base + 15) & ~15));
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
@@ -160,7 +180,7 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int kvalid = (kb < num_kb_main) ? min(BK, p.k - kb * BK) : p.k2;
                     const int nmma = (kvalid + 15) / 16;
                     for (int j = 0; j < nmma; ++j)
-                        umma2_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb | j) != 0 ? 1u : 0u);
+                        umma2_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb > kb0 || j != 0) ? 1u : 0u);
                     umma2_commit_both(&empty_bar[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -176,13 +196,17 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            const int m0 = tile_m(tile, p) * 2 * BM + (int)rank * BM;
-            const int n0 = tile_n(tile, p) * BN2;
+            const int t2 = tile % p.tiles_mn;
+            const int m0 = tile_m(t2, p) * 2 * BM + (int)rank * BM;
+            const int n0 = tile_n(t2, p) * BN2;
             if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + row_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN2);
-            epilogue_bf16_tma<EPI, BN2>(p, &map_d, store_smem, taddr, q, lane, row, m0 + q * 32, n0, box_ctr);
+            if (EPI == EPI_STORE && p.d_is_f32)
+                epilogue_f32_tma<BN2>(p, &map_d, store_smem, taddr, q, lane, m0 + q * 32, n0, p.bias != nullptr && tile < p.tiles_mn, box_ctr);
+            else
+                epilogue_bf16_tma<EPI, BN2>(p, &map_d, store_smem, taddr, q, lane, row, m0 + q * 32, n0, box_ctr);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc]) & PEER_MASK);   // the accumulator buffer is free (count 8: 4 warps x 2 CTAs)
@@ -201,50 +225,88 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-template <int EPI>
+template <int EPI, int BN2>
 int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2, const CUtensorMap& md,
                GemmParams p, cudaStream_t stream) {
+    using Cfg = PairCfg<BN2>;
     static bool configured = false;
     if (!configured) {
-        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_2cta_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), "gemm 2cta smem attr")) return s;
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_2cta_kernel<EPI, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm 2cta smem attr")) return s;
         configured = true;
     }
-    p.num_m_tiles = (p.m + 2 * BM - 1) / (2 * BM);
-    p.num_n_tiles = (p.n + BN2 - 1) / BN2;
-    const int tiles = p.num_m_tiles * p.num_n_tiles;
+    const int tiles = p.tiles_mn * p.splits;
     int clusters = num_sms() / 2;
     if (tiles < clusters) clusters = tiles;
-    gemm_nt_2cta_kernel<EPI><<<2 * clusters, THREADS, SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, md, p);
+    gemm_nt_2cta_kernel<EPI, BN2><<<2 * clusters, THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, md, p);
     MFT_LAUNCH_CHECK("gemm_nt_2cta");
     return MFT_OK;
+}
+
+// Number of K ranges for an f32 output whose caller leaves the choice open: fewest waves of tiles over the
+// clusters per unit of work, each extra range charged 0.2 % for its pass over D.  (A ragged last column tile
+// counts as a full one: narrowing its MMAs was measured to save nothing, the main loop is bound by operand
+// delivery.)
+int choose_splits(int64_t m, int64_t n, int64_t kb) {
+    const int64_t clusters = num_sms() / 2, tiles_mn = ((m + 255) / 256) * ((n + 255) / 256);
+    int best_sp = 1;
+    double best = 1e300;
+    for (int sp = 1; sp <= 8; ++sp) {
+        if (sp > 1 && kb / sp < 32) break;
+        const int64_t per = (kb + sp - 1) / sp, waves = (tiles_mn * sp + clusters - 1) / clusters;
+        const double cost = (double)waves * ((double)per + 4.0) * (1.0 + 0.002 * (sp - 1));
+        if (cost < best * 0.995) { best = cost; best_sp = sp; }
+    }
+    return best_sp;
 }
 
 }  // namespace
 
 int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
-    const bool ok = (c.epi == EPI_STORE || c.epi == EPI_CE_GRAD || c.epi == EPI_CE_P) && !c.d_is_f32 && !c.accumulate && c.d && (c.ldd % 8 == 0) &&
-                    (reinterpret_cast<uintptr_t>(c.d) % 16 == 0) && c.m >= 256 && c.n >= 192;
+    const bool ce = c.epi == EPI_CE_GRAD || c.epi == EPI_CE_P;
+    const bool bf16_ok = !c.d_is_f32 && !c.accumulate && (c.ldd % 8 == 0);
+    const bool f32_ok = c.d_is_f32 && c.epi == EPI_STORE && (c.ldd % 4 == 0);
+    const bool ok = (c.epi == EPI_STORE || ce) && (bf16_ok || f32_ok) && c.d && (reinterpret_cast<uintptr_t>(c.d) % 16 == 0) &&
+                    c.m >= 256 && c.n >= 192 && c.splits >= 0 && c.splits <= 64;
     if (!ok) return MFT_ERR_UNSUPPORTED;
+    const bool can_split = f32_ok && c.k2 == 0;
+    if (c.splits > 1 && !can_split) return MFT_ERR_UNSUPPORTED;
+    const int64_t kb = (c.k + BK - 1) / BK + (c.k2 > 0 ? 1 : 0);
+    const int bn = 256;
+    const int splits = !can_split ? 1 : (c.splits == 0 ? choose_splits(c.m, c.n, kb) : c.splits);
     CUtensorMap ma, mb, ma2, mb2, md;
     if (int32_t s = make_tmap_bf16(&ma, c.a, c.m, c.k, c.lda, BM)) return s;
-    if (int32_t s = make_tmap_bf16(&mb, c.b, c.n, c.k, c.ldb, BN2 / 2)) return s;
+    if (int32_t s = make_tmap_bf16(&mb, c.b, c.n, c.k, c.ldb, bn / 2)) return s;
     if (c.k2 > 0) {
         if (int32_t s = make_tmap_bf16(&ma2, c.a2, c.m, c.k2, c.lda2, BM)) return s;
-        if (int32_t s = make_tmap_bf16(&mb2, c.b2, c.n, c.k2, c.ldb2, BN2 / 2)) return s;
+        if (int32_t s = make_tmap_bf16(&mb2, c.b2, c.n, c.k2, c.ldb2, bn / 2)) return s;
     } else {
         ma2 = ma; mb2 = mb;
     }
-    if (int32_t s = make_tmap_bf16(&md, c.d, c.m, c.n, c.ldd, 32)) return s;
+    if (c.d_is_f32) {
+        if (int32_t s = make_tmap_f32_out(&md, c.d, c.m, c.n, c.ldd)) return s;
+    } else {
+        if (int32_t s = make_tmap_bf16(&md, c.d, c.m, c.n, c.ldd, 32)) return s;
+    }
     GemmParams p{};
     p.m = (int)c.m; p.n = (int)c.n; p.k = (int)c.k; p.k2 = (int)c.k2;
     p.alpha = c.alpha; p.bias = c.bias; p.d = c.d; p.ldd = c.ldd; p.tma_store = 1;
+    p.d_is_f32 = c.d_is_f32; p.accumulate = c.accumulate; p.f32_reduce = (c.d_is_f32 && c.accumulate) ? 1 : 0;
     p.status = device_status_word();
     p.ce_tgt = c.ce_tgt; p.ce_lse = c.ce_lse; p.ce_nvalid = c.ce_nvalid; p.ce_nvalid_override = c.ce_nvalid_override;
     p.ce_dloss = c.ce_dloss; p.ce_col_offset = c.ce_col_offset;
     p.ce_partials = c.ce_partials; p.ce_partial_ld = c.ce_partial_ld; p.ce_tgt_logit = c.ce_tgt_logit; p.ce_flag = c.ce_flag;
-    if (c.epi == EPI_CE_GRAD) return launch<EPI_CE_GRAD>(ma, mb, ma2, mb2, md, p, stream);
-    if (c.epi == EPI_CE_P) return launch<EPI_CE_P>(ma, mb, ma2, mb2, md, p, stream);
-    return launch<EPI_STORE>(ma, mb, ma2, mb2, md, p, stream);
+    p.num_m_tiles = (p.m + 2 * BM - 1) / (2 * BM);
+    p.num_n_tiles = (p.n + bn - 1) / bn;
+    p.tiles_mn = p.num_m_tiles * p.num_n_tiles;
+    p.kb_per_split = (int)((kb + splits - 1) / splits);
+    p.splits = (int)((kb + p.kb_per_split - 1) / p.kb_per_split);
+    if (p.splits > 1 && !p.f32_reduce) {
+        if (int32_t s = check_cuda(cudaMemset2DAsync(p.d, (size_t)p.ldd * 4, 0, (size_t)p.n * 4, (size_t)p.m, stream), "gemm split-K memset")) return s;
+        p.f32_reduce = 1;
+    }
+    if (c.epi == EPI_CE_GRAD) return launch<EPI_CE_GRAD, 256>(ma, mb, ma2, mb2, md, p, stream);
+    if (c.epi == EPI_CE_P) return launch<EPI_CE_P, 256>(ma, mb, ma2, mb2, md, p, stream);
+    return launch<EPI_STORE, 256>(ma, mb, ma2, mb2, md, p, stream);
 }
 
 }  // namespace mft

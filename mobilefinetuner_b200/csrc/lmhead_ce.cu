@@ -24,7 +24,8 @@
 namespace mft {
 namespace {
 
-constexpr int64_t PANEL = 8192;
+constexpr int64_t PANEL = 8192;                         // granularity of a vocabulary panel, and the probe of the fused sweep
+int64_t g_panel_budget = 12ll << 30;                    // bytes the bf16 [T, panel] buffer may take
 
 inline int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
@@ -44,7 +45,11 @@ struct CeWorkspace {
 CeWorkspace carve(void* base, int64_t T, int64_t H, int64_t V) {
     CeWorkspace w{};
     w.ntiles = (V + CE_TILE_N - 1) / CE_TILE_N;
-    w.panel = V < PANEL ? (V + 255) / 256 * 256 : PANEL;
+    // as many PANEL-column blocks as the budget allows: one GEMM pair per panel, so fewer panels mean longer
+    // K loops in the dHidden GEMM and fewer passes over its f32 accumulator
+    const int64_t v_pad = (V + 255) / 256 * 256;
+    const int64_t by_budget = std::max<int64_t>(1, g_panel_budget / (T * 2) / PANEL) * PANEL;
+    w.panel = std::min(v_pad, by_budget);
     uint8_t* p = static_cast<uint8_t*>(base);
     int64_t off = 0;
     auto take = [&](int64_t bytes) { uint8_t* r = p ? p + off : nullptr; off += align256(bytes); return r; };
@@ -263,6 +268,12 @@ __global__ void ce_dense_bwd_kernel(const float* __restrict__ logits, const int3
 
 using namespace mft;
 
+extern "C" int64_t mft_lmhead_ce_set_panel_budget(int64_t bytes) {
+    const int64_t old = g_panel_budget;
+    if (bytes > 0) g_panel_budget = bytes;
+    return old;
+}
+
 extern "C" int64_t mft_lmhead_ce_workspace_bytes(int64_t n_tokens, int64_t hidden, int64_t vocab) {
     if (n_tokens <= 0 || hidden <= 0 || vocab <= 0) return 0;
     return carve(nullptr, n_tokens, hidden, vocab).total;
@@ -351,7 +362,7 @@ extern "C" int32_t mft_lmhead_ce_fused(const void* hidden_bf16, const void* tabl
     MFT_LAUNCH_CHECK("ce_prepare");
     // reference exponent per row: log-sum-exp of panel 0
     {
-        const int64_t vc = std::min(w.panel, vocab);
+        const int64_t vc = std::min(PANEL, vocab);
         GemmCall c;
         c.a = hidden_bf16; c.lda = H; c.b = table_bf16; c.ldb = H; c.m = T; c.n = vc; c.k = H;
         c.epi = EPI_CE_STATS; c.ce_tgt = w.tgt; c.ce_partials = w.partials; c.ce_partial_ld = (int)w.ntiles; c.ce_tgt_logit = w.tgt_logit;
@@ -374,7 +385,7 @@ extern "C" int32_t mft_lmhead_ce_fused(const void* hidden_bf16, const void* tabl
         d.a = w.g; d.lda = w.panel;
         d.b = static_cast<const __nv_bfloat16*>(table_t_bf16) + v0; d.ldb = table_t_ld;
         d.m = T; d.n = H; d.k = vc;
-        d.d = w.dh_acc; d.ldd = H; d.d_is_f32 = 1; d.accumulate = v0 > 0;
+        d.d = w.dh_acc; d.ldd = H; d.d_is_f32 = 1; d.accumulate = v0 > 0; d.splits = 0;
         if (int32_t s = gemm_nt_run(d, st)) return s;
     }
     ce_fused_finish_kernel<<<(unsigned)T, 128, 0, st>>>(w.partials, w.ntiles, w.tgt, w.tgt_logit, w.m_ref, w.row_flag, w.dh_acc,

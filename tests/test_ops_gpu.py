@@ -72,6 +72,20 @@ def test_gemm_nt_lora_segment_bias_alpha_accumulate(ops):
     assert rel_err(host(out), want) < 1e-5
 
 
+@pytest.mark.parametrize("m,n,k,accumulate", [(256, 192, 8192, False), (300, 200, 20000, True), (130, 1152, 4104, False), (512, 1152, 8192, False), (768, 384, 16384, True)])
+def test_gemm_nt_f32_deep_k_is_split_and_reduced(ops, m, n, k, accumulate):
+    """f32 outputs with a long K: ranges of K run as separate tiles whose partial sums are added in memory."""
+    g = np.random.Generator(np.random.PCG64(k + m))
+    a, b = rb(g.standard_normal((m, k))), rb(g.standard_normal((n, k)))
+    bias = g.standard_normal(n).astype(np.float32)
+    prev = g.standard_normal((m, n)).astype(np.float32)
+    want = a.astype(np.float64) @ b.astype(np.float64).T + bias + (prev if accumulate else 0.0)
+    out = dev(prev)
+    ops.gemm_nt(dev(a, torch.bfloat16), dev(b, torch.bfloat16), bias=dev(bias), out=out, accumulate=accumulate)
+    assert rel_err(host(out), want) < 1e-5
+    assert ops.device_status() == 0
+
+
 def test_gemm_rejects_bad_arguments(ops):
     from mobilefinetuner_b200._lib import MftError
     a = torch.zeros(8, 12, device="cuda", dtype=torch.bfloat16)   # row stride 12: not a multiple of 8
@@ -327,7 +341,7 @@ def test_lm_head_ce_golden(ops, golden):
     assert ops.device_status() == 0
 
 
-def test_lm_head_ce_large_vocab_vs_restatement(ops):
+def test_lm_head_ce_large_vocab_vs_restatement(ops, ce_panels):
     g = np.random.Generator(np.random.PCG64(31))
     B, S, H, V = 2, 70, 640, 20000          # several vocabulary panels, ragged last tile
     hid = rb(g.standard_normal((B, S, H)))
@@ -358,7 +372,16 @@ def test_lm_head_ce_fused_golden_and_two_sweep(ops, golden):
     assert ops.device_status() == 0
 
 
-def test_lm_head_ce_fused_large_vocab_dp_scaling(ops):
+@pytest.fixture(params=["whole vocabulary", "8192-column panels"])
+def ce_panels(request):
+    """The lm-head loss walks the vocabulary in panels; by default one panel covers it when the buffer fits."""
+    from mobilefinetuner_b200 import _lib as L
+    old = L.call("mft_lmhead_ce_set_panel_budget", 1 if request.param != "whole vocabulary" else 12 << 30)
+    yield request.param
+    L.call("mft_lmhead_ce_set_panel_budget", old)
+
+
+def test_lm_head_ce_fused_large_vocab_dp_scaling(ops, ce_panels):
     g = np.random.Generator(np.random.PCG64(32))
     B, S, H, V = 2, 70, 640, 20000
     hid = rb(g.standard_normal((B, S, H)))
@@ -377,7 +400,7 @@ def test_lm_head_ce_fused_large_vocab_dp_scaling(ops):
     close_bf16(host(dh2), want_dh / 2)
 
 
-def test_lm_head_ce_fused_recomputes_rows_out_of_range(ops):
+def test_lm_head_ce_fused_recomputes_rows_out_of_range(ops, ce_panels):
     """Logits far above the first panel's log-sum-exp: the sweep flags those rows and recomputes them exactly."""
     g = np.random.Generator(np.random.PCG64(33))
     B, S, H, V = 1, 40, 128, 16384 + 300       # second panel holds the large logits
