@@ -43,8 +43,10 @@ int32_t group_bwd(const Ctx& c, LinearGroup& g, const bf16* dy, const bf16* x, c
         TRY(mft_gemm_nt(dy, g.n_total, g.b_kn, g.n_total, c.T, 64, g.n_total, nullptr, 0, nullptr, 0, 0, nullptr, c.lora_scale, gb, 64, MFT_BF16, 0, c.st));
         if (dx) TRY(mft_gemm_nt(dy, g.n_total, g.w_kn, g.n_total, c.T, g.in, g.n_total, gb, 64, g.a_kn, 64, g.k2, nullptr, 1.0f, dx, g.in, MFT_BF16, 0, c.st));
         if (lora_grads) {
-            TRY(mft_gemm_tn_acc(x, g.in, gb, 64, c.T, g.in, 64, 1.0f, g.da_pan, 64, c.st));
-            TRY(mft_gemm_tn_acc(xa, 64, dy, g.n_total, c.T, 64, g.n_total, 1.0f, g.db_pan, g.n_total, c.st));
+            // only the rank columns in use (rounded up to 16) of the 64-wide panels take part
+            const int rq = (g.k2 + 15) / 16 * 16;
+            TRY(mft_gemm_tn_acc(x, g.in, gb, 64, c.T, g.in, rq, 1.0f, g.da_pan, 64, c.st));
+            TRY(mft_gemm_tn_acc(xa, 64, dy, g.n_total, c.T, rq, g.n_total, 1.0f, g.db_pan, g.n_total, c.st));
         }
         return MFT_OK;
     }

@@ -5,6 +5,8 @@
 // by reading U and V once from HBM; the tiny fp32 result is reduced across the
 // T-splits with atomics.  Warp-level mma.sync (m16n8k16, bf16 -> f32) with
 // ldmatrix.trans on both operands, cp.async double buffering.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace mft {
@@ -52,6 +54,8 @@ gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bflo
     if (t_begin >= t_end) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsteps = (int)((t_end - t_begin + TN_TC - 1) / TN_TC);
+    // 8-column blocks of the q-tile that exist (in pairs): a rank-16 panel costs a quarter of the MMAs of a full tile
+    const int nb_lim = min(8, ((Q - q0 + 15) / 16) * 2);
 
     auto load_step = [&](int step, int buf) {
         const int64_t t0 = t_begin + (int64_t)step * TN_TC;
@@ -95,6 +99,7 @@ gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bflo
             }
 #pragma unroll
             for (int nb = 0; nb < 8; nb += 2) {
+                if (nb >= nb_lim) break;
                 uint32_t b[4];
                 const int t = kk + (lane & 7) + ((lane >> 3) & 1) * 8;
                 const int q = nb * 8 + (lane >> 4) * 8;
@@ -138,11 +143,18 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
     const int64_t stride_p = swap ? 1 : ldo, stride_q = swap ? ldo : 1;
     const int tiles_p = (int)((pp + TN_PT - 1) / TN_PT), tiles_q = (int)((qq + TN_QT - 1) / TN_QT);
     const int64_t tiles = (int64_t)tiles_p * tiles_q;
-    int64_t splits = (148 * 6 + tiles - 1) / tiles;
-    const int64_t max_splits = (t + 2 * TN_TC - 1) / (2 * TN_TC);
-    if (splits > max_splits) splits = max_splits;
-    if (splits < 1) splits = 1;
-    if (splits > 65535) splits = 65535;
+    // Split T so that the CTAs fill whole waves (2 resident CTAs per SM): per wave a CTA streams its token range
+    // plus a fixed pipeline-fill / atomic-flush part worth ~256 tokens.
+    const int64_t slots = 148 * 2;
+    const int64_t max_splits = std::min<int64_t>(65535, std::max<int64_t>(1, (t + 2 * TN_TC - 1) / (2 * TN_TC)));
+    int64_t splits = 1;
+    double best = 1e300;
+    for (int64_t sp = 1; sp <= max_splits && sp <= 4096; ++sp) {
+        const int64_t per = ((t + sp - 1) / sp + TN_TC - 1) / TN_TC * TN_TC;
+        const int64_t waves = (tiles * sp + slots - 1) / slots;
+        const double cost = (double)waves * (double)(per + 256);
+        if (cost < best) { best = cost; splits = sp; }
+    }
     int64_t t_per = (t + splits - 1) / splits;
     t_per = (t_per + TN_TC - 1) / TN_TC * TN_TC;
     splits = (t + t_per - 1) / t_per;

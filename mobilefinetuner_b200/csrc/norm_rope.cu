@@ -1,8 +1,10 @@
 // RMSNorm / LayerNorm forward and backward, and the fused per-head
-// RMSNorm + rotary embedding used on Q and K.  One CTA per row for the
-// model-width norms (row cached in registers between the reduction and the
-// write), one warp per (token, head) for the per-head kernel.  HBM-bound:
-// every element is read once and written once with 128-bit accesses.
+// RMSNorm + rotary embedding used on Q and K.  Model-width RMSNorm rows up to
+// 2048 elements are handled one WARP per row (all of the row's 128-bit loads
+// in flight at once, shuffle reductions, no block barrier); wider rows and
+// LayerNorm use one CTA per row.  The row stays in registers between the
+// reduction and the write.  One warp per (token, head) for the per-head
+// kernel.  HBM-bound: every element is read once and written once.
 #include <cmath>
 #include <vector>
 
@@ -101,6 +103,114 @@ rmsnorm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const f
 #pragma unroll
     for (int k = 0; k < NORM_VPT; ++k) {
         const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < nvec) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = g[k][j] * rstd - xv[k][j] * coeff;
+            if (accumulate) {
+                float prev[8];
+                load8(dx + row * dim + i * 8, prev);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] += prev[j];
+            }
+            store8(dx + row * dim + i * 8, o);
+        }
+    }
+}
+
+
+// ---------------------------------------------------------------- RMSNorm, one warp per row (dim <= 256 * VPL)
+constexpr int NORM_WARPS = 8;     // rows per CTA
+
+template <typename TX, typename TY, int VPL>
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rmsnorm_fwd_warp_kernel(const TX* __restrict__ x, const float* __restrict__ w, float eps, int unit_offset,
+                        TY* __restrict__ y, float* __restrict__ rstd_out, const float* __restrict__ residual,
+                        float* __restrict__ sum_out, int64_t rows, int64_t dim) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const TX* xr = x + row * dim;
+    const int nvec = (int)(dim / 8);
+    float v[VPL][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) load8(xr + i * 8, v[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        if (lane + k * 32 < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
+        }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)dim + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float wv[8], o[8];
+            load8(w + i * 8, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = v[k][j] * rstd * (unit_offset ? 1.0f + wv[j] : wv[j]);
+            if (y) store8(y + row * dim + i * 8, o);
+            if (residual) {
+                float r[8];
+                load8(residual + row * dim + i * 8, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) r[j] += o[j];
+                store8(sum_out + row * dim + i * 8, r);
+            }
+        }
+    }
+}
+
+template <typename TDY, typename TX, typename TDX, int VPL>
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rmsnorm_bwd_warp_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
+                        const float* __restrict__ rstd_in, float eps, int unit_offset, TDX* __restrict__ dx,
+                        int accumulate, float* __restrict__ dweight, int64_t rows, int64_t dim) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int nvec = (int)(dim / 8);
+    float xv[VPL][8], g[VPL][8];
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            load8(x + row * dim + i * 8, xv[k]);
+            load8(dy + row * dim + i * 8, g[k]);
+        }
+    }
+    const float rs_in = rstd_in ? rstd_in[row] : 0.f;
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float wv[8];
+            load8(w + i * 8, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (dweight) atomicAdd(dweight + i * 8 + j, g[k][j] * xv[k][j] * rs_in);
+                g[k][j] *= (unit_offset ? 1.0f + wv[j] : wv[j]);
+                dot += g[k][j] * xv[k][j];
+                ss += xv[k][j] * xv[k][j];
+            }
+        }
+    }
+    dot = warp_sum(dot);
+    float rstd = rs_in;
+    if (!rstd_in) rstd = rsqrtf(warp_sum(ss) / (float)dim + eps);
+    const float coeff = rstd * rstd * rstd / (float)dim * dot;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
         if (i < nvec) {
             float o[8];
 #pragma unroll
@@ -321,9 +431,15 @@ int32_t mft_rmsnorm_fwd(const void* x, int32_t xd, const float* w, float eps, in
     MFT_CHECK_ARG(y || (residual && sum_out), "mft_rmsnorm_fwd: nothing to write");
     MFT_CHECK_ARG(!residual || sum_out, "mft_rmsnorm_fwd: residual needs sum_out");
     MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_rmsnorm_fwd: dim must be a multiple of 8 and <= 4096");
-#define CALL(TX, TY) rmsnorm_fwd_kernel<TX, TY><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TX*)x, w, eps, unit_offset, (TY*)y, rstd, residual, sum_out, dim);
+    const unsigned wblocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
+#define WCALL(TX, TY, VPL) rmsnorm_fwd_warp_kernel<TX, TY, VPL><<<wblocks, NORM_WARPS * 32, 0, as_stream(stream)>>>((const TX*)x, w, eps, unit_offset, (TY*)y, rstd, residual, sum_out, rows, dim);
+#define CALL(TX, TY)                                                                                     \
+    if (dim <= 1280) { WCALL(TX, TY, 5) }                                                                \
+    else if (dim <= 2048) { WCALL(TX, TY, 8) }                                                           \
+    else rmsnorm_fwd_kernel<TX, TY><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TX*)x, w, eps, unit_offset, (TY*)y, rstd, residual, sum_out, dim);
     DISPATCH_2(xd, yd, CALL)
 #undef CALL
+#undef WCALL
     MFT_LAUNCH_CHECK("rmsnorm_fwd");
     return MFT_OK;
 }
@@ -335,11 +451,17 @@ int32_t mft_rmsnorm_bwd(const void* dy, int32_t dyd, const void* x, int32_t xd, 
     MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_rmsnorm_bwd: dim must be a multiple of 8 and <= 4096");
     MFT_CHECK_ARG(!accumulate || dxd == MFT_F32, "mft_rmsnorm_bwd: accumulate needs f32 dx");
     MFT_CHECK_ARG(!dweight || rstd, "mft_rmsnorm_bwd: dweight needs rstd");
-#define LAUNCH(TDY, TX, TDX) rmsnorm_bwd_kernel<TDY, TX, TDX><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TDY*)dy, (const TX*)x, w, rstd, eps, unit_offset, (TDX*)dx, accumulate, dweight, dim);
+    const unsigned wblocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
+#define WLAUNCH(TDY, TX, TDX, VPL) rmsnorm_bwd_warp_kernel<TDY, TX, TDX, VPL><<<wblocks, NORM_WARPS * 32, 0, as_stream(stream)>>>((const TDY*)dy, (const TX*)x, w, rstd, eps, unit_offset, (TDX*)dx, accumulate, dweight, rows, dim);
+#define LAUNCH(TDY, TX, TDX)                                                                             \
+    if (dim <= 1280) { WLAUNCH(TDY, TX, TDX, 5) }                                                        \
+    else if (dim <= 2048) { WLAUNCH(TDY, TX, TDX, 8) }                                                   \
+    else rmsnorm_bwd_kernel<TDY, TX, TDX><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TDY*)dy, (const TX*)x, w, rstd, eps, unit_offset, (TDX*)dx, accumulate, dweight, dim);
 #define CALL(TDY, TX) if (dxd == MFT_F32) { LAUNCH(TDY, TX, float) } else if (dxd == MFT_BF16) { LAUNCH(TDY, TX, __nv_bfloat16) } else return fail(MFT_ERR_INVALID_ARG, "mft_rmsnorm_bwd: bad dx dtype");
     DISPATCH_2(dyd, xd, CALL)
 #undef CALL
 #undef LAUNCH
+#undef WLAUNCH
     MFT_LAUNCH_CHECK("rmsnorm_bwd");
     return MFT_OK;
 }
