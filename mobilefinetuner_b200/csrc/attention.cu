@@ -22,6 +22,8 @@
 
 #include <cstdlib>
 
+#include "attention.h"
+
 namespace mft {
 
 namespace {
@@ -64,17 +66,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-struct AttnParams {
-    const __nv_bfloat16 *q, *k, *v, *o, *d_o;
-    __nv_bfloat16 *out, *dq, *dk, *dv;
-    float* lse;
-    float* delta;
-    float* dkv_acc;          // optional f32 [2][batch, seq, n_kv, hd] accumulator of the per-head dK/dV kernel
-    mft_strides_t sq, sk, sv, so, sdo;
-    int batch, seq, n_heads, n_kv, rep;
-    float scale;
-    int window;
-};
 
 // Copy a [ROWS x HD] bf16 tile (row r at g + r*stride, rows >= rows_valid zero-filled)
 // into shared memory with padded row stride HD+8.
@@ -585,6 +576,10 @@ extern "C" int32_t mft_attn_fwd(const void* q, mft_strides_t sq, const void* k, 
     p.batch = (int)batch; p.seq = (int)seq; p.n_heads = (int)n_heads; p.n_kv = (int)n_kv; p.rep = (int)(n_heads / n_kv);
     p.scale = scale; p.window = (int)window;
     if (int32_t s = check_common(p, hd)) return s;
+    {   // tcgen05 kernel when the problem qualifies
+        const int32_t s2 = attn_fwd_sm100(p, (int)hd, as_stream(stream));
+        if (s2 != MFT_ERR_UNSUPPORTED) return s2;
+    }
 #define FWD(HD, BM, BN, ST)                                                                  \
     {                                                                                        \
         dim3 grid((unsigned)((seq + BM - 1) / BM), (unsigned)n_heads, (unsigned)batch);      \

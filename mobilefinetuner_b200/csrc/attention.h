@@ -1,0 +1,25 @@
+// Parameter block shared by the attention kernels (mma.sync kernels in attention.cu, tcgen05 kernels in
+// attention_sm100.cu).
+#pragma once
+#include "common.cuh"
+
+namespace mft {
+
+struct AttnParams {
+    const __nv_bfloat16 *q, *k, *v, *o, *d_o;
+    __nv_bfloat16 *out, *dq, *dk, *dv;
+    float* lse;
+    float* delta;
+    float* dkv_acc;          // optional f32 [2][batch, seq, n_kv, hd] accumulator of the per-head dK/dV kernel
+    mft_strides_t sq, sk, sv, so, sdo;
+    int batch, seq, n_heads, n_kv, rep;
+    float scale;
+    int window;
+};
+
+// Forward pass on the 5th-generation tensor cores (head_dim 256, sequence a multiple of 128, token-major
+// operands).  Returns MFT_ERR_UNSUPPORTED when the problem does not qualify; the caller then uses the
+// mma.sync kernel.
+int32_t attn_fwd_sm100(const AttnParams& p, int hd, cudaStream_t stream);
+
+}  // namespace mft

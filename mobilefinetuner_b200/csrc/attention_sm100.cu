@@ -1,0 +1,354 @@
+// Causal / sliding-window GQA attention on the 5th-generation tensor cores (tcgen05) for head_dim 256.
+//
+// Forward: one CTA per (128 queries, head, batch).  Scores and the output accumulator live in tensor memory:
+//     S = Q K^T      128 x 64 per key tile, two buffers (128 columns)
+//     O += P V       128 x 256 (256 columns)
+// Warp 0 streams K and V tiles with TMA (128-byte swizzle, two stages each), warp 1's one thread issues the
+// MMAs, warps 2..9 are the softmax: two threads share a query row (one tensor-memory lane, 32 of the tile's 64
+// keys each; they exchange their maxima through shared memory), apply the mask as an index predicate,
+// exponentiate against a running reference maximum and write the bf16 probabilities into a swizzled
+// shared-memory tile that the next MMA consumes as its A operand.
+// V is consumed as it lies in memory ([key][d], "MN-major" B operand), so nothing is transposed.
+// The reference maximum is only raised (and O rescaled in tensor memory) when a row's maximum grew by more
+// than 2^8 since the last rescale, which keeps the exponentials below 256 and makes rescales rare.
+// Every mbarrier wait is bounded; a wait that runs out sets the library status word and the CTA leaves.
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "attention.h"
+#include "common.cuh"
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace mft {
+
+using namespace ptx;
+
+namespace {
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int HD = 256, BM = 128, BN = 64, THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps
+constexpr int Q_BYTES = BM * HD * 2;           // 4 boxes of [128 rows x 64 columns]
+constexpr int KV_BYTES = BN * HD * 2;          // 4 boxes of [64 rows x 64 columns]
+constexpr int P_BYTES = BM * BN * 2;           // [128 rows x 64 keys], 128-byte rows
+constexpr int FWD_SMEM = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 160 + 2 * 2 * BM * 4;   // 231,584 of 232,448 bytes
+constexpr int S_COL = 0, O_COL = 128;          // tensor-memory columns: S buffers at 0 / 64, O at 128..383
+constexpr float RESCALE_GAP = 8.0f;            // log2 units
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// B operand stored [k][n] with n contiguous (128-byte swizzled boxes of 64 n-columns, `chunk_bytes` apart):
+// leading byte offset = distance between 64-column chunks, stride byte offset = 1024 (8 k-rows).
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr, uint32_t chunk_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((chunk_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+constexpr uint32_t IDESC_B_MN = 1u << 16;      // instruction-descriptor bit: B operand is MN-major
+
+struct FwdParams {
+    int seq, n_heads, rep, window;
+    float scale;
+    __nv_bfloat16* out;
+    long long so_b, so_s, so_h;
+    float* lse;
+    int32_t* status;
+    int q_col0_stride, kv_col0_stride;         // column of head h in the q / kv tensor maps = h * stride
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ bool visible(int i, int j, int window) { return j <= i && (window <= 0 || i - j < window); }
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+    // The swizzled tiles need 1024-byte alignment and the tiles fill the SM's shared memory to within 1 KB, so
+    // there is no room for alignment slack: the dynamic segment is declared aligned and checked below.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* base = smem_raw;
+    uint8_t* q_smem = base;
+    uint8_t* k_smem = q_smem + Q_BYTES;            // 2 stages
+    uint8_t* v_smem = k_smem + 2 * KV_BYTES;       // 2 stages
+    uint8_t* p_smem = v_smem + 2 * KV_BYTES;       // 2 buffers
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * P_BYTES);
+    uint64_t* q_full = bars;            // [1]
+    uint64_t* k_full = bars + 1;        // [2]
+    uint64_t* v_full = bars + 3;        // [2]
+    uint64_t* k_empty = bars + 5;       // [2]
+    uint64_t* v_empty = bars + 7;       // [2]
+    uint64_t* s_full = bars + 9;        // [2]
+    uint64_t* s_free = bars + 11;       // [2]  256 arrivals
+    uint64_t* p_full = bars + 13;       // [2]  256 arrivals
+    uint64_t* p_free = bars + 15;       // [2]
+    uint64_t* o_done = bars + 17;       // [1]  one completion per P V product
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* mx_smem = reinterpret_cast<float*>(bars + 20);   // [2 buffers][2 halves][128] row maxima, later row sums
+    float* l_smem = mx_smem;
+    if ((smem_u32(smem_raw) & 1023u) != 0) {               // uniform: nothing has been allocated or armed yet
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, MFT_ERR_INVALID_ARG);
+        return;
+    }
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = gridDim.x - 1 - blockIdx.x;     // longest rows first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / p.rep;
+    const int i0 = qb * BM;
+    const int jb_hi = (i0 + BM - 1) / BN;
+    const int jb_lo = p.window > 0 ? max(0, i0 - p.window + 1) / BN : 0;
+    const int n_tiles = jb_hi - jb_lo + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 256); mbar_init(&p_full[s], 256); mbar_init(&p_free[s], 1);
+        }
+        mbar_init(o_done, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const int qx = h * p.q_col0_stride, kx = kvh * p.kv_col0_stride;
+            mbar_arrive_expect_tx(q_full, Q_BYTES);
+            for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + c * (BM * 128), &map_q, q_full, qx + c * 64, b * p.seq + i0);
+            for (int t = 0; t < n_tiles; ++t) {
+                const int st = t & 1;
+                const uint32_t ph = (t >> 1) & 1;
+                const int row = b * p.seq + (jb_lo + t) * BN;
+                if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) break;
+                mbar_arrive_expect_tx(&k_full[st], KV_BYTES);
+                for (int c = 0; c < 4; ++c) tma_load_2d(k_smem + st * KV_BYTES + c * (BN * 128), &map_k, &k_full[st], kx + c * 64, row);
+                if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) break;
+                mbar_arrive_expect_tx(&v_full[st], KV_BYTES);
+                for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + st * KV_BYTES + c * (BN * 128), &map_v, &v_full[st], kx + c * 64, row);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16_f32(BM, BN);
+            constexpr uint32_t idesc_o = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            auto issue_s = [&](int t) {
+                const int st = t & 1;
+                const uint32_t ph = (t >> 1) & 1;
+                if (!mbar_wait(&k_full[st], ph, abort_flag) || !mbar_wait(&s_free[st], ph ^ 1, abort_flag)) { ok = false; return; }
+                tc_fence_after();
+                const uint32_t qa = smem_u32(q_smem), ka = smem_u32(k_smem + st * KV_BYTES);
+                const uint32_t tmem_s = tmem_base + S_COL + st * BN;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        umma_bf16(tmem_s, smem_desc_sw128(qa + c * (BM * 128)) + (uint64_t)(2 * j),
+                                  smem_desc_sw128(ka + c * (BN * 128)) + (uint64_t)(2 * j), idesc_s, (c | j) != 0 ? 1u : 0u);
+                umma_commit(&k_empty[st]);
+                umma_commit(&s_full[st]);
+            };
+            auto issue_pv = [&](int t) {
+                const int st = t & 1;
+                const uint32_t ph = (t >> 1) & 1;
+                if (!mbar_wait(&v_full[st], ph, abort_flag) || !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; return; }
+                tc_fence_after();
+                const uint32_t pa = smem_u32(p_smem + st * P_BYTES), va = smem_u32(v_smem + st * KV_BYTES);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    umma_bf16(tmem_base + O_COL, smem_desc_sw128(pa) + (uint64_t)(2 * j), smem_desc_mn_sw128(va + j * 2048, BN * 128),
+                              idesc_o, (t | j) != 0 ? 1u : 0u);
+                umma_commit(&v_empty[st]);
+                umma_commit(&p_free[st]);
+                umma_commit(o_done);
+            };
+            if (ok) issue_s(0);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                if (t + 1 < n_tiles) issue_s(t + 1);
+                if (ok) issue_pv(t);
+            }
+        }
+    } else {
+        // ------------------------------------------------ softmax: two threads per query row (32 keys each)
+        const int q4 = warp & 3;                       // tensor-memory lane quarter of this warp
+        const int half = (warp - 2) >> 2;              // which 32 of the tile's 64 keys
+        const int r = q4 * 32 + lane;                  // row within the tile
+        const int i = i0 + r;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
+        const float sl2 = p.scale * LOG2E;
+        float m_used = -INFINITY, l = 0.f;             // both threads of a row keep identical m_used; l is per half
+        bool ok = true;
+        for (int t = 0; t < n_tiles && ok; ++t) {
+            const int st = t & 1;
+            const uint32_t ph = (t >> 1) & 1;
+            const int j0 = (jb_lo + t) * BN + half * 32;
+            if (!mbar_wait(&s_full[st], ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sr[32];
+            tmem_ld_32x32(lane_addr + S_COL + st * BN + half * 32, sr);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&s_free[st]);                  // the scores are in registers: the buffer may be overwritten
+            const bool need_mask = (j0 + 31 > i0) || (p.window > 0 && j0 < i0 + BM - p.window);
+            if (need_mask) {
+#pragma unroll
+                for (int x = 0; x < 32; ++x)
+                    if (!visible(i, j0 + x, p.window)) sr[x] = 0xff800000u;   // -inf
+            }
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int x = 0; x < 32; x += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) m4[e] = fmaxf(m4[e], __uint_as_float(sr[x + e]));
+            }
+            float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl2;      // scale > 0
+            // the row maximum over both halves
+            mx_smem[(st * 2 + half) * BM + r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + q4) : "memory");
+            mx = fmaxf(mx, mx_smem[(st * 2 + (half ^ 1)) * BM + r]);
+            // raise the reference maximum only when it is far behind; O and l are rescaled with it
+            const bool first = m_used == -INFINITY;
+            const bool need = !first && mx > m_used + RESCALE_GAP;
+            if (__any_sync(0xffffffffu, need)) {
+                // the previous P V product must have landed before O is modified (none is in flight after it:
+                // the next one waits for the probabilities written below)
+                if (!mbar_wait(o_done, (uint32_t)((t - 1) & 1), abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const float f = need ? ex2(m_used - mx) : 1.0f;
+#pragma unroll 1
+                for (int c = 0; c < HD / 2; c += 32) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(lane_addr + O_COL + half * (HD / 2) + c, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * f);
+                    tmem_st_32x32(lane_addr + O_COL + half * (HD / 2) + c, o);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                l *= f;
+                if (need) m_used = mx;
+            }
+            if (first && mx > -INFINITY) m_used = mx;  // nothing accumulated yet for this row: no rescale needed
+            const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+            float ps[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[16];
+#pragma unroll
+            for (int x = 0; x < 32; x += 4) {
+                float e4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    e4[e] = ex2(fmaf(__uint_as_float(sr[x + e]), sl2, neg_m));      // -inf -> 0
+                    ps[e] += e4[e];
+                }
+                const __nv_bfloat162 w0 = __floats2bfloat162_rn(e4[0], e4[1]), w1 = __floats2bfloat162_rn(e4[2], e4[3]);
+                pk[x >> 1] = *reinterpret_cast<const uint32_t*>(&w0);
+                pk[(x >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&w1);
+            }
+            l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+            if (!mbar_wait(&p_free[st], ph ^ 1, abort_flag)) { ok = false; break; }
+            const uint32_t prow = smem_u32(p_smem + st * P_BYTES) + (uint32_t)r * 128u;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                st_shared_v4(prow + (uint32_t)(((half * 4 + c) ^ (r & 7)) * 16), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            fence_proxy_async();
+            mbar_arrive(&p_full[st]);
+        }
+        // ---- epilogue: O / l -> bf16 (each thread its half of the row), row log-sum-exp
+        const int lb = n_tiles & 1;                    // the exchange buffer the last tile did not use
+        l_smem[(lb * 2 + half) * BM + r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + q4) : "memory");
+        l += l_smem[(lb * 2 + (half ^ 1)) * BM + r];
+        if (ok && mbar_wait(o_done, (uint32_t)((n_tiles - 1) & 1), abort_flag)) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            __nv_bfloat16* orow = p.out + (long long)b * p.so_b + (long long)i * p.so_s + (long long)h * p.so_h + half * (HD / 2);
+#pragma unroll 1
+            for (int c = 0; c < HD / 2; c += 32) {
+                uint32_t o[32];
+                tmem_ld_32x32(lane_addr + O_COL + half * (HD / 2) + c, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int x = 0; x < 32; x += 8) {
+                    float t8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) t8[e] = __uint_as_float(o[x + e]) * inv;
+                    store8(orow + c + x, t8);
+                }
+            }
+            if (half == 0) p.lse[((long long)b * p.n_heads + h) * p.seq + i] = (m_used + log2f(l)) / LOG2E;
+        }
+    }
+
+    // ------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+bool token_major(const mft_strides_t& s, int seq) { return s.stride_b == (int64_t)seq * s.stride_s; }
+
+}  // namespace
+
+int32_t attn_fwd_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
+    static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
+    if (!enabled || hd != HD || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq)) return MFT_ERR_UNSUPPORTED;
+    if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.so.stride_s % 8 || a.so.stride_h % 8 || a.so.stride_b % 8) return MFT_ERR_UNSUPPORTED;
+    if ((int64_t)a.batch * a.seq >= (1ll << 31)) return MFT_ERR_UNSUPPORTED;
+    CUtensorMap mq, mk, mv;
+    const int64_t rows = (int64_t)a.batch * a.seq;
+    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + HD, a.sq.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + HD, a.sk.stride_s, BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + HD, a.sv.stride_s, BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (a.sk.stride_h != a.sv.stride_h) return MFT_ERR_UNSUPPORTED;
+    FwdParams p{};
+    p.seq = a.seq; p.n_heads = a.n_heads; p.rep = a.rep; p.window = a.window; p.scale = a.scale;
+    p.out = a.out; p.so_b = a.so.stride_b; p.so_s = a.so.stride_s; p.so_h = a.so.stride_h; p.lse = a.lse;
+    p.status = device_status_word();
+    p.q_col0_stride = (int)a.sq.stride_h; p.kv_col0_stride = (int)a.sk.stride_h;
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM), "attention smem attribute")) return s;
+        configured = true;
+    }
+    dim3 grid((unsigned)(a.seq / BM), (unsigned)a.n_heads, (unsigned)a.batch);
+    attn_fwd_tc_kernel<<<grid, THREADS, FWD_SMEM, stream>>>(mq, mk, mv, p);
+    MFT_LAUNCH_CHECK("attn_fwd_tc");
+    return MFT_OK;
+}
+
+}  // namespace mft

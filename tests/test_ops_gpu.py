@@ -205,6 +205,23 @@ def test_attention_mask_predicate_is_exact(ops):
     assert np.array_equal(visible, (j <= i) & (i - j < window))
 
 
+@pytest.mark.parametrize("S,window,nkv,amp", [(128, 0, 1, 1.0), (384, 0, 2, 1.0), (512, 200, 1, 1.0), (256, 64, 4, 1.0), (384, 0, 1, 6.0)])
+def test_attention_head_dim_256_tensor_memory_path(ops, S, window, nkv, amp):
+    """head_dim 256 with a sequence that is a multiple of 128 runs on the tcgen05 kernels (scores and output
+    accumulator in tensor memory).  amp > 1 makes the row maxima grow quickly along the keys, which exercises the
+    rescale of the accumulator."""
+    g = np.random.Generator(np.random.PCG64(9000 + S + window))
+    B, nh, hd = 2, 4, 256
+    q, dO = rb(g.standard_normal((B, nh, S, hd)) * amp), rb(g.standard_normal((B, nh, S, hd)))
+    k, v = rb(g.standard_normal((B, nkv, S, hd)) * amp), rb(g.standard_normal((B, nkv, S, hd)))
+    if amp > 1.0:
+        k = rb(k * np.linspace(0.2, 1.0, S, dtype=np.float32)[None, None, :, None])    # later keys score higher
+    out, dq, dk, dv = run_attention(ops, q, k, v, dO, hd ** -0.5, window, 0.0)
+    w_out, w_dq, w_dk, w_dv = R.attention_fwd_bwd(q, k, v, dO, hd ** -0.5, window)
+    close_bf16(out, w_out); close_bf16(dq, w_dq); close_bf16(dk, w_dk); close_bf16(dv, w_dv)
+    assert ops.device_status() == 0
+
+
 def test_attention_full_size_properties(ops):
     """S = 4096 (too large for the dense CPU chain): uniform-attention identity.  With Q = 0 every
     visible key gets the same weight, so O[i] is the running mean of V and dV[j] = sum_{i>=j} dO[i]/(i+1)."""
