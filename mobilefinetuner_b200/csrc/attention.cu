@@ -645,7 +645,9 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
     {                                                                                                       \
         attn_delta_kernel<HD><<<dblocks, 256, 0, as_stream(stream)>>>(p);                                   \
         MFT_LAUNCH_CHECK("attn_delta");                                                                     \
-        DQ(HD, BM, BN, ST)                                                                                  \
+        const int32_t sdq = attn_dq_sm100(p, HD, as_stream(stream));                                        \
+        if (sdq != MFT_OK && sdq != MFT_ERR_UNSUPPORTED) return sdq;                                        \
+        if (sdq == MFT_ERR_UNSUPPORTED) DQ(HD, BM, BN, ST)                                                  \
         if (split) DKV(HD, WN, true) else DKV(HD, WN, false)                                                \
     }
     if (hd == 64) { if (shape == 1) BWD(64, 1, 128, 64, 2) else BWD(64, 1, 64, 64, 2) }

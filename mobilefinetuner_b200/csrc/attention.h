@@ -21,5 +21,7 @@ struct AttnParams {
 // operands).  Returns MFT_ERR_UNSUPPORTED when the problem does not qualify; the caller then uses the
 // mma.sync kernel.
 int32_t attn_fwd_sm100(const AttnParams& p, int hd, cudaStream_t stream);
+// dQ of the backward pass, same conditions (p.delta must already hold rowsum(O * dO)).
+int32_t attn_dq_sm100(const AttnParams& p, int hd, cudaStream_t stream);
 
 }  // namespace mft

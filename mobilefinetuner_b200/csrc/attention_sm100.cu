@@ -101,8 +101,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint64_t* s_free = bars + 11;       // [2]  256 arrivals
     uint64_t* p_full = bars + 13;       // [2]  256 arrivals
     uint64_t* p_free = bars + 15;       // [2]
-    uint64_t* o_done = bars + 17;       // [1]  one completion per P V product
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+    uint64_t* o_done = bars + 17;       // [2]  P V product t completes o_done[t & 1] (two barriers, so that a waiter
+                                        //      one product behind cannot mistake an older phase for the one it needs)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* mx_smem = reinterpret_cast<float*>(bars + 20);   // [2 buffers][2 halves][128] row maxima, later row sums
     float* l_smem = mx_smem;
@@ -126,7 +127,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 256); mbar_init(&p_full[s], 256); mbar_init(&p_free[s], 1);
         }
-        mbar_init(o_done, 1);
+        mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
@@ -161,19 +162,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             constexpr uint32_t idesc_s = idesc_bf16_f32(BM, BN);
             constexpr uint32_t idesc_o = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
             bool ok = mbar_wait(q_full, 0, abort_flag);
+            const uint64_t qd = smem_desc_sw128(smem_u32(q_smem));
             auto issue_s = [&](int t) {
                 const int st = t & 1;
                 const uint32_t ph = (t >> 1) & 1;
                 if (!mbar_wait(&k_full[st], ph, abort_flag) || !mbar_wait(&s_free[st], ph ^ 1, abort_flag)) { ok = false; return; }
                 tc_fence_after();
-                const uint32_t qa = smem_u32(q_smem), ka = smem_u32(k_smem + st * KV_BYTES);
+                // descriptors advance by constants (16-byte units): the issuing thread must stay cheap, these MMAs are short
+                const uint64_t kd = smem_desc_sw128(smem_u32(k_smem + st * KV_BYTES));
                 const uint32_t tmem_s = tmem_base + S_COL + st * BN;
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        umma_bf16(tmem_s, smem_desc_sw128(qa + c * (BM * 128)) + (uint64_t)(2 * j),
-                                  smem_desc_sw128(ka + c * (BN * 128)) + (uint64_t)(2 * j), idesc_s, (c | j) != 0 ? 1u : 0u);
+                        umma_bf16(tmem_s, qd + (uint64_t)(c * (BM * 128 / 16) + 2 * j), kd + (uint64_t)(c * (BN * 128 / 16) + 2 * j), idesc_s,
+                                  (c | j) != 0 ? 1u : 0u);
                 umma_commit(&k_empty[st]);
                 umma_commit(&s_full[st]);
             };
@@ -182,14 +185,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const uint32_t ph = (t >> 1) & 1;
                 if (!mbar_wait(&v_full[st], ph, abort_flag) || !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; return; }
                 tc_fence_after();
-                const uint32_t pa = smem_u32(p_smem + st * P_BYTES), va = smem_u32(v_smem + st * KV_BYTES);
+                const uint64_t pd = smem_desc_sw128(smem_u32(p_smem + st * P_BYTES));
+                const uint64_t vd = smem_desc_mn_sw128(smem_u32(v_smem + st * KV_BYTES), BN * 128);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    umma_bf16(tmem_base + O_COL, smem_desc_sw128(pa) + (uint64_t)(2 * j), smem_desc_mn_sw128(va + j * 2048, BN * 128),
-                              idesc_o, (t | j) != 0 ? 1u : 0u);
+                    umma_bf16(tmem_base + O_COL, pd + (uint64_t)(2 * j), vd + (uint64_t)(j * (2048 / 16)), idesc_o, (t | j) != 0 ? 1u : 0u);
                 umma_commit(&v_empty[st]);
                 umma_commit(&p_free[st]);
-                umma_commit(o_done);
+                umma_commit(&o_done[st]);
             };
             if (ok) issue_s(0);
             for (int t = 0; t < n_tiles && ok; ++t) {
@@ -241,7 +244,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (__any_sync(0xffffffffu, need)) {
                 // the previous P V product must have landed before O is modified (none is in flight after it:
                 // the next one waits for the probabilities written below)
-                if (!mbar_wait(o_done, (uint32_t)((t - 1) & 1), abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&o_done[(t - 1) & 1], (uint32_t)(((t - 1) >> 1) & 1), abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const float f = need ? ex2(m_used - mx) : 1.0f;
 #pragma unroll 1
@@ -288,7 +291,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         l_smem[(lb * 2 + half) * BM + r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + q4) : "memory");
         l += l_smem[(lb * 2 + (half ^ 1)) * BM + r];
-        if (ok && mbar_wait(o_done, (uint32_t)((n_tiles - 1) & 1), abort_flag)) {
+        if (ok && mbar_wait(&o_done[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), abort_flag)) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             __nv_bfloat16* orow = p.out + (long long)b * p.so_b + (long long)i * p.so_s + (long long)h * p.so_h + half * (HD / 2);
@@ -310,6 +313,233 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
 
     // ------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------- backward: dQ
+// One CTA per (128 queries, head, batch).  Q and dO stay in shared memory; K streams in 32-key tiles through
+// three stages, V through two.  Per tile: S = Q K^T and dP = dO V^T into tensor memory, the element-wise threads
+// form dS = P (dP - delta) with P = exp2(S scale log2e - lse log2e) and write it as bf16 into a swizzled
+// shared-memory tile, and dQ += dS K accumulates in tensor memory (K consumed MN-major).  The element-wise work
+// has no state across tiles, so two groups of 256 threads (two threads per query row each) take alternate tiles
+// and overlap each other's latency; group g owns S/dP buffer g and the g-th 64-byte half of the dS rows.
+constexpr int DQ_BN = 32;
+constexpr int DQ_KV_BYTES = DQ_BN * HD * 2;        // 4 chunks of [32 rows x 64 columns]
+constexpr int DQ_KST = 3, DQ_VST = 2;              // K / V stages
+constexpr int DS_BYTES = BM * 128;                 // [128 rows x 128 bytes]: keys of group 0 in bytes 0..63, of group 1 in 64..127
+constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + DS_BYTES + 192;
+constexpr int DQ_THREADS = 64 + 2 * 256;
+constexpr int DQ_S_COL = 0, DQ_DP_COL = 64, DQ_ACC_COL = 128;
+
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct BwdParams {
+    int seq, n_heads, n_kv, rep, window;
+    float scale;
+    const float* lse;
+    const float* delta;
+    __nv_bfloat16* dq;
+    long long sq_b, sq_s, sq_h;
+    float* dkv_acc;
+    int32_t* status;
+    int q_col0_stride, do_col0_stride, k_col0_stride, v_col0_stride;
+};
+
+__global__ void __launch_bounds__(DQ_THREADS, 1)
+attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                  const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* q_smem = smem_raw;
+    uint8_t* do_smem = q_smem + Q_BYTES;
+    uint8_t* k_smem = do_smem + Q_BYTES;                   // DQ_KST stages
+    uint8_t* v_smem = k_smem + DQ_KST * DQ_KV_BYTES;       // DQ_VST stages
+    uint8_t* ds_smem = v_smem + DQ_VST * DQ_KV_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ds_smem + DS_BYTES);
+    uint64_t* qdo_full = bars;          // [1]
+    uint64_t* k_full = bars + 1;        // [3]
+    uint64_t* k_empty = bars + 4;       // [3]
+    uint64_t* v_full = bars + 7;        // [2]
+    uint64_t* v_empty = bars + 9;       // [2]
+    uint64_t* sdp_full = bars + 11;     // [2]  per group
+    uint64_t* sdp_free = bars + 13;     // [2]  256 arrivals
+    uint64_t* ds_full = bars + 15;      // [2]  256 arrivals
+    uint64_t* ds_free = bars + 17;      // [2]
+    uint64_t* acc_done = bars + 19;     // [1]  completed once, by the last dQ product
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, MFT_ERR_INVALID_ARG);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / p.rep;
+    const int i0 = qb * BM;
+    const int jb_hi = (i0 + BM - 1) / DQ_BN;
+    const int jb_lo = p.window > 0 ? max(0, i0 - p.window + 1) / DQ_BN : 0;
+    const int n_tiles = jb_hi - jb_lo + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(qdo_full, 1);
+        for (int s = 0; s < DQ_KST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&sdp_full[s], 1); mbar_init(&sdp_free[s], 256); mbar_init(&ds_full[s], 256); mbar_init(&ds_free[s], 1);
+        }
+        mbar_init(acc_done, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(qdo_full, 2 * Q_BYTES);
+            for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + c * (BM * 128), &map_q, qdo_full, h * p.q_col0_stride + c * 64, b * p.seq + i0);
+            for (int c = 0; c < 4; ++c) tma_load_2d(do_smem + c * (BM * 128), &map_do, qdo_full, h * p.do_col0_stride + c * 64, b * p.seq + i0);
+            for (int t = 0; t < n_tiles; ++t) {
+                const int ks = t % DQ_KST, vs = t & 1;
+                const uint32_t kph = (t / DQ_KST) & 1, vph = (t >> 1) & 1;
+                const int row = b * p.seq + (jb_lo + t) * DQ_BN;
+                if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag)) break;
+                mbar_arrive_expect_tx(&k_full[ks], DQ_KV_BYTES);
+                for (int c = 0; c < 4; ++c) tma_load_2d(k_smem + ks * DQ_KV_BYTES + c * (DQ_BN * 128), &map_k, &k_full[ks], kvh * p.k_col0_stride + c * 64, row);
+                if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag)) break;
+                mbar_arrive_expect_tx(&v_full[vs], DQ_KV_BYTES);
+                for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + vs * DQ_KV_BYTES + c * (DQ_BN * 128), &map_v, &v_full[vs], kvh * p.v_col0_stride + c * 64, row);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16_f32(BM, DQ_BN);
+            constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
+            bool ok = mbar_wait(qdo_full, 0, abort_flag);
+            const uint64_t qd = smem_desc_sw128(smem_u32(q_smem)), dd = smem_desc_sw128(smem_u32(do_smem)), sd = smem_desc_sw128(smem_u32(ds_smem));
+            auto issue_sdp = [&](int t) {
+                const int g = t & 1, ks = t % DQ_KST;
+                const uint32_t gph = (t >> 1) & 1, kph = (t / DQ_KST) & 1;
+                if (!mbar_wait(&k_full[ks], kph, abort_flag) || !mbar_wait(&v_full[g], gph, abort_flag) ||
+                    !mbar_wait(&sdp_free[g], gph ^ 1, abort_flag)) { ok = false; return; }
+                tc_fence_after();
+                // descriptors advance by constants (16-byte units): the issuing thread must stay cheap, these MMAs are short
+                const uint64_t kd = smem_desc_sw128(smem_u32(k_smem + ks * DQ_KV_BYTES)), vd = smem_desc_sw128(smem_u32(v_smem + g * DQ_KV_BYTES));
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        umma_bf16(tmem_base + DQ_S_COL + g * DQ_BN, qd + (uint64_t)(c * (BM * 128 / 16) + 2 * j),
+                                  kd + (uint64_t)(c * (DQ_BN * 128 / 16) + 2 * j), idesc_s, (c | j) != 0 ? 1u : 0u);
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        umma_bf16(tmem_base + DQ_DP_COL + g * DQ_BN, dd + (uint64_t)(c * (BM * 128 / 16) + 2 * j),
+                                  vd + (uint64_t)(c * (DQ_BN * 128 / 16) + 2 * j), idesc_s, (c | j) != 0 ? 1u : 0u);
+                umma_commit(&v_empty[g]);
+                umma_commit(&sdp_full[g]);
+            };
+            auto issue_acc = [&](int t) {
+                const int g = t & 1, ks = t % DQ_KST;
+                const uint32_t gph = (t >> 1) & 1;
+                if (!mbar_wait(&ds_full[g], gph, abort_flag)) { ok = false; return; }
+                tc_fence_after();
+                const uint64_t kd = smem_desc_mn_sw128(smem_u32(k_smem + ks * DQ_KV_BYTES), DQ_BN * 128);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    umma_bf16(tmem_base + DQ_ACC_COL, sd + (uint64_t)(4 * g + 2 * j), kd + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
+                umma_commit(&k_empty[ks]);
+                umma_commit(&ds_free[g]);
+                if (t == n_tiles - 1) umma_commit(acc_done);
+            };
+            if (ok) issue_sdp(0);
+            if (ok && n_tiles > 1) issue_sdp(1);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                issue_acc(t);
+                if (ok && t + 2 < n_tiles) issue_sdp(t + 2);
+            }
+        }
+    } else {
+        const int g = (warp - 2) >> 3;                 // element-wise group: tiles t = g, g + 2, ...
+        const int q4 = warp & 3;
+        const int half = ((warp - 2) >> 2) & 1;        // which 16 of the tile's 32 keys
+        const int r = q4 * 32 + lane;
+        const int i = i0 + r;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
+        const float sl2 = p.scale * LOG2E;
+        const long long sidx = ((long long)b * p.n_heads + h) * p.seq + i;
+        const float neg_lse2 = -p.lse[sidx] * LOG2E, dlt = p.delta[sidx];
+        bool ok = true;
+        for (int t = g; t < n_tiles && ok; t += 2) {
+            const uint32_t ph = (t >> 1) & 1;
+            const int j0 = (jb_lo + t) * DQ_BN + half * 16;
+            if (!mbar_wait(&sdp_full[g], ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sr[16], dr[16];
+            tmem_ld_32x16(lane_addr + DQ_S_COL + g * DQ_BN + half * 16, sr);
+            tmem_ld_32x16(lane_addr + DQ_DP_COL + g * DQ_BN + half * 16, dr);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&sdp_free[g]);
+            const bool need_mask = (j0 + 15 > i0) || (p.window > 0 && j0 < i0 + BM - p.window);
+            uint32_t pk[8];
+#pragma unroll
+            for (int x = 0; x < 16; x += 2) {
+                float d2[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float pv = ex2(fmaf(__uint_as_float(sr[x + e]), sl2, neg_lse2));
+                    if (need_mask && !visible(i, j0 + x + e, p.window)) pv = 0.f;
+                    d2[e] = pv * (__uint_as_float(dr[x + e]) - dlt);
+                }
+                const __nv_bfloat162 w = __floats2bfloat162_rn(d2[0], d2[1]);
+                pk[x >> 1] = *reinterpret_cast<const uint32_t*>(&w);
+            }
+            if (!mbar_wait(&ds_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
+            const uint32_t drow = smem_u32(ds_smem) + (uint32_t)r * 128u;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+                st_shared_v4(drow + (uint32_t)(((g * 4 + half * 2 + c) ^ (r & 7)) * 16), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            fence_proxy_async();
+            mbar_arrive(&ds_full[g]);
+        }
+        if (g == 0 && ok && mbar_wait(acc_done, 0, abort_flag)) {
+            tc_fence_after();
+            __nv_bfloat16* row = p.dq + (long long)b * p.sq_b + (long long)i * p.sq_s + (long long)h * p.sq_h + half * (HD / 2);
+#pragma unroll 1
+            for (int c = 0; c < HD / 2; c += 32) {
+                uint32_t o[32];
+                tmem_ld_32x32(lane_addr + DQ_ACC_COL + half * (HD / 2) + c, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int x = 0; x < 32; x += 8) {
+                    float t8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) t8[e] = __uint_as_float(o[x + e]) * p.scale;
+                    store8(row + c + x, t8);
+                }
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
@@ -348,6 +578,35 @@ int32_t attn_fwd_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
     dim3 grid((unsigned)(a.seq / BM), (unsigned)a.n_heads, (unsigned)a.batch);
     attn_fwd_tc_kernel<<<grid, THREADS, FWD_SMEM, stream>>>(mq, mk, mv, p);
     MFT_LAUNCH_CHECK("attn_fwd_tc");
+    return MFT_OK;
+}
+
+int32_t attn_dq_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
+    static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
+    if (!enabled || hd != HD || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq) || !token_major(a.sdo, a.seq)) return MFT_ERR_UNSUPPORTED;
+    if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.sdo.stride_h % 8) return MFT_ERR_UNSUPPORTED;
+    if ((int64_t)a.batch * a.seq >= (1ll << 31)) return MFT_ERR_UNSUPPORTED;
+    CUtensorMap mq, md, mk, mv;
+    const int64_t rows = (int64_t)a.batch * a.seq;
+    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + HD, a.sq.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&md, a.d_o, rows, (int64_t)(a.n_heads - 1) * a.sdo.stride_h + HD, a.sdo.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + HD, a.sk.stride_s, DQ_BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + HD, a.sv.stride_s, DQ_BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    BwdParams p{};
+    p.seq = a.seq; p.n_heads = a.n_heads; p.n_kv = a.n_kv; p.rep = a.rep; p.window = a.window; p.scale = a.scale;
+    p.lse = a.lse; p.delta = a.delta; p.dq = a.dq; p.sq_b = a.sq.stride_b; p.sq_s = a.sq.stride_s; p.sq_h = a.sq.stride_h;
+    p.dkv_acc = a.dkv_acc; p.status = device_status_word();
+    p.q_col0_stride = (int)a.sq.stride_h; p.do_col0_stride = (int)a.sdo.stride_h;
+    p.k_col0_stride = (int)a.sk.stride_h; p.v_col0_stride = (int)a.sv.stride_h;
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM), "attention smem attribute")) return s;
+        configured = true;
+    }
+    dim3 grid((unsigned)(a.seq / BM), (unsigned)a.n_heads, (unsigned)a.batch);
+    attn_dq_tc_kernel<<<grid, DQ_THREADS, DQ_SMEM, stream>>>(mq, md, mk, mv, p);
+    MFT_LAUNCH_CHECK("attn_dq_tc");
     return MFT_OK;
 }
 
