@@ -28,7 +28,8 @@ using namespace ptx;
 namespace {
 
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr int HD = 256, BM = 128, BN = 64, THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps
+constexpr int HD = 256, BM = 128, BN = 64;
+constexpr int THREADS = 352;   // TMA warp, S-issuing warp, 8 softmax warps, P V-issuing warp
 constexpr int Q_BYTES = BM * HD * 2;           // 4 boxes of [128 rows x 64 columns]
 constexpr int KV_BYTES = BN * HD * 2;          // 4 boxes of [64 rows x 64 columns]
 constexpr int P_BYTES = BM * BN * 2;           // [128 rows x 64 keys], 128-byte rows
@@ -157,18 +158,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer
+        // ------------------------------------------------ MMA issuer 1: S = Q K^T
+        // (The tensor pipe takes MMAs from a thread only about as fast as that thread issues them: every wait,
+        // fence and commit between two MMAs is exposed when the MMAs are short.  Two issuing threads overlap
+        // one product's bookkeeping with the other product's MMAs.)
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_bf16_f32(BM, BN);
-            constexpr uint32_t idesc_o = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
             bool ok = mbar_wait(q_full, 0, abort_flag);
             const uint64_t qd = smem_desc_sw128(smem_u32(q_smem));
-            auto issue_s = [&](int t) {
+            for (int t = 0; t < n_tiles && ok; ++t) {
                 const int st = t & 1;
                 const uint32_t ph = (t >> 1) & 1;
-                if (!mbar_wait(&k_full[st], ph, abort_flag) || !mbar_wait(&s_free[st], ph ^ 1, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(&k_full[st], ph, abort_flag) || !mbar_wait(&s_free[st], ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                // descriptors advance by constants (16-byte units): the issuing thread must stay cheap, these MMAs are short
                 const uint64_t kd = smem_desc_sw128(smem_u32(k_smem + st * KV_BYTES));
                 const uint32_t tmem_s = tmem_base + S_COL + st * BN;
 #pragma unroll
@@ -179,11 +181,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                                   (c | j) != 0 ? 1u : 0u);
                 umma_commit(&k_empty[st]);
                 umma_commit(&s_full[st]);
-            };
-            auto issue_pv = [&](int t) {
+            }
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------ MMA issuer 2: O += P V
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
+            bool ok = true;
+            for (int t = 0; t < n_tiles && ok; ++t) {
                 const int st = t & 1;
                 const uint32_t ph = (t >> 1) & 1;
-                if (!mbar_wait(&v_full[st], ph, abort_flag) || !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(&v_full[st], ph, abort_flag) || !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t pd = smem_desc_sw128(smem_u32(p_smem + st * P_BYTES));
                 const uint64_t vd = smem_desc_mn_sw128(smem_u32(v_smem + st * KV_BYTES), BN * 128);
@@ -193,15 +201,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 umma_commit(&v_empty[st]);
                 umma_commit(&p_free[st]);
                 umma_commit(&o_done[st]);
-            };
-            if (ok) issue_s(0);
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                if (t + 1 < n_tiles) issue_s(t + 1);
-                if (ok) issue_pv(t);
             }
         }
     } else {
-        // ------------------------------------------------ softmax: two threads per query row (32 keys each)
+        // ------------------------------------------------ softmax (warps 2..9): two threads per query row (32 keys each)
         const int q4 = warp & 3;                       // tensor-memory lane quarter of this warp
         const int half = (warp - 2) >> 2;              // which 32 of the tile's 64 keys
         const int r = q4 * 32 + lane;                  // row within the tile
@@ -334,7 +337,7 @@ constexpr int DQ_KV_BYTES = DQ_BN * HD * 2;        // 4 chunks of [32 rows x 64 
 constexpr int DQ_KST = 3, DQ_VST = 2;              // K / V stages
 constexpr int DS_BYTES = BM * 128;                 // [128 rows x 128 bytes]: keys of group 0 in bytes 0..63, of group 1 in 64..127
 constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + DS_BYTES + 192;
-constexpr int DQ_THREADS = 64 + 2 * 256;
+constexpr int DQ_THREADS = 64 + 2 * 256 + 64;     // TMA warp, S issuer, 16 element-wise warps, dP issuer, dQ issuer
 constexpr int DQ_S_COL = 0, DQ_DP_COL = 64, DQ_ACC_COL = 128;
 
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -374,7 +377,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     uint64_t* k_empty = bars + 4;       // [3]
     uint64_t* v_full = bars + 7;        // [2]
     uint64_t* v_empty = bars + 9;       // [2]
-    uint64_t* sdp_full = bars + 11;     // [2]  per group
+    uint64_t* sdp_full = bars + 11;     // [2]  per group; two arrivals (S and dP)
     uint64_t* sdp_free = bars + 13;     // [2]  256 arrivals
     uint64_t* ds_full = bars + 15;      // [2]  256 arrivals
     uint64_t* ds_free = bars + 17;      // [2]
@@ -399,7 +402,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         for (int s = 0; s < DQ_KST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-            mbar_init(&sdp_full[s], 1); mbar_init(&sdp_free[s], 256); mbar_init(&ds_full[s], 256); mbar_init(&ds_free[s], 1);
+            mbar_init(&sdp_full[s], 2); mbar_init(&sdp_free[s], 256); mbar_init(&ds_full[s], 256); mbar_init(&ds_free[s], 1);
         }
         mbar_init(acc_done, 1);
         *abort_flag = 0;
@@ -429,39 +432,41 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + vs * DQ_KV_BYTES + c * (DQ_BN * 128), &map_v, &v_full[vs], kvh * p.v_col0_stride + c * 64, row);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 18) {
+        // ------------------------------------------------ MMA issuers 1 and 2: S = Q K^T (warp 1), dP = dO V^T (warp 18)
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_bf16_f32(BM, DQ_BN);
-            constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
+            const bool is_s = warp == 1;
             bool ok = mbar_wait(qdo_full, 0, abort_flag);
-            const uint64_t qd = smem_desc_sw128(smem_u32(q_smem)), dd = smem_desc_sw128(smem_u32(do_smem)), sd = smem_desc_sw128(smem_u32(ds_smem));
-            auto issue_sdp = [&](int t) {
+            const uint64_t ad = smem_desc_sw128(smem_u32(is_s ? q_smem : do_smem));
+            for (int t = 0; t < n_tiles && ok; ++t) {
                 const int g = t & 1, ks = t % DQ_KST;
                 const uint32_t gph = (t >> 1) & 1, kph = (t / DQ_KST) & 1;
-                if (!mbar_wait(&k_full[ks], kph, abort_flag) || !mbar_wait(&v_full[g], gph, abort_flag) ||
-                    !mbar_wait(&sdp_free[g], gph ^ 1, abort_flag)) { ok = false; return; }
+                if (is_s ? !mbar_wait(&k_full[ks], kph, abort_flag) : !mbar_wait(&v_full[g], gph, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&sdp_free[g], gph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                // descriptors advance by constants (16-byte units): the issuing thread must stay cheap, these MMAs are short
-                const uint64_t kd = smem_desc_sw128(smem_u32(k_smem + ks * DQ_KV_BYTES)), vd = smem_desc_sw128(smem_u32(v_smem + g * DQ_KV_BYTES));
+                const uint64_t bd = smem_desc_sw128(smem_u32(is_s ? k_smem + ks * DQ_KV_BYTES : v_smem + g * DQ_KV_BYTES));
+                const uint32_t tmem_d = tmem_base + (is_s ? DQ_S_COL : DQ_DP_COL) + g * DQ_BN;
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        umma_bf16(tmem_base + DQ_S_COL + g * DQ_BN, qd + (uint64_t)(c * (BM * 128 / 16) + 2 * j),
-                                  kd + (uint64_t)(c * (DQ_BN * 128 / 16) + 2 * j), idesc_s, (c | j) != 0 ? 1u : 0u);
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        umma_bf16(tmem_base + DQ_DP_COL + g * DQ_BN, dd + (uint64_t)(c * (BM * 128 / 16) + 2 * j),
-                                  vd + (uint64_t)(c * (DQ_BN * 128 / 16) + 2 * j), idesc_s, (c | j) != 0 ? 1u : 0u);
-                umma_commit(&v_empty[g]);
-                umma_commit(&sdp_full[g]);
-            };
-            auto issue_acc = [&](int t) {
+                        umma_bf16(tmem_d, ad + (uint64_t)(c * (BM * 128 / 16) + 2 * j), bd + (uint64_t)(c * (DQ_BN * 128 / 16) + 2 * j), idesc_s,
+                                  (c | j) != 0 ? 1u : 0u);
+                if (!is_s) umma_commit(&v_empty[g]);
+                umma_commit(&sdp_full[g]);            // two arrivals complete it: S and dP
+            }
+        }
+    } else if (warp == 19) {
+        // ------------------------------------------------ MMA issuer 3: dQ += dS K
+        if (lane == 0) {
+            constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
+            const uint64_t sd = smem_desc_sw128(smem_u32(ds_smem));
+            bool ok = true;
+            for (int t = 0; t < n_tiles && ok; ++t) {
                 const int g = t & 1, ks = t % DQ_KST;
                 const uint32_t gph = (t >> 1) & 1;
-                if (!mbar_wait(&ds_full[g], gph, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(&ds_full[g], gph, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t kd = smem_desc_mn_sw128(smem_u32(k_smem + ks * DQ_KV_BYTES), DQ_BN * 128);
 #pragma unroll
@@ -470,12 +475,6 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 umma_commit(&k_empty[ks]);
                 umma_commit(&ds_free[g]);
                 if (t == n_tiles - 1) umma_commit(acc_done);
-            };
-            if (ok) issue_sdp(0);
-            if (ok && n_tiles > 1) issue_sdp(1);
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                issue_acc(t);
-                if (ok && t + 2 < n_tiles) issue_sdp(t + 2);
             }
         }
     } else {
