@@ -616,11 +616,13 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
     if (int32_t s = check_common(p, hd)) return s;
     const int64_t rows = batch * n_heads * seq;
     const unsigned dblocks = (unsigned)((rows * 32 + 255) / 256);
-    // One CTA per query head adding into the f32 scratch when a KV group has several heads (more, shorter CTAs)
-    const bool split = dkv_acc != nullptr && p.rep > 1;
+    // dK / dV are collected in the caller's f32 scratch when it is given: by the tensor-memory kernel, or with one
+    // mma.sync CTA per query head when a KV group has several heads (more, shorter CTAs)
     const int shape = attn_shape_override();
-    if (split)
+    bool dkv_tc = false;
+    if (dkv_acc != nullptr)
         if (int32_t s = check_cuda(cudaMemsetAsync(dkv_acc, 0, (size_t)(2 * batch * seq * n_kv * hd) * sizeof(float), as_stream(stream)), "attention dkv memset")) return s;
+    const bool split = dkv_acc != nullptr && p.rep > 1;
     dim3 gk((unsigned)((seq + 63) / 64), (unsigned)(split ? n_heads : n_kv), (unsigned)batch);
 #define DQ(HD, BM, BN, ST)                                                                                  \
     {                                                                                                       \
@@ -648,7 +650,13 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
         const int32_t sdq = attn_dq_sm100(p, HD, as_stream(stream));                                        \
         if (sdq != MFT_OK && sdq != MFT_ERR_UNSUPPORTED) return sdq;                                        \
         if (sdq == MFT_ERR_UNSUPPORTED) DQ(HD, BM, BN, ST)                                                  \
-        if (split) DKV(HD, WN, true) else DKV(HD, WN, false)                                                \
+        const int32_t skv = attn_dkv_sm100(p, HD, as_stream(stream));                                       \
+        if (skv != MFT_OK && skv != MFT_ERR_UNSUPPORTED) return skv;                                        \
+        dkv_tc = skv == MFT_OK;                                                                             \
+        if (dkv_tc) {                                                                                       \
+            attn_dkv_store_kernel<HD><<<148 * 8, 256, 0, as_stream(stream)>>>(p);                           \
+            MFT_LAUNCH_CHECK("attn_dkv_store");                                                             \
+        } else if (split) DKV(HD, WN, true) else DKV(HD, WN, false)                                         \
     }
     if (hd == 64) { if (shape == 1) BWD(64, 1, 128, 64, 2) else BWD(64, 1, 64, 64, 2) }
     else if (hd == 128) BWD(128, 1, 64, 64, 2)

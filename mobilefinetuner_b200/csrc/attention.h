@@ -23,5 +23,8 @@ struct AttnParams {
 int32_t attn_fwd_sm100(const AttnParams& p, int hd, cudaStream_t stream);
 // dQ of the backward pass, same conditions (p.delta must already hold rowsum(O * dO)).
 int32_t attn_dq_sm100(const AttnParams& p, int hd, cudaStream_t stream);
+// dK / dV of the backward pass ADDED into p.dkv_acc (f32 [2][batch, seq, n_kv, head_dim], zeroed by the caller);
+// needs p.dkv_acc and p.delta.
+int32_t attn_dkv_sm100(const AttnParams& p, int hd, cudaStream_t stream);
 
 }  // namespace mft

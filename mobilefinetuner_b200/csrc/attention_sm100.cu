@@ -548,6 +548,230 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
+// ---------------------------------------------------------------- backward: dK, dV
+// One CTA per (128 keys, query head, half of head_dim, batch): dK and dV for 128 keys x 256 columns would fill
+// the whole tensor memory, so each CTA accumulates 128 of the 256 columns (both halves recompute S and dP).
+// K and V stay in shared memory; Q, dO and the per-query log-sum-exp / delta stream in 32-query tiles (stage g
+// of two belongs to element-wise group g).  Per tile: S^T = K Q^T and dP^T = V dO^T (128 keys x 32 queries) into
+// tensor memory, the group forms P^T and dS^T and writes them as bf16 into the two 64-byte halves of a swizzled
+// shared-memory tile, and dV += P^T dO, dK += dS^T Q accumulate in tensor memory with dO / Q consumed MN-major.
+// The result is added into the caller's f32 [2][batch, seq, n_kv, 256] scratch (query heads of a KV group and
+// the two halves write disjoint columns or add).
+constexpr int KV_BQ = 32;                              // queries per tile
+constexpr int KV_Q_BYTES = KV_BQ * HD * 2;             // 4 chunks of [32 rows x 64 columns]
+constexpr int KV_STATS_BYTES = 2 * KV_BQ * 4;          // lse, delta of the tile's queries
+constexpr int KV_PDS_BYTES = BM * 128;                 // [128 keys x 128 bytes]: P^T in bytes 0..63, dS^T in 64..127
+constexpr int DKV_SMEM = 2 * Q_BYTES + 4 * KV_Q_BYTES + 2 * KV_PDS_BYTES + 2 * KV_STATS_BYTES + 192;
+constexpr int DKV_THREADS = 64 + 2 * 256 + 64;         // TMA warp, S^T issuer, 16 element-wise warps, dP^T issuer, dV/dK issuer
+constexpr int KV_S_COL = 0, KV_DP_COL = 64, KV_DK_COL = 128, KV_DV_COL = 256;
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :
+                 : "r"(smem_u32(smem_dst)), "l"(gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(DKV_THREADS, 1)
+attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                   const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* k_smem = smem_raw;                            // [128 keys x 256], 4 chunks
+    uint8_t* v_smem = k_smem + Q_BYTES;
+    uint8_t* q_smem = v_smem + Q_BYTES;                    // 2 stages
+    uint8_t* do_smem = q_smem + 2 * KV_Q_BYTES;            // 2 stages
+    uint8_t* pds_smem = do_smem + 2 * KV_Q_BYTES;          // 2 buffers (one per group)
+    float* stats = reinterpret_cast<float*>(pds_smem + 2 * KV_PDS_BYTES);   // [2 stages][lse 32 | delta 32]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + 2 * KV_STATS_BYTES);
+    uint64_t* kv_full = bars;           // [1]
+    uint64_t* qdo_full = bars + 1;      // [2]
+    uint64_t* qdo_empty = bars + 3;     // [2]
+    uint64_t* sdp_full = bars + 5;      // [2]  two arrivals (S^T and dP^T)
+    uint64_t* sdp_free = bars + 7;      // [2]  256 arrivals
+    uint64_t* pds_full = bars + 9;      // [2]  256 arrivals
+    uint64_t* pds_free = bars + 11;     // [2]
+    uint64_t* acc_done = bars + 13;     // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, MFT_ERR_INVALID_ARG);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int jb = blockIdx.x, b = blockIdx.z;
+    const int h = blockIdx.y >> 1, hh = blockIdx.y & 1;    // query head, half of head_dim
+    const int kvh = h / p.rep;
+    const int j0 = jb * BM;
+    // queries that can see keys j0 .. j0+127: i >= j0 and i - j < window
+    const int i_max = p.window > 0 ? min(p.seq - 1, j0 + BM - 1 + p.window - 1) : p.seq - 1;
+    const int qs_lo = j0 / KV_BQ, qs_hi = i_max / KV_BQ;
+    const int n_tiles = qs_hi - qs_lo + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1);
+            mbar_init(&sdp_full[s], 2); mbar_init(&sdp_free[s], 256); mbar_init(&pds_full[s], 256); mbar_init(&pds_free[s], 1);
+        }
+        mbar_init(acc_done, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(kv_full, 2 * Q_BYTES);
+            for (int c = 0; c < 4; ++c) tma_load_2d(k_smem + c * (BM * 128), &map_k, kv_full, kvh * p.k_col0_stride + c * 64, b * p.seq + j0);
+            for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + c * (BM * 128), &map_v, kv_full, kvh * p.v_col0_stride + c * 64, b * p.seq + j0);
+            const long long srow = ((long long)b * p.n_heads + h) * p.seq;
+            for (int t = 0; t < n_tiles; ++t) {
+                const int g = t & 1;
+                const uint32_t ph = (t >> 1) & 1;
+                const int i0 = (qs_lo + t) * KV_BQ;
+                if (!mbar_wait(&qdo_empty[g], ph ^ 1, abort_flag)) break;
+                mbar_arrive_expect_tx(&qdo_full[g], 2 * KV_Q_BYTES + KV_STATS_BYTES);
+                for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + g * KV_Q_BYTES + c * (KV_BQ * 128), &map_q, &qdo_full[g], h * p.q_col0_stride + c * 64, b * p.seq + i0);
+                for (int c = 0; c < 4; ++c) tma_load_2d(do_smem + g * KV_Q_BYTES + c * (KV_BQ * 128), &map_do, &qdo_full[g], h * p.do_col0_stride + c * 64, b * p.seq + i0);
+                bulk_load_1d(stats + g * 2 * KV_BQ, p.lse + srow + i0, KV_BQ * 4, &qdo_full[g]);
+                bulk_load_1d(stats + g * 2 * KV_BQ + KV_BQ, p.delta + srow + i0, KV_BQ * 4, &qdo_full[g]);
+            }
+        }
+    } else if (warp == 1 || warp == 18) {
+        // ------------------------------------------------ MMA issuers 1 and 2: S^T = K Q^T (warp 1), dP^T = V dO^T (warp 18)
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16_f32(BM, KV_BQ);
+            const bool is_s = warp == 1;
+            bool ok = mbar_wait(kv_full, 0, abort_flag);
+            const uint64_t ad = smem_desc_sw128(smem_u32(is_s ? k_smem : v_smem));
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                const int g = t & 1;
+                const uint32_t ph = (t >> 1) & 1;
+                if (!mbar_wait(&qdo_full[g], ph, abort_flag) || !mbar_wait(&sdp_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t bd = smem_desc_sw128(smem_u32((is_s ? q_smem : do_smem) + g * KV_Q_BYTES));
+                const uint32_t tmem_d = tmem_base + (is_s ? KV_S_COL : KV_DP_COL) + g * KV_BQ;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        umma_bf16(tmem_d, ad + (uint64_t)(c * (BM * 128 / 16) + 2 * j), bd + (uint64_t)(c * (KV_BQ * 128 / 16) + 2 * j), idesc_s,
+                                  (c | j) != 0 ? 1u : 0u);
+                umma_commit(&sdp_full[g]);
+            }
+        }
+    } else if (warp == 19) {
+        // ------------------------------------------------ MMA issuer 3: dV += P^T dO, dK += dS^T Q (this CTA's 128 columns)
+        if (lane == 0) {
+            constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, HD / 2) | IDESC_B_MN;
+            bool ok = true;
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                const int g = t & 1;
+                const uint32_t ph = (t >> 1) & 1;
+                if (!mbar_wait(&pds_full[g], ph, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t pd = smem_desc_sw128(smem_u32(pds_smem + g * KV_PDS_BYTES));
+                const uint64_t dod = smem_desc_mn_sw128(smem_u32(do_smem + g * KV_Q_BYTES + hh * 2 * (KV_BQ * 128)), KV_BQ * 128);
+                const uint64_t qd = smem_desc_mn_sw128(smem_u32(q_smem + g * KV_Q_BYTES + hh * 2 * (KV_BQ * 128)), KV_BQ * 128);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    umma_bf16(tmem_base + KV_DV_COL, pd + (uint64_t)(2 * j), dod + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    umma_bf16(tmem_base + KV_DK_COL, pd + (uint64_t)(4 + 2 * j), qd + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
+                umma_commit(&qdo_empty[g]);
+                umma_commit(&pds_free[g]);
+                if (t == n_tiles - 1) umma_commit(acc_done);
+            }
+        }
+    } else {
+        // ------------------------------------------------ element-wise groups (warps 2..17): key row per thread pair
+        const int g = (warp - 2) >> 3;
+        const int q4 = warp & 3;
+        const int half = ((warp - 2) >> 2) & 1;        // which 16 of the tile's 32 queries
+        const int r = q4 * 32 + lane;                  // key within the tile
+        const int j = j0 + r;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
+        const float sl2 = p.scale * LOG2E;
+        bool ok = true;
+        for (int t = g; t < n_tiles && ok; t += 2) {
+            const uint32_t ph = (t >> 1) & 1;
+            const int i0 = (qs_lo + t) * KV_BQ + half * 16;
+            if (!mbar_wait(&sdp_full[g], ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sr[16], dr[16];
+            tmem_ld_32x16(lane_addr + KV_S_COL + g * KV_BQ + half * 16, sr);
+            tmem_ld_32x16(lane_addr + KV_DP_COL + g * KV_BQ + half * 16, dr);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&sdp_free[g]);
+            // lse / delta of the 16 queries (the stage's loads completed before S^T was issued)
+            const float* st_l = stats + g * 2 * KV_BQ + half * 16;
+            const float* st_d = st_l + KV_BQ;
+            const bool need_mask = (i0 < j0 + BM - 1) || (p.window > 0 && i0 + 15 - j0 >= p.window);
+            uint32_t pk[8], dk[8];
+#pragma unroll
+            for (int x = 0; x < 16; x += 2) {
+                float p2[2], d2[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float pv = ex2(fmaf(__uint_as_float(sr[x + e]), sl2, -st_l[x + e] * LOG2E));
+                    if (need_mask && !visible(i0 + x + e, j, p.window)) pv = 0.f;
+                    p2[e] = pv;
+                    d2[e] = pv * (__uint_as_float(dr[x + e]) - st_d[x + e]);
+                }
+                const __nv_bfloat162 w0 = __floats2bfloat162_rn(p2[0], p2[1]), w1 = __floats2bfloat162_rn(d2[0], d2[1]);
+                pk[x >> 1] = *reinterpret_cast<const uint32_t*>(&w0);
+                dk[x >> 1] = *reinterpret_cast<const uint32_t*>(&w1);
+            }
+            if (!mbar_wait(&pds_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
+            const uint32_t row = smem_u32(pds_smem + g * KV_PDS_BYTES) + (uint32_t)r * 128u;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                st_shared_v4(row + (uint32_t)(((half * 2 + c) ^ (r & 7)) * 16), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                st_shared_v4(row + (uint32_t)(((4 + half * 2 + c) ^ (r & 7)) * 16), dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
+            }
+            fence_proxy_async();
+            mbar_arrive(&pds_full[g]);
+        }
+        // ---- epilogue (group 0): add this CTA's 128 columns of dK (scaled) and dV into the f32 scratch
+        if (g == 0 && ok && mbar_wait(acc_done, 0, abort_flag)) {
+            tc_fence_after();
+            const long long half_elems = (long long)gridDim.z * p.seq * p.n_kv * HD;
+            float* krow = p.dkv_acc + (((long long)b * p.seq + j) * p.n_kv + kvh) * HD + hh * (HD / 2) + half * (HD / 4);
+            float* vrow = krow + half_elems;
+#pragma unroll 1
+            for (int c = 0; c < HD / 4; c += 32) {
+                uint32_t o[32];
+                tmem_ld_32x32(lane_addr + KV_DK_COL + half * (HD / 4) + c, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int x = 0; x < 32; x += 4)
+                    atomicAdd(reinterpret_cast<float4*>(krow + c + x), make_float4(__uint_as_float(o[x]) * p.scale, __uint_as_float(o[x + 1]) * p.scale,
+                                                                                 __uint_as_float(o[x + 2]) * p.scale, __uint_as_float(o[x + 3]) * p.scale));
+                tmem_ld_32x32(lane_addr + KV_DV_COL + half * (HD / 4) + c, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int x = 0; x < 32; x += 4)
+                    atomicAdd(reinterpret_cast<float4*>(vrow + c + x), make_float4(__uint_as_float(o[x]), __uint_as_float(o[x + 1]),
+                                                                                 __uint_as_float(o[x + 2]), __uint_as_float(o[x + 3])));
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 bool token_major(const mft_strides_t& s, int seq) { return s.stride_b == (int64_t)seq * s.stride_s; }
 
 }  // namespace
@@ -606,6 +830,36 @@ int32_t attn_dq_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
     dim3 grid((unsigned)(a.seq / BM), (unsigned)a.n_heads, (unsigned)a.batch);
     attn_dq_tc_kernel<<<grid, DQ_THREADS, DQ_SMEM, stream>>>(mq, md, mk, mv, p);
     MFT_LAUNCH_CHECK("attn_dq_tc");
+    return MFT_OK;
+}
+
+int32_t attn_dkv_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
+    static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
+    if (!enabled || hd != HD || a.seq % BM != 0 || !a.dkv_acc || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq) || !token_major(a.sdo, a.seq)) return MFT_ERR_UNSUPPORTED;
+    if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.sdo.stride_h % 8) return MFT_ERR_UNSUPPORTED;
+    if ((int64_t)a.batch * a.seq >= (1ll << 31) || 2 * a.n_heads > 65535) return MFT_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(a.lse) % 16 || reinterpret_cast<uintptr_t>(a.delta) % 16 || reinterpret_cast<uintptr_t>(a.dkv_acc) % 16) return MFT_ERR_UNSUPPORTED;
+    CUtensorMap mq, md, mk, mv;
+    const int64_t rows = (int64_t)a.batch * a.seq;
+    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + HD, a.sq.stride_s, KV_BQ) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&md, a.d_o, rows, (int64_t)(a.n_heads - 1) * a.sdo.stride_h + HD, a.sdo.stride_s, KV_BQ) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + HD, a.sk.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + HD, a.sv.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    BwdParams p{};
+    p.seq = a.seq; p.n_heads = a.n_heads; p.n_kv = a.n_kv; p.rep = a.rep; p.window = a.window; p.scale = a.scale;
+    p.lse = a.lse; p.delta = a.delta; p.dq = a.dq; p.sq_b = a.sq.stride_b; p.sq_s = a.sq.stride_s; p.sq_h = a.sq.stride_h;
+    p.dkv_acc = a.dkv_acc; p.status = device_status_word();
+    p.q_col0_stride = (int)a.sq.stride_h; p.do_col0_stride = (int)a.sdo.stride_h;
+    p.k_col0_stride = (int)a.sk.stride_h; p.v_col0_stride = (int)a.sv.stride_h;
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM), "attention smem attribute")) return s;
+        configured = true;
+    }
+    dim3 grid((unsigned)(a.seq / BM), (unsigned)(2 * a.n_heads), (unsigned)a.batch);
+    attn_dkv_tc_kernel<<<grid, DKV_THREADS, DKV_SMEM, stream>>>(mq, md, mk, mv, p);
+    MFT_LAUNCH_CHECK("attn_dkv_tc");
     return MFT_OK;
 }
 

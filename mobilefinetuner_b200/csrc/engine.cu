@@ -87,6 +87,11 @@ void add_lora(mft_model* m, LinearSlot& s, int rank, bool peft_layout, bool has_
 extern "C" int32_t mft_model_destroy(mft_model_t* m) {
     if (!m) return MFT_OK;
     cudaStreamSynchronize(m->stream);
+    if (m->graph_stream) cudaStreamSynchronize(m->graph_stream);
+    for (auto& g : m->graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
+    if (m->graph_in) cudaEventDestroy(m->graph_in);
+    if (m->graph_out) cudaEventDestroy(m->graph_out);
+    if (m->graph_stream) cudaStreamDestroy(m->graph_stream);
     for (void* p : m->allocations) mft_free(p);
     delete m;
     return MFT_OK;
@@ -353,6 +358,7 @@ extern "C" int32_t mft_model_create(const mft_model_config_t* cfg, mft_stream_t 
     G(dalloc(m, &m->ce_lse, T));
     m->ce_ws_bytes = mft_lmhead_ce_workspace_bytes(T, H, V);
     if (const char* e = std::getenv("MFT_CE_ONEPASS")) m->ce_onepass = std::atoi(e) != 0;
+    if (const char* e = std::getenv("MFT_STEP_GRAPH")) m->use_graph = std::atoi(e) != 0;
     { uint8_t* ws = nullptr; G(dalloc(m, &ws, m->ce_ws_bytes, false, true)); m->ce_ws = ws; }
     m->stage_floats = 32ll << 20;
     G(dalloc(m, &m->stage_f32, m->stage_floats));

@@ -86,9 +86,27 @@ struct LayerWeights {
 
 }  // namespace mft
 
+namespace mft {
+bool gemm_profiling_enabled();   // per-launch GEMM event timing is on (it records events: incompatible with capture)
+}
+
+// One captured forward + backward (a fixed sequence of ~1100 launches for a given batch shape).
+struct StepGraph {
+    int64_t batch = 0, seq = 0, n_valid_global = 0;
+    int calls = 0;                   // eager runs seen with this key (the first one also performs one-time set-up)
+    cudaGraphExec_t exec = nullptr;
+};
+
 struct mft_model {
     mft_model_config_t cfg;
     cudaStream_t stream = nullptr;
+    // Replay of the training step as a CUDA graph: the launches of one step are issued faster than the host can
+    // make them one by one (tensor-map encodes + ~1100 launches per step).  Captured on a private stream that is
+    // ordered against `stream` with events.  MFT_STEP_GRAPH=0 disables it.
+    bool use_graph = true;
+    cudaStream_t graph_stream = nullptr;
+    cudaEvent_t graph_in = nullptr, graph_out = nullptr;
+    std::vector<StepGraph> graphs;
     int64_t max_tokens = 0;
     std::vector<void*> allocations;
     int64_t activation_bytes = 0;

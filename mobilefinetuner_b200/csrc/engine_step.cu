@@ -212,6 +212,63 @@ int32_t check_status(mft_model* m) {
     return MFT_OK;
 }
 
+// Forward + backward of a training step.  The second call with the same (batch, seq, n_valid_global) captures the
+// launches into a CUDA graph on the model's private stream; later calls replay it.  Anything that prevents a
+// capture (a profiling hook, a failing call) falls back to issuing the launches directly.
+int32_t forward_backward(Ctx& c, int64_t n_valid_global) {
+    mft_model* m = c.m;
+    auto eager = [&]() -> int32_t {
+        TRY(forward(c, true, n_valid_global));
+        return backward(c, n_valid_global);
+    };
+    if (!m->use_graph || gemm_profiling_enabled()) return eager();
+    StepGraph* g = nullptr;
+    for (auto& e : m->graphs)
+        if (e.batch == c.B && e.seq == c.S && e.n_valid_global == n_valid_global) { g = &e; break; }
+    if (!g) {
+        if (m->graphs.size() >= 8) return eager();         // the key keeps changing (e.g. varying global counts): do not hoard graphs
+        m->graphs.push_back(StepGraph{c.B, c.S, n_valid_global, 0, nullptr});
+        g = &m->graphs.back();
+    }
+    if (!g->exec) {
+        if (g->calls++ == 0) return eager();                // first run: one-time attribute set-up happens outside any capture
+        if (!m->graph_stream) {
+            if (cudaStreamCreateWithFlags(&m->graph_stream, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&m->graph_in, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&m->graph_out, cudaEventDisableTiming) != cudaSuccess) {
+                cudaGetLastError();
+                m->use_graph = false;
+                return eager();
+            }
+        }
+        Ctx cc = c;
+        cc.st = m->graph_stream;
+        cudaGraph_t graph = nullptr;
+        if (cudaStreamBeginCapture(m->graph_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();
+            m->use_graph = false;
+            return eager();
+        }
+        int32_t s = forward(cc, true, n_valid_global);
+        if (s == MFT_OK) s = backward(cc, n_valid_global);
+        const cudaError_t ce = cudaStreamEndCapture(m->graph_stream, &graph);
+        if (s != MFT_OK || ce != cudaSuccess || !graph || cudaGraphInstantiate(&g->exec, graph, 0) != cudaSuccess) {
+            cudaGetLastError();
+            if (graph) cudaGraphDestroy(graph);
+            g->exec = nullptr;
+            m->use_graph = false;
+            return eager();
+        }
+        cudaGraphDestroy(graph);
+    }
+    // order the replay after what the caller queued on its stream, and the caller's stream after the replay
+    if (int32_t s = check_cuda(cudaEventRecord(m->graph_in, m->stream), "step graph event")) return s;
+    if (int32_t s = check_cuda(cudaStreamWaitEvent(m->graph_stream, m->graph_in, 0), "step graph wait")) return s;
+    if (int32_t s = check_cuda(cudaGraphLaunch(g->exec, m->graph_stream), "step graph launch")) return s;
+    if (int32_t s = check_cuda(cudaEventRecord(m->graph_out, m->graph_stream), "step graph event")) return s;
+    return check_cuda(cudaStreamWaitEvent(m->stream, m->graph_out, 0), "step graph wait");
+}
+
 }  // namespace
 
 extern "C" int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t* ids_dev, const int32_t* labels_dev, int32_t batch,
@@ -221,8 +278,7 @@ extern "C" int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t*
     MFT_CHECK_ARG(ids_dev && labels_dev, "mft_model_forward_backward_dev: null input");
     if (ids_dev != m->ids) TRY(mft_memcpy_d2d(m->ids, ids_dev, (size_t)c.T * 4, c.st));
     if (labels_dev != m->labels) TRY(mft_memcpy_d2d(m->labels, labels_dev, (size_t)c.T * 4, c.st));
-    TRY(forward(c, true, n_valid_global));
-    TRY(backward(c, n_valid_global));
+    TRY(forward_backward(c, n_valid_global));
     if (loss_dev) *loss_dev = m->loss_dev;
     if (n_valid_dev) *n_valid_dev = m->n_valid_dev;
     return MFT_OK;
@@ -235,8 +291,7 @@ extern "C" int32_t mft_model_forward_backward(mft_model_t* m, const int32_t* ids
     MFT_CHECK_ARG(ids_host && labels_host, "mft_model_forward_backward: null input");
     TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)c.T * 4, c.st));
     TRY(mft_memcpy_h2d(m->labels, labels_host, (size_t)c.T * 4, c.st));
-    TRY(forward(c, true, n_valid_global));
-    TRY(backward(c, n_valid_global));
+    TRY(forward_backward(c, n_valid_global));
     if (loss_host) TRY(mft_memcpy_d2h(loss_host, m->loss_dev, 4, c.st));
     if (n_valid_host) TRY(mft_memcpy_d2h(n_valid_host, m->n_valid_dev, 4, c.st));
     return check_status(m);

@@ -432,6 +432,8 @@ static bool g_prof_on = false;
 
 static int32_t gemm_nt_run_inner(const GemmCall& c, cudaStream_t stream);
 
+bool gemm_profiling_enabled() { return g_prof_on; }
+
 int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream) {
     if (!g_prof_on) return gemm_nt_run_inner(c, stream);
     ProfEntry e;

@@ -87,5 +87,6 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream);
 int32_t make_tmap_bf16(struct CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
 int32_t make_tmap_f32_out(struct CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld);
 int num_sms();
+bool gemm_profiling_enabled();       // per-launch event timing is on (incompatible with stream capture)
 
 }  // namespace mft
