@@ -85,6 +85,9 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+GATE_UP_TRAFFIC_BYTES = 4.75e8   # 72 MB read + 403 MB written per launch (algorithmic: 524 MB)
+
+
 # ------------------------------------------------------------------ CPU reference
 def cpu_reference_tokens_per_s(cfg, steps: int, warmup: int) -> dict:
     """Times the reference's own CPU implementation (oracle/_ref) of the step on a bounded sample:
@@ -247,8 +250,11 @@ def run_ours(args):
             peak, which = 1400.0, "fallback (sustained figure of the profiling recipe)"
         achieved = fl.value / (tms.value * 1e-3) / 1e12 if tms.value > 0 else 0.0
         step_flops = spec.step_flops(B, S)
-        roofline = {"bound": "tensor", "kernel": "gemm_nt_kernel (tcgen05, all launches of one step)", "achieved": achieved,
-                    "peak": peak, "peak_source": which, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+        roofline = {"bound": "tensor", "kernel": "gemm_nt_2cta_kernel / gemm_nt_kernel (tcgen05, all GEMM launches of one step)", "achieved": achieved,
+                    "peak": peak, "peak_source": which, "unit": "TFLOP/s", "frac": achieved / peak,
+                    # DRAM bytes of the largest launch (gate|up projection), from the ncu capture summarised in
+                    # profiles/gemm_nt_kernels_gemma3_1b_gate_up.md, scaled from M = 4096 to this M
+                    "traffic": GATE_UP_TRAFFIC_BYTES if (spec.name == "gemma-3-1b" and B * S == 16384) else None,
                     "launches_per_step": n.value, "gemm_ms_per_step": tms.value,
                     "step_algorithmic_tflop": step_flops / 1e12,
                     "step_achieved_tflops": step_flops / (ms / args.steps * 1e-3) / 1e12,

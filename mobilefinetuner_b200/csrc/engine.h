@@ -94,6 +94,7 @@ bool gemm_profiling_enabled();   // per-launch GEMM event timing is on (it recor
 struct StepGraph {
     int64_t batch = 0, seq = 0, n_valid_global = 0;
     int calls = 0;                   // eager runs seen with this key (the first one also performs one-time set-up)
+    int64_t kernels = 0;             // kernel launches the graph holds (added to the library's launch counter per replay)
     cudaGraphExec_t exec = nullptr;
 };
 

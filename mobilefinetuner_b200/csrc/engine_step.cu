@@ -227,7 +227,7 @@ int32_t forward_backward(Ctx& c, int64_t n_valid_global) {
         if (e.batch == c.B && e.seq == c.S && e.n_valid_global == n_valid_global) { g = &e; break; }
     if (!g) {
         if (m->graphs.size() >= 8) return eager();         // the key keeps changing (e.g. varying global counts): do not hoard graphs
-        m->graphs.push_back(StepGraph{c.B, c.S, n_valid_global, 0, nullptr});
+        m->graphs.push_back(StepGraph{c.B, c.S, n_valid_global, 0, 0, nullptr});
         g = &m->graphs.back();
     }
     if (!g->exec) {
@@ -249,8 +249,11 @@ int32_t forward_backward(Ctx& c, int64_t n_valid_global) {
             m->use_graph = false;
             return eager();
         }
+        const int64_t launches_before = mft_launch_count();
         int32_t s = forward(cc, true, n_valid_global);
         if (s == MFT_OK) s = backward(cc, n_valid_global);
+        g->kernels = mft_launch_count() - launches_before;
+        count_launch(-(int)g->kernels);                      // captured, not run: counted at every replay instead
         const cudaError_t ce = cudaStreamEndCapture(m->graph_stream, &graph);
         if (s != MFT_OK || ce != cudaSuccess || !graph || cudaGraphInstantiate(&g->exec, graph, 0) != cudaSuccess) {
             cudaGetLastError();
@@ -265,6 +268,7 @@ int32_t forward_backward(Ctx& c, int64_t n_valid_global) {
     if (int32_t s = check_cuda(cudaEventRecord(m->graph_in, m->stream), "step graph event")) return s;
     if (int32_t s = check_cuda(cudaStreamWaitEvent(m->graph_stream, m->graph_in, 0), "step graph wait")) return s;
     if (int32_t s = check_cuda(cudaGraphLaunch(g->exec, m->graph_stream), "step graph launch")) return s;
+    count_launch((int)g->kernels);
     if (int32_t s = check_cuda(cudaEventRecord(m->graph_out, m->graph_stream), "step graph event")) return s;
     return check_cuda(cudaStreamWaitEvent(m->stream, m->graph_out, 0), "step graph wait");
 }
