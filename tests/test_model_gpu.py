@@ -100,6 +100,60 @@ def test_gradient_accumulation_and_zero_grad():
     eng.close()
 
 
+def test_replayed_step_graph_matches_direct_launches():
+    """From the third call with one batch shape the step engine replays a captured CUDA graph: same gradients, same
+    loss, and the launch counter keeps counting the kernels a replay runs."""
+    from mobilefinetuner_b200 import _lib as L, synth
+    from mobilefinetuner_b200.engine import LoraStepEngine
+    case = CASES["gemma_tiny"]
+    spec = case["spec"]
+    eng = LoraStepEngine(spec, case["batch"], case["seq"])
+    eng.set_params(synth.make_params(spec, 1, 0.1))
+    eng.set_lora(synth.make_lora(spec, 2))
+    ids, labels = synth.make_batch(spec, case["batch"], case["seq"], 3)
+    losses, grads, launches = [], [], []
+    for _ in range(4):                       # direct, capture, replay, replay
+        before = L.call("mft_launch_count")
+        loss, _ = eng.forward_backward(ids, labels)
+        launches.append(L.call("mft_launch_count") - before)
+        losses.append(loss)
+        grads.append(eng.grad_bucket().clone())
+        eng.zero_grad()
+    for k in range(1, 4):
+        assert abs(losses[k] - losses[0]) <= 1e-5 * abs(losses[0])
+        assert float((grads[k] - grads[0]).abs().max()) <= 1e-4 * float(grads[0].abs().max())
+        assert launches[k] >= launches[0] - 8 and launches[k] > 0      # replays are counted (memsets are not kernels)
+    eng.close()
+
+
+def test_data_parallel_shards_add_up_to_the_full_batch():
+    """What two data-parallel ranks compute: each runs its own samples with the GLOBAL count of scored tokens as the
+    loss denominator; the sum of their LoRA-gradient buckets (the all-reduce) is the full-batch gradient."""
+    from mobilefinetuner_b200 import synth
+    from mobilefinetuner_b200.engine import LoraStepEngine
+    case = CASES["qwen_tiny"]
+    spec = case["spec"]
+    B, S = 2, case["seq"]
+    eng = LoraStepEngine(spec, B, S)
+    eng.set_params(synth.make_params(spec, 1, 0.1))
+    eng.set_lora(synth.make_lora(spec, 2))
+    ids, labels = synth.make_batch(spec, B, S, 3)
+    labels = labels.copy()
+    labels[1, S // 2:] = -100                      # unequal numbers of scored tokens per rank
+    loss_full, n_full = eng.forward_backward(ids, labels)
+    g_full = eng.grad_bucket().clone()
+    eng.zero_grad()
+    loss_sum = 0.0
+    for r in range(B):
+        loss_r, n_r = eng.forward_backward(ids[r:r + 1], labels[r:r + 1], n_valid_global=n_full)
+        loss_sum += loss_r * n_r / n_full            # ranks report their local mean; the global mean weights by count
+    g_sum = eng.grad_bucket().clone()
+    assert abs(loss_sum - loss_full) <= 2e-3 * abs(loss_full)
+    assert float((g_sum - g_full).abs().max()) <= 5e-3 * float(g_full.abs().max())
+    assert cosine(g_sum.cpu().numpy(), g_full.cpu().numpy()) >= 0.9999
+    eng.close()
+
+
 def test_out_of_range_token_raises():
     from mobilefinetuner_b200 import synth
     from mobilefinetuner_b200._lib import MftError
