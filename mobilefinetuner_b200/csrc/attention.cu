@@ -645,11 +645,13 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
     }
 #define BWD(HD, WN, BM, BN, ST)                                                                             \
     {                                                                                                       \
-        attn_delta_kernel<HD><<<dblocks, 256, 0, as_stream(stream)>>>(p);                                   \
-        MFT_LAUNCH_CHECK("attn_delta");                                                                     \
-        const int32_t sdq = attn_dq_sm100(p, HD, as_stream(stream));                                        \
+        const int32_t sdq = attn_dq_sm100(p, HD, true, as_stream(stream));   /* also forms delta */         \
         if (sdq != MFT_OK && sdq != MFT_ERR_UNSUPPORTED) return sdq;                                        \
-        if (sdq == MFT_ERR_UNSUPPORTED) DQ(HD, BM, BN, ST)                                                  \
+        if (sdq == MFT_ERR_UNSUPPORTED) {                                                                   \
+            attn_delta_kernel<HD><<<dblocks, 256, 0, as_stream(stream)>>>(p);                               \
+            MFT_LAUNCH_CHECK("attn_delta");                                                                 \
+            DQ(HD, BM, BN, ST)                                                                              \
+        }                                                                                                   \
         const int32_t skv = attn_dkv_sm100(p, HD, as_stream(stream));                                       \
         if (skv != MFT_OK && skv != MFT_ERR_UNSUPPORTED) return skv;                                        \
         dkv_tc = skv == MFT_OK;                                                                             \

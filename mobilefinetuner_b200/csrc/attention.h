@@ -21,8 +21,9 @@ struct AttnParams {
 // operands).  Returns MFT_ERR_UNSUPPORTED when the problem does not qualify; the caller then uses the
 // mma.sync kernel.
 int32_t attn_fwd_sm100(const AttnParams& p, int hd, cudaStream_t stream);
-// dQ of the backward pass, same conditions (p.delta must already hold rowsum(O * dO)).
-int32_t attn_dq_sm100(const AttnParams& p, int hd, cudaStream_t stream);
+// dQ of the backward pass, same conditions.  With compute_delta the kernel also forms delta = rowsum(O * dO) and
+// stores it in p.delta (for the dK/dV kernel that follows); otherwise p.delta must already hold it.
+int32_t attn_dq_sm100(const AttnParams& p, int hd, bool compute_delta, cudaStream_t stream);
 // dK / dV of the backward pass ADDED into p.dkv_acc (f32 [2][batch, seq, n_kv, head_dim], zeroed by the caller);
 // needs p.dkv_acc and p.delta.
 int32_t attn_dkv_sm100(const AttnParams& p, int hd, cudaStream_t stream);

@@ -336,7 +336,7 @@ constexpr int DQ_BN = 32;
 constexpr int DQ_KV_BYTES = DQ_BN * HD * 2;        // 4 chunks of [32 rows x 64 columns]
 constexpr int DQ_KST = 3, DQ_VST = 2;              // K / V stages
 constexpr int DS_BYTES = BM * 128;                 // [128 rows x 128 bytes]: keys of group 0 in bytes 0..63, of group 1 in 64..127
-constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + DS_BYTES + 192;
+constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + DS_BYTES + 192 + BM * 4;
 constexpr int DQ_THREADS = 64 + 2 * 256 + 64;     // TMA warp, S issuer, 16 element-wise warps, dP issuer, dQ issuer
 constexpr int DQ_S_COL = 0, DQ_DP_COL = 64, DQ_ACC_COL = 128;
 
@@ -360,6 +360,10 @@ struct BwdParams {
     float* dkv_acc;
     int32_t* status;
     int q_col0_stride, do_col0_stride, k_col0_stride, v_col0_stride;
+    // dQ kernel only: when o != nullptr the kernel first forms delta[row] = sum_d O * dO for its rows and stores it
+    const __nv_bfloat16 *o, *d_o;
+    long long so_b, so_s, so_h, sdo_b, sdo_s, sdo_h;
+    float* delta_out;
 };
 
 __global__ void __launch_bounds__(DQ_THREADS, 1)
@@ -384,6 +388,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     uint64_t* acc_done = bars + 19;     // [1]  completed once, by the last dQ product
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* delta_smem = reinterpret_cast<float*>(bars + 24);   // [128] rowsum(O * dO) of this CTA's queries
     if ((smem_u32(smem_raw) & 1023u) != 0) {
         if (threadIdx.x == 0 && p.status) atomicExch(p.status, MFT_ERR_INVALID_ARG);
         return;
@@ -486,7 +491,30 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
         const float sl2 = p.scale * LOG2E;
         const long long sidx = ((long long)b * p.n_heads + h) * p.seq + i;
-        const float neg_lse2 = -p.lse[sidx] * LOG2E, dlt = p.delta[sidx];
+        const float neg_lse2 = -p.lse[sidx] * LOG2E;
+        float dlt;
+        if (p.o != nullptr) {
+            // delta = rowsum(O * dO): one thread per row computes it, stores it for the dK/dV kernel and shares it
+            if (g == 0 && half == 0) {
+                const __nv_bfloat16* orow = p.o + (long long)b * p.so_b + (long long)i * p.so_s + (long long)h * p.so_h;
+                const __nv_bfloat16* drow = p.d_o + (long long)b * p.sdo_b + (long long)i * p.sdo_s + (long long)h * p.sdo_h;
+                float acc = 0.f;
+#pragma unroll 4
+                for (int d = 0; d < HD; d += 8) {
+                    float a8[8], c8[8];
+                    load8(orow + d, a8);
+                    load8(drow + d, c8);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc = fmaf(a8[e], c8[e], acc);
+                }
+                delta_smem[r] = acc;
+                p.delta_out[sidx] = acc;
+            }
+            asm volatile("bar.sync 1, 512;" ::: "memory");     // the 16 element-wise warps
+            dlt = delta_smem[r];
+        } else {
+            dlt = p.delta[sidx];
+        }
         bool ok = true;
         for (int t = g; t < n_tiles && ok; t += 2) {
             const uint32_t ph = (t >> 1) & 1;
@@ -804,7 +832,7 @@ int32_t attn_fwd_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
     return MFT_OK;
 }
 
-int32_t attn_dq_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
+int32_t attn_dq_sm100(const AttnParams& a, int hd, bool compute_delta, cudaStream_t stream) {
     static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
     if (!enabled || hd != HD || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
     if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq) || !token_major(a.sdo, a.seq)) return MFT_ERR_UNSUPPORTED;
@@ -822,6 +850,12 @@ int32_t attn_dq_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
     p.dkv_acc = a.dkv_acc; p.status = device_status_word();
     p.q_col0_stride = (int)a.sq.stride_h; p.do_col0_stride = (int)a.sdo.stride_h;
     p.k_col0_stride = (int)a.sk.stride_h; p.v_col0_stride = (int)a.sv.stride_h;
+    if (compute_delta) {
+        if (a.so.stride_b % 8 || a.so.stride_s % 8 || a.so.stride_h % 8 || a.sdo.stride_b % 8 || a.sdo.stride_s % 8) return MFT_ERR_UNSUPPORTED;
+        p.o = a.o; p.d_o = a.d_o; p.delta_out = a.delta;
+        p.so_b = a.so.stride_b; p.so_s = a.so.stride_s; p.so_h = a.so.stride_h;
+        p.sdo_b = a.sdo.stride_b; p.sdo_s = a.sdo.stride_s; p.sdo_h = a.sdo.stride_h;
+    }
     static bool configured = false;
     if (!configured) {
         if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM), "attention smem attribute")) return s;
