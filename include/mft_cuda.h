@@ -242,7 +242,11 @@ int32_t mft_accumulate_blocks_f32(const mft_block_copy_t* table_dev, int32_t n_e
  * tensor lives at base[b*stride_b + s*stride_s + h*stride_h + d] (bf16).
  * Query head h reads KV head h / (n_heads / n_kv_heads): repeat_kv is an index
  * remap, never a copy.  Key j is visible to query i iff j <= i and
- * (window <= 0 or i - j < window).  lse is f32 [batch, n_heads, seq]. */
+ * (window <= 0 or i - j < window).  lse is f32 [batch, n_heads, seq].
+ * head_dim 256 with seq a multiple of 128 and token-major tensors
+ * (stride_b == seq * stride_s) runs on tensor-memory (tcgen05) kernels; every
+ * other case on mma.sync kernels with the same results to bf16 rounding.
+ * MFT_ATTN_TC=0 in the environment selects the mma.sync kernels everywhere. */
 typedef struct {
     int64_t stride_b, stride_s, stride_h;
 } mft_strides_t;
@@ -252,9 +256,11 @@ int32_t mft_attn_fwd(const void* q, mft_strides_t sq, const void* k, mft_strides
                      float scale, int64_t window, mft_stream_t stream);
 /* dq/dk/dv are bf16 with the strides of q/k/v; dk/dv are per KV head (the sum
  * over the query heads of a group, RepeatKVHeadsBackward).  `delta` is an f32
- * [batch, n_heads, seq] scratch buffer supplied by the caller; dk/dv
- * accumulate in f32 scratch `dkv_acc` of 2*batch*seq*n_kv_heads*head_dim
- * floats supplied by the caller. */
+ * [batch, n_heads, seq] scratch buffer supplied by the caller (the call fills
+ * it with rowsum(O * dO)); dk/dv accumulate in f32 scratch `dkv_acc` of
+ * 2*batch*seq*n_kv_heads*head_dim floats supplied by the caller.  `dkv_acc`
+ * may be NULL: dk/dv are then produced by one CTA per KV head without scratch
+ * (slower for grouped KV heads, and the tensor-memory dK/dV kernel needs it). */
 int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, mft_strides_t sk,
                      const void* v, mft_strides_t sv, const void* o, mft_strides_t so,
                      const void* d_o, mft_strides_t sdo, const float* lse,
