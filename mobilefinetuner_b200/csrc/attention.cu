@@ -108,6 +108,8 @@ __device__ __forceinline__ bool visible(int i, int j, int seq, int window) {
 template <int HD, int BM, int BN, int STAGES>
 __global__ void __launch_bounds__(BM * 2)
 attn_fwd_kernel(const AttnParams p) {
+    dep_trigger();
+    dep_wait();
     constexpr int LD = HD + 8, THREADS = BM * 2, NB = BN / 8;
     extern __shared__ __align__(16) uint8_t smem_attn[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_attn);
@@ -240,6 +242,8 @@ attn_fwd_kernel(const AttnParams p) {
 // delta[b,h,i] = sum_d O[i,d] * dO[i,d]; one warp per row.
 template <int HD>
 __global__ void attn_delta_kernel(const AttnParams p) {
+    dep_trigger();
+    dep_wait();
     const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int64_t total = (int64_t)p.batch * p.n_heads * p.seq;
@@ -261,6 +265,8 @@ __global__ void attn_delta_kernel(const AttnParams p) {
 template <int HD, int BM, int BN, int STAGES>
 __global__ void __launch_bounds__(BM * 2)
 attn_bwd_dq_kernel(const AttnParams p) {
+    dep_trigger();
+    dep_wait();
     constexpr int LD = HD + 8, THREADS = BM * 2, NB = BN / 8;
     extern __shared__ __align__(16) uint8_t smem_attn[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_attn);
@@ -369,6 +375,8 @@ attn_bwd_dq_kernel(const AttnParams p) {
 template <int HD, int WN, bool SPLIT>
 __global__ void __launch_bounds__(128 * WN)
 attn_bwd_dkv_kernel(const AttnParams p) {
+    dep_trigger();
+    dep_wait();
     constexpr int BM = 64, BN = 64;
     constexpr int LD = HD + 8;
     constexpr int THREADS = 128 * WN;
@@ -524,6 +532,8 @@ attn_bwd_dkv_kernel(const AttnParams p) {
 // f32 accumulator [2][batch, seq, n_kv, HD] -> bf16 dK / dV with the caller's strides
 template <int HD>
 __global__ void attn_dkv_store_kernel(const AttnParams p) {
+    dep_trigger();
+    dep_wait();
     const int64_t half = (int64_t)p.batch * p.seq * p.n_kv * HD;
     const int64_t total = 2 * half / 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -585,7 +595,7 @@ extern "C" int32_t mft_attn_fwd(const void* q, mft_strides_t sq, const void* k, 
         dim3 grid((unsigned)((seq + BM - 1) / BM), (unsigned)n_heads, (unsigned)batch);      \
         const int bytes = (BM + 2 * ST * BN) * (HD + 8) * 2;                                 \
         if (int32_t s = set_smem(attn_fwd_kernel<HD, BM, BN, ST>, bytes)) return s;          \
-        attn_fwd_kernel<HD, BM, BN, ST><<<grid, BM * 2, bytes, as_stream(stream)>>>(p);      \
+        launch_dep(attn_fwd_kernel<HD, BM, BN, ST>, dim3(grid), dim3(BM * 2), (size_t)(bytes), as_stream(stream), p);      \
     }
     const int shape = attn_shape_override();
     // measured best on B200: 64-query CTAs (two resident per SM) beat 128-query ones; at head_dim 256 the
@@ -629,17 +639,17 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
         dim3 gq((unsigned)((seq + BM - 1) / BM), (unsigned)n_heads, (unsigned)batch);                       \
         const int b1 = (2 * BM + 2 * ST * BN) * (HD + 8) * 2;                                               \
         if (int32_t s = set_smem(attn_bwd_dq_kernel<HD, BM, BN, ST>, b1)) return s;                         \
-        attn_bwd_dq_kernel<HD, BM, BN, ST><<<gq, BM * 2, b1, as_stream(stream)>>>(p);                       \
+        launch_dep(attn_bwd_dq_kernel<HD, BM, BN, ST>, dim3(gq), dim3(BM * 2), (size_t)(b1), as_stream(stream), p);                       \
         MFT_LAUNCH_CHECK("attn_bwd_dq");                                                                    \
     }
 #define DKV(HD, WN, SPLIT)                                                                                  \
     {                                                                                                       \
         const int b2 = 6 * 64 * (HD + 8) * 2 + 2 * 64 * (64 + 8) * 2 + 4 * 64 * 4;                          \
         if (int32_t s = set_smem(attn_bwd_dkv_kernel<HD, WN, SPLIT>, b2)) return s;                         \
-        attn_bwd_dkv_kernel<HD, WN, SPLIT><<<gk, 128 * WN, b2, as_stream(stream)>>>(p);                     \
+        launch_dep(attn_bwd_dkv_kernel<HD, WN, SPLIT>, dim3(gk), dim3(128 * WN), (size_t)(b2), as_stream(stream), p);                     \
         MFT_LAUNCH_CHECK("attn_bwd_dkv");                                                                   \
         if (SPLIT) {                                                                                        \
-            attn_dkv_store_kernel<HD><<<148 * 8, 256, 0, as_stream(stream)>>>(p);                           \
+            launch_dep(attn_dkv_store_kernel<HD>, dim3(148 * 8), dim3(256), (size_t)(0), as_stream(stream), p);                           \
             MFT_LAUNCH_CHECK("attn_dkv_store");                                                             \
         }                                                                                                   \
     }
@@ -648,7 +658,7 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
         const int32_t sdq = attn_dq_sm100(p, HD, true, as_stream(stream));   /* also forms delta */         \
         if (sdq != MFT_OK && sdq != MFT_ERR_UNSUPPORTED) return sdq;                                        \
         if (sdq == MFT_ERR_UNSUPPORTED) {                                                                   \
-            attn_delta_kernel<HD><<<dblocks, 256, 0, as_stream(stream)>>>(p);                               \
+            launch_dep(attn_delta_kernel<HD>, dim3(dblocks), dim3(256), (size_t)(0), as_stream(stream), p);                               \
             MFT_LAUNCH_CHECK("attn_delta");                                                                 \
             DQ(HD, BM, BN, ST)                                                                              \
         }                                                                                                   \
@@ -656,7 +666,7 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
         if (skv != MFT_OK && skv != MFT_ERR_UNSUPPORTED) return skv;                                        \
         dkv_tc = skv == MFT_OK;                                                                             \
         if (dkv_tc) {                                                                                       \
-            attn_dkv_store_kernel<HD><<<148 * 8, 256, 0, as_stream(stream)>>>(p);                           \
+            launch_dep(attn_dkv_store_kernel<HD>, dim3(148 * 8), dim3(256), (size_t)(0), as_stream(stream), p);                           \
             MFT_LAUNCH_CHECK("attn_dkv_store");                                                             \
         } else if (split) DKV(HD, WN, true) else DKV(HD, WN, false)                                         \
     }

@@ -84,6 +84,7 @@ __device__ __forceinline__ bool visible(int i, int j, int window) { return j <= 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+    dep_trigger();
     // The swizzled tiles need 1024-byte alignment and the tiles fill the SM's shared memory to within 1 KB, so
     // there is no room for alignment slack: the dynamic segment is declared aligned and checked below.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -138,6 +139,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    dep_wait();     // set-up above overlapped the previous kernel's tail; its results are needed from here on
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer
@@ -369,6 +371,7 @@ struct BwdParams {
 __global__ void __launch_bounds__(DQ_THREADS, 1)
 attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                   const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
+    dep_trigger();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* q_smem = smem_raw;
     uint8_t* do_smem = q_smem + Q_BYTES;
@@ -419,6 +422,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    dep_wait();     // set-up above overlapped the previous kernel's tail; its results are needed from here on
 
     if (warp == 0) {
         if (lane == 0) {
@@ -603,6 +607,7 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem, u
 __global__ void __launch_bounds__(DKV_THREADS, 1)
 attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
+    dep_trigger();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* k_smem = smem_raw;                            // [128 keys x 256], 4 chunks
     uint8_t* v_smem = k_smem + Q_BYTES;
@@ -651,6 +656,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    dep_wait();     // set-up above overlapped the previous kernel's tail; its results are needed from here on
 
     if (warp == 0) {
         if (lane == 0) {
@@ -827,7 +833,7 @@ int32_t attn_fwd_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid((unsigned)(a.seq / BM), (unsigned)a.n_heads, (unsigned)a.batch);
-    attn_fwd_tc_kernel<<<grid, THREADS, FWD_SMEM, stream>>>(mq, mk, mv, p);
+    launch_dep(attn_fwd_tc_kernel, dim3(grid), dim3(THREADS), (size_t)(FWD_SMEM), stream, mq, mk, mv, p);
     MFT_LAUNCH_CHECK("attn_fwd_tc");
     return MFT_OK;
 }
@@ -862,7 +868,7 @@ int32_t attn_dq_sm100(const AttnParams& a, int hd, bool compute_delta, cudaStrea
         configured = true;
     }
     dim3 grid((unsigned)(a.seq / BM), (unsigned)a.n_heads, (unsigned)a.batch);
-    attn_dq_tc_kernel<<<grid, DQ_THREADS, DQ_SMEM, stream>>>(mq, md, mk, mv, p);
+    launch_dep(attn_dq_tc_kernel, dim3(grid), dim3(DQ_THREADS), (size_t)(DQ_SMEM), stream, mq, md, mk, mv, p);
     MFT_LAUNCH_CHECK("attn_dq_tc");
     return MFT_OK;
 }
@@ -892,7 +898,7 @@ int32_t attn_dkv_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid((unsigned)(a.seq / BM), (unsigned)(2 * a.n_heads), (unsigned)a.batch);
-    attn_dkv_tc_kernel<<<grid, DKV_THREADS, DKV_SMEM, stream>>>(mq, md, mk, mv, p);
+    launch_dep(attn_dkv_tc_kernel, dim3(grid), dim3(DKV_THREADS), (size_t)(DKV_SMEM), stream, mq, md, mk, mv, p);
     MFT_LAUNCH_CHECK("attn_dkv_tc");
     return MFT_OK;
 }

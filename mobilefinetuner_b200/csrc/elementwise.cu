@@ -15,6 +15,8 @@ static inline int grid_for(int64_t work_items, int threads, int max_blocks = 148
 
 // ---------------------------------------------------------------- casts
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n) {
+    dep_trigger();
+    dep_wait();
     const int64_t nv = n / 8;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
@@ -25,6 +27,8 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat1
     for (int64_t i = nv * 8 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = f32_to_bf16(src[i]);
 }
 __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int64_t n) {
+    dep_trigger();
+    dep_wait();
     const int64_t nv = n / 8;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
@@ -39,6 +43,8 @@ __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, floa
 template <typename TS>
 __global__ void transpose_to_bf16_kernel(const TS* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                          int64_t rows, int64_t cols, int64_t dst_ld) {
+    dep_trigger();
+    dep_wait();
     __shared__ float tile[32][33];
     const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
     for (int j = threadIdx.y; j < 32; j += blockDim.y) {
@@ -62,6 +68,8 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const __nv_bfl
                                  const __nv_bfloat16* __restrict__ pos, float* __restrict__ out,
                                  int64_t seq_len, int64_t hidden, int64_t vocab, float scale,
                                  int32_t* __restrict__ status) {
+    dep_trigger();
+    dep_wait();
     const int64_t t = blockIdx.x;
     const int32_t id = ids[t];
     float* o = out + t * hidden;
@@ -116,6 +124,8 @@ __device__ __forceinline__ float gelu_tanh_fast(float x) {
 template <int KIND>
 __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
                                int64_t ld, __nv_bfloat16* __restrict__ y, int64_t rows, int64_t cols) {
+    dep_trigger();
+    dep_wait();
     const int64_t vpr = cols / 8;
     const int64_t total = rows * vpr;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -138,6 +148,8 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_
                                const __nv_bfloat16* __restrict__ up, int64_t ld,
                                __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dup,
                                int64_t rows, int64_t cols) {
+    dep_trigger();
+    dep_wait();
     const int64_t vpr = cols / 8;
     const int64_t total = rows * vpr;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -171,6 +183,8 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_
 
 template <typename TB>
 __global__ void add_kernel(const float* __restrict__ a, const TB* __restrict__ b, float* __restrict__ out, int64_t n) {
+    dep_trigger();
+    dep_wait();
     const int64_t nv = n / 8;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
@@ -188,6 +202,8 @@ __global__ void add_kernel(const float* __restrict__ a, const TB* __restrict__ b
     }
 }
 __global__ void scale_kernel(float* __restrict__ x, float alpha, int64_t n) {
+    dep_trigger();
+    dep_wait();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] *= alpha;
 }
@@ -196,6 +212,8 @@ __global__ void scale_kernel(float* __restrict__ x, float alpha, int64_t n) {
 template <typename T>
 __global__ void repeat_kv_kernel(const T* __restrict__ kv, T* __restrict__ out, int64_t n_kv, int64_t seq,
                                  int64_t hd, int64_t rep, int64_t total) {
+    dep_trigger();
+    dep_wait();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int64_t d = i % hd, s = (i / hd) % seq, h = (i / (hd * seq)) % (n_kv * rep), b = i / (hd * seq * n_kv * rep);
@@ -204,6 +222,8 @@ __global__ void repeat_kv_kernel(const T* __restrict__ kv, T* __restrict__ out, 
 }
 __global__ void repeat_kv_bwd_kernel(const float* __restrict__ dout, float* __restrict__ dkv, int64_t n_kv,
                                      int64_t seq, int64_t hd, int64_t rep, int64_t total) {
+    dep_trigger();
+    dep_wait();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int64_t d = i % hd, s = (i / hd) % seq, h = (i / (hd * seq)) % n_kv, b = i / (hd * seq * n_kv);
@@ -216,6 +236,8 @@ __global__ void repeat_kv_bwd_kernel(const float* __restrict__ dout, float* __re
 // ---------------------------------------------------------------- LoRA panel pack / unpack
 template <bool ACCUM_F32>
 __global__ void block_copy_kernel(const mft_block_copy_t* __restrict__ table) {
+    dep_trigger();
+    dep_wait();
     const mft_block_copy_t e = table[blockIdx.x];
     const int64_t total = (int64_t)e.rows * e.cols;
     const float* src = static_cast<const float*>(e.src);
@@ -230,6 +252,8 @@ __global__ void block_copy_kernel(const mft_block_copy_t* __restrict__ table) {
 
 // ---------------------------------------------------------------- optimizer
 __global__ void sqnorm_kernel(const float* __restrict__ g, int64_t n, float* __restrict__ out) {
+    dep_trigger();
+    dep_wait();
     __shared__ float scratch[32];
     float acc = 0.f;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -240,6 +264,8 @@ __global__ void sqnorm_kernel(const float* __restrict__ g, int64_t n, float* __r
 __global__ void adam_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                             int64_t n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                             const float* __restrict__ sqnorm, float max_norm, float clip_eps, int zero_grad) {
+    dep_trigger();
+    dep_wait();
     float clip = 1.0f;
     if (sqnorm != nullptr && max_norm > 0.f) {
         const float norm = sqrtf(*sqnorm);
@@ -268,14 +294,14 @@ extern "C" {
 int32_t mft_cast_f32_to_bf16(const float* src, void* dst, int64_t n, mft_stream_t stream) {
     MFT_CHECK_ARG(src && dst && n >= 0, "mft_cast_f32_to_bf16: bad argument");
     if (n == 0) return MFT_OK;
-    cast_f32_bf16_kernel<<<grid_for(n / 8 + 1, 256), 256, 0, as_stream(stream)>>>(src, (__nv_bfloat16*)dst, n);
+    launch_dep(cast_f32_bf16_kernel, dim3(grid_for(n / 8 + 1, 256)), dim3(256), (size_t)(0), as_stream(stream), src, (__nv_bfloat16*)dst, n);
     MFT_LAUNCH_CHECK("cast_f32_bf16");
     return MFT_OK;
 }
 int32_t mft_cast_bf16_to_f32(const void* src, float* dst, int64_t n, mft_stream_t stream) {
     MFT_CHECK_ARG(src && dst && n >= 0, "mft_cast_bf16_to_f32: bad argument");
     if (n == 0) return MFT_OK;
-    cast_bf16_f32_kernel<<<grid_for(n / 8 + 1, 256), 256, 0, as_stream(stream)>>>((const __nv_bfloat16*)src, dst, n);
+    launch_dep(cast_bf16_f32_kernel, dim3(grid_for(n / 8 + 1, 256)), dim3(256), (size_t)(0), as_stream(stream), (const __nv_bfloat16*)src, dst, n);
     MFT_LAUNCH_CHECK("cast_bf16_f32");
     return MFT_OK;
 }
@@ -283,7 +309,7 @@ int32_t mft_transpose_f32_to_bf16(const float* src, void* dst, int64_t rows, int
     MFT_CHECK_ARG(src && dst && rows > 0 && cols > 0, "mft_transpose_f32_to_bf16: bad argument");
     dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
     MFT_CHECK_ARG(grid.y <= 65535, "mft_transpose_f32_to_bf16: too many rows");
-    transpose_to_bf16_kernel<float><<<grid, dim3(32, 8), 0, as_stream(stream)>>>(src, (__nv_bfloat16*)dst, rows, cols, rows);
+    launch_dep(transpose_to_bf16_kernel<float>, dim3(grid), dim3(dim3(32, 8)), (size_t)(0), as_stream(stream), src, (__nv_bfloat16*)dst, rows, cols, rows);
     MFT_LAUNCH_CHECK("transpose_f32_bf16");
     return MFT_OK;
 }
@@ -294,7 +320,7 @@ int32_t mft_transpose_bf16_ld(const void* src, void* dst, int64_t rows, int64_t 
     MFT_CHECK_ARG(src && dst && rows > 0 && cols > 0 && dst_ld >= rows, "mft_transpose_bf16_ld: bad argument");
     dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
     MFT_CHECK_ARG(grid.y <= 65535, "mft_transpose_bf16_ld: too many rows");
-    transpose_to_bf16_kernel<__nv_bfloat16><<<grid, dim3(32, 8), 0, as_stream(stream)>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, rows, cols, dst_ld);
+    launch_dep(transpose_to_bf16_kernel<__nv_bfloat16>, dim3(grid), dim3(dim3(32, 8)), (size_t)(0), as_stream(stream), (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, rows, cols, dst_ld);
     MFT_LAUNCH_CHECK("transpose_bf16");
     return MFT_OK;
 }
@@ -304,7 +330,7 @@ int32_t mft_embedding_gather(const int32_t* ids, const void* table, const void* 
                              mft_stream_t stream) {
     MFT_CHECK_ARG(ids && table && out && n_tokens > 0 && hidden > 0 && vocab > 0 && seq_len > 0, "mft_embedding_gather: bad argument");
     MFT_CHECK_ARG(hidden % 8 == 0, "mft_embedding_gather: hidden must be a multiple of 8");
-    embedding_kernel<<<(unsigned)n_tokens, 128, 0, as_stream(stream)>>>(ids, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos, out,
+    launch_dep(embedding_kernel, dim3((unsigned)n_tokens), dim3(128), (size_t)(0), as_stream(stream), ids, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos, out,
                                                                         seq_len, hidden, vocab, scale, status_dev);
     MFT_LAUNCH_CHECK("embedding_gather");
     return MFT_OK;
@@ -316,9 +342,9 @@ int32_t mft_act_fwd(int32_t kind, const void* gate, const void* up, int64_t ld, 
     MFT_CHECK_ARG(kind == MFT_ACT_GELU || up, "mft_act_fwd: gated activation needs `up`");
     const int g = grid_for(rows * cols / 8, 256);
     auto G = (const __nv_bfloat16*)gate; auto U = (const __nv_bfloat16*)up; auto Y = (__nv_bfloat16*)y;
-    if (kind == MFT_ACT_GELU) act_fwd_kernel<MFT_ACT_GELU><<<g, 256, 0, as_stream(stream)>>>(G, U, ld, Y, rows, cols);
-    else if (kind == MFT_ACT_SWIGLU) act_fwd_kernel<MFT_ACT_SWIGLU><<<g, 256, 0, as_stream(stream)>>>(G, U, ld, Y, rows, cols);
-    else if (kind == MFT_ACT_GEGLU) act_fwd_kernel<MFT_ACT_GEGLU><<<g, 256, 0, as_stream(stream)>>>(G, U, ld, Y, rows, cols);
+    if (kind == MFT_ACT_GELU) launch_dep(act_fwd_kernel<MFT_ACT_GELU>, dim3(g), dim3(256), (size_t)(0), as_stream(stream), G, U, ld, Y, rows, cols);
+    else if (kind == MFT_ACT_SWIGLU) launch_dep(act_fwd_kernel<MFT_ACT_SWIGLU>, dim3(g), dim3(256), (size_t)(0), as_stream(stream), G, U, ld, Y, rows, cols);
+    else if (kind == MFT_ACT_GEGLU) launch_dep(act_fwd_kernel<MFT_ACT_GEGLU>, dim3(g), dim3(256), (size_t)(0), as_stream(stream), G, U, ld, Y, rows, cols);
     else return fail(MFT_ERR_INVALID_ARG, "mft_act_fwd: unknown kind");
     MFT_LAUNCH_CHECK("act_fwd");
     return MFT_OK;
@@ -330,28 +356,28 @@ int32_t mft_act_bwd(int32_t kind, const void* dy, const void* gate, const void* 
     const int g = grid_for(rows * cols / 8, 256);
     auto D = (const __nv_bfloat16*)dy; auto G = (const __nv_bfloat16*)gate; auto U = (const __nv_bfloat16*)up;
     auto DG = (__nv_bfloat16*)dgate; auto DU = (__nv_bfloat16*)dup;
-    if (kind == MFT_ACT_GELU) act_bwd_kernel<MFT_ACT_GELU><<<g, 256, 0, as_stream(stream)>>>(D, G, U, ld, DG, DU, rows, cols);
-    else if (kind == MFT_ACT_SWIGLU) act_bwd_kernel<MFT_ACT_SWIGLU><<<g, 256, 0, as_stream(stream)>>>(D, G, U, ld, DG, DU, rows, cols);
-    else if (kind == MFT_ACT_GEGLU) act_bwd_kernel<MFT_ACT_GEGLU><<<g, 256, 0, as_stream(stream)>>>(D, G, U, ld, DG, DU, rows, cols);
+    if (kind == MFT_ACT_GELU) launch_dep(act_bwd_kernel<MFT_ACT_GELU>, dim3(g), dim3(256), (size_t)(0), as_stream(stream), D, G, U, ld, DG, DU, rows, cols);
+    else if (kind == MFT_ACT_SWIGLU) launch_dep(act_bwd_kernel<MFT_ACT_SWIGLU>, dim3(g), dim3(256), (size_t)(0), as_stream(stream), D, G, U, ld, DG, DU, rows, cols);
+    else if (kind == MFT_ACT_GEGLU) launch_dep(act_bwd_kernel<MFT_ACT_GEGLU>, dim3(g), dim3(256), (size_t)(0), as_stream(stream), D, G, U, ld, DG, DU, rows, cols);
     else return fail(MFT_ERR_INVALID_ARG, "mft_act_bwd: unknown kind");
     MFT_LAUNCH_CHECK("act_bwd");
     return MFT_OK;
 }
 int32_t mft_add_f32(const float* a, const float* b, float* out, int64_t n, mft_stream_t stream) {
     MFT_CHECK_ARG(a && b && out && n > 0, "mft_add_f32: bad argument");
-    add_kernel<float><<<grid_for(n / 8 + 1, 256), 256, 0, as_stream(stream)>>>(a, b, out, n);
+    launch_dep(add_kernel<float>, dim3(grid_for(n / 8 + 1, 256)), dim3(256), (size_t)(0), as_stream(stream), a, b, out, n);
     MFT_LAUNCH_CHECK("add_f32");
     return MFT_OK;
 }
 int32_t mft_add_f32_bf16(const float* a, const void* b, float* out, int64_t n, mft_stream_t stream) {
     MFT_CHECK_ARG(a && b && out && n > 0, "mft_add_f32_bf16: bad argument");
-    add_kernel<__nv_bfloat16><<<grid_for(n / 8 + 1, 256), 256, 0, as_stream(stream)>>>(a, (const __nv_bfloat16*)b, out, n);
+    launch_dep(add_kernel<__nv_bfloat16>, dim3(grid_for(n / 8 + 1, 256)), dim3(256), (size_t)(0), as_stream(stream), a, (const __nv_bfloat16*)b, out, n);
     MFT_LAUNCH_CHECK("add_f32_bf16");
     return MFT_OK;
 }
 int32_t mft_scale_f32(float* x, float alpha, int64_t n, mft_stream_t stream) {
     MFT_CHECK_ARG(x && n > 0, "mft_scale_f32: bad argument");
-    scale_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(x, alpha, n);
+    launch_dep(scale_kernel, dim3(grid_for(n, 256)), dim3(256), (size_t)(0), as_stream(stream), x, alpha, n);
     MFT_LAUNCH_CHECK("scale_f32");
     return MFT_OK;
 }
@@ -360,8 +386,8 @@ int32_t mft_repeat_kv(const void* kv, int32_t dtype, void* out, int64_t batch, i
                       int64_t rep, mft_stream_t stream) {
     MFT_CHECK_ARG(kv && out && batch > 0 && n_kv > 0 && seq > 0 && hd > 0 && rep > 0, "mft_repeat_kv: bad argument");
     const int64_t total = batch * n_kv * rep * seq * hd;
-    if (dtype == MFT_F32) repeat_kv_kernel<float><<<grid_for(total, 256), 256, 0, as_stream(stream)>>>((const float*)kv, (float*)out, n_kv, seq, hd, rep, total);
-    else if (dtype == MFT_BF16) repeat_kv_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, as_stream(stream)>>>((const __nv_bfloat16*)kv, (__nv_bfloat16*)out, n_kv, seq, hd, rep, total);
+    if (dtype == MFT_F32) launch_dep(repeat_kv_kernel<float>, dim3(grid_for(total, 256)), dim3(256), (size_t)(0), as_stream(stream), (const float*)kv, (float*)out, n_kv, seq, hd, rep, total);
+    else if (dtype == MFT_BF16) launch_dep(repeat_kv_kernel<__nv_bfloat16>, dim3(grid_for(total, 256)), dim3(256), (size_t)(0), as_stream(stream), (const __nv_bfloat16*)kv, (__nv_bfloat16*)out, n_kv, seq, hd, rep, total);
     else return fail(MFT_ERR_INVALID_ARG, "mft_repeat_kv: dtype must be f32 or bf16");
     MFT_LAUNCH_CHECK("repeat_kv");
     return MFT_OK;
@@ -370,7 +396,7 @@ int32_t mft_repeat_kv_bwd(const float* dout, float* dkv, int64_t batch, int64_t 
                           mft_stream_t stream) {
     MFT_CHECK_ARG(dout && dkv && batch > 0 && n_kv > 0 && seq > 0 && hd > 0 && rep > 0, "mft_repeat_kv_bwd: bad argument");
     const int64_t total = batch * n_kv * seq * hd;
-    repeat_kv_bwd_kernel<<<grid_for(total, 256), 256, 0, as_stream(stream)>>>(dout, dkv, n_kv, seq, hd, rep, total);
+    launch_dep(repeat_kv_bwd_kernel, dim3(grid_for(total, 256)), dim3(256), (size_t)(0), as_stream(stream), dout, dkv, n_kv, seq, hd, rep, total);
     MFT_LAUNCH_CHECK("repeat_kv_bwd");
     return MFT_OK;
 }
@@ -378,14 +404,14 @@ int32_t mft_repeat_kv_bwd(const float* dout, float* dkv, int64_t batch, int64_t 
 int32_t mft_pack_blocks_bf16(const mft_block_copy_t* table_dev, int32_t n, mft_stream_t stream) {
     MFT_CHECK_ARG(table_dev && n >= 0, "mft_pack_blocks_bf16: bad argument");
     if (n == 0) return MFT_OK;
-    block_copy_kernel<false><<<dim3((unsigned)n, 8), 256, 0, as_stream(stream)>>>(table_dev);
+    launch_dep(block_copy_kernel<false>, dim3(dim3((unsigned)n, 8)), dim3(256), (size_t)(0), as_stream(stream), table_dev);
     MFT_LAUNCH_CHECK("pack_blocks_bf16");
     return MFT_OK;
 }
 int32_t mft_accumulate_blocks_f32(const mft_block_copy_t* table_dev, int32_t n, mft_stream_t stream) {
     MFT_CHECK_ARG(table_dev && n >= 0, "mft_accumulate_blocks_f32: bad argument");
     if (n == 0) return MFT_OK;
-    block_copy_kernel<true><<<dim3((unsigned)n, 8), 256, 0, as_stream(stream)>>>(table_dev);
+    launch_dep(block_copy_kernel<true>, dim3(dim3((unsigned)n, 8)), dim3(256), (size_t)(0), as_stream(stream), table_dev);
     MFT_LAUNCH_CHECK("accumulate_blocks_f32");
     return MFT_OK;
 }
@@ -393,7 +419,7 @@ int32_t mft_accumulate_blocks_f32(const mft_block_copy_t* table_dev, int32_t n, 
 int32_t mft_grad_sqnorm(const float* grads, int64_t n, float* sqnorm_dev, mft_stream_t stream) {
     MFT_CHECK_ARG(grads && sqnorm_dev && n > 0, "mft_grad_sqnorm: bad argument");
     if (int32_t s = check_cuda(cudaMemsetAsync(sqnorm_dev, 0, 4, as_stream(stream)), "sqnorm memset")) return s;
-    sqnorm_kernel<<<grid_for(n, 256, 148 * 4), 256, 0, as_stream(stream)>>>(grads, n, sqnorm_dev);
+    launch_dep(sqnorm_kernel, dim3(grid_for(n, 256, 148 * 4)), dim3(256), (size_t)(0), as_stream(stream), grads, n, sqnorm_dev);
     MFT_LAUNCH_CHECK("grad_sqnorm");
     return MFT_OK;
 }
@@ -404,7 +430,7 @@ int32_t mft_adam_step(float* params, float* grads, float* m, float* v, int64_t n
     // bias corrections exactly as the reference computes them: 1 - powf(beta, step)
     const float bc1 = 1.0f - powf(beta1, (float)step);
     const float bc2 = 1.0f - powf(beta2, (float)step);
-    adam_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(params, grads, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2,
+    launch_dep(adam_kernel, dim3(grid_for(n, 256)), dim3(256), (size_t)(0), as_stream(stream), params, grads, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2,
                                                                   sqnorm_dev, max_norm, clip_eps, zero_grad);
     MFT_LAUNCH_CHECK("adam_step");
     return MFT_OK;

@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
+    dep_trigger();
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atoms (8 rows x 128 B)
@@ -86,6 +87,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
+    dep_wait();     // set-up above overlapped the previous kernel's tail; its results are needed from here on
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer
@@ -408,7 +410,7 @@ static int32_t launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const C
     }
     const int tiles = p.tiles_mn * p.splits;
     const int grid = tiles < num_sms() ? tiles : num_sms();
-    gemm_nt_kernel<BN, EPI><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, md, p);
+    launch_dep(gemm_nt_kernel<BN, EPI>, dim3(grid), dim3(GEMM_THREADS), (size_t)(Cfg::SMEM_BYTES), stream, ma, mb, ma2, mb2, md, p);
     MFT_LAUNCH_CHECK("gemm_nt");
     return MFT_OK;
 }

@@ -90,6 +90,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                     const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
+    dep_trigger();
     constexpr int STAGES = PairCfg<BN2>::STAGES, STAGE_BYTES = PairCfg<BN2>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -123,6 +124,7 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     cluster_sync();             // barrier inits of both CTAs are visible before anyone arrives remotely
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    dep_wait();     // set-up above overlapped the previous kernel's tail; its results are needed from here on
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer (one per CTA)
@@ -237,7 +239,7 @@ int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& 
     const int tiles = p.tiles_mn * p.splits;
     int clusters = num_sms() / 2;
     if (tiles < clusters) clusters = tiles;
-    gemm_nt_2cta_kernel<EPI, BN2><<<2 * clusters, THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, ma2, mb2, md, p);
+    launch_dep(gemm_nt_2cta_kernel<EPI, BN2>, dim3(2 * clusters), dim3(THREADS), (size_t)(Cfg::SMEM_BYTES), stream, ma, mb, ma2, mb2, md, p);
     MFT_LAUNCH_CHECK("gemm_nt_2cta");
     return MFT_OK;
 }

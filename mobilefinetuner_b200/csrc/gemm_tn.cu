@@ -43,6 +43,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 __global__ void __launch_bounds__(TN_THREADS)
 gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bfloat16* __restrict__ V, int64_t ldv,
                int64_t T, int P, int Q, float alpha, float* __restrict__ out, int64_t stride_p, int64_t stride_q, int64_t t_per_split) {
+    dep_trigger();
+    dep_wait();
     extern __shared__ __align__(16) uint8_t tn_smem[];
     typedef __nv_bfloat16 (*UsT)[TN_TC][TN_US];
     typedef __nv_bfloat16 (*VsT)[TN_TC][TN_VS];
@@ -166,7 +168,7 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
         if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tn smem attr")) return s;
         configured = true;
     }
-    gemm_tn_kernel<<<grid, TN_THREADS, smem, as_stream(stream)>>>((const __nv_bfloat16*)uu, ldu2, (const __nv_bfloat16*)vv, ldv2, t,
+    launch_dep(gemm_tn_kernel, dim3(grid), dim3(TN_THREADS), (size_t)(smem), as_stream(stream), (const __nv_bfloat16*)uu, ldu2, (const __nv_bfloat16*)vv, ldv2, t,
                                                                   (int)pp, (int)qq, alpha, out, stride_p, stride_q, t_per);
     MFT_LAUNCH_CHECK("gemm_tn");
     return MFT_OK;

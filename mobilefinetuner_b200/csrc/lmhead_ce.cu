@@ -69,6 +69,8 @@ CeWorkspace carve(void* base, int64_t T, int64_t H, int64_t V) {
 __global__ void ce_prepare_kernel(const int32_t* __restrict__ labels, int64_t batch, int64_t seq, int64_t vocab,
                                   int ignore_index, int32_t* __restrict__ tgt, int32_t* __restrict__ n_valid,
                                   int32_t* __restrict__ status) {
+    dep_trigger();
+    dep_wait();
     __shared__ float scratch[32];
     const int64_t total = batch * seq;
     int local = 0;
@@ -91,6 +93,8 @@ __global__ void ce_prepare_kernel(const int32_t* __restrict__ labels, int64_t ba
 __global__ void ce_reduce_kernel(const float2* __restrict__ partials, int64_t ntiles, int64_t ld, const int32_t* __restrict__ tgt,
                                  const float* __restrict__ tgt_logit, float* __restrict__ lse, double* __restrict__ loss_sum,
                                  int64_t T) {
+    dep_trigger();
+    dep_wait();
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (row >= T) return;
@@ -116,6 +120,8 @@ __global__ void ce_reduce_kernel(const float2* __restrict__ partials, int64_t nt
 }
 
 __global__ void ce_finalize_kernel(const double* loss_sum, const int32_t* n_valid, float* loss) {
+    dep_trigger();
+    dep_wait();
     const int n = *n_valid;
     *loss = n > 0 ? (float)(*loss_sum / (double)n) : NAN;
 }
@@ -128,6 +134,8 @@ __global__ void ce_fused_finish_kernel(const float2* __restrict__ partials, int6
                                        const __nv_bfloat16* __restrict__ table, int64_t H, const int32_t* __restrict__ n_valid,
                                        int64_t nv_override, float dloss, float* __restrict__ lse, double* __restrict__ loss_sum,
                                        __nv_bfloat16* __restrict__ dh) {
+    dep_trigger();
+    dep_wait();
     __shared__ float scratch[32];
     const int64_t row = blockIdx.x;
     if (row_flag[row]) return;
@@ -164,6 +172,8 @@ __global__ void ce_row_fixup_kernel(const __nv_bfloat16* __restrict__ hidden, co
                                     const int32_t* __restrict__ tgt, const int32_t* __restrict__ row_flag, int64_t T, int64_t H,
                                     int64_t V, const int32_t* __restrict__ n_valid, int64_t nv_override, float dloss,
                                     float* __restrict__ lse, double* __restrict__ loss_sum, __nv_bfloat16* __restrict__ dh) {
+    dep_trigger();
+    dep_wait();
     extern __shared__ float fix_smem[];
     __shared__ float red_m[32], red_s[32], tgt_l, row_lse;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -224,6 +234,8 @@ __global__ void ce_row_fixup_kernel(const __nv_bfloat16* __restrict__ hidden, co
 // ---- dense-logits variants
 __global__ void ce_dense_fwd_kernel(const float* __restrict__ logits, const int32_t* __restrict__ tgt, int64_t vocab,
                                     float* __restrict__ lse, double* __restrict__ loss_sum) {
+    dep_trigger();
+    dep_wait();
     __shared__ float scratch[32];
     __shared__ float bmax;
     const int64_t row = blockIdx.x;
@@ -252,6 +264,8 @@ __global__ void ce_dense_fwd_kernel(const float* __restrict__ logits, const int3
 __global__ void ce_dense_bwd_kernel(const float* __restrict__ logits, const int32_t* __restrict__ tgt, int64_t vocab,
                                     const float* __restrict__ lse, const int32_t* __restrict__ n_valid, float dloss,
                                     float* __restrict__ dlogits) {
+    dep_trigger();
+    dep_wait();
     const int64_t row = blockIdx.x;
     const int t = tgt[row];
     const int n = *n_valid;
@@ -291,15 +305,15 @@ extern "C" int32_t mft_lmhead_ce_fwd(const void* hidden_bf16, const void* table_
     cudaStream_t st = as_stream(stream);
     if (int32_t s = check_cuda(cudaMemsetAsync(n_valid_dev, 0, 4, st), "ce memset")) return s;
     if (int32_t s = check_cuda(cudaMemsetAsync(w.loss_sum, 0, 8, st), "ce memset")) return s;
-    ce_prepare_kernel<<<(unsigned)std::min<int64_t>((T + 255) / 256, 1024), 256, 0, st>>>(labels, batch, seq, vocab, ignore_index, w.tgt, n_valid_dev, status_dev);
+    launch_dep(ce_prepare_kernel, dim3((unsigned)std::min<int64_t>((T + 255) / 256, 1024)), dim3(256), (size_t)(0), st, labels, batch, seq, vocab, ignore_index, w.tgt, n_valid_dev, status_dev);
     MFT_LAUNCH_CHECK("ce_prepare");
     GemmCall c;
     c.a = hidden_bf16; c.lda = hidden; c.b = table_bf16; c.ldb = hidden; c.m = T; c.n = vocab; c.k = hidden;
     c.epi = EPI_CE_STATS; c.ce_tgt = w.tgt; c.ce_partials = w.partials; c.ce_partial_ld = (int)w.ntiles; c.ce_tgt_logit = w.tgt_logit;
     if (int32_t s = gemm_nt_run(c, st)) return s;
-    ce_reduce_kernel<<<(unsigned)((T * 32 + 255) / 256), 256, 0, st>>>(w.partials, w.ntiles, w.ntiles, w.tgt, w.tgt_logit, lse, w.loss_sum, T);
+    launch_dep(ce_reduce_kernel, dim3((unsigned)((T * 32 + 255) / 256)), dim3(256), (size_t)(0), st, w.partials, w.ntiles, w.ntiles, w.tgt, w.tgt_logit, lse, w.loss_sum, T);
     MFT_LAUNCH_CHECK("ce_reduce");
-    ce_finalize_kernel<<<1, 1, 0, st>>>(w.loss_sum, n_valid_dev, loss_dev);
+    launch_dep(ce_finalize_kernel, dim3(1), dim3(1), (size_t)(0), st, w.loss_sum, n_valid_dev, loss_dev);
     MFT_LAUNCH_CHECK("ce_finalize");
     return MFT_OK;
 }
@@ -316,7 +330,7 @@ extern "C" int32_t mft_lmhead_ce_bwd(const void* hidden_bf16, const void* table_
     MFT_CHECK_ARG(workspace_bytes >= w.total, "mft_lmhead_ce_bwd: workspace too small");
     cudaStream_t st = as_stream(stream);
     if (int32_t s = check_cuda(cudaMemsetAsync(w.count, 0, 4, st), "ce memset")) return s;
-    ce_prepare_kernel<<<(unsigned)std::min<int64_t>((T + 255) / 256, 1024), 256, 0, st>>>(labels, batch, seq, vocab, ignore_index, w.tgt, w.count, nullptr);
+    launch_dep(ce_prepare_kernel, dim3((unsigned)std::min<int64_t>((T + 255) / 256, 1024)), dim3(256), (size_t)(0), st, labels, batch, seq, vocab, ignore_index, w.tgt, w.count, nullptr);
     MFT_LAUNCH_CHECK("ce_prepare");
     for (int64_t v0 = 0; v0 < vocab; v0 += w.panel) {
         const int64_t vc = std::min(w.panel, vocab - v0);
@@ -358,7 +372,7 @@ extern "C" int32_t mft_lmhead_ce_fused(const void* hidden_bf16, const void* tabl
     if (int32_t s = check_cuda(cudaMemsetAsync(n_valid_dev, 0, 4, st), "ce memset")) return s;
     if (int32_t s = check_cuda(cudaMemsetAsync(w.loss_sum, 0, 8, st), "ce memset")) return s;
     if (int32_t s = check_cuda(cudaMemsetAsync(w.row_flag, 0, (size_t)T * 4, st), "ce memset")) return s;
-    ce_prepare_kernel<<<(unsigned)std::min<int64_t>((T + 255) / 256, 1024), 256, 0, st>>>(labels, batch, seq, vocab, ignore_index, w.tgt, n_valid_dev, status_dev);
+    launch_dep(ce_prepare_kernel, dim3((unsigned)std::min<int64_t>((T + 255) / 256, 1024)), dim3(256), (size_t)(0), st, labels, batch, seq, vocab, ignore_index, w.tgt, n_valid_dev, status_dev);
     MFT_LAUNCH_CHECK("ce_prepare");
     // reference exponent per row: log-sum-exp of panel 0
     {
@@ -367,7 +381,7 @@ extern "C" int32_t mft_lmhead_ce_fused(const void* hidden_bf16, const void* tabl
         c.a = hidden_bf16; c.lda = H; c.b = table_bf16; c.ldb = H; c.m = T; c.n = vc; c.k = H;
         c.epi = EPI_CE_STATS; c.ce_tgt = w.tgt; c.ce_partials = w.partials; c.ce_partial_ld = (int)w.ntiles; c.ce_tgt_logit = w.tgt_logit;
         if (int32_t s = gemm_nt_run(c, st)) return s;
-        ce_reduce_kernel<<<(unsigned)((T * 32 + 255) / 256), 256, 0, st>>>(w.partials, (vc + CE_TILE_N - 1) / CE_TILE_N, w.ntiles, w.tgt,
+        launch_dep(ce_reduce_kernel, dim3((unsigned)((T * 32 + 255) / 256)), dim3(256), (size_t)(0), st, w.partials, (vc + CE_TILE_N - 1) / CE_TILE_N, w.ntiles, w.tgt,
                                                                          w.tgt_logit, w.m_ref, nullptr, T);
         MFT_LAUNCH_CHECK("ce_reduce");
     }
@@ -388,7 +402,7 @@ extern "C" int32_t mft_lmhead_ce_fused(const void* hidden_bf16, const void* tabl
         d.d = w.dh_acc; d.ldd = H; d.d_is_f32 = 1; d.accumulate = v0 > 0; d.splits = 0;
         if (int32_t s = gemm_nt_run(d, st)) return s;
     }
-    ce_fused_finish_kernel<<<(unsigned)T, 128, 0, st>>>(w.partials, w.ntiles, w.tgt, w.tgt_logit, w.m_ref, w.row_flag, w.dh_acc,
+    launch_dep(ce_fused_finish_kernel, dim3((unsigned)T), dim3(128), (size_t)(0), st, w.partials, w.ntiles, w.tgt, w.tgt_logit, w.m_ref, w.row_flag, w.dh_acc,
                                                        static_cast<const __nv_bfloat16*>(table_bf16), H, n_valid_dev, n_valid_override,
                                                        dloss, lse, w.loss_sum, static_cast<__nv_bfloat16*>(dhidden_bf16));
     MFT_LAUNCH_CHECK("ce_fused_finish");
@@ -397,11 +411,11 @@ extern "C" int32_t mft_lmhead_ce_fused(const void* hidden_bf16, const void* tabl
         if (int32_t s = check_cuda(cudaFuncSetAttribute(ce_row_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "ce fixup attribute")) return s;
         fix_attr = true;
     }
-    ce_row_fixup_kernel<<<(unsigned)std::min<int64_t>(T, 148 * 4), FIX_THREADS, fix_smem, st>>>(
+    launch_dep(ce_row_fixup_kernel, dim3((unsigned)std::min<int64_t>(T, 148 * 4)), dim3(FIX_THREADS), (size_t)(fix_smem), st, 
         static_cast<const __nv_bfloat16*>(hidden_bf16), static_cast<const __nv_bfloat16*>(table_bf16), w.tgt, w.row_flag, T, H, vocab,
         n_valid_dev, n_valid_override, dloss, lse, w.loss_sum, static_cast<__nv_bfloat16*>(dhidden_bf16));
     MFT_LAUNCH_CHECK("ce_row_fixup");
-    ce_finalize_kernel<<<1, 1, 0, st>>>(w.loss_sum, n_valid_dev, loss_dev);
+    launch_dep(ce_finalize_kernel, dim3(1), dim3(1), (size_t)(0), st, w.loss_sum, n_valid_dev, loss_dev);
     MFT_LAUNCH_CHECK("ce_finalize");
     return MFT_OK;
 }
@@ -415,11 +429,11 @@ extern "C" int32_t mft_ce_dense_fwd(const float* logits, const int32_t* labels, 
     cudaStream_t st = as_stream(stream);
     if (int32_t s = check_cuda(cudaMemsetAsync(n_valid_dev, 0, 4, st), "ce memset")) return s;
     if (int32_t s = check_cuda(cudaMemsetAsync(loss_scratch, 0, 8, st), "ce memset")) return s;
-    ce_prepare_kernel<<<(unsigned)std::min<int64_t>((T + 255) / 256, 1024), 256, 0, st>>>(labels, batch, seq, vocab, ignore_index, tgt_scratch, n_valid_dev, status_dev);
+    launch_dep(ce_prepare_kernel, dim3((unsigned)std::min<int64_t>((T + 255) / 256, 1024)), dim3(256), (size_t)(0), st, labels, batch, seq, vocab, ignore_index, tgt_scratch, n_valid_dev, status_dev);
     MFT_LAUNCH_CHECK("ce_prepare");
-    ce_dense_fwd_kernel<<<(unsigned)T, 256, 0, st>>>(logits, tgt_scratch, vocab, lse, loss_scratch);
+    launch_dep(ce_dense_fwd_kernel, dim3((unsigned)T), dim3(256), (size_t)(0), st, logits, tgt_scratch, vocab, lse, loss_scratch);
     MFT_LAUNCH_CHECK("ce_dense_fwd");
-    ce_finalize_kernel<<<1, 1, 0, st>>>(loss_scratch, n_valid_dev, loss_dev);
+    launch_dep(ce_finalize_kernel, dim3(1), dim3(1), (size_t)(0), st, loss_scratch, n_valid_dev, loss_dev);
     MFT_LAUNCH_CHECK("ce_finalize");
     return MFT_OK;
 }
@@ -428,7 +442,7 @@ extern "C" int32_t mft_ce_dense_bwd(const float* logits, const int32_t* tgt_scra
                                     const float* lse, const int32_t* n_valid_dev, float dloss, float* dlogits,
                                     mft_stream_t stream) {
     MFT_CHECK_ARG(logits && tgt_scratch && lse && n_valid_dev && dlogits && batch > 0 && seq > 0 && vocab > 0, "mft_ce_dense_bwd: bad argument");
-    ce_dense_bwd_kernel<<<(unsigned)(batch * seq), 256, 0, as_stream(stream)>>>(logits, tgt_scratch, vocab, lse, n_valid_dev, dloss, dlogits);
+    launch_dep(ce_dense_bwd_kernel, dim3((unsigned)(batch * seq)), dim3(256), (size_t)(0), as_stream(stream), logits, tgt_scratch, vocab, lse, n_valid_dev, dloss, dlogits);
     MFT_LAUNCH_CHECK("ce_dense_bwd");
     return MFT_OK;
 }

@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, float eps, int unit_offset,
                    TY* __restrict__ y, float* __restrict__ rstd_out, const float* __restrict__ residual,
                    float* __restrict__ sum_out, int64_t dim) {
+    dep_trigger();
+    dep_wait();
     __shared__ float scratch[32];
     const int64_t row = blockIdx.x;
     const TX* xr = x + row * dim;
@@ -70,6 +72,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
                    const float* __restrict__ rstd_in, float eps, int unit_offset, TDX* __restrict__ dx,
                    int accumulate, float* __restrict__ dweight, int64_t dim) {
+    dep_trigger();
+    dep_wait();
     __shared__ float scratch[32];
     const int64_t row = blockIdx.x;
     const int nvec = (int)(dim / 8);
@@ -127,6 +131,8 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
 rmsnorm_fwd_warp_kernel(const TX* __restrict__ x, const float* __restrict__ w, float eps, int unit_offset,
                         TY* __restrict__ y, float* __restrict__ rstd_out, const float* __restrict__ residual,
                         float* __restrict__ sum_out, int64_t rows, int64_t dim) {
+    dep_trigger();
+    dep_wait();
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -174,6 +180,8 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
 rmsnorm_bwd_warp_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
                         const float* __restrict__ rstd_in, float eps, int unit_offset, TDX* __restrict__ dx,
                         int accumulate, float* __restrict__ dweight, int64_t rows, int64_t dim) {
+    dep_trigger();
+    dep_wait();
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -231,6 +239,8 @@ template <typename TX, typename TY>
 __global__ void __launch_bounds__(NORM_THREADS)
 layernorm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
                      TY* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t dim) {
+    dep_trigger();
+    dep_wait();
     __shared__ float scratch[32];
     const int64_t row = blockIdx.x;
     const int nvec = (int)(dim / 8);
@@ -281,6 +291,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 layernorm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
                      const float* __restrict__ mean_in, const float* __restrict__ rstd_in, TDX* __restrict__ dx,
                      int accumulate, float* __restrict__ dweight, float* __restrict__ dbias, int64_t dim) {
+    dep_trigger();
+    dep_wait();
     __shared__ float scratch[32];
     const int64_t row = blockIdx.x;
     const int nvec = (int)(dim / 8);
@@ -338,6 +350,8 @@ __global__ void headnorm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64
                                      const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
                                      __nv_bfloat16* __restrict__ out, int64_t ld_out,
                                      int64_t n_tokens, int64_t seq_len, int64_t n_heads) {
+    dep_trigger();
+    dep_wait();
     constexpr int HD = PER * 64, HALF = PER * 32;
     const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -432,11 +446,11 @@ int32_t mft_rmsnorm_fwd(const void* x, int32_t xd, const float* w, float eps, in
     MFT_CHECK_ARG(!residual || sum_out, "mft_rmsnorm_fwd: residual needs sum_out");
     MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_rmsnorm_fwd: dim must be a multiple of 8 and <= 4096");
     const unsigned wblocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
-#define WCALL(TX, TY, VPL) rmsnorm_fwd_warp_kernel<TX, TY, VPL><<<wblocks, NORM_WARPS * 32, 0, as_stream(stream)>>>((const TX*)x, w, eps, unit_offset, (TY*)y, rstd, residual, sum_out, rows, dim);
+#define WCALL(TX, TY, VPL) launch_dep(rmsnorm_fwd_warp_kernel<TX, TY, VPL>, dim3(wblocks), dim3(NORM_WARPS * 32), (size_t)(0), as_stream(stream), (const TX*)x, w, eps, unit_offset, (TY*)y, rstd, residual, sum_out, rows, dim);
 #define CALL(TX, TY)                                                                                     \
     if (dim <= 1280) { WCALL(TX, TY, 5) }                                                                \
     else if (dim <= 2048) { WCALL(TX, TY, 8) }                                                           \
-    else rmsnorm_fwd_kernel<TX, TY><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TX*)x, w, eps, unit_offset, (TY*)y, rstd, residual, sum_out, dim);
+    else launch_dep(rmsnorm_fwd_kernel<TX, TY>, dim3((unsigned)rows), dim3(NORM_THREADS), (size_t)(0), as_stream(stream), (const TX*)x, w, eps, unit_offset, (TY*)y, rstd, residual, sum_out, dim);
     DISPATCH_2(xd, yd, CALL)
 #undef CALL
 #undef WCALL
@@ -452,11 +466,11 @@ int32_t mft_rmsnorm_bwd(const void* dy, int32_t dyd, const void* x, int32_t xd, 
     MFT_CHECK_ARG(!accumulate || dxd == MFT_F32, "mft_rmsnorm_bwd: accumulate needs f32 dx");
     MFT_CHECK_ARG(!dweight || rstd, "mft_rmsnorm_bwd: dweight needs rstd");
     const unsigned wblocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
-#define WLAUNCH(TDY, TX, TDX, VPL) rmsnorm_bwd_warp_kernel<TDY, TX, TDX, VPL><<<wblocks, NORM_WARPS * 32, 0, as_stream(stream)>>>((const TDY*)dy, (const TX*)x, w, rstd, eps, unit_offset, (TDX*)dx, accumulate, dweight, rows, dim);
+#define WLAUNCH(TDY, TX, TDX, VPL) launch_dep(rmsnorm_bwd_warp_kernel<TDY, TX, TDX, VPL>, dim3(wblocks), dim3(NORM_WARPS * 32), (size_t)(0), as_stream(stream), (const TDY*)dy, (const TX*)x, w, rstd, eps, unit_offset, (TDX*)dx, accumulate, dweight, rows, dim);
 #define LAUNCH(TDY, TX, TDX)                                                                             \
     if (dim <= 1280) { WLAUNCH(TDY, TX, TDX, 5) }                                                        \
     else if (dim <= 2048) { WLAUNCH(TDY, TX, TDX, 8) }                                                   \
-    else rmsnorm_bwd_kernel<TDY, TX, TDX><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TDY*)dy, (const TX*)x, w, rstd, eps, unit_offset, (TDX*)dx, accumulate, dweight, dim);
+    else launch_dep(rmsnorm_bwd_kernel<TDY, TX, TDX>, dim3((unsigned)rows), dim3(NORM_THREADS), (size_t)(0), as_stream(stream), (const TDY*)dy, (const TX*)x, w, rstd, eps, unit_offset, (TDX*)dx, accumulate, dweight, dim);
 #define CALL(TDY, TX) if (dxd == MFT_F32) { LAUNCH(TDY, TX, float) } else if (dxd == MFT_BF16) { LAUNCH(TDY, TX, __nv_bfloat16) } else return fail(MFT_ERR_INVALID_ARG, "mft_rmsnorm_bwd: bad dx dtype");
     DISPATCH_2(dyd, xd, CALL)
 #undef CALL
@@ -470,7 +484,7 @@ int32_t mft_layernorm_fwd(const void* x, int32_t xd, const float* w, const float
                           float* mean, float* rstd, int64_t rows, int64_t dim, mft_stream_t stream) {
     MFT_CHECK_ARG(x && w && b && y && rows > 0 && dim > 0, "mft_layernorm_fwd: bad argument");
     MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_layernorm_fwd: dim must be a multiple of 8 and <= 4096");
-#define CALL(TX, TY) layernorm_fwd_kernel<TX, TY><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TX*)x, w, b, eps, (TY*)y, mean, rstd, dim);
+#define CALL(TX, TY) launch_dep(layernorm_fwd_kernel<TX, TY>, dim3((unsigned)rows), dim3(NORM_THREADS), (size_t)(0), as_stream(stream), (const TX*)x, w, b, eps, (TY*)y, mean, rstd, dim);
     DISPATCH_2(xd, yd, CALL)
 #undef CALL
     MFT_LAUNCH_CHECK("layernorm_fwd");
@@ -483,7 +497,7 @@ int32_t mft_layernorm_bwd(const void* dy, int32_t dyd, const void* x, int32_t xd
     MFT_CHECK_ARG(dy && x && w && mean && rstd && dx && rows > 0 && dim > 0, "mft_layernorm_bwd: bad argument");
     MFT_CHECK_ARG(dim % 8 == 0 && dim <= 8 * NORM_THREADS * NORM_VPT, "mft_layernorm_bwd: dim must be a multiple of 8 and <= 4096");
     MFT_CHECK_ARG(!accumulate || dxd == MFT_F32, "mft_layernorm_bwd: accumulate needs f32 dx");
-#define LAUNCH(TDY, TX, TDX) layernorm_bwd_kernel<TDY, TX, TDX><<<(unsigned)rows, NORM_THREADS, 0, as_stream(stream)>>>((const TDY*)dy, (const TX*)x, w, mean, rstd, (TDX*)dx, accumulate, dweight, dbias, dim);
+#define LAUNCH(TDY, TX, TDX) launch_dep(layernorm_bwd_kernel<TDY, TX, TDX>, dim3((unsigned)rows), dim3(NORM_THREADS), (size_t)(0), as_stream(stream), (const TDY*)dy, (const TX*)x, w, mean, rstd, (TDX*)dx, accumulate, dweight, dbias, dim);
 #define CALL(TDY, TX) if (dxd == MFT_F32) { LAUNCH(TDY, TX, float) } else if (dxd == MFT_BF16) { LAUNCH(TDY, TX, __nv_bfloat16) } else return fail(MFT_ERR_INVALID_ARG, "mft_layernorm_bwd: bad dx dtype");
     DISPATCH_2(dyd, xd, CALL)
 #undef CALL
@@ -513,7 +527,7 @@ static int32_t launch_headnorm_rope(bool bwd, const void* in, int64_t ld_in, con
     const int64_t warps = n_tokens * n_heads;
     const int threads = 256;
     const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
-#define HL(PER, B) headnorm_rope_kernel<PER, B><<<blocks, threads, 0, as_stream(stream)>>>((const __nv_bfloat16*)in, ld_in, (const __nv_bfloat16*)x, ld_x, nw, eps, rstd, cos_tab, sin_tab, (__nv_bfloat16*)out, ld_out, n_tokens, seq_len, n_heads)
+#define HL(PER, B) launch_dep(headnorm_rope_kernel<PER, B>, dim3(blocks), dim3(threads), (size_t)(0), as_stream(stream), (const __nv_bfloat16*)in, ld_in, (const __nv_bfloat16*)x, ld_x, nw, eps, rstd, cos_tab, sin_tab, (__nv_bfloat16*)out, ld_out, n_tokens, seq_len, n_heads)
     if (hd == 64) { if (bwd) HL(1, true); else HL(1, false); }
     else if (hd == 128) { if (bwd) HL(2, true); else HL(2, false); }
     else if (hd == 256) { if (bwd) HL(4, true); else HL(4, false); }

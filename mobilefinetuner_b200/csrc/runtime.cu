@@ -1,6 +1,7 @@
 // Runtime part of libmft_cuda.so: initialisation, error reporting, the caching
 // device allocator (the device analogue of the reference's MemoryManager /
 // MemoryPool, operator/finetune_ops/core/memory_manager.cpp:34-145) and copies.
+#include <cstdlib>
 #include <atomic>
 #include <map>
 #include <mutex>
@@ -19,6 +20,10 @@ static std::mutex g_init_mutex;
 
 void set_error(const std::string& msg) { g_last_error = msg; }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+bool dep_launch_enabled() {
+    static const bool on = [] { const char* e = std::getenv("MFT_PDL"); return e ? std::atoi(e) != 0 : false; }();
+    return on;
+}
 int32_t* device_status_word() { return g_status_word; }
 
 int32_t fail(int32_t code, const std::string& msg) {
