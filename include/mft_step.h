@@ -100,6 +100,40 @@ int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_host, const in
 int32_t mft_model_optimizer_step(mft_model_t* m, float lr, float beta1, float beta2, float eps,
                                  float weight_decay, float max_norm, float clip_eps);
 int32_t mft_model_zero_grad(mft_model_t* m);
+/* Factor applied to d(loss) in the next forward_backward calls (default 1): a driver that accumulates
+ * gradients over several micro-batches passes 1 / grad_accum_steps, as the reference's trainers do by
+ * back-propagating mul(loss, 1 / grad_accum_steps). */
+int32_t mft_model_set_loss_scale(mft_model_t* m, float scale);
+
+/* ---- step driver: the loop body of GemmaLoRATrainer::train_step (optim/gemma_trainer.cpp:85-147) and
+ *      LoRATrainer::train_step (optim/trainer.cpp:102-146) with everything after the batch upload on the device:
+ *      micro-batch forward + loss + backward with the loss scaled by 1/grad_accum_steps, gradients accumulated
+ *      in the LoRA bucket; every grad_accum_steps-th call clips (if ||g|| > max_grad_norm: g *= max / (||g|| + 1e-6),
+ *      the trainers' rule), sets the learning rate from the schedule, runs Adam and clears the gradients.
+ *      The LoRA gradients never leave the GPU. */
+enum { MFT_LR_LINEAR = 0, MFT_LR_COSINE = 1, MFT_LR_CONSTANT = 2 };
+typedef struct {
+    float learning_rate, weight_decay, adam_beta1, adam_beta2, adam_eps;
+    float max_grad_norm;         /* <= 0: no clipping */
+    float warmup_ratio;
+    int32_t lr_scheduler;        /* MFT_LR_*: GemmaLoRATrainer treats every name but "cosine" as linear; LoRATrainer
+                                    keeps the rate constant after the warm-up for a name it does not know */
+    int32_t grad_accum_steps;
+    int64_t total_updates;       /* optimizer steps of the run: ceil(ceil(num_sequences / micro_batch) * epochs / grad_accum) */
+} mft_trainer_config_t;
+typedef struct mft_trainer mft_trainer_t;
+/* Learning rate of optimizer step `step` (1-based), get_lr of both trainers.  Pure host arithmetic. */
+float mft_trainer_lr(const mft_trainer_config_t* cfg, int64_t step);
+int32_t mft_trainer_create(mft_model_t* model, const mft_trainer_config_t* cfg, mft_trainer_t** out);
+int32_t mft_trainer_destroy(mft_trainer_t* t);
+/* One micro-batch (host ids / labels, as Batch carries them).  *stepped = 1 and *avg_loss = mean of the window's
+ * micro-batch losses when this call closed an accumulation window (the reference returns that mean), else
+ * *stepped = 0 (the reference returns -1).  n_valid_global as in mft_model_forward_backward.
+ * *lr_used (optional) receives the learning rate of the step taken. */
+int32_t mft_trainer_train_step(mft_trainer_t* t, const int32_t* ids_host, const int32_t* labels_host,
+                               int32_t batch, int32_t seq, int64_t n_valid_global,
+                               int32_t* stepped, float* avg_loss, float* lr_used);
+int64_t mft_trainer_global_step(const mft_trainer_t* t);
 /* Debug/parity taps: copy the final hidden states (f32 [batch*seq, hidden], after the last norm). */
 int32_t mft_model_get_final_hidden_host(mft_model_t* m, float* out_host, int64_t n_elements);
 int64_t mft_model_activation_bytes(const mft_model_t* m);

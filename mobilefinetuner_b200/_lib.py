@@ -28,6 +28,16 @@ class BlockCopy(C.Structure):
                 ("src_ld", C.c_int32), ("dst_ld", C.c_int32), ("transpose", C.c_int32), ("pad", C.c_int32)]
 
 
+class TrainerConfig(C.Structure):
+    """mft_trainer_config_t of include/mft_step.h (fields of GemmaTrainerConfig / TrainerConfig that drive a step)."""
+    _fields_ = [("learning_rate", C.c_float), ("weight_decay", C.c_float), ("adam_beta1", C.c_float), ("adam_beta2", C.c_float),
+                ("adam_eps", C.c_float), ("max_grad_norm", C.c_float), ("warmup_ratio", C.c_float), ("lr_scheduler", C.c_int32),
+                ("grad_accum_steps", C.c_int32), ("total_updates", C.c_int64)]
+
+
+LR_SCHEDULERS = {"linear": 0, "cosine": 1, "constant": 2}
+
+
 class ModelConfig(C.Structure):
     """mft_model_config_t of include/mft_step.h."""
     _fields_ = [("family", C.c_int32), ("vocab", C.c_int32), ("hidden", C.c_int32), ("inter", C.c_int32),
@@ -126,15 +136,21 @@ _SIGS = {
     "mft_model_forward_loss": [vp, vp, vp, i32, i32, C.POINTER(f32)],
     "mft_model_optimizer_step": [vp, f32, f32, f32, f32, f32, f32, f32],
     "mft_model_zero_grad": [vp],
+    "mft_model_set_loss_scale": [vp, f32],
+    "mft_trainer_lr": [vp, i64],
+    "mft_trainer_create": [vp, vp, vp],
+    "mft_trainer_destroy": [vp],
+    "mft_trainer_train_step": [vp, vp, vp, i32, i32, i64, vp, vp, vp],
+    "mft_trainer_global_step": [vp],
     "mft_model_get_final_hidden_host": [vp, vp, i64],
     "mft_model_activation_bytes": [vp],
     "mft_adam_step": [vp, vp, vp, vp, i64, i64, f32, f32, f32, f32, f32, vp, f32, f32, i32, vp],
 }
 _RET = {"mft_launch_count": i64, "mft_last_error": C.c_char_p, "mft_lmhead_ce_workspace_bytes": i64,
         "mft_lmhead_ce_set_panel_budget": i64,
-        "mft_model_activation_bytes": i64}
+        "mft_model_activation_bytes": i64, "mft_trainer_lr": f32, "mft_trainer_global_step": i64}
 _NO_STATUS = {"mft_version", "mft_lmhead_ce_workspace_bytes", "mft_lmhead_ce_set_panel_budget", "mft_model_param_count", "mft_model_lora_count",
-              "mft_model_lora_has_grad"}
+              "mft_model_lora_has_grad", "mft_trainer_lr", "mft_trainer_global_step"}
 
 
 def exported_names() -> list[str]:

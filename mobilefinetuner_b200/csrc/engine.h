@@ -93,6 +93,7 @@ bool gemm_profiling_enabled();   // per-launch GEMM event timing is on (it recor
 // One captured forward + backward (a fixed sequence of ~1100 launches for a given batch shape).
 struct StepGraph {
     int64_t batch = 0, seq = 0, n_valid_global = 0;
+    float loss_scale = 1.0f;
     int calls = 0;                   // eager runs seen with this key (the first one also performs one-time set-up)
     int64_t kernels = 0;             // kernel launches the graph holds (added to the library's launch counter per replay)
     cudaGraphExec_t exec = nullptr;
@@ -104,6 +105,7 @@ struct mft_model {
     // Replay of the training step as a CUDA graph: the launches of one step are issued faster than the host can
     // make them one by one (tensor-map encodes + ~1100 launches per step).  Captured on a private stream that is
     // ordered against `stream` with events.  MFT_STEP_GRAPH=0 disables it.
+    float loss_scale = 1.0f;         // d(loss) of the next backward passes (1 / grad_accum_steps under a step driver)
     bool use_graph = true;
     cudaStream_t graph_stream = nullptr;
     cudaEvent_t graph_in = nullptr, graph_out = nullptr;

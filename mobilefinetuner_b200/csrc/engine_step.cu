@@ -119,7 +119,7 @@ int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
     // lm head + shifted cross entropy; the [T,V] logits are never written.  A training step gets the loss and
     // d(loss)/d(final hidden) (into t_h) from one sweep over the vocabulary.
     if (for_training && m->ce_onepass)
-        return mft_lmhead_ce_fused(m->hf, m->embed, m->embed_t, m->ld_t, m->labels, c.B, S, H, cfg.vocab, -100, n_valid_global, 1.0f,
+        return mft_lmhead_ce_fused(m->hf, m->embed, m->embed_t, m->ld_t, m->labels, c.B, S, H, cfg.vocab, -100, n_valid_global, m->loss_scale,
                                    m->loss_dev, m->n_valid_dev, m->ce_lse, m->t_h, m->status_dev, m->ce_ws, m->ce_ws_bytes, c.st);
     return mft_lmhead_ce_fwd(m->hf, m->embed, m->labels, c.B, S, H, cfg.vocab, -100, m->loss_dev, m->n_valid_dev, m->ce_lse, m->status_dev,
                              m->ce_ws, m->ce_ws_bytes, c.st);
@@ -137,7 +137,7 @@ int32_t backward(Ctx& c, int64_t n_valid_global) {
     // d(loss)/d(final hidden), then through the final norm into the residual gradient dx (f32)
     if (!m->ce_onepass)
         TRY(mft_lmhead_ce_bwd(m->hf, m->embed, m->embed_t, m->ld_t, m->labels, c.B, S, H, cfg.vocab, -100, m->ce_lse, m->n_valid_dev,
-                              n_valid_global, 1.0f, m->t_h, m->ce_ws, m->ce_ws_bytes, c.st));
+                              n_valid_global, m->loss_scale, m->t_h, m->ce_ws, m->ce_ws_bytes, c.st));
     if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, m->x_final, MFT_F32, m->final_w, m->mean_f, m->rstd_f, m->dx, MFT_F32, 0, nullptr, nullptr, T, H, c.st));
     else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, m->x_final, MFT_F32, m->final_w, m->rstd_f, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 0, nullptr, T, H, c.st));
 
@@ -224,10 +224,10 @@ int32_t forward_backward(Ctx& c, int64_t n_valid_global) {
     if (!m->use_graph || gemm_profiling_enabled()) return eager();
     StepGraph* g = nullptr;
     for (auto& e : m->graphs)
-        if (e.batch == c.B && e.seq == c.S && e.n_valid_global == n_valid_global) { g = &e; break; }
+        if (e.batch == c.B && e.seq == c.S && e.n_valid_global == n_valid_global && e.loss_scale == m->loss_scale) { g = &e; break; }
     if (!g) {
         if (m->graphs.size() >= 8) return eager();         // the key keeps changing (e.g. varying global counts): do not hoard graphs
-        m->graphs.push_back(StepGraph{c.B, c.S, n_valid_global, 0, 0, nullptr});
+        m->graphs.push_back(StepGraph{c.B, c.S, n_valid_global, m->loss_scale, 0, 0, nullptr});
         g = &m->graphs.back();
     }
     if (!g->exec) {
@@ -329,6 +329,89 @@ extern "C" int32_t mft_model_optimizer_step(mft_model_t* m, float lr, float beta
                       weight_decay, sq, max_norm, clip_eps, 1, m->stream));
     m->panels_dirty = true;
     return MFT_OK;
+}
+
+extern "C" int32_t mft_model_set_loss_scale(mft_model_t* m, float scale) {
+    MFT_CHECK_ARG(m && std::isfinite(scale) && scale != 0.f, "mft_model_set_loss_scale: bad argument");
+    m->loss_scale = scale;
+    return MFT_OK;
+}
+
+// ---------------------------------------------------------------- step driver
+struct mft_trainer {
+    mft_model* model;
+    mft_trainer_config_t cfg;
+    int64_t global_step = 0;
+    int accum_counter = 0;
+    float* loss_acc = nullptr;        // device: sum of the window's micro-batch losses
+};
+
+extern "C" float mft_trainer_lr(const mft_trainer_config_t* cfg, int64_t step) {
+    if (!cfg) return 0.f;
+    // same integer / float arithmetic as get_lr of the trainers
+    const int64_t total = std::max<int64_t>(1, cfg->total_updates);
+    const int warmup_steps = static_cast<int>(total * cfg->warmup_ratio);
+    if (warmup_steps > 0 && step <= warmup_steps) return cfg->learning_rate * (static_cast<float>(step) / warmup_steps);
+    float progress = static_cast<float>(step - warmup_steps) / std::max<int64_t>(1, total - warmup_steps);
+    progress = std::min(std::max(progress, 0.0f), 1.0f);
+    if (cfg->lr_scheduler == MFT_LR_COSINE) return cfg->learning_rate * 0.5f * (1.0f + std::cos(3.14159265f * progress));
+    if (cfg->lr_scheduler == MFT_LR_LINEAR) return cfg->learning_rate * (1.0f - progress);
+    return cfg->learning_rate;
+}
+
+extern "C" int32_t mft_trainer_create(mft_model_t* model, const mft_trainer_config_t* cfg, mft_trainer_t** out) {
+    MFT_CHECK_ARG(model && cfg && out, "mft_trainer_create: null argument");
+    MFT_CHECK_ARG(cfg->grad_accum_steps >= 1 && cfg->lr_scheduler >= MFT_LR_LINEAR && cfg->lr_scheduler <= MFT_LR_CONSTANT,
+                  "mft_trainer_create: bad configuration");
+    auto* t = new mft_trainer();
+    t->model = model;
+    t->cfg = *cfg;
+    void* p = nullptr;
+    if (int32_t s = mft_malloc(4, &p)) { delete t; return s; }
+    t->loss_acc = static_cast<float*>(p);
+    if (int32_t s = mft_memset(t->loss_acc, 0, 4, model->stream)) { mft_free(p); delete t; return s; }
+    *out = t;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_trainer_destroy(mft_trainer_t* t) {
+    if (!t) return MFT_OK;
+    cudaStreamSynchronize(t->model->stream);
+    mft_free(t->loss_acc);
+    delete t;
+    return MFT_OK;
+}
+
+extern "C" int64_t mft_trainer_global_step(const mft_trainer_t* t) { return t ? t->global_step : 0; }
+
+extern "C" int32_t mft_trainer_train_step(mft_trainer_t* t, const int32_t* ids_host, const int32_t* labels_host, int32_t batch,
+                                          int32_t seq, int64_t n_valid_global, int32_t* stepped, float* avg_loss, float* lr_used) {
+    MFT_CHECK_ARG(t && ids_host && labels_host && stepped, "mft_trainer_train_step: null argument");
+    mft_model* m = t->model;
+    Ctx c;
+    TRY(make_ctx(m, batch, seq, &c));
+    const float saved_scale = m->loss_scale;
+    m->loss_scale = 1.0f / static_cast<float>(t->cfg.grad_accum_steps);
+    TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)c.T * 4, c.st));
+    TRY(mft_memcpy_h2d(m->labels, labels_host, (size_t)c.T * 4, c.st));
+    const int32_t s = forward_backward(c, n_valid_global);
+    m->loss_scale = saved_scale;
+    if (s != MFT_OK) return s;
+    // window loss on the device: loss_acc += loss (the micro-batch means, unscaled, as the trainers sum them)
+    TRY(mft_add_f32(t->loss_acc, m->loss_dev, t->loss_acc, 1, c.st));
+    *stepped = 0;
+    if (++t->accum_counter < t->cfg.grad_accum_steps) return MFT_OK;
+    t->global_step += 1;
+    const float lr = mft_trainer_lr(&t->cfg, t->global_step);
+    TRY(mft_model_optimizer_step(m, lr, t->cfg.adam_beta1, t->cfg.adam_beta2, t->cfg.adam_eps, t->cfg.weight_decay, t->cfg.max_grad_norm, 1e-6f));
+    float sum = 0.f;
+    TRY(mft_memcpy_d2h(&sum, t->loss_acc, 4, c.st));             // the one read-back of the window (synchronises)
+    TRY(mft_memset(t->loss_acc, 0, 4, c.st));
+    t->accum_counter = 0;
+    *stepped = 1;
+    if (avg_loss) *avg_loss = sum / static_cast<float>(t->cfg.grad_accum_steps);
+    if (lr_used) *lr_used = lr;
+    return check_status(m);
 }
 
 extern "C" int32_t mft_model_zero_grad(mft_model_t* m) {

@@ -168,6 +168,48 @@ class LoraStepEngine:
         return L.call("mft_model_activation_bytes", self._h)
 
 
+class LoraTrainer:
+    """The step driver of the reference's trainers (GemmaLoRATrainer / LoRATrainer ::train_step) over a
+    LoraStepEngine: micro-batches accumulate gradients on the device with the loss scaled by 1/grad_accum_steps;
+    every grad_accum_steps-th call clips, sets the scheduled learning rate, runs Adam and clears the gradients."""
+
+    def __init__(self, engine: LoraStepEngine, *, learning_rate=2e-4, weight_decay=0.0, adam_beta1=0.9, adam_beta2=0.999,
+                 adam_eps=1e-8, max_grad_norm=1.0, lr_scheduler="linear", warmup_ratio=0.03, grad_accum_steps=1,
+                 num_sequences=None, micro_batch_size=1, num_epochs=3, total_updates=None):
+        if total_updates is None:
+            micro_per_epoch = (int(num_sequences) + micro_batch_size - 1) // micro_batch_size
+            total_updates = max(1, (micro_per_epoch * num_epochs + grad_accum_steps - 1) // grad_accum_steps)
+        self.engine = engine
+        self.cfg = L.TrainerConfig(learning_rate, weight_decay, adam_beta1, adam_beta2, adam_eps, max_grad_norm, warmup_ratio,
+                                   L.LR_SCHEDULERS[lr_scheduler], grad_accum_steps, total_updates)
+        h = C.c_void_p()
+        L.call("mft_trainer_create", engine._h, C.byref(self.cfg), C.byref(h))
+        self._h = h
+
+    def lr(self, step: int) -> float:
+        return L.call("mft_trainer_lr", C.byref(self.cfg), int(step))
+
+    @property
+    def global_step(self) -> int:
+        return L.call("mft_trainer_global_step", self._h)
+
+    def train_step(self, ids: np.ndarray, labels: np.ndarray, n_valid_global: int = 0):
+        """Returns the mean loss of the accumulation window when this call closed it, else -1.0 (as the reference)."""
+        b, s = ids.shape
+        ids = np.ascontiguousarray(ids, np.int32)
+        labels = np.ascontiguousarray(labels, np.int32)
+        stepped, loss, lr = C.c_int32(), C.c_float(), C.c_float()
+        L.call("mft_trainer_train_step", self._h, ids.ctypes.data, labels.ctypes.data, b, s, int(n_valid_global),
+               C.byref(stepped), C.byref(loss), C.byref(lr))
+        self.last_lr = lr.value if stepped.value else None
+        return loss.value if stepped.value else -1.0
+
+    def close(self):
+        if self._h:
+            L.call("mft_trainer_destroy", self._h)
+            self._h = None
+
+
 def _as_tensor(ptr: int, n: int, device: int) -> torch.Tensor:
     """Wrap device memory owned by the engine as a 1-D float32 torch tensor (no copy)."""
     class _Holder:

@@ -279,3 +279,21 @@ def embedding(ids, table, scale=1.0, pos_table=None):
     if pos_table is not None:
         out = out + pos_table[np.arange(ids.shape[1])][None, :, :]
     return out.astype(f32)
+
+
+def trainer_lr(step, learning_rate, warmup_ratio, lr_scheduler, total_updates):
+    """get_lr of the trainers (optim/gemma_trainer.cpp:44-62, optim/trainer.cpp:46-73) for optimizer step `step`
+    (1-based), with float32 arithmetic where the reference uses float.  `lr_scheduler`: "linear", "cosine" or any
+    other name (GemmaLoRATrainer: linear; LoRATrainer: constant after the warm-up -> pass "constant")."""
+    f = np.float32
+    total = max(1, int(total_updates))
+    warmup_steps = int(f(total) * f(warmup_ratio))          # int64 * float -> float, truncated
+    if warmup_steps > 0 and step <= warmup_steps:
+        return float(f(learning_rate) * (f(step) / f(warmup_steps)))
+    progress = f(step - warmup_steps) / f(max(1, total - warmup_steps))
+    progress = min(max(progress, f(0)), f(1))
+    if lr_scheduler == "cosine":
+        return float(f(learning_rate) * f(0.5) * (f(1) + f(np.cos(f(3.14159265) * progress))))
+    if lr_scheduler == "linear":
+        return float(f(learning_rate) * (f(1) - progress))
+    return float(f(learning_rate))

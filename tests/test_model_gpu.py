@@ -154,6 +154,52 @@ def test_data_parallel_shards_add_up_to_the_full_batch():
     eng.close()
 
 
+def test_step_driver_accumulates_clips_and_schedules_like_the_trainers():
+    """LoraTrainer.train_step == the trainers' loop body: two micro-batches with the loss scaled by 1/2 accumulate,
+    the call that closes the window clips with max/(norm + 1e-6), takes the scheduled learning rate and steps Adam.
+    Compared with the same sequence issued by hand through the step engine (itself pinned to the reference)."""
+    from mobilefinetuner_b200 import _lib as L, synth
+    from mobilefinetuner_b200.engine import LoraStepEngine, LoraTrainer
+    from oracle import restate as R
+    case = CASES["gemma_tiny"]
+    spec = case["spec"]
+    B, S = case["batch"], case["seq"]
+    params, lora = synth.make_params(spec, 1, 0.1), synth.make_lora(spec, 2)
+    batches = [synth.make_batch(spec, B, S, 10 + k) for k in range(4)]
+    sched = dict(learning_rate=3e-4, warmup_ratio=0.5, lr_scheduler="cosine", total_updates=4)
+
+    eng = LoraStepEngine(spec, B, S)
+    eng.set_params(params); eng.set_lora(lora)
+    tr = LoraTrainer(eng, grad_accum_steps=2, max_grad_norm=0.05, weight_decay=0.01, **sched)
+    seen = [tr.train_step(*batches[k]) for k in range(4)]
+    assert seen[0] == -1.0 and seen[2] == -1.0 and seen[1] > 0 and seen[3] > 0
+    assert tr.global_step == 2
+    assert abs(tr.last_lr - R.trainer_lr(2, 3e-4, 0.5, "cosine", 4)) <= 1e-10
+    got = eng.get_lora()
+    tr.close(); eng.close()
+
+    ref = LoraStepEngine(spec, B, S)
+    ref.set_params(params); ref.set_lora(lora)
+    losses = []
+    for step in (1, 2):
+        L.call("mft_model_set_loss_scale", ref._h, 0.5)
+        for k in (2 * step - 2, 2 * step - 1):
+            losses.append(ref.forward_backward(*batches[k])[0])
+        L.call("mft_model_optimizer_step", ref._h, R.trainer_lr(step, 3e-4, 0.5, "cosine", 4), 0.9, 0.999, 1e-8, 0.01, 0.05, 1e-6)
+    want = ref.get_lora()
+    ref.close()
+    assert abs(seen[1] - 0.5 * (losses[0] + losses[1])) <= 1e-5 * abs(seen[1])
+    assert abs(seen[3] - 0.5 * (losses[2] + losses[3])) <= 1e-5 * abs(seen[3])
+    # Two runs of the same step are not bit-identical (f32 atomics in the LoRA-gradient and dK/dV reductions), and
+    # Adam's early steps move an element by about lr * sign(g): an element whose tiny gradient changes sign between
+    # the runs differs by up to 2 lr per step.  Everything else agrees to rounding.
+    lr_max = 3e-4
+    for a, b in zip(got, want):
+        d = np.abs(a - b)
+        assert d.max() <= 2 * 2.1 * lr_max
+        assert (d <= 1e-6 + 1e-4 * np.abs(b).max()).mean() >= 0.99
+
+
 def test_out_of_range_token_raises():
     from mobilefinetuner_b200 import synth
     from mobilefinetuner_b200._lib import MftError
