@@ -96,6 +96,24 @@ int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t* ids_dev, c
 /* Forward only: mean loss for a batch (evaluation). */
 int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_host, const int32_t* labels_host,
                                int32_t batch, int32_t seq, float* loss_host);
+/* ---- evaluation drivers (no gradients, same forward kernels).
+ * Perplexity, the loop body of examples/gpt2_small_lora_finetune/src/eval_ppl.cpp:170-210: one batch's mean loss
+ * is weighted by the number of labels != -100 in the WHOLE labels tensor (the reference counts them unshifted),
+ * summed in double; mean_nll = sum_loss / sum_tokens, ppl = expf(mean_nll). */
+typedef struct {
+    double sum_loss;
+    int64_t sum_tokens;
+    int64_t n_batches;
+} mft_ppl_accum_t;
+int32_t mft_model_eval_ppl_batch(mft_model_t* m, mft_ppl_accum_t* acc, const int32_t* ids_host, const int32_t* labels_host,
+                                 int32_t batch, int32_t seq);
+int32_t mft_ppl_result(const mft_ppl_accum_t* acc, float* mean_nll, float* ppl);
+/* Letter scoring, MMLURunner::predict_letter (examples/common/mmlu/mmlu_runner.cpp:141-192): forward of ONE prompt
+ * (seq >= 2 token ids), log_softmax of the logits at its last position, read at n_cand candidate token ids
+ * (<= 64).  logprob_host[c] = log p(cand[c] | prompt); an id outside the vocabulary gets -1e30 as in the
+ * reference.  The [seq, V] logits are never formed: only the last position is projected. */
+int32_t mft_model_score_tokens(mft_model_t* m, const int32_t* ids_host, int32_t seq, const int32_t* cand_host,
+                               int32_t n_cand, float* logprob_host);
 /* clip (max_norm <= 0: none; clip_eps 0 = Optimizer::clip_grad_norm, 1e-6 = trainers) + Adam + zero_grad. */
 int32_t mft_model_optimizer_step(mft_model_t* m, float lr, float beta1, float beta2, float eps,
                                  float weight_decay, float max_norm, float clip_eps);

@@ -38,6 +38,11 @@ class TrainerConfig(C.Structure):
 LR_SCHEDULERS = {"linear": 0, "cosine": 1, "constant": 2}
 
 
+class PplAccum(C.Structure):
+    """mft_ppl_accum_t of include/mft_step.h."""
+    _fields_ = [("sum_loss", C.c_double), ("sum_tokens", C.c_int64), ("n_batches", C.c_int64)]
+
+
 class ModelConfig(C.Structure):
     """mft_model_config_t of include/mft_step.h."""
     _fields_ = [("family", C.c_int32), ("vocab", C.c_int32), ("hidden", C.c_int32), ("inter", C.c_int32),
@@ -137,6 +142,9 @@ _SIGS = {
     "mft_model_optimizer_step": [vp, f32, f32, f32, f32, f32, f32, f32],
     "mft_model_zero_grad": [vp],
     "mft_model_set_loss_scale": [vp, f32],
+    "mft_model_eval_ppl_batch": [vp, vp, vp, vp, i32, i32],
+    "mft_ppl_result": [vp, vp, vp],
+    "mft_model_score_tokens": [vp, vp, i32, vp, i32, vp],
     "mft_trainer_lr": [vp, i64],
     "mft_trainer_create": [vp, vp, vp],
     "mft_trainer_destroy": [vp],

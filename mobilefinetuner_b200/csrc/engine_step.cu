@@ -313,6 +313,66 @@ extern "C" int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_hos
     return check_status(m);
 }
 
+extern "C" int32_t mft_model_eval_ppl_batch(mft_model_t* m, mft_ppl_accum_t* acc, const int32_t* ids_host, const int32_t* labels_host,
+                                            int32_t batch, int32_t seq) {
+    MFT_CHECK_ARG(m && acc && ids_host && labels_host, "mft_model_eval_ppl_batch: null argument");
+    float loss_val = 0.f;
+    TRY(mft_model_forward_loss(m, ids_host, labels_host, batch, seq, &loss_val));
+    int64_t valid = 0;
+    for (int64_t i = 0; i < (int64_t)batch * seq; ++i)
+        if (labels_host[i] != -100) valid++;
+    acc->sum_loss += loss_val * valid;      // float * int64 -> float, then widened: the reference's expression
+    acc->sum_tokens += valid;
+    acc->n_batches += 1;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_ppl_result(const mft_ppl_accum_t* acc, float* mean_nll, float* ppl) {
+    MFT_CHECK_ARG(acc && mean_nll && ppl, "mft_ppl_result: null argument");
+    *mean_nll = acc->sum_tokens > 0 ? (float)(acc->sum_loss / (double)acc->sum_tokens) : 0.0f;
+    *ppl = std::exp(*mean_nll);
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_model_score_tokens(mft_model_t* m, const int32_t* ids_host, int32_t seq, const int32_t* cand_host,
+                                          int32_t n_cand, float* logprob_host) {
+    MFT_CHECK_ARG(m && ids_host && cand_host && logprob_host && n_cand > 0 && n_cand <= 64, "mft_model_score_tokens: bad argument");
+    Ctx c;
+    TRY(make_ctx(m, 1, seq, &c));
+    const int64_t H = m->cfg.hidden, V = m->cfg.vocab;
+    TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)seq * 4, c.st));
+    TRY(mft_memcpy_h2d(m->labels, ids_host, (size_t)seq * 4, c.st));      // any valid labels: the loss is not used
+    TRY(forward(c, false));
+    // scratch inside the staging buffer: candidate rows (f32, then bf16), the last hidden row twice, logits, ids
+    MFT_CHECK_ARG((64 + 2) * H * 2 + 1024 <= m->stage_floats - 64, "mft_model_score_tokens: staging buffer too small");
+    float* rows_f32 = m->stage_f32;
+    bf16* rows_bf16 = reinterpret_cast<bf16*>(rows_f32 + 64 * H);
+    bf16* pair = rows_bf16 + 64 * H;
+    float* logits = reinterpret_cast<float*>(pair + 2 * H + 64);
+    float* lse = logits + 64;
+    float* loss_tmp = lse + 8;
+    int32_t* ints = reinterpret_cast<int32_t*>(loss_tmp + 8);                 // cand[64], labels2[2], n_valid[1]
+    int32_t cand_clean[64], labels2[2] = {0, 0};
+    for (int i = 0; i < n_cand; ++i) cand_clean[i] = (cand_host[i] >= 0 && cand_host[i] < V) ? cand_host[i] : 0;
+    TRY(mft_memcpy_h2d(ints, cand_clean, (size_t)n_cand * 4, c.st));
+    TRY(mft_memcpy_h2d(ints + 64, labels2, 8, c.st));
+    TRY(mft_embedding_gather(ints, m->embed, nullptr, rows_f32, n_cand, 1, H, V, 1.0f, m->status_dev, c.st));
+    TRY(mft_cast_f32_to_bf16(rows_f32, rows_bf16, (int64_t)n_cand * H, c.st));
+    const bf16* h_last = m->hf + (int64_t)(seq - 1) * H;
+    TRY(mft_memcpy_d2d(pair, h_last, (size_t)H * 2, c.st));
+    TRY(mft_memcpy_d2d(pair + H, h_last, (size_t)H * 2, c.st));
+    TRY(mft_gemm_nt(h_last, H, rows_bf16, H, 1, n_cand, H, nullptr, 0, nullptr, 0, 0, nullptr, 1.0f, logits, 64, MFT_F32, 0, c.st));
+    // log-sum-exp of the last position over the whole vocabulary: row 0 of a 1 x 2 "batch" made of that row twice
+    TRY(mft_lmhead_ce_fwd(pair, m->embed, ints + 64, 1, 2, H, V, -100, loss_tmp, ints + 66, lse, m->status_dev, m->ce_ws, m->ce_ws_bytes, c.st));
+    float logits_host[64], lse_host = 0.f;
+    TRY(mft_memcpy_d2h(logits_host, logits, (size_t)n_cand * 4, c.st));
+    TRY(mft_memcpy_d2h(&lse_host, lse, 4, c.st));
+    TRY(check_status(m));
+    for (int i = 0; i < n_cand; ++i)
+        logprob_host[i] = (cand_host[i] >= 0 && cand_host[i] < V) ? logits_host[i] - lse_host : -1e30f;
+    return MFT_OK;
+}
+
 extern "C" int32_t mft_model_optimizer_step(mft_model_t* m, float lr, float beta1, float beta2, float eps, float weight_decay,
                                             float max_norm, float clip_eps) {
     MFT_CHECK_ARG(m, "mft_model_optimizer_step: null model");

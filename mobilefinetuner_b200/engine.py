@@ -141,6 +141,27 @@ class LoraStepEngine:
         L.call("mft_model_forward_loss", self._h, ids.ctypes.data, labels.ctypes.data, b, s, C.byref(loss))
         return loss.value
 
+    # ---- evaluation drivers
+    def perplexity(self, batches):
+        """eval_ppl of the reference over an iterable of (ids, labels): returns (mean_nll, ppl, tokens)."""
+        acc = L.PplAccum(0.0, 0, 0)
+        for ids, labels in batches:
+            b, s = ids.shape
+            ids = np.ascontiguousarray(ids, np.int32)
+            labels = np.ascontiguousarray(labels, np.int32)
+            L.call("mft_model_eval_ppl_batch", self._h, C.byref(acc), ids.ctypes.data, labels.ctypes.data, b, s)
+        nll, ppl = C.c_float(), C.c_float()
+        L.call("mft_ppl_result", C.byref(acc), C.byref(nll), C.byref(ppl))
+        return nll.value, ppl.value, acc.sum_tokens
+
+    def score_tokens(self, prompt_ids, candidate_ids) -> np.ndarray:
+        """log p(candidate | prompt) at the prompt's last position (MMLU letter scoring)."""
+        ids = np.ascontiguousarray(prompt_ids, np.int32).ravel()
+        cand = np.ascontiguousarray(candidate_ids, np.int32).ravel()
+        out = np.empty(cand.size, np.float32)
+        L.call("mft_model_score_tokens", self._h, ids.ctypes.data, ids.size, cand.ctypes.data, cand.size, out.ctypes.data)
+        return out
+
     def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, max_grad_norm=0.0, clip_eps=0.0):
         L.call("mft_model_optimizer_step", self._h, float(lr), float(beta1), float(beta2), float(eps), float(weight_decay),
                float(max_grad_norm), float(clip_eps))

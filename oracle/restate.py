@@ -297,3 +297,16 @@ def trainer_lr(step, learning_rate, warmup_ratio, lr_scheduler, total_updates):
     if lr_scheduler == "linear":
         return float(f(learning_rate) * (f(1) - progress))
     return float(f(learning_rate))
+
+
+def ppl_accumulate(batch_losses, batch_labels):
+    """Aggregation of examples/gpt2_small_lora_finetune/src/eval_ppl.cpp:166-210: each batch's float mean loss is
+    weighted by the count of labels != -100 in the whole (unshifted) labels tensor, float * int64 -> float, summed
+    in double; returns (mean_nll float32, ppl = exp(mean_nll) float32, tokens)."""
+    sum_loss, sum_tokens = 0.0, 0
+    for loss, labels in zip(batch_losses, batch_labels):
+        valid = int((np.asarray(labels) != -100).sum())
+        sum_loss += float(np.float32(loss) * np.float32(valid))
+        sum_tokens += valid
+    mean_nll = np.float32(sum_loss / sum_tokens) if sum_tokens > 0 else np.float32(0)
+    return float(mean_nll), float(np.exp(mean_nll, dtype=np.float32)), sum_tokens

@@ -200,6 +200,41 @@ def test_step_driver_accumulates_clips_and_schedules_like_the_trainers():
         assert (d <= 1e-6 + 1e-4 * np.abs(b).max()).mean() >= 0.99
 
 
+def test_evaluation_drivers_perplexity_and_letter_scores():
+    """eval_ppl aggregation over batches and MMLU-style letter scoring (log_softmax of the last position read at the
+    candidate ids), against the restated aggregation and a float64 projection of the engine's own final hidden state."""
+    from mobilefinetuner_b200 import synth
+    from mobilefinetuner_b200.engine import LoraStepEngine
+    from oracle import restate as R
+    case = CASES["qwen_tiny"]
+    spec = case["spec"]
+    B, S = case["batch"], case["seq"]
+    params = synth.make_params(spec, 1, 0.1)
+    eng = LoraStepEngine(spec, B, S)
+    eng.set_params(params); eng.set_lora(synth.make_lora(spec, 2))
+    batches = []
+    for k in range(3):
+        ids, labels = synth.make_batch(spec, B, S, 20 + k)
+        labels = labels.copy(); labels[0, : 3 + k] = -100
+        batches.append((ids, labels))
+    nll, ppl, tokens = eng.perplexity(batches)
+    losses = [eng.forward_loss(i, l) for i, l in batches]
+    w_nll, w_ppl, w_tokens = R.ppl_accumulate(losses, [l for _, l in batches])
+    assert tokens == w_tokens and abs(nll - w_nll) <= 1e-6 * w_nll and abs(ppl - w_ppl) <= 1e-5 * w_ppl
+
+    prompt = batches[0][0][0, : S - 3]
+    cand = np.array([5, 17, spec.vocab - 1, 0, spec.vocab + 3], np.int32)     # the last id is outside the vocabulary
+    got = eng.score_tokens(prompt, cand)
+    hidden = eng.final_hidden(prompt.size)[-1].astype(np.float64)              # final-norm output of the last position (bf16 values)
+    import torch
+    table = torch.from_numpy(params[0]).bfloat16().double().numpy()           # the tied table as the GPU holds it
+    logits = table @ hidden
+    logp = logits - (np.log(np.exp(logits - logits.max()).sum()) + logits.max())
+    assert got[4] == np.float32(-1e30)
+    np.testing.assert_allclose(got[:4], logp[cand[:4]], rtol=0, atol=2e-3)
+    eng.close()
+
+
 def test_out_of_range_token_raises():
     from mobilefinetuner_b200 import synth
     from mobilefinetuner_b200._lib import MftError

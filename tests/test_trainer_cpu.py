@@ -41,3 +41,26 @@ def test_total_updates_formula_of_the_wrapper():
         L.call = orig
     assert made["cfg"].total_updates == (251 * 3 + 7) // 8
     assert made["cfg"].grad_accum_steps == 8
+
+
+def test_perplexity_result_matches_the_reference_aggregation():
+    """mft_ppl_result is host arithmetic: sum of loss * count in double, float mean, expf."""
+    import numpy as np
+    from mobilefinetuner_b200 import _lib as L
+    g = np.random.Generator(np.random.PCG64(5))
+    losses = g.uniform(2.0, 11.0, 7).astype(np.float32)
+    labels = [np.where(g.random((3, 40)) < 0.2, -100, 5).astype(np.int32) for _ in losses]
+    acc = L.PplAccum(0.0, 0, 0)
+    for loss, lab in zip(losses, labels):          # what mft_model_eval_ppl_batch adds per batch
+        valid = int((lab != -100).sum())
+        acc.sum_loss += float(np.float32(loss) * np.float32(valid))
+        acc.sum_tokens += valid
+        acc.n_batches += 1
+    nll, ppl = C.c_float(), C.c_float()
+    L.call("mft_ppl_result", C.byref(acc), C.byref(nll), C.byref(ppl))
+    w_nll, w_ppl, w_tokens = R.ppl_accumulate(losses, labels)
+    assert acc.sum_tokens == w_tokens
+    assert abs(nll.value - w_nll) <= 1e-6 * w_nll and abs(ppl.value - w_ppl) <= 2e-6 * w_ppl
+    empty = L.PplAccum(0.0, 0, 0)
+    L.call("mft_ppl_result", C.byref(empty), C.byref(nll), C.byref(ppl))
+    assert nll.value == 0.0 and ppl.value == 1.0
