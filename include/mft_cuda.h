@@ -64,6 +64,9 @@ int32_t mft_empty_cache(void);
 /* stats_host[0..3] = bytes in use, bytes cached, peak bytes in use, #cudaMalloc calls */
 int32_t mft_mem_stats(int64_t* stats_host);
 int32_t mft_memcpy_h2d(void* dst, const void* src_host, size_t bytes, mft_stream_t stream);
+/* Page-locked host memory (asynchronous copies need it to overlap with kernels). */
+int32_t mft_host_alloc(size_t bytes, void** out_host);
+int32_t mft_host_free(void* host);
 int32_t mft_memcpy_d2h(void* dst_host, const void* src, size_t bytes, mft_stream_t stream);
 int32_t mft_memcpy_d2d(void* dst, const void* src, size_t bytes, mft_stream_t stream);
 int32_t mft_memset(void* dst, int32_t byte_value, size_t bytes, mft_stream_t stream);

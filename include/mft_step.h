@@ -96,6 +96,22 @@ int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t* ids_dev, c
 /* Forward only: mean loss for a batch (evaluation). */
 int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_host, const int32_t* labels_host,
                                int32_t batch, int32_t seq, float* loss_host);
+/* ---- double-buffered input (the Batch tensors of WikiText2Dataset::get_batch, data/wikitext2_dataset.cpp:451-519,
+ *      are rebuilt in the same host buffers for every batch): batch k+1 is copied to the device on a copy stream
+ *      while step k computes, and the loss of step k is read back without stalling step k+1.
+ *      mft_model_stage_batch(slot): asynchronous copy of ids / labels ([batch, seq] int32, PAGE-LOCKED host memory,
+ *      e.g. from mft_host_alloc) into device slot 0 or 1; the host buffers may be refilled once
+ *      mft_model_stage_wait(slot) returned (or after the step that consumes the slot was queued and synchronised).
+ *      mft_model_step_staged(slot): forward + backward on the staged batch; the mean loss and the count of scored
+ *      tokens are copied asynchronously to page-locked host words that are valid after mft_model_sync (or after
+ *      any later synchronising call on the model). */
+int32_t mft_model_stage_batch(mft_model_t* m, int32_t slot, const int32_t* ids_pinned, const int32_t* labels_pinned,
+                              int32_t batch, int32_t seq);
+int32_t mft_model_stage_wait(mft_model_t* m, int32_t slot);
+int32_t mft_model_step_staged(mft_model_t* m, int32_t slot, int32_t batch, int32_t seq, int64_t n_valid_global,
+                              float* loss_pinned, int32_t* n_valid_pinned);
+int32_t mft_model_sync(mft_model_t* m);
+
 /* ---- evaluation drivers (no gradients, same forward kernels).
  * Perplexity, the loop body of examples/gpt2_small_lora_finetune/src/eval_ppl.cpp:170-210: one batch's mean loss
  * is weighted by the number of labels != -100 in the WHOLE labels tensor (the reference counts them unshifted),

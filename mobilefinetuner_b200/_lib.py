@@ -69,6 +69,8 @@ _SIGS = {
     "mft_free": [vp],
     "mft_empty_cache": [],
     "mft_mem_stats": [C.POINTER(i64)],
+    "mft_host_alloc": [C.c_size_t, vp],
+    "mft_host_free": [vp],
     "mft_memcpy_h2d": [vp, vp, sz, vp],
     "mft_memcpy_d2h": [vp, vp, sz, vp],
     "mft_memcpy_d2d": [vp, vp, sz, vp],
@@ -142,6 +144,10 @@ _SIGS = {
     "mft_model_optimizer_step": [vp, f32, f32, f32, f32, f32, f32, f32],
     "mft_model_zero_grad": [vp],
     "mft_model_set_loss_scale": [vp, f32],
+    "mft_model_stage_batch": [vp, i32, vp, vp, i32, i32],
+    "mft_model_stage_wait": [vp, i32],
+    "mft_model_step_staged": [vp, i32, i32, i32, i64, vp, vp],
+    "mft_model_sync": [vp],
     "mft_model_eval_ppl_batch": [vp, vp, vp, vp, i32, i32],
     "mft_ppl_result": [vp, vp, vp],
     "mft_model_score_tokens": [vp, vp, i32, vp, i32, vp],

@@ -92,6 +92,11 @@ extern "C" int32_t mft_model_destroy(mft_model_t* m) {
     if (m->graph_in) cudaEventDestroy(m->graph_in);
     if (m->graph_out) cudaEventDestroy(m->graph_out);
     if (m->graph_stream) cudaStreamDestroy(m->graph_stream);
+    if (m->copy_stream) { cudaStreamSynchronize(m->copy_stream); cudaStreamDestroy(m->copy_stream); }
+    for (int i = 0; i < 2; ++i) {
+        if (m->slot_ready[i]) cudaEventDestroy(m->slot_ready[i]);
+        if (m->slot_free[i]) cudaEventDestroy(m->slot_free[i]);
+    }
     for (void* p : m->allocations) mft_free(p);
     delete m;
     return MFT_OK;

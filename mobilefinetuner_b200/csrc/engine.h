@@ -105,6 +105,11 @@ struct mft_model {
     // Replay of the training step as a CUDA graph: the launches of one step are issued faster than the host can
     // make them one by one (tensor-map encodes + ~1100 launches per step).  Captured on a private stream that is
     // ordered against `stream` with events.  MFT_STEP_GRAPH=0 disables it.
+    // double-buffered input: two device slots filled on a copy stream
+    cudaStream_t copy_stream = nullptr;
+    int32_t* slot_ids[2] = {nullptr, nullptr};
+    int32_t* slot_labels[2] = {nullptr, nullptr};
+    cudaEvent_t slot_ready[2] = {nullptr, nullptr}, slot_free[2] = {nullptr, nullptr};
     float loss_scale = 1.0f;         // d(loss) of the next backward passes (1 / grad_accum_steps under a step driver)
     bool use_graph = true;
     cudaStream_t graph_stream = nullptr;

@@ -313,6 +313,61 @@ extern "C" int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_hos
     return check_status(m);
 }
 
+// ---------------------------------------------------------------- double-buffered input
+static int32_t ensure_slots(mft_model* m) {
+    if (m->copy_stream) return MFT_OK;
+    if (int32_t s = check_cuda(cudaStreamCreateWithFlags(&m->copy_stream, cudaStreamNonBlocking), "copy stream")) return s;
+    for (int i = 0; i < 2; ++i) {
+        void* p = nullptr;
+        TRY(mft_malloc((size_t)m->max_tokens * 4, &p)); m->slot_ids[i] = static_cast<int32_t*>(p); m->allocations.push_back(p);
+        TRY(mft_malloc((size_t)m->max_tokens * 4, &p)); m->slot_labels[i] = static_cast<int32_t*>(p); m->allocations.push_back(p);
+        if (int32_t s = check_cuda(cudaEventCreateWithFlags(&m->slot_ready[i], cudaEventDisableTiming), "slot event")) return s;
+        if (int32_t s = check_cuda(cudaEventCreateWithFlags(&m->slot_free[i], cudaEventDisableTiming), "slot event")) return s;
+    }
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_model_stage_batch(mft_model_t* m, int32_t slot, const int32_t* ids_pinned, const int32_t* labels_pinned,
+                                         int32_t batch, int32_t seq) {
+    MFT_CHECK_ARG(m && (slot == 0 || slot == 1) && ids_pinned && labels_pinned, "mft_model_stage_batch: bad argument");
+    Ctx c;
+    TRY(make_ctx(m, batch, seq, &c));
+    TRY(ensure_slots(m));
+    // the step that last consumed this slot must have copied it out before it is overwritten
+    if (int32_t s = check_cuda(cudaStreamWaitEvent(m->copy_stream, m->slot_free[slot], 0), "slot wait")) return s;
+    TRY(mft_memcpy_h2d(m->slot_ids[slot], ids_pinned, (size_t)c.T * 4, m->copy_stream));
+    TRY(mft_memcpy_h2d(m->slot_labels[slot], labels_pinned, (size_t)c.T * 4, m->copy_stream));
+    return check_cuda(cudaEventRecord(m->slot_ready[slot], m->copy_stream), "slot event");
+}
+
+extern "C" int32_t mft_model_stage_wait(mft_model_t* m, int32_t slot) {
+    MFT_CHECK_ARG(m && (slot == 0 || slot == 1) && m->copy_stream, "mft_model_stage_wait: nothing was staged");
+    return check_cuda(cudaEventSynchronize(m->slot_ready[slot]), "slot wait");
+}
+
+extern "C" int32_t mft_model_step_staged(mft_model_t* m, int32_t slot, int32_t batch, int32_t seq, int64_t n_valid_global,
+                                         float* loss_pinned, int32_t* n_valid_pinned) {
+    MFT_CHECK_ARG(m && (slot == 0 || slot == 1) && m->copy_stream, "mft_model_step_staged: nothing was staged");
+    Ctx c;
+    TRY(make_ctx(m, batch, seq, &c));
+    if (int32_t s = check_cuda(cudaStreamWaitEvent(m->stream, m->slot_ready[slot], 0), "slot wait")) return s;
+    TRY(mft_memcpy_d2d(m->ids, m->slot_ids[slot], (size_t)c.T * 4, c.st));
+    TRY(mft_memcpy_d2d(m->labels, m->slot_labels[slot], (size_t)c.T * 4, c.st));
+    if (int32_t s = check_cuda(cudaEventRecord(m->slot_free[slot], m->stream), "slot event")) return s;
+    TRY(forward_backward(c, n_valid_global));
+    if (loss_pinned)
+        if (int32_t s = check_cuda(cudaMemcpyAsync(loss_pinned, m->loss_dev, 4, cudaMemcpyDeviceToHost, m->stream), "loss copy")) return s;
+    if (n_valid_pinned)
+        if (int32_t s = check_cuda(cudaMemcpyAsync(n_valid_pinned, m->n_valid_dev, 4, cudaMemcpyDeviceToHost, m->stream), "count copy")) return s;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_model_sync(mft_model_t* m) {
+    MFT_CHECK_ARG(m, "mft_model_sync: null model");
+    if (int32_t s = check_cuda(cudaStreamSynchronize(m->stream), "model sync")) return s;
+    return check_status(m);
+}
+
 extern "C" int32_t mft_model_eval_ppl_batch(mft_model_t* m, mft_ppl_accum_t* acc, const int32_t* ids_host, const int32_t* labels_host,
                                             int32_t batch, int32_t seq) {
     MFT_CHECK_ARG(m && acc && ids_host && labels_host, "mft_model_eval_ppl_batch: null argument");

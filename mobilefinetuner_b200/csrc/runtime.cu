@@ -186,6 +186,11 @@ int32_t mft_memcpy_d2h(void* dst, const void* src, size_t bytes, mft_stream_t st
     if (int32_t s = check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, as_stream(stream)), "memcpy d2h")) return s;
     return check_cuda(cudaStreamSynchronize(as_stream(stream)), "memcpy d2h sync");
 }
+int32_t mft_host_alloc(size_t bytes, void** out_host) {
+    MFT_CHECK_ARG(out_host && bytes > 0, "mft_host_alloc: bad argument");
+    return check_cuda(cudaHostAlloc(out_host, bytes, cudaHostAllocDefault), "pinned host allocation");
+}
+int32_t mft_host_free(void* host) { return host ? check_cuda(cudaFreeHost(host), "pinned host free") : MFT_OK; }
 int32_t mft_memcpy_d2d(void* dst, const void* src, size_t bytes, mft_stream_t stream) {
     return check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, as_stream(stream)), "memcpy d2d");
 }

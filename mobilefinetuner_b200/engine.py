@@ -231,6 +231,66 @@ class LoraTrainer:
             self._h = None
 
 
+class BatchPipeline:
+    """Double-buffered input for a LoraStepEngine: while step k computes, batch k+1 is copied from page-locked host
+    buffers to the device on a copy stream, and the loss of step k is read back one step later, so the GPU never
+    waits for the host between steps.  The host buffers play the role of the reusable Batch buffers of
+    WikiText2Dataset::get_batch."""
+
+    def __init__(self, engine: LoraStepEngine, batch: int, seq: int):
+        self.engine, self.batch, self.seq = engine, batch, seq
+        n = batch * seq
+        self.ids = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.labels = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.loss = torch.zeros(2, dtype=torch.float32).pin_memory()
+        self.n_valid = torch.zeros(2, dtype=torch.int32).pin_memory()
+
+    def _stage(self, slot, ids, labels):
+        self.ids[slot].copy_(torch.from_numpy(np.ascontiguousarray(ids, np.int32).ravel()))
+        self.labels[slot].copy_(torch.from_numpy(np.ascontiguousarray(labels, np.int32).ravel()))
+        L.call("mft_model_stage_batch", self.engine._h, slot, self.ids[slot].data_ptr(), self.labels[slot].data_ptr(),
+               self.batch, self.seq)
+
+    def run(self, batches, after_backward=None, n_valid_global=0):
+        """Runs forward + backward on every (ids, labels) of `batches`; `after_backward(k)` (e.g. the optimizer step)
+        is queued right after step k.  Yields (k, loss, n_valid) for every step, one step late."""
+        h = self.engine._h
+        it = iter(batches)
+        try:
+            first = next(it)
+        except StopIteration:
+            return
+        self._stage(0, *first)
+        done, pending, used = None, None, [True, False]
+        k, slot = 0, 0
+        while True:
+            nxt = next(it, None)
+            L.call("mft_model_step_staged", h, slot, self.batch, self.seq, int(n_valid_global),
+                   self.loss[slot:].data_ptr(), self.n_valid[slot:].data_ptr())
+            ev = torch.cuda.Event()
+            ev.record()
+            if after_backward is not None:
+                after_backward(k)
+            if nxt is not None:
+                other = slot ^ 1
+                if used[other]:
+                    L.call("mft_model_stage_wait", h, other)      # its previous copy has left the host buffers
+                self._stage(other, *nxt)
+                used[other] = True
+            if pending is not None:                               # results of the step before: already complete or nearly
+                pk, pslot, pev = pending
+                pev.synchronize()
+                yield pk, float(self.loss[pslot]), int(self.n_valid[pslot])
+            pending = (k, slot, ev)
+            if nxt is None:
+                break
+            k, slot = k + 1, slot ^ 1
+        pk, pslot, pev = pending
+        pev.synchronize()
+        L.call("mft_model_sync", h)
+        yield pk, float(self.loss[pslot]), int(self.n_valid[pslot])
+
+
 def _as_tensor(ptr: int, n: int, device: int) -> torch.Tensor:
     """Wrap device memory owned by the engine as a 1-D float32 torch tensor (no copy)."""
     class _Holder:

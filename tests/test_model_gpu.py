@@ -200,6 +200,44 @@ def test_step_driver_accumulates_clips_and_schedules_like_the_trainers():
         assert (d <= 1e-6 + 1e-4 * np.abs(b).max()).mean() >= 0.99
 
 
+def test_double_buffered_input_gives_the_same_steps():
+    """BatchPipeline (next batch copied on a copy stream during the current step, loss read back one step late)
+    against the plain one-call-per-step path: same losses, same scored-token counts, same parameters."""
+    from mobilefinetuner_b200 import synth
+    from mobilefinetuner_b200.engine import BatchPipeline, LoraStepEngine
+    case = CASES["gemma_tiny"]
+    spec = case["spec"]
+    B, S = case["batch"], case["seq"]
+    params, lora = synth.make_params(spec, 1, 0.1), synth.make_lora(spec, 2)
+    batches = []
+    for k in range(5):
+        ids, labels = synth.make_batch(spec, B, S, 40 + k)
+        labels = labels.copy(); labels[0, S - 1 - k:] = -100
+        batches.append((ids, labels))
+
+    plain = LoraStepEngine(spec, B, S)
+    plain.set_params(params); plain.set_lora(lora)
+    want = []
+    for ids, labels in batches:
+        want.append(plain.forward_backward(ids, labels))
+        plain.optimizer_step(1e-4, max_grad_norm=1.0)
+    want_lora = plain.get_lora()
+    plain.close()
+
+    eng = LoraStepEngine(spec, B, S)
+    eng.set_params(params); eng.set_lora(lora)
+    pipe = BatchPipeline(eng, B, S)
+    got = list(pipe.run(batches, after_backward=lambda k: eng.optimizer_step(1e-4, max_grad_norm=1.0)))
+    got_lora = eng.get_lora()
+    eng.close()
+    assert [g[0] for g in got] == list(range(5))
+    for (k, loss, nv), (wloss, wnv) in zip(got, want):
+        assert nv == wnv and abs(loss - wloss) <= 2e-4 * abs(wloss), (k, loss, wloss)
+    for a, b in zip(got_lora, want_lora):
+        d = np.abs(a - b)
+        assert d.max() <= 5 * 2.1 * 1e-4 and (d <= 1e-6 + 1e-4 * np.abs(b).max()).mean() >= 0.98
+
+
 def test_evaluation_drivers_perplexity_and_letter_scores():
     """eval_ppl aggregation over batches and MMLU-style letter scoring (log_softmax of the last position read at the
     candidate ids), against the restated aggregation and a float64 projection of the engine's own final hidden state."""
