@@ -96,6 +96,35 @@ int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t* ids_dev, c
 /* Forward only: mean loss for a batch (evaluation). */
 int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_host, const int32_t* labels_host,
                                int32_t batch, int32_t seq, float* loss_host);
+/* ---- SafeTensors ingest and adapter files (host code; SafeTensorsReader / SafeTensorsModelReader
+ *      graph/safetensors_loader.h:35-124, key mappers graph/safetensors_loader.cpp:470-590, LoraSaver
+ *      graph/lora_saver.cpp:123-198, GemmaLoraInjector::save_lora_safetensors graph/gemma_lora_injector.cpp:179-264).
+ * A container is one .safetensors file, a directory holding model.safetensors, or a sharded HuggingFace snapshot
+ * (model.safetensors.index.json).  F32, F16 and BF16 tensors are read as f32; transpose2d returns a 2-D tensor
+ * transposed (HF Linear weights are [out, in], the graphs use [in, out]). */
+typedef struct mft_safetensors mft_safetensors_t;
+int32_t mft_safetensors_open(const char* path_or_dir, mft_safetensors_t** out);
+int32_t mft_safetensors_close(mft_safetensors_t* h);
+int64_t mft_safetensors_count(const mft_safetensors_t* h);
+const char* mft_safetensors_name(const mft_safetensors_t* h, int64_t i);
+const char* mft_safetensors_metadata(const mft_safetensors_t* h, const char* key);     /* NULL when absent */
+int32_t mft_safetensors_info(const mft_safetensors_t* h, const char* name, char* dtype8, int32_t* ndim, int64_t* shape8);
+int32_t mft_safetensors_read_f32(const mft_safetensors_t* h, const char* name, float* out_host, int32_t transpose2d);
+/* Writes n f32 tensors (shapes8: 8 extents per tensor, ndims[i] used) sorted by name, plus string metadata. */
+int32_t mft_safetensors_write_f32(const char* path, int32_t n, const char* const* names, const int32_t* ndims,
+                                  const int64_t* shapes8, const float* const* data, int32_t n_meta,
+                                  const char* const* meta_keys, const char* const* meta_values);
+/* HuggingFace key of frozen parameter idx ("" for a tensor the checkpoint does not carry, e.g. a tied lm_head)
+ * and whether the file's tensor is the transpose of the parameter. */
+int32_t mft_model_hf_key(const mft_model_t* m, int32_t idx, char* key_out, int32_t key_cap, int32_t* transpose);
+/* Loads every frozen parameter from a HuggingFace checkpoint of the model's family (GPT-2 keys with or without
+ * the "transformer." prefix) through the staging path (host f32 -> device, cast / fused-group packing there). */
+int32_t mft_model_load_safetensors(mft_model_t* m, const char* path_or_dir);
+/* Adapter file: keys layer.{i}.{target}.lora_A / .lora_B in the reference's tensor layouts, F32, sorted, with
+ * rank / alpha / dropout / targets in __metadata__.  Load checks rank and shapes. */
+int32_t mft_model_save_lora_safetensors(mft_model_t* m, const char* path);
+int32_t mft_model_load_lora_safetensors(mft_model_t* m, const char* path);
+
 /* ---- double-buffered input (the Batch tensors of WikiText2Dataset::get_batch, data/wikitext2_dataset.cpp:451-519,
  *      are rebuilt in the same host buffers for every batch): batch k+1 is copied to the device on a copy stream
  *      while step k computes, and the loss of step k is read back without stalling step k+1.

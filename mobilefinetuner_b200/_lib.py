@@ -144,6 +144,18 @@ _SIGS = {
     "mft_model_optimizer_step": [vp, f32, f32, f32, f32, f32, f32, f32],
     "mft_model_zero_grad": [vp],
     "mft_model_set_loss_scale": [vp, f32],
+    "mft_safetensors_open": [C.c_char_p, vp],
+    "mft_safetensors_close": [vp],
+    "mft_safetensors_count": [vp],
+    "mft_safetensors_name": [vp, i64],
+    "mft_safetensors_metadata": [vp, C.c_char_p],
+    "mft_safetensors_info": [vp, C.c_char_p, vp, vp, vp],
+    "mft_safetensors_read_f32": [vp, C.c_char_p, vp, i32],
+    "mft_safetensors_write_f32": [C.c_char_p, i32, vp, vp, vp, vp, i32, vp, vp],
+    "mft_model_hf_key": [vp, i32, vp, i32, vp],
+    "mft_model_load_safetensors": [vp, C.c_char_p],
+    "mft_model_save_lora_safetensors": [vp, C.c_char_p],
+    "mft_model_load_lora_safetensors": [vp, C.c_char_p],
     "mft_model_stage_batch": [vp, i32, vp, vp, i32, i32],
     "mft_model_stage_wait": [vp, i32],
     "mft_model_step_staged": [vp, i32, i32, i32, i64, vp, vp],
@@ -162,9 +174,11 @@ _SIGS = {
 }
 _RET = {"mft_launch_count": i64, "mft_last_error": C.c_char_p, "mft_lmhead_ce_workspace_bytes": i64,
         "mft_lmhead_ce_set_panel_budget": i64,
-        "mft_model_activation_bytes": i64, "mft_trainer_lr": f32, "mft_trainer_global_step": i64}
+        "mft_model_activation_bytes": i64, "mft_trainer_lr": f32, "mft_trainer_global_step": i64,
+        "mft_safetensors_count": i64, "mft_safetensors_name": C.c_char_p, "mft_safetensors_metadata": C.c_char_p}
 _NO_STATUS = {"mft_version", "mft_lmhead_ce_workspace_bytes", "mft_lmhead_ce_set_panel_budget", "mft_model_param_count", "mft_model_lora_count",
-              "mft_model_lora_has_grad", "mft_trainer_lr", "mft_trainer_global_step"}
+              "mft_model_lora_has_grad", "mft_trainer_lr", "mft_trainer_global_step",
+              "mft_safetensors_count", "mft_safetensors_name", "mft_safetensors_metadata"}
 
 
 def exported_names() -> list[str]:

@@ -238,6 +238,77 @@ def test_double_buffered_input_gives_the_same_steps():
         assert d.max() <= 5 * 2.1 * 1e-4 and (d <= 1e-6 + 1e-4 * np.abs(b).max()).mean() >= 0.98
 
 
+@pytest.mark.parametrize("name,storage", [("gemma_tiny", "BF16"), ("qwen_tiny", "F32"), ("gpt2_tiny", "F16")])
+def test_checkpoint_ingest_and_adapter_files_round_trip(name, storage, tmp_path):
+    """A HuggingFace-style checkpoint (HF keys, Linear weights [out,in], F32 / F16 / BF16 storage, two shards + index)
+    loaded through mft_model_load_safetensors gives the same model as installing the tensors one by one; an adapter
+    saved with mft_model_save_lora_safetensors loads back bit-identically and carries the PEFT-style keys."""
+    import ctypes as C
+    import json
+    import struct
+    import torch
+    from mobilefinetuner_b200 import _lib as L, synth
+    from mobilefinetuner_b200.engine import LoraStepEngine
+    from test_safetensors_cpu import bf16_bits, write_container
+    case = CASES[name]
+    spec = case["spec"]
+    B, S = case["batch"], case["seq"]
+    params, lora = synth.make_params(spec, 1, 0.1), synth.make_lora(spec, 2)
+    if storage == "F16":                                 # what the file can hold
+        params = [p.astype(np.float16).astype(np.float32) for p in params]
+    elif storage == "BF16":
+        params = [(bf16_bits(p).astype(np.uint32) << 16).view(np.float32).reshape(p.shape) for p in params]
+    ids, labels = synth.make_batch(spec, B, S, 3)
+    ref = LoraStepEngine(spec, B, S)
+    ref.set_params(params); ref.set_lora(lora)
+    want_loss = ref.forward_loss(ids, labels)
+
+    def store(a):
+        if storage == "F32":
+            return "F32", a.astype(np.float32)
+        if storage == "F16":
+            return "F16", a.astype(np.float16)
+        return "BF16", bf16_bits(a)
+
+    tensors = {}
+    for i, p in enumerate(params):
+        key, tr = C.create_string_buffer(256), C.c_int32()
+        L.call("mft_model_hf_key", ref._h, i, key, 256, C.byref(tr))
+        if key.value:
+            tensors[key.value.decode()] = store(p.T if tr.value else p)
+    assert any(k.endswith("q_proj.weight") or k.endswith("c_attn.weight") for k in tensors)
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    items = list(tensors.items())
+    half = len(items) // 2
+    write_container(d / "model-00001-of-00002.safetensors", dict(items[:half]), {"format": "pt"})
+    write_container(d / "model-00002-of-00002.safetensors", dict(items[half:]))
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {k: ("model-00001-of-00002.safetensors" if i < half else "model-00002-of-00002.safetensors") for i, (k, _) in enumerate(items)}}))
+
+    eng = LoraStepEngine(spec, B, S)
+    L.call("mft_model_load_safetensors", eng._h, str(d).encode())
+    eng.set_lora(lora)
+    got_loss = eng.forward_loss(ids, labels)
+    assert abs(got_loss - want_loss) <= 1e-6 * abs(want_loss)
+
+    # adapter save -> load into a fresh engine
+    path = tmp_path / "adapter.safetensors"
+    L.call("mft_model_save_lora_safetensors", ref._h, str(path).encode())
+    raw = path.read_bytes()
+    header = json.loads(raw[8:8 + struct.unpack("<Q", raw[:8])[0]])
+    assert header["__metadata__"]["rank"] == str(spec.lora_rank) and "targets" in header["__metadata__"]
+    keys = [k for k in header if k != "__metadata__"]
+    assert keys == sorted(keys) and all(k.startswith("layer.") and k.rsplit(".", 1)[1] in ("lora_A", "lora_B") for k in keys)
+    assert len(keys) == len(lora)
+    other = LoraStepEngine(spec, B, S)
+    other.set_params(params)
+    L.call("mft_model_load_lora_safetensors", other._h, str(path).encode())
+    for a, b in zip(other.get_lora(), ref.get_lora()):
+        np.testing.assert_array_equal(a, b)
+    assert abs(other.forward_loss(ids, labels) - want_loss) <= 1e-6 * abs(want_loss)
+    ref.close(); eng.close(); other.close()
+
+
 def test_evaluation_drivers_perplexity_and_letter_scores():
     """eval_ppl aggregation over batches and MMLU-style letter scoring (log_softmax of the last position read at the
     candidate ids), against the restated aggregation and a float64 projection of the engine's own final hidden state."""
