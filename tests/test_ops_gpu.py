@@ -236,6 +236,37 @@ def test_attention_full_size_properties(ops):
     assert torch.allclose(lse, torch.log(torch.arange(1, S + 1, device="cuda").float()).expand(B, nh, S), atol=1e-3)
 
 
+@pytest.mark.parametrize("window", [0, 512])
+def test_attention_head_dim_256_full_size_properties(ops, window):
+    """The headline shape (S = 2048, head_dim 256, 4 query heads on 1 KV head) on the tensor-memory kernels, checked
+    through the uniform-attention identity: with Q = 0 every visible key has the same weight, so O[i] is the mean of
+    the visible V rows, lse[i] = log(#visible), dV[j] = sum over the queries that see j of dO[i] / #visible(i),
+    and dQ = scale * (P (dP - delta)) K with dP - delta = dO[i] . (V[j] - O[i])."""
+    B, nh, nkv, S, hd = 1, 4, 1, 2048, 256
+    g = torch.Generator(device="cuda").manual_seed(7)
+    q = torch.zeros(B, S, nh, hd, device="cuda", dtype=torch.bfloat16).permute(0, 2, 1, 3)
+    k = torch.randn(B, S, nkv, hd, device="cuda", generator=g).bfloat16().permute(0, 2, 1, 3)
+    v = torch.randn(B, S, nkv, hd, device="cuda", generator=g).bfloat16().permute(0, 2, 1, 3)
+    do = torch.randn(B, S, nh, hd, device="cuda", generator=g).bfloat16().permute(0, 2, 1, 3)
+    scale = hd ** -0.5
+    o, lse = ops.attention_fwd(q, k, v, scale, window)
+    i = torch.arange(S, device="cuda")
+    vis = (i[None, :] <= i[:, None]) & ((i[:, None] - i[None, :] < window) if window > 0 else torch.ones(S, S, dtype=torch.bool, device="cuda"))
+    cnt = vis.sum(1).double()                                            # visible keys per query
+    P = vis.double() / cnt[:, None]
+    want_o = (P @ v[0, 0].double())                                      # [S, hd], same for every head
+    assert (o.double() - want_o[None, None]).abs().max().item() < 2e-2
+    assert torch.allclose(lse.double(), torch.log(cnt).expand(B, nh, S), atol=1e-3)
+    dq, dk, dv = ops.attention_bwd(q, k, v, o, do, lse, scale, window)
+    want_dv = sum(P.T @ do[0, h].double() for h in range(nh))            # [S, hd]
+    assert cosine(host(dv[0, 0].float()), want_dv.cpu().numpy()) >= 0.9995
+    dP = do[0, 0].double() @ v[0, 0].double().T                          # head 0
+    delta = (do[0, 0].double() * o[0, 0].double()).sum(1, keepdim=True)
+    want_dq0 = scale * ((P * (dP - delta)) @ k[0, 0].double())
+    assert cosine(host(dq[0, 0].float()), want_dq0.cpu().numpy()) >= 0.9995
+    assert ops.device_status() == 0
+
+
 # ------------------------------------------------------------------ norms, activations, RoPE, gathers
 @pytest.mark.parametrize("name,unit", [("rms_norm", 1), ("rms_norm_affine", 0)])
 def test_rms_norm_golden_fp32(ops, golden, name, unit):
