@@ -109,18 +109,19 @@ def build_operators(force: bool = False) -> Path:
     return OPERATORS_LIB
 
 
-def build_cpp_tests() -> Path:
-    """Compile tests/cpp/auto_trainer_step.cpp (the C++ API driven like the reference's own AutoTrainer test)."""
-    src = PKG.parent / "tests" / "cpp" / "auto_trainer_step.cpp"
-    exe = OBJ / "auto_trainer_step"
+def build_cpp_tests(name: str = "auto_trainer_step") -> Path:
+    """Compile tests/cpp/<name>.cpp against the C++ API (auto_trainer_step: driven like the reference's own
+    AutoTrainer test; safetensors_reader: the checkpoint reader classes)."""
+    src = PKG.parent / "tests" / "cpp" / f"{name}.cpp"
+    exe = OBJ / name
     if exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, OPERATORS_LIB.stat().st_mtime):
         return exe
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-    cmd = [cxx, "-std=c++17", "-O1", f"-I{OPERATORS}", f"-I{OPERATORS / 'finetune_ops'}", f"-I{OPERATORS / 'include'}", str(src),
+    cmd = [cxx, "-std=c++17", "-O1", f"-I{OPERATORS}", f"-I{OPERATORS / 'finetune_ops'}", f"-I{OPERATORS / 'include'}", f"-I{PKG.parent / 'include'}", str(src),
            f"-L{PKG}", "-lmft_operators", "-lmft_cuda", f"-Wl,-rpath,{PKG}", "-Wl,-rpath,$ORIGIN/../..", "-o", str(exe)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError(f"building auto_trainer_step failed:\n{res.stdout}\n{res.stderr}")
+        raise RuntimeError(f"building {name} failed:\n{res.stdout}\n{res.stderr}")
     return exe
 
 

@@ -139,3 +139,16 @@ def test_rejects_truncated_and_malformed_files(L, tmp_path):
         open_(L, p)
     with pytest.raises(L.MftError):
         open_(L, tmp_path / "does_not_exist")
+
+
+def test_cpp_reader_classes_and_key_maps(tmp_path):
+    """tests/cpp/safetensors_reader.cpp: SafeTensorsModelReader / SafeTensorsReader / the three key mappers of the
+    C++ API, used the way the reference's loading code uses them (host only)."""
+    import subprocess
+    from mobilefinetuner_b200 import build
+    build.build()
+    build.build_operators()
+    exe = build.build_cpp_tests("safetensors_reader")
+    res = subprocess.run([str(exe), str(tmp_path)], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "all checks passed" in res.stdout
