@@ -120,6 +120,19 @@ int32_t mft_rmsnorm_bwd(const void* dy, int32_t dy_dtype, const void* x, int32_t
                         const float* weight, const float* rstd, float eps, int32_t unit_offset,
                         void* dx, int32_t dx_dtype, int32_t accumulate, float* dweight,
                         int64_t rows, int64_t dim, mft_stream_t stream);
+/* Gemma's block wrapper in one pass per row (rows up to 2048 wide; MFT_ERR_UNSUPPORTED beyond):
+ *   forward : sum_out = residual + rms_norm(y; w_post) ,  h_next = rms_norm(sum_out; w_next)
+ *             (post-norm of one block + residual add + pre-norm of the next, gemma_model.cpp:615-640), the row
+ *             stays in registers between the two norms; both rstd vectors are stored for the backward.
+ *   backward: dx_inout += d rms_norm(x_sum; w_next)(dy_next)   then   d_branch = d rms_norm(y_branch; w_post)(dx_inout)
+ * Results are bit-identical to the two separate mft_rmsnorm_* calls. */
+int32_t mft_rmsnorm_add_norm_fwd(const void* y_bf16, const float* w_post, int32_t unit_post, const float* residual,
+                                 const float* w_next, int32_t unit_next, float eps, float* sum_out, float* rstd_post,
+                                 void* h_next_bf16, float* rstd_next, int64_t rows, int64_t dim, mft_stream_t stream);
+int32_t mft_rmsnorm_pair_bwd(const void* dy_next_bf16, const float* x_sum, const float* w_next, int32_t unit_next,
+                             const float* rstd_next, float* dx_inout, const void* y_branch_bf16, const float* w_post,
+                             int32_t unit_post, const float* rstd_post, void* d_branch_bf16, int64_t rows, int64_t dim,
+                             mft_stream_t stream);
 int32_t mft_layernorm_fwd(const void* x, int32_t x_dtype, const float* weight, const float* bias,
                           float eps, void* y, int32_t y_dtype, float* mean, float* rstd,
                           int64_t rows, int64_t dim, mft_stream_t stream);

@@ -83,6 +83,8 @@ _SIGS = {
     "mft_embedding_gather": [vp, vp, vp, vp, i64, i64, i64, i64, f32, vp, vp],
     "mft_rmsnorm_fwd": [vp, i32, vp, f32, i32, vp, i32, vp, vp, vp, i64, i64, vp],
     "mft_rmsnorm_bwd": [vp, i32, vp, i32, vp, vp, f32, i32, vp, i32, i32, vp, i64, i64, vp],
+    "mft_rmsnorm_add_norm_fwd": [vp, vp, i32, vp, vp, i32, f32, vp, vp, vp, vp, i64, i64, vp],
+    "mft_rmsnorm_pair_bwd": [vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, i64, i64, vp],
     "mft_layernorm_fwd": [vp, i32, vp, vp, f32, vp, i32, vp, vp, i64, i64, vp],
     "mft_layernorm_bwd": [vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, vp, vp, i64, i64, vp],
     "mft_act_fwd": [i32, vp, vp, i64, vp, i64, i64, vp],

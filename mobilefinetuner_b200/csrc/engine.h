@@ -155,6 +155,7 @@ struct mft_model {
     float* attn_dkv_acc = nullptr;   // f32 [2][T, n_kv, hd]: per-head dK/dV contributions are added here (grouped-query models)
     float* loss_dev = nullptr; int32_t* n_valid_dev = nullptr; float* ce_lse = nullptr; int32_t* status_dev = nullptr;
     void* ce_ws = nullptr; int64_t ce_ws_bytes = 0;
+    bool fuse_norms = true;          // Gemma: post-norm + residual + pre-norm pairs in one kernel (MFT_FUSE_NORMS=0: separate calls)
     bool ce_onepass = true;          // training steps use mft_lmhead_ce_fused (MFT_CE_ONEPASS=0 selects the two-sweep pair)
     float* stage_f32 = nullptr; int64_t stage_floats = 0;   // upload staging
 };

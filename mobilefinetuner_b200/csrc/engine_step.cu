@@ -66,6 +66,7 @@ int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
     const int QD = nh * hd, KD = nkv * hd, QKV = QD + 2 * KD;
     const int64_t T = c.T, S = c.S;
     (void)for_training;
+    const bool fuse = gemma && m->fuse_norms && H <= 2048;      // Gemma's post-norm + residual + pre-norm pairs in one kernel
     if (m->panels_dirty && m->n_pack > 0) {
         TRY(mft_pack_blocks_bf16(m->pack_table, m->n_pack, c.st));
         m->panels_dirty = false;
@@ -80,7 +81,8 @@ int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
         float* x_next = (l + 1 < L) ? m->bufs[l + 1].x : m->x_final;
         // ---- attention block
         if (gpt2) TRY(mft_layernorm_fwd(b.x, MFT_F32, w.ln1_w, w.ln1_b, 1e-5f, b.h1, MFT_BF16, b.mean1, b.rstd1, T, H, c.st));
-        else TRY(mft_rmsnorm_fwd(b.x, MFT_F32, w.ln1_w, cfg.norm_eps, gemma ? 1 : 0, b.h1, MFT_BF16, b.rstd1, nullptr, nullptr, T, H, c.st));
+        else if (!(fuse && l > 0))     // with fused norms the previous layer's last kernel already produced h1 / rstd1
+            TRY(mft_rmsnorm_fwd(b.x, MFT_F32, w.ln1_w, cfg.norm_eps, gemma ? 1 : 0, b.h1, MFT_BF16, b.rstd1, nullptr, nullptr, T, H, c.st));
         TRY(group_fwd(c, w.qkv, b.h1, b.xa_qkv, b.qkv));
         const bf16 *q, *k, *v = b.qkv + QD + KD;
         int64_t ldqk;
@@ -97,7 +99,10 @@ int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
         TRY(mft_attn_fwd(q, tok_strides(S, ldqk, hd), k, tok_strides(S, ldqk, hd), v, tok_strides(S, QKV, hd), b.o, tok_strides(S, QD, hd),
                          b.lse, c.B, S, nh, nkv, hd, cfg.attn_scale, window, c.st));
         TRY(group_fwd(c, w.o, b.o, b.xa_o, b.attn_out));
-        if (gemma) {
+        if (fuse) {
+            // x_mid = x + rms_norm(attn_out) and the pre-feedforward norm of x_mid, one pass per row
+            TRY(mft_rmsnorm_add_norm_fwd(b.attn_out, w.post_attn_w, 1, b.x, w.ln2_w, 1, cfg.norm_eps, b.x_mid, b.rstd2, b.h2, b.rstd3, T, H, c.st));
+        } else if (gemma) {
             // x_mid = x + rms_norm(attn_out) in one pass, then the pre-feedforward norm
             TRY(mft_rmsnorm_fwd(b.attn_out, MFT_BF16, w.post_attn_w, cfg.norm_eps, 1, nullptr, MFT_BF16, b.rstd2, b.x, b.x_mid, T, H, c.st));
             TRY(mft_rmsnorm_fwd(b.x_mid, MFT_F32, w.ln2_w, cfg.norm_eps, 1, b.h2, MFT_BF16, b.rstd3, nullptr, nullptr, T, H, c.st));
@@ -111,11 +116,16 @@ int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
         if (gpt2) TRY(mft_act_fwd(MFT_ACT_GELU, b.gu, nullptr, I, b.act, T, I, c.st));
         else TRY(mft_act_fwd(gemma ? MFT_ACT_GEGLU : MFT_ACT_SWIGLU, b.gu, b.gu + I, 2 * I, b.act, T, I, c.st));
         TRY(group_fwd(c, w.down, b.act, b.xa_d, b.mlp_out));
-        if (gemma) TRY(mft_rmsnorm_fwd(b.mlp_out, MFT_BF16, w.post_ffn_w, cfg.norm_eps, 1, nullptr, MFT_BF16, b.rstd4, b.x_mid, x_next, T, H, c.st));
+        if (fuse) {
+            // x_next = x_mid + rms_norm(mlp_out) and the norm that reads x_next: the next layer's input norm, or the final norm
+            const bool last = l + 1 == L;
+            TRY(mft_rmsnorm_add_norm_fwd(b.mlp_out, w.post_ffn_w, 1, b.x_mid, last ? m->final_w : m->layers[l + 1].ln1_w, 1, cfg.norm_eps, x_next,
+                                         b.rstd4, last ? m->hf : m->bufs[l + 1].h1, last ? m->rstd_f : m->bufs[l + 1].rstd1, T, H, c.st));
+        } else if (gemma) TRY(mft_rmsnorm_fwd(b.mlp_out, MFT_BF16, w.post_ffn_w, cfg.norm_eps, 1, nullptr, MFT_BF16, b.rstd4, b.x_mid, x_next, T, H, c.st));
         else TRY(mft_add_f32_bf16(b.x_mid, b.mlp_out, x_next, T * H, c.st));
     }
     if (gpt2) TRY(mft_layernorm_fwd(m->x_final, MFT_F32, m->final_w, m->final_b, 1e-5f, m->hf, MFT_BF16, m->mean_f, m->rstd_f, T, H, c.st));
-    else TRY(mft_rmsnorm_fwd(m->x_final, MFT_F32, m->final_w, cfg.norm_eps, gemma ? 1 : 0, m->hf, MFT_BF16, m->rstd_f, nullptr, nullptr, T, H, c.st));
+    else if (!fuse) TRY(mft_rmsnorm_fwd(m->x_final, MFT_F32, m->final_w, cfg.norm_eps, gemma ? 1 : 0, m->hf, MFT_BF16, m->rstd_f, nullptr, nullptr, T, H, c.st));
     // lm head + shifted cross entropy; the [T,V] logits are never written.  A training step gets the loss and
     // d(loss)/d(final hidden) (into t_h) from one sweep over the vocabulary.
     if (for_training && m->ce_onepass)
@@ -141,13 +151,18 @@ int32_t backward(Ctx& c, int64_t n_valid_global) {
     if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, m->x_final, MFT_F32, m->final_w, m->mean_f, m->rstd_f, m->dx, MFT_F32, 0, nullptr, nullptr, T, H, c.st));
     else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, m->x_final, MFT_F32, m->final_w, m->rstd_f, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 0, nullptr, T, H, c.st));
 
+    const bool fuse = gemma && m->fuse_norms && H <= 2048;
+    bool have_d_mlp_out = false;
     for (int l = L - 1; l >= 0; --l) {
         LayerWeights& w = m->layers[l];
         LayerBuffers& b = m->bufs[l];
         // ---- MLP block: dx is d(loss)/d(x_next) on entry
         const bf16* d_mlp_out;
         if (gemma) {
-            TRY(mft_rmsnorm_bwd(m->dx, MFT_F32, b.mlp_out, MFT_BF16, w.post_ffn_w, b.rstd4, cfg.norm_eps, 1, m->t_h, MFT_BF16, 0, nullptr, T, H, c.st));
+            // (with fused norms the layer above already pushed dx through this layer's post-feedforward norm into t_h)
+            if (!have_d_mlp_out)
+                TRY(mft_rmsnorm_bwd(m->dx, MFT_F32, b.mlp_out, MFT_BF16, w.post_ffn_w, b.rstd4, cfg.norm_eps, 1, m->t_h, MFT_BF16, 0, nullptr, T, H, c.st));
+            have_d_mlp_out = false;
         } else {
             TRY(mft_cast_f32_to_bf16(m->dx, m->t_h, T * H, c.st));
         }
@@ -158,9 +173,12 @@ int32_t backward(Ctx& c, int64_t n_valid_global) {
         TRY(group_bwd(c, w.gu, m->t_gu, b.h2, b.xa_gu, m->t_h, true));
         // through the pre-MLP norm, accumulated onto the residual gradient: dx = d(loss)/d(x_mid)
         if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, b.x_mid, MFT_F32, w.ln2_w, b.mean3, b.rstd3, m->dx, MFT_F32, 1, nullptr, nullptr, T, H, c.st));
+        else if (fuse)   // pre-feedforward norm (adds into dx) and post-attention norm (dx -> t_h) in one pass per row
+            TRY(mft_rmsnorm_pair_bwd(m->t_h, b.x_mid, w.ln2_w, 1, b.rstd3, m->dx, b.attn_out, w.post_attn_w, 1, b.rstd2, m->t_h, T, H, c.st));
         else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, b.x_mid, MFT_F32, w.ln2_w, b.rstd3, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 1, nullptr, T, H, c.st));
         // ---- attention block
-        if (gemma) TRY(mft_rmsnorm_bwd(m->dx, MFT_F32, b.attn_out, MFT_BF16, w.post_attn_w, b.rstd2, cfg.norm_eps, 1, m->t_h, MFT_BF16, 0, nullptr, T, H, c.st));
+        if (fuse) {}
+        else if (gemma) TRY(mft_rmsnorm_bwd(m->dx, MFT_F32, b.attn_out, MFT_BF16, w.post_attn_w, b.rstd2, cfg.norm_eps, 1, m->t_h, MFT_BF16, 0, nullptr, T, H, c.st));
         else TRY(mft_cast_f32_to_bf16(m->dx, m->t_h, T * H, c.st));
         if (detach) {
             // Reference-parity GPT-2: the QKV split severs autograd, so c_proj gets its LoRA gradients
@@ -187,7 +205,12 @@ int32_t backward(Ctx& c, int64_t n_valid_global) {
         TRY(group_bwd(c, w.qkv, m->t_qkv, b.h1, b.xa_qkv, need_dx ? m->t_h : nullptr, true));
         if (need_dx) {
             if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, b.x, MFT_F32, w.ln1_w, b.mean1, b.rstd1, m->dx, MFT_F32, 1, nullptr, nullptr, T, H, c.st));
-            else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, b.x, MFT_F32, w.ln1_w, b.rstd1, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 1, nullptr, T, H, c.st));
+            else if (fuse) {
+                // this layer's input norm (adds into dx) and the post-feedforward norm of the layer below (dx -> t_h)
+                TRY(mft_rmsnorm_pair_bwd(m->t_h, b.x, w.ln1_w, 1, b.rstd1, m->dx, m->bufs[l - 1].mlp_out, m->layers[l - 1].post_ffn_w, 1,
+                                         m->bufs[l - 1].rstd4, m->t_h, T, H, c.st));
+                have_d_mlp_out = true;
+            } else TRY(mft_rmsnorm_bwd(m->t_h, MFT_BF16, b.x, MFT_F32, w.ln1_w, b.rstd1, cfg.norm_eps, gemma ? 1 : 0, m->dx, MFT_F32, 1, nullptr, T, H, c.st));
         }
     }
     if (m->n_unpack > 0) TRY(mft_accumulate_blocks_f32(m->unpack_table, m->n_unpack, c.st));

@@ -234,6 +234,159 @@ rmsnorm_bwd_warp_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, co
     }
 }
 
+
+// ---------------------------------------------------------------- fused post-norm + residual add + next pre-norm
+// Gemma wraps every block as  x_sum = x + rms(y_branch) ,  h_next = rms(x_sum)  (post-norm of one block, residual
+// add, pre-norm of the next).  One warp per row keeps x_sum in registers between the two norms, so x_sum is
+// written once and never re-read: same arithmetic, in the same order, as the two separate kernels.
+template <int VPL>
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rmsnorm_add_norm_fwd_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ w_post, int unit_post,
+                            const float* __restrict__ residual, const float* __restrict__ w_next, int unit_next, float eps,
+                            float* __restrict__ sum_out, float* __restrict__ rstd_post, __nv_bfloat16* __restrict__ h_next,
+                            float* __restrict__ rstd_next, int64_t rows, int64_t dim) {
+    dep_trigger();
+    dep_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int nvec = (int)(dim / 8);
+    float v[VPL][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) load8(y + row * dim + i * 8, v[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k)
+        if (lane + k * 32 < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
+        }
+    ss = warp_sum(ss);
+    const float rp = rsqrtf(ss / (float)dim + eps);
+    if (lane == 0) rstd_post[row] = rp;
+    float ss2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float wv[8], r[8];
+            load8(w_post + i * 8, wv);
+            load8(residual + row * dim + i * 8, r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float o = v[k][j] * rp * (unit_post ? 1.0f + wv[j] : wv[j]);
+                v[k][j] = r[j] + o;
+            }
+            store8(sum_out + row * dim + i * 8, v[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k)
+        if (lane + k * 32 < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss2 += v[k][j] * v[k][j];
+        }
+    ss2 = warp_sum(ss2);
+    const float rn = rsqrtf(ss2 / (float)dim + eps);
+    if (lane == 0) rstd_next[row] = rn;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float wv[8], o[8];
+            load8(w_next + i * 8, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = v[k][j] * rn * (unit_next ? 1.0f + wv[j] : wv[j]);
+            store8(h_next + row * dim + i * 8, o);
+        }
+    }
+}
+
+// Backward of the same pair: dx (f32, the gradient on x_sum that came down the residual path) first receives the
+// gradient through the next pre-norm (dy_next), is stored, and then goes through the post-norm of the branch.
+template <int VPL>
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rmsnorm_pair_bwd_kernel(const __nv_bfloat16* __restrict__ dy_next, const float* __restrict__ x_sum, const float* __restrict__ w_next,
+                        int unit_next, const float* __restrict__ rstd_next, float* __restrict__ dx,
+                        const __nv_bfloat16* __restrict__ y_branch, const float* __restrict__ w_post, int unit_post,
+                        const float* __restrict__ rstd_post, __nv_bfloat16* __restrict__ d_branch, int64_t rows, int64_t dim) {
+    dep_trigger();
+    dep_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int nvec = (int)(dim / 8);
+    float xv[VPL][8], g[VPL][8];
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            load8(x_sum + row * dim + i * 8, xv[k]);
+            load8(dy_next + row * dim + i * 8, g[k]);
+        }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float wv[8];
+            load8(w_next + i * 8, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                g[k][j] *= (unit_next ? 1.0f + wv[j] : wv[j]);
+                dot += g[k][j] * xv[k][j];
+            }
+        }
+    }
+    dot = warp_sum(dot);
+    const float rn = rstd_next[row];
+    const float coeff = rn * rn * rn / (float)dim * dot;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float prev[8];
+            load8(dx + row * dim + i * 8, prev);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[k][j] = (g[k][j] * rn - xv[k][j] * coeff) + prev[j];
+            store8(dx + row * dim + i * 8, g[k]);
+        }
+    }
+    // post-norm of the branch: dy = the dx row just formed
+    float dot2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float wv[8];
+            load8(y_branch + row * dim + i * 8, xv[k]);
+            load8(w_post + i * 8, wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                g[k][j] *= (unit_post ? 1.0f + wv[j] : wv[j]);
+                dot2 += g[k][j] * xv[k][j];
+            }
+        }
+    }
+    dot2 = warp_sum(dot2);
+    const float rp = rstd_post[row];
+    const float coeff2 = rp * rp * rp / (float)dim * dot2;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = g[k][j] * rp - xv[k][j] * coeff2;
+            store8(d_branch + row * dim + i * 8, o);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- LayerNorm
 template <typename TX, typename TY>
 __global__ void __launch_bounds__(NORM_THREADS)
@@ -477,6 +630,40 @@ int32_t mft_rmsnorm_bwd(const void* dy, int32_t dyd, const void* x, int32_t xd, 
 #undef LAUNCH
 #undef WLAUNCH
     MFT_LAUNCH_CHECK("rmsnorm_bwd");
+    return MFT_OK;
+}
+
+int32_t mft_rmsnorm_add_norm_fwd(const void* y_bf16, const float* w_post, int32_t unit_post, const float* residual,
+                                 const float* w_next, int32_t unit_next, float eps, float* sum_out, float* rstd_post,
+                                 void* h_next_bf16, float* rstd_next, int64_t rows, int64_t dim, mft_stream_t stream) {
+    MFT_CHECK_ARG(y_bf16 && w_post && residual && w_next && sum_out && rstd_post && h_next_bf16 && rstd_next && rows > 0, "mft_rmsnorm_add_norm_fwd: bad argument");
+    MFT_CHECK_ARG(dim > 0 && dim % 8 == 0, "mft_rmsnorm_add_norm_fwd: dim must be a multiple of 8");
+    if (dim > 2048) return fail(MFT_ERR_UNSUPPORTED, "mft_rmsnorm_add_norm_fwd: rows wider than 2048 use the separate norm calls");
+    const unsigned wblocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
+#define FCALL(VPL) launch_dep(rmsnorm_add_norm_fwd_kernel<VPL>, dim3(wblocks), dim3(NORM_WARPS * 32), (size_t)0, as_stream(stream), \
+                              (const __nv_bfloat16*)y_bf16, w_post, (int)unit_post, residual, w_next, (int)unit_next, eps, sum_out, rstd_post, \
+                              (__nv_bfloat16*)h_next_bf16, rstd_next, rows, dim)
+    if (dim <= 1280) FCALL(5); else FCALL(8);
+#undef FCALL
+    MFT_LAUNCH_CHECK("rmsnorm_add_norm_fwd");
+    return MFT_OK;
+}
+
+int32_t mft_rmsnorm_pair_bwd(const void* dy_next_bf16, const float* x_sum, const float* w_next, int32_t unit_next,
+                             const float* rstd_next, float* dx_inout, const void* y_branch_bf16, const float* w_post,
+                             int32_t unit_post, const float* rstd_post, void* d_branch_bf16, int64_t rows, int64_t dim,
+                             mft_stream_t stream) {
+    MFT_CHECK_ARG(dy_next_bf16 && x_sum && w_next && rstd_next && dx_inout && y_branch_bf16 && w_post && rstd_post && d_branch_bf16 && rows > 0,
+                  "mft_rmsnorm_pair_bwd: bad argument");
+    MFT_CHECK_ARG(dim > 0 && dim % 8 == 0, "mft_rmsnorm_pair_bwd: dim must be a multiple of 8");
+    if (dim > 2048) return fail(MFT_ERR_UNSUPPORTED, "mft_rmsnorm_pair_bwd: rows wider than 2048 use the separate norm calls");
+    const unsigned wblocks = (unsigned)((rows + NORM_WARPS - 1) / NORM_WARPS);
+#define BCALL(VPL) launch_dep(rmsnorm_pair_bwd_kernel<VPL>, dim3(wblocks), dim3(NORM_WARPS * 32), (size_t)0, as_stream(stream), \
+                              (const __nv_bfloat16*)dy_next_bf16, x_sum, w_next, (int)unit_next, rstd_next, dx_inout, \
+                              (const __nv_bfloat16*)y_branch_bf16, w_post, (int)unit_post, rstd_post, (__nv_bfloat16*)d_branch_bf16, rows, dim)
+    if (dim <= 1280) BCALL(5); else BCALL(8);
+#undef BCALL
+    MFT_LAUNCH_CHECK("rmsnorm_pair_bwd");
     return MFT_OK;
 }
 

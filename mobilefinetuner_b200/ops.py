@@ -90,6 +90,29 @@ def rms_norm_bwd(dy, x, weight, rstd, eps, unit_offset, out_dtype=F32, dweight=N
     return dx
 
 
+def rms_norm_add_norm_fwd(y, w_post, residual, w_next, eps, unit_post=1, unit_next=1):
+    """sum = residual + rms_norm(y; w_post), h = rms_norm(sum; w_next) in one pass: returns (sum, rstd_post, h, rstd_next)."""
+    _init(y)
+    rows, dim = y.numel() // y.shape[-1], y.shape[-1]
+    sum_out = torch.empty(y.shape, device=y.device, dtype=F32)
+    h = torch.empty(y.shape, device=y.device, dtype=BF16)
+    rp = torch.empty(rows, device=y.device, dtype=F32)
+    rn = torch.empty(rows, device=y.device, dtype=F32)
+    L.call("mft_rmsnorm_add_norm_fwd", _p(y), _p(w_post), int(unit_post), _p(residual), _p(w_next), int(unit_next), float(eps),
+           _p(sum_out), _p(rp), _p(h), _p(rn), rows, dim, _stream())
+    return sum_out, rp, h, rn
+
+
+def rms_norm_pair_bwd(dy_next, x_sum, w_next, rstd_next, dx_inout, y_branch, w_post, rstd_post, unit_post=1, unit_next=1):
+    """dx_inout += d rms_norm(x_sum; w_next)(dy_next); returns d rms_norm(y_branch; w_post)(dx_inout) as bf16."""
+    _init(x_sum)
+    rows, dim = x_sum.numel() // x_sum.shape[-1], x_sum.shape[-1]
+    d_branch = torch.empty(y_branch.shape, device=x_sum.device, dtype=BF16)
+    L.call("mft_rmsnorm_pair_bwd", _p(dy_next), _p(x_sum), _p(w_next), int(unit_next), _p(rstd_next), _p(dx_inout), _p(y_branch),
+           _p(w_post), int(unit_post), _p(rstd_post), _p(d_branch), rows, dim, _stream())
+    return d_branch
+
+
 def layer_norm_fwd(x, weight, bias, eps, out_dtype=BF16):
     _init(x)
     rows, dim = x.numel() // x.shape[-1], x.shape[-1]

@@ -233,9 +233,11 @@ def test_double_buffered_input_gives_the_same_steps():
     assert [g[0] for g in got] == list(range(5))
     for (k, loss, nv), (wloss, wnv) in zip(got, want):
         assert nv == wnv and abs(loss - wloss) <= 2e-4 * abs(wloss), (k, loss, wloss)
-    for a, b in zip(got_lora, want_lora):
-        d = np.abs(a - b)
-        assert d.max() <= 5 * 2.1 * 1e-4 and (d <= 1e-6 + 1e-4 * np.abs(b).max()).mean() >= 0.98
+    # Two runs of five Adam steps are not bit-identical (f32 atomics in the gradient reductions; an element whose tiny
+    # gradient changes sign moves the other way by up to 2 lr per step): compare the parameter UPDATES as vectors.
+    for a, b, p0 in zip(got_lora, want_lora, lora):
+        assert np.abs(a - b).max() <= 5 * 2.1 * 1e-4
+        assert cosine(a - p0, b - p0) >= 0.97
 
 
 @pytest.mark.parametrize("name,storage", [("gemma_tiny", "BF16"), ("qwen_tiny", "F32"), ("gpt2_tiny", "F16")])

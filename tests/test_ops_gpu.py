@@ -268,6 +268,29 @@ def test_attention_head_dim_256_full_size_properties(ops, window):
 
 
 # ------------------------------------------------------------------ norms, activations, RoPE, gathers
+@pytest.mark.parametrize("dim", [640, 1152, 2048])
+def test_fused_norm_pairs_equal_the_separate_kernels(ops, dim):
+    """Gemma's post-norm + residual add + next pre-norm in one kernel, forward and backward: bit-identical to the
+    separate rms_norm kernels (which are pinned to the reference's golden vectors)."""
+    g = torch.Generator(device="cuda").manual_seed(dim)
+    rows, eps = 300, 1e-6
+    y = torch.randn(rows, dim, device="cuda", generator=g).bfloat16()
+    x = torch.randn(rows, dim, device="cuda", generator=g)
+    wp = torch.randn(dim, device="cuda", generator=g) * 0.1
+    wn = torch.randn(dim, device="cuda", generator=g) * 0.1
+    _, rp_ref, sum_ref = ops.rms_norm_fwd(y, wp, eps, 1, out_dtype=torch.bfloat16, residual=x)
+    h_ref, rn_ref = ops.rms_norm_fwd(sum_ref, wn, eps, 1, out_dtype=torch.bfloat16)
+    s, rp, h, rn = ops.rms_norm_add_norm_fwd(y, wp, x, wn, eps)
+    assert torch.equal(s, sum_ref) and torch.equal(rp, rp_ref) and torch.equal(h, h_ref) and torch.equal(rn, rn_ref)
+    dy = torch.randn(rows, dim, device="cuda", generator=g).bfloat16()
+    dx0 = torch.randn(rows, dim, device="cuda", generator=g)
+    dx_ref = ops.rms_norm_bwd(dy, sum_ref, wn, rn_ref, eps, 1, accumulate_into=dx0.clone())
+    db_ref = ops.rms_norm_bwd(dx_ref, y, wp, rp_ref, eps, 1, out_dtype=torch.bfloat16)
+    dx = dx0.clone()
+    db = ops.rms_norm_pair_bwd(dy, s, wn, rn, dx, y, wp, rp)
+    assert torch.equal(dx, dx_ref) and torch.equal(db, db_ref)
+
+
 @pytest.mark.parametrize("name,unit", [("rms_norm", 1), ("rms_norm_affine", 0)])
 def test_rms_norm_golden_fp32(ops, golden, name, unit):
     i, o, p = golden.case(name)
