@@ -655,13 +655,13 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
     }
 #define BWD(HD, WN, BM, BN, ST)                                                                             \
     {                                                                                                       \
-        const int32_t sdq = attn_dq_sm100(p, HD, true, as_stream(stream));   /* also forms delta */         \
+        /* rowsum(O * dO) in its own kernel: forming it inside the tensor-memory dQ kernel (compute_delta) was */ \
+        /* measured 0.1 ms per layer slower, it delays the start of every CTA's tile pipeline */              \
+        launch_dep(attn_delta_kernel<HD>, dim3(dblocks), dim3(256), (size_t)(0), as_stream(stream), p);     \
+        MFT_LAUNCH_CHECK("attn_delta");                                                                     \
+        const int32_t sdq = attn_dq_sm100(p, HD, false, as_stream(stream));                                 \
         if (sdq != MFT_OK && sdq != MFT_ERR_UNSUPPORTED) return sdq;                                        \
-        if (sdq == MFT_ERR_UNSUPPORTED) {                                                                   \
-            launch_dep(attn_delta_kernel<HD>, dim3(dblocks), dim3(256), (size_t)(0), as_stream(stream), p);                               \
-            MFT_LAUNCH_CHECK("attn_delta");                                                                 \
-            DQ(HD, BM, BN, ST)                                                                              \
-        }                                                                                                   \
+        if (sdq == MFT_ERR_UNSUPPORTED) DQ(HD, BM, BN, ST)                                                  \
         const int32_t skv = attn_dkv_sm100(p, HD, as_stream(stream));                                       \
         if (skv != MFT_OK && skv != MFT_ERR_UNSUPPORTED) return skv;                                        \
         dkv_tc = skv == MFT_OK;                                                                             \

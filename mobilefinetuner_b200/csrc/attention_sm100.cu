@@ -338,7 +338,7 @@ constexpr int DQ_BN = 32;
 constexpr int DQ_KV_BYTES = DQ_BN * HD * 2;        // 4 chunks of [32 rows x 64 columns]
 constexpr int DQ_KST = 3, DQ_VST = 2;              // K / V stages
 constexpr int DS_BYTES = BM * 128;                 // [128 rows x 128 bytes]: keys of group 0 in bytes 0..63, of group 1 in 64..127
-constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + DS_BYTES + 192 + BM * 4;
+constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + DS_BYTES + 192 + 4 * BM * 4;
 constexpr int DQ_THREADS = 64 + 2 * 256 + 64;     // TMA warp, S issuer, 16 element-wise warps, dP issuer, dQ issuer
 constexpr int DQ_S_COL = 0, DQ_DP_COL = 64, DQ_ACC_COL = 128;
 
@@ -391,7 +391,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     uint64_t* acc_done = bars + 19;     // [1]  completed once, by the last dQ product
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* delta_smem = reinterpret_cast<float*>(bars + 24);   // [128] rowsum(O * dO) of this CTA's queries
+    float* delta_smem = reinterpret_cast<float*>(bars + 24);   // [4][128] partial rowsum(O * dO) of this CTA's queries
     if ((smem_u32(smem_raw) & 1023u) != 0) {
         if (threadIdx.x == 0 && p.status) atomicExch(p.status, MFT_ERR_INVALID_ARG);
         return;
@@ -498,24 +498,27 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const float neg_lse2 = -p.lse[sidx] * LOG2E;
         float dlt;
         if (p.o != nullptr) {
-            // delta = rowsum(O * dO): one thread per row computes it, stores it for the dK/dV kernel and shares it
-            if (g == 0 && half == 0) {
-                const __nv_bfloat16* orow = p.o + (long long)b * p.so_b + (long long)i * p.so_s + (long long)h * p.so_h;
-                const __nv_bfloat16* drow = p.d_o + (long long)b * p.sdo_b + (long long)i * p.sdo_s + (long long)h * p.sdo_h;
-                float acc = 0.f;
-#pragma unroll 4
-                for (int d = 0; d < HD; d += 8) {
-                    float a8[8], c8[8];
-                    load8(orow + d, a8);
-                    load8(drow + d, c8);
+            // delta = rowsum(O * dO): the four element-wise threads of a row (2 groups x 2 halves) take 64 columns
+            // each, the partial sums meet in shared memory; thread (group 0, half 0) stores the row's delta for the
+            // dK/dV kernel
+            {
+                const int part = g * 2 + half;
+                const __nv_bfloat16* orow = p.o + (long long)b * p.so_b + (long long)i * p.so_s + (long long)h * p.so_h + part * (HD / 4);
+                const __nv_bfloat16* drow = p.d_o + (long long)b * p.sdo_b + (long long)i * p.sdo_s + (long long)h * p.sdo_h + part * (HD / 4);
+                float a8[8][8], c8[8][8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc = fmaf(a8[e], c8[e], acc);
-                }
-                delta_smem[r] = acc;
-                p.delta_out[sidx] = acc;
+                for (int d = 0; d < 8; ++d) { load8(orow + d * 8, a8[d]); load8(drow + d * 8, c8[d]); }
+                float acc = 0.f;
+#pragma unroll
+                for (int d = 0; d < 8; ++d)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc = fmaf(a8[d][e], c8[d][e], acc);
+                delta_smem[part * BM + r] = acc;
             }
             asm volatile("bar.sync 1, 512;" ::: "memory");     // the 16 element-wise warps
-            dlt = delta_smem[r];
+            const float dsum = (delta_smem[r] + delta_smem[BM + r]) + (delta_smem[2 * BM + r] + delta_smem[3 * BM + r]);
+            if (g == 0 && half == 0) p.delta_out[sidx] = dsum;
+            dlt = dsum;
         } else {
             dlt = p.delta[sidx];
         }
