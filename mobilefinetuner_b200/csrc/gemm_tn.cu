@@ -5,9 +5,14 @@
 // by reading U and V once from HBM; the tiny fp32 result is reduced across the
 // T-splits with atomics.  Warp-level mma.sync (m16n8k16, bf16 -> f32) with
 // ldmatrix.trans on both operands, cp.async double buffering.
+#include <cuda.h>
+
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
 
 namespace mft {
 
@@ -126,6 +131,123 @@ gemm_tn_kernel(const __nv_bfloat16* __restrict__ U, int64_t ldu, const __nv_bflo
     }
 }
 
+
+// ---------------------------------------------------------------- the same product on the tensor-memory path
+// U^T V with the token dimension as the MMA's K: both operands are consumed exactly as they lie in memory (rows =
+// tokens, features contiguous), i.e. as "MN-major" A and B operands of tcgen05.mma; nothing is transposed.
+// One CTA per (128 U-columns, 64 V-columns, token range): warp 0 streams [64 tokens x 64 columns] boxes with TMA
+// (128-byte swizzle, 4 stages), warp 1's one thread issues 4 MMAs per 64 tokens into a 128 x 64 f32 accumulator in
+// tensor memory, warps 2..5 add the result into `out` with f32 atomics (the token ranges of a tile meet there).
+namespace tn_tc {
+using namespace ptx;
+constexpr int PT = 128, QT = 64, TC = 64, STAGES = 4, THREADS = 192;
+constexpr int U_BYTES = 2 * TC * 128, V_BYTES = TC * 128, STAGE_BYTES = U_BYTES + V_BYTES;     // 16 KB + 8 KB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 128;
+
+__device__ __forceinline__ uint64_t desc_mn(uint32_t addr, uint32_t chunk_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((chunk_bytes >> 4) & 0x3FFF) << 16;     // distance between 64-column chunks
+    d |= (uint64_t)(1024 >> 4) << 32;                       // 8 token rows
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__global__ void __launch_bounds__(THREADS)
+gemm_tn_tc_kernel(const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_v, int64_t T, int P, int Q,
+                  float alpha, float* __restrict__ out, int64_t stride_p, int64_t stride_q, int64_t t_per_split, int32_t* status) {
+    dep_trigger();
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+    uint64_t* full_bar = bars;              // [STAGES]
+    uint64_t* empty_bar = bars + STAGES;    // [STAGES]
+    uint64_t* done_bar = bars + 2 * STAGES; // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p0 = blockIdx.x * PT, q0 = blockIdx.y * QT;
+    const int64_t t_begin = (int64_t)blockIdx.z * t_per_split;
+    const int64_t t_end = min(T, t_begin + t_per_split);
+    const int nsteps = t_begin < t_end ? (int)((t_end - t_begin + TC - 1) / TC) : 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(done_bar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&map_u); tma_prefetch_desc(&map_v);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 64); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    dep_wait();
+    if (nsteps > 0) {
+        if (warp == 0) {
+            if (lane == 0) {
+                for (int s = 0; s < nsteps; ++s) {
+                    const int st = s % STAGES;
+                    const uint32_t ph = (s / STAGES) & 1;
+                    if (!mbar_wait(&empty_bar[st], ph ^ 1, abort_flag)) break;
+                    uint8_t* u = tiles + st * STAGE_BYTES;
+                    const int row = (int)(t_begin + (int64_t)s * TC);
+                    mbar_arrive_expect_tx(&full_bar[st], STAGE_BYTES);
+                    tma_load_2d(u, &map_u, &full_bar[st], p0, row);
+                    tma_load_2d(u + TC * 128, &map_u, &full_bar[st], p0 + 64, row);
+                    tma_load_2d(u + U_BYTES, &map_v, &full_bar[st], q0, row);
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                const int n_eff = min(QT, (Q - q0 + 15) & ~15);
+                const uint32_t idesc = idesc_bf16_f32(PT, (uint32_t)n_eff) | (1u << 15) | (1u << 16);    // A and B MN-major
+                bool ok = true;
+                for (int s = 0; s < nsteps && ok; ++s) {
+                    const int st = s % STAGES;
+                    const uint32_t ph = (s / STAGES) & 1;
+                    if (!mbar_wait(&full_bar[st], ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t ua = smem_u32(tiles + st * STAGE_BYTES);
+                    const uint64_t ud = desc_mn(ua, TC * 128), vd = desc_mn(ua + U_BYTES, TC * 128);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        umma_bf16(tmem_base, ud + (uint64_t)(j * (2048 / 16)), vd + (uint64_t)(j * (2048 / 16)), idesc, (s | j) != 0 ? 1u : 0u);
+                    umma_commit(&empty_bar[st]);
+                }
+                if (ok) umma_commit(done_bar);
+            }
+        } else {
+            const int q4 = warp & 3;
+            const int p = p0 + q4 * 32 + lane;
+            if (mbar_wait(done_bar, 0, abort_flag)) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < QT; c += 32) {
+                    if (q0 + c >= Q) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    if (p < P) {
+#pragma unroll
+                        for (int x = 0; x < 32; ++x)
+                            if (q0 + c + x < Q) atomicAdd(out + (int64_t)p * stride_p + (int64_t)(q0 + c + x) * stride_q, alpha * __uint_as_float(r[x]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, MFT_ERR_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 64);
+    }
+}
+}  // namespace tn_tc
+
 }  // namespace mft
 
 using namespace mft;
@@ -161,6 +283,29 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
     t_per = (t_per + TN_TC - 1) / TN_TC * TN_TC;
     splits = (t + t_per - 1) / t_per;
     MFT_CHECK_ARG(tiles_q <= 65535, "mft_gemm_tn_acc: Q too large");
+    // Tensor-memory kernel: same tiles, 2 resident CTAs per SM.  Measured at 16384 tokens, rank 16: 42.5 us against
+    // 56.5 us at P = 6912 (5.3 TB/s), but 15.4 against 13.9 us at P = 1152, where each CTA streams only 8 boxes and its
+    // set-up (barriers, tensor-memory allocation) shows; so it takes the wide products only.
+    // MFT_TN_TC=0 keeps the mma.sync kernel everywhere, MFT_TN_TC=2 uses this one wherever it applies.
+    static const int use_tc = [] { const char* e = std::getenv("MFT_TN_TC"); return e ? std::atoi(e) : 1; }();
+    if (use_tc && device_status_word() && pp >= (use_tc >= 2 ? 64 : 2048) && t < (1ll << 31)) {
+        // token ranges in whole 64-token boxes, so that no box straddles two ranges
+        t_per = (t_per + tn_tc::TC - 1) / tn_tc::TC * tn_tc::TC;
+        splits = (t + t_per - 1) / t_per;
+        CUtensorMap mu, mv;
+        if (make_tmap_bf16(&mu, uu, t, pp, ldu2, tn_tc::TC) == MFT_OK && make_tmap_bf16(&mv, vv, t, qq, ldv2, tn_tc::TC) == MFT_OK) {
+            static bool tc_configured = false;
+            if (!tc_configured) {
+                if (int32_t s = check_cuda(cudaFuncSetAttribute(tn_tc::gemm_tn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tn_tc::SMEM_BYTES), "gemm_tn smem attr")) return s;
+                tc_configured = true;
+            }
+            dim3 grid_tc((unsigned)tiles_p, (unsigned)tiles_q, (unsigned)splits);
+            launch_dep(tn_tc::gemm_tn_tc_kernel, grid_tc, dim3(tn_tc::THREADS), (size_t)tn_tc::SMEM_BYTES, as_stream(stream), mu, mv, t, (int)pp, (int)qq,
+                       alpha, out, stride_p, stride_q, t_per, device_status_word());
+            MFT_LAUNCH_CHECK("gemm_tn_tc");
+            return MFT_OK;
+        }
+    }
     dim3 grid((unsigned)tiles_p, (unsigned)tiles_q, (unsigned)splits);
     constexpr int smem = (int)(sizeof(__nv_bfloat16) * TN_STAGES * TN_TC * (TN_US + TN_VS));
     static bool configured = false;

@@ -105,6 +105,26 @@ def test_gemm_tn_acc(ops, t, p, q):
     assert rel_err(host(out), want) < 2e-5
 
 
+@pytest.mark.parametrize("t,p,r,swap", [(2048 + 40, 1152, 16, False), (4096, 6912, 16, True), (1024, 256, 24, False)])
+def test_gemm_tn_acc_rank_slice(ops, t, p, r, swap):
+    """The LoRA-gradient shape: one operand is the first r columns of a 64-wide buffer (row stride 64).
+    P = 6912 takes the tcgen05 kernel (both operands MN-major), the narrower ones the mma.sync kernel."""
+    g = np.random.Generator(np.random.PCG64(t + p + r))
+    u = rb(g.standard_normal((t, p)))
+    wide = rb(g.standard_normal((t, 64)))
+    ud, wd = dev(u, torch.bfloat16), dev(wide, torch.bfloat16)
+    if swap:
+        want = wide[:, :r].astype(np.float64).T @ u.astype(np.float64)
+        out = torch.zeros(r, p, device="cuda")
+        ops.gemm_tn_acc(wd[:, :r], ud, out)
+    else:
+        want = u.astype(np.float64).T @ wide[:, :r].astype(np.float64)
+        out = torch.zeros(p, r, device="cuda")
+        ops.gemm_tn_acc(ud, wd[:, :r], out)
+    assert rel_err(host(out), want) < 2e-5
+    assert ops.device_status() == 0
+
+
 def lora_linear_cuda(ops, x, W, bias, A, B, scale, dY):
     """The LoRA-augmented linear as the step composes it: the rank-r update rides in the base
     GEMM as an extra 64-wide k-block (forward and dX); dA/dB are token-contracting TN products."""
