@@ -159,6 +159,15 @@ int32_t mft_ppl_result(const mft_ppl_accum_t* acc, float* mean_nll, float* ppl);
  * reference.  The [seq, V] logits are never formed: only the last position is projected. */
 int32_t mft_model_score_tokens(mft_model_t* m, const int32_t* ids_host, int32_t seq, const int32_t* cand_host,
                                int32_t n_cand, float* logprob_host);
+/* LoRALinear::merge_to_base / unmerge_from_base (nn/lora_linear.cpp:470-508; LoraInjector::merge / unmerge and
+ * GemmaLoraInjector::merge_all / unmerge_all call them per layer): fold scale * A B of every adapted slice into the
+ * device copies of the frozen weights, W[i, col0+o] += scale * float(sum_r double(A[i,r]) double(B[r,o])), rounded
+ * to the weights' bf16 storage as the reference rounds to its weight dtype.  While merged, forward / evaluation
+ * calls skip the adapter products and training calls (forward_backward, optimizer_step, set_lora) return
+ * MFT_ERR_INVALID_ARG.  Unmerge restores the saved weights byte for byte, as the reference's backup does. */
+int32_t mft_model_merge_lora(mft_model_t* m);
+int32_t mft_model_unmerge_lora(mft_model_t* m);
+int32_t mft_model_is_merged(const mft_model_t* m);
 /* clip (max_norm <= 0: none; clip_eps 0 = Optimizer::clip_grad_norm, 1e-6 = trainers) + Adam + zero_grad. */
 int32_t mft_model_optimizer_step(mft_model_t* m, float lr, float beta1, float beta2, float eps,
                                  float weight_decay, float max_norm, float clip_eps);

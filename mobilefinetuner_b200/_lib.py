@@ -165,6 +165,9 @@ _SIGS = {
     "mft_model_eval_ppl_batch": [vp, vp, vp, vp, i32, i32],
     "mft_ppl_result": [vp, vp, vp],
     "mft_model_score_tokens": [vp, vp, i32, vp, i32, vp],
+    "mft_model_merge_lora": [vp],
+    "mft_model_unmerge_lora": [vp],
+    "mft_model_is_merged": [vp],
     "mft_trainer_lr": [vp, i64],
     "mft_trainer_create": [vp, vp, vp],
     "mft_trainer_destroy": [vp],

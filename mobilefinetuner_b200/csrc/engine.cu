@@ -97,6 +97,7 @@ extern "C" int32_t mft_model_destroy(mft_model_t* m) {
         if (m->slot_ready[i]) cudaEventDestroy(m->slot_ready[i]);
         if (m->slot_free[i]) cudaEventDestroy(m->slot_free[i]);
     }
+    for (auto& b : m->merge_backup) { mft_free(b.w_nk); mft_free(b.w_kn); }
     for (void* p : m->allocations) mft_free(p);
     delete m;
     return MFT_OK;
@@ -462,6 +463,7 @@ extern "C" int32_t mft_model_lora_has_grad(const mft_model_t* m, int32_t idx) {
 }
 extern "C" int32_t mft_model_set_lora_host(mft_model_t* m, int32_t idx, const float* data_host) {
     MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->loras.size() && data_host, "mft_model_set_lora_host: bad argument");
+    MFT_CHECK_ARG(!m->merged, "mft_model_set_lora_host: the adapters are merged into the base weights: unmerge first");
     const LoraInfo& t = m->loras[idx];
     TRY(mft_memcpy_h2d(m->p_bucket + t.offset, data_host, (size_t)t.rows * t.cols * 4, m->stream));
     m->panels_dirty = true;
@@ -484,4 +486,85 @@ extern "C" int32_t mft_model_buckets(mft_model_t* m, float** params_dev, float**
     if (n) *n = m->bucket_n;
     return MFT_OK;
 }
+// ---------------------------------------------------------------- merge / unmerge of the adapters
+// LoRALinear::merge_to_base (nn/lora_linear.cpp:470-483, apply_lora_delta_to_base :107-139): for every adapted slice
+//   W[i, col0 + o] <- W[i, col0 + o] + scale * float( sum_r double(A[i,r]) * double(B[r,o]) ),
+// written back in the weight's storage type (bf16 here); both device layouts of the weight get the same value.
+// unmerge_from_base (:485-508) restores the saved bytes.
+namespace {
+__global__ void lora_merge_kernel(const float* __restrict__ A, const float* __restrict__ B, int a_is_r_by_in, int in, int out, int r,
+                                  float scale, mft::bf16* __restrict__ w_nk, mft::bf16* __restrict__ w_kn, int n_total, int col0) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)in * out) return;
+    const int i = (int)(idx / out), o = (int)(idx % out);
+    double delta = 0.0;
+    for (int k = 0; k < r; ++k) {
+        const float a = a_is_r_by_in ? A[(int64_t)k * in + i] : A[(int64_t)i * r + k];      // Gemma keeps A [r,in], B [out,r]
+        const float b = a_is_r_by_in ? B[(int64_t)o * r + k] : B[(int64_t)k * out + o];
+        delta += (double)a * (double)b;
+    }
+    const int64_t kn = (int64_t)i * n_total + col0 + o;
+    const float updated = __fadd_rn(__bfloat162float(w_kn[kn]), __fmul_rn(scale, (float)delta));
+    const mft::bf16 v = __float2bfloat16_rn(updated);
+    w_kn[kn] = v;
+    w_nk[(int64_t)(col0 + o) * in + i] = v;
+}
+}  // namespace
+
+extern "C" int32_t mft_model_merge_lora(mft_model_t* m) {
+    MFT_CHECK_ARG(m, "mft_model_merge_lora: null model");
+    if (m->merged || m->cfg.lora_rank <= 0) return MFT_OK;
+    const bool gemma = m->cfg.family == MFT_FAMILY_GEMMA;
+    const int r = m->cfg.lora_rank;
+    const float scale = m->cfg.lora_alpha / (float)r;
+    for (auto& w : m->layers)
+        for (LinearGroup* g : {&w.qkv, &w.o, &w.gu, &w.down}) {
+            if (!g->any_lora) continue;
+            const size_t bytes = (size_t)g->in * g->n_total * sizeof(bf16);
+            void *b1 = nullptr, *b2 = nullptr;
+            int32_t s = mft_malloc(bytes, &b1);
+            if (s == MFT_OK) s = mft_malloc(bytes, &b2);
+            if (s == MFT_OK) s = mft_memcpy_d2d(b1, g->w_nk, bytes, m->stream);
+            if (s == MFT_OK) s = mft_memcpy_d2d(b2, g->w_kn, bytes, m->stream);
+            if (s != MFT_OK) {
+                if (b1) mft_free(b1);
+                if (b2) mft_free(b2);
+                m->merged = true;                  // so that the partial merge is rolled back
+                mft_model_unmerge_lora(m);
+                return s;
+            }
+            m->merge_backup.push_back({g, static_cast<bf16*>(b1), static_cast<bf16*>(b2)});
+            for (auto& sl : g->slots) {
+                if (!sl.has_lora) continue;
+                const float* A = m->p_bucket + m->loras[sl.lora_idx].offset;
+                const float* B = m->p_bucket + m->loras[sl.lora_idx + 1].offset;
+                const int64_t n = (int64_t)sl.in * sl.out;
+                lora_merge_kernel<<<(unsigned)((n + 255) / 256), 256, 0, m->stream>>>(A, B, gemma ? 1 : 0, sl.in, sl.out, r, scale, g->w_nk, g->w_kn,
+                                                                                      g->n_total, sl.col0);
+                MFT_LAUNCH_CHECK("lora_merge");
+            }
+        }
+    m->merged = true;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_model_unmerge_lora(mft_model_t* m) {
+    MFT_CHECK_ARG(m, "mft_model_unmerge_lora: null model");
+    if (!m->merged) return MFT_OK;
+    int32_t first = MFT_OK;
+    for (auto& b : m->merge_backup) {
+        const size_t bytes = (size_t)b.group->in * b.group->n_total * sizeof(bf16);
+        int32_t s = mft_memcpy_d2d(b.group->w_nk, b.w_nk, bytes, m->stream);
+        if (s == MFT_OK) s = mft_memcpy_d2d(b.group->w_kn, b.w_kn, bytes, m->stream);
+        if (s != MFT_OK && first == MFT_OK) first = s;
+    }
+    if (int32_t s = check_cuda(cudaStreamSynchronize(m->stream), "unmerge sync")) { if (first == MFT_OK) first = s; }
+    for (auto& b : m->merge_backup) { mft_free(b.w_nk); mft_free(b.w_kn); }
+    m->merge_backup.clear();
+    m->merged = false;
+    return first;
+}
+
+extern "C" int32_t mft_model_is_merged(const mft_model_t* m) { return m && m->merged ? 1 : 0; }
+
 extern "C" int64_t mft_model_activation_bytes(const mft_model_t* m) { return m ? m->activation_bytes : 0; }

@@ -140,6 +140,11 @@ struct mft_model {
     int n_pack = 0, n_unpack = 0;
     float* grad_pan_base = nullptr; int64_t grad_pan_floats = 0;
     bool panels_dirty = true;
+    // LoRA merged into the frozen weights (evaluation / export): forward passes skip the adapter products, training
+    // calls are refused.  The backups restore the weights byte for byte on unmerge.
+    bool merged = false;
+    struct MergeBackup { mft::LinearGroup* group; mft::bf16* w_nk; mft::bf16* w_kn; };
+    std::vector<MergeBackup> merge_backup;
 
     // rope tables
     float *cos_g = nullptr, *sin_g = nullptr, *cos_l = nullptr, *sin_l = nullptr;

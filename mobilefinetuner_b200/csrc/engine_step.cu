@@ -29,7 +29,7 @@ struct Ctx {
 // y[T, n_total] = x W (+ bias) + scale (x A) B for every linear of the group, one GEMM
 // (plus the 64-column x A panel product when the group carries LoRA).
 int32_t group_fwd(const Ctx& c, LinearGroup& g, const bf16* x, bf16* xa, bf16* y) {
-    if (g.any_lora) {
+    if (g.any_lora && !c.m->merged) {
         TRY(mft_gemm_nt(x, g.in, g.a_nk, g.in, c.T, 64, g.in, nullptr, 0, nullptr, 0, 0, nullptr, c.lora_scale, xa, 64, MFT_BF16, 0, c.st));
         return mft_gemm_nt(x, g.in, g.w_nk, g.in, c.T, g.n_total, g.in, xa, 64, g.b_nk, 64, g.k2, g.bias, 1.0f, y, g.n_total, MFT_BF16, 0, c.st);
     }
@@ -240,6 +240,7 @@ int32_t check_status(mft_model* m) {
 // capture (a profiling hook, a failing call) falls back to issuing the launches directly.
 int32_t forward_backward(Ctx& c, int64_t n_valid_global) {
     mft_model* m = c.m;
+    if (m->merged) return fail(MFT_ERR_INVALID_ARG, "the adapters are merged into the base weights: call mft_model_unmerge_lora before training");
     auto eager = [&]() -> int32_t {
         TRY(forward(c, true, n_valid_global));
         return backward(c, n_valid_global);
@@ -454,6 +455,7 @@ extern "C" int32_t mft_model_score_tokens(mft_model_t* m, const int32_t* ids_hos
 extern "C" int32_t mft_model_optimizer_step(mft_model_t* m, float lr, float beta1, float beta2, float eps, float weight_decay,
                                             float max_norm, float clip_eps) {
     MFT_CHECK_ARG(m, "mft_model_optimizer_step: null model");
+    MFT_CHECK_ARG(!m->merged, "mft_model_optimizer_step: the adapters are merged into the base weights");
     if (m->bucket_n == 0) return MFT_OK;
     m->adam_step += 1;
     const float* sq = nullptr;

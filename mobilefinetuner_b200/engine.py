@@ -162,6 +162,19 @@ class LoraStepEngine:
         L.call("mft_model_score_tokens", self._h, ids.ctypes.data, ids.size, cand.ctypes.data, cand.size, out.ctypes.data)
         return out
 
+    def merge_to_base(self):
+        """Fold scale * A B into the device weights (LoRALinear::merge_to_base, nn/lora_linear.cpp:470-483); forward and
+        evaluation calls then skip the adapter products, training calls raise until unmerge_from_base()."""
+        L.call("mft_model_merge_lora", self._h)
+
+    def unmerge_from_base(self):
+        """Restore the weights saved by merge_to_base() byte for byte (nn/lora_linear.cpp:485-508)."""
+        L.call("mft_model_unmerge_lora", self._h)
+
+    @property
+    def is_merged(self) -> bool:
+        return bool(L.load().mft_model_is_merged(self._h))
+
     def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, max_grad_norm=0.0, clip_eps=0.0):
         L.call("mft_model_optimizer_step", self._h, float(lr), float(beta1), float(beta2), float(eps), float(weight_decay),
                float(max_grad_norm), float(clip_eps))

@@ -346,6 +346,66 @@ def test_evaluation_drivers_perplexity_and_letter_scores():
     eng.close()
 
 
+@pytest.mark.parametrize("name", ["gemma_tiny", "qwen_tiny", "gpt2_tiny"])
+def test_merge_to_base_and_unmerge(name):
+    """LoRALinear::merge_to_base / unmerge_from_base on the device weights: the merged forward agrees with the
+    adapter forward (bf16 path tolerance), equals an engine that was GIVEN W + scale * A B (the reference's update
+    rule evaluated in numpy: double accumulation, float update, rounded to the bf16 storage) with idle adapters, training
+    is refused while merged, and unmerge brings the original loss back."""
+    from mobilefinetuner_b200 import synth
+    from mobilefinetuner_b200._lib import MftError
+    from mobilefinetuner_b200.configs import GEMMA
+    from mobilefinetuner_b200.engine import LoraStepEngine
+    case = CASES[name]
+    spec = case["spec"]
+    B, S = case["batch"], case["seq"]
+    params = [synth.bf16_round(p) if p.ndim == 2 else p for p in synth.make_params(spec, case["seeds"][0], case["norm_jitter"])]
+    lora = synth.make_lora(spec, case["seeds"][1])
+    ids, labels = synth.make_batch(spec, B, S, case["seeds"][2])
+    eng = LoraStepEngine(spec, B, S)
+    eng.set_params(params); eng.set_lora(lora)
+    loss0 = eng.forward_loss(ids, labels)
+    eng.merge_to_base()
+    assert eng.is_merged
+    loss_m = eng.forward_loss(ids, labels)
+    assert abs(loss_m - loss0) <= LOSS_REL * abs(loss0)
+    with pytest.raises(MftError):
+        eng.forward_backward(ids, labels)
+    with pytest.raises(MftError):
+        eng.set_lora(lora)
+    eng.merge_to_base()                                   # a second merge is a no-op, as in the reference
+    assert abs(eng.forward_loss(ids, labels) - loss_m) <= 1e-6 * abs(loss_m)
+
+    # the same update in numpy, applied to the frozen weights of a second engine whose adapters contribute nothing
+    linear_idx = [i for i, (kind, _) in enumerate(spec.param_shapes()) if kind == "linear"]
+    per_layer = len(linear_idx) // spec.layers
+    order = {"q_proj": 0, "k_proj": 1, "v_proj": 2, "o_proj": 3, "gate_proj": 4, "up_proj": 5, "down_proj": 6,
+             "c_attn": 0, "c_proj": 1, "c_fc": 2, "mlp_c_proj": 3}
+    names = [n for n, _ in spec.lora_shapes()]
+    per_layer_lora = len(names) // spec.layers
+    scale = np.float32(spec.lora_alpha / spec.lora_rank)
+    merged = [p.copy() for p in params]
+    for j in range(0, len(names), 2):
+        layer, target = j // per_layer_lora, names[j][:-2]
+        A, Bm = lora[j].astype(np.float64), lora[j + 1].astype(np.float64)
+        delta = (A.T @ Bm.T) if spec.family == GEMMA else (A @ Bm)               # [in, out]
+        w = merged[linear_idx[layer * per_layer + order[target]]]
+        w += scale * delta.astype(np.float32)
+    idle = [a if n.endswith(".A") else np.zeros_like(a) for a, (n, _) in zip(lora, spec.lora_shapes())]
+    eng2 = LoraStepEngine(spec, B, S)
+    eng2.set_params(merged); eng2.set_lora(idle)
+    loss2 = eng2.forward_loss(ids, labels)
+    eng2.close()
+    assert abs(loss2 - loss_m) <= 1e-6 * abs(loss_m)
+
+    eng.unmerge_from_base()
+    assert not eng.is_merged
+    assert abs(eng.forward_loss(ids, labels) - loss0) <= 1e-6 * abs(loss0)
+    loss_t, _ = eng.forward_backward(ids, labels)         # training works again
+    assert abs(loss_t - loss0) <= LOSS_REL * abs(loss0)
+    eng.close()
+
+
 def test_out_of_range_token_raises():
     from mobilefinetuner_b200 import synth
     from mobilefinetuner_b200._lib import MftError
