@@ -252,10 +252,24 @@ __global__ void attn_delta_kernel(const AttnParams p) {
     const __nv_bfloat16* orow = p.o + (int64_t)b * p.so.stride_b + (int64_t)i * p.so.stride_s + (int64_t)h * p.so.stride_h;
     const __nv_bfloat16* drow = p.d_o + (int64_t)b * p.sdo.stride_b + (int64_t)i * p.sdo.stride_s + (int64_t)h * p.sdo.stride_h;
     float acc = 0.f;
-    for (int d = lane * 2; d < HD; d += 64) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(orow + d));
-        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(drow + d));
-        acc += a.x * c.x + a.y * c.y;
+    if (HD >= 256 && ((reinterpret_cast<uintptr_t>(orow) | reinterpret_cast<uintptr_t>(drow)) & 15) == 0) {
+        // 16-byte accesses: one per operand and lane at head_dim 256
+        for (int d = lane * 8; d < HD; d += 256) {
+            const uint4 a4 = *reinterpret_cast<const uint4*>(orow + d), c4 = *reinterpret_cast<const uint4*>(drow + d);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a4);
+            const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 a = __bfloat1622float2(a2[j]), c = __bfloat1622float2(c2[j]);
+                acc += a.x * c.x + a.y * c.y;
+            }
+        }
+    } else {
+        for (int d = lane * 2; d < HD; d += 64) {
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(orow + d));
+            const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(drow + d));
+            acc += a.x * c.x + a.y * c.y;
+        }
     }
     acc = warp_sum(acc);
     if (lane == 0) p.delta[wid] = acc;

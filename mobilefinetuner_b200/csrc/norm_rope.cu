@@ -493,9 +493,52 @@ layernorm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const
 }
 
 // ---------------------------------------------------------------- per-head norm + RoPE
+// PER consecutive elements in one access when VEC (the launcher has checked the alignment), one by one otherwise.
+template <int PER, bool VEC>
+__device__ __forceinline__ void ld_bf16_run(const __nv_bfloat16* p, float (&v)[PER]) {
+    if constexpr (VEC && PER == 4) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+    } else if constexpr (VEC && PER == 2) {
+        const __nv_bfloat162 u = *reinterpret_cast<const __nv_bfloat162*>(p);
+        v[0] = __low2float(u); v[1] = __high2float(u);
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) v[j] = bf16_to_f32(p[j]);
+    }
+}
+template <int PER, bool VEC>
+__device__ __forceinline__ void st_bf16_run(__nv_bfloat16* p, const float (&v)[PER]) {
+    if constexpr (VEC && PER == 4) {
+        const __nv_bfloat162 lo = __halves2bfloat162(f32_to_bf16(v[0]), f32_to_bf16(v[1])), hi = __halves2bfloat162(f32_to_bf16(v[2]), f32_to_bf16(v[3]));
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t*>(&lo); u.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = u;
+    } else if constexpr (VEC && PER == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __halves2bfloat162(f32_to_bf16(v[0]), f32_to_bf16(v[1]));
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) p[j] = f32_to_bf16(v[j]);
+    }
+}
+template <int PER, bool VEC>
+__device__ __forceinline__ void ld_f32_run(const float* p, float (&v)[PER]) {
+    if constexpr (VEC && PER == 4) {
+        const float4 u = __ldg(reinterpret_cast<const float4*>(p));
+        v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+    } else if constexpr (VEC && PER == 2) {
+        const float2 u = __ldg(reinterpret_cast<const float2*>(p));
+        v[0] = u.x; v[1] = u.y;
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) v[j] = __ldg(p + j);
+    }
+}
+
 // One warp per (token, head).  Lane l owns PER = head_dim/64 consecutive
 // elements of the first half (d = l*PER ..) and the paired elements d + hd/2.
-template <int PER, bool BWD>
+template <int PER, bool BWD, bool VEC>
 __global__ void headnorm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64_t ld_in,   // fwd: x ; bwd: dy
                                      const __nv_bfloat16* __restrict__ x, int64_t ld_x,     // bwd only: forward input
                                      const float* __restrict__ nw, float eps,
@@ -515,20 +558,26 @@ __global__ void headnorm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64
     float a[PER], b[PER];   // first-half / second-half values of `in`
     {
         const __nv_bfloat16* p = in + tok * ld_in + head * HD;
-#pragma unroll
-        for (int j = 0; j < PER; ++j) { a[j] = bf16_to_f32(p[d0 + j]); b[j] = bf16_to_f32(p[HALF + d0 + j]); }
+        ld_bf16_run<PER, VEC>(p + d0, a);
+        ld_bf16_run<PER, VEC>(p + HALF + d0, b);
     }
     float c[PER], s[PER];
+    if (cos_tab) {
+        ld_f32_run<PER, VEC>(cos_tab + pos * HALF + d0, c);
+        ld_f32_run<PER, VEC>(sin_tab + pos * HALF + d0, s);
+    } else {
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        if (cos_tab) { c[j] = cos_tab[pos * HALF + d0 + j]; s[j] = sin_tab[pos * HALF + d0 + j]; }
-        else { c[j] = 1.f; s[j] = 0.f; }
+        for (int j = 0; j < PER; ++j) { c[j] = 1.f; s[j] = 0.f; }
     }
     float w1[PER], w2[PER];
+    if (nw) {
+        ld_f32_run<PER, VEC>(nw + d0, w1);
+        ld_f32_run<PER, VEC>(nw + HALF + d0, w2);
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        w1[j] = nw ? 1.0f + nw[d0 + j] : 1.0f;
-        w2[j] = nw ? 1.0f + nw[HALF + d0 + j] : 1.0f;
+        for (int j = 0; j < PER; ++j) { w1[j] = 1.0f + w1[j]; w2[j] = 1.0f + w2[j]; }
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) { w1[j] = 1.0f; w2[j] = 1.0f; }
     }
     __nv_bfloat16* o = out + tok * ld_out + head * HD;
     if (!BWD) {
@@ -541,12 +590,15 @@ __global__ void headnorm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64
             rstd = rsqrtf(ss / (float)HD + eps);
             if (lane == 0 && rstd_buf) rstd_buf[wid] = rstd;
         }
+        float y1[PER], y2[PER];
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const float x1 = a[j] * rstd * w1[j], x2 = b[j] * rstd * w2[j];
-            o[d0 + j] = f32_to_bf16(x1 * c[j] - x2 * s[j]);
-            o[HALF + d0 + j] = f32_to_bf16(x1 * s[j] + x2 * c[j]);
+            y1[j] = x1 * c[j] - x2 * s[j];
+            y2[j] = x1 * s[j] + x2 * c[j];
         }
+        st_bf16_run<PER, VEC>(o + d0, y1);
+        st_bf16_run<PER, VEC>(o + HALF + d0, y2);
     } else {
         // undo the rotation: dxn1 = dy1*c + dy2*s ; dxn2 = -dy1*s + dy2*c
         float g1[PER], g2[PER];
@@ -559,9 +611,10 @@ __global__ void headnorm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64
             const __nv_bfloat16* xp = x + tok * ld_x + head * HD;
             float x1[PER], x2[PER];
             float dot = 0.f;
+            ld_bf16_run<PER, VEC>(xp + d0, x1);
+            ld_bf16_run<PER, VEC>(xp + HALF + d0, x2);
 #pragma unroll
             for (int j = 0; j < PER; ++j) {
-                x1[j] = bf16_to_f32(xp[d0 + j]); x2[j] = bf16_to_f32(xp[HALF + d0 + j]);
                 g1[j] *= w1[j]; g2[j] *= w2[j];
                 dot += g1[j] * x1[j] + g2[j] * x2[j];
             }
@@ -574,8 +627,8 @@ __global__ void headnorm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64
                 g2[j] = g2[j] * rstd - x2[j] * coeff;
             }
         }
-#pragma unroll
-        for (int j = 0; j < PER; ++j) { o[d0 + j] = f32_to_bf16(g1[j]); o[HALF + d0 + j] = f32_to_bf16(g2[j]); }
+        st_bf16_run<PER, VEC>(o + d0, g1);
+        st_bf16_run<PER, VEC>(o + HALF + d0, g2);
     }
 }
 
@@ -714,12 +767,18 @@ static int32_t launch_headnorm_rope(bool bwd, const void* in, int64_t ld_in, con
     const int64_t warps = n_tokens * n_heads;
     const int threads = 256;
     const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
-#define HL(PER, B) launch_dep(headnorm_rope_kernel<PER, B>, dim3(blocks), dim3(threads), (size_t)(0), as_stream(stream), (const __nv_bfloat16*)in, ld_in, (const __nv_bfloat16*)x, ld_x, nw, eps, rstd, cos_tab, sin_tab, (__nv_bfloat16*)out, ld_out, n_tokens, seq_len, n_heads)
-    if (hd == 64) { if (bwd) HL(1, true); else HL(1, false); }
+    // one 4- / 8-byte access per run of a lane's elements when every operand allows it
+    auto al = [](const void* p, uintptr_t a) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % a == 0; };
+    const bool vec = al(in, 8) && al(x, 8) && al(out, 8) && al(nw, 16) && al(cos_tab, 16) && al(sin_tab, 16) && ld_in % 4 == 0 &&
+                     ld_out % 4 == 0 && (x == nullptr || ld_x % 4 == 0);
+#define HL(PER, B) do { if (vec) HL2(PER, B, true); else HL2(PER, B, false); } while (0)
+#define HL2(PER, B, V) launch_dep(headnorm_rope_kernel<PER, B, V>, dim3(blocks), dim3(threads), (size_t)(0), as_stream(stream), (const __nv_bfloat16*)in, ld_in, (const __nv_bfloat16*)x, ld_x, nw, eps, rstd, cos_tab, sin_tab, (__nv_bfloat16*)out, ld_out, n_tokens, seq_len, n_heads)
+    if (hd == 64) { if (bwd) HL2(1, true, false); else HL2(1, false, false); }
     else if (hd == 128) { if (bwd) HL(2, true); else HL(2, false); }
     else if (hd == 256) { if (bwd) HL(4, true); else HL(4, false); }
     else return fail(MFT_ERR_UNSUPPORTED, "headnorm_rope: head_dim must be 64, 128 or 256");
 #undef HL
+#undef HL2
     MFT_LAUNCH_CHECK("headnorm_rope");
     return MFT_OK;
 }
