@@ -235,6 +235,10 @@ rmsnorm_bwd_warp_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, co
 }
 
 
+// Ask for the 32 bytes at p early (no register is held): the fused norm kernels read some rows only after a
+// warp reduction, and without this their latency adds to that of the first loads.
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" :: "l"(p)); }
+
 // ---------------------------------------------------------------- fused post-norm + residual add + next pre-norm
 // Gemma wraps every block as  x_sum = x + rms(y_branch) ,  h_next = rms(x_sum)  (post-norm of one block, residual
 // add, pre-norm of the next).  One warp per row keeps x_sum in registers between the two norms, so x_sum is
@@ -257,6 +261,11 @@ rmsnorm_add_norm_fwd_kernel(const __nv_bfloat16* __restrict__ y, const float* __
     for (int k = 0; k < VPL; ++k) {
         const int i = lane + k * 32;
         if (i < nvec) load8(y + row * dim + i * 8, v[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) prefetch_l1(residual + row * dim + i * 8);
     }
 #pragma unroll
     for (int k = 0; k < VPL; ++k)
@@ -326,6 +335,14 @@ rmsnorm_pair_bwd_kernel(const __nv_bfloat16* __restrict__ dy_next, const float* 
         if (i < nvec) {
             load8(x_sum + row * dim + i * 8, xv[k]);
             load8(dy_next + row * dim + i * 8, g[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+        const int i = lane + k * 32;
+        if (i < nvec) {
+            prefetch_l1(dx + row * dim + i * 8);
+            if ((i & 1) == 0) prefetch_l1(y_branch + row * dim + i * 8);      // 16-byte pieces: every other lane names a new 32 bytes
         }
     }
     float dot = 0.f;
