@@ -595,10 +595,28 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 constexpr int KV_BQ = 32;                              // queries per tile
 constexpr int KV_Q_BYTES = KV_BQ * HD * 2;             // 4 chunks of [32 rows x 64 columns]
 constexpr int KV_STATS_BYTES = 2 * KV_BQ * 4;          // lse, delta of the tile's queries
-constexpr int KV_PDS_BYTES = BM * 128;                 // [128 keys x 128 bytes]: P^T in bytes 0..63, dS^T in 64..127
-constexpr int DKV_SMEM = 2 * Q_BYTES + 4 * KV_Q_BYTES + 2 * KV_PDS_BYTES + 2 * KV_STATS_BYTES + 192;
+constexpr int KV_STAGES = 3;                           // Q / dO stages: the load of tile t+2 must not wait for the MMAs of tile t
+constexpr int DKV_SMEM = 2 * Q_BYTES + KV_STAGES * 2 * KV_Q_BYTES + KV_STAGES * KV_STATS_BYTES + 256;
 constexpr int DKV_THREADS = 64 + 2 * 256 + 64;         // TMA warp, S^T issuer, 16 element-wise warps, dP^T issuer, dV/dK issuer
 constexpr int KV_S_COL = 0, KV_DP_COL = 64, KV_DK_COL = 128, KV_DV_COL = 256;
+constexpr int KV_PDS_COL = 384;                        // per group 32 columns: P^T (16: 32 queries as bf16 pairs) | dS^T (16)
+
+// A operand from tensor memory (lane = row, two bf16 of consecutive k per 32-bit column), B from shared memory.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :
+                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -614,20 +632,19 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* k_smem = smem_raw;                            // [128 keys x 256], 4 chunks
     uint8_t* v_smem = k_smem + Q_BYTES;
-    uint8_t* q_smem = v_smem + Q_BYTES;                    // 2 stages
-    uint8_t* do_smem = q_smem + 2 * KV_Q_BYTES;            // 2 stages
-    uint8_t* pds_smem = do_smem + 2 * KV_Q_BYTES;          // 2 buffers (one per group)
-    float* stats = reinterpret_cast<float*>(pds_smem + 2 * KV_PDS_BYTES);   // [2 stages][lse 32 | delta 32]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + 2 * KV_STATS_BYTES);
+    uint8_t* q_smem = v_smem + Q_BYTES;                    // KV_STAGES stages
+    uint8_t* do_smem = q_smem + KV_STAGES * KV_Q_BYTES;    // KV_STAGES stages
+    float* stats = reinterpret_cast<float*>(do_smem + KV_STAGES * KV_Q_BYTES);   // [stage][lse 32 | delta 32]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stats) + KV_STAGES * KV_STATS_BYTES);
     uint64_t* kv_full = bars;           // [1]
-    uint64_t* qdo_full = bars + 1;      // [2]
-    uint64_t* qdo_empty = bars + 3;     // [2]
-    uint64_t* sdp_full = bars + 5;      // [2]  two arrivals (S^T and dP^T)
-    uint64_t* sdp_free = bars + 7;      // [2]  256 arrivals
-    uint64_t* pds_full = bars + 9;      // [2]  256 arrivals
-    uint64_t* pds_free = bars + 11;     // [2]
-    uint64_t* acc_done = bars + 13;     // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t* qdo_full = bars + 1;      // [3]
+    uint64_t* qdo_empty = bars + 4;     // [3]
+    uint64_t* sdp_full = bars + 7;      // [2]  two arrivals (S^T and dP^T)
+    uint64_t* sdp_free = bars + 9;      // [2]  256 arrivals
+    uint64_t* pds_full = bars + 11;     // [2]  256 arrivals
+    uint64_t* pds_free = bars + 13;     // [2]
+    uint64_t* acc_done = bars + 15;     // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     if ((smem_u32(smem_raw) & 1023u) != 0) {
         if (threadIdx.x == 0 && p.status) atomicExch(p.status, MFT_ERR_INVALID_ARG);
@@ -645,8 +662,8 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1);
             mbar_init(&sdp_full[s], 2); mbar_init(&sdp_free[s], 256); mbar_init(&pds_full[s], 256); mbar_init(&pds_free[s], 1);
         }
         mbar_init(acc_done, 1);
@@ -667,16 +684,17 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             for (int c = 0; c < 4; ++c) tma_load_2d(k_smem + c * (BM * 128), &map_k, kv_full, kvh * p.k_col0_stride + c * 64, b * p.seq + j0);
             for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + c * (BM * 128), &map_v, kv_full, kvh * p.v_col0_stride + c * 64, b * p.seq + j0);
             const long long srow = ((long long)b * p.n_heads + h) * p.seq;
+            int st = 0;
+            uint32_t sph = 0;                           // stage of tile t and its phase parity (t / KV_STAGES) & 1
             for (int t = 0; t < n_tiles; ++t) {
-                const int g = t & 1;
-                const uint32_t ph = (t >> 1) & 1;
                 const int i0 = (qs_lo + t) * KV_BQ;
-                if (!mbar_wait(&qdo_empty[g], ph ^ 1, abort_flag)) break;
-                mbar_arrive_expect_tx(&qdo_full[g], 2 * KV_Q_BYTES + KV_STATS_BYTES);
-                for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + g * KV_Q_BYTES + c * (KV_BQ * 128), &map_q, &qdo_full[g], h * p.q_col0_stride + c * 64, b * p.seq + i0);
-                for (int c = 0; c < 4; ++c) tma_load_2d(do_smem + g * KV_Q_BYTES + c * (KV_BQ * 128), &map_do, &qdo_full[g], h * p.do_col0_stride + c * 64, b * p.seq + i0);
-                bulk_load_1d(stats + g * 2 * KV_BQ, p.lse + srow + i0, KV_BQ * 4, &qdo_full[g]);
-                bulk_load_1d(stats + g * 2 * KV_BQ + KV_BQ, p.delta + srow + i0, KV_BQ * 4, &qdo_full[g]);
+                if (!mbar_wait(&qdo_empty[st], sph ^ 1, abort_flag)) break;
+                mbar_arrive_expect_tx(&qdo_full[st], 2 * KV_Q_BYTES + KV_STATS_BYTES);
+                for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + st * KV_Q_BYTES + c * (KV_BQ * 128), &map_q, &qdo_full[st], h * p.q_col0_stride + c * 64, b * p.seq + i0);
+                for (int c = 0; c < 4; ++c) tma_load_2d(do_smem + st * KV_Q_BYTES + c * (KV_BQ * 128), &map_do, &qdo_full[st], h * p.do_col0_stride + c * 64, b * p.seq + i0);
+                bulk_load_1d(stats + st * 2 * KV_BQ, p.lse + srow + i0, KV_BQ * 4, &qdo_full[st]);
+                bulk_load_1d(stats + st * 2 * KV_BQ + KV_BQ, p.delta + srow + i0, KV_BQ * 4, &qdo_full[st]);
+                if (++st == KV_STAGES) { st = 0; sph ^= 1; }
             }
         }
     } else if (warp == 1 || warp == 18) {
@@ -686,12 +704,14 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const bool is_s = warp == 1;
             bool ok = mbar_wait(kv_full, 0, abort_flag);
             const uint64_t ad = smem_desc_sw128(smem_u32(is_s ? k_smem : v_smem));
+            int st = 0;
+            uint32_t sph = 0;
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int g = t & 1;
                 const uint32_t ph = (t >> 1) & 1;
-                if (!mbar_wait(&qdo_full[g], ph, abort_flag) || !mbar_wait(&sdp_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&qdo_full[st], sph, abort_flag) || !mbar_wait(&sdp_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t bd = smem_desc_sw128(smem_u32((is_s ? q_smem : do_smem) + g * KV_Q_BYTES));
+                const uint64_t bd = smem_desc_sw128(smem_u32((is_s ? q_smem : do_smem) + st * KV_Q_BYTES));
                 const uint32_t tmem_d = tmem_base + (is_s ? KV_S_COL : KV_DP_COL) + g * KV_BQ;
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -700,6 +720,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         umma_bf16(tmem_d, ad + (uint64_t)(c * (BM * 128 / 16) + 2 * j), bd + (uint64_t)(c * (KV_BQ * 128 / 16) + 2 * j), idesc_s,
                                   (c | j) != 0 ? 1u : 0u);
                 umma_commit(&sdp_full[g]);
+                if (++st == KV_STAGES) { st = 0; sph ^= 1; }
             }
         }
     } else if (warp == 19) {
@@ -707,23 +728,26 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (lane == 0) {
             constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, HD / 2) | IDESC_B_MN;
             bool ok = true;
+            int st = 0;
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int g = t & 1;
                 const uint32_t ph = (t >> 1) & 1;
                 if (!mbar_wait(&pds_full[g], ph, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t pd = smem_desc_sw128(smem_u32(pds_smem + g * KV_PDS_BYTES));
-                const uint64_t dod = smem_desc_mn_sw128(smem_u32(do_smem + g * KV_Q_BYTES + hh * 2 * (KV_BQ * 128)), KV_BQ * 128);
-                const uint64_t qd = smem_desc_mn_sw128(smem_u32(q_smem + g * KV_Q_BYTES + hh * 2 * (KV_BQ * 128)), KV_BQ * 128);
+                // A operands P^T / dS^T come from tensor memory (8 columns per 16 queries), B operands dO / Q MN-major from the stage
+                const uint32_t pa = tmem_base + KV_PDS_COL + g * 32;
+                const uint64_t dod = smem_desc_mn_sw128(smem_u32(do_smem + st * KV_Q_BYTES + hh * 2 * (KV_BQ * 128)), KV_BQ * 128);
+                const uint64_t qd = smem_desc_mn_sw128(smem_u32(q_smem + st * KV_Q_BYTES + hh * 2 * (KV_BQ * 128)), KV_BQ * 128);
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                    umma_bf16(tmem_base + KV_DV_COL, pd + (uint64_t)(2 * j), dod + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
+                    umma_bf16_ts(tmem_base + KV_DV_COL, pa + 8 * j, dod + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                    umma_bf16(tmem_base + KV_DK_COL, pd + (uint64_t)(4 + 2 * j), qd + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
-                umma_commit(&qdo_empty[g]);
+                    umma_bf16_ts(tmem_base + KV_DK_COL, pa + 16 + 8 * j, qd + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
+                umma_commit(&qdo_empty[st]);
                 umma_commit(&pds_free[g]);
                 if (t == n_tiles - 1) umma_commit(acc_done);
+                if (++st == KV_STAGES) st = 0;
             }
         }
     } else {
@@ -748,7 +772,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tc_fence_before();
             mbar_arrive(&sdp_free[g]);
             // lse / delta of the 16 queries (the stage's loads completed before S^T was issued)
-            const float* st_l = stats + g * 2 * KV_BQ + half * 16;
+            const float* st_l = stats + (t % KV_STAGES) * 2 * KV_BQ + half * 16;
             const float* st_d = st_l + KV_BQ;
             const bool need_mask = (i0 < j0 + BM - 1) || (p.window > 0 && i0 + 15 - j0 >= p.window);
             uint32_t pk[8], dk[8];
@@ -767,13 +791,11 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 dk[x >> 1] = *reinterpret_cast<const uint32_t*>(&w1);
             }
             if (!mbar_wait(&pds_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
-            const uint32_t row = smem_u32(pds_smem + g * KV_PDS_BYTES) + (uint32_t)r * 128u;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                st_shared_v4(row + (uint32_t)(((half * 2 + c) ^ (r & 7)) * 16), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-                st_shared_v4(row + (uint32_t)(((4 + half * 2 + c) ^ (r & 7)) * 16), dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
-            }
-            fence_proxy_async();
+            tc_fence_after();
+            tmem_st_32x8(lane_addr + KV_PDS_COL + g * 32 + half * 8, pk);
+            tmem_st_32x8(lane_addr + KV_PDS_COL + g * 32 + 16 + half * 8, dk);
+            tmem_st_wait();
+            tc_fence_before();
             mbar_arrive(&pds_full[g]);
         }
         // ---- epilogue (group 0): add this CTA's 128 columns of dK (scaled) and dV into the f32 scratch
