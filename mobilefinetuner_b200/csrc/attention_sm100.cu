@@ -336,11 +336,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // and overlap each other's latency; group g owns S/dP buffer g and the g-th 64-byte half of the dS rows.
 constexpr int DQ_BN = 32;
 constexpr int DQ_KV_BYTES = DQ_BN * HD * 2;        // 4 chunks of [32 rows x 64 columns]
-constexpr int DQ_KST = 3, DQ_VST = 2;              // K / V stages
-constexpr int DS_BYTES = BM * 128;                 // [128 rows x 128 bytes]: keys of group 0 in bytes 0..63, of group 1 in 64..127
-constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + DS_BYTES + 192 + 4 * BM * 4;
+constexpr int DQ_KST = 4, DQ_VST = 2;              // K / V stages (K is held until the tile's dQ product, V only for dP)
+constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + 256 + 4 * BM * 4;
 constexpr int DQ_THREADS = 64 + 2 * 256 + 64;     // TMA warp, S issuer, 16 element-wise warps, dP issuer, dQ issuer
 constexpr int DQ_S_COL = 0, DQ_DP_COL = 64, DQ_ACC_COL = 128;
+constexpr int DQ_DS_COL = 384;                       // dS as the A operand of the dQ product: 16 columns (32 keys as bf16 pairs) per group
 
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -350,6 +350,23 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+
+// A operand from tensor memory (lane = row, two bf16 of consecutive k per 32-bit column), B from shared memory.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :
+                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
 }
 
 struct BwdParams {
@@ -377,21 +394,20 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     uint8_t* do_smem = q_smem + Q_BYTES;
     uint8_t* k_smem = do_smem + Q_BYTES;                   // DQ_KST stages
     uint8_t* v_smem = k_smem + DQ_KST * DQ_KV_BYTES;       // DQ_VST stages
-    uint8_t* ds_smem = v_smem + DQ_VST * DQ_KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ds_smem + DS_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + DQ_VST * DQ_KV_BYTES);
     uint64_t* qdo_full = bars;          // [1]
-    uint64_t* k_full = bars + 1;        // [3]
-    uint64_t* k_empty = bars + 4;       // [3]
-    uint64_t* v_full = bars + 7;        // [2]
-    uint64_t* v_empty = bars + 9;       // [2]
-    uint64_t* sdp_full = bars + 11;     // [2]  per group; two arrivals (S and dP)
-    uint64_t* sdp_free = bars + 13;     // [2]  256 arrivals
-    uint64_t* ds_full = bars + 15;      // [2]  256 arrivals
-    uint64_t* ds_free = bars + 17;      // [2]
-    uint64_t* acc_done = bars + 19;     // [1]  completed once, by the last dQ product
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    uint64_t* k_full = bars + 1;        // [4]
+    uint64_t* k_empty = bars + 5;       // [4]
+    uint64_t* v_full = bars + 9;        // [2]
+    uint64_t* v_empty = bars + 11;      // [2]
+    uint64_t* sdp_full = bars + 13;     // [2]  per group; two arrivals (S and dP)
+    uint64_t* sdp_free = bars + 15;     // [2]  256 arrivals
+    uint64_t* ds_full = bars + 17;      // [2]  256 arrivals
+    uint64_t* ds_free = bars + 19;      // [2]
+    uint64_t* acc_done = bars + 21;     // [1]  completed once, by the last dQ product
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* delta_smem = reinterpret_cast<float*>(bars + 24);   // [4][128] partial rowsum(O * dO) of this CTA's queries
+    float* delta_smem = reinterpret_cast<float*>(bars + 32);   // [4][128] partial rowsum(O * dO) of this CTA's queries
     if ((smem_u32(smem_raw) & 1023u) != 0) {
         if (threadIdx.x == 0 && p.status) atomicExch(p.status, MFT_ERR_INVALID_ARG);
         return;
@@ -470,7 +486,6 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         // ------------------------------------------------ MMA issuer 3: dQ += dS K
         if (lane == 0) {
             constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
-            const uint64_t sd = smem_desc_sw128(smem_u32(ds_smem));
             bool ok = true;
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int g = t & 1, ks = t % DQ_KST;
@@ -480,7 +495,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const uint64_t kd = smem_desc_mn_sw128(smem_u32(k_smem + ks * DQ_KV_BYTES), DQ_BN * 128);
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                    umma_bf16(tmem_base + DQ_ACC_COL, sd + (uint64_t)(4 * g + 2 * j), kd + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
+                    umma_bf16_ts(tmem_base + DQ_ACC_COL, tmem_base + DQ_DS_COL + g * 16 + 8 * j, kd + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
                 umma_commit(&k_empty[ks]);
                 umma_commit(&ds_free[g]);
                 if (t == n_tiles - 1) umma_commit(acc_done);
@@ -549,11 +564,10 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 pk[x >> 1] = *reinterpret_cast<const uint32_t*>(&w);
             }
             if (!mbar_wait(&ds_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
-            const uint32_t drow = smem_u32(ds_smem) + (uint32_t)r * 128u;
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-                st_shared_v4(drow + (uint32_t)(((g * 4 + half * 2 + c) ^ (r & 7)) * 16), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            fence_proxy_async();
+            tc_fence_after();
+            tmem_st_32x8(lane_addr + DQ_DS_COL + g * 16 + half * 8, pk);
+            tmem_st_wait();
+            tc_fence_before();
             mbar_arrive(&ds_full[g]);
         }
         if (g == 0 && ok && mbar_wait(acc_done, 0, abort_flag)) {
@@ -600,23 +614,6 @@ constexpr int DKV_SMEM = 2 * Q_BYTES + KV_STAGES * 2 * KV_Q_BYTES + KV_STAGES * 
 constexpr int DKV_THREADS = 64 + 2 * 256 + 64;         // TMA warp, S^T issuer, 16 element-wise warps, dP^T issuer, dV/dK issuer
 constexpr int KV_S_COL = 0, KV_DP_COL = 64, KV_DK_COL = 128, KV_DV_COL = 256;
 constexpr int KV_PDS_COL = 384;                        // per group 32 columns: P^T (16: 32 queries as bf16 pairs) | dS^T (16)
-
-// A operand from tensor memory (lane = row, two bf16 of consecutive k per 32-bit column), B from shared memory.
-__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        :
-        : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 :
-                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
 
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
