@@ -33,8 +33,10 @@ constexpr int THREADS = 352;   // TMA warp, S-issuing warp, 8 softmax warps, P V
 constexpr int Q_BYTES = BM * HD * 2;           // 4 boxes of [128 rows x 64 columns]
 constexpr int KV_BYTES = BN * HD * 2;          // 4 boxes of [64 rows x 64 columns]
 constexpr int P_BYTES = BM * BN * 2;           // [128 rows x 64 keys], 128-byte rows
-constexpr int FWD_SMEM = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 160 + 2 * 2 * BM * 4;   // 231,584 of 232,448 bytes
+constexpr int FWD_VST = 3;                     // V stages (a V tile is held until its P V product is done; K only for S)
+constexpr int FWD_SMEM = Q_BYTES + (2 + FWD_VST) * KV_BYTES + 192 + 2 * 2 * BM * 4;   // 231,616 of 232,448 bytes
 constexpr int S_COL = 0, O_COL = 128;          // tensor-memory columns: S buffers at 0 / 64, O at 128..383
+constexpr int P_COL = 384;                     // bf16 probabilities as the A operand of P V: 32 columns (64 keys) per buffer
 constexpr float RESCALE_GAP = 8.0f;            // log2 units
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -50,6 +52,30 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// A operand from tensor memory (lane = row, two bf16 of consecutive k per 32-bit column), B from shared memory.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :
+                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 :
+                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                   "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
 
 // B operand stored [k][n] with n contiguous (128-byte swizzled boxes of 64 n-columns, `chunk_bytes` apart):
 // leading byte offset = distance between 64-column chunks, stride byte offset = 1024 (8 k-rows).
@@ -91,23 +117,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint8_t* base = smem_raw;
     uint8_t* q_smem = base;
     uint8_t* k_smem = q_smem + Q_BYTES;            // 2 stages
-    uint8_t* v_smem = k_smem + 2 * KV_BYTES;       // 2 stages
-    uint8_t* p_smem = v_smem + 2 * KV_BYTES;       // 2 buffers
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * P_BYTES);
+    uint8_t* v_smem = k_smem + 2 * KV_BYTES;       // FWD_VST stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + FWD_VST * KV_BYTES);
     uint64_t* q_full = bars;            // [1]
     uint64_t* k_full = bars + 1;        // [2]
-    uint64_t* v_full = bars + 3;        // [2]
-    uint64_t* k_empty = bars + 5;       // [2]
-    uint64_t* v_empty = bars + 7;       // [2]
-    uint64_t* s_full = bars + 9;        // [2]
-    uint64_t* s_free = bars + 11;       // [2]  256 arrivals
-    uint64_t* p_full = bars + 13;       // [2]  256 arrivals
-    uint64_t* p_free = bars + 15;       // [2]
-    uint64_t* o_done = bars + 17;       // [2]  P V product t completes o_done[t & 1] (two barriers, so that a waiter
+    uint64_t* v_full = bars + 3;        // [3]
+    uint64_t* k_empty = bars + 6;       // [2]
+    uint64_t* v_empty = bars + 8;       // [3]
+    uint64_t* s_full = bars + 11;       // [2]
+    uint64_t* s_free = bars + 13;       // [2]  256 arrivals
+    uint64_t* p_full = bars + 15;       // [2]  256 arrivals
+    uint64_t* p_free = bars + 17;       // [2]
+    uint64_t* o_done = bars + 19;       // [2]  P V product t completes o_done[t & 1] (two barriers, so that a waiter
                                         //      one product behind cannot mistake an older phase for the one it needs)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* mx_smem = reinterpret_cast<float*>(bars + 20);   // [2 buffers][2 halves][128] row maxima, later row sums
+    float* mx_smem = reinterpret_cast<float*>(bars + 24);   // [2 buffers][2 halves][128] row maxima, later row sums
     float* l_smem = mx_smem;
     if ((smem_u32(smem_raw) & 1023u) != 0) {               // uniform: nothing has been allocated or armed yet
         if (threadIdx.x == 0 && p.status) atomicExch(p.status, MFT_ERR_INVALID_ARG);
@@ -126,9 +151,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
             mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 256); mbar_init(&p_full[s], 256); mbar_init(&p_free[s], 1);
         }
+        for (int s = 0; s < FWD_VST; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
         mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -147,6 +173,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const int qx = h * p.q_col0_stride, kx = kvh * p.kv_col0_stride;
             mbar_arrive_expect_tx(q_full, Q_BYTES);
             for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + c * (BM * 128), &map_q, q_full, qx + c * 64, b * p.seq + i0);
+            int vs = 0;
+            uint32_t vph = 0;                           // V stage of tile t and its phase parity
             for (int t = 0; t < n_tiles; ++t) {
                 const int st = t & 1;
                 const uint32_t ph = (t >> 1) & 1;
@@ -154,9 +182,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) break;
                 mbar_arrive_expect_tx(&k_full[st], KV_BYTES);
                 for (int c = 0; c < 4; ++c) tma_load_2d(k_smem + st * KV_BYTES + c * (BN * 128), &map_k, &k_full[st], kx + c * 64, row);
-                if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) break;
-                mbar_arrive_expect_tx(&v_full[st], KV_BYTES);
-                for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + st * KV_BYTES + c * (BN * 128), &map_v, &v_full[st], kx + c * 64, row);
+                if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag)) break;
+                mbar_arrive_expect_tx(&v_full[vs], KV_BYTES);
+                for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + vs * KV_BYTES + c * (BN * 128), &map_v, &v_full[vs], kx + c * 64, row);
+                if (++vs == FWD_VST) { vs = 0; vph ^= 1; }
             }
         }
     } else if (warp == 1) {
@@ -190,19 +219,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (lane == 0) {
             constexpr uint32_t idesc_o = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
             bool ok = true;
+            int vs = 0;
+            uint32_t vph = 0;
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int st = t & 1;
                 const uint32_t ph = (t >> 1) & 1;
-                if (!mbar_wait(&v_full[st], ph, abort_flag) || !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&v_full[vs], vph, abort_flag) || !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t pd = smem_desc_sw128(smem_u32(p_smem + st * P_BYTES));
-                const uint64_t vd = smem_desc_mn_sw128(smem_u32(v_smem + st * KV_BYTES), BN * 128);
+                // A = the bf16 probabilities in tensor memory (8 columns per 16 keys), B = V as it lies in memory
+                const uint32_t pa = tmem_base + P_COL + st * 32;
+                const uint64_t vd = smem_desc_mn_sw128(smem_u32(v_smem + vs * KV_BYTES), BN * 128);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    umma_bf16(tmem_base + O_COL, pd + (uint64_t)(2 * j), vd + (uint64_t)(j * (2048 / 16)), idesc_o, (t | j) != 0 ? 1u : 0u);
-                umma_commit(&v_empty[st]);
+                    umma_bf16_ts(tmem_base + O_COL, pa + 8 * j, vd + (uint64_t)(j * (2048 / 16)), idesc_o, (t | j) != 0 ? 1u : 0u);
+                umma_commit(&v_empty[vs]);
                 umma_commit(&p_free[st]);
                 umma_commit(&o_done[st]);
+                if (++vs == FWD_VST) { vs = 0; vph ^= 1; }
             }
         }
     } else {
@@ -284,11 +317,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
             if (!mbar_wait(&p_free[st], ph ^ 1, abort_flag)) { ok = false; break; }
-            const uint32_t prow = smem_u32(p_smem + st * P_BYTES) + (uint32_t)r * 128u;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                st_shared_v4(prow + (uint32_t)(((half * 4 + c) ^ (r & 7)) * 16), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            fence_proxy_async();
+            tc_fence_after();
+            tmem_st_32x16(lane_addr + P_COL + st * 32 + half * 16, pk);
+            tmem_st_wait();
+            tc_fence_before();
             mbar_arrive(&p_full[st]);
         }
         // ---- epilogue: O / l -> bf16 (each thread its half of the row), row log-sum-exp
@@ -350,23 +382,6 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
-}
-
-// A operand from tensor memory (lane = row, two bf16 of consecutive k per 32-bit column), B from shared memory.
-__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        :
-        : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 :
-                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
 }
 
 struct BwdParams {
