@@ -3,11 +3,13 @@
 // Forward: one CTA per (128 queries, head, batch).  Scores and the output accumulator live in tensor memory:
 //     S = Q K^T      128 x 64 per key tile, two buffers (128 columns)
 //     O += P V       128 x 256 (256 columns)
-// Warp 0 streams K and V tiles with TMA (128-byte swizzle, two stages each), warp 1's one thread issues the
-// MMAs, warps 2..9 are the softmax: two threads share a query row (one tensor-memory lane, 32 of the tile's 64
-// keys each; they exchange their maxima through shared memory), apply the mask as an index predicate,
-// exponentiate against a running reference maximum and write the bf16 probabilities into a swizzled
-// shared-memory tile that the next MMA consumes as its A operand.
+//     P              128 x 64 bf16 per key tile, two buffers (64 columns): the A operand of P V
+// Warp 0 streams K and V tiles with TMA (128-byte swizzle; K two stages, V three: a V tile is held until its
+// P V product is done), warp 1's one thread issues S, warp 10's one thread issues P V, warps 2..9 are the
+// softmax: two threads share a query row (one tensor-memory lane, 32 of the tile's 64 keys each; they exchange
+// their maxima through shared memory), apply the mask as an index predicate, exponentiate against a running
+// reference maximum and store the bf16 probabilities back into tensor memory (tcgen05.st), from where the
+// P V MMA reads them as its A operand (no shared-memory tile, no proxy fence on the softmax path).
 // V is consumed as it lies in memory ([key][d], "MN-major" B operand), so nothing is transposed.
 // The reference maximum is only raised (and O rescaled in tensor memory) when a row's maximum grew by more
 // than 2^8 since the last rescale, which keeps the exponentials below 256 and makes rescales rare.
@@ -361,11 +363,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 // ---------------------------------------------------------------- backward: dQ
 // One CTA per (128 queries, head, batch).  Q and dO stay in shared memory; K streams in 32-key tiles through
-// three stages, V through two.  Per tile: S = Q K^T and dP = dO V^T into tensor memory, the element-wise threads
-// form dS = P (dP - delta) with P = exp2(S scale log2e - lse log2e) and write it as bf16 into a swizzled
-// shared-memory tile, and dQ += dS K accumulates in tensor memory (K consumed MN-major).  The element-wise work
-// has no state across tiles, so two groups of 256 threads (two threads per query row each) take alternate tiles
-// and overlap each other's latency; group g owns S/dP buffer g and the g-th 64-byte half of the dS rows.
+// four stages (held until the tile's dQ product), V through two.  Per tile: S = Q K^T and dP = dO V^T into tensor
+// memory, the element-wise threads form dS = P (dP - delta) with P = exp2(S scale log2e - lse log2e) and store it
+// as bf16 back into tensor memory, and dQ += dS K accumulates in tensor memory (dS read as the A operand from
+// tensor memory, K consumed MN-major).  The element-wise work has no state across tiles, so two groups of 256
+// threads (two threads per query row each) take alternate tiles and overlap each other's latency; group g owns
+// S/dP buffer g and 16 tensor-memory columns for its dS.
 constexpr int DQ_BN = 32;
 constexpr int DQ_KV_BYTES = DQ_BN * HD * 2;        // 4 chunks of [32 rows x 64 columns]
 constexpr int DQ_KST = 4, DQ_VST = 2;              // K / V stages (K is held until the tile's dQ product, V only for dP)
@@ -615,10 +618,12 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // ---------------------------------------------------------------- backward: dK, dV
 // One CTA per (128 keys, query head, half of head_dim, batch): dK and dV for 128 keys x 256 columns would fill
 // the whole tensor memory, so each CTA accumulates 128 of the 256 columns (both halves recompute S and dP).
-// K and V stay in shared memory; Q, dO and the per-query log-sum-exp / delta stream in 32-query tiles (stage g
-// of two belongs to element-wise group g).  Per tile: S^T = K Q^T and dP^T = V dO^T (128 keys x 32 queries) into
-// tensor memory, the group forms P^T and dS^T and writes them as bf16 into the two 64-byte halves of a swizzled
-// shared-memory tile, and dV += P^T dO, dK += dS^T Q accumulate in tensor memory with dO / Q consumed MN-major.
+// K and V stay in shared memory; Q, dO and the per-query log-sum-exp / delta stream in 32-query tiles through
+// three stages (a stage is held until the tile's dV / dK products are done, and the next load into it takes
+// longer than one tile's MMAs: with two stages the tensor pipe waited for it).  Per tile: S^T = K Q^T and
+// dP^T = V dO^T (128 keys x 32 queries) into tensor memory, element-wise group t & 1 forms P^T and dS^T and stores
+// them as bf16 back into tensor memory (32 columns per group), and dV += P^T dO, dK += dS^T Q accumulate in tensor
+// memory with P^T / dS^T read as A operands from tensor memory and dO / Q consumed MN-major from the stage.
 // The result is added into the caller's f32 [2][batch, seq, n_kv, 256] scratch (query heads of a KV group and
 // the two halves write disjoint columns or add).
 constexpr int KV_BQ = 32;                              // queries per tile
