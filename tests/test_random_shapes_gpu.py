@@ -129,7 +129,7 @@ def sweep_attn(sw):
     for nm, a, b in (("o", o, wo), ("dq", dq, wdq), ("dk", dk, wdk), ("dv", dv, wdv)):
         # absolute floor of 4e-3 * amp per element: where a query sees one key (window 1) or its softmax is one-hot,
         # dS is 0 in exact arithmetic and what is left is the bf16 rounding of the stored O in rowsum(O dO)
-        check("attn_" + nm, cfg, relerr(a, b, floor=4e-3 * amp), 1.2e-2)
+        check("attn_" + nm, cfg, relerr(a, b, floor=4e-3 * amp), 2e-2)
     check("attn_status", cfg, ops.device_status(), 1)
 
 
