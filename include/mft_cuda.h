@@ -33,6 +33,7 @@ extern "C" {
 #define MFT_ERR_INVALID_ARG (-1)
 #define MFT_ERR_OOM (-2)
 #define MFT_ERR_CUDA (-3)
+#define MFT_ERR_NCCL (-4)
 #define MFT_ERR_TIMEOUT (-5)
 #define MFT_ERR_BOUNDS (-6)
 #define MFT_ERR_UNSUPPORTED (-7)
@@ -55,13 +56,26 @@ int32_t mft_stream_sync(mft_stream_t stream);
 int32_t mft_device_status(mft_stream_t stream, int32_t* status_host);
 
 /* ---- memory: the device analogue of MemoryManager / MemoryPool
- *      (operator/finetune_ops/core/memory_manager.h:103-153) ----------------
- * Size-bucketed caching allocator: freed blocks are kept for reuse and only
- * returned to the driver by mft_empty_cache (what force_cleanup maps to). */
-int32_t mft_malloc(size_t bytes, void** ptr);
-int32_t mft_free(void* ptr);
+ *      (operator/finetune_ops/core/memory_manager.h:103-153; allocate
+ *      memory_manager.cpp:34-73, deallocate :75-97, clear_unused :99-145) ---
+ * Size-bucketed, stream-ordered caching allocator: freed blocks are kept for
+ * reuse and only returned to the driver by mft_empty_cache (what force_cleanup
+ * maps to).  mft_free(ptr, stream) states that every use of the block has been
+ * queued on `stream`; the block may be handed out again at once, and a request
+ * from ANOTHER stream is ordered after those uses on the device (an event
+ * wait), never by blocking the host.  A block used on several streams must be
+ * made visible to the stream it is freed on first (event wait or sync). */
+int32_t mft_malloc(size_t bytes, mft_stream_t stream, void** ptr);
+int32_t mft_free(void* ptr, mft_stream_t stream);
 int32_t mft_empty_cache(void);
-/* stats_host[0..3] = bytes in use, bytes cached, peak bytes in use, #cudaMalloc calls */
+/* Returns cached blocks to the driver, largest first, until at most keep_bytes
+ * stay cached: the per-step MemoryManager::force_cleanup() / clear_unused_memory()
+ * of the reference's training loops (trainer.cpp:143, gemma_trainer.cpp:137) maps
+ * to this with a high-water mark, so a steady-state step allocates nothing. */
+int32_t mft_trim_cache(int64_t keep_bytes);
+/* stats_host[0..5] = bytes in use, bytes cached, peak bytes in use, #cudaMalloc
+ * calls, #requests served from the cache, #of those that had to be ordered
+ * behind another stream. */
 int32_t mft_mem_stats(int64_t* stats_host);
 int32_t mft_memcpy_h2d(void* dst, const void* src_host, size_t bytes, mft_stream_t stream);
 /* Page-locked host memory (asynchronous copies need it to overlap with kernels). */
@@ -378,6 +392,41 @@ int32_t mft_adam_step(float* params, float* grads, float* m, float* v, int64_t n
                       float lr, float beta1, float beta2, float eps, float weight_decay,
                       const float* sqnorm_dev, float max_norm, float clip_eps, int32_t zero_grad,
                       mft_stream_t stream);
+
+/* ---- data-parallel exchange -------------------------------------------------
+ * The reference is a single-device library (no collective call sites); the
+ * sharded job built on it runs one process per GPU, each with a full replica
+ * and its own slice of the batch, and exchanges exactly one thing per step:
+ * the sum of the flat f32 LoRA-gradient bucket (what Optimizer::clip_grad_norm
+ * optim/optimizer.cpp:6-38 and Adam::step optim/adam.cpp:25-90 then consume on
+ * every rank).  These entry points are that exchange over NCCL, one
+ * communicator per process.  NCCL is opened at run time (libnccl.so.2, or the
+ * path in MFT_NCCL_LIB), so hosts that stay on one GPU need no NCCL at all.
+ *
+ * Rendezvous is the host's job: rank 0 calls mft_comm_unique_id and sends the
+ * 128 bytes to the other ranks by any means (a file, a socket, MPI, a store);
+ * every rank then calls mft_comm_init with its own device current.  world = 1
+ * is legal and makes every call below a no-op.
+ *
+ * Failure handling: none of these calls blocks on a peer.  A rank that knows a
+ * peer has left (heartbeat, store) calls mft_comm_abort before its next launch;
+ * afterwards every exchange returns MFT_ERR_NCCL.  mft_comm_async_error reports
+ * what NCCL's watchdog has seen.  mft_comm_wait polls the stream until the
+ * queued work has finished, an asynchronous NCCL error shows up, or the
+ * deadline passes; in the last two cases it aborts the communicator (which
+ * releases a collective that waits for a missing peer) and returns
+ * MFT_ERR_NCCL / MFT_ERR_TIMEOUT. */
+#define MFT_COMM_ID_BYTES 128
+int32_t mft_comm_unique_id(uint8_t* id_host);
+int32_t mft_comm_init(int32_t rank, int32_t world, const uint8_t* id_host);
+int32_t mft_comm_info(int32_t* rank, int32_t* world, int32_t* nccl_version);
+/* In-place sum over all ranks, asynchronous on `stream`. */
+int32_t mft_allreduce_sum_f32(float* buf, int64_t n, mft_stream_t stream);
+int32_t mft_allreduce_sum_i64(int64_t* buf, int64_t n, mft_stream_t stream);
+int32_t mft_comm_async_error(int32_t* nccl_result_host);
+int32_t mft_comm_wait(mft_stream_t stream, int32_t timeout_ms);
+int32_t mft_comm_abort(void);
+int32_t mft_comm_destroy(void);
 
 /* ---- generic fp32 operators behind the eager ops:: surface (add/sub/mul/div with broadcasting
  *      ops.cpp:299-560, unary maps :1221-1305, sum/mean :1970-2127, transpose/permute :990-1149,

@@ -65,9 +65,19 @@ _SIGS = {
     "mft_version": [],
     "mft_stream_sync": [vp],
     "mft_device_status": [vp, C.POINTER(i32)],
-    "mft_malloc": [sz, C.POINTER(vp)],
-    "mft_free": [vp],
+    "mft_malloc": [sz, vp, C.POINTER(vp)],
+    "mft_free": [vp, vp],
+    "mft_comm_unique_id": [vp],
+    "mft_comm_init": [i32, i32, vp],
+    "mft_comm_info": [C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)],
+    "mft_allreduce_sum_f32": [vp, i64, vp],
+    "mft_allreduce_sum_i64": [vp, i64, vp],
+    "mft_comm_async_error": [C.POINTER(i32)],
+    "mft_comm_wait": [vp, i32],
+    "mft_comm_abort": [],
+    "mft_comm_destroy": [],
     "mft_empty_cache": [],
+    "mft_trim_cache": [i64],
     "mft_mem_stats": [C.POINTER(i64)],
     "mft_host_alloc": [C.c_size_t, vp],
     "mft_host_free": [vp],

@@ -25,7 +25,7 @@ template <typename T>
 int32_t dalloc(mft_model* m, T** out, int64_t n, bool zero = false, bool activation = false) {
     void* p = nullptr;
     const size_t bytes = (size_t)std::max<int64_t>(n, 1) * sizeof(T);
-    TRY(mft_malloc(bytes, &p));
+    TRY(mft_malloc(bytes, m->stream, &p));
     m->allocations.push_back(p);
     if (zero) TRY(mft_memset(p, 0, bytes, m->stream));
     if (activation) m->activation_bytes += (int64_t)bytes;
@@ -97,8 +97,8 @@ extern "C" int32_t mft_model_destroy(mft_model_t* m) {
         if (m->slot_ready[i]) cudaEventDestroy(m->slot_ready[i]);
         if (m->slot_free[i]) cudaEventDestroy(m->slot_free[i]);
     }
-    for (auto& b : m->merge_backup) { mft_free(b.w_nk); mft_free(b.w_kn); }
-    for (void* p : m->allocations) mft_free(p);
+    for (auto& b : m->merge_backup) { mft_free(b.w_nk, m->stream); mft_free(b.w_kn, m->stream); }
+    for (void* p : m->allocations) mft_free(p, m->stream);
     delete m;
     return MFT_OK;
 }
@@ -522,13 +522,13 @@ extern "C" int32_t mft_model_merge_lora(mft_model_t* m) {
             if (!g->any_lora) continue;
             const size_t bytes = (size_t)g->in * g->n_total * sizeof(bf16);
             void *b1 = nullptr, *b2 = nullptr;
-            int32_t s = mft_malloc(bytes, &b1);
-            if (s == MFT_OK) s = mft_malloc(bytes, &b2);
+            int32_t s = mft_malloc(bytes, m->stream, &b1);
+            if (s == MFT_OK) s = mft_malloc(bytes, m->stream, &b2);
             if (s == MFT_OK) s = mft_memcpy_d2d(b1, g->w_nk, bytes, m->stream);
             if (s == MFT_OK) s = mft_memcpy_d2d(b2, g->w_kn, bytes, m->stream);
             if (s != MFT_OK) {
-                if (b1) mft_free(b1);
-                if (b2) mft_free(b2);
+                if (b1) mft_free(b1, m->stream);
+                if (b2) mft_free(b2, m->stream);
                 m->merged = true;                  // so that the partial merge is rolled back
                 mft_model_unmerge_lora(m);
                 return s;
@@ -559,7 +559,7 @@ extern "C" int32_t mft_model_unmerge_lora(mft_model_t* m) {
         if (s != MFT_OK && first == MFT_OK) first = s;
     }
     if (int32_t s = check_cuda(cudaStreamSynchronize(m->stream), "unmerge sync")) { if (first == MFT_OK) first = s; }
-    for (auto& b : m->merge_backup) { mft_free(b.w_nk); mft_free(b.w_kn); }
+    for (auto& b : m->merge_backup) { mft_free(b.w_nk, m->stream); mft_free(b.w_kn, m->stream); }
     m->merge_backup.clear();
     m->merged = false;
     return first;

@@ -58,6 +58,17 @@ mft_strides_t tok_strides(int64_t S, int64_t ld, int64_t hd) {
     mft_strides_t s; s.stride_b = S * ld; s.stride_s = ld; s.stride_h = hd; return s;
 }
 
+// Re-packs the bf16 LoRA panels from the f32 masters when an optimizer step or an upload changed them.  Always
+// issued on the model's own stream and never inside forward(): forward() may run under stream capture, and a
+// pack that depended on this host flag would be frozen into (or left out of) the replayed graph.
+int32_t refresh_panels(mft_model* m) {
+    if (m->panels_dirty && m->n_pack > 0) {
+        TRY(mft_pack_blocks_bf16(m->pack_table, m->n_pack, m->stream));
+        m->panels_dirty = false;
+    }
+    return MFT_OK;
+}
+
 int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
     mft_model* m = c.m;
     const mft_model_config_t& cfg = m->cfg;
@@ -67,10 +78,6 @@ int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
     const int64_t T = c.T, S = c.S;
     (void)for_training;
     const bool fuse = gemma && m->fuse_norms && H <= 2048;      // Gemma's post-norm + residual + pre-norm pairs in one kernel
-    if (m->panels_dirty && m->n_pack > 0) {
-        TRY(mft_pack_blocks_bf16(m->pack_table, m->n_pack, c.st));
-        m->panels_dirty = false;
-    }
     TRY(mft_memset(m->status_dev, 0, 4, c.st));
     const float emb_scale = gemma ? std::sqrt((float)H) : 1.0f;
     TRY(mft_embedding_gather(m->ids, m->embed, gpt2 ? m->pos_embed : nullptr, m->bufs[0].x, T, S, H, cfg.vocab, emb_scale, m->status_dev, c.st));
@@ -241,6 +248,7 @@ int32_t check_status(mft_model* m) {
 int32_t forward_backward(Ctx& c, int64_t n_valid_global) {
     mft_model* m = c.m;
     if (m->merged) return fail(MFT_ERR_INVALID_ARG, "the adapters are merged into the base weights: call mft_model_unmerge_lora before training");
+    TRY(refresh_panels(m));
     auto eager = [&]() -> int32_t {
         TRY(forward(c, true, n_valid_global));
         return backward(c, n_valid_global);
@@ -332,6 +340,7 @@ extern "C" int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_hos
     MFT_CHECK_ARG(ids_host && labels_host && loss_host, "mft_model_forward_loss: null argument");
     TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)c.T * 4, c.st));
     TRY(mft_memcpy_h2d(m->labels, labels_host, (size_t)c.T * 4, c.st));
+    TRY(refresh_panels(m));
     TRY(forward(c, false));
     TRY(mft_memcpy_d2h(loss_host, m->loss_dev, 4, c.st));
     return check_status(m);
@@ -343,8 +352,8 @@ static int32_t ensure_slots(mft_model* m) {
     if (int32_t s = check_cuda(cudaStreamCreateWithFlags(&m->copy_stream, cudaStreamNonBlocking), "copy stream")) return s;
     for (int i = 0; i < 2; ++i) {
         void* p = nullptr;
-        TRY(mft_malloc((size_t)m->max_tokens * 4, &p)); m->slot_ids[i] = static_cast<int32_t*>(p); m->allocations.push_back(p);
-        TRY(mft_malloc((size_t)m->max_tokens * 4, &p)); m->slot_labels[i] = static_cast<int32_t*>(p); m->allocations.push_back(p);
+        TRY(mft_malloc((size_t)m->max_tokens * 4, m->stream, &p)); m->slot_ids[i] = static_cast<int32_t*>(p); m->allocations.push_back(p);
+        TRY(mft_malloc((size_t)m->max_tokens * 4, m->stream, &p)); m->slot_labels[i] = static_cast<int32_t*>(p); m->allocations.push_back(p);
         if (int32_t s = check_cuda(cudaEventCreateWithFlags(&m->slot_ready[i], cudaEventDisableTiming), "slot event")) return s;
         if (int32_t s = check_cuda(cudaEventCreateWithFlags(&m->slot_free[i], cudaEventDisableTiming), "slot event")) return s;
     }
@@ -421,6 +430,7 @@ extern "C" int32_t mft_model_score_tokens(mft_model_t* m, const int32_t* ids_hos
     const int64_t H = m->cfg.hidden, V = m->cfg.vocab;
     TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)seq * 4, c.st));
     TRY(mft_memcpy_h2d(m->labels, ids_host, (size_t)seq * 4, c.st));      // any valid labels: the loss is not used
+    TRY(refresh_panels(m));
     TRY(forward(c, false));
     // scratch inside the staging buffer: candidate rows (f32, then bf16), the last hidden row twice, logits, ids
     MFT_CHECK_ARG((64 + 2) * H * 2 + 1024 <= m->stage_floats - 64, "mft_model_score_tokens: staging buffer too small");
@@ -507,9 +517,9 @@ extern "C" int32_t mft_trainer_create(mft_model_t* model, const mft_trainer_conf
     t->model = model;
     t->cfg = *cfg;
     void* p = nullptr;
-    if (int32_t s = mft_malloc(4, &p)) { delete t; return s; }
+    if (int32_t s = mft_malloc(4, model->stream, &p)) { delete t; return s; }
     t->loss_acc = static_cast<float*>(p);
-    if (int32_t s = mft_memset(t->loss_acc, 0, 4, model->stream)) { mft_free(p); delete t; return s; }
+    if (int32_t s = mft_memset(t->loss_acc, 0, 4, model->stream)) { mft_free(p, model->stream); delete t; return s; }
     *out = t;
     return MFT_OK;
 }
@@ -517,7 +527,7 @@ extern "C" int32_t mft_trainer_create(mft_model_t* model, const mft_trainer_conf
 extern "C" int32_t mft_trainer_destroy(mft_trainer_t* t) {
     if (!t) return MFT_OK;
     cudaStreamSynchronize(t->model->stream);
-    mft_free(t->loss_acc);
+    mft_free(t->loss_acc, t->model->stream);
     delete t;
     return MFT_OK;
 }

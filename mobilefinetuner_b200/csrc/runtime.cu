@@ -40,11 +40,26 @@ int32_t check_cuda(cudaError_t e, const char* what) {
 // Blocks are rounded up to a size class (512 B granularity below 1 MiB, 2 MiB
 // granularity above) and kept in per-class free lists when released.  Lookup of
 // a live pointer is a hash probe, not the reference's linear scan.
+//
+// Stream order: mft_free(ptr, stream) promises that every use of the block was
+// queued on `stream` (or made visible to it) before the call.  The block goes
+// to the free list with an event recorded on that stream.  mft_malloc(bytes,
+// stream) hands a cached block out at once when it was freed on the same stream
+// (later work on the stream runs after the earlier uses anyway) or when its
+// event has completed; otherwise the requesting stream is made to wait for the
+// event, so a kernel of another stream that still reads the block finishes
+// before the new owner's first write.  Nothing blocks the host.
 struct Allocator {
+    struct Cached {
+        void* ptr;
+        cudaStream_t stream;     // stream the block was released on
+        cudaEvent_t done;        // recorded on that stream at release (null: released with no work pending)
+    };
     std::mutex mu;
-    std::unordered_map<void*, size_t> live;             // ptr -> rounded size
-    std::map<size_t, std::vector<void*>> free_lists;    // rounded size -> cached blocks
-    int64_t in_use = 0, cached = 0, peak = 0, n_cuda_malloc = 0;
+    std::unordered_map<void*, size_t> live;              // ptr -> rounded size
+    std::map<size_t, std::vector<Cached>> free_lists;    // rounded size -> cached blocks
+    std::vector<cudaEvent_t> event_pool;
+    int64_t in_use = 0, cached = 0, peak = 0, n_cuda_malloc = 0, n_reuse = 0, n_cross_stream_waits = 0;
 
     static size_t round_size(size_t b) {
         if (b == 0) b = 1;
@@ -52,15 +67,42 @@ struct Allocator {
         if (b < (size_t(1) << 20)) return (b + small - 1) / small * small;
         return (b + big - 1) / big * big;
     }
-    int32_t alloc(size_t bytes, void** out) {
+    cudaEvent_t take_event() {
+        if (!event_pool.empty()) { cudaEvent_t e = event_pool.back(); event_pool.pop_back(); return e; }
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        return e;
+    }
+    int32_t alloc(size_t bytes, cudaStream_t stream, void** out) {
         const size_t sz = round_size(bytes);
         std::lock_guard<std::mutex> lk(mu);
         auto it = free_lists.find(sz);
         void* p = nullptr;
         if (it != free_lists.end() && !it->second.empty()) {
-            p = it->second.back();
-            it->second.pop_back();
+            // prefer a block whose release is already ordered before `stream`: same stream, or event complete
+            std::vector<Cached>& fl = it->second;
+            size_t pick = fl.size() - 1;
+            for (size_t i = fl.size(); i-- > 0;) {
+                if (!fl[i].done || fl[i].stream == stream) { pick = i; break; }
+                if (cudaEventQuery(fl[i].done) == cudaSuccess) { pick = i; break; }
+                cudaGetLastError();
+            }
+            Cached c = fl[pick];
+            fl.erase(fl.begin() + (std::ptrdiff_t)pick);
+            if (c.done) {
+                if (c.stream != stream && cudaEventQuery(c.done) != cudaSuccess) {
+                    cudaGetLastError();
+                    if (int32_t s = check_cuda(cudaStreamWaitEvent(stream, c.done, 0), "mft_malloc: wait for the releasing stream")) {
+                        fl.push_back(c);
+                        return s;
+                    }
+                    ++n_cross_stream_waits;
+                }
+                event_pool.push_back(c.done);
+            }
+            p = c.ptr;
             cached -= (int64_t)sz;
+            ++n_reuse;
         } else {
             cudaError_t e = cudaMalloc(&p, sz);
             if (e != cudaSuccess) {
@@ -80,21 +122,46 @@ struct Allocator {
         *out = p;
         return MFT_OK;
     }
-    int32_t release(void* p) {
+    int32_t release(void* p, cudaStream_t stream) {
         if (!p) return MFT_OK;
         std::lock_guard<std::mutex> lk(mu);
         auto it = live.find(p);
         if (it == live.end()) return fail(MFT_ERR_INVALID_ARG, "mft_free: unknown pointer");
         const size_t sz = it->second;
+        Cached c{p, stream, take_event()};
+        if (c.done && cudaEventRecord(c.done, stream) != cudaSuccess) {
+            // cannot order the release (e.g. the stream is being captured): fall back to a full device wait on reuse
+            cudaGetLastError();
+            event_pool.push_back(c.done);
+            c.done = nullptr;
+            cudaDeviceSynchronize();
+        }
         live.erase(it);
-        free_lists[sz].push_back(p);
+        free_lists[sz].push_back(c);
         in_use -= (int64_t)sz;
         cached += (int64_t)sz;
         return MFT_OK;
     }
+    // Frees cached blocks, largest size class first, until at most `keep_bytes` stay cached.
+    void trim_locked(int64_t keep_bytes) {
+        for (auto it = free_lists.rbegin(); it != free_lists.rend() && cached > keep_bytes; ++it) {
+            std::vector<Cached>& fl = it->second;
+            while (!fl.empty() && cached > keep_bytes) {
+                Cached c = fl.back();
+                fl.pop_back();
+                cudaFree(c.ptr);
+                if (c.done) event_pool.push_back(c.done);
+                cached -= (int64_t)it->first;
+            }
+        }
+    }
+    // cudaFree waits for the device to go idle, so no event needs to be consulted here.
     void release_cached_locked() {
         for (auto& kv : free_lists)
-            for (void* p : kv.second) cudaFree(p);
+            for (Cached& c : kv.second) {
+                cudaFree(c.ptr);
+                if (c.done) event_pool.push_back(c.done);
+            }
         free_lists.clear();
         cached = 0;
     }
@@ -162,20 +229,27 @@ int32_t mft_device_status(mft_stream_t stream, int32_t* status_host) {
     return MFT_OK;
 }
 
-int32_t mft_malloc(size_t bytes, void** ptr) {
+int32_t mft_malloc(size_t bytes, mft_stream_t stream, void** ptr) {
     MFT_CHECK_ARG(ptr != nullptr, "mft_malloc: null out pointer");
-    return g_alloc.alloc(bytes, ptr);
+    return g_alloc.alloc(bytes, as_stream(stream), ptr);
 }
-int32_t mft_free(void* ptr) { return g_alloc.release(ptr); }
+int32_t mft_free(void* ptr, mft_stream_t stream) { return g_alloc.release(ptr, as_stream(stream)); }
 int32_t mft_empty_cache(void) {
     std::lock_guard<std::mutex> lk(g_alloc.mu);
     g_alloc.release_cached_locked();
+    return MFT_OK;
+}
+int32_t mft_trim_cache(int64_t keep_bytes) {
+    MFT_CHECK_ARG(keep_bytes >= 0, "mft_trim_cache: negative size");
+    std::lock_guard<std::mutex> lk(g_alloc.mu);
+    g_alloc.trim_locked(keep_bytes);
     return MFT_OK;
 }
 int32_t mft_mem_stats(int64_t* s) {
     MFT_CHECK_ARG(s != nullptr, "mft_mem_stats: null pointer");
     std::lock_guard<std::mutex> lk(g_alloc.mu);
     s[0] = g_alloc.in_use; s[1] = g_alloc.cached; s[2] = g_alloc.peak; s[3] = g_alloc.n_cuda_malloc;
+    s[4] = g_alloc.n_reuse; s[5] = g_alloc.n_cross_stream_waits;
     return MFT_OK;
 }
 

@@ -1,6 +1,7 @@
 #include "memory_manager.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <iostream>
 
@@ -12,15 +13,25 @@ MemoryManager& MemoryManager::instance() {
     static MemoryManager m;
     return m;
 }
-void MemoryManager::force_cleanup() { mft_empty_cache(); }
-void MemoryManager::clear_unused_memory() { mft_empty_cache(); }
-size_t MemoryManager::device_bytes_in_use() const { int64_t s[4] = {0, 0, 0, 0}; mft_mem_stats(s); return (size_t)s[0]; }
-size_t MemoryManager::device_bytes_cached() const { int64_t s[4] = {0, 0, 0, 0}; mft_mem_stats(s); return (size_t)s[1]; }
+// The reference's loops call these after every step to hand host memory back to the OS.  On the device the cache is
+// what makes the next step allocation-free, so only what exceeds a high-water mark (MFT_CACHE_HIGH_WATER_MB,
+// default 16 GiB) is returned to the driver.
+static int64_t cache_high_water() {
+    static const int64_t v = [] {
+        const char* e = std::getenv("MFT_CACHE_HIGH_WATER_MB");
+        return (e ? std::atoll(e) : 16384LL) << 20;
+    }();
+    return v;
+}
+void MemoryManager::force_cleanup() { mft_trim_cache(cache_high_water()); }
+void MemoryManager::clear_unused_memory() { mft_trim_cache(cache_high_water()); }
+size_t MemoryManager::device_bytes_in_use() const { int64_t s[6] = {0}; mft_mem_stats(s); return (size_t)s[0]; }
+size_t MemoryManager::device_bytes_cached() const { int64_t s[6] = {0}; mft_mem_stats(s); return (size_t)s[1]; }
 void MemoryManager::print_memory_stats() const {
-    int64_t s[4] = {0, 0, 0, 0};
+    int64_t s[6] = {0};
     mft_mem_stats(s);
     std::cout << "[memory] device in use " << s[0] / (1 << 20) << " MiB, cached " << s[1] / (1 << 20) << " MiB, peak " << s[2] / (1 << 20)
-              << " MiB, driver allocations " << s[3] << ", host RSS " << MemoryMonitor::get_system_memory_usage() / (1 << 20) << " MiB" << std::endl;
+              << " MiB, driver allocations " << s[3] << ", reuses " << s[4] << ", host RSS " << MemoryMonitor::get_system_memory_usage() / (1 << 20) << " MiB" << std::endl;
 }
 
 static size_t read_status_kb(const char* key) {

@@ -49,7 +49,7 @@ void Tensor::allocate_host() {
 }
 
 void Tensor::release() {
-    if (dev_) { mft_free(dev_); dev_ = nullptr; }
+    if (dev_) { mft_free(dev_, detail::stream()); dev_ = nullptr; }
     if (host_ && owns_host_) std::free(host_);
     host_ = nullptr;
     bytes_ = 0;
@@ -115,7 +115,7 @@ void Tensor::ensure_device() const {
     detail::ensure_runtime();
     if (!dev_) {
         void* p = nullptr;
-        detail::check(mft_malloc(bytes_ ? bytes_ : 4, &p), "mft_malloc");
+        detail::check(mft_malloc(bytes_ ? bytes_ : 4, detail::stream(), &p), "mft_malloc");
         dev_ = p;
         valid_ &= ~DEV_VALID;
     }
@@ -137,7 +137,7 @@ void* Tensor::device_write() {
     detail::ensure_runtime();
     if (!dev_) {
         void* p = nullptr;
-        detail::check(mft_malloc(bytes_ ? bytes_ : 4, &p), "mft_malloc");
+        detail::check(mft_malloc(bytes_ ? bytes_ : 4, detail::stream(), &p), "mft_malloc");
         dev_ = p;
     }
     valid_ = DEV_VALID;

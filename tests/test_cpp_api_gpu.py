@@ -17,8 +17,7 @@ EXE = ROOT / "mobilefinetuner_b200" / "csrc" / "build" / "auto_trainer_step"
 
 @pytest.mark.parametrize("name", ["gemma_tiny", "qwen_tiny", "gpt2_tiny"])
 def test_cpp_auto_trainer_step_matches_reference(tmp_path, name):
-    if not EXE.exists():
-        pytest.skip("auto_trainer_step was not built (python -m mobilefinetuner_b200.build)")
+    assert EXE.exists(), "auto_trainer_step was not built (python -m mobilefinetuner_b200.build)"
     from mobilefinetuner_b200 import synth
     case = CASES[name]
     spec = case["spec"]

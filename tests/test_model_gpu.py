@@ -21,27 +21,7 @@ def model_golden():
     return np.load(ROOT / "tests" / "golden" / "model_golden.npz")
 
 
-def run_engine(case, two_steps=False):
-    from mobilefinetuner_b200 import synth
-    from mobilefinetuner_b200.engine import LoraStepEngine
-    spec = case["spec"]
-    params = synth.make_params(spec, case["seeds"][0], case["norm_jitter"])
-    lora = synth.make_lora(spec, case["seeds"][1])
-    ids, labels = synth.make_batch(spec, case["batch"], case["seq"], case["seeds"][2])
-    eng = LoraStepEngine(spec, case["batch"], case["seq"])
-    eng.set_params(params)
-    eng.set_lora(lora)
-    loss, n_valid = eng.forward_backward(ids, labels)
-    grads = eng.get_lora_grads()
-    eng.optimizer_step(STEP["lr"], max_grad_norm=STEP["max_grad_norm"])
-    after = eng.get_lora()
-    assert float(eng.grad_bucket().abs().max()) == 0.0        # zero_grad is part of the step
-    assert n_valid == case["batch"] * (case["seq"] - 1)       # integer work: exact
-    eng.close()
-    return loss, grads, after, lora
-
-
-from parity import check  # noqa: E402
+from parity import check, require_reference, run_engine  # noqa: E402
 
 
 @pytest.mark.parametrize("name", list(CASES))
@@ -64,9 +44,8 @@ def test_gpt2_reference_gives_no_gradient_to_c_attn(model_golden):
 def test_step_matches_live_reference_at_model_width():
     """Full Gemma-3-1B layer widths (hidden 1152, 4x256 heads, GeGLU 6912, window 512 active) on a
     2-layer stack with a reduced vocabulary, against the reference driver run on this machine."""
-    from oracle import model_case, refrun
-    if refrun.driver() is None:
-        pytest.skip("oracle/_ref is not built on this machine")
+    from oracle import model_case
+    require_reference()
     from mobilefinetuner_b200 import configs as Cf
     spec = Cf.reduced(Cf.GEMMA3_1B, vocab=4096, layers=2, global_every=2)
     case = dict(spec=spec, batch=1, seq=640, seeds=(401, 402, 403), norm_jitter=0.05)
@@ -189,7 +168,8 @@ def test_step_driver_accumulates_clips_and_schedules_like_the_trainers():
     want = ref.get_lora()
     ref.close()
     assert abs(seen[1] - 0.5 * (losses[0] + losses[1])) <= 1e-5 * abs(seen[1])
-    assert abs(seen[3] - 0.5 * (losses[2] + losses[3])) <= 1e-5 * abs(seen[3])
+    # the second window runs on parameters that went through one Adam step in each arm (see below: not bit-identical)
+    assert abs(seen[3] - 0.5 * (losses[2] + losses[3])) <= 1e-4 * abs(seen[3])
     # Two runs of the same step are not bit-identical (f32 atomics in the LoRA-gradient and dK/dV reductions), and
     # Adam's early steps move an element by about lr * sign(g): an element whose tiny gradient changes sign between
     # the runs differs by up to 2 lr per step.  Everything else agrees to rounding.
@@ -198,6 +178,49 @@ def test_step_driver_accumulates_clips_and_schedules_like_the_trainers():
         d = np.abs(a - b)
         assert d.max() <= 2 * 2.1 * lr_max
         assert (d <= 1e-6 + 1e-4 * np.abs(b).max()).mean() >= 0.99
+
+
+def _accum_run(monkeypatch, graph, probe_between):
+    """Three optimizer steps of two micro-batches each on one repeated batch; returns the window losses and the
+    final adapters.  `graph` selects CUDA-graph replay of the step, `probe_between` adds an evaluation forward
+    between the first two micro-batches (so that the call that gets captured starts with clean panels)."""
+    from mobilefinetuner_b200 import synth
+    from mobilefinetuner_b200.engine import LoraStepEngine, LoraTrainer
+    case = CASES["gemma_tiny"]
+    spec = case["spec"]
+    B, S = case["batch"], case["seq"]
+    monkeypatch.setenv("MFT_STEP_GRAPH", "1" if graph else "0")
+    eng = LoraStepEngine(spec, B, S)
+    eng.set_params(synth.make_params(spec, 1, 0.1)); eng.set_lora(synth.make_lora(spec, 2))
+    ids, labels = synth.make_batch(spec, B, S, 10)
+    tr = LoraTrainer(eng, grad_accum_steps=2, max_grad_norm=0.0, learning_rate=5e-3, lr_scheduler="constant", total_updates=3)
+    losses = []
+    for k in range(6):
+        out = tr.train_step(ids, labels)
+        if k == 0 and probe_between:
+            eng.forward_loss(ids, labels)
+        if out >= 0:
+            losses.append(out)
+    got = eng.get_lora()
+    tr.close(); eng.close()
+    return losses, got
+
+
+@pytest.mark.parametrize("probe_between", [False, True])
+def test_graph_replay_sees_every_optimizer_step(monkeypatch, probe_between):
+    """The bf16 LoRA panels the GEMMs read are re-packed from the f32 masters after every optimizer step whether the
+    step runs as a replayed CUDA graph or launch by launch: with gradient accumulation the captured call is a second
+    micro-batch (panels already clean), and an evaluation forward before it has the same effect.  Both orders must
+    train exactly like the uncaptured schedule; with stale panels the loss would not move after the first window."""
+    eager_losses, eager_lora = _accum_run(monkeypatch, False, probe_between)
+    graph_losses, graph_lora = _accum_run(monkeypatch, True, probe_between)
+    assert len(eager_losses) == len(graph_losses) == 3
+    assert eager_losses[2] < eager_losses[1] < eager_losses[0] - 1e-3          # lr 5e-3 on a repeated batch: it learns
+    for a, b in zip(graph_losses, eager_losses):
+        assert abs(a - b) <= 2e-4 * abs(b), (graph_losses, eager_losses)
+    for a, b in zip(graph_lora, eager_lora):
+        d = np.abs(a - b)
+        assert (d <= 1e-6 + 1e-3 * np.abs(b).max()).mean() >= 0.98
 
 
 def test_double_buffered_input_gives_the_same_steps():

@@ -20,8 +20,7 @@ NAMES = ["test_qkt_softmax_grad", "test_repeat_kv_softmax_grad", "test_attention
 
 @pytest.mark.parametrize("name", NAMES)
 def test_reference_unit_test_passes_on_gpu(name):
-    exe = BIN / name
-    if not exe.exists():
-        pytest.skip("oracle/_ref/api_tests was not built on this machine")
+    from parity import require_built
+    exe = require_built(BIN / name, "the reference unit test compiled against this repository's operator API")
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, f"{name} failed:\n{r.stdout[-3000:]}\n{r.stderr[-2000:]}"
