@@ -388,6 +388,8 @@ int32_t mft_ce_dense_bwd(const float* logits, const int32_t* tgt_scratch, int64_
  * for Optimizer::clip_grad_norm, 1e-6 for the trainers' variant).
  * zero_grad != 0 clears grads in the same pass. */
 int32_t mft_grad_sqnorm(const float* grads, int64_t n, float* sqnorm_dev, mft_stream_t stream);
+/* Same without clearing sqnorm_dev first: sums over several tensors with one read-back at the end. */
+int32_t mft_grad_sqnorm_add(const float* grads, int64_t n, float* sqnorm_dev, mft_stream_t stream);
 int32_t mft_adam_step(float* params, float* grads, float* m, float* v, int64_t n, int64_t step,
                       float lr, float beta1, float beta2, float eps, float weight_decay,
                       const float* sqnorm_dev, float max_norm, float clip_eps, int32_t zero_grad,

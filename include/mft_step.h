@@ -76,6 +76,13 @@ int32_t mft_model_get_lora_host(mft_model_t* m, int32_t idx, float* data_host);
 int32_t mft_model_get_lora_grad_host(mft_model_t* m, int32_t idx, float* data_host);
 /* 1 if the reference's graph delivers a gradient to this tensor (GPT-2 c_attn does not). */
 int32_t mft_model_lora_has_grad(const mft_model_t* m, int32_t idx);
+/* Offset (in floats) of a LoRA tensor inside the flat buckets below. */
+int32_t mft_model_lora_offset(const mft_model_t* m, int32_t idx, int64_t* offset);
+/* Tells the model that the f32 LoRA values in the parameter bucket were changed
+ * from outside (an optimizer that works on the bucket memory directly, as
+ * ops::Adam over tensors bound to it does): the bf16 panels the GEMMs read are
+ * re-packed before the next forward pass. */
+int32_t mft_model_mark_lora_dirty(mft_model_t* m);
 /* The flat f32 buckets every LoRA tensor lives in (params, grads): what a
  * data-parallel caller all-reduces between backward and the optimizer. */
 int32_t mft_model_buckets(mft_model_t* m, float** params_dev, float** grads_dev, int64_t* n);
@@ -96,6 +103,13 @@ int32_t mft_model_forward_backward_dev(mft_model_t* m, const int32_t* ids_dev, c
 /* Forward only: mean loss for a batch (evaluation). */
 int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_host, const int32_t* labels_host,
                                int32_t batch, int32_t seq, float* loss_host);
+/* XModel::forward of the reference (gpt2_model.cpp:320-406, qwen_model.cpp:335-394,
+ * gemma_model.cpp:579-646) with the logits written out: f32 [batch*seq, vocab]
+ * on the device.  The loss paths above never need this tensor; it exists for
+ * callers that read logits directly. */
+int32_t mft_model_forward_logits(mft_model_t* m, const int32_t* ids_host, int32_t batch, int32_t seq, float* logits_dev);
+/* QwenModel::forward_hidden (qwen_model.cpp:335-386): the final-norm output, f32 [batch*seq, hidden] on the device. */
+int32_t mft_model_forward_hidden(mft_model_t* m, const int32_t* ids_host, int32_t batch, int32_t seq, float* hidden_dev);
 /* ---- SafeTensors ingest and adapter files (host code; SafeTensorsReader / SafeTensorsModelReader
  *      graph/safetensors_loader.h:35-124, key mappers graph/safetensors_loader.cpp:470-590, LoraSaver
  *      graph/lora_saver.cpp:123-198, GemmaLoraInjector::save_lora_safetensors graph/gemma_lora_injector.cpp:179-264).

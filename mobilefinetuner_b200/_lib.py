@@ -149,6 +149,10 @@ _SIGS = {
     "mft_model_get_lora_host": [vp, i32, vp],
     "mft_model_get_lora_grad_host": [vp, i32, vp],
     "mft_model_lora_has_grad": [vp, i32],
+    "mft_model_lora_offset": [vp, i32, C.POINTER(i64)],
+    "mft_model_mark_lora_dirty": [vp],
+    "mft_model_forward_logits": [vp, vp, i32, i32, vp],
+    "mft_model_forward_hidden": [vp, vp, i32, i32, vp],
     "mft_model_buckets": [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(i64)],
     "mft_model_forward_backward": [vp, vp, vp, i32, i32, i64, C.POINTER(f32), C.POINTER(i32)],
     "mft_model_forward_backward_dev": [vp, vp, vp, i32, i32, i64, C.POINTER(vp), C.POINTER(vp)],
@@ -185,6 +189,7 @@ _SIGS = {
     "mft_trainer_global_step": [vp],
     "mft_model_get_final_hidden_host": [vp, vp, i64],
     "mft_model_activation_bytes": [vp],
+    "mft_grad_sqnorm_add": [vp, i64, vp, vp],
     "mft_adam_step": [vp, vp, vp, vp, i64, i64, f32, f32, f32, f32, f32, vp, f32, f32, i32, vp],
 }
 _RET = {"mft_launch_count": i64, "mft_last_error": C.c_char_p, "mft_lmhead_ce_workspace_bytes": i64,

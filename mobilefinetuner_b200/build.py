@@ -95,14 +95,16 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 def build_operators(force: bool = False) -> Path:
     """Compile the C++ operator API (namespace ops: Tensor, autograd, ops::, LoRALinear, Adam) that sits on
     top of the C ABI into libmft_operators.so."""
-    srcs = sorted(OPERATORS.glob("finetune_ops/*/*.cpp"))
+    # the two dataset-driven trainer classes need the reference's dataset / tokenizer host code: they are built by
+    # operator/CMakeLists.txt when that code is available, not here
+    srcs = sorted(p for p in OPERATORS.glob("finetune_ops/*/*.cpp") if p.name not in ("trainer.cpp", "gemma_trainer.cpp"))
     hdrs = sorted(OPERATORS.glob("finetune_ops/*/*.h")) + sorted((PKG.parent / "include").glob("*.h"))
     newest = max(p.stat().st_mtime for p in srcs + hdrs + [LIB])
     if not force and OPERATORS_LIB.exists() and OPERATORS_LIB.stat().st_mtime >= newest:
         return OPERATORS_LIB
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
     cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", f"-I{OPERATORS}", f"-I{OPERATORS / 'finetune_ops'}", f"-I{OPERATORS / 'include'}",
-           *map(str, srcs), f"-L{PKG}", "-lmft_cuda", "-Wl,-rpath,$ORIGIN", "-o", str(OPERATORS_LIB)]
+           f"-I{PKG.parent / 'include'}", *map(str, srcs), f"-L{PKG}", "-lmft_cuda", "-Wl,-rpath,$ORIGIN", "-o", str(OPERATORS_LIB)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"building libmft_operators.so failed:\n{res.stdout}\n{res.stderr}")

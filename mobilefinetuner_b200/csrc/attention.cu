@@ -599,6 +599,8 @@ extern "C" int32_t mft_attn_fwd(const void* q, mft_strides_t sq, const void* k, 
     p.lse = lse; p.sq = sq; p.sk = sk; p.sv = sv; p.so = so; p.sdo = so;
     p.batch = (int)batch; p.seq = (int)seq; p.n_heads = (int)n_heads; p.n_kv = (int)n_kv; p.rep = (int)(n_heads / n_kv);
     p.scale = scale; p.window = (int)window;
+    MFT_CHECK_ARG(seq <= 65535 || (hd == 64 || hd == 128 || hd == 256), "mft_attn_fwd: sequence too long for this head_dim");
+    if (!(hd == 64 || hd == 128 || hd == 256)) return attn_generic_fwd(p, (int)hd, as_stream(stream));
     if (int32_t s = check_common(p, hd)) return s;
     {   // tcgen05 kernel when the problem qualifies
         const int32_t s2 = attn_fwd_sm100(p, (int)hd, as_stream(stream));
@@ -637,6 +639,8 @@ extern "C" int32_t mft_attn_bwd(const void* q, mft_strides_t sq, const void* k, 
     p.sq = sq; p.sk = sk; p.sv = sv; p.so = so; p.sdo = sdo;
     p.batch = (int)batch; p.seq = (int)seq; p.n_heads = (int)n_heads; p.n_kv = (int)n_kv; p.rep = (int)(n_heads / n_kv);
     p.scale = scale; p.window = (int)window;
+    MFT_CHECK_ARG(seq <= 65535 || (hd == 64 || hd == 128 || hd == 256), "mft_attn_bwd: sequence too long for this head_dim");
+    if (!(hd == 64 || hd == 128 || hd == 256)) return attn_generic_bwd(p, (int)hd, as_stream(stream));
     if (int32_t s = check_common(p, hd)) return s;
     const int64_t rows = batch * n_heads * seq;
     const unsigned dblocks = (unsigned)((rows * 32 + 255) / 256);
@@ -708,7 +712,10 @@ extern "C" int32_t mft_attn_bwd_noalloc(const void* q, mft_strides_t sq, const v
                                         int64_t n_heads, int64_t n_kv, int64_t hd, float scale, int64_t window,
                                         mft_stream_t stream) {
     MFT_CHECK_ARG(batch > 0 && seq > 0 && n_heads > 0, "mft_attn_bwd_noalloc: bad size");
-    if (batch * n_heads * seq > MFT_ATTN_NOALLOC_MAX_ROWS)
+    // each factor is bounded before the product is formed, so the product cannot wrap
+    MFT_CHECK_ARG(batch <= MFT_ATTN_NOALLOC_MAX_ROWS && seq <= MFT_ATTN_NOALLOC_MAX_ROWS && n_heads <= MFT_ATTN_NOALLOC_MAX_ROWS,
+                  "mft_attn_bwd_noalloc: size beyond the built-in scratch");
+    if (batch * n_heads > MFT_ATTN_NOALLOC_MAX_ROWS || batch * n_heads * seq > MFT_ATTN_NOALLOC_MAX_ROWS)
         return fail(MFT_ERR_INVALID_ARG, "mft_attn_bwd_noalloc: batch*n_heads*seq = " + std::to_string(batch * n_heads * seq) +
                                              " exceeds the built-in scratch of " + std::to_string(MFT_ATTN_NOALLOC_MAX_ROWS) +
                                              " rows; use mft_attn_bwd with a caller-supplied delta buffer");

@@ -28,4 +28,9 @@ int32_t attn_dq_sm100(const AttnParams& p, int hd, bool compute_delta, cudaStrea
 // needs p.dkv_acc and p.delta.
 int32_t attn_dkv_sm100(const AttnParams& p, int hd, cudaStream_t stream);
 
+// Any other head size (1..256): plain CUDA-core kernels, one CTA per row (attention_generic.cu).  The backward needs
+// p.delta as scratch; dK / dV are written directly (p.dkv_acc is not used).
+int32_t attn_generic_fwd(const AttnParams& p, int hd, cudaStream_t stream);
+int32_t attn_generic_bwd(const AttnParams& p, int hd, cudaStream_t stream);
+
 }  // namespace mft

@@ -13,6 +13,10 @@ namespace mft {
 // Thread-local last-error message plus the process-wide launch counter.
 void set_error(const std::string& msg);
 void count_launch(int n = 1);
+// With MFT_LAUNCH_REPORT=<file> in the environment the library also counts launches per kernel family (the name given
+// to MFT_LAUNCH_CHECK; kernels captured into a step graph are counted once, at capture) and writes "name count" lines
+// to that file when the process exits: a way to see from outside which kernels a host program ran.
+void note_launch(const char* name);
 int32_t* device_status_word();   // int32 in device memory, set by kernels whose bounded waits ran out
 
 int32_t fail(int32_t code, const std::string& msg);
@@ -52,6 +56,7 @@ cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 #define MFT_LAUNCH_CHECK(name)                                                 \
     do {                                                                       \
         ::mft::count_launch();                                                 \
+        ::mft::note_launch(name);                                              \
         cudaError_t e__ = cudaGetLastError();                                  \
         if (e__ != cudaSuccess) return ::mft::check_cuda(e__, name);           \
     } while (0)

@@ -423,6 +423,12 @@ int32_t mft_grad_sqnorm(const float* grads, int64_t n, float* sqnorm_dev, mft_st
     MFT_LAUNCH_CHECK("grad_sqnorm");
     return MFT_OK;
 }
+int32_t mft_grad_sqnorm_add(const float* grads, int64_t n, float* sqnorm_dev, mft_stream_t stream) {
+    MFT_CHECK_ARG(grads && sqnorm_dev && n > 0, "mft_grad_sqnorm_add: bad argument");
+    launch_dep(sqnorm_kernel, dim3(grid_for(n, 256, 148 * 4)), dim3(256), (size_t)(0), as_stream(stream), grads, n, sqnorm_dev);
+    MFT_LAUNCH_CHECK("grad_sqnorm_add");
+    return MFT_OK;
+}
 int32_t mft_adam_step(float* params, float* grads, float* m, float* v, int64_t n, int64_t step, float lr, float beta1,
                       float beta2, float eps, float wd, const float* sqnorm_dev, float max_norm, float clip_eps,
                       int32_t zero_grad, mft_stream_t stream) {

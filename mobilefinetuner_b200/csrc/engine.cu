@@ -110,8 +110,12 @@ extern "C" int32_t mft_model_create(const mft_model_config_t* cfg, mft_stream_t 
                   cfg->n_kv_heads > 0 && cfg->head_dim > 0 && cfg->max_batch > 0 && cfg->max_seq > 0, "mft_model_create: bad size");
     MFT_CHECK_ARG(cfg->hidden % 8 == 0 && cfg->inter % 8 == 0, "mft_model_create: hidden and inter must be multiples of 8");
     MFT_CHECK_ARG(cfg->n_heads % cfg->n_kv_heads == 0, "mft_model_create: n_heads must be a multiple of n_kv_heads");
-    MFT_CHECK_ARG(cfg->head_dim == 64 || cfg->head_dim == 128 || cfg->head_dim == 256, "mft_model_create: head_dim must be 64, 128 or 256");
-    MFT_CHECK_ARG(cfg->lora_rank >= 0 && cfg->lora_rank <= 64 && cfg->lora_rank % 8 == 0, "mft_model_create: LoRA rank must be a multiple of 8, at most 64");
+    // head sizes 64 / 128 / 256 run on the tiled tensor-core attention kernels, any other even size (test-sized models)
+    // on the plain CUDA-core ones; the projections' widths are GEMM row strides and must be multiples of 8 elements
+    MFT_CHECK_ARG(cfg->head_dim >= 2 && cfg->head_dim <= 256 && cfg->head_dim % 2 == 0, "mft_model_create: head_dim must be even, at most 256");
+    MFT_CHECK_ARG((cfg->n_heads * cfg->head_dim) % 8 == 0 && ((cfg->n_heads + 2 * cfg->n_kv_heads) * cfg->head_dim) % 8 == 0,
+                  "mft_model_create: n_heads*head_dim and (n_heads + 2 n_kv_heads)*head_dim must be multiples of 8");
+    MFT_CHECK_ARG(cfg->lora_rank >= 0 && cfg->lora_rank <= 64, "mft_model_create: LoRA rank must be at most 64");
     if (!device_status_word()) return fail(MFT_ERR_INVALID_ARG, "mft_model_create: call mft_init first");
     const bool gpt2 = cfg->family == MFT_FAMILY_GPT2, qwen = cfg->family == MFT_FAMILY_QWEN, gemma = cfg->family == MFT_FAMILY_GEMMA;
     MFT_CHECK_ARG(!gpt2 || (cfg->n_heads == cfg->n_kv_heads && cfg->n_heads * cfg->head_dim == cfg->hidden && cfg->n_positions >= cfg->max_seq),
@@ -478,6 +482,17 @@ extern "C" int32_t mft_model_get_lora_grad_host(mft_model_t* m, int32_t idx, flo
     MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->loras.size() && data_host, "mft_model_get_lora_grad_host: bad argument");
     const LoraInfo& t = m->loras[idx];
     return mft_memcpy_d2h(data_host, m->g_bucket + t.offset, (size_t)t.rows * t.cols * 4, m->stream);
+}
+extern "C" int32_t mft_model_lora_offset(const mft_model_t* m, int32_t idx, int64_t* offset) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->loras.size() && offset, "mft_model_lora_offset: bad argument");
+    *offset = m->loras[idx].offset;
+    return MFT_OK;
+}
+extern "C" int32_t mft_model_mark_lora_dirty(mft_model_t* m) {
+    MFT_CHECK_ARG(m, "mft_model_mark_lora_dirty: null model");
+    MFT_CHECK_ARG(!m->merged, "mft_model_mark_lora_dirty: the adapters are merged into the base weights: unmerge first");
+    m->panels_dirty = true;
+    return MFT_OK;
 }
 extern "C" int32_t mft_model_buckets(mft_model_t* m, float** params_dev, float** grads_dev, int64_t* n) {
     MFT_CHECK_ARG(m, "mft_model_buckets: null model");

@@ -346,6 +346,35 @@ extern "C" int32_t mft_model_forward_loss(mft_model_t* m, const int32_t* ids_hos
     return check_status(m);
 }
 
+// Dense logits of the positions computed by the last forward pass: out[t, v] = hidden_final[t, :] . table[v, :]
+// (f32 [batch*seq, vocab]).  Only for callers that insist on the materialised [B,S,V] tensor; training and
+// evaluation never form it.
+extern "C" int32_t mft_model_forward_logits(mft_model_t* m, const int32_t* ids_host, int32_t batch, int32_t seq, float* logits_dev) {
+    Ctx c;
+    TRY(make_ctx(m, batch, seq, &c));
+    MFT_CHECK_ARG(ids_host && logits_dev, "mft_model_forward_logits: null argument");
+    TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)c.T * 4, c.st));
+    TRY(mft_memcpy_h2d(m->labels, ids_host, (size_t)c.T * 4, c.st));      // any valid labels: the loss is not used
+    TRY(refresh_panels(m));
+    TRY(forward(c, false));
+    TRY(mft_gemm_nt(m->hf, m->cfg.hidden, m->embed, m->cfg.hidden, c.T, m->cfg.vocab, m->cfg.hidden, nullptr, 0, nullptr, 0, 0, nullptr, 1.0f,
+                    logits_dev, m->cfg.vocab, MFT_F32, 0, c.st));
+    return check_status(m);
+}
+
+// The final-norm output of a forward pass as f32 [batch*seq, hidden] on the device (QwenModel::forward_hidden).
+extern "C" int32_t mft_model_forward_hidden(mft_model_t* m, const int32_t* ids_host, int32_t batch, int32_t seq, float* hidden_dev) {
+    Ctx c;
+    TRY(make_ctx(m, batch, seq, &c));
+    MFT_CHECK_ARG(ids_host && hidden_dev, "mft_model_forward_hidden: null argument");
+    TRY(mft_memcpy_h2d(m->ids, ids_host, (size_t)c.T * 4, c.st));
+    TRY(mft_memcpy_h2d(m->labels, ids_host, (size_t)c.T * 4, c.st));
+    TRY(refresh_panels(m));
+    TRY(forward(c, false));
+    TRY(mft_cast_bf16_to_f32(m->hf, hidden_dev, c.T * m->cfg.hidden, c.st));
+    return check_status(m);
+}
+
 // ---------------------------------------------------------------- double-buffered input
 static int32_t ensure_slots(mft_model* m) {
     if (m->copy_stream) return MFT_OK;

@@ -649,6 +649,65 @@ __global__ void headnorm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64
     }
 }
 
+// Same operation for any even head size (test-sized models: 4, 8, 16, ... wide heads): one warp per (token, head),
+// lanes stride over the pairs (d, d + hd/2), scalar accesses only.
+template <bool BWD>
+__global__ void headnorm_rope_any_kernel(const __nv_bfloat16* __restrict__ in, int64_t ld_in, const __nv_bfloat16* __restrict__ x, int64_t ld_x,
+                                         const float* __restrict__ nw, float eps, float* __restrict__ rstd_buf,
+                                         const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                         __nv_bfloat16* __restrict__ out, int64_t ld_out, int64_t n_tokens, int64_t seq_len, int64_t n_heads, int hd) {
+    dep_trigger();
+    dep_wait();
+    const int half = hd / 2;
+    const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= n_tokens * n_heads) return;
+    const int64_t tok = wid / n_heads, head = wid % n_heads, pos = tok % seq_len;
+    const __nv_bfloat16* p = in + tok * ld_in + head * hd;
+    __nv_bfloat16* o = out + tok * ld_out + head * hd;
+    if (!BWD) {
+        float rstd = 1.0f;
+        if (nw) {
+            float ss = 0.f;
+            for (int d = lane; d < hd; d += 32) { const float v = bf16_to_f32(p[d]); ss += v * v; }
+            ss = warp_sum(ss);
+            rstd = rsqrtf(ss / (float)hd + eps);
+            if (lane == 0 && rstd_buf) rstd_buf[wid] = rstd;
+        }
+        for (int d = lane; d < half; d += 32) {
+            const float c = cos_tab ? cos_tab[pos * half + d] : 1.f, sn = sin_tab ? sin_tab[pos * half + d] : 0.f;
+            const float x1 = bf16_to_f32(p[d]) * rstd * (nw ? 1.0f + nw[d] : 1.0f);
+            const float x2 = bf16_to_f32(p[half + d]) * rstd * (nw ? 1.0f + nw[half + d] : 1.0f);
+            o[d] = f32_to_bf16(x1 * c - x2 * sn);
+            o[half + d] = f32_to_bf16(x1 * sn + x2 * c);
+        }
+    } else {
+        const __nv_bfloat16* xp = nw ? x + tok * ld_x + head * hd : nullptr;
+        float dot = 0.f;
+        if (nw)
+            for (int d = lane; d < half; d += 32) {
+                const float c = cos_tab ? cos_tab[pos * half + d] : 1.f, sn = sin_tab ? sin_tab[pos * half + d] : 0.f;
+                const float a = bf16_to_f32(p[d]), b = bf16_to_f32(p[half + d]);
+                const float g1 = (a * c + b * sn) * (1.0f + nw[d]), g2 = (-a * sn + b * c) * (1.0f + nw[half + d]);
+                dot += g1 * bf16_to_f32(xp[d]) + g2 * bf16_to_f32(xp[half + d]);
+            }
+        dot = warp_sum(dot);
+        const float rstd = nw ? rstd_buf[wid] : 1.0f;
+        const float coeff = nw ? rstd * rstd * rstd / (float)hd * dot : 0.f;
+        for (int d = lane; d < half; d += 32) {
+            const float c = cos_tab ? cos_tab[pos * half + d] : 1.f, sn = sin_tab ? sin_tab[pos * half + d] : 0.f;
+            const float a = bf16_to_f32(p[d]), b = bf16_to_f32(p[half + d]);
+            float g1 = a * c + b * sn, g2 = -a * sn + b * c;
+            if (nw) {
+                g1 = g1 * (1.0f + nw[d]) * rstd - bf16_to_f32(xp[d]) * coeff;
+                g2 = g2 * (1.0f + nw[half + d]) * rstd - bf16_to_f32(xp[half + d]) * coeff;
+            }
+            o[d] = f32_to_bf16(g1);
+            o[half + d] = f32_to_bf16(g2);
+        }
+    }
+}
+
 }  // namespace mft
 
 using namespace mft;
@@ -793,7 +852,11 @@ static int32_t launch_headnorm_rope(bool bwd, const void* in, int64_t ld_in, con
     if (hd == 64) { if (bwd) HL2(1, true, false); else HL2(1, false, false); }
     else if (hd == 128) { if (bwd) HL(2, true); else HL(2, false); }
     else if (hd == 256) { if (bwd) HL(4, true); else HL(4, false); }
-    else return fail(MFT_ERR_UNSUPPORTED, "headnorm_rope: head_dim must be 64, 128 or 256");
+    else if (hd > 0 && hd % 2 == 0 && hd <= 4096) {
+        if (bwd) launch_dep(headnorm_rope_any_kernel<true>, dim3(blocks), dim3(threads), (size_t)(0), as_stream(stream), (const __nv_bfloat16*)in, ld_in, (const __nv_bfloat16*)x, ld_x, nw, eps, rstd, cos_tab, sin_tab, (__nv_bfloat16*)out, ld_out, n_tokens, seq_len, n_heads, (int)hd);
+        else launch_dep(headnorm_rope_any_kernel<false>, dim3(blocks), dim3(threads), (size_t)(0), as_stream(stream), (const __nv_bfloat16*)in, ld_in, (const __nv_bfloat16*)x, ld_x, nw, eps, rstd, cos_tab, sin_tab, (__nv_bfloat16*)out, ld_out, n_tokens, seq_len, n_heads, (int)hd);
+    }
+    else return fail(MFT_ERR_UNSUPPORTED, "headnorm_rope: head_dim must be even");
 #undef HL
 #undef HL2
     MFT_LAUNCH_CHECK("headnorm_rope");

@@ -1,6 +1,7 @@
 // Runtime part of libmft_cuda.so: initialisation, error reporting, the caching
 // device allocator (the device analogue of the reference's MemoryManager /
 // MemoryPool, operator/finetune_ops/core/memory_manager.cpp:34-145) and copies.
+#include <cstdio>
 #include <cstdlib>
 #include <atomic>
 #include <map>
@@ -20,6 +21,29 @@ static std::mutex g_init_mutex;
 
 void set_error(const std::string& msg) { g_last_error = msg; }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+struct LaunchReport {
+    std::string path;
+    std::mutex mu;
+    std::map<std::string, int64_t> counts;
+    LaunchReport() { if (const char* e = std::getenv("MFT_LAUNCH_REPORT")) path = e; }
+    ~LaunchReport() {
+        if (path.empty()) return;
+        if (FILE* f = std::fopen(path.c_str(), "w")) {
+            for (const auto& kv : counts) std::fprintf(f, "%s %lld\n", kv.first.c_str(), (long long)kv.second);
+            std::fclose(f);
+        }
+    }
+};
+LaunchReport& launch_report() { static LaunchReport r; return r; }
+}  // namespace
+void note_launch(const char* name) {
+    LaunchReport& r = launch_report();
+    if (r.path.empty()) return;
+    std::lock_guard<std::mutex> lk(r.mu);
+    ++r.counts[name];
+}
 bool dep_launch_enabled() {
     static const bool on = [] { const char* e = std::getenv("MFT_PDL"); return e ? std::atoi(e) != 0 : false; }();
     return on;

@@ -2,7 +2,8 @@
 
 #include <stdexcept>
 
-#include "../../../../include/mft_cuda.h"
+#include "mft_cuda.h"
+#include "../graph/engine_model.h"
 #include "ops.h"
 
 namespace ops {
@@ -10,8 +11,20 @@ namespace ops {
 using detail::check;
 using detail::stream;
 
+// The producer behind a model's forward() / forward_hidden() result, while nothing has forced the dense value yet.
+static std::shared_ptr<detail::LazyLogits> deferred_model_output(const TensorPtr& t, bool hidden) {
+    if (!t || !t->deferred()) return nullptr;
+    auto ll = std::dynamic_pointer_cast<detail::LazyLogits>(t->deferred());
+    return (ll && ll->hidden == hidden) ? ll : nullptr;
+}
+
 TensorPtr lm_cross_entropy(const TensorPtr& logits, const TensorPtr& labels, int ignore_index, const std::string& reduction) {
     if (!logits || !labels) throw std::runtime_error("lm_cross_entropy: null tensor");
+    // Logits that a model's forward() handed out and nobody has read: run the fused lm head + loss (+ backward)
+    // on the device, the [B,S,V] tensor is never formed (lm_cross_entropy core/lm_loss.cpp:268-382 on the values it
+    // would hold).
+    if (auto ll = deferred_model_output(logits, false))
+        if (auto m = ll->model.lock()) return m->loss(ll->ids, ll->batch, ll->seq, labels, ignore_index, reduction);
     if (logits->dtype() != kFloat32 || labels->dtype() != kInt32) throw std::runtime_error("lm_cross_entropy: expects float32 logits and int32 labels");
     if (logits->shape().size() != 3 || labels->shape().size() != 2) throw std::runtime_error("lm_cross_entropy: expects logits [B,S,V] and labels [B,S]");
     if (reduction != "mean" && reduction != "sum") throw std::runtime_error("lm_cross_entropy: reduction must be 'mean' or 'sum' on this backend");
@@ -43,6 +56,11 @@ TensorPtr lm_cross_entropy(const TensorPtr& logits, const TensorPtr& labels, int
 
 TensorPtr selected_token_lm_cross_entropy(const TensorPtr& hidden, const TensorPtr& W, const TensorPtr& labels, int ignore_index, const std::string& reduction) {
     if (!hidden || !W || !labels) throw std::runtime_error("selected_token_lm_cross_entropy: null tensor");
+    // hidden states a model's forward_hidden() handed out, scored against that model's own (tied) table: fused path
+    if (auto ll = deferred_model_output(hidden, true))
+        if (auto m = ll->model.lock())
+            if (W->shape().size() == 2 && W->shape()[0] == m->architecture().vocab && W->shape()[1] == m->architecture().hidden)
+                return m->loss(ll->ids, ll->batch, ll->seq, labels, ignore_index, reduction);
     if (hidden->shape().size() != 3 || W->shape().size() != 2 || W->shape()[1] != hidden->shape()[2])
         throw std::runtime_error("selected_token_lm_cross_entropy: expects hidden [B,S,H] and weight [V,H]");
     // fp32 operator path: logits are formed by the generic matmul so that loss and gradients keep fp32 accuracy;

@@ -5,7 +5,7 @@
 #include <cstring>
 #include <iostream>
 
-#include "../../../../include/mft_cuda.h"
+#include "mft_cuda.h"
 
 namespace ops {
 

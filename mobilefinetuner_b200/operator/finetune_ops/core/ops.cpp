@@ -9,7 +9,7 @@
 #include <numeric>
 #include <stdexcept>
 
-#include "../../../../include/mft_cuda.h"
+#include "mft_cuda.h"
 #include "autograd_engine.h"
 
 namespace ops {

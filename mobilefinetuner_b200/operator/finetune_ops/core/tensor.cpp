@@ -8,7 +8,7 @@
 #include <random>
 #include <sstream>
 
-#include "../../../../include/mft_cuda.h"
+#include "mft_cuda.h"
 #include "autograd_engine.h"
 #include "ops.h"
 
@@ -49,7 +49,10 @@ void Tensor::allocate_host() {
 }
 
 void Tensor::release() {
-    if (dev_) { mft_free(dev_, detail::stream()); dev_ = nullptr; }
+    if (dev_ && owns_dev_) mft_free(dev_, detail::stream());
+    dev_ = nullptr;
+    owns_dev_ = true;
+    deferred_.reset();
     if (host_ && owns_host_) std::free(host_);
     host_ = nullptr;
     bytes_ = 0;
@@ -95,17 +98,65 @@ Tensor& Tensor::operator=(Tensor&& o) noexcept {
     if (this == &o) return *this;
     release();
     shape_ = std::move(o.shape_); dtype_ = o.dtype_; device_ = o.device_;
-    host_ = o.host_; dev_ = o.dev_; bytes_ = o.bytes_; owns_host_ = o.owns_host_; valid_ = o.valid_;
+    host_ = o.host_; dev_ = o.dev_; bytes_ = o.bytes_; owns_host_ = o.owns_host_; owns_dev_ = o.owns_dev_; valid_ = o.valid_;
+    host_escaped_ = o.host_escaped_; host_writes_ = o.host_writes_; deferred_ = std::move(o.deferred_);
     requires_grad_ = o.requires_grad_; grad_ = std::move(o.grad_); grad_fn_ = std::move(o.grad_fn_);
     retain_grad_ = o.retain_grad_; grad_node_ = std::move(o.grad_node_);
-    o.host_ = nullptr; o.dev_ = nullptr; o.bytes_ = 0;
+    o.host_ = nullptr; o.dev_ = nullptr; o.bytes_ = 0; o.owns_dev_ = true;
     return *this;
 }
 
 Tensor::~Tensor() { release(); }
 
 // ---------------------------------------------------------------- coherence
+TensorPtr Tensor::make_deferred(const std::vector<int64_t>& shape, DType dtype, std::shared_ptr<Deferred> producer) {
+    auto t = std::make_shared<Tensor>();
+    t->shape_ = shape;
+    t->dtype_ = dtype;
+    t->bytes_ = static_cast<size_t>(t->numel()) * DTypeUtils::size_of(dtype);
+    t->valid_ = 0;
+    t->deferred_ = std::move(producer);
+    return t;
+}
+
+void Tensor::materialize() const {
+    if (!deferred_) return;
+    std::shared_ptr<Deferred> p = std::move(deferred_);
+    deferred_.reset();
+    p->materialize(*const_cast<Tensor*>(this));          // fills the device copy
+}
+
+void Tensor::bind_device(void* dev) {
+    if (!dev) throw TensorError("bind_device: null pointer");
+    materialize();
+    if (dev_ == dev) return;
+    if (bytes_) {
+        if ((valid_ & DEV_VALID) && dev_) detail::check(mft_memcpy_d2d(dev, dev_, bytes_, detail::stream()), "bind_device");
+        else {
+            detail::check(mft_memcpy_h2d(dev, host_, bytes_, detail::stream()), "bind_device upload");
+            detail::check(mft_stream_sync(detail::stream()), "stream sync");
+        }
+    }
+    if (dev_ && owns_dev_) mft_free(dev_, detail::stream());
+    dev_ = dev;
+    owns_dev_ = false;
+    valid_ |= DEV_VALID;
+}
+
+void Tensor::unbind_device() {
+    if (owns_dev_) return;
+    sync_to_host();
+    dev_ = nullptr;
+    owns_dev_ = true;
+    valid_ = HOST_VALID;
+}
+
 void Tensor::sync_to_host() const {
+    materialize();
+    if (!host_) {
+        host_ = std::calloc(bytes_ ? bytes_ : 1, 1);
+        if (!host_) throw TensorError("out of host memory");
+    }
     if (valid_ & HOST_VALID) return;
     if (bytes_) detail::check(mft_memcpy_d2h(host_, dev_, bytes_, detail::stream()), "device -> host copy");
     valid_ |= HOST_VALID;
@@ -113,6 +164,7 @@ void Tensor::sync_to_host() const {
 
 void Tensor::ensure_device() const {
     detail::ensure_runtime();
+    materialize();
     if (!dev_) {
         void* p = nullptr;
         detail::check(mft_malloc(bytes_ ? bytes_ : 4, detail::stream(), &p), "mft_malloc");
@@ -130,11 +182,12 @@ void Tensor::ensure_device() const {
 }
 
 const void* Tensor::host_ro() const { sync_to_host(); return host_; }
-void* Tensor::host_rw() { sync_to_host(); valid_ = HOST_VALID; host_escaped_ = true; return host_; }
+void* Tensor::host_rw() { sync_to_host(); valid_ = HOST_VALID; host_escaped_ = true; ++host_writes_; return host_; }
 const void* Tensor::device_read() const { ensure_device(); return dev_; }
 void* Tensor::device_readwrite() { ensure_device(); valid_ = DEV_VALID; host_escaped_ = false; return dev_; }
 void* Tensor::device_write() {
     detail::ensure_runtime();
+    deferred_.reset();
     if (!dev_) {
         void* p = nullptr;
         detail::check(mft_malloc(bytes_ ? bytes_ : 4, detail::stream(), &p), "mft_malloc");

@@ -21,8 +21,9 @@
 #include <exception>
 #include <functional>
 #include <initializer_list>
-#include <iosfwd>
+#include <iostream>      // callers written against the reference's header count on <iostream> / <stdexcept> arriving with it
 #include <memory>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -39,6 +40,16 @@ class Node;
 class Engine;
 using NodePtr = std::shared_ptr<Node>;
 }  // namespace autograd
+
+// A value that is computed on first use.  A tensor built by Tensor::make_deferred has a shape and a dtype but no
+// storage; the first host or device access calls materialize(), which must fill the device copy through
+// Tensor::device_write().  Consumers that can do better than the dense value (lm_cross_entropy on a model's
+// logits) look at deferred() first and never trigger it.
+class Deferred {
+public:
+    virtual ~Deferred() = default;
+    virtual void materialize(Tensor& into) = 0;
+};
 
 class TensorError : public std::exception {
 public:
@@ -82,6 +93,18 @@ public:
     void* device_write();                // device copy about to be fully overwritten: host copy becomes stale
     void* device_readwrite();            // valid device copy that a kernel will modify
     size_t nbytes() const { return bytes_; }
+    // Makes `dev` (caller-owned device memory of nbytes(), e.g. a slice of a flat parameter bucket) this tensor's
+    // device copy.  The current value moves there; from then on kernels that read or update the tensor work on
+    // that memory directly.  unbind_device() brings the value back into storage the tensor owns.
+    void bind_device(void* dev);
+    void unbind_device();
+    const void* bound_device() const { return owns_dev_ ? nullptr : dev_; }
+    // Counts the mutable host pointers handed out (every one may have been written through).
+    uint64_t host_write_count() const { return host_writes_; }
+    bool host_dirty() const { return host_escaped_ || !(valid_ & DEV_VALID); }
+    // A tensor whose value is produced on first access.
+    static TensorPtr make_deferred(const std::vector<int64_t>& shape, DType dtype, std::shared_ptr<Deferred> producer);
+    const std::shared_ptr<Deferred>& deferred() const { return deferred_; }
 
     TensorPtr to(const Device& device) const;
     TensorPtr cpu() const { return to(kCPU); }
@@ -129,6 +152,9 @@ private:
     mutable void* dev_ = nullptr;
     size_t bytes_ = 0;
     bool owns_host_ = true;
+    bool owns_dev_ = true;
+    uint64_t host_writes_ = 0;
+    mutable std::shared_ptr<Deferred> deferred_;
     mutable uint8_t valid_ = HOST_VALID;
     bool host_escaped_ = false;      // a mutable host pointer is out: the device copy can go stale at any time
 
@@ -143,6 +169,7 @@ private:
     void* host_rw();
     const void* host_ro() const;
     void sync_to_host() const;
+    void materialize() const;
     void ensure_device() const;
     TensorPtr self() const;
 

@@ -5,8 +5,8 @@
 #include <iostream>
 #include <stdexcept>
 
-#include "../../../../include/mft_cuda.h"
-#include "../../../../include/mft_step.h"
+#include "mft_cuda.h"
+#include "mft_step.h"
 
 namespace ops {
 

@@ -4,7 +4,7 @@
 #include <fstream>
 #include <stdexcept>
 
-#include "../../../../include/mft_cuda.h"
+#include "mft_cuda.h"
 
 namespace ops {
 
@@ -13,15 +13,16 @@ using detail::stream;
 
 float Optimizer::compute_grad_norm(const std::vector<TensorPtr>& parameters) {
     detail::ensure_runtime();
+    // one device accumulator for all tensors, one read-back
     auto acc = std::make_shared<Tensor>(std::vector<int64_t>{1}, kFloat32, kCPU);
-    float total = 0.f;
+    float* sum = (float*)acc->device_write();
+    check(mft_memset(sum, 0, 4, stream()), "grad norm");
     for (auto& p : parameters) {
         if (!p || !p->grad()) continue;
         auto g = p->grad();
-        check(mft_grad_sqnorm((const float*)g->device_read(), g->numel(), (float*)acc->device_write(), stream()), "grad norm");
-        total += static_cast<const Tensor&>(*acc).data<float>()[0];
+        check(mft_grad_sqnorm_add((const float*)g->device_read(), g->numel(), sum, stream()), "grad norm");
     }
-    return std::sqrt(total);
+    return std::sqrt(static_cast<const Tensor&>(*acc).data<float>()[0]);
 }
 void Optimizer::scale_gradients(const std::vector<TensorPtr>& parameters, float scale) {
     for (auto& p : parameters)

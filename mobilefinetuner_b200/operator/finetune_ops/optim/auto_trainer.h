@@ -1,5 +1,7 @@
 // AutoTrainer of the operator API (same interface as the reference's optim/auto_trainer.h): one call =
-// forward + lm_cross_entropy + backward + clip_grad_norm + Adam::step + zero_grad, all on the device.
+// forward -> lm_cross_entropy -> backward -> clip_grad_norm -> Adam::step -> zero_grad.  With a model of graph/*.h the
+// forward / loss / backward part is one fused device pass and the adapters, their gradients and the Adam moments
+// never leave the GPU.
 #pragma once
 #include <memory>
 
@@ -23,11 +25,12 @@ struct AutoTrainStepResult {
 
 class AutoTrainer {
 public:
-    AutoTrainer(AutoModelForCausalLM& model, const AutoTrainerConfig& config = AutoTrainerConfig()) : model_(model), config_(config) {}
+    AutoTrainer(AutoModelForCausalLM& model, const AutoTrainerConfig& config = AutoTrainerConfig());
     AutoTrainStepResult train_step(const TensorPtr& input_ids, const TensorPtr& attention_mask, const TensorPtr& labels);
 private:
     AutoModelForCausalLM& model_;
     AutoTrainerConfig config_;
+    std::unique_ptr<Adam> optimizer_;
 };
 
 }  // namespace ops

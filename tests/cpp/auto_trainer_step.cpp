@@ -16,6 +16,7 @@
 
 #include "mobile_finetuner/mobile_finetuner.h"
 #include "finetune_ops/graph/auto_model.h"
+#include "finetune_ops/core/lm_loss.h"
 #include "finetune_ops/optim/auto_trainer.h"
 
 static void read_bin(const std::string& path, void* dst, size_t bytes) {
@@ -62,16 +63,18 @@ int main(int argc, char** argv) {
         read_bin(dir + "/ids.bin", ids->data<int32_t>(), (size_t)B * S * 4);
         read_bin(dir + "/labels.bin", labels->data<int32_t>(), (size_t)B * S * 4);
 
-        // gradients of the same batch first (the trainer zeroes them as part of its step)
-        const float loss0 = model->forward_backward(ids, labels);
-        auto grads = model->lora_gradients();
-        for (size_t i = 0; i < grads.size(); ++i)
-            if (grads[i]) write_bin(dir + "/out/grad_" + idx(i) + ".bin", grads[i]->data<float>(), (size_t)grads[i]->numel() * 4);
-        model->optimizer_step(0.f, 0.9f, 0.999f, 1e-8f, 0.f, 0.f);      // lr = 0: only clears the accumulated gradients
-        // ... then Adam's moments must not carry that dummy step into the measured one: rebuild the model state
-        model->init_lora(lc);
-        lora = model->trainable_parameters();
-        for (size_t i = 0; i < lora.size(); ++i) read_bin(dir + "/lora/" + idx(i) + ".bin", lora[i]->data<float>(), (size_t)lora[i]->numel() * 4);
+        // gradients of the same batch first, through the reference's own sequence (forward -> lm_cross_entropy ->
+        // backward); the trainer's step below starts from cleared gradients again
+        {
+            auto logits = model->forward(ids, mask);
+            auto loss = ops::lm_cross_entropy(logits, labels, -100, "mean");
+            loss->backward();
+            const float loss0 = static_cast<const ops::Tensor&>(*loss).data<float>()[0];
+            write_bin(dir + "/out/loss0.bin", &loss0, 4);
+            for (size_t i = 0; i < lora.size(); ++i)
+                if (auto g = lora[i]->grad()) write_bin(dir + "/out/grad_" + idx(i) + ".bin", static_cast<const ops::Tensor&>(*g).data<float>(), (size_t)g->numel() * 4);
+            for (auto& p : lora) p->zero_grad();
+        }
 
         ops::AutoTrainerConfig tc;
         tc.learning_rate = std::stof(kv.at("lr"));
@@ -79,7 +82,6 @@ int main(int argc, char** argv) {
         ops::AutoTrainer trainer(*model, tc);
         const auto res = trainer.train_step(ids, mask, labels);
         write_bin(dir + "/out/loss.bin", &res.loss, 4);
-        write_bin(dir + "/out/loss0.bin", &loss0, 4);
         auto after = model->trainable_parameters();
         for (size_t i = 0; i < after.size(); ++i) write_bin(dir + "/out/lora_" + idx(i) + ".bin", static_cast<const ops::Tensor&>(*after[i]).data<float>(), (size_t)after[i]->numel() * 4);
         std::printf("loss %.6f tensors %d\n", res.loss, res.trainable_tensor_count);

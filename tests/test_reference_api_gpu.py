@@ -1,9 +1,14 @@
 """GPU suite: the reference's OWN unit tests for the step's path (analytic attention / softmax /
-repeat-kv / RMSNorm / RoPE / cross-entropy / LoRA-merge / leaf-accumulation answers), compiled
-unchanged against this repo's C++ operator API (mobilefinetuner_b200/operator, namespace ops) and
-linked with libmft_operators.so -> libmft_cuda.so, so every operator they call runs as CUDA kernels.
-The executables are built by `make -C oracle api_tests` where the reference tree is mounted and
-travel with the repo; their sources are never copied into it."""
+repeat-kv / RMSNorm / RoPE / cross-entropy / LoRA-merge / leaf-accumulation / mixed-precision answers,
+the AutoModel + AutoTrainer step of all three families, the two-step GPT-2 LoRA smoke, adapter file
+round trips, the model registry), compiled unchanged against this repo's C++ operator API
+(mobilefinetuner_b200/operator, namespace ops) and linked with libmft_operators.so -> libmft_cuda.so,
+so every operator they call runs as CUDA kernels.  Likewise one of the reference's example programs
+(examples/gpt2_small_lora_finetune), configured and built UNCHANGED through this repo's `operators`
+CMake target and run in its self-contained --synthetic_smoke mode.  The executables are built by
+`make -C oracle api_tests cli` where the reference tree is mounted and travel with the repo; their
+sources are never copied into it."""
+import os
 import subprocess
 from pathlib import Path
 
@@ -15,7 +20,8 @@ ROOT = Path(__file__).resolve().parents[1]
 BIN = ROOT / "oracle" / "_ref" / "api_tests"
 NAMES = ["test_qkt_softmax_grad", "test_repeat_kv_softmax_grad", "test_attention_single_layer_backward", "test_rmsnorm_unit",
          "test_apply_rope_layout", "test_autograd_leaf_accum", "test_selected_token_lm_loss", "test_memory_efficient_attention_grad",
-         "test_lora_linear", "test_tensor_slice"]
+         "test_lora_linear", "test_tensor_slice", "test_dtype_mixed_precision", "test_auto_model", "test_gpt2_lora_two_step_smoke",
+         "test_lora_roundtrip", "test_gemma_lora_roundtrip", "test_model_registry"]
 
 
 @pytest.mark.parametrize("name", NAMES)
@@ -24,3 +30,21 @@ def test_reference_unit_test_passes_on_gpu(name):
     exe = require_built(BIN / name, "the reference unit test compiled against this repository's operator API")
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, f"{name} failed:\n{r.stdout[-3000:]}\n{r.stderr[-2000:]}"
+
+
+def test_reference_gpt2_cli_builds_unchanged_and_trains(tmp_path):
+    """examples/gpt2_small_lora_finetune `train --synthetic_smoke`: GPT2Model + LoraInjector + the program's own
+    forward -> lm_cross_entropy -> backward -> Adam loop.  The library's launch report must show the tensor-core GEMM
+    and the fused attention / loss kernels, not the generic fp32 operators."""
+    from parity import require_built
+    exe = require_built(ROOT / "oracle" / "_ref" / "cli" / "gpt2_small_train", "the reference's GPT-2 example built against this repository's operators target")
+    report = tmp_path / "launches.txt"
+    env = dict(os.environ, MFT_LAUNCH_REPORT=str(report), LD_LIBRARY_PATH=str(ROOT / "mobilefinetuner_b200") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+    out = tmp_path / "adapter.safetensors"
+    r = subprocess.run([str(exe), "--synthetic_smoke", "--smoke_steps", "3", "--lora_out", str(out)], capture_output=True, text=True, timeout=300, env=env, cwd=tmp_path)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert "[PASS]" in r.stdout
+    assert out.exists() and out.stat().st_size > 0
+    names = report.read_text()
+    assert "gemm_nt" in names and "attn_" in names, names
+    assert "matmul_f32" not in names, names

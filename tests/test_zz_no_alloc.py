@@ -18,7 +18,9 @@ def _problem(seed, b, nh, nkv, s, hd):
 
 def test_noalloc_backward_matches_regular_entry_point_twice():
     from mobilefinetuner_b200 import ops as O
-    for seed, shape, window in [(1, (2, 4, 1, 300, 256), 64), (2, (1, 6, 2, 129, 64), 0)]:
+    # the last two shapes (head_dim 256, sequence a multiple of 128) take the tensor-memory dQ kernel, which reads the
+    # row sums straight from the built-in array; the first two take the mma.sync kernels
+    for seed, shape, window in [(1, (2, 4, 1, 300, 256), 64), (2, (1, 6, 2, 129, 64), 0), (3, (1, 4, 1, 256, 256), 0), (4, (1, 4, 1, 256, 256), 64)]:
         q, k, v, d_o = _problem(seed, *shape)
         scale = shape[-1] ** -0.5
         o, lse = O.attention_fwd(q, k, v, scale, window)
