@@ -714,7 +714,7 @@ extern "C" int32_t mft_attn_bwd_noalloc(const void* q, mft_strides_t sq, const v
     MFT_CHECK_ARG(batch > 0 && seq > 0 && n_heads > 0, "mft_attn_bwd_noalloc: bad size");
     // each factor is bounded before the product is formed, so the product cannot wrap
     MFT_CHECK_ARG(batch <= MFT_ATTN_NOALLOC_MAX_ROWS && seq <= MFT_ATTN_NOALLOC_MAX_ROWS && n_heads <= MFT_ATTN_NOALLOC_MAX_ROWS,
-                  "mft_attn_bwd_noalloc: size beyond the built-in scratch");
+                  "mft_attn_bwd_noalloc: the problem exceeds the built-in scratch; use mft_attn_bwd with a caller-supplied delta buffer");
     if (batch * n_heads > MFT_ATTN_NOALLOC_MAX_ROWS || batch * n_heads * seq > MFT_ATTN_NOALLOC_MAX_ROWS)
         return fail(MFT_ERR_INVALID_ARG, "mft_attn_bwd_noalloc: batch*n_heads*seq = " + std::to_string(batch * n_heads * seq) +
                                              " exceeds the built-in scratch of " + std::to_string(MFT_ATTN_NOALLOC_MAX_ROWS) +
