@@ -37,7 +37,7 @@ def mode_step(world, out):
     ids, labels = synth.make_batch(spec, B, S, 3)
     labels = labels.copy()
     labels[1, S // 2:] = -100                          # ranks score different numbers of tokens
-    cfg = StepConfig(lr=2e-4, max_grad_norm=1.0)
+    cfg = StepConfig("two_rank_case", spec, B, S, lr=2e-4, max_grad_norm=1.0)
     sl = world.shard(B)
     eng = make_engine(spec, B, S, world.local_rank)
     n_global = world.global_valid_count(labels[sl])
