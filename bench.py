@@ -85,14 +85,31 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-GATE_UP_TRAFFIC_BYTES = 4.75e8   # 72 MB read + 403 MB written per launch (algorithmic: 524 MB)
+def profiled_traffic_bytes(spec_name: str, tokens: int):
+    """DRAM bytes per launch of the dominant kernel (the gate|up projection GEMM), read from the ncu summary under
+    profiles/: the line `traffic_bytes_per_launch <model> <tokens> <bytes>` there is derived from the capture
+    described next to it.  None when no capture covers this workload."""
+    path = ROOT / "profiles" / "gemm_nt_kernels_gemma3_1b_gate_up.md"
+    if not path.exists():
+        return None
+    for line in path.read_text().splitlines():
+        f = line.strip().strip("`").split()
+        if len(f) == 4 and f[0] == "traffic_bytes_per_launch" and f[1] == spec_name and f[2] == str(tokens):
+            return float(f[3])
+    return None
 
 
 # ------------------------------------------------------------------ CPU reference
-def cpu_reference_tokens_per_s(cfg, steps: int, warmup: int) -> dict:
-    """Times the reference's own CPU implementation (oracle/_ref) of the step on a bounded sample:
-    full layer widths and vocabulary, 1 x 128 tokens, 1-layer and 2-layer stacks; the per-layer time
-    is their difference and the full-depth step time is extrapolated linearly in the layer count."""
+CPU_SAMPLE_TOKENS = 640          # longer than the 512-token sliding window, so the window is active in the sample
+
+
+def cpu_reference_sample(cfg, steps: int, warmup: int, with_depth_estimate: bool = False) -> dict:
+    """Times the reference's own CPU implementation (oracle/_ref) of the step on a bounded sample of the workload:
+    the model's full layer widths and full vocabulary on a 2-layer stack (for Gemma one sliding and one global
+    layer), batch 1 x min(seq, 640) tokens.  `value` is what was measured: the sample's tokens divided by the median
+    wall time of the timed steps (the first step, which page-faults the reference's pools in, is never timed).
+    Nothing is extrapolated into `value`; with_depth_estimate adds a separately labelled full-depth estimate from a
+    second, 1-layer run."""
     from mobilefinetuner_b200 import configs as Cf, synth
     from oracle import model_case, refrun
     binary = refrun.driver()
@@ -100,24 +117,34 @@ def cpu_reference_tokens_per_s(cfg, steps: int, warmup: int) -> dict:
         return {"value": None, "unit": "tokens/s", "cores": 0, "kind": "reference", "sample": "oracle/_ref not built"}
     spec = cfg.spec
     cores = os.cpu_count() or 1
-    seq = min(128, cfg.seq)
-    per_step = {}
-    for nl in (1, 2):
+    seq = min(CPU_SAMPLE_TOKENS, cfg.seq)
+    warmup = max(1, warmup)
+
+    def run(nl, n_steps):
         s = Cf.reduced(spec, layers=nl, global_every=2 if spec.family == Cf.GEMMA else 0)
-        params = synth.make_params(s, 7)
-        lora = synth.make_lora(s, 8)
-        ids, labels = synth.make_batch(s, 1, seq, 9)
-        r = model_case.run_reference_step(s, params, lora, ids, labels, lr=cfg.lr, max_grad_norm=cfg.max_grad_norm,
-                                          steps=warmup + steps, threads=cores)
+        r = model_case.run_reference_step(s, synth.make_params(s, 7), synth.make_lora(s, 8), *synth.make_batch(s, 1, seq, 9), lr=cfg.lr,
+                                          max_grad_norm=cfg.max_grad_norm, steps=warmup + n_steps, threads=cores)
         totals = [float(line.split(" total ")[1]) for line in r["timing"].strip().splitlines()]
-        per_step[nl] = statistics.median(totals[warmup:]) if len(totals) > warmup else totals[-1]
-    t_layer = max(per_step[2] - per_step[1], 1e-9)
-    t_full = per_step[1] + (spec.layers - 1) * t_layer
-    return {"value": seq / t_full, "unit": "tokens/s", "cores": cores, "kind": "reference",
-            "sample": (f"reference CPU path ({refrun.kind(binary)}: OpenBLAS sgemm on {cores} threads, every other loop single-threaded), "
-                       f"{spec.name} widths and full vocabulary, batch 1 x seq {seq}; measured 1-layer step {per_step[1]:.2f} s and "
-                       f"2-layer step {per_step[2]:.2f} s, extrapolated linearly to {spec.layers} layers = {t_full:.1f} s per step"),
-            "seconds_per_step_extrapolated": t_full}
+        return totals[warmup:]
+
+    layers = min(2, spec.layers)
+    timed = run(layers, steps)
+    t_step = statistics.median(timed)
+    win = f"(the {spec.sliding_window}-token window is active)" if 0 < spec.sliding_window < seq else "(causal attention)"
+    out = {"value": seq / t_step, "unit": "tokens/s", "cores": cores, "kind": "reference",
+           "seconds_per_step": t_step, "steps_timed": len(timed), "sample_tokens": seq, "sample_layers": layers,
+           "sample": (f"reference CPU path ({refrun.kind(binary)}: OpenBLAS sgemm on {cores} threads, every other loop single-threaded) on a "
+                      f"bounded sample: {spec.name} layer widths and full vocabulary, {layers} of {spec.layers} layers, batch 1 x seq {seq} "
+                      f"{win}; {len(timed)} timed steps after {warmup} untimed, median "
+                      f"{t_step:.2f} s per step; tokens/s is for THIS reduced shape (full size is infeasible on the CPU: memory)")}
+    if with_depth_estimate and spec.layers > layers:
+        t1 = statistics.median(run(1, min(steps, 2)))
+        t_layer = max(t_step - t1, 1e-9)
+        t_full = t1 + (spec.layers - 1) * t_layer
+        out["full_depth_estimate"] = {"seconds_per_step": t_full, "tokens_per_s": seq / t_full,
+                                      "how": f"1-layer step {t1:.2f} s, per-layer difference {t_layer:.2f} s, linear in the layer count "
+                                             f"to {spec.layers} layers; an estimate, not a measurement"}
+    return out
 
 
 # ------------------------------------------------------------------ our arm
@@ -254,7 +281,7 @@ def run_ours(args):
                     "peak": peak, "peak_source": which, "unit": "TFLOP/s", "frac": achieved / peak,
                     # DRAM bytes of the largest launch (gate|up projection), from the ncu capture summarised in
                     # profiles/gemm_nt_kernels_gemma3_1b_gate_up.md, scaled from M = 4096 to this M
-                    "traffic": GATE_UP_TRAFFIC_BYTES if (spec.name == "gemma-3-1b" and B * S == 16384) else None,
+                    "traffic": profiled_traffic_bytes(spec.name, B * S),
                     "launches_per_step": n.value, "gemm_ms_per_step": tms.value,
                     "step_algorithmic_tflop": step_flops / 1e12,
                     "step_achieved_tflops": step_flops / (ms / args.steps * 1e-3) / 1e12,
@@ -273,7 +300,7 @@ def run_ours(args):
                "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
                "final_loss": losses[-1] if losses else None}
         if not args.no_cpu_baseline and world.size == 1:
-            out["cpu_baseline"] = cpu_reference_tokens_per_s(cfg, steps=2, warmup=1)
+            out["cpu_baseline"] = cpu_reference_sample(cfg, steps=2, warmup=1)
     eng.close()
     world.close()
     if out is not None:
@@ -288,23 +315,73 @@ def run_reference(args):
     cfg = Cf.CONFIGS[args.config]
     spec = cfg.spec
     t0 = time.time()
-    base = cpu_reference_tokens_per_s(cfg, steps=max(1, args.steps), warmup=max(0, min(args.warmup, 1)))
+    base = cpu_reference_sample(cfg, steps=max(1, args.steps), warmup=max(1, min(args.warmup, 2)), with_depth_estimate=True)
     if base["value"] is None:
         print(json.dumps({"impl": "reference", "unavailable": base["sample"]}), flush=True)
         return
+    # value / ms_per_step are the MEASURED figures of the bounded sample; the full-depth estimate sits in its own field
     out = {"impl": "reference", "metric": "LoRA fine-tune train tokens/sec (fwd+bwd+AdamW)", "value": base["value"], "unit": "tokens/s",
-           "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["seconds_per_step_extrapolated"] * 1e3,
+           "n_gpus": args.gpus, "steps": base["steps_timed"], "warmup": args.warmup, "ms_per_step": base["seconds_per_step"] * 1e3,
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": f"{spec.name} LoRA step on the host CPU (reference implementation), bounded sample", "name": cfg.name},
+           "config": {"workload": f"{spec.name} LoRA step on the host CPU (reference implementation), bounded sample: "
+                                  f"{base['sample_layers']} layers, batch 1 x seq {base['sample_tokens']}, full widths and vocabulary",
+                      "name": cfg.name},
            "cpu_baseline": base,
            "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0, "wall_s": time.time() - t0}
     print(json.dumps(out), flush=True)
 
 
+# ------------------------------------------------------------------ operator-level attention sweep
+def run_attention_sweep(args):
+    """--config attn_sweep: causal GQA attention forward + backward (batch 8, 14 query heads on 2 KV heads, head_dim 64,
+    N(0,1) inputs) over S = 256 ... 4096.  Algorithmic FLOPs: 4 * head_dim per visible (query, key) pair forward, 8 backward."""
+    import torch
+    from mobilefinetuner_b200 import ops as O
+    B, nh, nkv, hd = 8, 14, 2, 64
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["bf16_tflops"]) if peaks_path.exists() else 1590.0
+    rows = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    for S in (256, 512, 1024, 2048, 4096):
+        g = torch.Generator(device="cuda").manual_seed(4000 + S)
+        mk = lambda h: torch.randn(B, S, h, hd, device="cuda", generator=g).bfloat16().permute(0, 2, 1, 3)
+        q, k, v, d_o = mk(nh), mk(nkv), mk(nkv), mk(nh)
+        o, lse = O.attention_fwd(q, k, v, 0.125, 0)
+        flush = torch.empty(64 << 20, dtype=torch.float32, device="cuda")     # 256 MiB > L2: written between timed launches
+
+        def timed(fn):
+            ms = []
+            for i in range(args.warmup + args.steps):
+                flush.fill_(float(i))
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record()
+                torch.cuda.synchronize()
+                if i >= args.warmup:
+                    ms.append(e0.elapsed_time(e1))
+            return statistics.median(ms)
+        t_f = timed(lambda: O.attention_fwd(q, k, v, 0.125, 0))
+        t_b = timed(lambda: O.attention_bwd(q, k, v, o, d_o, lse, 0.125, 0))
+        pairs = B * nh * S * (S + 1) / 2
+        rows.append({"seq": S, "fwd_ms": t_f, "bwd_ms": t_b, "fwd_tflops": 4 * hd * pairs / t_f / 1e9, "bwd_tflops": 8 * hd * pairs / t_b / 1e9,
+                     "fwd_bwd_tflops": 12 * hd * pairs / (t_f + t_b) / 1e9})
+    clocks = sampler.stop()
+    best = max(rows, key=lambda r: r["fwd_bwd_tflops"])
+    print(json.dumps({"metric": "causal GQA attention forward + backward, algorithmic TFLOP/s", "value": best["fwd_bwd_tflops"], "unit": "TFLOP/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "batch 8, 14 query heads / 2 KV heads, head_dim 64, causal, S in 256..4096", "name": "attn_sweep",
+                                 "l2": "a 256 MiB buffer is written between timed launches"},
+                      "per_seq": rows, "clocks": clocks,
+                      "roofline": {"bound": "tensor", "achieved": best["fwd_bwd_tflops"], "peak": peak, "unit": "TFLOP/s",
+                                   "frac": best["fwd_bwd_tflops"] / peak, "peak_source": "measured burst cuBLAS bf16 (a kernel timed alone)"}}), flush=True)
+
+
 if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.config == "attn_sweep":
+        run_attention_sweep(a)
     else:
         run_ours(a)

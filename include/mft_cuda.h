@@ -263,6 +263,28 @@ int32_t mft_pack_blocks_bf16(const mft_block_copy_t* table_dev, int32_t n_entrie
 /* dst(f32) += src(f32) for every table entry. */
 int32_t mft_accumulate_blocks_f32(const mft_block_copy_t* table_dev, int32_t n_entries, mft_stream_t stream);
 
+/* ---- gated MLP with the gating fused into the GEMM epilogues
+ *      (GemmaModel::apply_mlp gemma_model.cpp:538-546: down(mul(gelu(gate(x)), up(x)));
+ *       QwenModel::mlp qwen_model.cpp:320-332: down(swiglu(gate(x), up(x)));
+ *       backward: MulBackward backward_functions.cpp:74-83, GeluBackward :164-186, SwiGLUBackward :277-295) ----
+ * kind = MFT_ACT_GEGLU or MFT_ACT_SWIGLU.  w_nk is the K-major gate|up weight [2*inter, k] (gate rows first), b_nk the
+ * matching LoRA panel [2*inter, 64], xa = scale * x A [m, 64] (k2 used columns; k2 = 0: no LoRA).
+ *   forward : gu[m, 2*inter] = x W (+ bias) + xa B   (kept for the backward pass)  and  act[m, inter] = f(gate) * up
+ *             in ONE launch: a CTA pair owns 128 gate columns and the 128 matching up columns of a tile.
+ *   backward: d_act = dy W_down^T + a2 b2^T is formed tile by tile in tensor memory and never stored; the epilogue loads
+ *             the saved gate|up tile and writes dgu[m, 2*inter] = (d_gate | d_up) directly.  w_kn = K-major [inter, k].
+ * Both return MFT_ERR_UNSUPPORTED (without an error message) when the shape does not qualify (m < 256, inter not a
+ * multiple of 128 / 64, unaligned operands): the caller then runs mft_gemm_nt followed by mft_act_fwd / mft_act_bwd,
+ * whose results these calls reproduce bit for bit. */
+int32_t mft_glu_linear_fwd(int32_t kind, const void* x_bf16, int64_t ldx, const void* w_nk_bf16, int64_t ldw, int64_t m,
+                           int64_t inter, int64_t k, const void* xa_bf16, int64_t ldxa, const void* b_nk_bf16, int64_t ldb2,
+                           int64_t k2, const float* bias, void* gu_bf16, int64_t ld_gu, void* act_bf16, int64_t ld_act,
+                           mft_stream_t stream);
+int32_t mft_glu_linear_bwd(int32_t kind, const void* dy_bf16, int64_t lddy, const void* w_kn_bf16, int64_t ldw, int64_t m,
+                           int64_t inter, int64_t k, const void* a2_bf16, int64_t lda2, const void* b2_bf16, int64_t ldb2,
+                           int64_t k2, const void* gu_bf16, int64_t ld_gu, void* dgu_bf16, int64_t ld_dgu,
+                           mft_stream_t stream);
+
 /* ---- attention: the chain repeat_kv_heads -> transpose -> matmul ->
  *      mul(scale) -> add(mask) -> softmax -> matmul of the model graphs
  *      (qwen_model.cpp:311-318, gemma_model.cpp:487-505, gpt2_model.cpp:630-657;

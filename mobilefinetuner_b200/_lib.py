@@ -13,6 +13,7 @@ _LIB_PATH = Path(__file__).resolve().parent / "libmft_cuda.so"
 
 MFT_F32, MFT_BF16, MFT_I32 = 0, 1, 2
 ACT_GELU, ACT_SWIGLU, ACT_GEGLU = 0, 1, 2
+MFT_ERR_UNSUPPORTED = -7
 
 
 class MftError(RuntimeError):
@@ -108,6 +109,8 @@ _SIGS = {
     "mft_repeat_kv": [vp, i32, vp, i64, i64, i64, i64, i64, vp],
     "mft_repeat_kv_bwd": [vp, vp, i64, i64, i64, i64, i64, vp],
     "mft_gemm_nt": [vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, f32, vp, i64, i32, i32, vp],
+    "mft_glu_linear_fwd": [i32, vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, vp, i64, vp, i64, vp],
+    "mft_glu_linear_bwd": [i32, vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, i64, vp, i64, vp],
     "mft_profile_gemm": [i32],
     "mft_profile_gemm_report": [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(i64)],
     "mft_gemm_tn_acc": [vp, i64, vp, i64, i64, i64, i64, f32, vp, i64, vp],

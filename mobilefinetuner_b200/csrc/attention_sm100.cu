@@ -1,4 +1,5 @@
-// Causal / sliding-window GQA attention on the 5th-generation tensor cores (tcgen05) for head_dim 256.
+// Causal / sliding-window GQA attention on the 5th-generation tensor cores (tcgen05) for head_dim 64, 128 and 256
+// (the kernels are templates over the head size; the comments quote the sizes of head_dim 256).
 //
 // Forward: one CTA per (128 queries, head, batch).  Scores and the output accumulator live in tensor memory:
 //     S = Q K^T      128 x 64 per key tile, two buffers (128 columns)
@@ -30,16 +31,23 @@ using namespace ptx;
 namespace {
 
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr int HD = 256, BM = 128, BN = 64;
+constexpr int BM = 128, BN = 64;
 constexpr int THREADS = 352;   // TMA warp, S-issuing warp, 8 softmax warps, P V-issuing warp
-constexpr int Q_BYTES = BM * HD * 2;           // 4 boxes of [128 rows x 64 columns]
-constexpr int KV_BYTES = BN * HD * 2;          // 4 boxes of [64 rows x 64 columns]
-constexpr int P_BYTES = BM * BN * 2;           // [128 rows x 64 keys], 128-byte rows
 constexpr int FWD_VST = 3;                     // V stages (a V tile is held until its P V product is done; K only for S)
-constexpr int FWD_SMEM = Q_BYTES + (2 + FWD_VST) * KV_BYTES + 192 + 2 * 2 * BM * 4;   // 231,616 of 232,448 bytes
-constexpr int S_COL = 0, O_COL = 128;          // tensor-memory columns: S buffers at 0 / 64, O at 128..383
-constexpr int P_COL = 384;                     // bf16 probabilities as the A operand of P V: 32 columns (64 keys) per buffer
 constexpr float RESCALE_GAP = 8.0f;            // log2 units
+// Sizes that depend on the head size.  Rows of Q / K / V tiles are cut into CH boxes of 64 columns (128-byte rows).
+template <int HD>
+struct Dim {
+    static_assert(HD == 64 || HD == 128 || HD == 256, "head_dim");
+    static constexpr int CH = HD / 64;
+    static constexpr int Q_BYTES = BM * HD * 2;            // CH boxes of [128 rows x 64 columns]
+    static constexpr int KV_BYTES = BN * HD * 2;           // CH boxes of [64 rows x 64 columns]
+    static constexpr int FWD_SMEM = Q_BYTES + (2 + FWD_VST) * KV_BYTES + 192 + 2 * 2 * BM * 4;   // head_dim 256: 231,616 of 232,448 bytes
+    // forward tensor-memory columns: S buffers at 0 / 64, O at 128 .. 128 + HD, then the bf16 probabilities (the A operand
+    // of P V: 32 columns = 64 keys per buffer)
+    static constexpr int S_COL = 0, O_COL = 128, P_COL = 128 + HD;
+    static constexpr int FWD_TMEM = HD == 64 ? 256 : 512;  // allocation (a power of two >= P_COL + 64)
+};
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -109,12 +117,15 @@ __device__ __forceinline__ float ex2(float x) {
 }
 __device__ __forceinline__ bool visible(int i, int j, int window) { return j <= i && (window <= 0 || i - j < window); }
 
+template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
     dep_trigger();
     // The swizzled tiles need 1024-byte alignment and the tiles fill the SM's shared memory to within 1 KB, so
     // there is no room for alignment slack: the dynamic segment is declared aligned and checked below.
+    constexpr int CH = Dim<HD>::CH, Q_BYTES = Dim<HD>::Q_BYTES, KV_BYTES = Dim<HD>::KV_BYTES;
+    constexpr int S_COL = Dim<HD>::S_COL, O_COL = Dim<HD>::O_COL, P_COL = Dim<HD>::P_COL;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* base = smem_raw;
     uint8_t* q_smem = base;
@@ -162,7 +173,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         fence_barrier_init();
         tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, Dim<HD>::FWD_TMEM); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -174,7 +185,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (lane == 0) {
             const int qx = h * p.q_col0_stride, kx = kvh * p.kv_col0_stride;
             mbar_arrive_expect_tx(q_full, Q_BYTES);
-            for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + c * (BM * 128), &map_q, q_full, qx + c * 64, b * p.seq + i0);
+            for (int c = 0; c < CH; ++c) tma_load_2d(q_smem + c * (BM * 128), &map_q, q_full, qx + c * 64, b * p.seq + i0);
             int vs = 0;
             uint32_t vph = 0;                           // V stage of tile t and its phase parity
             for (int t = 0; t < n_tiles; ++t) {
@@ -183,10 +194,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const int row = b * p.seq + (jb_lo + t) * BN;
                 if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) break;
                 mbar_arrive_expect_tx(&k_full[st], KV_BYTES);
-                for (int c = 0; c < 4; ++c) tma_load_2d(k_smem + st * KV_BYTES + c * (BN * 128), &map_k, &k_full[st], kx + c * 64, row);
+                for (int c = 0; c < CH; ++c) tma_load_2d(k_smem + st * KV_BYTES + c * (BN * 128), &map_k, &k_full[st], kx + c * 64, row);
                 if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag)) break;
                 mbar_arrive_expect_tx(&v_full[vs], KV_BYTES);
-                for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + vs * KV_BYTES + c * (BN * 128), &map_v, &v_full[vs], kx + c * 64, row);
+                for (int c = 0; c < CH; ++c) tma_load_2d(v_smem + vs * KV_BYTES + c * (BN * 128), &map_v, &v_full[vs], kx + c * 64, row);
                 if (++vs == FWD_VST) { vs = 0; vph ^= 1; }
             }
         }
@@ -207,7 +218,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const uint64_t kd = smem_desc_sw128(smem_u32(k_smem + st * KV_BYTES));
                 const uint32_t tmem_s = tmem_base + S_COL + st * BN;
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < CH; ++c)
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         umma_bf16(tmem_s, qd + (uint64_t)(c * (BM * 128 / 16) + 2 * j), kd + (uint64_t)(c * (BN * 128 / 16) + 2 * j), idesc_s,
@@ -357,7 +368,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, Dim<HD>::FWD_TMEM);
     }
 }
 
@@ -370,12 +381,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // threads (two threads per query row each) take alternate tiles and overlap each other's latency; group g owns
 // S/dP buffer g and 16 tensor-memory columns for its dS.
 constexpr int DQ_BN = 32;
-constexpr int DQ_KV_BYTES = DQ_BN * HD * 2;        // 4 chunks of [32 rows x 64 columns]
 constexpr int DQ_KST = 4, DQ_VST = 2;              // K / V stages (K is held until the tile's dQ product, V only for dP)
-constexpr int DQ_SMEM = 2 * Q_BYTES + (DQ_KST + DQ_VST) * DQ_KV_BYTES + 256 + 4 * BM * 4;
 constexpr int DQ_THREADS = 64 + 2 * 256 + 64;     // TMA warp, S issuer, 16 element-wise warps, dP issuer, dQ issuer
 constexpr int DQ_S_COL = 0, DQ_DP_COL = 64, DQ_ACC_COL = 128;
-constexpr int DQ_DS_COL = 384;                       // dS as the A operand of the dQ product: 16 columns (32 keys as bf16 pairs) per group
+template <int HD>
+struct DqDim {
+    static constexpr int KV_BYTES = DQ_BN * HD * 2;    // CH chunks of [32 rows x 64 columns]
+    static constexpr int SMEM = 2 * Dim<HD>::Q_BYTES + (DQ_KST + DQ_VST) * KV_BYTES + 256 + 4 * BM * 4;
+    static constexpr int DS_COL = 128 + HD;            // dS as the A operand of the dQ product: 16 columns (32 keys as bf16 pairs) per group
+    static constexpr int TMEM = HD == 64 ? 256 : 512;
+};
 
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -403,10 +418,12 @@ struct BwdParams {
     float* delta_out;
 };
 
+template <int HD>
 __global__ void __launch_bounds__(DQ_THREADS, 1)
 attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                   const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
     dep_trigger();
+    constexpr int CH = Dim<HD>::CH, Q_BYTES = Dim<HD>::Q_BYTES, DQ_KV_BYTES = DqDim<HD>::KV_BYTES, DQ_DS_COL = DqDim<HD>::DS_COL;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* q_smem = smem_raw;
     uint8_t* do_smem = q_smem + Q_BYTES;
@@ -451,7 +468,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         fence_barrier_init();
         tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, DqDim<HD>::TMEM); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -461,18 +478,18 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             mbar_arrive_expect_tx(qdo_full, 2 * Q_BYTES);
-            for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + c * (BM * 128), &map_q, qdo_full, h * p.q_col0_stride + c * 64, b * p.seq + i0);
-            for (int c = 0; c < 4; ++c) tma_load_2d(do_smem + c * (BM * 128), &map_do, qdo_full, h * p.do_col0_stride + c * 64, b * p.seq + i0);
+            for (int c = 0; c < CH; ++c) tma_load_2d(q_smem + c * (BM * 128), &map_q, qdo_full, h * p.q_col0_stride + c * 64, b * p.seq + i0);
+            for (int c = 0; c < CH; ++c) tma_load_2d(do_smem + c * (BM * 128), &map_do, qdo_full, h * p.do_col0_stride + c * 64, b * p.seq + i0);
             for (int t = 0; t < n_tiles; ++t) {
                 const int ks = t % DQ_KST, vs = t & 1;
                 const uint32_t kph = (t / DQ_KST) & 1, vph = (t >> 1) & 1;
                 const int row = b * p.seq + (jb_lo + t) * DQ_BN;
                 if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag)) break;
                 mbar_arrive_expect_tx(&k_full[ks], DQ_KV_BYTES);
-                for (int c = 0; c < 4; ++c) tma_load_2d(k_smem + ks * DQ_KV_BYTES + c * (DQ_BN * 128), &map_k, &k_full[ks], kvh * p.k_col0_stride + c * 64, row);
+                for (int c = 0; c < CH; ++c) tma_load_2d(k_smem + ks * DQ_KV_BYTES + c * (DQ_BN * 128), &map_k, &k_full[ks], kvh * p.k_col0_stride + c * 64, row);
                 if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag)) break;
                 mbar_arrive_expect_tx(&v_full[vs], DQ_KV_BYTES);
-                for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + vs * DQ_KV_BYTES + c * (DQ_BN * 128), &map_v, &v_full[vs], kvh * p.v_col0_stride + c * 64, row);
+                for (int c = 0; c < CH; ++c) tma_load_2d(v_smem + vs * DQ_KV_BYTES + c * (DQ_BN * 128), &map_v, &v_full[vs], kvh * p.v_col0_stride + c * 64, row);
             }
         }
     } else if (warp == 1 || warp == 18) {
@@ -491,7 +508,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const uint64_t bd = smem_desc_sw128(smem_u32(is_s ? k_smem + ks * DQ_KV_BYTES : v_smem + g * DQ_KV_BYTES));
                 const uint32_t tmem_d = tmem_base + (is_s ? DQ_S_COL : DQ_DP_COL) + g * DQ_BN;
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < CH; ++c)
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         umma_bf16(tmem_d, ad + (uint64_t)(c * (BM * 128 / 16) + 2 * j), bd + (uint64_t)(c * (DQ_BN * 128 / 16) + 2 * j), idesc_s,
@@ -530,14 +547,14 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const long long sidx = ((long long)b * p.n_heads + h) * p.seq + i;
         const float neg_lse2 = -p.lse[sidx] * LOG2E;
         float dlt;
-        if (p.o != nullptr) {
+        if (HD == 256 && p.o != nullptr) {
             // delta = rowsum(O * dO): the four element-wise threads of a row (2 groups x 2 halves) take 64 columns
             // each, the partial sums meet in shared memory; thread (group 0, half 0) stores the row's delta for the
             // dK/dV kernel
             {
                 const int part = g * 2 + half;
-                const __nv_bfloat16* orow = p.o + (long long)b * p.so_b + (long long)i * p.so_s + (long long)h * p.so_h + part * (HD / 4);
-                const __nv_bfloat16* drow = p.d_o + (long long)b * p.sdo_b + (long long)i * p.sdo_s + (long long)h * p.sdo_h + part * (HD / 4);
+                const __nv_bfloat16* orow = p.o + (long long)b * p.so_b + (long long)i * p.so_s + (long long)h * p.so_h + part * 64;
+                const __nv_bfloat16* drow = p.d_o + (long long)b * p.sdo_b + (long long)i * p.sdo_s + (long long)h * p.sdo_h + part * 64;
                 float a8[8][8], c8[8][8];
 #pragma unroll
                 for (int d = 0; d < 8; ++d) { load8(orow + d * 8, a8[d]); load8(drow + d * 8, c8[d]); }
@@ -611,7 +628,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, DqDim<HD>::TMEM);
     }
 }
 
@@ -627,13 +644,19 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 // The result is added into the caller's f32 [2][batch, seq, n_kv, 256] scratch (query heads of a KV group and
 // the two halves write disjoint columns or add).
 constexpr int KV_BQ = 32;                              // queries per tile
-constexpr int KV_Q_BYTES = KV_BQ * HD * 2;             // 4 chunks of [32 rows x 64 columns]
 constexpr int KV_STATS_BYTES = 2 * KV_BQ * 4;          // lse, delta of the tile's queries
 constexpr int KV_STAGES = 3;                           // Q / dO stages: the load of tile t+2 must not wait for the MMAs of tile t
-constexpr int DKV_SMEM = 2 * Q_BYTES + KV_STAGES * 2 * KV_Q_BYTES + KV_STAGES * KV_STATS_BYTES + 256;
 constexpr int DKV_THREADS = 64 + 2 * 256 + 64;         // TMA warp, S^T issuer, 16 element-wise warps, dP^T issuer, dV/dK issuer
-constexpr int KV_S_COL = 0, KV_DP_COL = 64, KV_DK_COL = 128, KV_DV_COL = 256;
-constexpr int KV_PDS_COL = 384;                        // per group 32 columns: P^T (16: 32 queries as bf16 pairs) | dS^T (16)
+constexpr int KV_S_COL = 0, KV_DP_COL = 64, KV_DK_COL = 128;
+template <int HD>
+struct KvDim {
+    static constexpr int ACC = HD == 256 ? 128 : HD;   // head_dim columns one CTA accumulates (head_dim 256: two CTAs per head)
+    static constexpr int NPART = HD / ACC;
+    static constexpr int Q_BYTES = KV_BQ * HD * 2;     // CH chunks of [32 rows x 64 columns]
+    static constexpr int SMEM = 2 * Dim<HD>::Q_BYTES + KV_STAGES * 2 * Q_BYTES + KV_STAGES * KV_STATS_BYTES + 256;
+    static constexpr int DV_COL = KV_DK_COL + ACC;
+    static constexpr int PDS_COL = KV_DK_COL + 2 * ACC;   // per group 32 columns: P^T (16: 32 queries as bf16 pairs) | dS^T (16)
+};
 
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -642,10 +665,13 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem, u
                  : "memory");
 }
 
+template <int HD>
 __global__ void __launch_bounds__(DKV_THREADS, 1)
 attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
     dep_trigger();
+    constexpr int CH = Dim<HD>::CH, Q_BYTES = Dim<HD>::Q_BYTES, KV_Q_BYTES = KvDim<HD>::Q_BYTES, ACC = KvDim<HD>::ACC, NPART = KvDim<HD>::NPART;
+    constexpr int KV_DV_COL = KvDim<HD>::DV_COL, KV_PDS_COL = KvDim<HD>::PDS_COL;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* k_smem = smem_raw;                            // [128 keys x 256], 4 chunks
     uint8_t* v_smem = k_smem + Q_BYTES;
@@ -669,7 +695,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int jb = blockIdx.x, b = blockIdx.z;
-    const int h = blockIdx.y >> 1, hh = blockIdx.y & 1;    // query head, half of head_dim
+    const int h = blockIdx.y / NPART, hh = blockIdx.y % NPART;    // query head, part of head_dim
     const int kvh = h / p.rep;
     const int j0 = jb * BM;
     // queries that can see keys j0 .. j0+127: i >= j0 and i - j < window
@@ -698,8 +724,8 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (warp == 0) {
         if (lane == 0) {
             mbar_arrive_expect_tx(kv_full, 2 * Q_BYTES);
-            for (int c = 0; c < 4; ++c) tma_load_2d(k_smem + c * (BM * 128), &map_k, kv_full, kvh * p.k_col0_stride + c * 64, b * p.seq + j0);
-            for (int c = 0; c < 4; ++c) tma_load_2d(v_smem + c * (BM * 128), &map_v, kv_full, kvh * p.v_col0_stride + c * 64, b * p.seq + j0);
+            for (int c = 0; c < CH; ++c) tma_load_2d(k_smem + c * (BM * 128), &map_k, kv_full, kvh * p.k_col0_stride + c * 64, b * p.seq + j0);
+            for (int c = 0; c < CH; ++c) tma_load_2d(v_smem + c * (BM * 128), &map_v, kv_full, kvh * p.v_col0_stride + c * 64, b * p.seq + j0);
             const long long srow = ((long long)b * p.n_heads + h) * p.seq;
             int st = 0;
             uint32_t sph = 0;                           // stage of tile t and its phase parity (t / KV_STAGES) & 1
@@ -707,8 +733,8 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const int i0 = (qs_lo + t) * KV_BQ;
                 if (!mbar_wait(&qdo_empty[st], sph ^ 1, abort_flag)) break;
                 mbar_arrive_expect_tx(&qdo_full[st], 2 * KV_Q_BYTES + KV_STATS_BYTES);
-                for (int c = 0; c < 4; ++c) tma_load_2d(q_smem + st * KV_Q_BYTES + c * (KV_BQ * 128), &map_q, &qdo_full[st], h * p.q_col0_stride + c * 64, b * p.seq + i0);
-                for (int c = 0; c < 4; ++c) tma_load_2d(do_smem + st * KV_Q_BYTES + c * (KV_BQ * 128), &map_do, &qdo_full[st], h * p.do_col0_stride + c * 64, b * p.seq + i0);
+                for (int c = 0; c < CH; ++c) tma_load_2d(q_smem + st * KV_Q_BYTES + c * (KV_BQ * 128), &map_q, &qdo_full[st], h * p.q_col0_stride + c * 64, b * p.seq + i0);
+                for (int c = 0; c < CH; ++c) tma_load_2d(do_smem + st * KV_Q_BYTES + c * (KV_BQ * 128), &map_do, &qdo_full[st], h * p.do_col0_stride + c * 64, b * p.seq + i0);
                 bulk_load_1d(stats + st * 2 * KV_BQ, p.lse + srow + i0, KV_BQ * 4, &qdo_full[st]);
                 bulk_load_1d(stats + st * 2 * KV_BQ + KV_BQ, p.delta + srow + i0, KV_BQ * 4, &qdo_full[st]);
                 if (++st == KV_STAGES) { st = 0; sph ^= 1; }
@@ -731,7 +757,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const uint64_t bd = smem_desc_sw128(smem_u32((is_s ? q_smem : do_smem) + st * KV_Q_BYTES));
                 const uint32_t tmem_d = tmem_base + (is_s ? KV_S_COL : KV_DP_COL) + g * KV_BQ;
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < CH; ++c)
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         umma_bf16(tmem_d, ad + (uint64_t)(c * (BM * 128 / 16) + 2 * j), bd + (uint64_t)(c * (KV_BQ * 128 / 16) + 2 * j), idesc_s,
@@ -743,7 +769,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     } else if (warp == 19) {
         // ------------------------------------------------ MMA issuer 3: dV += P^T dO, dK += dS^T Q (this CTA's 128 columns)
         if (lane == 0) {
-            constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, HD / 2) | IDESC_B_MN;
+            constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, ACC) | IDESC_B_MN;
             bool ok = true;
             int st = 0;
             for (int t = 0; t < n_tiles && ok; ++t) {
@@ -753,8 +779,8 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tc_fence_after();
                 // A operands P^T / dS^T come from tensor memory (8 columns per 16 queries), B operands dO / Q MN-major from the stage
                 const uint32_t pa = tmem_base + KV_PDS_COL + g * 32;
-                const uint64_t dod = smem_desc_mn_sw128(smem_u32(do_smem + st * KV_Q_BYTES + hh * 2 * (KV_BQ * 128)), KV_BQ * 128);
-                const uint64_t qd = smem_desc_mn_sw128(smem_u32(q_smem + st * KV_Q_BYTES + hh * 2 * (KV_BQ * 128)), KV_BQ * 128);
+                const uint64_t dod = smem_desc_mn_sw128(smem_u32(do_smem + st * KV_Q_BYTES + hh * (ACC / 64) * (KV_BQ * 128)), KV_BQ * 128);
+                const uint64_t qd = smem_desc_mn_sw128(smem_u32(q_smem + st * KV_Q_BYTES + hh * (ACC / 64) * (KV_BQ * 128)), KV_BQ * 128);
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
                     umma_bf16_ts(tmem_base + KV_DV_COL, pa + 8 * j, dod + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
@@ -819,18 +845,18 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (g == 0 && ok && mbar_wait(acc_done, 0, abort_flag)) {
             tc_fence_after();
             const long long half_elems = (long long)gridDim.z * p.seq * p.n_kv * HD;
-            float* krow = p.dkv_acc + (((long long)b * p.seq + j) * p.n_kv + kvh) * HD + hh * (HD / 2) + half * (HD / 4);
+            float* krow = p.dkv_acc + (((long long)b * p.seq + j) * p.n_kv + kvh) * HD + hh * ACC + half * (ACC / 2);
             float* vrow = krow + half_elems;
 #pragma unroll 1
-            for (int c = 0; c < HD / 4; c += 32) {
+            for (int c = 0; c < ACC / 2; c += 32) {
                 uint32_t o[32];
-                tmem_ld_32x32(lane_addr + KV_DK_COL + half * (HD / 4) + c, o);
+                tmem_ld_32x32(lane_addr + KV_DK_COL + half * (ACC / 2) + c, o);
                 tmem_ld_wait();
 #pragma unroll
                 for (int x = 0; x < 32; x += 4)
                     atomicAdd(reinterpret_cast<float4*>(krow + c + x), make_float4(__uint_as_float(o[x]) * p.scale, __uint_as_float(o[x + 1]) * p.scale,
                                                                                  __uint_as_float(o[x + 2]) * p.scale, __uint_as_float(o[x + 3]) * p.scale));
-                tmem_ld_32x32(lane_addr + KV_DV_COL + half * (HD / 4) + c, o);
+                tmem_ld_32x32(lane_addr + KV_DV_COL + half * (ACC / 2) + c, o);
                 tmem_ld_wait();
 #pragma unroll
                 for (int x = 0; x < 32; x += 4)
@@ -850,48 +876,86 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 bool token_major(const mft_strides_t& s, int seq) { return s.stride_b == (int64_t)seq * s.stride_s; }
 
+bool tc_shape_ok(int hd) { return hd == 64 || hd == 128 || hd == 256; }
+
+template <int HD>
+int32_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdParams& p, dim3 grid, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dim<HD>::FWD_SMEM), "attention smem attribute")) return s;
+        configured = true;
+    }
+    launch_dep(attn_fwd_tc_kernel<HD>, dim3(grid), dim3(THREADS), (size_t)(Dim<HD>::FWD_SMEM), stream, mq, mk, mv, p);
+    MFT_LAUNCH_CHECK("attn_fwd_tc");
+    return MFT_OK;
+}
+template <int HD>
+int32_t launch_dq(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMap& mk, const CUtensorMap& mv, const BwdParams& p, dim3 grid, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqDim<HD>::SMEM), "attention smem attribute")) return s;
+        configured = true;
+    }
+    launch_dep(attn_dq_tc_kernel<HD>, dim3(grid), dim3(DQ_THREADS), (size_t)(DqDim<HD>::SMEM), stream, mq, md, mk, mv, p);
+    MFT_LAUNCH_CHECK("attn_dq_tc");
+    return MFT_OK;
+}
+template <int HD>
+int32_t launch_dkv(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMap& mk, const CUtensorMap& mv, const BwdParams& p, int seq, int n_heads, int batch,
+                   cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dkv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, KvDim<HD>::SMEM), "attention smem attribute")) return s;
+        configured = true;
+    }
+    dim3 grid((unsigned)(seq / BM), (unsigned)(KvDim<HD>::NPART * n_heads), (unsigned)batch);
+    launch_dep(attn_dkv_tc_kernel<HD>, dim3(grid), dim3(DKV_THREADS), (size_t)(KvDim<HD>::SMEM), stream, mq, md, mk, mv, p);
+    MFT_LAUNCH_CHECK("attn_dkv_tc");
+    return MFT_OK;
+}
+#define HD_DISPATCH(hd, CALL64, CALL128, CALL256) ((hd) == 64 ? (CALL64) : (hd) == 128 ? (CALL128) : (CALL256))
+
 }  // namespace
 
 int32_t attn_fwd_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
     static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
-    if (!enabled || hd != HD || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    if (!enabled || !tc_shape_ok(hd) || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    // measured (batch 8, 14 / 2 heads of 64): at 256 and 512 tokens the mma.sync forward is as fast or faster
+    // (0.022 / 0.042 ms against 0.026 / 0.045 ms), from 1024 tokens on this kernel wins (0.096 against 0.108 ms, 1.6 x at 4096)
+    if (hd != 256 && a.seq < 1024 && enabled < 2) return MFT_ERR_UNSUPPORTED;
     if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq)) return MFT_ERR_UNSUPPORTED;
     if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.so.stride_s % 8 || a.so.stride_h % 8 || a.so.stride_b % 8) return MFT_ERR_UNSUPPORTED;
     if ((int64_t)a.batch * a.seq >= (1ll << 31)) return MFT_ERR_UNSUPPORTED;
     CUtensorMap mq, mk, mv;
     const int64_t rows = (int64_t)a.batch * a.seq;
-    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + HD, a.sq.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
-    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + HD, a.sk.stride_s, BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
-    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + HD, a.sv.stride_s, BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + hd, a.sq.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + hd, a.sk.stride_s, BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + hd, a.sv.stride_s, BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
     if (a.sk.stride_h != a.sv.stride_h) return MFT_ERR_UNSUPPORTED;
     FwdParams p{};
     p.seq = a.seq; p.n_heads = a.n_heads; p.rep = a.rep; p.window = a.window; p.scale = a.scale;
     p.out = a.out; p.so_b = a.so.stride_b; p.so_s = a.so.stride_s; p.so_h = a.so.stride_h; p.lse = a.lse;
     p.status = device_status_word();
     p.q_col0_stride = (int)a.sq.stride_h; p.kv_col0_stride = (int)a.sk.stride_h;
-    static bool configured = false;
-    if (!configured) {
-        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM), "attention smem attribute")) return s;
-        configured = true;
-    }
     dim3 grid((unsigned)(a.seq / BM), (unsigned)a.n_heads, (unsigned)a.batch);
-    launch_dep(attn_fwd_tc_kernel, dim3(grid), dim3(THREADS), (size_t)(FWD_SMEM), stream, mq, mk, mv, p);
-    MFT_LAUNCH_CHECK("attn_fwd_tc");
-    return MFT_OK;
+    return HD_DISPATCH(hd, launch_fwd<64>(mq, mk, mv, p, grid, stream), launch_fwd<128>(mq, mk, mv, p, grid, stream), launch_fwd<256>(mq, mk, mv, p, grid, stream));
 }
 
 int32_t attn_dq_sm100(const AttnParams& a, int hd, bool compute_delta, cudaStream_t stream) {
     static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
-    if (!enabled || hd != HD || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    if (!enabled || !tc_shape_ok(hd) || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    // the backward kernels win from 512 tokens on (0.129 against 0.164 ms at 512, 2 x at 4096); MFT_ATTN_TC=2 forces them
+    if (hd != 256 && a.seq < 512 && enabled < 2) return MFT_ERR_UNSUPPORTED;
+    if (compute_delta && hd != 256) return MFT_ERR_UNSUPPORTED;
     if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq) || !token_major(a.sdo, a.seq)) return MFT_ERR_UNSUPPORTED;
     if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.sdo.stride_h % 8) return MFT_ERR_UNSUPPORTED;
     if ((int64_t)a.batch * a.seq >= (1ll << 31)) return MFT_ERR_UNSUPPORTED;
     CUtensorMap mq, md, mk, mv;
     const int64_t rows = (int64_t)a.batch * a.seq;
-    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + HD, a.sq.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
-    if (make_tmap_bf16(&md, a.d_o, rows, (int64_t)(a.n_heads - 1) * a.sdo.stride_h + HD, a.sdo.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
-    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + HD, a.sk.stride_s, DQ_BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
-    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + HD, a.sv.stride_s, DQ_BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + hd, a.sq.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&md, a.d_o, rows, (int64_t)(a.n_heads - 1) * a.sdo.stride_h + hd, a.sdo.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + hd, a.sk.stride_s, DQ_BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + hd, a.sv.stride_s, DQ_BN) != MFT_OK) return MFT_ERR_UNSUPPORTED;
     BwdParams p{};
     p.seq = a.seq; p.n_heads = a.n_heads; p.n_kv = a.n_kv; p.rep = a.rep; p.window = a.window; p.scale = a.scale;
     p.lse = a.lse; p.delta = a.delta; p.dq = a.dq; p.sq_b = a.sq.stride_b; p.sq_s = a.sq.stride_s; p.sq_h = a.sq.stride_h;
@@ -904,45 +968,33 @@ int32_t attn_dq_sm100(const AttnParams& a, int hd, bool compute_delta, cudaStrea
         p.so_b = a.so.stride_b; p.so_s = a.so.stride_s; p.so_h = a.so.stride_h;
         p.sdo_b = a.sdo.stride_b; p.sdo_s = a.sdo.stride_s; p.sdo_h = a.sdo.stride_h;
     }
-    static bool configured = false;
-    if (!configured) {
-        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM), "attention smem attribute")) return s;
-        configured = true;
-    }
     dim3 grid((unsigned)(a.seq / BM), (unsigned)a.n_heads, (unsigned)a.batch);
-    launch_dep(attn_dq_tc_kernel, dim3(grid), dim3(DQ_THREADS), (size_t)(DQ_SMEM), stream, mq, md, mk, mv, p);
-    MFT_LAUNCH_CHECK("attn_dq_tc");
-    return MFT_OK;
+    return HD_DISPATCH(hd, launch_dq<64>(mq, md, mk, mv, p, grid, stream), launch_dq<128>(mq, md, mk, mv, p, grid, stream), launch_dq<256>(mq, md, mk, mv, p, grid, stream));
 }
 
 int32_t attn_dkv_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
     static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
-    if (!enabled || hd != HD || a.seq % BM != 0 || !a.dkv_acc || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    if (!enabled || !tc_shape_ok(hd) || a.seq % BM != 0 || !a.dkv_acc || !device_status_word()) return MFT_ERR_UNSUPPORTED;
+    // the backward kernels win from 512 tokens on (0.129 against 0.164 ms at 512, 2 x at 4096); MFT_ATTN_TC=2 forces them
+    if (hd != 256 && a.seq < 512 && enabled < 2) return MFT_ERR_UNSUPPORTED;
     if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq) || !token_major(a.sdo, a.seq)) return MFT_ERR_UNSUPPORTED;
     if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.sdo.stride_h % 8) return MFT_ERR_UNSUPPORTED;
     if ((int64_t)a.batch * a.seq >= (1ll << 31) || 2 * a.n_heads > 65535) return MFT_ERR_UNSUPPORTED;
     if (reinterpret_cast<uintptr_t>(a.lse) % 16 || reinterpret_cast<uintptr_t>(a.delta) % 16 || reinterpret_cast<uintptr_t>(a.dkv_acc) % 16) return MFT_ERR_UNSUPPORTED;
     CUtensorMap mq, md, mk, mv;
     const int64_t rows = (int64_t)a.batch * a.seq;
-    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + HD, a.sq.stride_s, KV_BQ) != MFT_OK) return MFT_ERR_UNSUPPORTED;
-    if (make_tmap_bf16(&md, a.d_o, rows, (int64_t)(a.n_heads - 1) * a.sdo.stride_h + HD, a.sdo.stride_s, KV_BQ) != MFT_OK) return MFT_ERR_UNSUPPORTED;
-    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + HD, a.sk.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
-    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + HD, a.sv.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mq, a.q, rows, (int64_t)(a.n_heads - 1) * a.sq.stride_h + hd, a.sq.stride_s, KV_BQ) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&md, a.d_o, rows, (int64_t)(a.n_heads - 1) * a.sdo.stride_h + hd, a.sdo.stride_s, KV_BQ) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mk, a.k, rows, (int64_t)(a.n_kv - 1) * a.sk.stride_h + hd, a.sk.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
+    if (make_tmap_bf16(&mv, a.v, rows, (int64_t)(a.n_kv - 1) * a.sv.stride_h + hd, a.sv.stride_s, BM) != MFT_OK) return MFT_ERR_UNSUPPORTED;
     BwdParams p{};
     p.seq = a.seq; p.n_heads = a.n_heads; p.n_kv = a.n_kv; p.rep = a.rep; p.window = a.window; p.scale = a.scale;
     p.lse = a.lse; p.delta = a.delta; p.dq = a.dq; p.sq_b = a.sq.stride_b; p.sq_s = a.sq.stride_s; p.sq_h = a.sq.stride_h;
     p.dkv_acc = a.dkv_acc; p.status = device_status_word();
     p.q_col0_stride = (int)a.sq.stride_h; p.do_col0_stride = (int)a.sdo.stride_h;
     p.k_col0_stride = (int)a.sk.stride_h; p.v_col0_stride = (int)a.sv.stride_h;
-    static bool configured = false;
-    if (!configured) {
-        if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM), "attention smem attribute")) return s;
-        configured = true;
-    }
-    dim3 grid((unsigned)(a.seq / BM), (unsigned)(2 * a.n_heads), (unsigned)a.batch);
-    launch_dep(attn_dkv_tc_kernel, dim3(grid), dim3(DKV_THREADS), (size_t)(DKV_SMEM), stream, mq, md, mk, mv, p);
-    MFT_LAUNCH_CHECK("attn_dkv_tc");
-    return MFT_OK;
+    return HD_DISPATCH(hd, launch_dkv<64>(mq, md, mk, mv, p, a.seq, a.n_heads, a.batch, stream), launch_dkv<128>(mq, md, mk, mv, p, a.seq, a.n_heads, a.batch, stream),
+                       launch_dkv<256>(mq, md, mk, mv, p, a.seq, a.n_heads, a.batch, stream));
 }
 
 }  // namespace mft

@@ -2,6 +2,7 @@
 // activations (GELU, SwiGLU, GeGLU) forward and backward, residual adds,
 // repeat_kv, the table-driven LoRA panel pack/unpack and the Adam update.
 // All of them are HBM-bound: 128-bit accesses, grid-stride loops, no reuse.
+#include "act_math.cuh"
 #include "common.cuh"
 
 namespace mft {
@@ -102,25 +103,6 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const __nv_bfl
 }
 
 // ---------------------------------------------------------------- activations
-// bf16 in / bf16 out: the hardware tanh approximation (relative error ~2^-11) is below the output rounding
-// (2^-9), and keeps these kernels at memory speed; the f32 operators use the exact tanhf.
-__device__ __forceinline__ float tanh_fast(float x) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-// value and derivative of the tanh-form GELU from one tanh
-__device__ __forceinline__ void gelu_tanh_both(float x, float& val, float& grad) {
-    const float x2 = x * x;
-    const float t = tanh_fast(0.7978845608f * (x + 0.044715f * x * x2));
-    const float dt = 0.7978845608f * (1.0f + 3.0f * 0.044715f * x2);
-    val = 0.5f * x * (1.0f + t);
-    grad = 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * dt;
-}
-__device__ __forceinline__ float gelu_tanh_fast(float x) {
-    return 0.5f * x * (1.0f + tanh_fast(0.7978845608f * (x + 0.044715f * x * x * x)));
-}
-
 template <int KIND>
 __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
                                int64_t ld, __nv_bfloat16* __restrict__ y, int64_t rows, int64_t cols) {

@@ -369,6 +369,7 @@ extern "C" int32_t mft_model_create(const mft_model_config_t* cfg, mft_stream_t 
     m->ce_ws_bytes = mft_lmhead_ce_workspace_bytes(T, H, V);
     if (const char* e = std::getenv("MFT_CE_ONEPASS")) m->ce_onepass = std::atoi(e) != 0;
     if (const char* e = std::getenv("MFT_STEP_GRAPH")) m->use_graph = std::atoi(e) != 0;
+    if (const char* e = std::getenv("MFT_FUSE_GLU")) { m->fuse_glu = std::atoi(e) != 0; m->fuse_glu_fwd = std::atoi(e) >= 2; }
     if (const char* e = std::getenv("MFT_FUSE_NORMS")) m->fuse_norms = std::atoi(e) != 0;
     { uint8_t* ws = nullptr; G(dalloc(m, &ws, m->ce_ws_bytes, false, true)); m->ce_ws = ws; }
     m->stage_floats = 32ll << 20;

@@ -36,12 +36,50 @@ int32_t group_fwd(const Ctx& c, LinearGroup& g, const bf16* x, bf16* xa, bf16* y
     return mft_gemm_nt(x, g.in, g.w_nk, g.in, c.T, g.n_total, g.in, nullptr, 0, nullptr, 0, 0, g.bias, 1.0f, y, g.n_total, MFT_BF16, 0, c.st);
 }
 
+// Gated MLP, forward: gate|up projection with f(gate) * up formed in the GEMM's epilogue; falls back to the GEMM
+// followed by the activation kernel when the shape does not qualify.
+int32_t glu_fwd(const Ctx& c, LinearGroup& g, int kind, int I, const bf16* x, bf16* xa, bf16* gu, bf16* act) {
+    if (c.m->fuse_glu_fwd) {
+        const bool lora = g.any_lora && !c.m->merged;
+        if (lora) TRY(mft_gemm_nt(x, g.in, g.a_nk, g.in, c.T, 64, g.in, nullptr, 0, nullptr, 0, 0, nullptr, c.lora_scale, xa, 64, MFT_BF16, 0, c.st));
+        const int32_t s = mft_glu_linear_fwd(kind, x, g.in, g.w_nk, g.in, c.T, I, g.in, lora ? xa : nullptr, 64, lora ? g.b_nk : nullptr, 64, lora ? g.k2 : 0,
+                                             g.bias, gu, 2 * I, act, I, c.st);
+        if (s != MFT_ERR_UNSUPPORTED) return s;
+    }
+    TRY(group_fwd(c, g, x, xa, gu));
+    return mft_act_fwd(kind, gu, gu + I, 2 * I, act, c.T, I, c.st);
+}
+
+// What the backward of a gated MLP hands to group_bwd of the down projection: instead of d(act) the GEMM's epilogue
+// writes d_gate|d_up from the saved gate|up.
+struct GluBwd {
+    int kind, inter;
+    const bf16* gu;      // saved gate|up [T, 2*inter]
+    bf16* dgu;           // out: d_gate|d_up [T, 2*inter]
+    bf16* d_act;         // scratch [T, inter] for the unfused fallback
+};
+
 // dx = dy W^T + scale (dy B^T) A^T ; dA-panel += x^T (scale dy B^T) ; dB-panel += (scale x A)^T dy.
-int32_t group_bwd(const Ctx& c, LinearGroup& g, const bf16* dy, const bf16* x, const bf16* xa, bf16* dx, bool lora_grads) {
+int32_t group_bwd(const Ctx& c, LinearGroup& g, const bf16* dy, const bf16* x, const bf16* xa, bf16* dx, bool lora_grads, const GluBwd* glu = nullptr) {
+    // dx of a gated MLP's down projection: fused with the gating's backward when possible
+    auto dx_gemm = [&](const bf16* gb) -> int32_t {
+        if (glu) {
+            if (c.m->fuse_glu) {
+                const int32_t s = mft_glu_linear_bwd(glu->kind, dy, g.n_total, g.w_kn, g.n_total, c.T, glu->inter, g.n_total, gb, 64, gb ? g.a_kn : nullptr, 64,
+                                                     gb ? g.k2 : 0, glu->gu, 2 * glu->inter, glu->dgu, 2 * glu->inter, c.st);
+                if (s != MFT_ERR_UNSUPPORTED) return s;
+            }
+            TRY(mft_gemm_nt(dy, g.n_total, g.w_kn, g.n_total, c.T, g.in, g.n_total, gb, 64, gb ? g.a_kn : nullptr, 64, gb ? g.k2 : 0, nullptr, 1.0f, glu->d_act,
+                            g.in, MFT_BF16, 0, c.st));
+            return mft_act_bwd(glu->kind, glu->d_act, glu->gu, glu->gu + glu->inter, 2 * glu->inter, glu->dgu, glu->dgu + glu->inter, c.T, glu->inter, c.st);
+        }
+        return mft_gemm_nt(dy, g.n_total, g.w_kn, g.n_total, c.T, g.in, g.n_total, gb, 64, gb ? g.a_kn : nullptr, 64, gb ? g.k2 : 0, nullptr, 1.0f, dx, g.in,
+                           MFT_BF16, 0, c.st);
+    };
     if (g.any_lora) {
         bf16* gb = c.m->t_pan;
         TRY(mft_gemm_nt(dy, g.n_total, g.b_kn, g.n_total, c.T, 64, g.n_total, nullptr, 0, nullptr, 0, 0, nullptr, c.lora_scale, gb, 64, MFT_BF16, 0, c.st));
-        if (dx) TRY(mft_gemm_nt(dy, g.n_total, g.w_kn, g.n_total, c.T, g.in, g.n_total, gb, 64, g.a_kn, 64, g.k2, nullptr, 1.0f, dx, g.in, MFT_BF16, 0, c.st));
+        if (dx || glu) TRY(dx_gemm(gb));
         if (lora_grads) {
             // only the rank columns in use (rounded up to 16) of the 64-wide panels take part
             const int rq = (g.k2 + 15) / 16 * 16;
@@ -50,7 +88,7 @@ int32_t group_bwd(const Ctx& c, LinearGroup& g, const bf16* dy, const bf16* x, c
         }
         return MFT_OK;
     }
-    if (dx) return mft_gemm_nt(dy, g.n_total, g.w_kn, g.n_total, c.T, g.in, g.n_total, nullptr, 0, nullptr, 0, 0, nullptr, 1.0f, dx, g.in, MFT_BF16, 0, c.st);
+    if (dx || glu) return dx_gemm(nullptr);
     return MFT_OK;
 }
 
@@ -119,9 +157,12 @@ int32_t forward(Ctx& c, bool for_training, int64_t n_valid_global = 0) {
             else TRY(mft_rmsnorm_fwd(b.x_mid, MFT_F32, w.ln2_w, cfg.norm_eps, 0, b.h2, MFT_BF16, b.rstd3, nullptr, nullptr, T, H, c.st));
         }
         // ---- MLP block
-        TRY(group_fwd(c, w.gu, b.h2, b.xa_gu, b.gu));
-        if (gpt2) TRY(mft_act_fwd(MFT_ACT_GELU, b.gu, nullptr, I, b.act, T, I, c.st));
-        else TRY(mft_act_fwd(gemma ? MFT_ACT_GEGLU : MFT_ACT_SWIGLU, b.gu, b.gu + I, 2 * I, b.act, T, I, c.st));
+        if (gpt2) {
+            TRY(group_fwd(c, w.gu, b.h2, b.xa_gu, b.gu));
+            TRY(mft_act_fwd(MFT_ACT_GELU, b.gu, nullptr, I, b.act, T, I, c.st));
+        } else {
+            TRY(glu_fwd(c, w.gu, gemma ? MFT_ACT_GEGLU : MFT_ACT_SWIGLU, I, b.h2, b.xa_gu, b.gu, b.act));
+        }
         TRY(group_fwd(c, w.down, b.act, b.xa_d, b.mlp_out));
         if (fuse) {
             // x_next = x_mid + rms_norm(mlp_out) and the norm that reads x_next: the next layer's input norm, or the final norm
@@ -174,9 +215,13 @@ int32_t backward(Ctx& c, int64_t n_valid_global) {
             TRY(mft_cast_f32_to_bf16(m->dx, m->t_h, T * H, c.st));
         }
         d_mlp_out = m->t_h;
-        TRY(group_bwd(c, w.down, d_mlp_out, b.act, b.xa_d, m->t_i, true));
-        if (gpt2) TRY(mft_act_bwd(MFT_ACT_GELU, m->t_i, b.gu, nullptr, I, m->t_gu, nullptr, T, I, c.st));
-        else TRY(mft_act_bwd(gemma ? MFT_ACT_GEGLU : MFT_ACT_SWIGLU, m->t_i, b.gu, b.gu + I, 2 * I, m->t_gu, m->t_gu + I, T, I, c.st));
+        if (gpt2) {
+            TRY(group_bwd(c, w.down, d_mlp_out, b.act, b.xa_d, m->t_i, true));
+            TRY(mft_act_bwd(MFT_ACT_GELU, m->t_i, b.gu, nullptr, I, m->t_gu, nullptr, T, I, c.st));
+        } else {
+            const GluBwd glu{gemma ? MFT_ACT_GEGLU : MFT_ACT_SWIGLU, I, b.gu, m->t_gu, m->t_i};
+            TRY(group_bwd(c, w.down, d_mlp_out, b.act, b.xa_d, nullptr, true, &glu));
+        }
         TRY(group_bwd(c, w.gu, m->t_gu, b.h2, b.xa_gu, m->t_h, true));
         // through the pre-MLP norm, accumulated onto the residual gradient: dx = d(loss)/d(x_mid)
         if (gpt2) TRY(mft_layernorm_bwd(m->t_h, MFT_BF16, b.x_mid, MFT_F32, w.ln2_w, b.mean3, b.rstd3, m->dx, MFT_F32, 1, nullptr, nullptr, T, H, c.st));

@@ -455,6 +455,7 @@ static int32_t gemm_nt_run_inner(const GemmCall& c, cudaStream_t stream) {
         const int32_t s2 = gemm_nt_run_2cta(c, stream);
         if (s2 != MFT_ERR_UNSUPPORTED) return s2;
     }
+    if (c.epi == EPI_GLU_FWD || c.epi == EPI_GLU_BWD) return MFT_ERR_UNSUPPORTED;     // CTA-pair kernel only: the caller runs the unfused pair
     MFT_CHECK_ARG(c.a && c.b && c.m > 0 && c.n > 0 && c.k > 0, "gemm_nt: bad argument");
     MFT_CHECK_ARG(c.m < (1ll << 31) && c.n < (1ll << 31) && c.k < (1ll << 31), "gemm_nt: dimension too large");
     MFT_CHECK_ARG(c.epi == EPI_CE_STATS || c.d, "gemm_nt: null output");
@@ -530,6 +531,32 @@ extern "C" int32_t mft_profile_gemm_report(double* flops, double* ms, int64_t* l
     }
     *flops = f; *ms = t; *launches = (int64_t)g_prof.size();
     return MFT_OK;
+}
+
+extern "C" int32_t mft_glu_linear_fwd(int32_t kind, const void* x, int64_t ldx, const void* w_nk, int64_t ldw, int64_t m, int64_t inter, int64_t k,
+                                      const void* xa, int64_t ldxa, const void* b_nk, int64_t ldb2, int64_t k2, const float* bias,
+                                      void* gu, int64_t ld_gu, void* act, int64_t ld_act, mft_stream_t stream) {
+    MFT_CHECK_ARG(kind == MFT_ACT_GEGLU || kind == MFT_ACT_SWIGLU, "mft_glu_linear_fwd: kind must be MFT_ACT_GEGLU or MFT_ACT_SWIGLU");
+    MFT_CHECK_ARG(x && w_nk && gu && act && m > 0 && inter > 0 && k > 0 && ld_gu >= 2 * inter && ld_act >= inter, "mft_glu_linear_fwd: bad argument");
+    GemmCall c;
+    c.a = x; c.lda = ldx; c.b = w_nk; c.ldb = ldw; c.m = m; c.n = 2 * inter; c.k = k;
+    c.a2 = xa; c.lda2 = ldxa; c.b2 = b_nk; c.ldb2 = ldb2; c.k2 = k2;
+    c.bias = bias; c.d = gu; c.ldd = ld_gu; c.epi = EPI_GLU_FWD;
+    c.glu_geglu = kind == MFT_ACT_GEGLU; c.glu_inter = inter; c.aux = act; c.ld_aux = ld_act;
+    return gemm_nt_run(c, as_stream(stream));
+}
+
+extern "C" int32_t mft_glu_linear_bwd(int32_t kind, const void* dy, int64_t lddy, const void* w_kn, int64_t ldw, int64_t m, int64_t inter, int64_t k,
+                                      const void* a2, int64_t lda2, const void* b2, int64_t ldb2, int64_t k2,
+                                      const void* gu, int64_t ld_gu, void* dgu, int64_t ld_dgu, mft_stream_t stream) {
+    MFT_CHECK_ARG(kind == MFT_ACT_GEGLU || kind == MFT_ACT_SWIGLU, "mft_glu_linear_bwd: kind must be MFT_ACT_GEGLU or MFT_ACT_SWIGLU");
+    MFT_CHECK_ARG(dy && w_kn && gu && dgu && m > 0 && inter > 0 && k > 0 && ld_gu >= 2 * inter && ld_dgu >= 2 * inter, "mft_glu_linear_bwd: bad argument");
+    GemmCall c;
+    c.a = dy; c.lda = lddy; c.b = w_kn; c.ldb = ldw; c.m = m; c.n = inter; c.k = k;
+    c.a2 = a2; c.lda2 = lda2; c.b2 = b2; c.ldb2 = ldb2; c.k2 = k2;
+    c.d = dgu; c.ldd = ld_dgu; c.epi = EPI_GLU_BWD;
+    c.glu_geglu = kind == MFT_ACT_GEGLU; c.glu_inter = inter; c.aux = const_cast<void*>(gu); c.ld_aux = ld_gu;
+    return gemm_nt_run(c, as_stream(stream));
 }
 
 extern "C" int32_t mft_gemm_nt(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,

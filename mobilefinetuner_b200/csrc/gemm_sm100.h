@@ -10,6 +10,9 @@ constexpr int EPI_STORE = 0;     // D = alpha*acc + bias (+ D)
 constexpr int EPI_CE_STATS = 1;  // per-row (max, sum exp) over each 256-column tile; nothing stored
 constexpr int EPI_CE_GRAD = 2;   // D(bf16) = (exp(acc - lse[row]) - [col == label[row]]) * dloss / n_valid
 constexpr int EPI_CE_P = 3;      // D(bf16) = exp(acc - m_ref[row]); per-row sums of the stored values; label logit; overflow flag
+// Gated MLP fused into the epilogue (CTA-pair kernel only).  The frozen gate|up weight is [2*inter, K]: gate rows first.
+constexpr int EPI_GLU_FWD = 4;   // a pair tile = 128 gate columns + the 128 matching up columns; D gets gate|up, `aux` gets f(gate)*up
+constexpr int EPI_GLU_BWD = 5;   // acc = d(act) tile of [M, inter]; reads gate|up from `aux`, D gets d_gate|d_up; d(act) is not stored
 constexpr int CE_TILE_N = 256;   // column tile of the CE epilogues (fixes the layout of the partials)
 
 struct GemmCall {
@@ -36,6 +39,10 @@ struct GemmCall {
     int ce_partial_ld = 0;
     float* ce_tgt_logit = nullptr;
     int32_t* ce_flag = nullptr;
+    // EPI_GLU_*: glu_geglu != 0 -> gelu(tanh) gating, else silu; inter = width of one half; aux = act out (FWD) / saved gate|up (BWD)
+    int glu_geglu = 0;
+    int64_t glu_inter = 0;
+    void* aux = nullptr; int64_t ld_aux = 0;
 };
 
 // Kernel-side parameter block (by value in the launch).
@@ -63,6 +70,7 @@ struct GemmParams {
     int ce_partial_ld;
     float* ce_tgt_logit;          // [m] logit of the label column (STATS / P modes)
     int32_t* ce_flag;             // [m] set to 1 for a row whose exp(acc - m_ref) leaves the trusted range (P mode)
+    int glu_geglu, glu_inter;     // EPI_GLU_*
 };
 
 // Tile order: groups of RASTER_GROUP column tiles, row tiles within a group, columns fastest.  CTAs that run at

@@ -31,12 +31,15 @@ constexpr int STORE_BYTES = 4 * 2 * EPI_BOX_BYTES;
 // BN2 = columns of the pair's tile.  256 is the only width in use: 192 measured 17 % slower per column and 128
 // 40 % slower (their operand loads per MMA cycle outrun what the L2 delivers), which costs more than the tile
 // quantisation they would save.  Each CTA stages A (16 KB) and BN2/2 rows of B per k-block.
-template <int BN2>
+// The gated-MLP backward epilogue keeps GLU_SETS sets of (gate, up) boxes per warp (loaded by TMA, rewritten in place,
+// stored by TMA): twice the box memory of the other epilogues, paid for with one pipeline stage.
+template <int EPI, int BN2>
 struct PairCfg {
     static constexpr int BH_BYTES = (BN2 / 2) * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + BH_BYTES;                  // 32 / 28 KB, multiples of 1024
-    static constexpr int STAGES = 6;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 + 256;
+    static constexpr int BOX_BYTES = EPI == EPI_GLU_BWD ? GLU_SETS * STORE_BYTES : STORE_BYTES;
+    static constexpr int STAGES = EPI == EPI_GLU_BWD ? 8 - GLU_SETS - 1 : 6;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BOX_BYTES + 1024 + 256;
 };
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;   // clears the bit that distinguishes the two CTAs of a pair: -> address in the leader
 
@@ -89,18 +92,21 @@ template <int EPI, int BN2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
-                    const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
     dep_trigger();
-    constexpr int STAGES = PairCfg<BN2>::STAGES, STAGE_BYTES = PairCfg<BN2>::STAGE_BYTES;
+    constexpr int STAGES = PairCfg<EPI, BN2>::STAGES, STAGE_BYTES = PairCfg<EPI, BN2>::STAGE_BYTES;
+    constexpr int BOX_BYTES = PairCfg<EPI, BN2>::BOX_BYTES;
+    constexpr bool GLU_FWD = EPI == EPI_GLU_FWD, GLU_BWD = EPI == EPI_GLU_BWD;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* store_smem = tiles + STAGES * STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(store_smem + STORE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(store_smem + BOX_BYTES);
     uint64_t* full_bar = bars;                    // [STAGES]  used in the leader
     uint64_t* empty_bar = bars + STAGES;          // [STAGES]  both CTAs
     uint64_t* tmem_full_bar = bars + 2 * STAGES;  // [2]       both CTAs
     uint64_t* tmem_empty_bar = tmem_full_bar + 2; // [2]       used in the leader
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+    uint64_t* glu_bar = tmem_empty_bar + 2;       // [4 warps][GLU_SETS]  gated-MLP backward: gate / up boxes have landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(glu_bar + 4 * GLU_SETS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -114,9 +120,11 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full_bar[b], 1); mbar_init(&tmem_empty_bar[b], 8); }
+        for (int b = 0; b < 4 * GLU_SETS; ++b) mbar_init(&glu_bar[b], 1);
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_b); tma_prefetch_desc(&map_d);
+        if (GLU_FWD || GLU_BWD) tma_prefetch_desc(&map_x);
     }
     __syncthreads();
     if (warp == 1) { tmem_alloc2(tmem_slot, 512); tmem_relinquish2(); }
@@ -138,7 +146,8 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // pair MMA of width n_eff reads n_eff/2 rows of B from each CTA, so the halves are cut there
                 const int n_base = tile_n(t2, p) * BN2;
                 const int n_eff = min(BN2, (p.n - n_base + 15) & ~15);
-                const int n0 = n_base + (int)rank * (n_eff / 2);
+                // gated-MLP forward: the leader loads 128 gate rows of the weight, the peer the 128 matching up rows
+                const int n0 = GLU_FWD ? tile_n(t2, p) * (BN2 / 2) + (int)rank * p.glu_inter : n_base + (int)rank * (n_eff / 2);
                 const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
@@ -172,7 +181,7 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int split = tile / p.tiles_mn;
                 const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
                 const int n_base = tile_n(tile % p.tiles_mn, p) * BN2;
-                const uint32_t idesc = idesc_bf16_f32(2 * BM, (uint32_t)min(BN2, (p.n - n_base + 15) & ~15));
+                const uint32_t idesc = idesc_bf16_f32(2 * BM, GLU_FWD ? (uint32_t)BN2 : (uint32_t)min(BN2, (p.n - n_base + 15) & ~15));
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
@@ -195,16 +204,30 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int row_in_tile = q * 32 + lane;
         int it = 0, box_ctr = 0;
         bool ok = true;
+        GluBwdState glu_state;
+        if (GLU_BWD) {                                            // gate / up boxes of this warp's first chunk(s)
+            glu_state.ahead_tile = cluster_id;
+            if (lane == 0)
+                for (int i = 0; i < GLU_SETS - 1; ++i) glu_bwd_prefetch(p, &map_x, store_smem, glu_bar, q, (int)rank, num_clusters, num_tiles, glu_state);
+        }
         for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             const int t2 = tile % p.tiles_mn;
             const int m0 = tile_m(t2, p) * 2 * BM + (int)rank * BM;
-            const int n0 = tile_n(t2, p) * BN2;
+            const int n0 = GLU_FWD ? tile_n(t2, p) * (BN2 / 2) : tile_n(t2, p) * BN2;
             if (!mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + row_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN2);
+            if constexpr (GLU_FWD) {
+                epilogue_glu_fwd(p, &map_d, &map_x, store_smem, taddr, q, lane, m0 + q * 32, n0, box_ctr);
+            } else if constexpr (GLU_BWD) {
+                ok = epilogue_glu_bwd(p, &map_d, &map_x, store_smem, glu_bar, abort_flag, taddr, q, lane, (int)rank, m0 + q * 32, n0, num_clusters,
+                                      num_tiles, glu_state);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && ok;
+                if (!ok) break;
+            } else
             if (EPI == EPI_STORE && p.d_is_f32)
                 epilogue_f32_tma<BN2>(p, &map_d, store_smem, taddr, q, lane, m0 + q * 32, n0, p.bias != nullptr && tile < p.tiles_mn, box_ctr);
             else
@@ -229,8 +252,8 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int EPI, int BN2>
 int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2, const CUtensorMap& md,
-               GemmParams p, cudaStream_t stream) {
-    using Cfg = PairCfg<BN2>;
+               const CUtensorMap& mx, GemmParams p, cudaStream_t stream) {
+    using Cfg = PairCfg<EPI, BN2>;
     static bool configured = false;
     if (!configured) {
         if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_2cta_kernel<EPI, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm 2cta smem attr")) return s;
@@ -239,7 +262,7 @@ int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& 
     const int tiles = p.tiles_mn * p.splits;
     int clusters = num_sms() / 2;
     if (tiles < clusters) clusters = tiles;
-    launch_dep(gemm_nt_2cta_kernel<EPI, BN2>, dim3(2 * clusters), dim3(THREADS), (size_t)(Cfg::SMEM_BYTES), stream, ma, mb, ma2, mb2, md, p);
+    launch_dep(gemm_nt_2cta_kernel<EPI, BN2>, dim3(2 * clusters), dim3(THREADS), (size_t)(Cfg::SMEM_BYTES), stream, ma, mb, ma2, mb2, md, mx, p);
     MFT_LAUNCH_CHECK("gemm_nt_2cta");
     return MFT_OK;
 }
@@ -265,17 +288,25 @@ int choose_splits(int64_t m, int64_t n, int64_t kb) {
 
 int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     const bool ce = c.epi == EPI_CE_GRAD || c.epi == EPI_CE_P;
+    const bool glu = c.epi == EPI_GLU_FWD || c.epi == EPI_GLU_BWD;
     const bool bf16_ok = !c.d_is_f32 && !c.accumulate && (c.ldd % 8 == 0);
     const bool f32_ok = c.d_is_f32 && c.epi == EPI_STORE && (c.ldd % 4 == 0);
-    const bool ok = (c.epi == EPI_STORE || ce) && (bf16_ok || f32_ok) && c.d && (reinterpret_cast<uintptr_t>(c.d) % 16 == 0) &&
+    const bool ok = (c.epi == EPI_STORE || ce || glu) && (bf16_ok || f32_ok) && c.d && (reinterpret_cast<uintptr_t>(c.d) % 16 == 0) &&
                     c.m >= 256 && c.n >= 192 && c.splits >= 0 && c.splits <= 64;
     if (!ok) return MFT_ERR_UNSUPPORTED;
+    if (glu) {
+        // forward: n = 2 * inter columns of D, tiles of 128 gate + 128 up columns; backward: n = inter
+        const int64_t inter = c.glu_inter;
+        const bool shape_ok = c.epi == EPI_GLU_FWD ? (c.n == 2 * inter && inter % 128 == 0) : (c.n == inter && inter % 64 == 0);
+        if (!shape_ok || !c.aux || c.ld_aux % 8 != 0 || reinterpret_cast<uintptr_t>(c.aux) % 16 != 0 || c.d_is_f32 || inter >= (1 << 30))
+            return MFT_ERR_UNSUPPORTED;
+    }
     const bool can_split = f32_ok && c.k2 == 0;
     if (c.splits > 1 && !can_split) return MFT_ERR_UNSUPPORTED;
     const int64_t kb = (c.k + BK - 1) / BK + (c.k2 > 0 ? 1 : 0);
     const int bn = 256;
     const int splits = !can_split ? 1 : (c.splits == 0 ? choose_splits(c.m, c.n, kb) : c.splits);
-    CUtensorMap ma, mb, ma2, mb2, md;
+    CUtensorMap ma, mb, ma2, mb2, md, mx;
     if (int32_t s = make_tmap_bf16(&ma, c.a, c.m, c.k, c.lda, BM)) return s;
     if (int32_t s = make_tmap_bf16(&mb, c.b, c.n, c.k, c.ldb, bn / 2)) return s;
     if (c.k2 > 0) {
@@ -287,8 +318,12 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     if (c.d_is_f32) {
         if (int32_t s = make_tmap_f32_out(&md, c.d, c.m, c.n, c.ldd)) return s;
     } else {
-        if (int32_t s = make_tmap_bf16(&md, c.d, c.m, c.n, c.ldd, 32)) return s;
+        // the gated-MLP backward writes d_gate|d_up: D is twice as wide as the GEMM
+        if (int32_t s = make_tmap_bf16(&md, c.d, c.m, c.epi == EPI_GLU_BWD ? 2 * c.n : c.n, c.ldd, 32)) return s;
     }
+    mx = md;
+    if (c.epi == EPI_GLU_FWD) { if (int32_t s = make_tmap_bf16(&mx, c.aux, c.m, c.glu_inter, c.ld_aux, 32)) return s; }
+    if (c.epi == EPI_GLU_BWD) { if (int32_t s = make_tmap_bf16(&mx, c.aux, c.m, 2 * c.glu_inter, c.ld_aux, 32)) return s; }
     GemmParams p{};
     p.m = (int)c.m; p.n = (int)c.n; p.k = (int)c.k; p.k2 = (int)c.k2;
     p.alpha = c.alpha; p.bias = c.bias; p.d = c.d; p.ldd = c.ldd; p.tma_store = 1;
@@ -297,8 +332,9 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     p.ce_tgt = c.ce_tgt; p.ce_lse = c.ce_lse; p.ce_nvalid = c.ce_nvalid; p.ce_nvalid_override = c.ce_nvalid_override;
     p.ce_dloss = c.ce_dloss; p.ce_col_offset = c.ce_col_offset;
     p.ce_partials = c.ce_partials; p.ce_partial_ld = c.ce_partial_ld; p.ce_tgt_logit = c.ce_tgt_logit; p.ce_flag = c.ce_flag;
+    p.glu_geglu = c.glu_geglu; p.glu_inter = (int)c.glu_inter;
     p.num_m_tiles = (p.m + 2 * BM - 1) / (2 * BM);
-    p.num_n_tiles = (p.n + bn - 1) / bn;
+    p.num_n_tiles = c.epi == EPI_GLU_FWD ? (int)(c.glu_inter / 128) : (p.n + bn - 1) / bn;
     p.tiles_mn = p.num_m_tiles * p.num_n_tiles;
     p.kb_per_split = (int)((kb + splits - 1) / splits);
     p.splits = (int)((kb + p.kb_per_split - 1) / p.kb_per_split);
@@ -306,9 +342,11 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
         if (int32_t s = check_cuda(cudaMemset2DAsync(p.d, (size_t)p.ldd * 4, 0, (size_t)p.n * 4, (size_t)p.m, stream), "gemm split-K memset")) return s;
         p.f32_reduce = 1;
     }
-    if (c.epi == EPI_CE_GRAD) return launch<EPI_CE_GRAD, 256>(ma, mb, ma2, mb2, md, p, stream);
-    if (c.epi == EPI_CE_P) return launch<EPI_CE_P, 256>(ma, mb, ma2, mb2, md, p, stream);
-    return launch<EPI_STORE, 256>(ma, mb, ma2, mb2, md, p, stream);
+    if (c.epi == EPI_CE_GRAD) return launch<EPI_CE_GRAD, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
+    if (c.epi == EPI_CE_P) return launch<EPI_CE_P, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
+    if (c.epi == EPI_GLU_FWD) return launch<EPI_GLU_FWD, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
+    if (c.epi == EPI_GLU_BWD) return launch<EPI_GLU_BWD, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
+    return launch<EPI_STORE, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
 }
 
 }  // namespace mft

@@ -150,6 +150,41 @@ def act_bwd(kind, dy, gate, up=None):
     return dgate, dup
 
 
+def glu_linear_fwd(kind, x, w_nk, *, xa=None, b_nk=None, bias=None):
+    """Gated MLP, forward, gating fused into the GEMM epilogue: returns (gate|up [M, 2I], act [M, I]) or None when the
+    shape does not qualify for the fused kernel.  w_nk [2I, K] (gate rows first), xa [M, r], b_nk [2I, r]."""
+    _init(x)
+    m, k = x.shape
+    inter = w_nk.shape[0] // 2
+    gu = torch.empty(m, 2 * inter, device=x.device, dtype=BF16)
+    act = torch.empty(m, inter, device=x.device, dtype=BF16)
+    k2 = 0 if xa is None else xa.shape[1]
+    rc = L.load().mft_glu_linear_fwd(kind, _p(x), x.stride(0), _p(w_nk), w_nk.stride(0), m, inter, k, _p(xa), 0 if xa is None else xa.stride(0),
+                                     _p(b_nk), 0 if b_nk is None else b_nk.stride(0), k2, _p(bias), _p(gu), gu.stride(0), _p(act), act.stride(0), _stream())
+    if rc == L.MFT_ERR_UNSUPPORTED:
+        return None
+    if rc != 0:
+        raise L.MftError(f"mft_glu_linear_fwd failed with status {rc}: {L.load().mft_last_error().decode(errors='replace')}")
+    return gu, act
+
+
+def glu_linear_bwd(kind, dy, w_kn, gu, *, a2=None, b2=None):
+    """Gated MLP, backward through the down projection and the gating in one launch: d_gate|d_up [M, 2I] from dy [M, K],
+    the down-projection weight w_kn [I, K] (K-major) and the saved gate|up; None when the shape does not qualify."""
+    _init(dy)
+    m, k = dy.shape
+    inter = w_kn.shape[0]
+    dgu = torch.empty(m, 2 * inter, device=dy.device, dtype=BF16)
+    k2 = 0 if a2 is None else a2.shape[1]
+    rc = L.load().mft_glu_linear_bwd(kind, _p(dy), dy.stride(0), _p(w_kn), w_kn.stride(0), m, inter, k, _p(a2), 0 if a2 is None else a2.stride(0),
+                                     _p(b2), 0 if b2 is None else b2.stride(0), k2, _p(gu), gu.stride(0), _p(dgu), dgu.stride(0), _stream())
+    if rc == L.MFT_ERR_UNSUPPORTED:
+        return None
+    if rc != 0:
+        raise L.MftError(f"mft_glu_linear_bwd failed with status {rc}: {L.load().mft_last_error().decode(errors='replace')}")
+    return dgu
+
+
 # ---------------------------------------------------------------- RoPE (+ per-head norm)
 def rope_tables(seq_len, head_dim, theta, device):
     cos = torch.empty(seq_len, head_dim // 2, dtype=F32)

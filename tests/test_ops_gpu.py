@@ -168,6 +168,53 @@ def test_lora_linear_model_width(ops):
     close_bf16(y, want_y); close_bf16(dx, want_dx); close_bf16(dA, want_dA); close_bf16(dB, want_dB)
 
 
+# ------------------------------------------------------------------ gated MLP fused into the GEMM epilogues
+@pytest.mark.parametrize("kind_name,m,inter,k,r,with_bias", [("geglu", 512, 256, 128, 16, False), ("geglu", 300, 384, 200, 0, False),
+                                                             ("swiglu", 1024, 4864, 896, 16, True), ("geglu", 768, 6912, 1152, 32, False)])
+def test_fused_gated_mlp_equals_gemm_plus_activation_kernel(ops, kind_name, m, inter, k, r, with_bias):
+    """mft_glu_linear_fwd / _bwd (gating inside the CTA-pair GEMM's epilogue) against the same GEMM followed by the
+    stand-alone activation kernels, which are pinned to the reference's golden vectors: bit-identical by construction
+    (both round gate / up / d_act to bf16 before the gating)."""
+    from mobilefinetuner_b200 import _lib as L
+    kind = L.ACT_GEGLU if kind_name == "geglu" else L.ACT_SWIGLU
+    g = torch.Generator(device="cuda").manual_seed(m + inter + k)
+    bf = torch.bfloat16
+    x = torch.randn(m, k, device="cuda", generator=g).to(bf)
+    w = (torch.randn(2 * inter, k, device="cuda", generator=g) * 0.05).to(bf)
+    xa = torch.randn(m, 64, device="cuda", generator=g).to(bf)[:, :r] if r else None
+    bp = (torch.randn(2 * inter, 64, device="cuda", generator=g) * 0.05).to(bf)[:, :r] if r else None
+    bias = torch.randn(2 * inter, device="cuda", generator=g) * 0.1 if with_bias else None
+    fused = ops.glu_linear_fwd(kind, x, w, xa=xa, b_nk=bp, bias=bias)
+    assert fused is not None, "the shape qualifies for the fused kernel"
+    gu_f, act_f = fused
+    gu = ops.gemm_nt(x, w, a2=xa, b2=bp, bias=bias)
+    act = ops.act_fwd(kind, gu[:, :inter], gu[:, inter:])
+    assert torch.equal(gu_f, gu) and torch.equal(act_f, act)
+    # sanity against float64 as well (the activation kernel itself is pinned by the golden tests)
+    assert torch.isfinite(act_f.float()).all()
+    # backward: dy [m, k'] x down-projection weight [inter, k'] -> d_act, then the gating's backward
+    kd = 128 if k < 512 else 640
+    dy = torch.randn(m, kd, device="cuda", generator=g).to(bf)
+    wd = (torch.randn(inter, kd, device="cuda", generator=g) * 0.05).to(bf)
+    a2 = torch.randn(m, 64, device="cuda", generator=g).to(bf)[:, :r] if r else None
+    b2 = (torch.randn(inter, 64, device="cuda", generator=g) * 0.05).to(bf)[:, :r] if r else None
+    dgu_f = ops.glu_linear_bwd(kind, dy, wd, gu, a2=a2, b2=b2)
+    assert dgu_f is not None
+    d_act = ops.gemm_nt(dy, wd, a2=a2, b2=b2)
+    dg, du = ops.act_bwd(kind, d_act, gu[:, :inter], gu[:, inter:])
+    assert torch.equal(dgu_f[:, :inter], dg) and torch.equal(dgu_f[:, inter:], du)
+    assert ops.device_status() == 0
+
+
+def test_fused_gated_mlp_declines_shapes_it_does_not_cover(ops):
+    from mobilefinetuner_b200 import _lib as L
+    bf = torch.bfloat16
+    x = torch.zeros(64, 128, device="cuda", dtype=bf)                     # fewer than 256 rows
+    assert ops.glu_linear_fwd(L.ACT_GEGLU, x, torch.zeros(512, 128, device="cuda", dtype=bf)) is None
+    x = torch.zeros(512, 128, device="cuda", dtype=bf)                    # inter = 200: not a multiple of 128
+    assert ops.glu_linear_fwd(L.ACT_GEGLU, x, torch.zeros(400, 128, device="cuda", dtype=bf)) is None
+
+
 # ------------------------------------------------------------------ attention
 def run_attention(ops, q, k, v, dO, scale, window, theta, split_heads=True):
     bf = torch.bfloat16
