@@ -117,8 +117,11 @@ __device__ __forceinline__ float ex2(float x) {
 }
 __device__ __forceinline__ bool visible(int i, int j, int window) { return j <= i && (window <= 0 || i - j < window); }
 
+// head_dim 64 needs 58 KB of shared memory and 256 tensor-memory columns per CTA: two CTAs share an SM and cover each
+// other's barrier / tensor-memory latencies (one tile's chain of S -> softmax -> P -> P V is several times longer than its
+// MMAs)
 template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, HD == 64 ? 2 : 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
     dep_trigger();
