@@ -234,6 +234,10 @@ int32_t mft_gemm_nt(const void* a_bf16, int64_t lda, const void* b_bf16, int64_t
  * since the last call of mft_profile_gemm. */
 int32_t mft_profile_gemm(int32_t enable);
 int32_t mft_profile_gemm_report(double* flops_host, double* ms_host, int64_t* launches_host);
+/* The same sums over the launches whose epilogue is selected by bit e of `epilogue_mask`: 0 plain store, 1..3 the
+ * lm-head cross-entropy epilogues (row statistics, gradient, probabilities), 4 / 5 the gated-MLP forward / backward
+ * epilogues.  A fused launch's time contains its epilogue's element-wise work, its flops only the product. */
+int32_t mft_profile_gemm_report_epi(int32_t epilogue_mask, double* flops_host, double* ms_host, int64_t* launches_host);
 
 /* "TN" product with the long dimension contracted (the LoRA weight gradients
  * dA = s*X^T*(dY*B^T), dB = s*(X*A)^T*dY of the generic MatmulBackward):

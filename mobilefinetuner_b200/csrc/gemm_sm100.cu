@@ -428,7 +428,7 @@ static int pick_bn(int64_t n) {
 }
 
 // ---- optional per-launch timing (bench / profiling only): CUDA events around every GEMM launch
-struct ProfEntry { cudaEvent_t e0, e1; double flops; };
+struct ProfEntry { cudaEvent_t e0, e1; double flops; int epi; };
 static std::vector<ProfEntry> g_prof;
 static bool g_prof_on = false;
 
@@ -441,6 +441,7 @@ int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream) {
     ProfEntry e;
     cudaEventCreate(&e.e0); cudaEventCreate(&e.e1);
     e.flops = 2.0 * (double)c.m * (double)c.n * ((double)c.k + (double)c.k2);
+    e.epi = c.epi;
     cudaEventRecord(e.e0, stream);
     const int32_t s = gemm_nt_run_inner(c, stream);
     cudaEventRecord(e.e1, stream);
@@ -520,17 +521,23 @@ extern "C" int32_t mft_profile_gemm(int32_t enable) {
     return MFT_OK;
 }
 
-extern "C" int32_t mft_profile_gemm_report(double* flops, double* ms, int64_t* launches) {
+extern "C" int32_t mft_profile_gemm_report_epi(int32_t epilogue_mask, double* flops, double* ms, int64_t* launches) {
     MFT_CHECK_ARG(flops && ms && launches, "mft_profile_gemm_report: null pointer");
     double f = 0, t = 0;
+    int64_t n = 0;
     for (auto& e : g_prof) {
+        if (!((epilogue_mask >> e.epi) & 1)) continue;
         if (int32_t s = check_cuda(cudaEventSynchronize(e.e1), "profile sync")) return s;
         float dt = 0.f;
         cudaEventElapsedTime(&dt, e.e0, e.e1);
-        f += e.flops; t += dt;
+        f += e.flops; t += dt; ++n;
     }
-    *flops = f; *ms = t; *launches = (int64_t)g_prof.size();
+    *flops = f; *ms = t; *launches = n;
     return MFT_OK;
+}
+
+extern "C" int32_t mft_profile_gemm_report(double* flops, double* ms, int64_t* launches) {
+    return mft_profile_gemm_report_epi(~0, flops, ms, launches);
 }
 
 extern "C" int32_t mft_glu_linear_fwd(int32_t kind, const void* x, int64_t ldx, const void* w_nk, int64_t ldw, int64_t m, int64_t inter, int64_t k,
