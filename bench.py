@@ -38,6 +38,8 @@ def parse():
     ap.add_argument("--config", default="gemma3_1b")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemm-shapes", default=None, metavar="FILE",
+                    help="write one line per GEMM shape of the profiled step (launches, device ms, TFLOP/s) to FILE")
     return ap.parse_args()
 
 
@@ -101,6 +103,27 @@ def profiled_traffic_bytes(spec_name: str, tokens: int):
 
 # ------------------------------------------------------------------ CPU reference
 CPU_SAMPLE_TOKENS = 640          # longer than the 512-token sliding window, so the window is active in the sample
+
+
+def write_gemm_shapes(path: str, launches: int):
+    """Per shape of the GEMM launches recorded by mft_profile_gemm: launches, summed device time, executed TFLOP/s."""
+    import ctypes as C
+    from mobilefinetuner_b200 import _lib as L
+    names = {0: "store", 1: "ce_stats", 2: "ce_grad", 3: "ce_p", 4: "glu_fwd", 5: "glu_bwd"}
+    rows = {}
+    for i in range(launches):
+        shp, epi, f32, ms = (C.c_int64 * 4)(), C.c_int32(), C.c_int32(), C.c_double()
+        L.call("mft_profile_gemm_launch", i, shp, C.byref(epi), C.byref(f32), C.byref(ms))
+        key = (shp[0], shp[1], shp[2], shp[3], names.get(epi.value, str(epi.value)), "f32" if f32.value else "bf16")
+        r = rows.setdefault(key, [0, 0.0])
+        r[0] += 1
+        r[1] += ms.value
+    with open(path, "w") as f:
+        f.write("m n k k_lora epilogue out launches total_ms avg_us tflops\n")
+        for key, (cnt, ms) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+            m, n, k, k2 = key[:4]
+            tf = 2.0 * m * n * (k + k2) * cnt / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
+            f.write(f"{m} {n} {k} {k2} {key[4]} {key[5]} {cnt} {ms:.3f} {ms / cnt * 1e3:.1f} {tf:.1f}\n")
 
 
 def cpu_reference_sample(cfg, steps: int, warmup: int, with_depth_estimate: bool = False) -> dict:
@@ -275,6 +298,8 @@ def run_ours(args):
         f_ce, t_ce, n_ce = report(0b001110)
         f_glu, t_glu, n_glu = report(0b110000)
         f_all, t_all, n_all = report(~0)
+        if args.gemm_shapes:
+            write_gemm_shapes(args.gemm_shapes, n_all)
         L.call("mft_profile_gemm", 0)
         peaks_path = ROOT / "MEASURED_PEAKS.json"
         if peaks_path.exists():

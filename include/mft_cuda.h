@@ -238,6 +238,9 @@ int32_t mft_profile_gemm_report(double* flops_host, double* ms_host, int64_t* la
  * lm-head cross-entropy epilogues (row statistics, gradient, probabilities), 4 / 5 the gated-MLP forward / backward
  * epilogues.  A fused launch's time contains its epilogue's element-wise work, its flops only the product. */
 int32_t mft_profile_gemm_report_epi(int32_t epilogue_mask, double* flops_host, double* ms_host, int64_t* launches_host);
+/* One recorded launch, 0 <= index < launches of mft_profile_gemm_report: its shape (m, n, k, k of the LoRA block),
+ * epilogue, output type and device time. */
+int32_t mft_profile_gemm_launch(int64_t index, int64_t* shape_mnk_k2_host, int32_t* epilogue_host, int32_t* d_is_f32_host, double* ms_host);
 
 /* "TN" product with the long dimension contracted (the LoRA weight gradients
  * dA = s*X^T*(dY*B^T), dB = s*(X*A)^T*dY of the generic MatmulBackward):

@@ -114,6 +114,7 @@ _SIGS = {
     "mft_profile_gemm": [i32],
     "mft_profile_gemm_report": [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(i64)],
     "mft_profile_gemm_report_epi": [i32, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(i64)],
+    "mft_profile_gemm_launch": [i64, C.POINTER(i64), C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_double)],
     "mft_gemm_tn_acc": [vp, i64, vp, i64, i64, i64, i64, f32, vp, i64, vp],
     "mft_pack_blocks_bf16": [vp, i32, vp],
     "mft_accumulate_blocks_f32": [vp, i32, vp],

@@ -15,14 +15,62 @@
 namespace mft {
 
 constexpr int EPI_BOX_BYTES = 32 * 64 * 2;
+
+// The CTA-pair kernel runs two epilogue warps per lane quadrant of tensor memory (a warp reaches only the 32 lanes
+// warp % 4 selects).  They share the quadrant's boxes: each fills one half of a box's columns, the `owner` (side 0)
+// waits until the previous store from the box has read it, tells the `helper` (side 1), and issues the TMA store once
+// the helper's half is in.  The per-element work of an epilogue is what bounds it (one warp per scheduler cannot hide
+// the latency of its own tensor-memory loads and special-function chains), so two warps per quadrant nearly halve it.
+// side -1: one warp fills the whole box (single-CTA kernel).  All waits are bounded.
+struct BoxPair {
+    uint64_t* free_bar = nullptr;     // owner -> helper: the box may be written            (count 1, one phase per box);
+                                      // gated-MLP backward: the owner has taken the helper's report of a chunk
+    uint64_t* filled_bar = nullptr;   // helper -> owner: the helper's half is in the box   (count 1, one phase per box)
+    uint64_t* sum_bar = nullptr;      // helper -> owner: per-row sums of a tile are in `sums` (EPI_CE_P; one phase per tile)
+    float* sums = nullptr;            // [32] floats of this quadrant
+    volatile int* abort_flag = nullptr;
+    int side = -1;
+    int uses = 0, tiles = 0;
+    __device__ __forceinline__ int half_begin() const { return side == 1 ? 1 : 0; }
+    __device__ __forceinline__ int half_end() const { return side == 0 ? 1 : 2; }
+};
+// Before a box is written.  PENDING = stores that may still be reading OTHER boxes of this warp.
+template <int PENDING>
+__device__ __forceinline__ bool box_acquire(BoxPair& bp, int lane) {
+    using namespace ptx;
+    if (bp.side == 1) return __all_sync(0xffffffffu, mbar_wait(bp.free_bar, (uint32_t)(bp.uses & 1), bp.abort_flag)) != 0;   // the same answer in every lane
+    if (lane == 0) {
+        tma_store_wait_read<PENDING>();
+        if (bp.side == 0) mbar_arrive(bp.free_bar);
+    }
+    __syncwarp();
+    return true;
+}
+// After a box is written.  Returns true in the warp whose lane 0 issues the store; `ok` turns false when a wait ran out.
+__device__ __forceinline__ bool box_release(BoxPair& bp, int lane, bool& ok) {
+    using namespace ptx;
+    fence_proxy_async();
+    __syncwarp();
+    if (bp.side == 1) {
+        if (lane == 0) mbar_arrive(bp.filled_bar);
+        ++bp.uses;
+        return false;
+    }
+    if (bp.side == 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bp.filled_bar, (uint32_t)(bp.uses & 1), bp.abort_flag)) != 0;
+        ++bp.uses;
+    }
+    return ok;
+}
 // EPI_CE_P trusts exp(acc - m_ref) only up to e^60 (the row sum over a 2^18-entry vocabulary stays finite in fp32);
 // rows beyond it are flagged and recomputed exactly by the caller.
 constexpr float CE_P_MAX_EXCESS = 60.f;
 
 template <int EPI, int BN>
-__device__ __forceinline__ void epilogue_bf16_tma(const GemmParams& p, const CUtensorMap* map_d, uint8_t* store_smem, uint32_t taddr,
-                                                  int q, int lane, int row, int store_row0, int n0, int& box_ctr) {
+__device__ __forceinline__ bool epilogue_bf16_tma(const GemmParams& p, const CUtensorMap* map_d, uint8_t* store_smem, uint32_t taddr,
+                                                  int q, int lane, int row, int store_row0, int n0, int& box_ctr, BoxPair& bp) {
     using namespace ptx;
+    bool ok = true;
     float lse = 0.f, coef = 0.f, row_sum = 0.f;
     int tgt = -1;
     if constexpr (EPI == EPI_CE_GRAD || EPI == EPI_CE_P) {
@@ -41,10 +89,8 @@ __device__ __forceinline__ void epilogue_bf16_tma(const GemmParams& p, const CUt
         if (n0 + c >= p.n) break;          // uniform across the warp
         uint8_t* buf = store_smem + (q * 2 + (box_ctr & 1)) * EPI_BOX_BYTES;
         const uint32_t buf_addr = smem_u32(buf) + (uint32_t)lane * 128u;
-        if (lane == 0) tma_store_wait_read<1>();   // the store that last used this buffer has read it
-        __syncwarp();
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        if (!box_acquire<1>(bp, lane)) return false;   // the store that last used this buffer has read it
+        for (int half = bp.half_begin(); half < bp.half_end(); ++half) {
             uint32_t r[32];
             tmem_ld_32x32(taddr + (uint32_t)(c + half * 32), r);
             tmem_ld_wait();
@@ -87,17 +133,28 @@ __device__ __forceinline__ void epilogue_bf16_tma(const GemmParams& p, const CUt
                              *reinterpret_cast<const uint32_t*>(&w2), *reinterpret_cast<const uint32_t*>(&w3));
             }
         }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
+        if (box_release(bp, lane, ok) && lane == 0) {
             tma_store_2d(map_d, buf, n0 + c, store_row0);
             tma_store_commit();
         }
+        if (!ok) return false;
         ++box_ctr;
     }
     if constexpr (EPI == EPI_CE_P) {
-        if (row < p.m) p.ce_partials[(long long)row * p.ce_partial_ld + (p.ce_col_offset + n0) / CE_TILE_N] = make_float2(0.f, row_sum);
+        if (bp.side == 1) {                  // the helper hands its part of the row sums to the owner
+            bp.sums[lane] = row_sum;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bp.sum_bar);
+        } else {
+            if (bp.side == 0) {
+                if (!__all_sync(0xffffffffu, mbar_wait(bp.sum_bar, (uint32_t)(bp.tiles & 1), bp.abort_flag))) return false;
+                row_sum += bp.sums[lane];
+            }
+            if (row < p.m) p.ce_partials[(long long)row * p.ce_partial_ld + (p.ce_col_offset + n0) / CE_TILE_N] = make_float2(0.f, row_sum);
+        }
+        ++bp.tiles;
     }
+    return true;
 }
 
 // ---- gated MLP, forward.  The accumulator of this CTA holds 128 rows x [128 gate columns | 128 up columns].  Per
@@ -119,10 +176,11 @@ __device__ __forceinline__ void epi_pack_store_half(uint32_t buf_addr, int half,
 }
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-__device__ __forceinline__ void epilogue_glu_fwd(const GemmParams& p, const CUtensorMap* map_d, const CUtensorMap* map_act, uint8_t* store_smem,
-                                                 uint32_t taddr, int q, int lane, int store_row0, int g0, int& box_ctr) {
+__device__ __forceinline__ bool epilogue_glu_fwd(const GemmParams& p, const CUtensorMap* map_d, const CUtensorMap* map_act, uint8_t* store_smem,
+                                                 uint32_t taddr, int q, int lane, int store_row0, int g0, int& box_ctr, BoxPair& bp) {
     using namespace ptx;
     const bool geglu = p.glu_geglu != 0;
+    bool ok = true;
 #pragma unroll 1
     for (int c = 0; c < 128; c += 64) {
         // pass 0: gate chunk -> D, pass 1: up chunk -> D, pass 2: f(gate) * up -> act
@@ -130,10 +188,8 @@ __device__ __forceinline__ void epilogue_glu_fwd(const GemmParams& p, const CUte
         for (int pass = 0; pass < 3; ++pass) {
             uint8_t* buf = store_smem + (q * 2 + (box_ctr & 1)) * EPI_BOX_BYTES;
             const uint32_t buf_addr = smem_u32(buf) + (uint32_t)lane * 128u;
-            if (lane == 0) tma_store_wait_read<1>();   // the store that last used this buffer has read it
-            __syncwarp();
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            if (!box_acquire<1>(bp, lane)) return false;   // the store that last used this buffer has read it
+            for (int half = bp.half_begin(); half < bp.half_end(); ++half) {
                 float v[32];
                 if (pass < 2) {
                     uint32_t r[32];
@@ -161,16 +217,16 @@ __device__ __forceinline__ void epilogue_glu_fwd(const GemmParams& p, const CUte
                 }
                 epi_pack_store_half(buf_addr, half, lane, v);
             }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
+            if (box_release(bp, lane, ok) && lane == 0) {
                 if (pass < 2) tma_store_2d(map_d, buf, pass * p.glu_inter + g0 + c, store_row0);
                 else tma_store_2d(map_act, buf, g0 + c, store_row0);
                 tma_store_commit();
             }
+            if (!ok) return false;
             ++box_ctr;
         }
     }
+    return true;
 }
 
 // ---- gated MLP, backward.  The accumulator holds d(act) for 128 rows x 256 columns of [M, inter].  Per 64-column
@@ -212,7 +268,7 @@ __device__ __forceinline__ void glu_bwd_prefetch(const GemmParams& p, const CUte
 // One tile.  Returns false when a wait ran out.
 __device__ __forceinline__ bool epilogue_glu_bwd(const GemmParams& p, const CUtensorMap* map_d, const CUtensorMap* map_gu, uint8_t* boxes, uint64_t* bars,
                                                  volatile int* abort_flag, uint32_t taddr, int q, int lane, int rank, int store_row0, int n0,
-                                                 int tile_step, int num_tiles, GluBwdState& st) {
+                                                 int tile_step, int num_tiles, GluBwdState& st, BoxPair& bp) {
     using namespace ptx;
     const bool geglu = p.glu_geglu != 0;
 #pragma unroll 1
@@ -220,15 +276,14 @@ __device__ __forceinline__ bool epilogue_glu_bwd(const GemmParams& p, const CUte
         if (n0 + c >= p.n) break;            // uniform across the warp (inter is a multiple of 64)
         const int set = st.chunk % GLU_SETS;
         // the next request goes into the set of the previous chunk, whose stores (the latest commit) must have read it
-        if (lane == 0) {
+        if (bp.side != 1 && lane == 0) {     // the helper issues neither loads nor stores
             tma_store_wait_read<0>();
             glu_bwd_prefetch(p, map_gu, boxes, bars, q, rank, tile_step, num_tiles, st);
         }
-        if (!mbar_wait(bars + q * GLU_SETS + set, (uint32_t)((st.chunk / GLU_SETS) & 1), abort_flag)) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(bars + q * GLU_SETS + set, (uint32_t)((st.chunk / GLU_SETS) & 1), abort_flag))) return false;
         uint8_t* gbox = boxes + ((q * GLU_SETS + set) * 2 + 0) * EPI_BOX_BYTES;
         const uint32_t g_addr = smem_u32(gbox) + (uint32_t)lane * 128u, u_addr = g_addr + EPI_BOX_BYTES;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = bp.half_begin(); half < bp.half_end(); ++half) {
             uint32_t r[32];
             tmem_ld_32x32(taddr + (uint32_t)(c + half * 32), r);
             tmem_ld_wait();
@@ -256,10 +311,20 @@ __device__ __forceinline__ bool epilogue_glu_bwd(const GemmParams& p, const CUte
         }
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) {
-            tma_store_2d(map_d, gbox, n0 + c, store_row0);
-            tma_store_2d(map_d, gbox + EPI_BOX_BYTES, p.glu_inter + n0 + c, store_row0);
-            tma_store_commit();
+        if (bp.side == 1) {
+            // Nothing else holds the helper back here (its boxes arrive by TMA, not from the owner), and a parity wait
+            // tells phases apart only one phase deep: the helper reports chunk k only after the owner has taken its
+            // report of chunk k - 1.
+            if (st.chunk > 0 && !__all_sync(0xffffffffu, mbar_wait(bp.free_bar, (uint32_t)((st.chunk - 1) & 1), abort_flag))) return false;
+            if (lane == 0) mbar_arrive(bp.filled_bar);
+        } else {
+            if (bp.side == 0 && !__all_sync(0xffffffffu, mbar_wait(bp.filled_bar, (uint32_t)(st.chunk & 1), abort_flag))) return false;
+            if (lane == 0) {
+                tma_store_2d(map_d, gbox, n0 + c, store_row0);
+                tma_store_2d(map_d, gbox + EPI_BOX_BYTES, p.glu_inter + n0 + c, store_row0);
+                tma_store_commit();
+                if (bp.side == 0) mbar_arrive(bp.free_bar);
+            }
         }
         ++st.chunk;
     }
@@ -269,40 +334,42 @@ __device__ __forceinline__ bool epilogue_glu_bwd(const GemmParams& p, const CUte
 // f32 outputs: boxes of 32 rows x 32 columns (128-byte rows, same swizzle), written with a tensor store or,
 // when D already holds a partial result (accumulate / K split), added to memory by a tensor reduction.
 template <int BN>
-__device__ __forceinline__ void epilogue_f32_tma(const GemmParams& p, const CUtensorMap* map_d, uint8_t* store_smem, uint32_t taddr,
-                                                 int q, int lane, int store_row0, int n0, bool add_bias, int& box_ctr) {
+__device__ __forceinline__ bool epilogue_f32_tma(const GemmParams& p, const CUtensorMap* map_d, uint8_t* store_smem, uint32_t taddr,
+                                                 int q, int lane, int store_row0, int n0, bool add_bias, int& box_ctr, BoxPair& bp) {
     using namespace ptx;
+    bool ok = true;
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {
         if (n0 + c >= p.n) break;          // uniform across the warp
         uint8_t* buf = store_smem + (q * 2 + (box_ctr & 1)) * EPI_BOX_BYTES;
         const uint32_t buf_addr = smem_u32(buf) + (uint32_t)lane * 128u;
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + (uint32_t)c, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c;
+        if (!box_acquire<1>(bp, lane)) return false;
+        for (int half = bp.half_begin(); half < bp.half_end(); ++half) {     // 16 of the box's 32 columns
+            uint32_t r[16];
+            tmem_ld_32x16(taddr + (uint32_t)(c + half * 16), r);
+            tmem_ld_wait();
+            const int col0 = n0 + c + half * 16;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * p.alpha);
-        if (add_bias) {
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * p.alpha);
+            if (add_bias) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (col0 + j < p.n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(p.bias + col0 + j));
+                for (int j = 0; j < 16; ++j) if (col0 + j < p.n) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(p.bias + col0 + j));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t pos = (uint32_t)((half * 4 + j) ^ (lane & 7));   // 128-byte swizzle
+                st_shared_v4(buf_addr + pos * 16u, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            }
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t pos = (uint32_t)(j ^ (lane & 7));   // 128-byte swizzle
-            st_shared_v4(buf_addr + pos * 16u, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-            if (p.f32_reduce) tma_reduce_add_2d(map_d, buf, col0, store_row0);
-            else tma_store_2d(map_d, buf, col0, store_row0);
+        if (box_release(bp, lane, ok) && lane == 0) {
+            if (p.f32_reduce) tma_reduce_add_2d(map_d, buf, n0 + c, store_row0);
+            else tma_store_2d(map_d, buf, n0 + c, store_row0);
             tma_store_commit();
         }
+        if (!ok) return false;
         ++box_ctr;
     }
+    return true;
 }
 
 }  // namespace mft

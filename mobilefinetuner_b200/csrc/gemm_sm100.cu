@@ -163,6 +163,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int it = 0;
         int box_ctr = 0;
         bool ok = true;
+        BoxPair solo;                              // one warp per lane quarter: it fills whole boxes
         const bool vec_ok = p.d_is_f32 ? ((p.ldd % 4) == 0 && (reinterpret_cast<uintptr_t>(p.d) % 16) == 0)
                                        : ((p.ldd % 8) == 0 && (reinterpret_cast<uintptr_t>(p.d) % 16) == 0);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -176,9 +177,9 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int row = m0 + row_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
             if (EPI == EPI_STORE && p.tma_store && p.d_is_f32) {
-                epilogue_f32_tma<BN>(p, &map_d, store_smem, taddr, q, lane, m0 + q * 32, n0, p.bias != nullptr && tile < p.tiles_mn, box_ctr);
+                epilogue_f32_tma<BN>(p, &map_d, store_smem, taddr, q, lane, m0 + q * 32, n0, p.bias != nullptr && tile < p.tiles_mn, box_ctr, solo);
             } else if (EPI != EPI_CE_STATS && p.tma_store) {
-                epilogue_bf16_tma<EPI, BN>(p, &map_d, store_smem, taddr, q, lane, row, m0 + q * 32, n0, box_ctr);
+                epilogue_bf16_tma<EPI, BN>(p, &map_d, store_smem, taddr, q, lane, row, m0 + q * 32, n0, box_ctr, solo);
             } else if constexpr (EPI == EPI_STORE) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
@@ -428,7 +429,7 @@ static int pick_bn(int64_t n) {
 }
 
 // ---- optional per-launch timing (bench / profiling only): CUDA events around every GEMM launch
-struct ProfEntry { cudaEvent_t e0, e1; double flops; int epi; };
+struct ProfEntry { cudaEvent_t e0, e1; double flops; int epi; int64_t m, n, k, k2; int d_is_f32; };
 static std::vector<ProfEntry> g_prof;
 static bool g_prof_on = false;
 
@@ -441,7 +442,7 @@ int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream) {
     ProfEntry e;
     cudaEventCreate(&e.e0); cudaEventCreate(&e.e1);
     e.flops = 2.0 * (double)c.m * (double)c.n * ((double)c.k + (double)c.k2);
-    e.epi = c.epi;
+    e.epi = c.epi; e.m = c.m; e.n = c.n; e.k = c.k; e.k2 = c.k2; e.d_is_f32 = c.d_is_f32;
     cudaEventRecord(e.e0, stream);
     const int32_t s = gemm_nt_run_inner(c, stream);
     cudaEventRecord(e.e1, stream);
@@ -533,6 +534,18 @@ extern "C" int32_t mft_profile_gemm_report_epi(int32_t epilogue_mask, double* fl
         f += e.flops; t += dt; ++n;
     }
     *flops = f; *ms = t; *launches = n;
+    return MFT_OK;
+}
+
+extern "C" int32_t mft_profile_gemm_launch(int64_t index, int64_t* shape_mnk_k2, int32_t* epilogue, int32_t* d_is_f32, double* ms) {
+    MFT_CHECK_ARG(shape_mnk_k2 && epilogue && d_is_f32 && ms, "mft_profile_gemm_launch: null pointer");
+    MFT_CHECK_ARG(index >= 0 && index < (int64_t)g_prof.size(), "mft_profile_gemm_launch: index beyond the recorded launches");
+    const ProfEntry& e = g_prof[(size_t)index];
+    if (int32_t s = check_cuda(cudaEventSynchronize(e.e1), "profile sync")) return s;
+    float dt = 0.f;
+    cudaEventElapsedTime(&dt, e.e0, e.e1);
+    shape_mnk_k2[0] = e.m; shape_mnk_k2[1] = e.n; shape_mnk_k2[2] = e.k; shape_mnk_k2[3] = e.k2;
+    *epilogue = e.epi; *d_is_f32 = e.d_is_f32; *ms = dt;
     return MFT_OK;
 }
 

@@ -25,7 +25,10 @@ using namespace ptx;
 
 namespace {
 
-constexpr int BM = 128, BK = 64, THREADS = 192;
+constexpr int BM = 128, BK = 64;
+constexpr int EPI_WARPS = 8;                  // two per lane quadrant of tensor memory: see BoxPair
+constexpr int THREADS = 64 + 32 * EPI_WARPS;  // TMA warp, MMA warp, epilogue warps
+constexpr int BAR_BYTES = 1024;               // barriers, tensor-memory slot, abort flag, per-quadrant row sums
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int STORE_BYTES = 4 * 2 * EPI_BOX_BYTES;
 // BN2 = columns of the pair's tile.  256 is the only width in use: 192 measured 17 % slower per column and 128
@@ -39,7 +42,7 @@ struct PairCfg {
     static constexpr int STAGE_BYTES = A_BYTES + BH_BYTES;                  // 32 / 28 KB, multiples of 1024
     static constexpr int BOX_BYTES = EPI == EPI_GLU_BWD ? GLU_SETS * STORE_BYTES : STORE_BYTES;
     static constexpr int STAGES = EPI == EPI_GLU_BWD ? 8 - GLU_SETS - 1 : 6;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BOX_BYTES + 1024 + 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BOX_BYTES + 1024 + BAR_BYTES;
 };
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;   // clears the bit that distinguishes the two CTAs of a pair: -> address in the leader
 
@@ -106,8 +109,11 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* tmem_full_bar = bars + 2 * STAGES;  // [2]       both CTAs
     uint64_t* tmem_empty_bar = tmem_full_bar + 2; // [2]       used in the leader
     uint64_t* glu_bar = tmem_empty_bar + 2;       // [4 warps][GLU_SETS]  gated-MLP backward: gate / up boxes have landed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(glu_bar + 4 * GLU_SETS);
+    uint64_t* pair_bar = glu_bar + 4 * GLU_SETS;  // [4 quadrants][free, filled, sums]: the two epilogue warps of a quadrant
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4 * 3);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* pair_sums = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + BAR_BYTES / 2);    // [4][32]
+    static_assert((2 * 8 + 4 + 4 * GLU_SETS + 12) * 8 + 8 <= BAR_BYTES / 2, "barrier block");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
@@ -119,8 +125,9 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full_bar[b], 1); mbar_init(&tmem_empty_bar[b], 8); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full_bar[b], 1); mbar_init(&tmem_empty_bar[b], 2 * EPI_WARPS); }
         for (int b = 0; b < 4 * GLU_SETS; ++b) mbar_init(&glu_bar[b], 1);
+        for (int b = 0; b < 4 * 3; ++b) mbar_init(&pair_bar[b], 1);
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&map_a); tma_prefetch_desc(&map_b); tma_prefetch_desc(&map_d);
@@ -204,10 +211,15 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int row_in_tile = q * 32 + lane;
         int it = 0, box_ctr = 0;
         bool ok = true;
+        BoxPair bp;
+        bp.free_bar = pair_bar + q * 3; bp.filled_bar = bp.free_bar + 1; bp.sum_bar = bp.free_bar + 2;
+        bp.sums = pair_sums + q * 32;
+        bp.abort_flag = abort_flag;
+        bp.side = (warp - 2) >> 2;                                // warps 2..5 own the boxes of quadrants 2, 3, 0, 1; warps 6..9 help
         GluBwdState glu_state;
-        if (GLU_BWD) {                                            // gate / up boxes of this warp's first chunk(s)
+        if (GLU_BWD) {                                            // gate / up boxes of this quadrant's first chunk(s)
             glu_state.ahead_tile = cluster_id;
-            if (lane == 0)
+            if (lane == 0 && bp.side == 0)
                 for (int i = 0; i < GLU_SETS - 1; ++i) glu_bwd_prefetch(p, &map_x, store_smem, glu_bar, q, (int)rank, num_clusters, num_tiles, glu_state);
         }
         for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
@@ -221,20 +233,20 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int row = m0 + row_in_tile;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN2);
             if constexpr (GLU_FWD) {
-                epilogue_glu_fwd(p, &map_d, &map_x, store_smem, taddr, q, lane, m0 + q * 32, n0, box_ctr);
+                ok = epilogue_glu_fwd(p, &map_d, &map_x, store_smem, taddr, q, lane, m0 + q * 32, n0, box_ctr, bp);
             } else if constexpr (GLU_BWD) {
                 ok = epilogue_glu_bwd(p, &map_d, &map_x, store_smem, glu_bar, abort_flag, taddr, q, lane, (int)rank, m0 + q * 32, n0, num_clusters,
-                                      num_tiles, glu_state);
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && ok;
-                if (!ok) break;
+                                      num_tiles, glu_state, bp);
             } else
             if (EPI == EPI_STORE && p.d_is_f32)
-                epilogue_f32_tma<BN2>(p, &map_d, store_smem, taddr, q, lane, m0 + q * 32, n0, p.bias != nullptr && tile < p.tiles_mn, box_ctr);
+                ok = epilogue_f32_tma<BN2>(p, &map_d, store_smem, taddr, q, lane, m0 + q * 32, n0, p.bias != nullptr && tile < p.tiles_mn, box_ctr, bp);
             else
-                epilogue_bf16_tma<EPI, BN2>(p, &map_d, store_smem, taddr, q, lane, row, m0 + q * 32, n0, box_ctr);
+                ok = epilogue_bf16_tma<EPI, BN2>(p, &map_d, store_smem, taddr, q, lane, row, m0 + q * 32, n0, box_ctr, bp);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc]) & PEER_MASK);   // the accumulator buffer is free (count 8: 4 warps x 2 CTAs)
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[acc]) & PEER_MASK);   // the accumulator buffer is free (count: 8 warps x 2 CTAs)
         }
         if (lane == 0) tma_store_wait<0>();
     }

@@ -4,7 +4,9 @@
 // a few dtype conversions of frozen weights.
 #include "ops.h"
 
+#include <atomic>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <numeric>
 #include <stdexcept>
@@ -16,6 +18,38 @@ namespace ops {
 
 using detail::check;
 using detail::stream;
+
+// ---------------------------------------------------------------- compute type of the eager operators
+static std::atomic<int>& compute_dtype_slot() {
+    static std::atomic<int> v([] {
+        const char* e = std::getenv("MFT_COMPUTE_DTYPE");
+        const std::string s = e ? e : "";
+        return (s == "bf16" || s == "bfloat16" || s == "BF16") ? (int)kBFloat16 : (int)kFloat32;
+    }());
+    return v;
+}
+void set_compute_dtype(DType dtype) {
+    if (dtype != kFloat32 && dtype != kBFloat16) throw TensorError("set_compute_dtype: float32 or bfloat16");
+    compute_dtype_slot().store((int)dtype);
+}
+DType compute_dtype() { return (DType)compute_dtype_slot().load(); }
+
+namespace detail {
+bool compute_bf16() { return compute_dtype() == kBFloat16; }
+TensorPtr to_bf16(const TensorPtr& t) {
+    if (t->dtype() == kBFloat16) return t;
+    if (t->dtype() != kFloat32) throw TensorError("to_bf16: float32 or bfloat16 tensor expected");
+    auto out = std::make_shared<Tensor>(t->shape(), kBFloat16, kCPU);
+    check(mft_cast_f32_to_bf16((const float*)t->device_read(), out->device_write(), t->numel(), stream()), "cast to bf16");
+    return out;
+}
+TensorPtr bf16_to_f32(const TensorPtr& t, const std::vector<int64_t>& shape) {
+    auto out = std::make_shared<Tensor>(shape, kFloat32, kCPU);
+    if (out->numel() != t->numel()) throw TensorError("bf16_to_f32: element count mismatch");
+    check(mft_cast_bf16_to_f32(t->device_read(), (float*)out->device_write(), t->numel(), stream()), "cast to f32");
+    return out;
+}
+}  // namespace detail
 
 namespace {
 
@@ -112,6 +146,21 @@ TensorPtr matmul_raw(const TensorPtr& a, const TensorPtr& b_in, bool trans_b) {
     out_shape.back() = N;
     auto out = make(out_shape);
     const int64_t lead = as.size() >= 2 ? prod(as, 0, as.size() - 2) : 1;
+    if (bs.size() == 2 && detail::compute_bf16() && K % 8 == 0 && N % 8 == 0 && lead * M > 0) {
+        // bf16 operands on the tensor cores, fp32 accumulation and result: A [T,K] x (B as [N,K])^T through mft_gemm_nt
+        auto a_bf = detail::to_bf16(a);
+        TensorPtr b_nk;
+        if (trans_b) {
+            b_nk = detail::to_bf16(b_in->dtype() == kBFloat16 ? b_in : b);
+        } else {
+            b_nk = std::make_shared<Tensor>(std::vector<int64_t>{N, K}, kBFloat16, kCPU);
+            if (b_in->dtype() == kBFloat16) check(mft_transpose_bf16(b_in->device_read(), b_nk->device_write(), K, N, stream()), "matmul: operand transpose");
+            else check(mft_transpose_f32_to_bf16((const float*)b->device_read(), b_nk->device_write(), K, N, stream()), "matmul: operand transpose");
+        }
+        check(mft_gemm_nt(a_bf->device_read(), K, b_nk->device_read(), K, lead * M, N, K, nullptr, 0, nullptr, 0, 0, nullptr, 1.0f,
+                          out->device_write(), N, MFT_F32, 0, stream()), "matmul (tensor cores)");
+        return out;
+    }
     if (bs.size() == 2) {
         check(mft_matmul_f32((const float*)a->device_read(), (const float*)b->device_read(), (float*)out->device_write(), 1, lead * M, N, K, 0, 0, 0,
                              trans_b ? 1 : 0, stream()), "matmul");

@@ -1,8 +1,17 @@
 // Operator surface of the API (namespace ops), same names and argument meaning
 // as the reference's core/ops.h.  Every function runs on the GPU through the C
-// ABI of libmft_cuda.so (fp32 generic kernels here; the fused bf16 tensor-core
-// kernels are used by LoRALinear and the step engine) and records an autograd
-// node when an input requires grad.
+// ABI of libmft_cuda.so and records an autograd node when an input requires grad.
+//
+// Arithmetic type.  By default the eager operators compute in fp32 (generic
+// kernels): that is what the reference's unit tests, with their 1e-5 bounds,
+// expect.  With the compute type set to bf16 (set_compute_dtype(kBFloat16), or
+// MFT_COMPUTE_DTYPE=bf16 in the environment) the operators that have a fused
+// tensor-core kernel use it: matmul / matmul_rhs_T / linear with a 2-D right
+// operand (and so LoRALinear::forward) run mft_gemm_nt, memory_efficient_attention
+// runs mft_attn_fwd / mft_attn_bwd, selected_token / streaming_lm_cross_entropy
+// run mft_lmhead_ce_fwd / _bwd; inputs are rounded to bf16, products accumulate
+// in fp32, results come back as fp32 tensors.  The models' own forward() always
+// runs the bf16 step engine, whatever this switch says.
 #pragma once
 #include <string>
 #include <vector>
@@ -71,6 +80,10 @@ bool same_shape(const TensorPtr& a, const TensorPtr& b);
 bool broadcastable(const TensorPtr& a, const TensorPtr& b);
 std::vector<int64_t> broadcast_shape(const TensorPtr& a, const TensorPtr& b);
 std::vector<int64_t> infer_broadcast_shape(const TensorPtr& a, const TensorPtr& b);
+
+// kFloat32 (default) or kBFloat16: see the head of this file.
+void set_compute_dtype(DType dtype);
+DType compute_dtype();
 
 // Registers `fn` as the backward rule of `out` if any input requires grad.
 void register_backward(const TensorPtr& out, const std::vector<TensorPtr>& inputs, BackwardFunctionPtr fn);

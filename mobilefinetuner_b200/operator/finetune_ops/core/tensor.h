@@ -208,6 +208,9 @@ void check(int32_t status, const char* what);          // throws TensorError wit
 void* stream();                                        // the stream every ops:: kernel is launched on
 void ensure_runtime();                                 // mft_init on first use; throws without a GPU
 TensorPtr new_like(const std::vector<int64_t>& shape, DType dtype = kFloat32);
+bool compute_bf16();                                   // the eager operators use the bf16 tensor-core kernels where they exist
+TensorPtr to_bf16(const TensorPtr& t);                 // f32 -> bf16 copy on the device (a bf16 tensor is returned as it is)
+TensorPtr bf16_to_f32(const TensorPtr& t, const std::vector<int64_t>& shape);
 }  // namespace detail
 
 }  // namespace ops

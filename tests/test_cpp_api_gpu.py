@@ -46,3 +46,13 @@ def test_cpp_auto_trainer_step_matches_reference(tmp_path, name):
     ref_grads = [z[f"{name}/grad/{i}"] if f"{name}/grad/{i}" in z.files else None for i in range(len(lora))]
     ref_after = [z[f"{name}/after/{i}"] for i in range(len(lora))]
     check(loss, grads, after, lora, float(z[f"{name}/loss"][0]), ref_grads, ref_after)
+
+
+def test_eager_operators_bf16_compute_type_matches_fp32():
+    """ops::set_compute_dtype(kBFloat16) routes matmul / LoRALinear / memory_efficient_attention / the streaming lm-head
+    loss to the tensor-core kernels; values and gradients must agree with the fp32 operators to bf16 rounding
+    (tests/cpp/compute_dtype.cpp prints and checks cosine >= 0.999 and max error <= 2e-2 of the largest magnitude)."""
+    exe = EXE.parent / "compute_dtype"
+    assert exe.exists(), "compute_dtype was not built (python -c 'import __graft_entry__ as g; g.build()')"
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ALL OK" in r.stdout, r.stdout[-3000:] + r.stderr[-2000:]
