@@ -65,6 +65,10 @@ int32_t mft_model_destroy(mft_model_t* m);
 int32_t mft_model_param_count(const mft_model_t* m);
 int32_t mft_model_param_shape(const mft_model_t* m, int32_t idx, int64_t* rows, int64_t* cols);
 int32_t mft_model_set_param_host(mft_model_t* m, int32_t idx, const float* data_host);
+/* The same from bf16 bits (a BF16 checkpoint: graph/safetensors_loader.h:35-46 of the reference converts such
+ * tensors to f32 on the host; here they go up as stored, which is exact and half the bytes).  stored_transposed != 0:
+ * a linear weight stored [out, in] (HuggingFace) instead of the API's [in, out]. */
+int32_t mft_model_set_param_host_bf16(mft_model_t* m, int32_t idx, const void* data_bf16_host, int32_t stored_transposed);
 /* Same, from a device f32 buffer (weights generated on the device). */
 int32_t mft_model_set_param_dev(mft_model_t* m, int32_t idx, const float* data_dev);
 

@@ -147,6 +147,7 @@ _SIGS = {
     "mft_model_param_count": [vp],
     "mft_model_param_shape": [vp, i32, C.POINTER(i64), C.POINTER(i64)],
     "mft_model_set_param_host": [vp, i32, vp],
+    "mft_model_set_param_host_bf16": [vp, i32, vp, i32],
     "mft_model_set_param_dev": [vp, i32, vp],
     "mft_model_lora_count": [vp],
     "mft_model_lora_shape": [vp, i32, C.POINTER(i64), C.POINTER(i64)],

@@ -5,6 +5,8 @@
 #include "act_math.cuh"
 #include "common.cuh"
 
+#include <atomic>
+
 namespace mft {
 
 static inline int grid_for(int64_t work_items, int threads, int max_blocks = 148 * 16) {
@@ -233,15 +235,42 @@ __global__ void block_copy_kernel(const mft_block_copy_t* __restrict__ table) {
 }
 
 // ---------------------------------------------------------------- optimizer
-__global__ void sqnorm_kernel(const float* __restrict__ g, int64_t n, float* __restrict__ out) {
+// Sum of squares with a result that does not depend on the order in which blocks finish (data-parallel replicas
+// clip by this norm and must stay bit-identical): every block leaves its partial sum in a slot of a static array,
+// the block that arrives last adds the partials in index order and adds the total to *out.  Calls that may overlap on
+// the device use different slots (the host hands them out round-robin).
+constexpr int SQ_SLOTS = 16, SQ_MAX_BLOCKS = 1024;
+__device__ float sq_partials[SQ_SLOTS][SQ_MAX_BLOCKS];
+__device__ unsigned int sq_arrived[SQ_SLOTS];
+__global__ void sqnorm_kernel(const float* __restrict__ g, int64_t n, float* __restrict__ out, int slot) {
     dep_trigger();
     dep_wait();
     __shared__ float scratch[32];
+    __shared__ int last;
     float acc = 0.f;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) acc += g[i] * g[i];
     acc = block_sum(acc, scratch);
-    if (threadIdx.x == 0) atomicAdd(out, acc);
+    if (threadIdx.x == 0) {
+        sq_partials[slot][blockIdx.x] = acc;
+        __threadfence();
+        last = atomicAdd(&sq_arrived[slot], 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    float total = 0.f;
+    for (unsigned i = threadIdx.x; i < gridDim.x; i += blockDim.x) total += *reinterpret_cast<volatile float*>(&sq_partials[slot][i]);
+    __syncthreads();                          // scratch is reused
+    total = block_sum(total, scratch);
+    if (threadIdx.x == 0) {
+        *out += total;
+        sq_arrived[slot] = 0;                 // ready for the next call that gets this slot
+    }
+}
+static int next_sq_slot() {
+    static std::atomic<unsigned> counter{0};
+    return (int)(counter.fetch_add(1) % SQ_SLOTS);
 }
 __global__ void adam_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                             int64_t n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
@@ -401,13 +430,13 @@ int32_t mft_accumulate_blocks_f32(const mft_block_copy_t* table_dev, int32_t n, 
 int32_t mft_grad_sqnorm(const float* grads, int64_t n, float* sqnorm_dev, mft_stream_t stream) {
     MFT_CHECK_ARG(grads && sqnorm_dev && n > 0, "mft_grad_sqnorm: bad argument");
     if (int32_t s = check_cuda(cudaMemsetAsync(sqnorm_dev, 0, 4, as_stream(stream)), "sqnorm memset")) return s;
-    launch_dep(sqnorm_kernel, dim3(grid_for(n, 256, 148 * 4)), dim3(256), (size_t)(0), as_stream(stream), grads, n, sqnorm_dev);
+    launch_dep(sqnorm_kernel, dim3(grid_for(n, 256, 148 * 4)), dim3(256), (size_t)(0), as_stream(stream), grads, n, sqnorm_dev, next_sq_slot());
     MFT_LAUNCH_CHECK("grad_sqnorm");
     return MFT_OK;
 }
 int32_t mft_grad_sqnorm_add(const float* grads, int64_t n, float* sqnorm_dev, mft_stream_t stream) {
     MFT_CHECK_ARG(grads && sqnorm_dev && n > 0, "mft_grad_sqnorm_add: bad argument");
-    launch_dep(sqnorm_kernel, dim3(grid_for(n, 256, 148 * 4)), dim3(256), (size_t)(0), as_stream(stream), grads, n, sqnorm_dev);
+    launch_dep(sqnorm_kernel, dim3(grid_for(n, 256, 148 * 4)), dim3(256), (size_t)(0), as_stream(stream), grads, n, sqnorm_dev, next_sq_slot());
     MFT_LAUNCH_CHECK("grad_sqnorm_add");
     return MFT_OK;
 }

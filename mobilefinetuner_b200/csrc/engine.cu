@@ -457,6 +457,52 @@ extern "C" int32_t mft_model_set_param_host(mft_model_t* m, int32_t idx, const f
     return check_cuda(cudaStreamSynchronize(m->stream), "param upload");
 }
 
+// bf16 source: the bits are the ones the device stores, so they go up as they are (half the bytes of the f32 path,
+// no conversion loop on the host) and are placed by device copies / transposes.
+extern "C" int32_t mft_model_set_param_host_bf16(mft_model_t* m, int32_t idx, const void* data_bf16_host, int32_t stored_transposed) {
+    MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->params.size() && data_bf16_host, "mft_model_set_param_host_bf16: bad argument");
+    const ParamInfo& p = m->params[idx];
+    const uint16_t* src = static_cast<const uint16_t*>(data_bf16_host);
+    const int64_t n = p.rows * p.cols;
+    MFT_CHECK_ARG(!stored_transposed || p.kind == ParamInfo::LINEAR, "mft_model_set_param_host_bf16: only linear weights come transposed");
+    auto sync = [&] { return check_cuda(cudaStreamSynchronize(m->stream), "param upload"); };
+    switch (p.kind) {
+        case ParamInfo::LM_HEAD_COPY:
+            return MFT_OK;
+        case ParamInfo::EMBED:
+        case ParamInfo::POS_EMBED: {        // straight into the table
+            __nv_bfloat16* dst = p.kind == ParamInfo::EMBED ? m->embed : m->pos_embed;
+            TRY(mft_memcpy_h2d(dst, src, (size_t)n * 2, m->stream));
+            TRY(finish_param(m, p));
+            return sync();
+        }
+        case ParamInfo::LINEAR: {
+            LinearGroup* g = p.group;
+            const LinearSlot& s = g->slots[p.slot];
+            const int64_t stage_bytes = (m->stage_floats - 64) * 4;
+            if (stored_transposed) {
+                // [out, in] as stored IS this slot's rows of w_nk; w_kn gets the transpose
+                __nv_bfloat16* nk = g->w_nk + (int64_t)s.col0 * g->in;
+                TRY(mft_memcpy_h2d(nk, src, (size_t)n * 2, m->stream));
+                TRY(mft_transpose_bf16_ld(nk, g->w_kn + s.col0, s.out, s.in, g->n_total, m->stream));
+                return sync();
+            }
+            if (n * 6 > stage_bytes) return fail(MFT_ERR_UNSUPPORTED, "mft_model_set_param_host_bf16: linear larger than the staging buffer");
+            break;                          // [in, out]: through the f32 staging path below
+        }
+        default:
+            MFT_CHECK_ARG(n * 6 <= (m->stage_floats - 64) * 4, "mft_model_set_param_host_bf16: tensor larger than the staging buffer");
+            break;
+    }
+    // raw bits behind the f32 staging area, widened on the device (exact), then the usual placement
+    void* raw = reinterpret_cast<uint8_t*>(m->stage_f32) + (size_t)((n * 4 + 255) / 256 * 256);
+    TRY(mft_memcpy_h2d(raw, src, (size_t)n * 2, m->stream));
+    TRY(mft_cast_bf16_to_f32(raw, m->stage_f32, n, m->stream));
+    TRY(install_rows(m, p, m->stage_f32, 0, p.rows));
+    TRY(finish_param(m, p));
+    return sync();
+}
+
 extern "C" int32_t mft_model_lora_count(const mft_model_t* m) { return m ? (int32_t)m->loras.size() : 0; }
 extern "C" int32_t mft_model_lora_shape(const mft_model_t* m, int32_t idx, int64_t* rows, int64_t* cols) {
     MFT_CHECK_ARG(m && idx >= 0 && idx < (int)m->loras.size() && rows && cols, "mft_model_lora_shape: bad argument");

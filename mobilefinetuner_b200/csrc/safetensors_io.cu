@@ -224,7 +224,10 @@ int32_t read_f32(const mft_safetensors* h, const std::string& name, float* out, 
     if (it == h->tensors.end()) return fail(MFT_ERR_INVALID_ARG, "safetensors: no tensor named " + name);
     const TensorEntry& e = it->second;
     int64_t n = 1;
-    for (int64_t d : e.shape) n *= d;
+    for (int64_t d : e.shape) {      // a header is untrusted input: no negative extents, no product that wraps
+        if (d < 0 || (d > 0 && n > (int64_t)(1ull << 40) / d)) return fail(MFT_ERR_INVALID_ARG, "safetensors: implausible shape of " + name);
+        n *= d;
+    }
     const int es = dtype_size(e.dtype);
     if (!(e.dtype == "F32" || e.dtype == "F16" || e.dtype == "BF16")) return fail(MFT_ERR_UNSUPPORTED, "safetensors: " + name + " has dtype " + e.dtype + " (F32, F16 or BF16 expected)");
     if ((uint64_t)n * es != e.end - e.begin) return fail(MFT_ERR_INVALID_ARG, "safetensors: byte size of " + name + " does not match its shape");
@@ -250,6 +253,28 @@ int32_t read_f32(const mft_safetensors* h, const std::string& name, float* out, 
         for (int64_t r = 0; r < R; ++r)
             for (int64_t c = 0; c < Cc; ++c) out[c * R + r] = value(r * Cc + c);
     }
+    return MFT_OK;
+}
+
+// The stored bytes of a tensor, unconverted.
+int32_t read_raw(const mft_safetensors* h, const std::string& name, std::vector<uint8_t>& raw, int64_t expect_elems) {
+    auto it = h->tensors.find(name);
+    if (it == h->tensors.end()) return fail(MFT_ERR_INVALID_ARG, "safetensors: no tensor named " + name);
+    const TensorEntry& e = it->second;
+    int64_t n = 1;
+    for (int64_t d : e.shape) {
+        if (d < 0 || (d > 0 && n > (int64_t)(1ull << 40) / d)) return fail(MFT_ERR_INVALID_ARG, "safetensors: implausible shape of " + name);
+        n *= d;
+    }
+    const int es = dtype_size(e.dtype);
+    if (es <= 0 || (uint64_t)n * es != e.end - e.begin) return fail(MFT_ERR_INVALID_ARG, "safetensors: byte size of " + name + " does not match its shape");
+    if (expect_elems >= 0 && n != expect_elems) return fail(MFT_ERR_INVALID_ARG, "safetensors: " + name + " has " + std::to_string(n) + " elements, " + std::to_string(expect_elems) + " expected");
+    std::ifstream f(h->files[(size_t)e.file].path, std::ios::binary);
+    if (!f) return fail(MFT_ERR_INVALID_ARG, "safetensors: cannot reopen " + h->files[(size_t)e.file].path);
+    f.seekg((std::streamoff)(h->files[(size_t)e.file].data_offset + e.begin));
+    raw.resize((size_t)n * es);
+    f.read(reinterpret_cast<char*>(raw.data()), (std::streamsize)raw.size());
+    if (!f) return fail(MFT_ERR_INVALID_ARG, "safetensors: short read of " + name);
     return MFT_OK;
 }
 
@@ -452,6 +477,7 @@ extern "C" int32_t mft_model_load_safetensors(mft_model_t* m, const char* path_o
     if (int32_t s = mft_safetensors_open(path_or_dir, &h)) return s;
     std::unique_ptr<mft_safetensors> guard(h);
     std::vector<float> host;
+    std::vector<uint8_t> raw;
     for (size_t i = 0; i < m->params.size(); ++i) {
         const ParamInfo& p = m->params[i];
         HfKey k = hf_key_of(m, p);
@@ -459,12 +485,20 @@ extern "C" int32_t mft_model_load_safetensors(mft_model_t* m, const char* path_o
         // GPT-2 checkpoints come with or without the "transformer." prefix
         if (m->cfg.family == MFT_FAMILY_GPT2 && !h->tensors.count(k.key) && h->tensors.count("transformer." + k.key)) k.key = "transformer." + k.key;
         if (!h->tensors.count(k.key)) return fail(MFT_ERR_INVALID_ARG, "safetensors: checkpoint has no tensor " + k.key + " (parameter " + p.name + ")");
+        const TensorEntry& entry = h->tensors[k.key];
+        if (k.transpose) {                                  // HF Linear weight [out, in]
+            if (entry.shape.size() != 2 || entry.shape[0] != p.cols || entry.shape[1] != p.rows)
+                return fail(MFT_ERR_INVALID_ARG, "safetensors: shape of " + k.key + " does not fit parameter " + p.name);
+        }
+        if (entry.dtype == "BF16") {
+            // the stored bits are what the device keeps: no f32 detour on the host
+            if (int32_t s = read_raw(h, k.key, raw, p.rows * p.cols)) return s;
+            const int32_t st = mft_model_set_param_host_bf16(m, (int32_t)i, raw.data(), k.transpose ? 1 : 0);
+            if (st == MFT_OK) continue;
+            if (st != MFT_ERR_UNSUPPORTED) return st;       // larger than the staging area: the f32 path below chunks it
+        }
         host.resize((size_t)(p.rows * p.cols));
         if (int32_t s = read_f32(h, k.key, host.data(), k.transpose, p.rows * p.cols)) return s;
-        if (k.transpose) {
-            const auto& sh = h->tensors[k.key].shape;       // HF Linear weight [out, in]
-            if (sh[0] != p.cols || sh[1] != p.rows) return fail(MFT_ERR_INVALID_ARG, "safetensors: shape of " + k.key + " does not fit parameter " + p.name);
-        }
         if (int32_t s = mft_model_set_param_host(m, (int32_t)i, host.data())) return s;
     }
     return MFT_OK;
