@@ -83,8 +83,11 @@ class ClockSampler:
                         reasons.add(n)
             except Exception:
                 pass
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+        # "under load": samples drawing at least 60 % of the largest power seen (a run of short launches with host
+        # synchronisation in between leaves the GPU idle, at idle clocks, in most samples)
+        busy = [c for c, w in zip(sm, power) if w >= 0.6 * max(power)] if power else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(busy), "samples_total": len(sm), "reasons": sorted(reasons)}
 
 
 def profiled_traffic_bytes(spec_name: str, tokens: int):

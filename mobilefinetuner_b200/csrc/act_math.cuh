@@ -24,9 +24,13 @@ __device__ __forceinline__ void gelu_tanh_both(float x, float& val, float& grad)
 __device__ __forceinline__ float gelu_tanh_fast(float x) {
     return 0.5f * x * (1.0f + tanh_fast(0.7978845608f * (x + 0.044715f * x * x * x)));
 }
+// logistic function from the hardware exponential and reciprocal (two special-function instructions; an IEEE
+// division costs ~10 more instructions per element, which shows in the GEMM epilogues that fuse the gating).
+// Relative error ~2^-21, far below the bf16 rounding of the result; exp overflow gives 1 / inf = 0, the right limit.
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 // act = f(gate) * up with f = gelu (geglu != 0) or silu
 __device__ __forceinline__ float glu_fwd(bool geglu, float g, float u) {
-    return geglu ? gelu_tanh_fast(g) * u : g / (1.0f + __expf(-g)) * u;
+    return geglu ? gelu_tanh_fast(g) * u : g * sigmoid_fast(g) * u;
 }
 __device__ __forceinline__ void glu_bwd(bool geglu, float d, float g, float u, float& dg, float& du) {
     if (geglu) {
@@ -35,7 +39,7 @@ __device__ __forceinline__ void glu_bwd(bool geglu, float d, float g, float u, f
         dg = d * u * grad;
         du = d * val;
     } else {
-        const float s = 1.0f / (1.0f + __expf(-g));
+        const float s = sigmoid_fast(g);
         dg = d * u * (s * (1.0f + g * (1.0f - s)));
         du = d * g * s;
     }

@@ -121,8 +121,7 @@ __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __n
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             if (KIND == MFT_ACT_GELU) o[j] = gelu_tanh_fast(g[j]);
-            else if (KIND == MFT_ACT_SWIGLU) o[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
-            else o[j] = gelu_tanh_fast(g[j]) * u[j];
+            else o[j] = glu_fwd(KIND == MFT_ACT_GEGLU, g[j], u[j]);
         }
         store8(y + r * cols + c, o);
     }
@@ -149,15 +148,8 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_
                 float val, grad;
                 gelu_tanh_both(g[j], val, grad);
                 dg[j] = d[j] * grad;
-            } else if (KIND == MFT_ACT_SWIGLU) {
-                float s = 1.0f / (1.0f + __expf(-g[j]));
-                dg[j] = d[j] * u[j] * (s * (1.0f + g[j] * (1.0f - s)));
-                du[j] = d[j] * g[j] * s;
             } else {
-                float val, grad;
-                gelu_tanh_both(g[j], val, grad);
-                dg[j] = d[j] * u[j] * grad;
-                du[j] = d[j] * val;
+                glu_bwd(KIND == MFT_ACT_GEGLU, d[j], g[j], u[j], dg[j], du[j]);     // the same code as the GEMM epilogue that fuses it
             }
         }
         store8(dgate + r * ld + c, dg);
