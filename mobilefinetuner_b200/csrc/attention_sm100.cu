@@ -874,7 +874,8 @@ bool tc_shape_ok(int hd) { return hd == 64 || hd == 128 || hd == 256; }
 
 template <int HD>
 int32_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdParams& p, dim3 grid, cudaStream_t stream) {
-    static bool configured = false;
+    static PerDeviceFlag configured_on;           // function attributes are per device
+    bool& configured = configured_on.here();
     if (!configured) {
         if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dim<HD>::FWD_SMEM), "attention smem attribute")) return s;
         configured = true;
@@ -885,7 +886,8 @@ int32_t launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 }
 template <int HD>
 int32_t launch_dq(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMap& mk, const CUtensorMap& mv, const BwdParams& p, dim3 grid, cudaStream_t stream) {
-    static bool configured = false;
+    static PerDeviceFlag configured_on;           // function attributes are per device
+    bool& configured = configured_on.here();
     if (!configured) {
         if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqDim<HD>::SMEM), "attention smem attribute")) return s;
         configured = true;
@@ -897,7 +899,8 @@ int32_t launch_dq(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMa
 template <int HD>
 int32_t launch_dkv(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMap& mk, const CUtensorMap& mv, const BwdParams& p, int seq, int n_heads, int batch,
                    cudaStream_t stream) {
-    static bool configured = false;
+    static PerDeviceFlag configured_on;           // function attributes are per device
+    bool& configured = configured_on.here();
     if (!configured) {
         if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dkv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, KvDim<HD>::SMEM), "attention smem attribute")) return s;
         configured = true;

@@ -10,6 +10,17 @@
 
 namespace mft {
 
+// One flag per device for set-up that CUDA keeps per device (cudaFuncSetAttribute): `here()` is the current device's.
+struct PerDeviceFlag {
+    bool v[64] = {};
+    bool& here() {
+        int d = 0;
+        cudaGetDevice(&d);
+        return v[(d >= 0 && d < 64) ? d : 0];
+    }
+};
+
+
 // Thread-local last-error message plus the process-wide launch counter.
 void set_error(const std::string& msg);
 void count_launch(int n = 1);

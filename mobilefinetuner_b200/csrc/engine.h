@@ -164,7 +164,7 @@ struct mft_model {
     // kernels).  The forward counterpart (gating in the gate|up GEMM's epilogue) is built and tested but off: its three
     // boxes per 64 columns make the epilogue the bound (0.77 ms against 0.45 + 0.11 ms at Gemma-3-1B widths);
     // MFT_FUSE_GLU=2 turns it on as well.
-    bool fuse_glu = true, fuse_glu_fwd = false;
+    bool fuse_glu = true, fuse_glu_fwd = true;
     bool fuse_norms = true;          // Gemma: post-norm + residual + pre-norm pairs in one kernel (MFT_FUSE_NORMS=0: separate calls)
     bool ce_onepass = true;          // training steps use mft_lmhead_ce_fused (MFT_CE_ONEPASS=0 selects the two-sweep pair)
     float* stage_f32 = nullptr; int64_t stage_floats = 0;   // upload staging

@@ -337,7 +337,28 @@ static EncodeTiledFn get_encode() {
 
 // Tensor map over a row-major bf16 matrix [rows, cols] (row stride ld elements),
 // box = {64 columns, box_rows rows}, 128-byte swizzle, zero fill outside.
+// A tensor map is a pure function of (type, base, extents, stride, box): encoding one costs a driver call of a
+// microsecond or two, and a GEMM launch needs three to six.  Each host thread keeps the maps it has encoded in a small
+// direct-mapped table; a map stays valid when its memory is freed and handed out again (it holds an address and a
+// geometry, nothing else).
+struct TmapKey {
+    const void* base; int64_t rows, cols, ld; int32_t box_rows, kind;
+    bool operator==(const TmapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && kind == o.kind; }
+};
+struct TmapSlot { TmapKey key; CUtensorMap map; bool used; };
+constexpr int TMAP_SLOTS = 2048;
+static TmapSlot* tmap_slot(const TmapKey& k) {
+    thread_local std::vector<TmapSlot> table(TMAP_SLOTS, TmapSlot{{nullptr, 0, 0, 0, 0, 0}, {}, false});
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) >> 4;
+    h = (h ^ (uint64_t)k.rows * 0x9E3779B97F4A7C15ull) * 0xBF58476D1CE4E5B9ull;
+    h = (h ^ (uint64_t)k.cols * 0x94D049BB133111EBull ^ (uint64_t)k.ld * 0xD6E8FEB86659FD93ull ^ (uint64_t)(k.box_rows * 7 + k.kind)) * 0x9E3779B97F4A7C15ull;
+    return &table[(size_t)((h >> 40) % TMAP_SLOTS)];
+}
+
 int32_t make_tmap_bf16(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    const TmapKey key{base, rows, cols, ld, box_rows, 0};
+    TmapSlot* slot = tmap_slot(key);
+    if (slot->used && slot->key == key) { *map = slot->map; return MFT_OK; }
     EncodeTiledFn enc = get_encode();
     if (!enc) return fail(MFT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return fail(MFT_ERR_INVALID_ARG, "GEMM operand base must be 16-byte aligned");
@@ -350,11 +371,15 @@ int32_t make_tmap_bf16(CUtensorMap* map, const void* base, int64_t rows, int64_t
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(MFT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    slot->key = key; slot->map = *map; slot->used = true;
     return MFT_OK;
 }
 
 // Tensor map over a row-major f32 matrix [rows, cols]: box = {32 columns, 32 rows}, 128-byte swizzle.
 int32_t make_tmap_f32_out(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+    const TmapKey key{base, rows, cols, ld, 32, 1};
+    TmapSlot* slot = tmap_slot(key);
+    if (slot->used && slot->key == key) { *map = slot->map; return MFT_OK; }
     EncodeTiledFn enc = get_encode();
     if (!enc) return fail(MFT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -365,6 +390,7 @@ int32_t make_tmap_f32_out(CUtensorMap* map, const void* base, int64_t rows, int6
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(MFT_ERR_CUDA, "cuTensorMapEncodeTiled (f32 output) failed with code " + std::to_string((int)r));
+    slot->key = key; slot->map = *map; slot->used = true;
     return MFT_OK;
 }
 
@@ -383,7 +409,8 @@ template <int BN, int EPI>
 static int32_t launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2, const CUtensorMap& md,
                            GemmParams p, cudaStream_t stream) {
     using Cfg = GemmCfg<BN>;
-    static bool configured = false;
+    static PerDeviceFlag configured_on;           // function attributes are per device
+    bool& configured = configured_on.here();
     if (!configured) {
         if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm smem attr")) return s;
         configured = true;

@@ -266,7 +266,8 @@ template <int EPI, int BN2>
 int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2, const CUtensorMap& md,
                const CUtensorMap& mx, GemmParams p, cudaStream_t stream) {
     using Cfg = PairCfg<EPI, BN2>;
-    static bool configured = false;
+    static PerDeviceFlag configured_on;           // function attributes are per device
+    bool& configured = configured_on.here();
     if (!configured) {
         if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_2cta_kernel<EPI, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm 2cta smem attr")) return s;
         configured = true;

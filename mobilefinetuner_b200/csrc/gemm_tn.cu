@@ -308,7 +308,8 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
     }
     dim3 grid((unsigned)tiles_p, (unsigned)tiles_q, (unsigned)splits);
     constexpr int smem = (int)(sizeof(__nv_bfloat16) * TN_STAGES * TN_TC * (TN_US + TN_VS));
-    static bool configured = false;
+    static PerDeviceFlag configured_on;           // function attributes are per device
+    bool& configured = configured_on.here();
     if (!configured) {
         if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tn smem attr")) return s;
         configured = true;
