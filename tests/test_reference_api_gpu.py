@@ -32,19 +32,45 @@ def test_reference_unit_test_passes_on_gpu(name):
     assert r.returncode == 0, f"{name} failed:\n{r.stdout[-3000:]}\n{r.stderr[-2000:]}"
 
 
-def test_reference_gpt2_cli_builds_unchanged_and_trains(tmp_path):
-    """examples/gpt2_small_lora_finetune `train --synthetic_smoke`: GPT2Model + LoraInjector + the program's own
-    forward -> lm_cross_entropy -> backward -> Adam loop.  The library's launch report must show the tensor-core GEMM
-    and the fused attention / loss kernels, not the generic fp32 operators."""
+# example, program, extra arguments, the file the smoke run leaves behind (relative to its working directory)
+CLI_SMOKES = [
+    ("gpt2_small_lora_finetune", "train", ["--lora_out", "adapter.safetensors"], "adapter.safetensors"),
+    ("gpt2_medium_lora_finetune", "train", ["--lora_out", "adapter.safetensors"], "adapter.safetensors"),
+    ("qwen_lora_finetune", "train_wikitext", ["--output_dir", "out"], "out/lora_weights.bin"),
+    ("gemma_3_270m_lora_finetune", "train", ["--output_dir", "out"], "out/gemma_lora_smoke.safetensors"),
+    ("gemma_3_1b_pt_lora_finetune", "train", ["--output_dir", "out"], "out/gemma_lora_smoke.safetensors"),
+]
+CLI_OTHERS = [("gpt2_small_lora_finetune", t) for t in ("eval_mmlu", "eval_ppl", "train_full")] + \
+             [("gpt2_medium_lora_finetune", t) for t in ("eval_mmlu", "eval_ppl")] + \
+             [("gemma_3_270m_lora_finetune", "eval_mmlu_gemma"), ("gemma_3_1b_pt_lora_finetune", "eval_mmlu_gemma")]
+
+
+@pytest.mark.parametrize("example,prog,extra,artifact", CLI_SMOKES, ids=[c[0] for c in CLI_SMOKES])
+def test_reference_cli_builds_unchanged_and_trains(tmp_path, example, prog, extra, artifact):
+    """The reference's example programs (examples/*/src, built unchanged against this repository's `operators` target
+    by `make -C oracle cli`) in their `--synthetic_smoke` mode: model class + LoRA injection + the program's own
+    forward -> lm_cross_entropy -> backward -> clip -> Adam loop.  The library's launch report must show the
+    tensor-core GEMM and the fused attention / loss kernels, not the generic fp32 operators."""
     from parity import require_built
-    exe = require_built(ROOT / "oracle" / "_ref" / "cli" / "gpt2_small_train", "the reference's GPT-2 example built against this repository's operators target")
+    exe = require_built(ROOT / "oracle" / "_ref" / "cli" / example / prog, f"the reference's {example} built against this repository's operators target")
     report = tmp_path / "launches.txt"
     env = dict(os.environ, MFT_LAUNCH_REPORT=str(report), LD_LIBRARY_PATH=str(ROOT / "mobilefinetuner_b200") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
-    out = tmp_path / "adapter.safetensors"
-    r = subprocess.run([str(exe), "--synthetic_smoke", "--smoke_steps", "3", "--lora_out", str(out)], capture_output=True, text=True, timeout=300, env=env, cwd=tmp_path)
+    r = subprocess.run([str(exe), "--synthetic_smoke", "--smoke_steps", "3"] + extra, capture_output=True, text=True, timeout=300, env=env, cwd=tmp_path)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
-    assert "[PASS]" in r.stdout
+    assert "[PASS]" in r.stdout, r.stdout[-2000:]
+    out = tmp_path / artifact
     assert out.exists() and out.stat().st_size > 0
     names = report.read_text()
     assert "gemm_nt" in names and "attn_" in names, names
     assert "matmul_f32" not in names, names
+
+
+@pytest.mark.parametrize("example,prog", CLI_OTHERS, ids=[f"{e}-{t}" for e, t in CLI_OTHERS])
+def test_reference_evaluation_programs_build_and_start(tmp_path, example, prog):
+    """The evaluation / full-fine-tuning programs need tokenizer files, checkpoints and datasets that do not exist
+    offline: they must build, load the kernel library and answer --help with their usage text."""
+    from parity import require_built
+    exe = require_built(ROOT / "oracle" / "_ref" / "cli" / example / prog, f"the reference's {example} {prog} built against this repository's operators target")
+    env = dict(os.environ, LD_LIBRARY_PATH=str(ROOT / "mobilefinetuner_b200") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+    r = subprocess.run([str(exe), "--help"], capture_output=True, text=True, timeout=120, env=env, cwd=tmp_path)
+    assert r.returncode == 0 and "--" in (r.stdout + r.stderr), (r.returncode, r.stdout[-1500:], r.stderr[-1500:])
