@@ -397,15 +397,16 @@ def run_attention_sweep(args):
         flush = torch.empty(64 << 20, dtype=torch.float32, device="cuda")     # 256 MiB > L2: written between timed launches
 
         def timed(fn):
-            ms = []
+            # all iterations are queued before the one synchronisation, so the GPU stays busy (and at its clocks)
+            # through the timed region; each timed call sits between its own pair of events
+            evs = []
             for i in range(args.warmup + args.steps):
                 flush.fill_(float(i))
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(); fn(); e1.record()
-                torch.cuda.synchronize()
-                if i >= args.warmup:
-                    ms.append(e0.elapsed_time(e1))
-            return statistics.median(ms)
+                evs.append((e0, e1))
+            torch.cuda.synchronize()
+            return statistics.median(e0.elapsed_time(e1) for e0, e1 in evs[args.warmup:])
         t_f = timed(lambda: O.attention_fwd(q, k, v, 0.125, 0))
         t_b = timed(lambda: O.attention_bwd(q, k, v, o, d_o, lse, 0.125, 0))
         pairs = B * nh * S * (S + 1) / 2

@@ -385,7 +385,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // S/dP buffer g and 16 tensor-memory columns for its dS.
 constexpr int DQ_BN = 32;
 constexpr int DQ_KST = 4, DQ_VST = 2;              // K / V stages (K is held until the tile's dQ product, V only for dP)
-constexpr int DQ_THREADS = 64 + 2 * 256 + 64;     // TMA warp, S issuer, 16 element-wise warps, dP issuer, dQ issuer
+// Threads: TMA warp, S issuer, GROUPS x 8 element-wise warps, dP issuer, dQ issuer.  With two groups, group g works on
+// the tiles t = g, g + 2, ... (tensor-memory buffer g); head_dim 64 runs ONE group that takes every tile (buffer t & 1):
+// 384 threads, 58 KB of shared memory and 256 tensor-memory columns per CTA let two CTAs share an SM, and the second
+// CTA's independent chain covers the first one's barrier / tensor-memory latencies.
 constexpr int DQ_S_COL = 0, DQ_DP_COL = 64, DQ_ACC_COL = 128;
 template <int HD>
 struct DqDim {
@@ -393,6 +396,9 @@ struct DqDim {
     static constexpr int SMEM = 2 * Dim<HD>::Q_BYTES + (DQ_KST + DQ_VST) * KV_BYTES + 256 + 4 * BM * 4;
     static constexpr int DS_COL = 128 + HD;            // dS as the A operand of the dQ product: 16 columns (32 keys as bf16 pairs) per group
     static constexpr int TMEM = HD == 64 ? 256 : 512;
+    static constexpr int GROUPS = HD == 64 ? 1 : 2;
+    static constexpr int THREADS = 64 + GROUPS * 256 + 64;
+    static constexpr int W_DP = 2 + 8 * GROUPS, W_DQ = 3 + 8 * GROUPS;   // warps of the dP and dQ issuers
 };
 
 
@@ -413,11 +419,12 @@ struct BwdParams {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(DQ_THREADS, 1)
+__global__ void __launch_bounds__(DqDim<HD>::THREADS, DqDim<HD>::GROUPS == 1 ? 2 : 1)
 attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                   const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
     dep_trigger();
     constexpr int CH = Dim<HD>::CH, Q_BYTES = Dim<HD>::Q_BYTES, DQ_KV_BYTES = DqDim<HD>::KV_BYTES, DQ_DS_COL = DqDim<HD>::DS_COL;
+    constexpr int GROUPS = DqDim<HD>::GROUPS, W_DP = DqDim<HD>::W_DP, W_DQ = DqDim<HD>::W_DQ;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* q_smem = smem_raw;
     uint8_t* do_smem = q_smem + Q_BYTES;
@@ -486,8 +493,8 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 for (int c = 0; c < CH; ++c) tma_load_2d(v_smem + vs * DQ_KV_BYTES + c * (DQ_BN * 128), &map_v, &v_full[vs], kvh * p.v_col0_stride + c * 64, row);
             }
         }
-    } else if (warp == 1 || warp == 18) {
-        // ------------------------------------------------ MMA issuers 1 and 2: S = Q K^T (warp 1), dP = dO V^T (warp 18)
+    } else if (warp == 1 || warp == W_DP) {
+        // ------------------------------------------------ MMA issuers 1 and 2: S = Q K^T (warp 1), dP = dO V^T (warp W_DP)
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_bf16_f32(BM, DQ_BN);
             const bool is_s = warp == 1;
@@ -511,7 +518,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 umma_commit(&sdp_full[g]);            // two arrivals complete it: S and dP
             }
         }
-    } else if (warp == 19) {
+    } else if (warp == W_DQ) {
         // ------------------------------------------------ MMA issuer 3: dQ += dS K
         if (lane == 0) {
             constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, HD) | IDESC_B_MN;
@@ -531,7 +538,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
         }
     } else {
-        const int g = (warp - 2) >> 3;                 // element-wise group: tiles t = g, g + 2, ...
+        const int g0 = (warp - 2) >> 3;                // element-wise group: tiles t = g0, g0 + GROUPS, ...
         const int q4 = warp & 3;
         const int half = ((warp - 2) >> 2) & 1;        // which 16 of the tile's 32 keys
         const int r = q4 * 32 + lane;
@@ -546,7 +553,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             // each, the partial sums meet in shared memory; thread (group 0, half 0) stores the row's delta for the
             // dK/dV kernel
             {
-                const int part = g * 2 + half;
+                const int part = g0 * 2 + half;
                 const __nv_bfloat16* orow = p.o + (long long)b * p.so_b + (long long)i * p.so_s + (long long)h * p.so_h + part * 64;
                 const __nv_bfloat16* drow = p.d_o + (long long)b * p.sdo_b + (long long)i * p.sdo_s + (long long)h * p.sdo_h + part * 64;
                 float a8[8][8], c8[8][8];
@@ -561,13 +568,14 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
             asm volatile("bar.sync 1, 512;" ::: "memory");     // the 16 element-wise warps
             const float dsum = (delta_smem[r] + delta_smem[BM + r]) + (delta_smem[2 * BM + r] + delta_smem[3 * BM + r]);
-            if (g == 0 && half == 0) p.delta_out[sidx] = dsum;
+            if (g0 == 0 && half == 0) p.delta_out[sidx] = dsum;
             dlt = dsum;
         } else {
             dlt = p.delta[sidx];
         }
         bool ok = true;
-        for (int t = g; t < n_tiles && ok; t += 2) {
+        for (int t = g0; t < n_tiles && ok; t += GROUPS) {
+            const int g = t & 1;                       // tensor-memory buffer of the tile
             const uint32_t ph = (t >> 1) & 1;
             const int j0 = (jb_lo + t) * DQ_BN + half * 16;
             if (!mbar_wait(&sdp_full[g], ph, abort_flag)) { ok = false; break; }
@@ -599,7 +607,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tc_fence_before();
             mbar_arrive(&ds_full[g]);
         }
-        if (g == 0 && ok && mbar_wait(acc_done, 0, abort_flag)) {
+        if (g0 == 0 && ok && mbar_wait(acc_done, 0, abort_flag)) {
             tc_fence_after();
             __nv_bfloat16* row = p.dq + (long long)b * p.sq_b + (long long)i * p.sq_s + (long long)h * p.sq_h + half * (HD / 2);
 #pragma unroll 1
@@ -640,7 +648,11 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 constexpr int KV_BQ = 32;                              // queries per tile
 constexpr int KV_STATS_BYTES = 2 * KV_BQ * 4;          // lse, delta of the tile's queries
 constexpr int KV_STAGES = 3;                           // Q / dO stages: the load of tile t+2 must not wait for the MMAs of tile t
-constexpr int DKV_THREADS = 64 + 2 * 256 + 64;         // TMA warp, S^T issuer, 16 element-wise warps, dP^T issuer, dV/dK issuer
+// Threads: TMA warp, S^T issuer, GROUPS x 8 element-wise warps, dP^T issuer, dV/dK issuer.  head_dim 64 runs one group
+// and keeps P^T / dS^T IN PLACE (each element-wise thread writes its 16 bf16 probabilities over the first 8 of the 16
+// S^T columns it has just read, dS^T likewise over dP^T): 256 tensor-memory columns, 384 threads and 57 KB of shared
+// memory per CTA, so that two CTAs share an SM.  The S^T / dP^T buffers are then free again only when the tile's
+// dV / dK products have read them.
 constexpr int KV_S_COL = 0, KV_DP_COL = 64, KV_DK_COL = 128;
 template <int HD>
 struct KvDim {
@@ -650,6 +662,11 @@ struct KvDim {
     static constexpr int SMEM = 2 * Dim<HD>::Q_BYTES + KV_STAGES * 2 * Q_BYTES + KV_STAGES * KV_STATS_BYTES + 256;
     static constexpr int DV_COL = KV_DK_COL + ACC;
     static constexpr int PDS_COL = KV_DK_COL + 2 * ACC;   // per group 32 columns: P^T (16: 32 queries as bf16 pairs) | dS^T (16)
+    static constexpr bool INPLACE = HD == 64;
+    static constexpr int TMEM = INPLACE ? 256 : 512;
+    static constexpr int GROUPS = HD == 64 ? 1 : 2;
+    static constexpr int THREADS = 64 + GROUPS * 256 + 64;
+    static constexpr int W_DP = 2 + 8 * GROUPS, W_ACC = 3 + 8 * GROUPS;   // warps of the dP^T and dV/dK issuers
 };
 
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
@@ -660,12 +677,14 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem, u
 }
 
 template <int HD>
-__global__ void __launch_bounds__(DKV_THREADS, 1)
+__global__ void __launch_bounds__(KvDim<HD>::THREADS, KvDim<HD>::GROUPS == 1 ? 2 : 1)
 attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const BwdParams p) {
     dep_trigger();
     constexpr int CH = Dim<HD>::CH, Q_BYTES = Dim<HD>::Q_BYTES, KV_Q_BYTES = KvDim<HD>::Q_BYTES, ACC = KvDim<HD>::ACC, NPART = KvDim<HD>::NPART;
     constexpr int KV_DV_COL = KvDim<HD>::DV_COL, KV_PDS_COL = KvDim<HD>::PDS_COL;
+    constexpr bool INPLACE = KvDim<HD>::INPLACE;
+    constexpr int GROUPS = KvDim<HD>::GROUPS, W_DP = KvDim<HD>::W_DP, W_ACC = KvDim<HD>::W_ACC;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* k_smem = smem_raw;                            // [128 keys x 256], 4 chunks
     uint8_t* v_smem = k_smem + Q_BYTES;
@@ -708,7 +727,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         fence_barrier_init();
         tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_do); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v);
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, KvDim<HD>::TMEM); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -734,8 +753,8 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (++st == KV_STAGES) { st = 0; sph ^= 1; }
             }
         }
-    } else if (warp == 1 || warp == 18) {
-        // ------------------------------------------------ MMA issuers 1 and 2: S^T = K Q^T (warp 1), dP^T = V dO^T (warp 18)
+    } else if (warp == 1 || warp == W_DP) {
+        // ------------------------------------------------ MMA issuers 1 and 2: S^T = K Q^T (warp 1), dP^T = V dO^T (warp W_DP)
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_bf16_f32(BM, KV_BQ);
             const bool is_s = warp == 1;
@@ -746,7 +765,8 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int g = t & 1;
                 const uint32_t ph = (t >> 1) & 1;
-                if (!mbar_wait(&qdo_full[st], sph, abort_flag) || !mbar_wait(&sdp_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
+                // in place: the buffer also holds P^T / dS^T of tile t - 2 until that tile's dV / dK products are done
+                if (!mbar_wait(&qdo_full[st], sph, abort_flag) || !mbar_wait(INPLACE ? &pds_free[g] : &sdp_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t bd = smem_desc_sw128(smem_u32((is_s ? q_smem : do_smem) + st * KV_Q_BYTES));
                 const uint32_t tmem_d = tmem_base + (is_s ? KV_S_COL : KV_DP_COL) + g * KV_BQ;
@@ -760,7 +780,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (++st == KV_STAGES) { st = 0; sph ^= 1; }
             }
         }
-    } else if (warp == 19) {
+    } else if (warp == W_ACC) {
         // ------------------------------------------------ MMA issuer 3: dV += P^T dO, dK += dS^T Q (this CTA's 128 columns)
         if (lane == 0) {
             constexpr uint32_t idesc_acc = idesc_bf16_f32(BM, ACC) | IDESC_B_MN;
@@ -772,15 +792,19 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (!mbar_wait(&pds_full[g], ph, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 // A operands P^T / dS^T come from tensor memory (8 columns per 16 queries), B operands dO / Q MN-major from the stage
-                const uint32_t pa = tmem_base + KV_PDS_COL + g * 32;
+                // separate: P^T at pa + {0, 8}, dS^T at pa + 16 + {0, 8}.  In place: P^T in the S^T buffer at +{0, 16}
+                // (the first 8 columns of each half's 16), dS^T in the dP^T buffer likewise
+                const uint32_t pa = tmem_base + (INPLACE ? KV_S_COL + g * KV_BQ : KV_PDS_COL + g * 32);
+                const uint32_t da = INPLACE ? tmem_base + KV_DP_COL + g * KV_BQ : pa + 16;
+                constexpr int A_STEP = INPLACE ? 16 : 8;
                 const uint64_t dod = smem_desc_mn_sw128(smem_u32(do_smem + st * KV_Q_BYTES + hh * (ACC / 64) * (KV_BQ * 128)), KV_BQ * 128);
                 const uint64_t qd = smem_desc_mn_sw128(smem_u32(q_smem + st * KV_Q_BYTES + hh * (ACC / 64) * (KV_BQ * 128)), KV_BQ * 128);
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                    umma_bf16_ts(tmem_base + KV_DV_COL, pa + 8 * j, dod + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
+                    umma_bf16_ts(tmem_base + KV_DV_COL, pa + A_STEP * j, dod + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                    umma_bf16_ts(tmem_base + KV_DK_COL, pa + 16 + 8 * j, qd + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
+                    umma_bf16_ts(tmem_base + KV_DK_COL, da + A_STEP * j, qd + (uint64_t)(j * (2048 / 16)), idesc_acc, (t | j) != 0 ? 1u : 0u);
                 umma_commit(&qdo_empty[st]);
                 umma_commit(&pds_free[g]);
                 if (t == n_tiles - 1) umma_commit(acc_done);
@@ -788,8 +812,8 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
         }
     } else {
-        // ------------------------------------------------ element-wise groups (warps 2..17): key row per thread pair
-        const int g = (warp - 2) >> 3;
+        // ------------------------------------------------ element-wise groups (warps 2 .. 1 + 8 * GROUPS): key row per thread pair
+        const int g0 = (warp - 2) >> 3;                // tiles t = g0, g0 + GROUPS, ...
         const int q4 = warp & 3;
         const int half = ((warp - 2) >> 2) & 1;        // which 16 of the tile's 32 queries
         const int r = q4 * 32 + lane;                  // key within the tile
@@ -797,7 +821,8 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
         const float sl2 = p.scale * LOG2E;
         bool ok = true;
-        for (int t = g; t < n_tiles && ok; t += 2) {
+        for (int t = g0; t < n_tiles && ok; t += GROUPS) {
+            const int g = t & 1;                       // tensor-memory buffer of the tile
             const uint32_t ph = (t >> 1) & 1;
             const int i0 = (qs_lo + t) * KV_BQ + half * 16;
             if (!mbar_wait(&sdp_full[g], ph, abort_flag)) { ok = false; break; }
@@ -807,7 +832,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tmem_ld_32x16(lane_addr + KV_DP_COL + g * KV_BQ + half * 16, dr);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(&sdp_free[g]);
+            if (!INPLACE) mbar_arrive(&sdp_free[g]);
             // lse / delta of the 16 queries (the stage's loads completed before S^T was issued)
             const float* st_l = stats + (t % KV_STAGES) * 2 * KV_BQ + half * 16;
             const float* st_d = st_l + KV_BQ;
@@ -827,16 +852,23 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 pk[x >> 1] = *reinterpret_cast<const uint32_t*>(&w0);
                 dk[x >> 1] = *reinterpret_cast<const uint32_t*>(&w1);
             }
-            if (!mbar_wait(&pds_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            tmem_st_32x8(lane_addr + KV_PDS_COL + g * 32 + half * 8, pk);
-            tmem_st_32x8(lane_addr + KV_PDS_COL + g * 32 + 16 + half * 8, dk);
+            if (INPLACE) {
+                // over the first 8 of the 16 columns this thread has just read (nobody else touches them; the buffer
+                // is this tile's until its dV / dK products complete pds_free, which the S^T / dP^T issuers wait for)
+                tmem_st_32x8(lane_addr + KV_S_COL + g * KV_BQ + half * 16, pk);
+                tmem_st_32x8(lane_addr + KV_DP_COL + g * KV_BQ + half * 16, dk);
+            } else {
+                if (!mbar_wait(&pds_free[g], ph ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                tmem_st_32x8(lane_addr + KV_PDS_COL + g * 32 + half * 8, pk);
+                tmem_st_32x8(lane_addr + KV_PDS_COL + g * 32 + 16 + half * 8, dk);
+            }
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&pds_full[g]);
         }
         // ---- epilogue (group 0): add this CTA's 128 columns of dK (scaled) and dV into the f32 scratch
-        if (g == 0 && ok && mbar_wait(acc_done, 0, abort_flag)) {
+        if (g0 == 0 && ok && mbar_wait(acc_done, 0, abort_flag)) {
             tc_fence_after();
             const long long half_elems = (long long)gridDim.z * p.seq * p.n_kv * HD;
             float* krow = p.dkv_acc + (((long long)b * p.seq + j) * p.n_kv + kvh) * HD + hh * ACC + half * (ACC / 2);
@@ -864,7 +896,7 @@ attn_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, MFT_ERR_TIMEOUT);
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, KvDim<HD>::TMEM);
     }
 }
 
@@ -892,7 +924,7 @@ int32_t launch_dq(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMa
         if (int32_t s = check_cuda(cudaFuncSetAttribute(attn_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqDim<HD>::SMEM), "attention smem attribute")) return s;
         configured = true;
     }
-    launch_dep(attn_dq_tc_kernel<HD>, dim3(grid), dim3(DQ_THREADS), (size_t)(DqDim<HD>::SMEM), stream, mq, md, mk, mv, p);
+    launch_dep(attn_dq_tc_kernel<HD>, dim3(grid), dim3(DqDim<HD>::THREADS), (size_t)(DqDim<HD>::SMEM), stream, mq, md, mk, mv, p);
     MFT_LAUNCH_CHECK("attn_dq_tc");
     return MFT_OK;
 }
@@ -906,7 +938,7 @@ int32_t launch_dkv(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorM
         configured = true;
     }
     dim3 grid((unsigned)(seq / BM), (unsigned)(KvDim<HD>::NPART * n_heads), (unsigned)batch);
-    launch_dep(attn_dkv_tc_kernel<HD>, dim3(grid), dim3(DKV_THREADS), (size_t)(KvDim<HD>::SMEM), stream, mq, md, mk, mv, p);
+    launch_dep(attn_dkv_tc_kernel<HD>, dim3(grid), dim3(KvDim<HD>::THREADS), (size_t)(KvDim<HD>::SMEM), stream, mq, md, mk, mv, p);
     MFT_LAUNCH_CHECK("attn_dkv_tc");
     return MFT_OK;
 }
