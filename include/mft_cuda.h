@@ -304,7 +304,7 @@ int32_t mft_glu_linear_bwd(int32_t kind, const void* dy_bf16, int64_t lddy, cons
  * (window <= 0 or i - j < window).  lse is f32 [batch, n_heads, seq].
  * head_dim 64 / 128 / 256 with seq a multiple of 128 and token-major tensors
  * (stride_b == seq * stride_s) runs on tensor-memory (tcgen05) kernels
- * (head_dim 64 / 128 only from seq 1024 forward / 512 backward on, where they
+ * (head_dim 64 / 128 only from seq 512 forward / 256 backward on, where they
  * are the faster ones); other shapes of those head sizes on mma.sync kernels,
  * any other even head_dim <= 256 on generic kernels, all with the same results
  * to bf16 rounding.  MFT_ATTN_TC=0 in the environment selects the mma.sync

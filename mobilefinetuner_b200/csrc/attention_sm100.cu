@@ -949,9 +949,9 @@ int32_t launch_dkv(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorM
 int32_t attn_fwd_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
     static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
     if (!enabled || !tc_shape_ok(hd) || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
-    // measured (batch 8, 14 / 2 heads of 64): at 256 and 512 tokens the mma.sync forward is as fast or faster
-    // (0.022 / 0.042 ms against 0.026 / 0.045 ms), from 1024 tokens on this kernel wins (0.096 against 0.108 ms, 1.6 x at 4096)
-    if (hd != 256 && a.seq < 1024 && enabled < 2) return MFT_ERR_UNSUPPORTED;
+    // measured (batch 8, 14 / 2 heads of 64): at 256 tokens the mma.sync forward is faster (0.0205 against 0.0225 ms),
+    // from 512 tokens on this kernel wins (0.039 against 0.041 ms, 2.3 x at 4096); MFT_ATTN_TC=2 forces it
+    if (hd != 256 && a.seq < 512 && enabled < 2) return MFT_ERR_UNSUPPORTED;
     if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq)) return MFT_ERR_UNSUPPORTED;
     if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.so.stride_s % 8 || a.so.stride_h % 8 || a.so.stride_b % 8) return MFT_ERR_UNSUPPORTED;
     if ((int64_t)a.batch * a.seq >= (1ll << 31)) return MFT_ERR_UNSUPPORTED;
@@ -973,8 +973,8 @@ int32_t attn_fwd_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
 int32_t attn_dq_sm100(const AttnParams& a, int hd, bool compute_delta, cudaStream_t stream) {
     static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
     if (!enabled || !tc_shape_ok(hd) || a.seq % BM != 0 || !device_status_word()) return MFT_ERR_UNSUPPORTED;
-    // the backward kernels win from 512 tokens on (0.129 against 0.164 ms at 512, 2 x at 4096); MFT_ATTN_TC=2 forces them
-    if (hd != 256 && a.seq < 512 && enabled < 2) return MFT_ERR_UNSUPPORTED;
+    // the backward kernels win from 256 tokens on (0.064 against 0.073 ms at 256, 2.6 x at 4096); MFT_ATTN_TC=2 forces them
+    if (hd != 256 && a.seq < 256 && enabled < 2) return MFT_ERR_UNSUPPORTED;
     if (compute_delta && hd != 256) return MFT_ERR_UNSUPPORTED;
     if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq) || !token_major(a.sdo, a.seq)) return MFT_ERR_UNSUPPORTED;
     if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.sdo.stride_h % 8) return MFT_ERR_UNSUPPORTED;
@@ -1004,8 +1004,8 @@ int32_t attn_dq_sm100(const AttnParams& a, int hd, bool compute_delta, cudaStrea
 int32_t attn_dkv_sm100(const AttnParams& a, int hd, cudaStream_t stream) {
     static const int enabled = [] { const char* e = std::getenv("MFT_ATTN_TC"); return e ? std::atoi(e) : 1; }();
     if (!enabled || !tc_shape_ok(hd) || a.seq % BM != 0 || !a.dkv_acc || !device_status_word()) return MFT_ERR_UNSUPPORTED;
-    // the backward kernels win from 512 tokens on (0.129 against 0.164 ms at 512, 2 x at 4096); MFT_ATTN_TC=2 forces them
-    if (hd != 256 && a.seq < 512 && enabled < 2) return MFT_ERR_UNSUPPORTED;
+    // the backward kernels win from 256 tokens on (0.064 against 0.073 ms at 256, 2.6 x at 4096); MFT_ATTN_TC=2 forces them
+    if (hd != 256 && a.seq < 256 && enabled < 2) return MFT_ERR_UNSUPPORTED;
     if (!token_major(a.sq, a.seq) || !token_major(a.sk, a.seq) || !token_major(a.sv, a.seq) || !token_major(a.sdo, a.seq)) return MFT_ERR_UNSUPPORTED;
     if (a.sq.stride_h % 8 || a.sk.stride_h % 8 || a.sv.stride_h % 8 || a.sdo.stride_h % 8) return MFT_ERR_UNSUPPORTED;
     if ((int64_t)a.batch * a.seq >= (1ll << 31) || 2 * a.n_heads > 65535) return MFT_ERR_UNSUPPORTED;
