@@ -1,6 +1,7 @@
 """Single-kernel microbenchmarks (CUDA-event timing) for the kernels of the LoRA step.
 
     python -m mobilefinetuner_b200.microbench gemm --m 4096 --n 13824 --k 1152 [--k2 32] [--f32] [--iters 20]
+    python -m mobilefinetuner_b200.microbench glu --m 16384 --n 6912 --k 1152 --k2 16      # gated MLP: fused launches against GEMM + activation
     python -m mobilefinetuner_b200.microbench attn --batch 8 --heads 4 --kv-heads 1 --seq 2048 --head-dim 256 [--window 512]
     python -m mobilefinetuner_b200.microbench tn --t 16384 --p 1152 --q 64
     python -m mobilefinetuner_b200.microbench ce --t 4096 --hidden 1152 --vocab 262144
@@ -35,7 +36,7 @@ def _time(fn, iters, warm=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemm", "attn", "tn", "ce"])
+    ap.add_argument("kind", choices=["gemm", "glu", "attn", "tn", "ce"])
     ap.add_argument("--no-split", action="store_true", help="attn: one CTA per KV group in the dK/dV kernel")
     ap.add_argument("--m", type=int, default=16384); ap.add_argument("--n", type=int, default=13824); ap.add_argument("--k", type=int, default=1152)
     ap.add_argument("--k2", type=int, default=0); ap.add_argument("--f32", action="store_true")
@@ -57,6 +58,29 @@ def main():
         ms = _time(lambda: O.gemm_nt(A, B, a2=A2, b2=B2, out=D), a.iters)
         fl = 2.0 * a.m * a.n * (a.k + a.k2)
         out.update(m=a.m, n=a.n, k=a.k, k2=a.k2, ms=ms, tflops=fl / ms / 1e9)
+    elif a.kind == "glu":
+        # gated MLP around the down projection: --n is the intermediate width, --k the hidden width, --k2 the LoRA rank
+        # columns of each projection.  Fused launches against GEMM + stand-alone activation kernel.
+        from . import _lib as L
+        M, I, K, r = a.m, a.n, a.k, a.k2
+        kind = L.ACT_GEGLU
+        x = torch.randn(M, K, device=dev, generator=g).to(BF)
+        w = (torch.randn(2 * I, K, device=dev, generator=g) * 0.05).to(BF)
+        xa = torch.randn(M, 64, device=dev, generator=g).to(BF)[:, :2 * r] if r else None
+        bp = (torch.randn(2 * I, 64, device=dev, generator=g) * 0.05).to(BF)[:, :2 * r] if r else None
+        gu = O.gemm_nt(x, w, a2=xa, b2=bp)
+        dy = torch.randn(M, K, device=dev, generator=g).to(BF)
+        wd = (torch.randn(I, K, device=dev, generator=g) * 0.05).to(BF)
+        a2 = torch.randn(M, 64, device=dev, generator=g).to(BF)[:, :r] if r else None
+        b2 = (torch.randn(I, 64, device=dev, generator=g) * 0.05).to(BF)[:, :r] if r else None
+        d_act = O.gemm_nt(dy, wd, a2=a2, b2=b2)
+        out.update(m=M, inter=I, k=K, k2=r,
+                   fwd_fused_ms=_time(lambda: O.glu_linear_fwd(kind, x, w, xa=xa, b_nk=bp), a.iters),
+                   fwd_gemm_ms=_time(lambda: O.gemm_nt(x, w, a2=xa, b2=bp), a.iters),
+                   fwd_act_ms=_time(lambda: O.act_fwd(kind, gu[:, :I], gu[:, I:]), a.iters),
+                   bwd_fused_ms=_time(lambda: O.glu_linear_bwd(kind, dy, wd, gu, a2=a2, b2=b2), a.iters),
+                   bwd_gemm_ms=_time(lambda: O.gemm_nt(dy, wd, a2=a2, b2=b2), a.iters),
+                   bwd_act_ms=_time(lambda: O.act_bwd(kind, d_act, gu[:, :I], gu[:, I:]), a.iters))
     elif a.kind == "attn":
         b, nh, nkv, s, hd = a.batch, a.heads, a.kv_heads, a.seq, a.head_dim
         q = torch.randn(b, s, nh, hd, device=dev, generator=g).to(BF).permute(0, 2, 1, 3)
