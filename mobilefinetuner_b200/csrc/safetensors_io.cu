@@ -523,8 +523,12 @@ extern "C" int32_t mft_model_save_lora_safetensors(mft_model_t* m, const char* p
     std::vector<const char*> name_ptrs, meta_k, meta_v;
     std::vector<const float*> data_ptrs;
     for (size_t i = 0; i < names.size(); ++i) { name_ptrs.push_back(names[i].c_str()); data_ptrs.push_back(bufs[i].data()); }
+    // the metadata lists the targets sorted for Gemma adapters (GemmaLoraInjector::save_lora_safetensors,
+    // graph/gemma_lora_injector.cpp:218) and in injection order otherwise (LoraSaver::join_targets, graph/lora_saver.cpp:74-82)
+    std::vector<std::string> listed = targets;
+    if (m->cfg.family == MFT_FAMILY_GEMMA) std::sort(listed.begin(), listed.end());
     std::string joined;
-    for (size_t t = 0; t < targets.size(); ++t) joined += (t ? "," : "") + targets[t];
+    for (size_t t = 0; t < listed.size(); ++t) joined += (t ? "," : "") + listed[t];
     const std::string rank = std::to_string(m->cfg.lora_rank), alpha = fmt_float(m->cfg.lora_alpha), dropout = "0";
     const char* keys[4] = {"rank", "alpha", "dropout", "targets"};
     const char* vals[4] = {rank.c_str(), alpha.c_str(), dropout.c_str(), joined.c_str()};
