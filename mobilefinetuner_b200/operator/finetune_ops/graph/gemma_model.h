@@ -16,26 +16,18 @@ namespace ops {
 
 namespace detail { class EngineModel; }
 
-struct GemmaTextConfig {
-    int vocab_size = 262144;
-    int hidden_size = 640;
-    int intermediate_size = 2048;
-    int num_hidden_layers = 18;
-    int num_attention_heads = 4;
-    int num_key_value_heads = 1;
-    int head_dim = 256;
+struct GemmaTextConfig {                       // defaults: Gemma-3-270M; names are config.json's
+    int vocab_size = 262144, hidden_size = 640, intermediate_size = 2048;
+    int num_hidden_layers = 18, num_attention_heads = 4, num_key_value_heads = 1, head_dim = 256;
     int max_position_embeddings = 32768;
-    int sliding_window = 512;
-    bool attention_bias = false;
-    bool use_bidirectional_attention = false;
-    bool use_cache = true;
+    int sliding_window = 512;                  // tokens a "sliding_attention" layer looks back
+    bool attention_bias = false, use_bidirectional_attention = false, use_cache = true;
     float attention_dropout = 0.0f;
     float rms_norm_eps = 1e-6f;
-    float query_pre_attn_scalar = 256.0f;
+    float query_pre_attn_scalar = 256.0f;      // attention scale = 1 / sqrt(this)
     float attn_logit_softcapping = 0.0f;       // parsed, never applied (as in the reference's graph)
     float final_logit_softcapping = 0.0f;
-    float rope_theta = 1000000.0f;
-    float rope_local_base_freq = 10000.0f;
+    float rope_theta = 1000000.0f, rope_local_base_freq = 10000.0f;      // global / sliding layers
     std::string hidden_activation = "gelu_pytorch_tanh";
     std::vector<std::string> layer_types;      // "sliding_attention" / "full_attention" per layer; empty = all sliding
     static GemmaTextConfig from_pretrained(const std::string& model_dir);

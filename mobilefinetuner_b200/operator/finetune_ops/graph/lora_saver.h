@@ -12,23 +12,22 @@
 
 namespace ops {
 
-struct LoRAState {
-    int rank = 8;
-    float alpha = 16.0f;
-    float dropout = 0.0f;
-    bool split_qkv = true;
+struct LoRAState {                    // what an adapter file holds
+    int rank = 8; float alpha = 16.0f, dropout = 0.0f;
+    bool split_qkv = true;            // q / k / v adapters (true) or one fused qkv adapter
     std::vector<LoraTarget> targets;
-    std::unordered_map<std::string, TensorPtr> tensors;
-    bool compatible_with(const GPT2Model& model) const;
+    std::unordered_map<std::string, TensorPtr> tensors;      // key -> f32 tensor as stored
+    bool compatible_with(const GPT2Model& model) const;      // layer count and shapes fit the model
 };
 
 class LoraSaver {
 public:
-    static void save_safetensors(const std::string& path, const GPT2Model& model, const LoraSpec& spec);
-    static LoRAState load_safetensors(const std::string& path);
-    static void attach_from_state(GPT2Model& model, const LoRAState& state);
+    // keys: "layer.<i>.<target>.lora_<A|B>"
     static std::string make_peft_key(int layer, const std::string& target, const std::string& ab);
     static bool parse_peft_key(const std::string& key, int& layer, std::string& target, std::string& ab);
+    static LoRAState load_safetensors(const std::string& path);
+    static void save_safetensors(const std::string& path, const GPT2Model& model, const LoraSpec& spec);
+    static void attach_from_state(GPT2Model& model, const LoRAState& state);     // injects and fills the adapters
 };
 
 }  // namespace ops

@@ -19,16 +19,17 @@ struct ModelAssetPaths {
 
 struct ModelArchitectureSpec {
     ModelFamily family = ModelFamily::Unknown;
-    std::string model_type;
+    std::string model_type;                           // config.json "model_type" as written
     ModelAssetPaths assets;
-    std::vector<std::string> default_lora_targets;
+    std::vector<std::string> default_lora_targets;    // HuggingFace module names the family's CLIs adapt by default
     bool tie_word_embeddings = false;
 };
 
 class ModelRegistry {
 public:
-    static ModelArchitectureSpec inspect_pretrained(const std::string& model_dir);   // throws without a config.json or for an unknown model_type
     static ModelFamily infer_family(const std::string& model_dir);
+    // throws without a config.json or for an unknown model_type
+    static ModelArchitectureSpec inspect_pretrained(const std::string& model_dir);
 };
 
 }  // namespace ops

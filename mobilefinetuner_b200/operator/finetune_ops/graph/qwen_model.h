@@ -14,21 +14,14 @@ namespace ops {
 
 namespace detail { class EngineModel; }
 
-struct QwenConfig {
-    int vocab_size = 151936;
-    int hidden_size = 896;
-    int intermediate_size = 4864;
-    int num_hidden_layers = 24;
-    int num_attention_heads = 14;
-    int num_key_value_heads = 2;
+struct QwenConfig {                    // defaults: Qwen2.5-0.5B; names are config.json's
+    int vocab_size = 151936, hidden_size = 896, intermediate_size = 4864;
+    int num_hidden_layers = 24, num_attention_heads = 14, num_key_value_heads = 2;
     int max_position_embeddings = 32768;
-    float rms_norm_eps = 1e-6f;
-    float rope_theta = 1000000.0f;
+    float rms_norm_eps = 1e-6f, rope_theta = 1000000.0f;
     std::string hidden_act = "silu";
-    int bos_token_id = -1;
-    int eos_token_id = -1;
-    int pad_token_id = -1;
-    static QwenConfig from_pretrained(const std::string& config_path);
+    int bos_token_id = -1, eos_token_id = -1, pad_token_id = -1;
+    static QwenConfig from_pretrained(const std::string& config_path);     // reads a config.json
 };
 
 struct QwenBlock {
@@ -49,18 +42,20 @@ public:
     QwenModel(const QwenModel&) = delete;
     QwenModel& operator=(const QwenModel&) = delete;
 
-    TensorPtr forward_hidden(const TensorPtr& input_ids, const TensorPtr& attention_mask = nullptr);   // [B,S,hidden] after the final norm
-    TensorPtr lm_head(const TensorPtr& hidden);                                                           // hidden . embed^T
-    TensorPtr forward(const TensorPtr& input_ids, const TensorPtr& attention_mask = nullptr);
+    const QwenConfig& config() const { return config_; }
     const TensorPtr& embedding_weight() const { return embed_tokens_; }
+    void assign_weight(const std::string& key, const TensorPtr& tensor);      // key: the reference's internal name
+    void freeze_base();
+    std::vector<TensorPtr> parameters() const;               // embed, final norm, 12 tensors per layer
 
     // A ~ U(-0.01, 0.01) from mt19937(seed), B = 0, on q and v (qv_only) or q, k, v, o.
     void init_lora(int rank = 8, float alpha = 16.0f, float dropout = 0.05f, bool qv_only = false, uint64_t seed = 42);
     std::vector<TensorPtr> get_lora_parameters() const;      // per layer: q, v, k, o (A then B)
-    std::vector<TensorPtr> parameters() const;               // embed, final norm, 12 tensors per layer
-    void freeze_base();
-    void assign_weight(const std::string& key, const TensorPtr& tensor);
-    const QwenConfig& config() const { return config_; }
+
+    // all three are deferred values served by the device step engine
+    TensorPtr forward(const TensorPtr& input_ids, const TensorPtr& attention_mask = nullptr);           // logits [B,S,V]
+    TensorPtr forward_hidden(const TensorPtr& input_ids, const TensorPtr& attention_mask = nullptr);    // [B,S,hidden] after the final norm
+    TensorPtr lm_head(const TensorPtr& hidden);                                                            // hidden . embed^T
 
 private:
     QwenConfig config_;

@@ -11,26 +11,22 @@
 
 namespace ops {
 
-struct AutoTrainerConfig {
-    float learning_rate = 2e-4f;
-    float weight_decay = 0.0f;
-    float max_grad_norm = 1.0f;
-    int ignore_index = -100;
+struct AutoTrainerConfig {            // field order as in the reference (aggregate initialisation)
+    float learning_rate = 2e-4f, weight_decay = 0.0f;
+    float max_grad_norm = 1.0f;       // <= 0: no clipping
+    int ignore_index = -100;          // label value that is not scored
 };
 
-struct AutoTrainStepResult {
-    float loss = 0.0f;
-    int trainable_tensor_count = 0;
-};
+struct AutoTrainStepResult { float loss = 0.0f; int trainable_tensor_count = 0; };
 
 class AutoTrainer {
-public:
-    AutoTrainer(AutoModelForCausalLM& model, const AutoTrainerConfig& config = AutoTrainerConfig());
-    AutoTrainStepResult train_step(const TensorPtr& input_ids, const TensorPtr& attention_mask, const TensorPtr& labels);
-private:
     AutoModelForCausalLM& model_;
     AutoTrainerConfig config_;
-    std::unique_ptr<Adam> optimizer_;
+    std::unique_ptr<Adam> optimizer_;     // created on the first step, over model_.trainable_parameters()
+public:
+    AutoTrainer(AutoModelForCausalLM& model, const AutoTrainerConfig& config = AutoTrainerConfig());
+    // ids / mask / labels: int32 [B, S]; the mask may be null or right-padded
+    AutoTrainStepResult train_step(const TensorPtr& input_ids, const TensorPtr& attention_mask, const TensorPtr& labels);
 };
 
 }  // namespace ops

@@ -17,22 +17,18 @@ class WikiText2Dataset;
 struct Batch;
 namespace detail { class StepDriver; }
 
-struct GemmaTrainerConfig {
-    float learning_rate = 2e-4f;
-    float weight_decay = 0.0f;
-    float adam_beta1 = 0.9f;
-    float adam_beta2 = 0.999f;
-    float adam_eps = 1e-8f;
+struct GemmaTrainerConfig {                // field order as in the reference
+    // optimizer (the reference's L2-style Adam)
+    float learning_rate = 2e-4f, weight_decay = 0.0f;
+    float adam_beta1 = 0.9f, adam_beta2 = 0.999f, adam_eps = 1e-8f;
     int num_epochs = 3;
     float max_grad_norm = 1.0f;
-    std::string lr_scheduler = "linear";
+    std::string lr_scheduler = "linear";   // or "cosine"; both after a linear warm-up over warmup_ratio of the updates
     float warmup_ratio = 0.03f;
-    int logging_steps = 10;
-    int eval_steps = 100;
+    int logging_steps = 10, eval_steps = 100;
     std::string output_dir = "./gemma_lora_ckpt";
-    int max_steps = -1;
-    int micro_batch_size = 1;
-    int grad_accum_steps = 1;
+    int max_steps = -1;                    // > 0: stop after this many optimizer steps
+    int micro_batch_size = 1, grad_accum_steps = 1;
     int save_every = 0;                    // > 0: save the adapters every N optimizer steps
     bool dump_embedding = false;           // accepted; the fused device path has no embedding tensor to dump
     int dump_embedding_step = 1;
@@ -40,24 +36,21 @@ struct GemmaTrainerConfig {
 };
 
 class GemmaLoRATrainer {
+    GemmaModel& model_;
+    GemmaLoraInjector& injector_;
+    WikiText2Dataset &train_data_, &eval_data_;
+    GemmaTrainerConfig config_;
+    std::unique_ptr<detail::StepDriver> driver_;      // accumulation window, clip rule, schedule, Adam on the device
+    std::chrono::time_point<std::chrono::steady_clock> start_;
+    bool started_ = false;
 public:
     GemmaLoRATrainer(GemmaModel& model, GemmaLoraInjector& injector, WikiText2Dataset& train_data, WikiText2Dataset& eval_data,
                      const GemmaTrainerConfig& config);
     ~GemmaLoRATrainer();
-    void train();
-    float train_step(const Batch& batch);
-    float evaluate();
+    void train();                               // epochs over train_data_, evaluation / checkpoints as configured
+    float train_step(const Batch& batch);       // one micro-batch; -1 inside an accumulation window, else the window's mean loss
+    float evaluate();                           // mean loss over eval_data_
     void save_lora(const std::string& path);
-
-private:
-    GemmaModel& model_;
-    GemmaLoraInjector& injector_;
-    WikiText2Dataset& train_data_;
-    WikiText2Dataset& eval_data_;
-    GemmaTrainerConfig config_;
-    std::unique_ptr<detail::StepDriver> driver_;
-    std::chrono::time_point<std::chrono::steady_clock> start_;
-    bool started_ = false;
 };
 
 }  // namespace ops
