@@ -1,0 +1,81 @@
+"""Synthetic assets for running the reference's command-line programs end to end: a small GPT-2 checkpoint directory
+(config.json, model.safetensors with HuggingFace keys, a byte-level vocab.json with no merges), a WikiText-style text
+file and a LoRA adapter file in the layout of the reference's LoraSaver.  Everything is seeded; nothing is downloaded."""
+import json
+from pathlib import Path
+
+import numpy as np
+
+from test_safetensors_cpu import write_container
+
+
+def bytes_to_unicode():
+    """The byte -> printable character table of GPT-2's byte-level BPE."""
+    bs = list(range(ord("!"), ord("~") + 1)) + list(range(161, 173)) + list(range(174, 256))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    return dict(zip(bs, (chr(c) for c in cs)))
+
+
+GPT2_TINY = dict(n_layer=2, n_embd=64, n_head=4, n_positions=128, vocab_size=50257)
+
+
+def write_gpt2_checkpoint(root: Path, seed: int = 7, scale: float = 0.08) -> dict:
+    """Returns the tensors written (HF key -> f32 array, Linear weights [in, out] as GPT-2 stores them)."""
+    c = GPT2_TINY
+    root.mkdir(parents=True, exist_ok=True)
+    (root / "config.json").write_text(json.dumps({"model_type": "gpt2", "n_layer": c["n_layer"], "n_embd": c["n_embd"], "n_head": c["n_head"],
+                                                  "n_positions": c["n_positions"], "n_ctx": c["n_positions"], "vocab_size": c["vocab_size"],
+                                                  "layer_norm_epsilon": 1e-5}))
+    vocab = {ch: i for i, (_, ch) in enumerate(sorted(bytes_to_unicode().items()))}     # token id = byte value
+    vocab["<|endoftext|>"] = 50256
+    (root / "vocab.json").write_text(json.dumps(vocab))
+    (root / "merges.txt").write_text("#version: 0.2\n")
+    rng = np.random.default_rng(seed)
+    E, V, P = c["n_embd"], c["vocab_size"], c["n_positions"]
+    t = {"wte.weight": rng.normal(0, scale, (V, E)), "wpe.weight": rng.normal(0, scale, (P, E)),
+         "ln_f.weight": 1 + rng.normal(0, 0.05, E), "ln_f.bias": rng.normal(0, 0.02, E)}
+    for i in range(c["n_layer"]):
+        h = f"h.{i}."
+        t[h + "ln_1.weight"] = 1 + rng.normal(0, 0.05, E); t[h + "ln_1.bias"] = rng.normal(0, 0.02, E)
+        t[h + "ln_2.weight"] = 1 + rng.normal(0, 0.05, E); t[h + "ln_2.bias"] = rng.normal(0, 0.02, E)
+        t[h + "attn.c_attn.weight"] = rng.normal(0, scale, (E, 3 * E)); t[h + "attn.c_attn.bias"] = rng.normal(0, 0.02, 3 * E)
+        t[h + "attn.c_proj.weight"] = rng.normal(0, scale, (E, E)); t[h + "attn.c_proj.bias"] = rng.normal(0, 0.02, E)
+        t[h + "mlp.c_fc.weight"] = rng.normal(0, scale, (E, 4 * E)); t[h + "mlp.c_fc.bias"] = rng.normal(0, 0.02, 4 * E)
+        t[h + "mlp.c_proj.weight"] = rng.normal(0, scale, (4 * E, E)); t[h + "mlp.c_proj.bias"] = rng.normal(0, 0.02, E)
+    t = {k: np.ascontiguousarray(v, np.float32) for k, v in t.items()}
+    write_container(root / "model.safetensors", {k: ("F32", v) for k, v in t.items()}, {"format": "pt"})
+    return t
+
+
+def write_text_corpus(root: Path, seed: int = 11, n_lines: int = 60):
+    """wiki.{train,valid,test}.raw: lines of seeded pseudo-words (ASCII), a heading line now and then."""
+    rng = np.random.default_rng(seed)
+    words = ["".join(chr(97 + int(x)) for x in rng.integers(0, 26, int(rng.integers(2, 9)))) for _ in range(200)]
+    root.mkdir(parents=True, exist_ok=True)
+    for split in ("train", "valid", "test"):
+        lines = []
+        for i in range(n_lines):
+            if i % 15 == 0:
+                lines.append(f" = {words[int(rng.integers(0, 200))].capitalize()} = ")
+            lines.append(" " + " ".join(words[int(x)] for x in rng.integers(0, 200, int(rng.integers(8, 30)))) + " . ")
+        (root / f"wiki.{split}.raw").write_text("\n".join(lines) + "\n")
+
+
+def write_gpt2_adapter(path: Path, seed: int = 13, rank: int = 4, alpha: float = 8.0, scale: float = 0.5):
+    """Adapter on attn.proj, mlp.fc_in and mlp.fc_out of every layer: A [in, r], B [r, out], both non-zero."""
+    c = GPT2_TINY
+    E = c["n_embd"]
+    rng = np.random.default_rng(seed)
+    dims = {"attn.proj": (E, E), "mlp.fc_in": (E, 4 * E), "mlp.fc_out": (4 * E, E)}
+    t = {}
+    for i in range(c["n_layer"]):
+        for name, (din, dout) in dims.items():
+            t[f"layer.{i}.{name}.lora_A"] = ("F32", np.ascontiguousarray(rng.normal(0, scale, (din, rank)), np.float32))
+            t[f"layer.{i}.{name}.lora_B"] = ("F32", np.ascontiguousarray(rng.normal(0, scale, (rank, dout)), np.float32))
+    write_container(path, t, {"rank": str(rank), "alpha": str(alpha), "dropout": "0", "split_qkv": "true", "targets": "AttnProj,MlpFcIn,MlpFcOut"})

@@ -74,3 +74,43 @@ def test_reference_evaluation_programs_build_and_start(tmp_path, example, prog):
     env = dict(os.environ, LD_LIBRARY_PATH=str(ROOT / "mobilefinetuner_b200") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
     r = subprocess.run([str(exe), "--help"], capture_output=True, text=True, timeout=120, env=env, cwd=tmp_path)
     assert r.returncode == 0 and "--" in (r.stdout + r.stderr), (r.returncode, r.stdout[-1500:], r.stderr[-1500:])
+
+
+def _eval_ppl(exe, root, extra, env=None):
+    import re
+    r = subprocess.run([str(exe), "--data_root", str(root / "data"), "--split", "valid", "--seq_len", "64", "--batch_size", "4",
+                        "--pretrained_dir", str(root / "model")] + extra, capture_output=True, text=True, timeout=600, env=env, cwd=root)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    m = re.search(r"split=valid\s+tokens=(\d+)\s+nll=([0-9.]+)", r.stdout)
+    assert m, r.stdout[-2000:]
+    return int(m.group(1)), float(m.group(2))
+
+
+def test_reference_eval_ppl_end_to_end_against_the_reference_build(tmp_path):
+    """examples/gpt2_small_lora_finetune/src/eval_ppl.cpp, one source, two builds: linked with the reference's CPU
+    operators (oracle/_ref/ref_cli) and with this repository's `operators` target (oracle/_ref/cli).  Both read the same
+    synthetic checkpoint directory (config.json, model.safetensors, byte-level vocab.json), tokenize the same text with
+    the reference's tokenizer and dataset code, and report the corpus NLL - without an adapter, with an adapter file
+    attached, and with it merged into the base weights.  Token counts are integer work (equal); the NLL within bf16."""
+    from parity import require_built
+    import cli_assets as A
+    ours = require_built(ROOT / "oracle" / "_ref" / "cli" / "gpt2_small_lora_finetune" / "eval_ppl", "the reference's eval_ppl built against this repository's operators target")
+    ref = require_built(ROOT / "oracle" / "_ref" / "ref_cli" / "eval_ppl", "the reference's eval_ppl built on the reference's own operators")
+    A.write_gpt2_checkpoint(tmp_path / "model")
+    A.write_text_corpus(tmp_path / "data")
+    A.write_gpt2_adapter(tmp_path / "adapter.safetensors")
+    report = tmp_path / "launches.txt"
+    env = dict(os.environ, MFT_LAUNCH_REPORT=str(report), LD_LIBRARY_PATH=str(ROOT / "mobilefinetuner_b200") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+    adapter = ["--lora_path", str(tmp_path / "adapter.safetensors")]
+    got, want = {}, {}
+    for name, extra in (("base", []), ("attached", adapter + ["--lora_merge", "0"]), ("merged", adapter + ["--lora_merge", "1"])):
+        want[name] = _eval_ppl(ref, tmp_path, extra)
+        got[name] = _eval_ppl(ours, tmp_path, extra, env)
+        assert got[name][0] == want[name][0]                                  # scored tokens: exact
+        assert abs(got[name][1] - want[name][1]) <= 5e-3, (name, got[name], want[name])
+    shift_ref = want["attached"][1] - want["base"][1]
+    assert abs(shift_ref) > 0.03                                              # the adapter matters in this set-up
+    for name in ("attached", "merged"):
+        assert abs((got[name][1] - got["base"][1]) - shift_ref) <= 0.15 * abs(shift_ref), (got, want)
+    names = report.read_text()
+    assert "gemm_nt" in names and "matmul_f32" not in names, names
