@@ -112,5 +112,8 @@ def test_reference_eval_ppl_end_to_end_against_the_reference_build(tmp_path):
     assert abs(shift_ref) > 0.03                                              # the adapter matters in this set-up
     for name in ("attached", "merged"):
         assert abs((got[name][1] - got["base"][1]) - shift_ref) <= 0.15 * abs(shift_ref), (got, want)
-    names = report.read_text()
-    assert "gemm_nt" in names and "matmul_f32" not in names, names
+    # the report is the last run's (adapters merged): the forward ran the tensor-core GEMMs and the fused loss; the six
+    # fp32 matmuls are the merge itself (W += scale * A B per adapted linear, kept in fp32 on purpose)
+    names = dict(line.split() for line in report.read_text().splitlines() if line.strip())
+    assert int(names.get("gemm_nt_2cta", 0)) > 0 and int(names.get("ce_reduce", 0)) > 0, names
+    assert int(names.get("matmul_f32", 0)) <= 6, names
