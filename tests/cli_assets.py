@@ -79,3 +79,19 @@ def write_gpt2_adapter(path: Path, seed: int = 13, rank: int = 4, alpha: float =
             t[f"layer.{i}.{name}.lora_A"] = ("F32", np.ascontiguousarray(rng.normal(0, scale, (din, rank)), np.float32))
             t[f"layer.{i}.{name}.lora_B"] = ("F32", np.ascontiguousarray(rng.normal(0, scale, (rank, dout)), np.float32))
     write_container(path, t, {"rank": str(rank), "alpha": str(alpha), "dropout": "0", "split_qkv": "true", "targets": "AttnProj,MlpFcIn,MlpFcOut"})
+
+
+def read_container(path: Path) -> dict:
+    """F32 tensors of a safetensors file as name -> ndarray (metadata dropped)."""
+    import struct
+    raw = Path(path).read_bytes()
+    n = struct.unpack("<Q", raw[:8])[0]
+    header = json.loads(raw[8:8 + n])
+    out = {}
+    for name, e in header.items():
+        if name == "__metadata__":
+            continue
+        assert e["dtype"] == "F32", (name, e["dtype"])
+        a, b = e["data_offsets"]
+        out[name] = np.frombuffer(raw[8 + n + a:8 + n + b], np.float32).reshape(e["shape"]).copy()
+    return out

@@ -117,3 +117,57 @@ def test_reference_eval_ppl_end_to_end_against_the_reference_build(tmp_path):
     names = dict(line.split() for line in report.read_text().splitlines() if line.strip())
     assert int(names.get("gemm_nt_2cta", 0)) > 0 and int(names.get("ce_reduce", 0)) > 0, names
     assert int(names.get("matmul_f32", 0)) <= 6, names
+
+
+def test_reference_gpt2_train_end_to_end_against_the_reference_build(tmp_path):
+    """examples/gpt2_small_lora_finetune/src/main.cpp in its real (non-smoke) mode, one source, two builds.  Both load
+    the same synthetic checkpoint, resume from the same adapter file (so the start does not depend on a random
+    initialisation), read the same corpus through the reference's tokenizer / dataset code with the same seed, and
+    run four optimizer steps with the program's own loop: forward -> lm_cross_entropy -> backward -> its clip ->
+    Adam::step with its cosine schedule.  Compared: the per-step loss and gradient norm the program prints, and the
+    adapter file it saves."""
+    import re
+    import numpy as np
+    from parity import require_built
+    from conftest import cosine
+    import cli_assets as A
+    from cli_assets import read_container
+    ours = require_built(ROOT / "oracle" / "_ref" / "cli" / "gpt2_small_lora_finetune" / "train", "the reference's GPT-2 train built against this repository's operators target")
+    ref = require_built(ROOT / "oracle" / "_ref" / "ref_cli" / "train", "the reference's GPT-2 train built on the reference's own operators")
+    A.write_gpt2_checkpoint(tmp_path / "model")
+    A.write_text_corpus(tmp_path / "data")
+    A.write_gpt2_adapter(tmp_path / "adapter.safetensors")
+    lr = 2e-3
+    report = tmp_path / "launches.txt"
+    env = dict(os.environ, MFT_LAUNCH_REPORT=str(report), LD_LIBRARY_PATH=str(ROOT / "mobilefinetuner_b200") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+
+    def run(exe, out, env=None):
+        r = subprocess.run([str(exe), "--data_dir", "data", "--pretrained_dir", "model", "--resume_from", "adapter.safetensors", "--lora_out", out,
+                            "--epochs", "0", "--steps", "4", "--batch_size", "4", "--seq_len", "64", "--lr", str(lr), "--warmup_steps", "0",
+                            "--eval_interval", "0", "--log_interval", "1", "--save_every", "0", "--seed", "5"],
+                           capture_output=True, text=True, timeout=900, env=env, cwd=tmp_path)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+        steps = re.findall(r"\(global (\d+)/4\).*?loss ([0-9.]+).*?grad_norm ([0-9.]+).*?tokens (\d+)", r.stdout)
+        assert len(steps) == 4, r.stdout[-3000:]
+        return [(float(l), float(g), int(t)) for _, l, g, t in steps], read_container(tmp_path / out)
+
+    want_steps, want = run(ref, "out_ref.safetensors")
+    got_steps, got = run(ours, "out_ours.safetensors", env)
+    for (l0, g0, t0), (l1, g1, t1) in zip(want_steps, got_steps):
+        assert t0 == t1                                                       # tokens per step: integer work
+        assert abs(l1 - l0) <= 2e-3 * abs(l0), (want_steps, got_steps)
+        assert abs(g1 - g0) <= 0.03 * abs(g0) + 2e-3, (want_steps, got_steps)
+    before = read_container(tmp_path / "adapter.safetensors")
+    assert sorted(got) == sorted(want) == sorted(before)
+    moved = 0.0
+    for k in want:
+        a, b, p0 = got[k].ravel(), want[k].ravel(), before[k].ravel()
+        assert cosine(a, b) >= 0.999, k
+        moved = max(moved, float(np.abs(b - p0).max()))
+        ok = np.abs(a - b) <= 2e-2 * np.maximum(np.abs(b), lr)
+        assert ok.mean() >= 0.97, (k, float(ok.mean()))
+        da, db = a - p0, b - p0                                               # the four Adam updates themselves
+        assert cosine(da, db) >= 0.98, (k, cosine(da, db))
+    assert moved > lr                                                         # the run did train
+    names = dict(line.split() for line in report.read_text().splitlines() if line.strip())
+    assert int(names.get("gemm_nt_2cta", 0)) + int(names.get("gemm_nt", 0)) > 0 and "matmul_f32" not in names, names
