@@ -95,3 +95,56 @@ def read_container(path: Path) -> dict:
         a, b = e["data_offsets"]
         out[name] = np.frombuffer(raw[8 + n + a:8 + n + b], np.float32).reshape(e["shape"]).copy()
     return out
+
+
+QWEN_TINY = dict(num_hidden_layers=2, hidden_size=64, intermediate_size=128, num_attention_heads=4, num_key_value_heads=2, vocab_size=151936)
+
+
+def write_qwen_checkpoint(root: Path, seed: int = 17, scale: float = 0.08) -> dict:
+    """A Qwen2-style model directory: config.json, byte-level vocab.json / merges.txt, tokenizer.json with the
+    <|endoftext|> added token (id 151643, as the reference's tokenizer assumes), model.safetensors with HuggingFace keys
+    (Linear weights [out, in], q / k / v biases).  Returns the tensors written."""
+    c = QWEN_TINY
+    root.mkdir(parents=True, exist_ok=True)
+    H, I, V, nh, nkv = c["hidden_size"], c["intermediate_size"], c["vocab_size"], c["num_attention_heads"], c["num_key_value_heads"]
+    hd = H // nh
+    (root / "config.json").write_text(json.dumps({"model_type": "qwen2", "hidden_size": H, "intermediate_size": I, "num_hidden_layers": c["num_hidden_layers"],
+                                                  "num_attention_heads": nh, "num_key_value_heads": nkv, "vocab_size": V, "max_position_embeddings": 512,
+                                                  "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "hidden_act": "silu", "tie_word_embeddings": True,
+                                                  "eos_token_id": 151643, "bos_token_id": 151643}))
+    vocab = {ch: i for i, (_, ch) in enumerate(sorted(bytes_to_unicode().items()))}
+    (root / "vocab.json").write_text(json.dumps(vocab))
+    (root / "merges.txt").write_text("#version: 0.2\n")
+    (root / "tokenizer.json").write_text(json.dumps({"added_tokens": [{"id": 151643, "content": "<|endoftext|>", "single_word": False, "lstrip": False,
+                                                                       "rstrip": False, "normalized": False, "special": True}],
+                                                     "model": {"type": "BPE"}}))
+    rng = np.random.default_rng(seed)
+    t = {"model.embed_tokens.weight": rng.normal(0, scale, (V, H)), "model.norm.weight": 1 + rng.normal(0, 0.05, H)}
+    for i in range(c["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        t[p + "input_layernorm.weight"] = 1 + rng.normal(0, 0.05, H)
+        t[p + "post_attention_layernorm.weight"] = 1 + rng.normal(0, 0.05, H)
+        for name, out in (("q_proj", nh * hd), ("k_proj", nkv * hd), ("v_proj", nkv * hd)):
+            t[p + f"self_attn.{name}.weight"] = rng.normal(0, scale, (out, H))
+            t[p + f"self_attn.{name}.bias"] = rng.normal(0, 0.02, out)
+        t[p + "self_attn.o_proj.weight"] = rng.normal(0, scale, (H, nh * hd))
+        t[p + "mlp.gate_proj.weight"] = rng.normal(0, scale, (I, H))
+        t[p + "mlp.up_proj.weight"] = rng.normal(0, scale, (I, H))
+        t[p + "mlp.down_proj.weight"] = rng.normal(0, scale, (H, I))
+    t = {k: np.ascontiguousarray(v, np.float32) for k, v in t.items()}
+    write_container(root / "model.safetensors", {k: ("F32", v) for k, v in t.items()}, {"format": "pt"})
+    return t
+
+
+def read_lora_weights_bin(path: Path) -> list:
+    """The adapter dump of the reference's Qwen programs: int32 count, then per tensor int32 ndim, int64 dims, f32 data."""
+    import struct
+    raw = Path(path).read_bytes()
+    (n,), off, out = struct.unpack_from("<i", raw, 0), 4, []
+    for _ in range(n):
+        (nd,) = struct.unpack_from("<i", raw, off); off += 4
+        dims = struct.unpack_from(f"<{nd}q", raw, off); off += 8 * nd
+        cnt = int(np.prod(dims))
+        out.append(np.frombuffer(raw, np.float32, cnt, off).reshape(dims).copy()); off += 4 * cnt
+    assert off == len(raw)
+    return out

@@ -171,3 +171,50 @@ def test_reference_gpt2_train_end_to_end_against_the_reference_build(tmp_path):
     assert moved > lr                                                         # the run did train
     names = dict(line.split() for line in report.read_text().splitlines() if line.strip())
     assert int(names.get("gemm_nt_2cta", 0)) + int(names.get("gemm_nt", 0)) > 0 and "matmul_f32" not in names, names
+
+
+@pytest.mark.parametrize("loss_impl,accum", [("dense", 1), ("full_streaming", 2)])
+def test_reference_qwen_train_end_to_end_against_the_reference_build(tmp_path, loss_impl, accum):
+    """examples/qwen_lora_finetune/src/wikitext_main.cpp in its real mode, one source, two builds: Qwen2-style
+    checkpoint with HuggingFace keys ([out,in] linears, q/k/v biases) loaded through the reference's key mapper,
+    QwenModel::init_lora (seeded), the reference's Qwen tokenizer and dataset, and the program's own loop - the dense
+    path (forward -> lm_cross_entropy) and the streaming path (forward_hidden -> streaming_lm_cross_entropy) with two
+    micro-batches accumulated and the gradients scaled on the host before the clip.  Compared: the loss of every step
+    (step_metrics.csv), the gradient norm printed after the first step, and the adapters saved at the end."""
+    import re
+    import numpy as np
+    from parity import require_built
+    from conftest import cosine
+    import cli_assets as A
+    ours = require_built(ROOT / "oracle" / "_ref" / "cli" / "qwen_lora_finetune" / "train_wikitext", "the reference's Qwen train_wikitext built against this repository's operators target")
+    ref = require_built(ROOT / "oracle" / "_ref" / "ref_cli" / "qwen_train_wikitext", "the reference's Qwen train_wikitext built on the reference's own operators")
+    A.write_qwen_checkpoint(tmp_path / "qwen")
+    A.write_text_corpus(tmp_path / "data")
+    lr, steps = 2e-3, 4
+    env = dict(os.environ, LD_LIBRARY_PATH=str(ROOT / "mobilefinetuner_b200") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+
+    def run(exe, out, env=None):
+        r = subprocess.run([str(exe), "--model_dir", "qwen", "--data_dir", "data", "--seq_len", "64", "--batch_size", "4", "--grad_accum_steps", str(accum),
+                            "--max_steps", str(steps), "--lr", str(lr), "--lora_r", "4", "--lora_alpha", "8", "--qkvo", "--seed", "5",
+                            "--output_dir", out, "--loss_impl", loss_impl], capture_output=True, text=True, timeout=1200, env=env, cwd=tmp_path)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+        rows = (tmp_path / out / "step_metrics.csv").read_text().strip().splitlines()[1:]
+        g = re.search(r"grad L2 \(all LoRA params\) = ([0-9.eE+-]+)", r.stdout)
+        assert len(rows) == steps and g, r.stdout[-2000:]
+        return [float(x.split(",")[1]) for x in rows], float(g.group(1)), A.read_lora_weights_bin(tmp_path / out / "lora_weights.bin")
+
+    want_loss, want_g, want = run(ref, "out_ref")
+    got_loss, got_g, got = run(ours, "out_ours", env)
+    for a, b in zip(got_loss, want_loss):
+        assert abs(a - b) <= 2e-3 * abs(b), (got_loss, want_loss)
+    assert abs(got_g - want_g) <= 0.03 * want_g, (got_g, want_g)
+    assert len(got) == len(want) == 2 * 4 * A.QWEN_TINY["num_hidden_layers"]
+    moved = 0.0
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert a.shape == b.shape
+        a, b = a.ravel(), b.ravel()
+        moved = max(moved, float(np.abs(b).max()) if i % 2 else 0.0)          # B tensors start at zero
+        assert cosine(a, b) >= 0.999, i
+        ok = np.abs(a - b) <= 2e-2 * np.maximum(np.abs(b), lr)
+        assert ok.mean() >= 0.97, (i, float(ok.mean()))
+    assert moved > lr
