@@ -100,7 +100,7 @@ def read_container(path: Path) -> dict:
 QWEN_TINY = dict(num_hidden_layers=2, hidden_size=64, intermediate_size=128, num_attention_heads=4, num_key_value_heads=2, vocab_size=151936)
 
 
-def write_qwen_checkpoint(root: Path, seed: int = 17, scale: float = 0.08) -> dict:
+def write_qwen_checkpoint(root: Path, seed: int = 17, scale: float = 0.15) -> dict:
     """A Qwen2-style model directory: config.json, byte-level vocab.json / merges.txt, tokenizer.json with the
     <|endoftext|> added token (id 151643, as the reference's tokenizer assumes), model.safetensors with HuggingFace keys
     (Linear weights [out, in], q / k / v biases).  Returns the tensors written."""

@@ -221,6 +221,7 @@ def test_reference_qwen_train_end_to_end_against_the_reference_build(tmp_path, l
         stats.append((i, round(cosine(a, b), 5), round(float(np.linalg.norm(a - b) / np.linalg.norm(b)), 4)))
         if i % 2:
             moved = max(moved, float(np.abs(b).max()))
+    print("adapter tensors (index, cosine, relative L2 error):", stats)
     for i, c, rel in stats:
         assert c >= 0.99 and rel <= 0.15, stats
     assert moved > lr, stats
