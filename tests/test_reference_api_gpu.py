@@ -159,16 +159,16 @@ def test_reference_gpt2_train_end_to_end_against_the_reference_build(tmp_path):
         assert abs(g1 - g0) <= 0.03 * abs(g0) + 2e-3, (want_steps, got_steps)
     before = read_container(tmp_path / "adapter.safetensors")
     assert sorted(got) == sorted(want) == sorted(before)
-    moved = 0.0
-    for k in want:
+    moved, stats = 0.0, []
+    for k in sorted(want):
         a, b, p0 = got[k].ravel(), want[k].ravel(), before[k].ravel()
-        assert cosine(a, b) >= 0.999, k
         moved = max(moved, float(np.abs(b - p0).max()))
-        ok = np.abs(a - b) <= 2e-2 * np.maximum(np.abs(b), lr)
-        assert ok.mean() >= 0.97, (k, float(ok.mean()))
-        da, db = a - p0, b - p0                                               # the four Adam updates themselves
-        assert cosine(da, db) >= 0.98, (k, cosine(da, db))
-    assert moved > lr                                                         # the run did train
+        ok = float((np.abs(a - b) <= 2e-2 * np.maximum(np.abs(b), lr)).mean())
+        stats.append((k, round(cosine(a, b), 6), round(ok, 4), round(cosine(a - p0, b - p0), 4)))   # last: the four Adam updates themselves
+    print("adapter tensors (key, cosine, fraction within the bound, cosine of the updates):", stats)
+    for k, c, ok, cu in stats:
+        assert c >= 0.999 and ok >= 0.97 and cu >= 0.98, stats
+    assert moved > lr, stats                                                  # the run did train
     names = dict(line.split() for line in report.read_text().splitlines() if line.strip())
     assert int(names.get("gemm_nt_2cta", 0)) + int(names.get("gemm_nt", 0)) > 0 and "matmul_f32" not in names, names
 
