@@ -148,3 +148,53 @@ def read_lora_weights_bin(path: Path) -> list:
         out.append(np.frombuffer(raw, np.float32, cnt, off).reshape(dims).copy()); off += 4 * cnt
     assert off == len(raw)
     return out
+
+
+GEMMA_TINY = dict(num_hidden_layers=2, hidden_size=64, intermediate_size=128, num_attention_heads=4, num_key_value_heads=1, head_dim=16,
+                  vocab_size=512, sliding_window=32)
+
+
+def write_gemma_checkpoint(root: Path, seed: int = 19, scale: float = 0.15) -> dict:
+    """A Gemma-3-text-style model directory (config.json with one sliding and one full-attention layer, model.safetensors with
+    HuggingFace keys: [out, in] linears, q / k norms, the four norms per layer) and a pretokenized corpus next to it
+    (tokens.bin int32 + meta.json with the split ranges), which the reference's Gemma program reads instead of
+    tokenizing text.  Returns the tensors written."""
+    c = GEMMA_TINY
+    root.mkdir(parents=True, exist_ok=True)
+    H, I, V, nh, nkv, hd = c["hidden_size"], c["intermediate_size"], c["vocab_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+    (root / "config.json").write_text(json.dumps({
+        "model_type": "gemma3_text", "vocab_size": V, "hidden_size": H, "intermediate_size": I, "num_hidden_layers": c["num_hidden_layers"],
+        "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": hd, "max_position_embeddings": 512, "sliding_window": c["sliding_window"],
+        "rms_norm_eps": 1e-6, "query_pre_attn_scalar": float(hd), "rope_theta": 1000000.0, "rope_local_base_freq": 10000.0,
+        "hidden_activation": "gelu_pytorch_tanh", "attention_bias": False, "layer_types": ["sliding_attention", "full_attention"],
+        "tie_word_embeddings": True}))
+    rng = np.random.default_rng(seed)
+    t = {"model.embed_tokens.weight": rng.normal(0, scale, (V, H)), "model.norm.weight": rng.normal(0, 0.05, H)}
+    for i in range(c["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        for n in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+            t[p + n + ".weight"] = rng.normal(0, 0.05, H)                      # (1 + w) norms: stored around zero
+        t[p + "self_attn.q_proj.weight"] = rng.normal(0, scale, (nh * hd, H))
+        t[p + "self_attn.k_proj.weight"] = rng.normal(0, scale, (nkv * hd, H))
+        t[p + "self_attn.v_proj.weight"] = rng.normal(0, scale, (nkv * hd, H))
+        t[p + "self_attn.o_proj.weight"] = rng.normal(0, scale, (H, nh * hd))
+        t[p + "self_attn.q_norm.weight"] = rng.normal(0, 0.05, hd)
+        t[p + "self_attn.k_norm.weight"] = rng.normal(0, 0.05, hd)
+        t[p + "mlp.gate_proj.weight"] = rng.normal(0, scale, (I, H))
+        t[p + "mlp.up_proj.weight"] = rng.normal(0, scale, (I, H))
+        t[p + "mlp.down_proj.weight"] = rng.normal(0, scale, (H, I))
+    t = {k: np.ascontiguousarray(v, np.float32) for k, v in t.items()}
+    write_container(root / "model.safetensors", {k: ("F32", v) for k, v in t.items()}, {"format": "pt"})
+    return t
+
+
+def write_pretokenized_corpus(root: Path, vocab: int, seed: int = 23, n_train: int = 6000, n_valid: int = 1500):
+    """tokens.bin (int32, train then valid) + meta.json: Zipf-distributed ids in [4, vocab), an end-of-text id 1 now and then."""
+    root.mkdir(parents=True, exist_ok=True)
+    rng = np.random.default_rng(seed)
+    ids = (4 + (rng.zipf(1.3, n_train + n_valid) - 1) % (vocab - 4)).astype(np.int32)
+    ids[rng.random(ids.size) < 0.02] = 1
+    ids.tofile(root / "tokens.bin")
+    (root / "meta.json").write_text(json.dumps({"total_tokens": int(ids.size), "eos_token_id": 1, "pad_token_id": 0, "bos_token_id": 2, "unk_token_id": 3,
+                                                "vocab_size": vocab, "insert_eos_between_lines": True,
+                                                "train": {"offset": 0, "length": n_train}, "valid": {"offset": n_train, "length": n_valid}}))

@@ -225,3 +225,51 @@ def test_reference_qwen_train_end_to_end_against_the_reference_build(tmp_path, l
     for i, c, rel in stats:
         assert c >= 0.98 and rel <= 0.25, stats          # observed over runs: cosine 0.9927 .. 0.99997, relative error 0.007 .. 0.12
     assert moved > lr, stats
+
+
+def test_reference_gemma_train_end_to_end_against_the_reference_build(tmp_path):
+    """examples/gemma_3_270m_lora_finetune/src/main.cpp in its real mode, one source, two builds: a Gemma-3-text-style
+    checkpoint (sliding + full attention layer, QK norms, four norms per layer, HuggingFace keys), GemmaLoraInjector's
+    seeded initialisation on all seven linears, a pretokenized corpus, and GemmaLoRATrainer - the class that drives the
+    device step driver here - with two accumulated micro-batches per update, clipping and its learning-rate schedule.
+    Compared: the loss and learning rate of every logged step and the adapter file saved at the end."""
+    import re
+    import numpy as np
+    from parity import require_built
+    from conftest import cosine
+    import cli_assets as A
+    ours = require_built(ROOT / "oracle" / "_ref" / "cli" / "gemma_3_270m_lora_finetune" / "train", "the reference's Gemma train built against this repository's operators target")
+    ref = require_built(ROOT / "oracle" / "_ref" / "ref_cli" / "gemma_train", "the reference's Gemma train built on the reference's own operators")
+    A.write_gemma_checkpoint(tmp_path / "gemma")
+    A.write_pretokenized_corpus(tmp_path / "data", A.GEMMA_TINY["vocab_size"])
+    lr = 2e-3
+    env = dict(os.environ, LD_LIBRARY_PATH=str(ROOT / "mobilefinetuner_b200") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+
+    def run(exe, out, env=None):
+        (tmp_path / out).mkdir()
+        r = subprocess.run([str(exe), "--model_dir", "gemma", "--pretokenized_path", "data/tokens.bin", "--output_dir", out, "--epochs", "1", "--max_steps", "4",
+                            "--seq_len", "64", "--batch", "4", "--grad_accum", "2", "--lr", str(lr), "--rank", "4", "--alpha", "8", "--warmup_ratio", "0.0",
+                            "--max_grad_norm", "1.0"], capture_output=True, text=True, timeout=900, env=env, cwd=tmp_path)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+        steps = [(float(l), float(x)) for l, x in re.findall(r"\[Step \d+\] Loss=([0-9.eE+-]+) PPL=\S+ LR=([0-9.eE+-]+)", r.stdout)]
+        assert len(steps) == 4, r.stdout[-3000:]
+        return steps, A.read_container(tmp_path / out / "gemma_lora.safetensors")
+
+    want_steps, want = run(ref, "out_ref")
+    got_steps, got = run(ours, "out_ours", env)
+    for (l0, x0), (l1, x1) in zip(want_steps, got_steps):
+        assert abs(l1 - l0) <= 2e-3 * abs(l0), (want_steps, got_steps)
+        assert abs(x1 - x0) <= 1e-4 * abs(x0) + 1e-9, (want_steps, got_steps)      # the schedule is host arithmetic
+    assert sorted(got) == sorted(want) and len(want) == 2 * 7 * A.GEMMA_TINY["num_hidden_layers"]
+    # adapters trained from B = 0 on a random model: the direction bound of the Qwen program test (see there)
+    stats, moved = [], 0.0
+    for k in sorted(want):
+        a, b = got[k].ravel(), want[k].ravel()
+        assert a.shape == b.shape
+        stats.append((k, round(cosine(a, b), 5), round(float(np.linalg.norm(a - b) / np.linalg.norm(b)), 4)))
+        if k.endswith("lora_B"):
+            moved = max(moved, float(np.abs(b).max()))
+    print("adapter tensors (key, cosine, relative L2 error):", stats)
+    for k, c, rel in stats:
+        assert c >= 0.98 and rel <= 0.25, stats
+    assert moved > lr, stats
