@@ -257,9 +257,12 @@ def test_reference_gemma_train_end_to_end_against_the_reference_build(tmp_path):
 
     want_steps, want = run(ref, "out_ref")
     got_steps, got = run(ours, "out_ours", env)
-    for (l0, x0), (l1, x1) in zip(want_steps, got_steps):
+    # the schedule (optim/gemma_trainer.cpp:44-63): 93 sequences -> 24 micro-batches -> 12 updates, no warm-up, linear decay.
+    # Both programs print it with few digits (the reference with three decimals once its timer has set std::fixed).
+    for i, ((l0, x0), (l1, x1)) in enumerate(zip(want_steps, got_steps)):
         assert abs(l1 - l0) <= 2e-3 * abs(l0), (want_steps, got_steps)
-        assert abs(x1 - x0) <= 1e-4 * abs(x0) + 1e-9, (want_steps, got_steps)      # the schedule is host arithmetic
+        expect = lr * (1.0 - (i + 1) / 12.0)
+        assert abs(x1 - expect) <= 0.01 * expect and abs(x0 - expect) <= 5.1e-4, (want_steps, got_steps, expect)
     assert sorted(got) == sorted(want) and len(want) == 2 * 7 * A.GEMMA_TINY["num_hidden_layers"]
     # adapters trained from B = 0 on a random model: the direction bound of the Qwen program test (see there)
     stats, moved = [], 0.0
