@@ -38,9 +38,21 @@ int32_t check_cuda(cudaError_t e, const char* what);
 // descriptor prefetch), then dep_wait() blocks until the previous kernel has completed and its writes are
 // visible.  Such a kernel must not touch global memory before dep_wait().  dep_trigger() tells the scheduler
 // that the NEXT kernel may start its own set-up.  Both are no-ops in a kernel launched the ordinary way.
-// Off by default: on this power-capped part the step measured 1 % SLOWER with it (118.5 vs 117.1 ms, alternating
-// runs on one GPU); MFT_PDL=1 in the environment turns it on.
+// Whether it pays depends on the step: a large step that sits at the power cap measured 1 % SLOWER with it (118.5 vs
+// 117.1 ms, alternating runs on one GPU), steps of a few thousand tokens, whose kernels are short against their own
+// set-up, measured faster (Qwen2.5-0.5B at 8 x 512: 16.63 -> 16.40 ms; GPT-2 small at 4 x 128: 2.30 -> 2.22 ms).  The
+// step engine therefore turns it on for its own launches when a step has at most 8192 tokens (DepLaunchScope);
+// MFT_PDL=0 / 1 in the environment overrides that for the whole process.
 bool dep_launch_enabled();
+bool set_dep_launch_hint(bool on);      // returns the previous hint of this host thread
+struct DepLaunchScope {
+    bool active = false, previous = false;
+    DepLaunchScope() = default;
+    DepLaunchScope(const DepLaunchScope&) = delete;
+    DepLaunchScope& operator=(const DepLaunchScope&) = delete;
+    void set(bool on) { if (!active) { previous = set_dep_launch_hint(on); active = true; } else set_dep_launch_hint(on); }
+    ~DepLaunchScope() { if (active) set_dep_launch_hint(previous); }
+};
 __device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

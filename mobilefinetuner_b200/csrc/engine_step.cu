@@ -24,6 +24,7 @@ struct Ctx {
     int64_t B, S, T;
     mft_stream_t st;
     float lora_scale;
+    mft::DepLaunchScope dep;       // programmatic dependent launch for this call's kernels when the step is small
 };
 
 // Columns of the 64-wide LoRA panels that the products read: the rank columns in use, rounded up to the MMA's K step.
@@ -280,6 +281,7 @@ int32_t make_ctx(mft_model* m, int32_t batch, int32_t seq, Ctx* c) {
     MFT_CHECK_ARG((int64_t)batch * seq <= m->max_tokens && seq <= m->cfg.max_seq, "step: batch*seq exceeds the model's capacity");
     c->m = m; c->B = batch; c->S = seq; c->T = (int64_t)batch * seq; c->st = m->stream;
     c->lora_scale = m->cfg.lora_rank > 0 ? m->cfg.lora_alpha / (float)m->cfg.lora_rank : 0.f;
+    c->dep.set(c->T <= 8192);
     return MFT_OK;
 }
 
@@ -324,7 +326,8 @@ int32_t forward_backward(Ctx& c, int64_t n_valid_global) {
                 return eager();
             }
         }
-        Ctx cc = c;
+        Ctx cc;                                 // the same call on the capture stream (the launch hint stays c's)
+        cc.m = c.m; cc.B = c.B; cc.S = c.S; cc.T = c.T; cc.lora_scale = c.lora_scale;
         cc.st = m->graph_stream;
         cudaGraph_t graph = nullptr;
         if (cudaStreamBeginCapture(m->graph_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {

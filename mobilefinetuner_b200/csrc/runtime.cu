@@ -44,9 +44,13 @@ void note_launch(const char* name) {
     std::lock_guard<std::mutex> lk(r.mu);
     ++r.counts[name];
 }
+// MFT_PDL=0 / 1 in the environment decides for the whole process; without it the caller's hint does (per host thread:
+// launches are issued synchronously by the thread that runs a step).
+static thread_local bool t_dep_hint = false;
+bool set_dep_launch_hint(bool on) { const bool old = t_dep_hint; t_dep_hint = on; return old; }
 bool dep_launch_enabled() {
-    static const bool on = [] { const char* e = std::getenv("MFT_PDL"); return e ? std::atoi(e) != 0 : false; }();
-    return on;
+    static const int mode = [] { const char* e = std::getenv("MFT_PDL"); return e ? (std::atoi(e) != 0 ? 1 : 0) : -1; }();
+    return mode >= 0 ? mode != 0 : t_dep_hint;
 }
 int32_t* device_status_word() { return g_status_word; }
 
