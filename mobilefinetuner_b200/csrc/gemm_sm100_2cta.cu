@@ -31,9 +31,14 @@ constexpr int THREADS = 64 + 32 * EPI_WARPS;  // TMA warp, MMA warp, epilogue wa
 constexpr int BAR_BYTES = 1024;               // barriers, tensor-memory slot, abort flag, per-quadrant row sums
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int STORE_BYTES = 4 * 2 * EPI_BOX_BYTES;
-// BN2 = columns of the pair's tile.  256 is the only width in use: 192 measured 17 % slower per column and 128
+// BN2 = columns of the pair's tile.  256 is the general width: 192 measured 17 % slower per column and 128
 // 40 % slower (their operand loads per MMA cycle outrun what the L2 delivers), which costs more than the tile
 // quantisation they would save.  Each CTA stages A (16 KB) and BN2/2 rows of B per k-block.
+// BN2 = 384 (WIDE) goes the other way for outputs whose width is a multiple of 384 under a long K: one A tile then
+// serves 384 columns (40 KB of operands per 256 x 384 x 64 block instead of 48 KB in 256-wide tiles, and no half-empty
+// fifth column tile at N = 1152).  Its accumulator takes 384 of the 512 tensor-memory columns, so there is one
+// accumulator buffer and the epilogue of a tile is not overlapped with the next tile's MMAs: it is used only where
+// the K loop is long against the epilogue.  One k-step is two MMAs of 192 columns, each reading 96 B rows per CTA.
 // The gated-MLP backward epilogue keeps GLU_SETS sets of (gate, up) boxes per warp (loaded by TMA, rewritten in place,
 // stored by TMA): twice the box memory of the other epilogues, paid for with one pipeline stage.
 template <int EPI, int BN2>
@@ -41,7 +46,11 @@ struct PairCfg {
     static constexpr int BH_BYTES = (BN2 / 2) * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + BH_BYTES;                  // 32 / 28 KB, multiples of 1024
     static constexpr int BOX_BYTES = EPI == EPI_GLU_BWD ? GLU_SETS * STORE_BYTES : STORE_BYTES;
-    static constexpr int STAGES = EPI == EPI_GLU_BWD ? 8 - GLU_SETS - 1 : 6;
+    static constexpr bool WIDE = BN2 > 256;
+    static constexpr int ACC_BUFS = WIDE ? 1 : 2;
+    static constexpr int MMA_N = WIDE ? BN2 / 2 : BN2;                      // columns of one MMA instruction
+    static constexpr int STAGES = EPI == EPI_GLU_BWD ? 8 - GLU_SETS - 1 : (WIDE ? 4 : 6);
+    static_assert(!WIDE || (EPI == EPI_STORE && BN2 == 384), "the wide tile is built for the plain store epilogue");
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BOX_BYTES + 1024 + BAR_BYTES;
 };
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;   // clears the bit that distinguishes the two CTAs of a pair: -> address in the leader
@@ -99,6 +108,8 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     dep_trigger();
     constexpr int STAGES = PairCfg<EPI, BN2>::STAGES, STAGE_BYTES = PairCfg<EPI, BN2>::STAGE_BYTES;
     constexpr int BOX_BYTES = PairCfg<EPI, BN2>::BOX_BYTES;
+    constexpr bool WIDE = PairCfg<EPI, BN2>::WIDE;
+    constexpr int ACC_BUFS = PairCfg<EPI, BN2>::ACC_BUFS, MMA_N = PairCfg<EPI, BN2>::MMA_N;
     constexpr bool GLU_FWD = EPI == EPI_GLU_FWD, GLU_BWD = EPI == EPI_GLU_BWD;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -154,7 +165,9 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int n_base = tile_n(t2, p) * BN2;
                 const int n_eff = min(BN2, (p.n - n_base + 15) & ~15);
                 // gated-MLP forward: the leader loads 128 gate rows of the weight, the peer the 128 matching up rows
-                const int n0 = GLU_FWD ? tile_n(t2, p) * (BN2 / 2) + (int)rank * p.glu_inter : n_base + (int)rank * (n_eff / 2);
+                // wide tile: the pair's first MMA takes columns 0..191 (96 B rows from each CTA), the second 192..383
+                const int n0 = WIDE ? n_base + (int)rank * (MMA_N / 2)
+                             : GLU_FWD ? tile_n(t2, p) * (BN2 / 2) + (int)rank * p.glu_inter : n_base + (int)rank * (n_eff / 2);
                 const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
@@ -162,13 +175,12 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     uint8_t* sb = sa + A_BYTES;
                     const uint32_t full_in_leader = smem_u32(&full_bar[stage]) & PEER_MASK;
                     mbar_arrive_expect_tx_cluster(full_in_leader, STAGE_BYTES);
-                    if (kb < num_kb_main) {
-                        tma_load_2d_pair(sa, &map_a, full_in_leader, kb * BK, m0);
-                        tma_load_2d_pair(sb, &map_b, full_in_leader, kb * BK, n0);
-                    } else {
-                        tma_load_2d_pair(sa, &map_a2, full_in_leader, 0, m0);
-                        tma_load_2d_pair(sb, &map_b2, full_in_leader, 0, n0);
-                    }
+                    const CUtensorMap* ta = kb < num_kb_main ? &map_a : &map_a2;
+                    const CUtensorMap* tb = kb < num_kb_main ? &map_b : &map_b2;
+                    const int k0 = kb < num_kb_main ? kb * BK : 0;
+                    tma_load_2d_pair(sa, ta, full_in_leader, k0, m0);
+                    tma_load_2d_pair(sb, tb, full_in_leader, k0, n0);
+                    if (WIDE) tma_load_2d_pair(sb + (MMA_N / 2) * BK * 2, tb, full_in_leader, k0, n0 + MMA_N);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -180,15 +192,15 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int it = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
-                const int acc = it & 1;
-                const uint32_t acc_phase = (it >> 1) & 1;
+                const int acc = ACC_BUFS == 2 ? it & 1 : 0;
+                const uint32_t acc_phase = ACC_BUFS == 2 ? (it >> 1) & 1 : it & 1;
                 if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN2;
                 const int split = tile / p.tiles_mn;
                 const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
                 const int n_base = tile_n(tile % p.tiles_mn, p) * BN2;
-                const uint32_t idesc = idesc_bf16_f32(2 * BM, GLU_FWD ? (uint32_t)BN2 : (uint32_t)min(BN2, (p.n - n_base + 15) & ~15));
+                const uint32_t idesc = idesc_bf16_f32(2 * BM, (GLU_FWD || WIDE) ? (uint32_t)MMA_N : (uint32_t)min(BN2, (p.n - n_base + 15) & ~15));
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
@@ -197,8 +209,13 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint64_t bdesc = smem_desc_sw128(sa + A_BYTES);
                     const int kvalid = (kb < num_kb_main) ? min(BK, p.k - kb * BK) : p.k2;
                     const int nmma = (kvalid + 15) / 16;
-                    for (int j = 0; j < nmma; ++j)
+                    for (int j = 0; j < nmma; ++j) {
                         umma2_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb > kb0 || j != 0) ? 1u : 0u);
+                        if (WIDE) {
+                            const uint64_t bdesc_hi = smem_desc_sw128(sa + A_BYTES + (MMA_N / 2) * BK * 2);
+                            umma2_bf16(tmem_d + MMA_N, adesc + (uint64_t)(2 * j), bdesc_hi + (uint64_t)(2 * j), idesc, (kb > kb0 || j != 0) ? 1u : 0u);
+                        }
+                    }
                     umma2_commit_both(&empty_bar[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -223,8 +240,8 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int i = 0; i < GLU_SETS - 1; ++i) glu_bwd_prefetch(p, &map_x, store_smem, glu_bar, q, (int)rank, num_clusters, num_tiles, glu_state);
         }
         for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
-            const int acc = it & 1;
-            const uint32_t acc_phase = (it >> 1) & 1;
+            const int acc = ACC_BUFS == 2 ? it & 1 : 0;
+            const uint32_t acc_phase = ACC_BUFS == 2 ? (it >> 1) & 1 : it & 1;
             const int t2 = tile % p.tiles_mn;
             const int m0 = tile_m(t2, p) * 2 * BM + (int)rank * BM;
             const int n0 = GLU_FWD ? tile_n(t2, p) * (BN2 / 2) : tile_n(t2, p) * BN2;
@@ -284,12 +301,12 @@ int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& 
 // clusters per unit of work, each extra range charged 0.2 % for its pass over D.  (A ragged last column tile
 // counts as a full one: narrowing its MMAs was measured to save nothing, the main loop is bound by operand
 // delivery.)
-int choose_splits(int64_t m, int64_t n, int64_t kb) {
-    const int64_t clusters = num_sms() / 2, tiles_mn = ((m + 255) / 256) * ((n + 255) / 256);
+int choose_splits(int64_t m, int64_t n, int64_t kb, int64_t bn) {
+    const int64_t clusters = num_sms() / 2, tiles_mn = ((m + 255) / 256) * ((n + bn - 1) / bn);
     int best_sp = 1;
     double best = 1e300;
     for (int sp = 1; sp <= 8; ++sp) {
-        if (sp > 1 && kb / sp < 32) break;
+        if (sp > 1 && kb / sp < (bn > 256 ? 64 : 32)) break;
         const int64_t per = (kb + sp - 1) / sp, waves = (tiles_mn * sp + clusters - 1) / clusters;
         const double cost = (double)waves * ((double)per + 4.0) * (1.0 + 0.002 * (sp - 1));
         if (cost < best * 0.995) { best = cost; best_sp = sp; }
@@ -317,14 +334,20 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     const bool can_split = f32_ok && c.k2 == 0;
     if (c.splits > 1 && !can_split) return MFT_ERR_UNSUPPORTED;
     const int64_t kb = (c.k + BK - 1) / BK + (c.k2 > 0 ? 1 : 0);
-    const int bn = 256;
-    const int splits = !can_split ? 1 : (c.splits == 0 ? choose_splits(c.m, c.n, kb) : c.splits);
+    // the wide tile: plain bf16 store, whole 384-column tiles, and a K loop of at least 64 blocks, against which the
+    // tile's unoverlapped epilogue is small (MFT_GEMM_WIDE=0 keeps every call on 256-wide tiles)
+    static const bool wide_allowed = [] { const char* e = std::getenv("MFT_GEMM_WIDE"); return !(e && e[0] == '0'); }();
+    const bool wide = wide_allowed && c.epi == EPI_STORE && c.n % 384 == 0 && c.m % 256 == 0 &&
+                      (can_split && c.splits > 1 ? kb / c.splits >= 64 : kb >= 64);
+    const int bn = wide ? 384 : 256;
+    const int splits = !can_split ? 1 : (c.splits == 0 ? choose_splits(c.m, c.n, kb, bn) : c.splits);
     CUtensorMap ma, mb, ma2, mb2, md, mx;
     if (int32_t s = make_tmap_bf16(&ma, c.a, c.m, c.k, c.lda, BM)) return s;
-    if (int32_t s = make_tmap_bf16(&mb, c.b, c.n, c.k, c.ldb, bn / 2)) return s;
+    const int b_box = wide ? 96 : 128;                 // B rows per box: see the producer
+    if (int32_t s = make_tmap_bf16(&mb, c.b, c.n, c.k, c.ldb, b_box)) return s;
     if (c.k2 > 0) {
         if (int32_t s = make_tmap_bf16(&ma2, c.a2, c.m, c.k2, c.lda2, BM)) return s;
-        if (int32_t s = make_tmap_bf16(&mb2, c.b2, c.n, c.k2, c.ldb2, bn / 2)) return s;
+        if (int32_t s = make_tmap_bf16(&mb2, c.b2, c.n, c.k2, c.ldb2, b_box)) return s;
     } else {
         ma2 = ma; mb2 = mb;
     }
@@ -359,6 +382,7 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     if (c.epi == EPI_CE_P) return launch<EPI_CE_P, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
     if (c.epi == EPI_GLU_FWD) return launch<EPI_GLU_FWD, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
     if (c.epi == EPI_GLU_BWD) return launch<EPI_GLU_BWD, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
+    if (wide) return launch<EPI_STORE, 384>(ma, mb, ma2, mb2, md, mx, p, stream);
     return launch<EPI_STORE, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
 }
 

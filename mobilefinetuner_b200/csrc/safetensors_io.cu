@@ -529,6 +529,8 @@ extern "C" int32_t mft_model_save_lora_safetensors(mft_model_t* m, const char* p
     if (m->cfg.family == MFT_FAMILY_GEMMA) std::sort(listed.begin(), listed.end());
     std::string joined;
     for (size_t t = 0; t < listed.size(); ++t) joined += (t ? "," : "") + listed[t];
+    // the step engine applies no LoRA dropout, so "0" is what was trained with (the operator API's injectors write their
+    // configured value through their own writer)
     const std::string rank = std::to_string(m->cfg.lora_rank), alpha = fmt_float(m->cfg.lora_alpha), dropout = "0";
     const char* keys[4] = {"rank", "alpha", "dropout", "targets"};
     const char* vals[4] = {rank.c_str(), alpha.c_str(), dropout.c_str(), joined.c_str()};
