@@ -109,6 +109,7 @@ _SIGS = {
     "mft_repeat_kv": [vp, i32, vp, i64, i64, i64, i64, i64, vp],
     "mft_repeat_kv_bwd": [vp, vp, i64, i64, i64, i64, i64, vp],
     "mft_gemm_nt": [vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, f32, vp, i64, i32, i32, vp],
+    "mft_gemm_nt_tile_cols": [i64, i64, i64, i64, i32, C.POINTER(i32)],
     "mft_glu_linear_fwd": [i32, vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, vp, i64, vp, i64, vp],
     "mft_glu_linear_bwd": [i32, vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, i64, vp, i64, vp],
     "mft_profile_gemm": [i32],

@@ -606,6 +606,13 @@ extern "C" int32_t mft_glu_linear_bwd(int32_t kind, const void* dy, int64_t lddy
     return gemm_nt_run(c, as_stream(stream));
 }
 
+extern "C" int32_t mft_gemm_nt_tile_cols(int64_t m, int64_t n, int64_t k, int64_t k2, int32_t d_dtype, int32_t* tile_cols_host) {
+    MFT_CHECK_ARG(tile_cols_host && m > 0 && n > 0 && k > 0 && k2 >= 0, "mft_gemm_nt_tile_cols: bad argument");
+    MFT_CHECK_ARG(d_dtype == MFT_F32 || d_dtype == MFT_BF16, "mft_gemm_nt_tile_cols: D must be f32 or bf16");
+    *tile_cols_host = gemm_nt_pair_tile_cols(m, n, k, k2, d_dtype == MFT_F32);
+    return MFT_OK;
+}
+
 extern "C" int32_t mft_gemm_nt(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,
                                const void* a2, int64_t lda2, const void* b2, int64_t ldb2, int64_t k2, const float* bias,
                                float alpha, void* d, int64_t ldd, int32_t d_dtype, int32_t accumulate, mft_stream_t stream) {

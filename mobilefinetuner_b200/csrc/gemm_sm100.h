@@ -92,6 +92,9 @@ __host__ __device__ inline int tile_n(int tile, const GemmParams& p) {
 int32_t gemm_nt_run(const GemmCall& c, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant for 256 x 256 cluster tiles; returns MFT_ERR_UNSUPPORTED when the call does not qualify.
 int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream);
+// columns of the pair kernel's tile for a plain-store call of this shape: 256, 384 (long K under a width that is a
+// multiple of 384), or 0 when the pair kernel does not take the call
+int gemm_nt_pair_tile_cols(int64_t m, int64_t n, int64_t k, int64_t k2, bool d_is_f32);
 int32_t make_tmap_bf16(struct CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
 int32_t make_tmap_f32_out(struct CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld);
 int num_sms();

@@ -297,24 +297,60 @@ int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& 
     return MFT_OK;
 }
 
-// Number of K ranges for an f32 output whose caller leaves the choice open: fewest waves of tiles over the
-// clusters per unit of work, each extra range charged 0.2 % for its pass over D.  (A ragged last column tile
-// counts as a full one: narrowing its MMAs was measured to save nothing, the main loop is bound by operand
-// delivery.)
-int choose_splits(int64_t m, int64_t n, int64_t kb, int64_t bn) {
+// Cost of a call in units of one k-block of a 256 x 256 tile: waves of tiles over the clusters times the k-blocks of a
+// tile (plus a per-tile charge), each extra K range charged 0.2 % for its pass over D.  A k-block of a 384-wide tile
+// measured 1.16 of a 256-wide one for 1.5 times the columns (1157 against about 1000 clocks at 16384 x 1152 x 6912 and
+// x 13824), and its per-tile charge is larger because its epilogue (about 7000 clocks) is not overlapped.  A ragged last
+// column tile counts as a full one: narrowing its MMAs was measured to save nothing, the main loop is bound by
+// operand delivery.
+double tile_cost(int64_t m, int64_t n, int64_t kb, int bn, int sp) {
     const int64_t clusters = num_sms() / 2, tiles_mn = ((m + 255) / 256) * ((n + bn - 1) / bn);
+    const int64_t per = (kb + sp - 1) / sp, waves = (tiles_mn * sp + clusters - 1) / clusters;
+    const double unit = bn > 256 ? 1.16 : 1.0, per_tile = bn > 256 ? 10.0 : 4.0;
+    return (double)waves * ((double)per + per_tile) * unit * (1.0 + 0.002 * (sp - 1));
+}
+// Number of K ranges for an f32 output whose caller leaves the choice open, and the cost of that choice.
+int choose_splits(int64_t m, int64_t n, int64_t kb, int bn, double* cost_out) {
     int best_sp = 1;
     double best = 1e300;
     for (int sp = 1; sp <= 8; ++sp) {
         if (sp > 1 && kb / sp < (bn > 256 ? 64 : 32)) break;
-        const int64_t per = (kb + sp - 1) / sp, waves = (tiles_mn * sp + clusters - 1) / clusters;
-        const double cost = (double)waves * ((double)per + 4.0) * (1.0 + 0.002 * (sp - 1));
+        const double cost = tile_cost(m, n, kb, bn, sp);
         if (cost < best * 0.995) { best = cost; best_sp = sp; }
     }
+    if (cost_out) *cost_out = best;
     return best_sp;
 }
 
+// Tile width (256 or 384 columns) and number of K ranges of a call.  `asked` = the caller's K ranges, 0 = choose.
+int plan_tiles(int64_t m, int64_t n, int64_t kb, bool wide_fits, bool can_split, int asked, int* splits_out) {
+    static const bool wide_allowed = [] { const char* e = std::getenv("MFT_GEMM_WIDE"); return !(e && e[0] == '0'); }();
+    wide_fits = wide_fits && wide_allowed;
+    bool wide = false;
+    int splits = 1;
+    if (!can_split || asked > 0) {
+        splits = can_split ? asked : 1;
+        wide = wide_fits && kb / splits >= 64 && tile_cost(m, n, kb, 384, splits) < tile_cost(m, n, kb, 256, splits);
+    } else {
+        double cost256 = 0, cost384 = 0;
+        const int sp256 = choose_splits(m, n, kb, 256, &cost256);
+        const int sp384 = wide_fits && kb >= 64 ? choose_splits(m, n, kb, 384, &cost384) : 0;
+        wide = sp384 > 0 && cost384 < cost256;
+        splits = wide ? sp384 : sp256;
+    }
+    *splits_out = splits;
+    return wide ? 384 : 256;
+}
+
 }  // namespace
+
+// what gemm_nt_run_2cta would choose for a plain-store call of this shape (0 when the pair kernel does not take it)
+int gemm_nt_pair_tile_cols(int64_t m, int64_t n, int64_t k, int64_t k2, bool d_is_f32) {
+    if (m < 256 || n < 192) return 0;
+    const int64_t kb = (k + BK - 1) / BK + (k2 > 0 ? 1 : 0);
+    int splits = 1;
+    return plan_tiles(m, n, kb, n % 384 == 0 && m % 256 == 0, d_is_f32 && k2 == 0, 0, &splits);
+}
 
 int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     const bool ce = c.epi == EPI_CE_GRAD || c.epi == EPI_CE_P;
@@ -334,13 +370,14 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     const bool can_split = f32_ok && c.k2 == 0;
     if (c.splits > 1 && !can_split) return MFT_ERR_UNSUPPORTED;
     const int64_t kb = (c.k + BK - 1) / BK + (c.k2 > 0 ? 1 : 0);
-    // the wide tile: plain bf16 store, whole 384-column tiles, and a K loop of at least 64 blocks, against which the
-    // tile's unoverlapped epilogue is small (MFT_GEMM_WIDE=0 keeps every call on 256-wide tiles)
-    static const bool wide_allowed = [] { const char* e = std::getenv("MFT_GEMM_WIDE"); return !(e && e[0] == '0'); }();
-    const bool wide = wide_allowed && c.epi == EPI_STORE && c.n % 384 == 0 && c.m % 256 == 0 &&
-                      (can_split && c.splits > 1 ? kb / c.splits >= 64 : kb >= 64);
-    const int bn = wide ? 384 : 256;
-    const int splits = !can_split ? 1 : (c.splits == 0 ? choose_splits(c.m, c.n, kb, bn) : c.splits);
+    // the wide tile: plain store, whole 384-column tiles, a K loop of at least 64 blocks per tile, against which the
+    // tile's unoverlapped epilogue is small, and enough tiles that the cost model prefers it (a call of a few tiles is
+    // one wave either way, and the wave of wide tiles is the longer one).  MFT_GEMM_WIDE=0 keeps every call on
+    // 256-wide tiles.
+    const bool wide_fits = c.epi == EPI_STORE && c.n % 384 == 0 && c.m % 256 == 0;
+    int splits = 1;
+    const int bn = plan_tiles(c.m, c.n, kb, wide_fits, can_split, (int)c.splits, &splits);
+    const bool wide = bn > 256;
     CUtensorMap ma, mb, ma2, mb2, md, mx;
     if (int32_t s = make_tmap_bf16(&ma, c.a, c.m, c.k, c.lda, BM)) return s;
     const int b_box = wide ? 96 : 128;                 // B rows per box: see the producer

@@ -60,6 +60,14 @@ def gemm_nt(a, b, *, a2=None, b2=None, bias=None, alpha=1.0, out=None, out_dtype
     return out
 
 
+def gemm_nt_tile_cols(m, n, k, k2=0, out_dtype=BF16):
+    """Columns of the CTA-pair kernel's tile for a gemm_nt call of this shape (256 / 384), 0 when another kernel runs it."""
+    L.init(torch.cuda.current_device())
+    cols = C.c_int32(0)
+    L.call("mft_gemm_nt_tile_cols", m, n, k, k2, L.MFT_BF16 if out_dtype == BF16 else L.MFT_F32, C.byref(cols))
+    return cols.value
+
+
 def gemm_tn_acc(u, v, out, alpha=1.0):
     """out[P,Q] += alpha * U^T V with U [T,P], V [T,Q] bf16, out f32."""
     _init(u)

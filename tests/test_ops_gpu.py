@@ -86,6 +86,34 @@ def test_gemm_nt_f32_deep_k_is_split_and_reduced(ops, m, n, k, accumulate):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k,r", [(4096, 1152, 4096, 16), (8192, 768, 4128, 32), (4096, 1152, 8192, 0), (16384, 384, 4096, 0)])
+def test_gemm_nt_wide_tile_long_k(ops, m, n, k, r):
+    """Outputs whose width is a multiple of 384 under K >= 4096 run on 256 x 384 tiles with one accumulator buffer
+    (two 192-column MMAs per k-step) when the call has enough tiles; bf16 and f32 outputs, with the LoRA segment,
+    bias and alpha."""
+    assert ops.gemm_nt_tile_cols(m, n, k, r) == 384
+    assert ops.gemm_nt_tile_cols(512, 384, 4096) == 256          # two tiles: one wave either way
+    assert ops.gemm_nt_tile_cols(m, n, 1152, r) == 256           # short K: the unoverlapped epilogue would show
+    g = np.random.Generator(np.random.PCG64(m + n + k))
+    a, b = rb(g.standard_normal((m, k))), rb(g.standard_normal((n, k)) * 0.05)
+    bias = g.standard_normal(n).astype(np.float32)
+    want = a @ b.T                                               # f32 BLAS; compared at bf16 / 1e-4 tolerances below
+    kw = {}
+    if r:
+        a2p = np.zeros((m, 64), np.float32); a2p[:, :r] = rb(g.standard_normal((m, r)))
+        b2p = np.zeros((n, 64), np.float32); b2p[:, :r] = rb(g.standard_normal((n, r)))
+        want = want + a2p @ b2p.T
+        kw = dict(a2=dev(a2p, torch.bfloat16)[:, :r], b2=dev(b2p, torch.bfloat16)[:, :r])
+    want = 0.25 * want + bias
+    got16 = host(ops.gemm_nt(dev(a, torch.bfloat16), dev(b, torch.bfloat16), bias=dev(bias), alpha=0.25, **kw))
+    close_bf16(got16, want, rel=6e-3)
+    if not r:        # f32 outputs take the K split, which has no second segment
+        assert ops.gemm_nt_tile_cols(m, n, k, 0, torch.float32) == 384
+        got = host(ops.gemm_nt(dev(a, torch.bfloat16), dev(b, torch.bfloat16), bias=dev(bias), alpha=0.25, out_dtype=torch.float32))
+        assert rel_err(got, want) < 1e-4
+    assert ops.device_status() == 0
+
+
 def test_gemm_rejects_bad_arguments(ops):
     from mobilefinetuner_b200._lib import MftError
     a = torch.zeros(8, 12, device="cuda", dtype=torch.bfloat16)   # row stride 12: not a multiple of 8
