@@ -229,6 +229,98 @@ __device__ __forceinline__ bool epilogue_glu_fwd(const GemmParams& p, const CUte
     return true;
 }
 
+__device__ __forceinline__ uint32_t ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
+    return a;
+}
+
+// ---- staged epilogue of the 256 x 384 tile (bf16 outputs).  The CTA's 128 x 384 accumulator goes, rounded to bf16, into
+// 24 boxes of 32 rows x 64 columns (box = quadrant * 6 + 64-column chunk of the accumulator), the tensor memory is
+// released, and the boxes are stored afterwards.  `side` 0 / 1 = the warp's 32-column half of every chunk.
+// Gated MLP: the chunks of the accumulator are gate 0, gate 1, up 0, up 1, gate 2, up 2 (64 columns each).
+__device__ __forceinline__ int staged_glu_kind(int chunk) { return (0x2C >> chunk) & 1; }           // 1 = up
+__device__ __forceinline__ int staged_glu_index(int chunk) { return chunk < 4 ? (chunk & 1) : 2; }   // 64-column block within gate / up
+// Chunks [CH0, CH1) of the accumulator.  The tensor-memory load of the next chunk is in flight while this one is
+// scaled, rounded and written (tcgen05.wait::ld waits for every load issued before it, so the next load is issued
+// after the wait and before the arithmetic).
+template <int EPI, int CH0, int CH1>
+__device__ __forceinline__ void staged_drain(const GemmParams& p, uint8_t* staging, uint32_t taddr, int q, int side, int lane, int n0) {
+    using namespace ptx;
+    uint32_t r[2][32];
+    tmem_ld_32x32(taddr + (uint32_t)(CH0 * 64 + side * 32), r[0]);
+    tmem_ld_wait();
+#pragma unroll
+    for (int ch = CH0; ch < CH1; ++ch) {
+        const int cur = (ch - CH0) & 1;
+        if (ch + 1 < CH1) tmem_ld_32x32(taddr + (uint32_t)((ch + 1) * 64 + side * 32), r[cur ^ 1]);
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[cur][j]) * p.alpha;
+        if (p.bias) {
+            const int col0 = (EPI == EPI_GLU_FWD ? staged_glu_kind(ch) * p.glu_inter + n0 + staged_glu_index(ch) * 64 : n0 + ch * 64) + side * 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + col0 + j);
+        }
+        epi_pack_store_half(smem_u32(staging + (q * 6 + ch) * EPI_BOX_BYTES) + (uint32_t)lane * 128u, side, lane, v);
+        if (ch + 1 < CH1) tmem_ld_wait();
+    }
+}
+// Plain store: epilogue warp `ew` of 8 stores boxes ew, ew + 8, ew + 16 (one lane issues).
+__device__ __forceinline__ void staged_store_plain(const CUtensorMap* map_d, uint8_t* staging, int ew, int lane, int m0, int n0) {
+    using namespace ptx;
+    if (lane != 0) return;
+    for (int b = ew; b < 24; b += 8) tma_store_2d(map_d, staging + b * EPI_BOX_BYTES, n0 + (b % 6) * 64, m0 + (b / 6) * 32);
+    tma_store_commit();
+}
+// Gated MLP: epilogue warp `ew` takes the (gate, up) box pairs ew and ew + 8 of the CTA's 12 (quadrant * 3 + block): it
+// forms f(gate) * up of its 32 rows x 64 columns from the staged bf16 values (bit-identical to the stand-alone
+// activation kernel on the stored tensors), stores the gate and up boxes into D, waits until those stores have read
+// them, writes the result over the gate box and stores that into the act tensor.
+__device__ __forceinline__ void staged_store_glu(const GemmParams& p, const CUtensorMap* map_d, const CUtensorMap* map_act, uint8_t* staging,
+                                                 int ew, int lane, int m0, int g0) {
+    using namespace ptx;
+    const bool geglu = p.glu_geglu != 0;
+#pragma unroll 1
+    for (int pr = ew; pr < 12; pr += 8) {
+        const int qq = pr / 3, j = pr % 3;
+        uint8_t* gbox = staging + (qq * 6 + (j < 2 ? j : 4)) * EPI_BOX_BYTES;
+        uint8_t* ubox = staging + (qq * 6 + (j < 2 ? 2 + j : 5)) * EPI_BOX_BYTES;
+        const uint32_t g_addr = smem_u32(gbox) + (uint32_t)lane * 128u, u_addr = smem_u32(ubox) + (uint32_t)lane * 128u;
+        uint32_t act[32];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t pos = (uint32_t)(u ^ (lane & 7)) * 16u;
+            uint32_t gw[4], uw[4];
+            ld_shared_v4(g_addr + pos, gw[0], gw[1], gw[2], gw[3]);
+            ld_shared_v4(u_addr + pos, uw[0], uw[1], uw[2], uw[3]);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float2 g2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[w]));
+                const float2 u2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[w]));
+                const __nv_bfloat162 a2 = __floats2bfloat162_rn(glu_fwd(geglu, g2.x, u2.x), glu_fwd(geglu, g2.y, u2.y));
+                act[4 * u + w] = *reinterpret_cast<const uint32_t*>(&a2);
+            }
+        }
+        __syncwarp();                           // every lane has read its rows of both boxes
+        if (lane == 0) {
+            tma_store_2d(map_d, gbox, g0 + j * 64, m0 + qq * 32);
+            tma_store_2d(map_d, ubox, p.glu_inter + g0 + j * 64, m0 + qq * 32);
+            tma_store_commit();
+            tma_store_wait_read<0>();
+        }
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            st_shared_v4(g_addr + (uint32_t)(u ^ (lane & 7)) * 16u, act[4 * u], act[4 * u + 1], act[4 * u + 2], act[4 * u + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(map_act, gbox, g0 + j * 64, m0 + qq * 32);
+            tma_store_commit();
+        }
+    }
+}
+
 // ---- gated MLP, backward.  The accumulator holds d(act) for 128 rows x 256 columns of [M, inter].  Per 64-column
 // chunk the warp loads the matching boxes of the saved gate and up activations with TMA (GLU_SETS sets of two boxes per
 // warp: the loads of the next chunk are in flight while this one is computed), forms d_gate and d_up IN PLACE in those
@@ -243,10 +335,6 @@ struct GluBwdState {
     int chunk = 0;               // chunks this warp has been through (selects the box set and the barrier parity)
     int ahead_tile = 0, ahead_c = 0, issued = 0;   // next chunk whose gate / up boxes have not been requested yet
 };
-__device__ __forceinline__ uint32_t ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
-    return a;
-}
 // Requests the boxes of the next not-yet-requested chunk (one lane calls this).  Tiles of this cluster are
 // first_tile, first_tile + tile_step, ...; a tile has up to four 64-column chunks.
 __device__ __forceinline__ void glu_bwd_prefetch(const GemmParams& p, const CUtensorMap* map_gu, uint8_t* boxes, uint64_t* bars, int q, int rank,

@@ -41,16 +41,24 @@ constexpr int STORE_BYTES = 4 * 2 * EPI_BOX_BYTES;
 // the K loop is long against the epilogue.  One k-step is two MMAs of 192 columns, each reading 96 B rows per CTA.
 // The gated-MLP backward epilogue keeps GLU_SETS sets of (gate, up) boxes per warp (loaded by TMA, rewritten in place,
 // stored by TMA): twice the box memory of the other epilogues, paid for with one pipeline stage.
-template <int EPI, int BN2>
+// STAGED (wide tiles with a bf16 output): the epilogue first moves the whole accumulator of the CTA, rounded to bf16,
+// into a 96 KB staging area of 24 swizzled boxes, hands the tensor memory back to the MMA issuer, and only then stores
+// the boxes (and, for the gated MLP, forms f(gate) * up from the staged values), which overlaps with the next tile's
+// K loop.  That keeps the exposed part of the epilogue short enough for K = 1152.  The staging area costs one pipeline
+// stage (3 x 40 KB in flight measured 2 % slower than 4 on the long-K shapes).
+template <int EPI, int BN2, bool STAGED>
 struct PairCfg {
     static constexpr int BH_BYTES = (BN2 / 2) * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + BH_BYTES;                  // 32 / 28 KB, multiples of 1024
-    static constexpr int BOX_BYTES = EPI == EPI_GLU_BWD ? GLU_SETS * STORE_BYTES : STORE_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + BH_BYTES;                  // 32 / 40 KB, multiples of 1024
+    static constexpr int STAGING_BYTES = BM * BN2 * 2;
+    static constexpr int BOX_BYTES = EPI == EPI_GLU_BWD ? GLU_SETS * STORE_BYTES : (STAGED ? STAGING_BYTES : STORE_BYTES);
     static constexpr bool WIDE = BN2 > 256;
     static constexpr int ACC_BUFS = WIDE ? 1 : 2;
-    static constexpr int MMA_N = WIDE ? BN2 / 2 : BN2;                      // columns of one MMA instruction
-    static constexpr int STAGES = EPI == EPI_GLU_BWD ? 8 - GLU_SETS - 1 : (WIDE ? 4 : 6);
-    static_assert(!WIDE || (EPI == EPI_STORE && BN2 == 384), "the wide tile is built for the plain store epilogue");
+    static constexpr int MMA_N = WIDE ? BN2 / 2 : BN2;                      // columns of one MMA instruction (plain wide tile)
+    static constexpr int STAGES = EPI == EPI_GLU_BWD ? 8 - GLU_SETS - 1 : (STAGED ? 3 : (WIDE ? 4 : 6));
+    static_assert(!WIDE || BN2 == 384, "wide tiles are 384 columns");
+    static_assert(!WIDE || EPI == EPI_STORE || (EPI == EPI_GLU_FWD && STAGED), "wide tiles: plain store, or the staged gated-MLP forward");
+    static_assert(!STAGED || WIDE, "the staged epilogue belongs to the wide tile");
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BOX_BYTES + 1024 + BAR_BYTES;
 };
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;   // clears the bit that distinguishes the two CTAs of a pair: -> address in the leader
@@ -77,6 +85,20 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
         : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1)
         : "memory");
 }
+// named barrier 1 over the 8 epilogue warps; the second form also tells every thread whether `ok` held in all of them
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory"); }
+__device__ __forceinline__ bool epi_barrier_and(bool ok) {
+    uint32_t all;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(all)
+        : "r"((uint32_t)ok), "n"(32 * EPI_WARPS)
+        : "memory");
+    return all != 0;
+}
 __device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols) : "memory");
 }
@@ -100,17 +122,24 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
-template <int EPI, int BN2>
+template <int EPI, int BN2, bool STAGED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                     const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
     dep_trigger();
-    constexpr int STAGES = PairCfg<EPI, BN2>::STAGES, STAGE_BYTES = PairCfg<EPI, BN2>::STAGE_BYTES;
-    constexpr int BOX_BYTES = PairCfg<EPI, BN2>::BOX_BYTES;
-    constexpr bool WIDE = PairCfg<EPI, BN2>::WIDE;
-    constexpr int ACC_BUFS = PairCfg<EPI, BN2>::ACC_BUFS, MMA_N = PairCfg<EPI, BN2>::MMA_N;
+    using Cfg = PairCfg<EPI, BN2, STAGED>;
+    constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int BOX_BYTES = Cfg::BOX_BYTES;
+    constexpr bool WIDE = Cfg::WIDE;
+    constexpr int ACC_BUFS = Cfg::ACC_BUFS, MMA_N = Cfg::MMA_N;
     constexpr bool GLU_FWD = EPI == EPI_GLU_FWD, GLU_BWD = EPI == EPI_GLU_BWD;
+    // wide tile, per CTA 192 rows of B in two boxes of 96.  Plain: two MMAs of 192 columns, the pair's first takes B rows
+    // 0..95 of each CTA (columns 0..191 of the tile), the second rows 96..191.  Gated MLP: the leader holds 192 gate rows,
+    // the peer the 192 matching up rows; an MMA of 256 columns over rows 0..127 of each CTA (accumulator columns 0..127
+    // gate, 128..255 up) and one of 128 columns over rows 128..191 (256..319 gate, 320..383 up) keep every 64-column
+    // chunk of the accumulator on one side.
+    constexpr int N_LO = !WIDE ? BN2 : (GLU_FWD ? 256 : MMA_N), N_HI = BN2 - N_LO;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* store_smem = tiles + STAGES * STAGE_BYTES;
@@ -166,8 +195,8 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int n_eff = min(BN2, (p.n - n_base + 15) & ~15);
                 // gated-MLP forward: the leader loads 128 gate rows of the weight, the peer the 128 matching up rows
                 // wide tile: the pair's first MMA takes columns 0..191 (96 B rows from each CTA), the second 192..383
-                const int n0 = WIDE ? n_base + (int)rank * (MMA_N / 2)
-                             : GLU_FWD ? tile_n(t2, p) * (BN2 / 2) + (int)rank * p.glu_inter : n_base + (int)rank * (n_eff / 2);
+                const int n0 = GLU_FWD ? tile_n(t2, p) * (BN2 / 2) + (int)rank * p.glu_inter
+                             : WIDE ? n_base + (int)rank * (MMA_N / 2) : n_base + (int)rank * (n_eff / 2);
                 const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
@@ -180,7 +209,7 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int k0 = kb < num_kb_main ? kb * BK : 0;
                     tma_load_2d_pair(sa, ta, full_in_leader, k0, m0);
                     tma_load_2d_pair(sb, tb, full_in_leader, k0, n0);
-                    if (WIDE) tma_load_2d_pair(sb + (MMA_N / 2) * BK * 2, tb, full_in_leader, k0, n0 + MMA_N);
+                    if (WIDE) tma_load_2d_pair(sb + (BN2 / 4) * BK * 2, tb, full_in_leader, k0, n0 + (GLU_FWD ? BN2 / 4 : MMA_N));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -200,7 +229,8 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int split = tile / p.tiles_mn;
                 const int kb0 = split * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
                 const int n_base = tile_n(tile % p.tiles_mn, p) * BN2;
-                const uint32_t idesc = idesc_bf16_f32(2 * BM, (GLU_FWD || WIDE) ? (uint32_t)MMA_N : (uint32_t)min(BN2, (p.n - n_base + 15) & ~15));
+                const uint32_t idesc = idesc_bf16_f32(2 * BM, WIDE ? (uint32_t)N_LO : GLU_FWD ? (uint32_t)BN2 : (uint32_t)min(BN2, (p.n - n_base + 15) & ~15));
+                const uint32_t idesc_hi = idesc_bf16_f32(2 * BM, WIDE ? (uint32_t)N_HI : 16u);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
@@ -209,11 +239,24 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint64_t bdesc = smem_desc_sw128(sa + A_BYTES);
                     const int kvalid = (kb < num_kb_main) ? min(BK, p.k - kb * BK) : p.k2;
                     const int nmma = (kvalid + 15) / 16;
-                    for (int j = 0; j < nmma; ++j) {
-                        umma2_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb > kb0 || j != 0) ? 1u : 0u);
-                        if (WIDE) {
-                            const uint64_t bdesc_hi = smem_desc_sw128(sa + A_BYTES + (MMA_N / 2) * BK * 2);
-                            umma2_bf16(tmem_d + MMA_N, adesc + (uint64_t)(2 * j), bdesc_hi + (uint64_t)(2 * j), idesc, (kb > kb0 || j != 0) ? 1u : 0u);
+                    if (STAGED && kb == kb0) {
+                        // first k-block of a tile: the second MMA's columns come back from the epilogue after the first's.
+                        // (This wait sits outside the loop that issues the MMAs: with a conditional wait inside that loop
+                        // every k-block of the call measured 40 % slower.)
+                        for (int j = 0; j < nmma; ++j)
+                            umma2_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, j != 0 ? 1u : 0u);
+                        if (!mbar_wait(&tmem_empty_bar[1], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint64_t bdesc_hi = smem_desc_sw128(sa + A_BYTES + (N_LO / 2) * BK * 2);
+                        for (int j = 0; j < nmma; ++j)
+                            umma2_bf16(tmem_d + N_LO, adesc + (uint64_t)(2 * j), bdesc_hi + (uint64_t)(2 * j), idesc_hi, j != 0 ? 1u : 0u);
+                    } else {
+                        for (int j = 0; j < nmma; ++j) {
+                            umma2_bf16(tmem_d, adesc + (uint64_t)(2 * j), bdesc + (uint64_t)(2 * j), idesc, (kb > kb0 || j != 0) ? 1u : 0u);
+                            if (WIDE) {
+                                const uint64_t bdesc_hi = smem_desc_sw128(sa + A_BYTES + (N_LO / 2) * BK * 2);
+                                umma2_bf16(tmem_d + N_LO, adesc + (uint64_t)(2 * j), bdesc_hi + (uint64_t)(2 * j), idesc_hi, (kb > kb0 || j != 0) ? 1u : 0u);
+                            }
                         }
                     }
                     umma2_commit_both(&empty_bar[stage]);
@@ -222,6 +265,36 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (ok) umma2_commit_both(&tmem_full_bar[acc]);
             }
         }
+    } else if constexpr (STAGED) {
+        // ------------------------------------------------ staged epilogue of the wide tile (see PairCfg)
+        const int q = warp & 3, ew = warp - 2, side = ew >> 2;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+        int it = 0;
+        for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
+            const int t2 = tile % p.tiles_mn;
+            const int m0 = tile_m(t2, p) * 2 * BM + (int)rank * BM;
+            const int n0 = GLU_FWD ? tile_n(t2, p) * (BN2 / 2) : tile_n(t2, p) * BN2;
+            const bool landed = mbar_wait(&tmem_full_bar[0], (uint32_t)(it & 1), abort_flag);
+            if (lane == 0) tma_store_wait_read<0>();       // this warp's stores of the previous tile have read their boxes
+            // every epilogue warp is here: the staging area is free, and all of them go on or all of them stop
+            if (!epi_barrier_and(landed)) break;
+            tc_fence_after();
+            // the columns of the tile's first MMA are handed back first (barrier 0), the second MMA's after them (1)
+            constexpr int LO_CHUNKS = N_LO / 64;
+            staged_drain<EPI, 0, LO_CHUNKS>(p, store_smem, taddr, q, side, lane, n0);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[0]) & PEER_MASK);   // count: 8 warps x 2 CTAs
+            staged_drain<EPI, LO_CHUNKS, 6>(p, store_smem, taddr, q, side, lane, n0);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[1]) & PEER_MASK);
+            fence_proxy_async();
+            epi_barrier();                                 // the whole staging area is written
+            if constexpr (GLU_FWD) staged_store_glu(p, &map_d, &map_x, store_smem, ew, lane, m0, n0);
+            else staged_store_plain(&map_d, store_smem, ew, lane, m0, n0);
+        }
+        if (lane == 0) tma_store_wait<0>();
     } else {
         // ------------------------------------------------ epilogue: this CTA's 128 rows of the pair tile
         const int q = warp & 3;
@@ -279,62 +352,66 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-template <int EPI, int BN2>
+template <int EPI, int BN2, bool STAGED = false>
 int32_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2, const CUtensorMap& mb2, const CUtensorMap& md,
                const CUtensorMap& mx, GemmParams p, cudaStream_t stream) {
-    using Cfg = PairCfg<EPI, BN2>;
+    using Cfg = PairCfg<EPI, BN2, STAGED>;
     static PerDeviceFlag configured_on;           // function attributes are per device
     bool& configured = configured_on.here();
     if (!configured) {
-        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_2cta_kernel<EPI, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm 2cta smem attr")) return s;
+        if (int32_t s = check_cuda(cudaFuncSetAttribute(gemm_nt_2cta_kernel<EPI, BN2, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES), "gemm 2cta smem attr")) return s;
         configured = true;
     }
     const int tiles = p.tiles_mn * p.splits;
     int clusters = num_sms() / 2;
     if (tiles < clusters) clusters = tiles;
-    launch_dep(gemm_nt_2cta_kernel<EPI, BN2>, dim3(2 * clusters), dim3(THREADS), (size_t)(Cfg::SMEM_BYTES), stream, ma, mb, ma2, mb2, md, mx, p);
+    launch_dep(gemm_nt_2cta_kernel<EPI, BN2, STAGED>, dim3(2 * clusters), dim3(THREADS), (size_t)(Cfg::SMEM_BYTES), stream, ma, mb, ma2, mb2, md, mx, p);
     MFT_LAUNCH_CHECK("gemm_nt_2cta");
     return MFT_OK;
 }
 
 // Cost of a call in units of one k-block of a 256 x 256 tile: waves of tiles over the clusters times the k-blocks of a
 // tile (plus a per-tile charge), each extra K range charged 0.2 % for its pass over D.  A k-block of a 384-wide tile
-// measured 1.16 of a 256-wide one for 1.5 times the columns (1157 against about 1000 clocks at 16384 x 1152 x 6912 and
-// x 13824), and its per-tile charge is larger because its epilogue (about 7000 clocks) is not overlapped.  A ragged last
-// column tile counts as a full one: narrowing its MMAs was measured to save nothing, the main loop is bound by
-// operand delivery.
-double tile_cost(int64_t m, int64_t n, int64_t kb, int bn, int sp) {
-    const int64_t clusters = num_sms() / 2, tiles_mn = ((m + 255) / 256) * ((n + bn - 1) / bn);
-    const int64_t per = (kb + sp - 1) / sp, waves = (tiles_mn * sp + clusters - 1) / clusters;
-    const double unit = bn > 256 ? 1.16 : 1.0, per_tile = bn > 256 ? 10.0 : 4.0;
-    return (double)waves * ((double)per + per_tile) * unit * (1.0 + 0.002 * (sp - 1));
+// measured 1.25 of a 256-wide one for 1.5 times the columns (0.643 against 0.515 us at 16384 x 1152 x 6912 and
+// x 13824).  Its per-tile charge: the streaming epilogue of the f32 output (about 7000 clocks) is not overlapped; the
+// staged one leaves a gap of about 3000 clocks in which no operand requests are in flight.  A ragged last column tile
+// counts as a full one: narrowing its MMAs was measured to save nothing, the main loop is bound by operand delivery.
+struct TileShape { int64_t m_tiles, n_tiles; bool wide, staged; };
+double tile_cost(const TileShape& t, int64_t kb, int sp) {
+    const int64_t clusters = num_sms() / 2;
+    const int64_t per = (kb + sp - 1) / sp, waves = (t.m_tiles * t.n_tiles * sp + clusters - 1) / clusters;
+    const double unit = t.wide ? 1.25 : 1.0, per_tile = t.wide ? (t.staged ? 6.5 : 11.0) : 4.0;
+    return (double)waves * ((double)per * unit + per_tile) * (1.0 + 0.002 * (sp - 1));
 }
 // Number of K ranges for an f32 output whose caller leaves the choice open, and the cost of that choice.
-int choose_splits(int64_t m, int64_t n, int64_t kb, int bn, double* cost_out) {
+int choose_splits(const TileShape& t, int64_t kb, double* cost_out) {
     int best_sp = 1;
     double best = 1e300;
     for (int sp = 1; sp <= 8; ++sp) {
-        if (sp > 1 && kb / sp < (bn > 256 ? 64 : 32)) break;
-        const double cost = tile_cost(m, n, kb, bn, sp);
+        if (sp > 1 && kb / sp < (t.wide ? 64 : 32)) break;
+        const double cost = tile_cost(t, kb, sp);
         if (cost < best * 0.995) { best = cost; best_sp = sp; }
     }
     if (cost_out) *cost_out = best;
     return best_sp;
 }
 
-// Tile width (256 or 384 columns) and number of K ranges of a call.  `asked` = the caller's K ranges, 0 = choose.
-int plan_tiles(int64_t m, int64_t n, int64_t kb, bool wide_fits, bool can_split, int asked, int* splits_out) {
+// Tile width (256 or 384 columns) and number of K ranges of a call.  n_tiles_wide = 0: the call has no whole 384-column
+// tiles.  `staged`: bf16 output (the wide tile's epilogue is the staged one; otherwise its K loop must be at least
+// 64 blocks long).  `asked` = the caller's K ranges, 0 = choose.  MFT_GEMM_WIDE=0 keeps every call on 256-wide tiles.
+int plan_tiles(int64_t m, int64_t n_tiles, int64_t n_tiles_wide, int64_t kb, bool staged, bool can_split, int asked, int* splits_out) {
     static const bool wide_allowed = [] { const char* e = std::getenv("MFT_GEMM_WIDE"); return !(e && e[0] == '0'); }();
-    wide_fits = wide_fits && wide_allowed;
+    const TileShape t256{(m + 255) / 256, n_tiles, false, false}, t384{(m + 255) / 256, n_tiles_wide, true, staged};
+    const bool wide_fits = wide_allowed && n_tiles_wide > 0 && m % 256 == 0;
     bool wide = false;
     int splits = 1;
     if (!can_split || asked > 0) {
         splits = can_split ? asked : 1;
-        wide = wide_fits && kb / splits >= 64 && tile_cost(m, n, kb, 384, splits) < tile_cost(m, n, kb, 256, splits);
+        wide = wide_fits && (staged || kb / splits >= 64) && tile_cost(t384, kb, splits) < tile_cost(t256, kb, splits);
     } else {
         double cost256 = 0, cost384 = 0;
-        const int sp256 = choose_splits(m, n, kb, 256, &cost256);
-        const int sp384 = wide_fits && kb >= 64 ? choose_splits(m, n, kb, 384, &cost384) : 0;
+        const int sp256 = choose_splits(t256, kb, &cost256);
+        const int sp384 = wide_fits && (staged || kb >= 64) ? choose_splits(t384, kb, &cost384) : 0;
         wide = sp384 > 0 && cost384 < cost256;
         splits = wide ? sp384 : sp256;
     }
@@ -349,7 +426,7 @@ int gemm_nt_pair_tile_cols(int64_t m, int64_t n, int64_t k, int64_t k2, bool d_i
     if (m < 256 || n < 192) return 0;
     const int64_t kb = (k + BK - 1) / BK + (k2 > 0 ? 1 : 0);
     int splits = 1;
-    return plan_tiles(m, n, kb, n % 384 == 0 && m % 256 == 0, d_is_f32 && k2 == 0, 0, &splits);
+    return plan_tiles(m, (n + 255) / 256, n % 384 == 0 ? n / 384 : 0, kb, !d_is_f32, d_is_f32 && k2 == 0, 0, &splits);
 }
 
 int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
@@ -370,13 +447,12 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     const bool can_split = f32_ok && c.k2 == 0;
     if (c.splits > 1 && !can_split) return MFT_ERR_UNSUPPORTED;
     const int64_t kb = (c.k + BK - 1) / BK + (c.k2 > 0 ? 1 : 0);
-    // the wide tile: plain store, whole 384-column tiles, a K loop of at least 64 blocks per tile, against which the
-    // tile's unoverlapped epilogue is small, and enough tiles that the cost model prefers it (a call of a few tiles is
-    // one wave either way, and the wave of wide tiles is the longer one).  MFT_GEMM_WIDE=0 keeps every call on
-    // 256-wide tiles.
-    const bool wide_fits = c.epi == EPI_STORE && c.n % 384 == 0 && c.m % 256 == 0;
+    // the wide tile: plain store or gated-MLP forward over whole 384-column tiles, when the cost model prefers it (a call
+    // of a few tiles is one wave either way, and the wave of wide tiles is the longer one)
     int splits = 1;
-    const int bn = plan_tiles(c.m, c.n, kb, wide_fits, can_split, (int)c.splits, &splits);
+    int bn = 256;
+    if (c.epi == EPI_STORE) bn = plan_tiles(c.m, (c.n + 255) / 256, c.n % 384 == 0 ? c.n / 384 : 0, kb, bf16_ok, can_split, (int)c.splits, &splits);
+    else if (c.epi == EPI_GLU_FWD) bn = plan_tiles(c.m, c.glu_inter / 128, c.glu_inter % 192 == 0 ? c.glu_inter / 192 : 0, kb, true, false, 0, &splits);
     const bool wide = bn > 256;
     CUtensorMap ma, mb, ma2, mb2, md, mx;
     if (int32_t s = make_tmap_bf16(&ma, c.a, c.m, c.k, c.lda, BM)) return s;
@@ -407,7 +483,7 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     p.ce_partials = c.ce_partials; p.ce_partial_ld = c.ce_partial_ld; p.ce_tgt_logit = c.ce_tgt_logit; p.ce_flag = c.ce_flag;
     p.glu_geglu = c.glu_geglu; p.glu_inter = (int)c.glu_inter;
     p.num_m_tiles = (p.m + 2 * BM - 1) / (2 * BM);
-    p.num_n_tiles = c.epi == EPI_GLU_FWD ? (int)(c.glu_inter / 128) : (p.n + bn - 1) / bn;
+    p.num_n_tiles = c.epi == EPI_GLU_FWD ? (int)(c.glu_inter / (bn / 2)) : (p.n + bn - 1) / bn;
     p.tiles_mn = p.num_m_tiles * p.num_n_tiles;
     p.kb_per_split = (int)((kb + splits - 1) / splits);
     p.splits = (int)((kb + p.kb_per_split - 1) / p.kb_per_split);
@@ -417,8 +493,10 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     }
     if (c.epi == EPI_CE_GRAD) return launch<EPI_CE_GRAD, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
     if (c.epi == EPI_CE_P) return launch<EPI_CE_P, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
+    if (c.epi == EPI_GLU_FWD && wide) return launch<EPI_GLU_FWD, 384, true>(ma, mb, ma2, mb2, md, mx, p, stream);
     if (c.epi == EPI_GLU_FWD) return launch<EPI_GLU_FWD, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
     if (c.epi == EPI_GLU_BWD) return launch<EPI_GLU_BWD, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
+    if (wide && !c.d_is_f32) return launch<EPI_STORE, 384, true>(ma, mb, ma2, mb2, md, mx, p, stream);
     if (wide) return launch<EPI_STORE, 384>(ma, mb, ma2, mb2, md, mx, p, stream);
     return launch<EPI_STORE, 256>(ma, mb, ma2, mb2, md, mx, p, stream);
 }

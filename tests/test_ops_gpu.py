@@ -93,7 +93,7 @@ def test_gemm_nt_wide_tile_long_k(ops, m, n, k, r):
     bias and alpha."""
     assert ops.gemm_nt_tile_cols(m, n, k, r) == 384
     assert ops.gemm_nt_tile_cols(512, 384, 4096) == 256          # two tiles: one wave either way
-    assert ops.gemm_nt_tile_cols(m, n, 1152, r) == 256           # short K: the unoverlapped epilogue would show
+    assert ops.gemm_nt_tile_cols(m, n, 1152, r, torch.float32) == 256      # f32 output under a short K: its epilogue is not overlapped
     g = np.random.Generator(np.random.PCG64(m + n + k))
     a, b = rb(g.standard_normal((m, k))), rb(g.standard_normal((n, k)) * 0.05)
     bias = g.standard_normal(n).astype(np.float32)
@@ -198,7 +198,8 @@ def test_lora_linear_model_width(ops):
 
 # ------------------------------------------------------------------ gated MLP fused into the GEMM epilogues
 @pytest.mark.parametrize("kind_name,m,inter,k,r,with_bias", [("geglu", 512, 256, 128, 16, False), ("geglu", 300, 384, 200, 0, False),
-                                                             ("swiglu", 1024, 4864, 896, 16, True), ("geglu", 768, 6912, 1152, 32, False)])
+                                                             ("swiglu", 1024, 4864, 896, 16, True), ("geglu", 768, 6912, 1152, 32, False),
+                                                             ("swiglu", 4096, 1536, 640, 16, True)])
 def test_fused_gated_mlp_equals_gemm_plus_activation_kernel(ops, kind_name, m, inter, k, r, with_bias):
     """mft_glu_linear_fwd / _bwd (gating inside the CTA-pair GEMM's epilogue) against the same GEMM followed by the
     stand-alone activation kernels, which are pinned to the reference's golden vectors: bit-identical by construction
