@@ -228,9 +228,10 @@ int32_t mft_gemm_nt(const void* a_bf16, int64_t lda, const void* b_bf16, int64_t
                     const float* bias, float alpha,
                     void* d, int64_t ldd, int32_t d_dtype, int32_t accumulate,
                     mft_stream_t stream);
-/* Tile plan of mft_gemm_nt for a call of this shape without bias-independent options: *tile_cols_host = columns of
- * the CTA-pair kernel's tile (256; 384 for a width that is a multiple of 384 under a K of at least 4096 when the
- * call has enough tiles), or 0 when another kernel takes the call.  Needs an initialised device (SM count). */
+/* Tile plan of mft_gemm_nt for a plain call (no accumulate) of this shape: *tile_cols_host = columns of the CTA-pair
+ * kernel's tile - 256, or 384 when the width is a multiple of 384, m a multiple of 256 and the cost model (waves of
+ * tiles x k-blocks per tile) prefers the wider tile; f32 outputs take it only under at least 64 k-blocks per tile - or
+ * 0 when another kernel takes the call.  Needs an initialised device (the SM count enters the plan). */
 int32_t mft_gemm_nt_tile_cols(int64_t m, int64_t n, int64_t k, int64_t k2, int32_t d_dtype, int32_t* tile_cols_host);
 /* Measurement aid: while enabled, every tensor-core GEMM launch (mft_gemm_nt and the GEMMs inside
  * the lm-head routines) is bracketed by CUDA events on its stream.  The report sums the

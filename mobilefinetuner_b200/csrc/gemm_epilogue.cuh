@@ -258,18 +258,21 @@ __device__ __forceinline__ void staged_drain(const GemmParams& p, uint8_t* stagi
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[cur][j]) * p.alpha;
         if (p.bias) {
             const int col0 = (EPI == EPI_GLU_FWD ? staged_glu_kind(ch) * p.glu_inter + n0 + staged_glu_index(ch) * 64 : n0 + ch * 64) + side * 32;
+            const int col_end = EPI == EPI_GLU_FWD ? 2 * p.glu_inter : p.n;     // a ragged last tile of the plain store
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + col0 + j);
+            for (int j = 0; j < 32; ++j) if (col0 + j < col_end) v[j] += __ldg(p.bias + col0 + j);
         }
         epi_pack_store_half(smem_u32(staging + (q * 6 + ch) * EPI_BOX_BYTES) + (uint32_t)lane * 128u, side, lane, v);
         if (ch + 1 < CH1) tmem_ld_wait();
     }
 }
 // Plain store: epilogue warp `ew` of 8 stores boxes ew, ew + 8, ew + 16 (one lane issues).
-__device__ __forceinline__ void staged_store_plain(const CUtensorMap* map_d, uint8_t* staging, int ew, int lane, int m0, int n0) {
+__device__ __forceinline__ void staged_store_plain(const CUtensorMap* map_d, uint8_t* staging, int ew, int lane, int m0, int n0, int n) {
     using namespace ptx;
     if (lane != 0) return;
-    for (int b = ew; b < 24; b += 8) tma_store_2d(map_d, staging + b * EPI_BOX_BYTES, n0 + (b % 6) * 64, m0 + (b / 6) * 32);
+    for (int b = ew; b < 24; b += 8)
+        if (n0 + (b % 6) * 64 < n)          // boxes past the last column of a ragged tile are not stored; a box across it is clipped
+            tma_store_2d(map_d, staging + b * EPI_BOX_BYTES, n0 + (b % 6) * 64, m0 + (b / 6) * 32);
     tma_store_commit();
 }
 // Gated MLP: epilogue warp `ew` takes the (gate, up) box pairs ew and ew + 8 of the CTA's 12 (quadrant * 3 + block): it

@@ -292,7 +292,7 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             fence_proxy_async();
             epi_barrier();                                 // the whole staging area is written
             if constexpr (GLU_FWD) staged_store_glu(p, &map_d, &map_x, store_smem, ew, lane, m0, n0);
-            else staged_store_plain(&map_d, store_smem, ew, lane, m0, n0);
+            else staged_store_plain(&map_d, store_smem, ew, lane, m0, n0, p.n);
         }
         if (lane == 0) tma_store_wait<0>();
     } else {
@@ -426,7 +426,7 @@ int gemm_nt_pair_tile_cols(int64_t m, int64_t n, int64_t k, int64_t k2, bool d_i
     if (m < 256 || n < 192) return 0;
     const int64_t kb = (k + BK - 1) / BK + (k2 > 0 ? 1 : 0);
     int splits = 1;
-    return plan_tiles(m, (n + 255) / 256, n % 384 == 0 ? n / 384 : 0, kb, !d_is_f32, d_is_f32 && k2 == 0, 0, &splits);
+    return plan_tiles(m, (n + 255) / 256, n >= 384 ? (n + 383) / 384 : 0, kb, !d_is_f32, d_is_f32 && k2 == 0, 0, &splits);
 }
 
 int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
@@ -451,7 +451,8 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     // of a few tiles is one wave either way, and the wave of wide tiles is the longer one)
     int splits = 1;
     int bn = 256;
-    if (c.epi == EPI_STORE) bn = plan_tiles(c.m, (c.n + 255) / 256, c.n % 384 == 0 ? c.n / 384 : 0, kb, bf16_ok, can_split, (int)c.splits, &splits);
+    // a ragged last 384-column tile is computed whole (the rows of B past N arrive as zeros) and stored clipped
+    if (c.epi == EPI_STORE) bn = plan_tiles(c.m, (c.n + 255) / 256, c.n >= 384 ? (c.n + 383) / 384 : 0, kb, bf16_ok, can_split, (int)c.splits, &splits);
     else if (c.epi == EPI_GLU_FWD) bn = plan_tiles(c.m, c.glu_inter / 128, c.glu_inter % 192 == 0 ? c.glu_inter / 192 : 0, kb, true, false, 0, &splits);
     const bool wide = bn > 256;
     CUtensorMap ma, mb, ma2, mb2, md, mx;

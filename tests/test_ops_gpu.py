@@ -86,7 +86,8 @@ def test_gemm_nt_f32_deep_k_is_split_and_reduced(ops, m, n, k, accumulate):
     assert ops.device_status() == 0
 
 
-@pytest.mark.parametrize("m,n,k,r", [(4096, 1152, 4096, 16), (8192, 768, 4128, 32), (4096, 1152, 8192, 0), (16384, 384, 4096, 0)])
+@pytest.mark.parametrize("m,n,k,r", [(4096, 1152, 4096, 16), (8192, 768, 4128, 32), (4096, 1152, 8192, 0), (16384, 384, 4096, 0),
+                                     (16384, 640, 2048, 8), (16384, 1000, 4096, 8)])   # the last two: a ragged last column tile
 def test_gemm_nt_wide_tile_long_k(ops, m, n, k, r):
     """Outputs whose width is a multiple of 384 under K >= 4096 run on 256 x 384 tiles with one accumulator buffer
     (two 192-column MMAs per k-step) when the call has enough tiles; bf16 and f32 outputs, with the LoRA segment,
