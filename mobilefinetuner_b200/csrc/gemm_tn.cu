@@ -294,7 +294,8 @@ extern "C" int32_t mft_gemm_tn_acc(const void* u, int64_t ldu, const void* v, in
         splits = (t + t_per - 1) / t_per;
         CUtensorMap mu, mv;
         if (make_tmap_bf16(&mu, uu, t, pp, ldu2, tn_tc::TC) == MFT_OK && make_tmap_bf16(&mv, vv, t, qq, ldv2, tn_tc::TC) == MFT_OK) {
-            static bool tc_configured = false;
+            static PerDeviceFlag tc_configured_on;           // function attributes are per device
+            bool& tc_configured = tc_configured_on.here();
             if (!tc_configured) {
                 if (int32_t s = check_cuda(cudaFuncSetAttribute(tn_tc::gemm_tn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tn_tc::SMEM_BYTES), "gemm_tn smem attr")) return s;
                 tc_configured = true;
