@@ -1,14 +1,14 @@
 // CTA-pair variant of the bf16 "NT" tcgen05 GEMM: two CTAs of a cluster (two SMs) cooperate on one
-// 256 x 256 output tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and HALF
-// of the B tile (128 of the 256 columns of the output), so the shared-memory operand traffic per SM
-// is 2/3 of the single-CTA kernel's (which is bound by it), while each SM's tensor memory holds the
-// accumulator rows of its own half of the tile.
+// 256 x 256 or 256 x 384 output tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and HALF
+// of the B tile, so the shared-memory operand traffic per SM is 2/3 of the single-CTA kernel's (which is bound by
+// it), while each SM's tensor memory holds the accumulator rows of its own half of the tile.  The main loop is bound by
+// how fast operands arrive from L2, so the tile shape is chosen for operand bytes per output column (PairCfg).
 //
-// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = tensor-memory allocation and - in the
-// leader CTA (cluster rank 0) only - the one MMA-issuing thread, warps 2..5 = epilogue for this CTA's
-// 128 rows.  Barriers: `full` and `tmem_empty` live in the leader (both CTAs arrive there, the peer
-// through the cluster shared-memory window); `empty` and `tmem_full` exist in both CTAs and are
-// signalled for both by one tcgen05.commit.  TMA loads are plain per-CTA loads (each CTA fetches its
+// Roles per CTA (320 threads): warp 0 = TMA producer, warp 1 = tensor-memory allocation and - in the
+// leader CTA (cluster rank 0) only - the one MMA-issuing thread, warps 2..9 = epilogue for this CTA's
+// 128 rows, two warps per lane quadrant of tensor memory.  Barriers: `full` and `tmem_empty` live in the leader (both
+// CTAs arrive there, the peer through the cluster shared-memory window); `empty` and `tmem_full` exist in both CTAs
+// and are signalled for both by one tcgen05.commit.  TMA loads are plain per-CTA loads (each CTA fetches its
 // own tiles; nothing is broadcast).  All waits are bounded, as in the single-CTA kernel.
 #include <cuda.h>
 
