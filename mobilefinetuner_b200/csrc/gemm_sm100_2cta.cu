@@ -399,20 +399,21 @@ int choose_splits(const TileShape& t, int64_t kb, double* cost_out) {
 // Tile width (256 or 384 columns) and number of K ranges of a call.  n_tiles_wide = 0: the call has no whole 384-column
 // tiles.  `staged`: bf16 output (the wide tile's epilogue is the staged one; otherwise its K loop must be at least
 // 64 blocks long).  `asked` = the caller's K ranges, 0 = choose.  MFT_GEMM_WIDE=0 keeps every call on 256-wide tiles.
-int plan_tiles(int64_t m, int64_t n_tiles, int64_t n_tiles_wide, int64_t kb, bool staged, bool can_split, int asked, int* splits_out) {
+int plan_tiles(int64_t m, int64_t n_tiles, int64_t n_tiles_wide, int64_t kb, bool staged, bool can_split, int asked, int* splits_out, bool ragged = false) {
     static const bool wide_allowed = [] { const char* e = std::getenv("MFT_GEMM_WIDE"); return !(e && e[0] == '0'); }();
     const TileShape t256{(m + 255) / 256, n_tiles, false, false}, t384{(m + 255) / 256, n_tiles_wide, true, staged};
     const bool wide_fits = wide_allowed && n_tiles_wide > 0 && m % 256 == 0;
     bool wide = false;
     int splits = 1;
+    const double margin = ragged ? 0.97 : 1.0;        // a ragged last tile computes columns that do not exist: ask for a clear gain
     if (!can_split || asked > 0) {
         splits = can_split ? asked : 1;
-        wide = wide_fits && (staged || kb / splits >= 64) && tile_cost(t384, kb, splits) < tile_cost(t256, kb, splits);
+        wide = wide_fits && (staged || kb / splits >= 64) && tile_cost(t384, kb, splits) < margin * tile_cost(t256, kb, splits);
     } else {
         double cost256 = 0, cost384 = 0;
         const int sp256 = choose_splits(t256, kb, &cost256);
         const int sp384 = wide_fits && (staged || kb >= 64) ? choose_splits(t384, kb, &cost384) : 0;
-        wide = sp384 > 0 && cost384 < cost256;
+        wide = sp384 > 0 && cost384 < margin * cost256;
         splits = wide ? sp384 : sp256;
     }
     *splits_out = splits;
@@ -426,7 +427,7 @@ int gemm_nt_pair_tile_cols(int64_t m, int64_t n, int64_t k, int64_t k2, bool d_i
     if (m < 256 || n < 192) return 0;
     const int64_t kb = (k + BK - 1) / BK + (k2 > 0 ? 1 : 0);
     int splits = 1;
-    return plan_tiles(m, (n + 255) / 256, n >= 384 ? (n + 383) / 384 : 0, kb, !d_is_f32, d_is_f32 && k2 == 0, 0, &splits);
+    return plan_tiles(m, (n + 255) / 256, n >= 384 ? (n + 383) / 384 : 0, kb, !d_is_f32, d_is_f32 && k2 == 0, 0, &splits, n % 384 != 0);
 }
 
 int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
@@ -452,7 +453,7 @@ int32_t gemm_nt_run_2cta(const GemmCall& c, cudaStream_t stream) {
     int splits = 1;
     int bn = 256;
     // a ragged last 384-column tile is computed whole (the rows of B past N arrive as zeros) and stored clipped
-    if (c.epi == EPI_STORE) bn = plan_tiles(c.m, (c.n + 255) / 256, c.n >= 384 ? (c.n + 383) / 384 : 0, kb, bf16_ok, can_split, (int)c.splits, &splits);
+    if (c.epi == EPI_STORE) bn = plan_tiles(c.m, (c.n + 255) / 256, c.n >= 384 ? (c.n + 383) / 384 : 0, kb, bf16_ok, can_split, (int)c.splits, &splits, c.n % 384 != 0);
     else if (c.epi == EPI_GLU_FWD) bn = plan_tiles(c.m, c.glu_inter / 128, c.glu_inter % 192 == 0 ? c.glu_inter / 192 : 0, kb, true, false, 0, &splits);
     const bool wide = bn > 256;
     CUtensorMap ma, mb, ma2, mb2, md, mx;
