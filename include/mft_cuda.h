@@ -233,6 +233,13 @@ int32_t mft_gemm_nt(const void* a_bf16, int64_t lda, const void* b_bf16, int64_t
  * tiles x k-blocks per tile) prefers the wider tile; f32 outputs take it only under at least 64 k-blocks per tile - or
  * 0 when another kernel takes the call.  Needs an initialised device (the SM count enters the plan). */
 int32_t mft_gemm_nt_tile_cols(int64_t m, int64_t n, int64_t k, int64_t k2, int32_t d_dtype, int32_t* tile_cols_host);
+/* Measurement aid: bytes per clock that one SM takes in from L2 through its TMA unit when nothing else uses its shared
+ * memory (one CTA per SM loads an L2-resident 64 MiB matrix into a ring of `stages` 32 KB stages that a second thread
+ * releases at once).  mode 0: two tensor boxes of 128 rows x 128 bytes per stage (what the GEMMs load); 1: two bulk
+ * copies of 16 KB; 2: one of each.  Results: bytes per clock of the slowest CTA, and TB/s over all `ctas`.  Allocates
+ * its own scratch and synchronises; not for use inside a step. */
+int32_t mft_probe_tma_delivery(int32_t mode, int32_t stages, int32_t ctas, int32_t iters, double* bytes_per_clock_per_sm_host,
+                               double* tb_per_s_host, mft_stream_t stream);
 /* Measurement aid: while enabled, every tensor-core GEMM launch (mft_gemm_nt and the GEMMs inside
  * the lm-head routines) is bracketed by CUDA events on its stream.  The report sums the
  * executed MACs*2 (including the LoRA k-block) and the device time over the launches recorded

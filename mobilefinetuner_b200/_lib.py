@@ -112,6 +112,7 @@ _SIGS = {
     "mft_gemm_nt_tile_cols": [i64, i64, i64, i64, i32, C.POINTER(i32)],
     "mft_glu_linear_fwd": [i32, vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, vp, i64, vp, i64, vp],
     "mft_glu_linear_bwd": [i32, vp, i64, vp, i64, i64, i64, i64, vp, i64, vp, i64, i64, vp, i64, vp, i64, vp],
+    "mft_probe_tma_delivery": [i32, i32, i32, i32, C.POINTER(C.c_double), C.POINTER(C.c_double), vp],
     "mft_profile_gemm": [i32],
     "mft_profile_gemm_report": [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(i64)],
     "mft_profile_gemm_report_epi": [i32, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(i64)],

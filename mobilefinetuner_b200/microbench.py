@@ -5,6 +5,7 @@
     python -m mobilefinetuner_b200.microbench attn --batch 8 --heads 4 --kv-heads 1 --seq 2048 --head-dim 256 [--window 512]
     python -m mobilefinetuner_b200.microbench tn --t 16384 --p 1152 --q 64
     python -m mobilefinetuner_b200.microbench ce --t 4096 --hidden 1152 --vocab 262144
+    python -m mobilefinetuner_b200.microbench tma                                          # L2 -> shared memory delivery per SM (no MMAs)
 
 Prints one JSON line per run with the achieved TFLOP/s or GB/s; the same command under a profiler
 captures just that kernel.
@@ -36,7 +37,7 @@ def _time(fn, iters, warm=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemm", "glu", "attn", "tn", "ce"])
+    ap.add_argument("kind", choices=["gemm", "glu", "attn", "tn", "ce", "tma"])
     ap.add_argument("--no-split", action="store_true", help="attn: one CTA per KV group in the dK/dV kernel")
     ap.add_argument("--m", type=int, default=16384); ap.add_argument("--n", type=int, default=13824); ap.add_argument("--k", type=int, default=1152)
     ap.add_argument("--k2", type=int, default=0); ap.add_argument("--f32", action="store_true")
@@ -49,6 +50,19 @@ def main():
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
     out = {"kind": a.kind}
+    if a.kind == "tma":
+        # one JSON line per (SMs pulling, load kind, stages in flight)
+        import ctypes as C
+        from . import _lib as L
+        L.init(torch.cuda.current_device())
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        names = {0: "two 128-row tensor boxes per stage", 1: "two 16 KB bulk copies per stage", 2: "one box and one bulk copy per stage"}
+        for ctas, mode, stages in [(sms, 0, 6), (sms, 1, 6), (sms, 2, 6), (sms // 2, 0, 6), (16, 0, 6), (sms, 0, 1), (sms, 0, 2), (sms, 0, 3), (sms, 0, 4)]:
+            bpc, tbs = C.c_double(), C.c_double()
+            L.call("mft_probe_tma_delivery", mode, stages, ctas, 4000, C.byref(bpc), C.byref(tbs), None)
+            print(json.dumps({"kind": "tma", "ctas": ctas, "loads": names[mode], "stages": stages, "bytes_per_clock_per_sm": round(bpc.value, 1),
+                              "tb_per_s": round(tbs.value, 2)}), flush=True)
+        return
     if a.kind == "gemm":
         A = torch.randn(a.m, a.k, device=dev, generator=g).to(BF)
         B = torch.randn(a.n, a.k, device=dev, generator=g).to(BF)
